@@ -1,0 +1,299 @@
+#!/usr/bin/env python
+"""Benchmark of the int8 inference hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this back end
+    python bench.py --impl reference --gpus N ...            # the reference's CPU path (oracle port)
+
+Workload: the reference's example CNN in QLinear int8 form (QuantizeLinear -> 2x[QLinearConv, ReLU,
+MaxPool] -> 2x QLinearMatMul -> DequantizeLinear) on seeded synthetic 1x28x28 inputs, batch 65536
+per GPU; a step is one pass of the plan over the batch.  `value` times the step with the batch
+already resident in HBM; `e2e` times the same call with pinned HOST buffers (H2D of the float
+inputs and D2H of the logits inside the timed region).  Prints one JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as ge  # noqa: E402
+
+BATCH_PER_GPU = 65536
+METRIC = "int8 images/sec (small CNN, QLinear int8, batch 65536 per GPU)"
+MACS_PER_IMAGE = 194688 + 2230272 + 819200 + 5120
+
+CLOCK_QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for line in self.lines:
+            f = [v.strip() for v in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=max(smax) if smax else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+def step_costs(graph):
+    """Algorithmic work of every graph node: MACs and bytes (each operand and result once)."""
+    itemsize = {0: 4, 1: 1, 2: 1, 3: 4}
+    out = {}
+    for i, n in enumerate(graph.nodes):
+        ts = [graph.tensors[t] for t in n["inputs"] if t >= 0] + [graph.tensors[t] for t in n["outputs"]]
+        nbytes = sum(int(np.prod(t["shape"])) * itemsize[t["dtype"]] for t in ts)
+        macs = 0
+        if n["op"] in ("QLinearConv", "Conv"):
+            w = graph.tensors[n["inputs"][1]]["shape"]; y = graph.tensors[n["outputs"][0]]["shape"]
+            macs = int(np.prod(y)) * w[1] * w[2] * w[3]
+        elif n["op"] in ("QLinearMatMul", "MatMul"):
+            a = graph.tensors[n["inputs"][0]]["shape"]; b = graph.tensors[n["inputs"][1]]["shape"]
+            macs = a[0] * a[1] * b[1]
+        out[i] = dict(op=n["op"], macs=macs, bytes=nbytes, out=graph.tensors[n["outputs"][0]]["name"])
+    return out
+
+
+def cpu_reference_rate(batch_hint, scales, budget_s=12.0):
+    """Times the CPU oracle (the reference's algorithm restated) on a bounded sample of the
+    workload with every host core (independent sample shards, one thread each)."""
+    zo = ge.load_oracle()
+    import graph_oracle
+    zb = ge.load_package()
+    from zant_b200 import models
+    cores = os.cpu_count() or 1
+
+    def run_shard(n, seed, box):
+        g = models.small_cnn_int8(n, act_scales=scales)
+        x = models.small_cnn_input(n, seed)
+        t0 = time.perf_counter()
+        graph_oracle.run(zo, g, x)
+        box.append(time.perf_counter() - t0)
+
+    probe = []
+    run_shard(4, 1, probe)
+    per_image = max(probe[0] / 4, 1e-6)
+    n = int(min(max(budget_s / per_image, 4), 2048))
+    boxes = [[] for _ in range(cores)]
+    threads = [threading.Thread(target=run_shard, args=(n, 10 + i, boxes[i])) for i in range(cores)]
+    t0 = time.perf_counter()
+    for t in threads: t.start()
+    for t in threads: t.join()
+    wall = time.perf_counter() - t0
+    return dict(value=n * cores / wall, unit="images/s", cores=cores, kind="port",
+                sample=f"{n} images per thread x {cores} threads of the same int8 CNN, oracle port of the reference's CPU algorithm "
+                       f"({wall:.1f} s wall); the reference (Zig) cannot be built here")
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    scales = dict(relu1=0.02, relu2=0.05, relu3=0.05, logits=0.1)
+    vals = []
+    for _ in range(max(args.warmup, 0)):
+        cpu_reference_rate(BATCH_PER_GPU, scales, budget_s=1.0)
+    res = None
+    for _ in range(max(args.steps, 1)):
+        res = cpu_reference_rate(BATCH_PER_GPU, scales, budget_s=4.0)
+        vals.append(res["value"])
+    v = float(np.mean(vals))
+    res["value"] = v
+    line = dict(impl="reference", metric=METRIC, value=v, unit="images/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                ms_per_step=None, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="int8", data="synthetic",
+                config=dict(workload="small CNN int8 (QLinear), batch 65536 per GPU; CPU arm times a bounded sample per step",
+                            batch_per_gpu=BATCH_PER_GPU), cpu_baseline=res,
+                e2e=dict(value=v, unit="images/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="zant_b200", choices=["zant_b200", "reference"])
+    ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU per step")
+    ap.add_argument("--no-fuse", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    zb = ge.load_package()
+    zb.lib()
+    from zant_b200 import models
+
+    ctx = zb.Context(local)
+    stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local))
+    batch = args.batch
+
+    # calibration on the GPU through the FP32 plan (configuration 1 at batch 256), then the int8 graph
+    scales = models.calibrate_on_gpu(ctx, models.small_cnn_fp32(256), models.small_cnn_input(256, models.DEFAULT_SEED + 1))
+    graph = models.small_cnn_int8(batch, act_scales=scales)
+    plan = zb.Plan(ctx, graph, fuse=not args.no_fuse)
+
+    begin, count = zb.shard_range(batch * world, world, rank)   # this rank's samples of the global batch
+    gen = torch.Generator(device="cpu").manual_seed(models.DEFAULT_SEED + 100 + rank)
+    x_host = torch.rand((batch, 1, 28, 28), generator=gen, dtype=torch.float32).pin_memory()
+    y_host = torch.empty((batch, 10), dtype=torch.float32).pin_memory()
+    x_dev = x_host.cuda(non_blocking=False)
+    y_dev = torch.empty((batch, 10), dtype=torch.float32, device="cuda")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, profile=False):
+        with torch.cuda.stream(stream):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            if profile:
+                plan.profile(True)
+            ctx.reset_launch_count()
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            barrier()
+            ms = e0.elapsed_time(e1)
+        launches = ctx.launch_count()
+        if world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, launches
+
+    resident = lambda: plan.run(x_dev, out=y_dev)        # noqa: E731
+    end_to_end = lambda: plan.run(x_host, out=y_host)    # noqa: E731
+
+    for _ in range(args.warmup):
+        resident()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms, launches = timed(resident, args.steps, profile=True)
+    step_ms, runs = plan.profile_read()
+    plan.profile(False)
+    clocks = sampler.stop() if sampler else None
+
+    for _ in range(2):
+        end_to_end()
+    ms_e2e, _ = timed(end_to_end, args.steps)
+
+    if rank == 0:
+        peaks = measured_peaks()
+        total_images = batch * world * args.steps
+        value = total_images / (ms / 1e3)
+        names = plan.step_names()
+        costs = step_costs(graph)
+        per_step = [m / max(runs, 1) for m in step_ms]
+        # dominant kernel = the step with the largest share of the timed region
+        top = int(np.argmax(per_step)) if per_step else 0
+        # map the step back to its node: unfused plans have one step per non-Reshape node
+        node_ids = [i for i, n in enumerate(graph.nodes) if n["op"] != "Reshape"]
+        shares = {f"{i}:{names[i]}": round(per_step[i] / max(sum(per_step), 1e-9), 4) for i in range(len(names))}
+        roof = None
+        if len(names) == len(node_ids):
+            c = costs[node_ids[top]]
+            int8_peak = 2.0 * peaks["bf16_tflops_sustained"]      # dense int8 = 2x dense bf16 on the same tensor pipes
+            intensity = 2.0 * c["macs"] / max(c["bytes"], 1)
+            ridge = int8_peak * 1e12 / (peaks["hbm_gbs"] * 1e9)
+            secs = per_step[top] / 1e3
+            if c["macs"] and intensity > ridge:
+                ach = 2.0 * c["macs"] / secs / 1e12
+                roof = dict(bound="tensor", achieved=ach, peak=int8_peak, unit="TFLOP/s", frac=ach / int8_peak)
+            else:
+                ach = c["bytes"] / secs / 1e9
+                roof = dict(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"])
+            roof.update(traffic=None, kernel=f"{names[top]} -> {c['out']}", launch_ms=per_step[top], peak_source=peaks["source"] +
+                        (" (int8 tensor peak taken as 2 x measured sustained bf16)" if roof["bound"] == "tensor" else ""),
+                        algorithmic_bytes=c["bytes"], macs=c["macs"])
+        else:
+            roof = dict(bound="hbm", achieved=None, peak=peaks["hbm_gbs"], unit="GB/s", frac=None, traffic=None,
+                        kernel="fused plan: see step_share", peak_source=peaks["source"])
+        cpu = None if args.skip_cpu else cpu_reference_rate(batch, scales)
+        line = dict(metric=METRIC, value=value, unit="images/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+                    ms_per_step=ms / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="int8",
+                    data="synthetic",
+                    config=dict(workload="small CNN int8 (QLinear form of the reference's example net), batch 65536 per GPU",
+                                batch_per_gpu=batch, global_batch=batch * world, fused=not args.no_fuse,
+                                l2="inputs larger than L2 (205 MB of float input per step)", calibration="256 seeded samples, FP32 plan on the GPU",
+                                macs_per_image=MACS_PER_IMAGE, parallelism=f"sample-sharded x{world}, no collective"),
+                    roofline=roof, step_share=shares, cpu_baseline=cpu,
+                    e2e=dict(value=total_images / (ms_e2e / 1e3), unit="images/s", h2d_bytes_per_step=batch * 784 * 4,
+                             d2h_bytes_per_step=batch * 10 * 4, ms_per_step=ms_e2e / args.steps),
+                    gpu_launches=int(launches) * world, clocks=clocks, arena_bytes=plan.arena_bytes)
+        print(json.dumps(line), flush=True)
+    plan.close()
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -448,8 +448,19 @@ int32_t zant_b200_plan_run(zant_plan* plan, const void* input, void* output);
 /* Bytes of the plan's arena and number of kernels one run launches. */
 size_t zant_b200_plan_arena_bytes(zant_plan* plan);
 int32_t zant_b200_plan_launches_per_run(zant_plan* plan);
+/* Number of launch steps of a finalized plan and the name of step i ("QLinearConv", ...). */
+int32_t zant_b200_plan_step_count(zant_plan* plan);
+const char* zant_b200_plan_step_name(zant_plan* plan, int32_t step);
+/* Per-step device timing: when enabled, every run records one CUDA event before each step and
+ * one after the last on the context's stream (no synchronisation is added).  _read drains the
+ * stream, adds the elapsed milliseconds of every recorded run to sum_ms[step] (step_count
+ * entries, zeroed by the caller), stores the number of runs in *runs and clears the record. */
+int32_t zant_b200_plan_profile(zant_plan* plan, int32_t enable);
+int32_t zant_b200_plan_profile_read(zant_plan* plan, float* sum_ms, int32_t* runs);
 /* Device pointer of a tensor's arena buffer (for tests that inspect intermediates). */
 void* zant_b200_plan_tensor_ptr(zant_plan* plan, int32_t id);
+/* Copies a tensor's current contents to `host_dst` (tensor-sized) after draining the stream. */
+int32_t zant_b200_plan_read_tensor(zant_plan* plan, int32_t id, void* host_dst);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,138 @@
+"""Whole-graph parity: the plan (the run-time form of a generated predict()) against the oracle
+executing the same graph node by node; then size-independent properties at the full batch."""
+import numpy as np
+import pytest
+
+import graph_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def models(zb):
+    from zant_b200 import models
+    return models
+
+
+@pytest.fixture(scope="module")
+def scales(zb, ctx, models):
+    fp32 = models.small_cnn_fp32(256)
+    return models.calibrate_on_gpu(ctx, fp32, models.small_cnn_input(256, models.DEFAULT_SEED + 1))
+
+
+@pytest.mark.parametrize("batch", [1, 5])
+@pytest.mark.parametrize("fuse", [False, True])
+def test_small_cnn_fp32_matches_oracle(zb, ctx, oracle, models, batch, fuse):
+    g = models.small_cnn_fp32(batch)
+    x = models.small_cnn_input(batch, 77)
+    want = graph_oracle.run(oracle, g, x)
+    plan = zb.Plan(ctx, g, fuse=fuse)
+    got = plan.run(x)
+    ref = want[g.output]
+    # FP32 contract: |gpu - ref| <= 1e-4 * max(|ref|, 1e-2 * max|ref|); the exact kernels are in fact bit-identical.
+    tol = 1e-4 * np.maximum(np.abs(ref), 1e-2 * np.abs(ref).max())
+    assert np.all(np.abs(got - ref) <= tol)
+    if not fuse:
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+        for name in ("conv1", "pool1", "conv2", "pool2", "fc1", "relu3"):
+            tid = g.id_of(name)
+            assert np.array_equal(plan.read_tensor(tid).view(np.uint32), want[tid].view(np.uint32)), name
+    plan.close()
+
+
+def test_calibration_agrees_with_oracle(zb, ctx, oracle, models, scales):
+    fp32 = models.small_cnn_fp32(16)
+    x = models.small_cnn_input(16, models.DEFAULT_SEED + 1)
+    cpu = graph_oracle.calibrate(oracle, fp32, x)
+    gpu = models.calibrate_on_gpu(ctx, fp32, x)
+    assert cpu == gpu
+    assert all(0 < v < 10 for v in scales.values())
+
+
+@pytest.mark.parametrize("batch", [1, 9])
+@pytest.mark.parametrize("fuse", [False, True])
+def test_small_cnn_int8_bit_exact(zb, ctx, oracle, models, scales, batch, fuse):
+    g = models.small_cnn_int8(batch, act_scales=scales)
+    x = models.small_cnn_input(batch, 99)
+    want = graph_oracle.run(oracle, g, x)
+    plan = zb.Plan(ctx, g, fuse=fuse)
+    got = plan.run(x)
+    assert np.array_equal(got.view(np.uint32), want[g.output].view(np.uint32))
+    if not fuse:
+        for name in ("xq", "conv1", "pool1", "conv2", "pool2", "fc1", "fc2"):
+            tid = g.id_of(name)
+            assert np.array_equal(plan.read_tensor(tid), want[tid]), name
+    # the quantized network is not degenerate: logits differ between samples and use many codes
+    assert len(np.unique(want[g.id_of("fc2")])) > 4
+    plan.close()
+
+
+def test_int8_close_to_fp32(zb, ctx, models, scales):
+    """Sanity of the quantisation itself: int8 logits track the FP32 logits."""
+    batch = 64
+    x = models.small_cnn_input(batch, 5)
+    pf = zb.Plan(ctx, models.small_cnn_fp32(batch), fuse=False)
+    pq = zb.Plan(ctx, models.small_cnn_int8(batch, act_scales=scales), fuse=True)
+    yf, yq = pf.run(x), pq.run(x)
+    pf.close(); pq.close()
+    assert np.abs(yf - yq).max() <= 0.15 * np.abs(yf).max()
+    assert (yf.argmax(1) == yq.argmax(1)).mean() > 0.8
+
+
+def test_full_batch_properties(zb, ctx, oracle, models, scales):
+    """Batch 4096: (1) fused and unfused plans agree bit for bit, (2) samples are independent —
+    any slice of the big batch equals a small-batch run of the same samples, which the oracle
+    checks on 4 of them, (3) sharding the batch over ranks reproduces the unsharded result."""
+    batch = 4096
+    x = models.small_cnn_input(batch, 1234)
+    g = models.small_cnn_int8(batch, act_scales=scales)
+    p0, p1 = zb.Plan(ctx, g, fuse=False), zb.Plan(ctx, g, fuse=True)
+    y0, y1 = p0.run(x), p1.run(x)
+    p0.close(); p1.close()
+    assert np.array_equal(y0, y1)
+    idx = [0, 1777, 4094, 4095]
+    gs = models.small_cnn_int8(len(idx), act_scales=scales)
+    want = graph_oracle.run(oracle, gs, x[idx])[gs.output]
+    assert np.array_equal(y1[idx], want)
+    world = 3
+    parts = []
+    for r in range(world):
+        b, c = zb.shard_range(batch, world, r)
+        ps = zb.Plan(ctx, models.small_cnn_int8(c, act_scales=scales), fuse=True)
+        parts.append(ps.run(x[b:b + c]))
+        ps.close()
+    assert np.array_equal(np.concatenate(parts), y1)
+
+
+def test_plan_accepts_device_buffers(zb, ctx, models, scales):
+    torch = pytest.importorskip("torch")
+    batch = 32
+    g = models.small_cnn_int8(batch, act_scales=scales)
+    x = models.small_cnn_input(batch, 8)
+    plan = zb.Plan(ctx, g, fuse=True)
+    want = plan.run(x)
+    xd = torch.from_numpy(x).cuda()
+    yd = torch.empty((batch, 10), dtype=torch.float32, device="cuda")
+    plan.run(xd, out=yd)
+    ctx.synchronize()
+    assert np.array_equal(yd.cpu().numpy(), want)
+    assert plan.launches_per_run > 0
+    plan.close()
+
+
+def test_plan_rejects_bad_graphs(zb, ctx, models):
+    g = models.small_cnn_fp32(2)
+    g.tensors[g.id_of("conv1")]["shape"] = [2, 32, 25, 26]
+    with pytest.raises(zb.ZantError) as e:
+        zb.Plan(ctx, g)
+    assert e.value.name == "InvalidDimensions"
+
+
+@pytest.mark.parametrize("name,batch", [("3a", 2), ("3b", 4), ("3c", 2), ("3d", 2)])
+def test_qconv_sweep_reduced_batch(zb, ctx, oracle, models, name, batch):
+    """Configuration 3 shapes at a batch the oracle finishes in seconds: bit-exact."""
+    c = models.qconv_case(name, batch=batch)
+    kw = dict(stride=c["stride"], pads=c["pads"], dilations=c["dilations"], group=c["group"])
+    got = ctx.qlinearconv(c["x"], c["x_scale"], 0, c["w"], c["w_scale"], None, c["y_scale"], 0, **kw)
+    want = oracle.qlinearconv(c["x"], c["x_scale"], 0, c["w"], c["w_scale"], None, c["y_scale"], 0, **kw)
+    assert np.array_equal(got, want)

@@ -1,0 +1,218 @@
+"""FP32 operators: CUDA (through the C ABI) against the CPU oracle on seeded random inputs.
+
+The back end's FP32 kernels keep the reference's order of operations (sequential k, separate
+multiply and add), so the comparison is bit-exact, which is stricter than the 1e-4 relative
+tolerance the float path is allowed.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def rnd(rng, shape):
+    return rng.standard_normal(shape).astype(np.float32)
+
+
+def same(a, b):
+    assert a.shape == b.shape, (a.shape, b.shape)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), f"max |d| = {np.abs(a - b).max()}"
+
+
+CONV_CASES = [
+    # N, C, H, W, M, KH, KW, stride, pads, dilations, auto_pad, bias
+    (1, 1, 28, 28, 32, 3, 3, (1, 1), (0, 0, 0, 0), (1, 1), "NOTSET", True),
+    (3, 32, 13, 13, 64, 3, 3, (1, 1), (0, 0, 0, 0), (1, 1), "NOTSET", True),
+    (2, 3, 17, 19, 5, 3, 3, (2, 2), (1, 1, 1, 1), (1, 1), "NOTSET", False),
+    (2, 4, 9, 11, 7, 2, 3, (1, 2), (0, 1, 2, 0), (2, 1), "NOTSET", True),
+    (1, 5, 10, 10, 70, 3, 3, (1,), None, None, "SAME_UPPER", True),
+    (1, 5, 11, 9, 3, 3, 2, (2,), None, None, "SAME_LOWER", False),
+    (2, 2, 8, 8, 4, 5, 5, (1, 1), None, (1,), "VALID", True),
+    (1, 3, 8, 8, 4, 1, 1, (1, 1), (1, 1, 1, 1), None, None, True),      # pads ignored without auto_pad
+    (2, 17, 6, 6, 130, 3, 3, (1, 1), (1, 1, 1, 1), (1, 1), "NOTSET", True),  # K and M not multiples of the tile
+    (1, 1, 5, 5, 1, 2, 2, (1,), None, (2,), None, True),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES, ids=[f"conv{i}" for i in range(len(CONV_CASES))])
+def test_conv_lean(ctx, oracle, case):
+    N, C, H, W, M, KH, KW, stride, pads, dil, ap, has_bias = case
+    rng = np.random.default_rng(100 + N * 7 + C)
+    x, w = rnd(rng, (N, C, H, W)), rnd(rng, (M, C, KH, KW))
+    b = rnd(rng, (M,)) if has_bias else None
+    if ap is None and pads is not None and any(pads):
+        # Quirk of the reference: the allocating wrapper sizes the output WITH the pads, the lean
+        # function ignores pads when auto_pad is null, so the call ends in InvalidDimensions.
+        with pytest.raises(oracle.OracleError) as eo:
+            oracle.Conv(x, w, b, stride, pads, dil, None, ap)
+        with pytest.raises(Exception) as ez:
+            ctx.Conv(x, w, b, stride, pads, dil, None, ap)
+        assert eo.value.name == ez.value.name == "InvalidDimensions"
+        pads = None
+    want = oracle.Conv(x, w, b, stride, pads, dil, None, ap)
+    got = ctx.conv_lean(x, w, want.shape, b, stride, pads, dil, None, ap)
+    same(got, want)
+
+
+def test_conv_zero_pad_taps_are_multiplied_like_the_reference(ctx, oracle):
+    # The reference multiplies the zero padding by the weight (0 * inf = NaN); skipping the tap would hide that.
+    x = np.ones((1, 1, 3, 3), np.float32)
+    w = np.full((1, 1, 3, 3), np.inf, np.float32)
+    want = oracle.Conv(x, w, None, (1,), (1, 1, 1, 1), None, None, "NOTSET")
+    got = ctx.conv_lean(x, w, want.shape, None, (1,), (1, 1, 1, 1), None, None, "NOTSET")
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 1, 1), (2, 2, 2), (7, 1600, 512), (3, 512, 10), (65, 33, 129), (128, 64, 64), (1, 300, 70)])
+def test_mat_mul(ctx, oracle, M, K, N):
+    rng = np.random.default_rng(M * 1000 + K + N)
+    a, b = rnd(rng, (M, K)), rnd(rng, (K, N))
+    same(ctx.mat_mul(a, b), oracle.mat_mul(a, b))
+
+
+def test_mat_mul_uses_last_two_dims_only(ctx, oracle):
+    rng = np.random.default_rng(3)
+    a, b = rnd(rng, (1, 1, 5, 6)), rnd(rng, (1, 1, 6, 4))
+    same(ctx.mat_mul(a, b), oracle.mat_mul(a, b))
+
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("cmode", ["none", "full", "row", "col", "scalar"])
+def test_gemm(ctx, oracle, ta, tb, cmode):
+    rng = np.random.default_rng(11 + ta * 2 + tb)
+    rows, K, cols = 37, 53, 29
+    a = rnd(rng, (1, 1, K, rows) if ta else (1, 1, rows, K))
+    b = rnd(rng, (1, 1, cols, K) if tb else (1, 1, K, cols))
+    c = {"none": None, "full": (1, 1, rows, cols), "row": (1, 1, 1, cols), "col": (1, 1, rows, 1), "scalar": (1, 1, 1, 1)}[cmode]
+    c = None if c is None else rnd(rng, c)
+    same(ctx.gemm(a, b, c, 1.5, -0.75, ta, tb), oracle.gemm(a, b, c, 1.5, -0.75, ta, tb))
+
+
+def test_gemm_classifier_shape(ctx, oracle):
+    rng = np.random.default_rng(12)
+    a, b, c = rnd(rng, (1, 1, 4, 1280)), rnd(rng, (1, 1, 1000, 1280)), rnd(rng, (1, 1, 1, 1000))
+    same(ctx.gemm(a, b, c, 1.0, 1.0, False, True), oracle.gemm(a, b, c, 1.0, 1.0, False, True))
+
+
+POOL_CASES = [
+    ((2, 32, 26, 26), (2, 2), (2, 2), (1, 1), (0, 0, 0, 0), "NOTSET", False),
+    ((1, 64, 11, 11), (2, 2), (2, 2), (1, 1), (0, 0, 0, 0), "NOTSET", False),
+    ((1, 3, 13, 13), (2, 2), (1, 1), (1, 1), (0, 0, 0, 0), "SAME_UPPER", False),
+    ((1, 3, 13, 13), (2, 2), (1, 1), (1, 1), (0, 0, 0, 0), "SAME_LOWER", False),
+    ((2, 2, 9, 7), (3, 2), (2, 1), (2, 2), (1, 0, 1, 1), "NOTSET", False),
+    ((1, 2, 7, 7), (3, 3), (2, 2), (1, 1), (0, 0, 0, 0), "NOTSET", True),
+    ((1, 1, 6, 6), (2, 2), (2, 2), (1, 1), (0, 0, 0, 0), "VALID", False),
+]
+
+
+@pytest.mark.parametrize("case", POOL_CASES, ids=[f"pool{i}" for i in range(len(POOL_CASES))])
+def test_onnx_maxpool(ctx, oracle, case):
+    xs, k, s, d, p, ap, ceil = case
+    x = rnd(np.random.default_rng(7), xs)
+    same(ctx.onnx_maxpool(x, k, s, d, p, ap, ceil), oracle.onnx_maxpool(x, k, s, d, p, ap, ceil))
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 4, 1023, 4096, 100003])
+def test_activations(ctx, oracle, n):
+    x = rnd(np.random.default_rng(n), (n,))
+    if n:
+        x[0] = 0.0
+    if n > 2:
+        x[1], x[2] = -0.0, np.float32(1e-38)
+    same(ctx.ReLU(x), oracle.ReLU(x))
+    same(ctx.leakyReLU(x, 0.1), oracle.leakyReLU(x, 0.1))
+    same(ctx.leakyReLU(x, 0.01), oracle.leakyReLU(x, 0.01))
+    same(ctx.clip(x, 0.0, 6.0), oracle.clip(x, 0.0, 6.0))
+
+
+def test_relu_does_not_need_a_zeroed_output(ctx):
+    # lean_ReLU writes only positive inputs (the generated code zeroes outputs first); this back end writes all.
+    x = np.array([-1.0, 2.0, -3.0, 4.0, 0.0], np.float32)
+    out = np.full(5, 7.0, np.float32)
+    ctx.ReLU(x, out=out)
+    assert out.tolist() == [0.0, 2.0, 0.0, 4.0, 0.0]
+
+
+ADD_CASES = [((2, 3, 4, 5), (2, 3, 4, 5)), ((6, 512), (512,)), ((2, 3, 4, 5), (5,)), ((2, 3, 4, 5), (1, 1, 4, 5)),
+             ((4, 5), (2, 3, 4, 5)), ((2, 8, 6, 6), (8, 1, 1)), ((2, 3, 1, 5), (1, 3, 4, 1)), ((24,), (2, 3, 4)), ((3, 1), (1, 4))]
+
+
+@pytest.mark.parametrize("sa,sb", ADD_CASES, ids=[f"add{i}" for i in range(len(ADD_CASES))])
+def test_sum_tensors(ctx, oracle, sa, sb):
+    rng = np.random.default_rng(len(sa) * 10 + len(sb))
+    a, b = rnd(rng, sa), rnd(rng, sb)
+    want, flag = oracle.sum_tensors(a, b, return_flag=True)
+    same(ctx.sum_tensors(a, b), want)
+    # flag != 0 marks shapes where the reference itself indexes outside the operand (documented deviation)
+    if (sa, sb) == ((2, 8, 6, 6), (8, 1, 1)):
+        assert flag == 1
+
+
+def test_sum_tensors_incompatible(zb, ctx):
+    with pytest.raises(zb.ZantError) as e:
+        ctx.sum_tensors(np.zeros((2, 3), np.float32), np.zeros((4,), np.float32))
+    assert e.value.name == "IncompatibleBroadcastShapes"
+
+
+@pytest.mark.parametrize("nt", [1, 2, 3, 8, 9, 17])
+def test_sum_tensor_list(ctx, oracle, nt):
+    rng = np.random.default_rng(nt)
+    ts = [rnd(rng, (5, 7, 3)) for _ in range(nt)]
+    same(ctx.sum_tensor_list(ts), oracle.sum_tensor_list(ts))
+
+
+CONCAT_CASES = [([(2, 128, 6, 6), (2, 256, 6, 6)], 1), ([(3, 4), (5, 4), (1, 4)], 0), ([(2, 3, 5), (2, 3, 2), (2, 3, 1)], -1),
+                ([(2, 3), (3,)], 0), ([(1, 7, 3, 3)], 1), ([(2, 3, 4, 5), (2, 3, 4, 5)], 2)]
+
+
+@pytest.mark.parametrize("shapes,axis", CONCAT_CASES, ids=[f"cat{i}" for i in range(len(CONCAT_CASES))])
+@pytest.mark.parametrize("dt", [np.float32, np.int8, np.uint8])
+def test_concatenate(ctx, oracle, shapes, axis, dt):
+    rng = np.random.default_rng(9)
+    ts = [(rng.standard_normal(s) * 50).astype(dt) for s in shapes]
+    got, want = ctx.concatenate(ts, axis), oracle.concatenate(ts, axis)
+    assert got.shape == want.shape and np.array_equal(got, want)
+
+
+RESIZE_CASES = [((2, 128, 13, 13), [1, 1, 2, 2], None, "half_pixel"), ((1, 3, 5, 7), [1, 1, 2, 2], None, "asymmetric"),
+                ((1, 2, 4, 4), [1, 1, 1.5, 2.5], None, "half_pixel"), ((1, 2, 6, 6), None, [1, 2, 9, 4], "align_corners"),
+                ((4,), [2.0], None, "half_pixel"), ((3, 5), None, [7, 2], "asymmetric")]
+
+
+@pytest.mark.parametrize("xs,scales,sizes,cm", RESIZE_CASES, ids=[f"rs{i}" for i in range(len(RESIZE_CASES))])
+@pytest.mark.parametrize("dt", [np.float32, np.uint8])
+def test_resize_nearest(ctx, oracle, xs, scales, sizes, cm, dt):
+    x = (np.random.default_rng(4).standard_normal(xs) * 40).astype(dt)
+    got, want = ctx.resize(x, "nearest", scales, sizes, cm), oracle.resize(x, "nearest", scales, sizes, cm)
+    assert got.shape == want.shape and np.array_equal(got, want)
+
+
+REDUCE_CASES = [((2, 1280, 7, 7), [2, 3], True), ((2, 3, 4, 5), [1], False), ((2, 3, 4, 5), [0, 2], True), ((2, 3, 4, 5), [-1], False),
+                ((2, 3, 4, 5), [3, 1], True), ((6, 5), None, True), ((2, 3, 4), [0, 1, 2], False)]
+
+
+@pytest.mark.parametrize("xs,axes,keep", REDUCE_CASES, ids=[f"rm{i}" for i in range(len(REDUCE_CASES))])
+def test_reduce_mean(ctx, oracle, xs, axes, keep):
+    x = rnd(np.random.default_rng(8), xs)
+    same(ctx.reduce_mean(x, axes, keep, False), oracle.reduce_mean(x, axes, keep, False))
+
+
+def test_reduce_mean_noop(ctx, oracle):
+    x = rnd(np.random.default_rng(8), (3, 4))
+    same(ctx.reduce_mean(x, None, True, True), x)
+
+
+def test_reshape(ctx, oracle):
+    x = rnd(np.random.default_rng(2), (4, 64, 5, 5))
+    got = ctx.reshape(x, [0, "SIZE_MAX"])
+    assert got.shape == (4, 1600) and np.array_equal(got, x.reshape(4, 1600))
+
+
+def test_device_pointers_are_used_in_place(ctx, oracle):
+    torch = pytest.importorskip("torch")
+    x = rnd(np.random.default_rng(21), (5, 1000))
+    xd = torch.from_numpy(x).cuda()
+    yd = torch.empty_like(xd)
+    ctx.ReLU(xd, out=yd)
+    ctx.synchronize()
+    same(yd.cpu().numpy(), oracle.ReLU(x))

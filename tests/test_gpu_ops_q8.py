@@ -1,0 +1,130 @@
+"""Quantized operators: CUDA against the pinned int8 definitions of the oracle, bit for bit.
+
+The reference tree has no quantized operators, so these definitions are the contract; the
+oracle itself is pinned by hand-computed vectors in tests/test_oracle_quant.py.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+I8, U8, I32 = 1, 2, 3
+NP = {I8: np.int8, U8: np.uint8}
+
+
+def q(rng, shape, dt):
+    return rng.integers(0, 256, shape, dtype=np.uint8) if dt == U8 else rng.integers(-128, 128, shape, dtype=np.int8)
+
+
+@pytest.mark.parametrize("n", [0, 1, 5, 784, 4099])
+@pytest.mark.parametrize("dt,scale,zp", [(U8, 1 / 255, 0), (I8, 0.02, 0), (I8, 0.013, -7), (U8, 0.031, 128)])
+def test_quantize_dequantize(ctx, oracle, n, dt, scale, zp):
+    rng = np.random.default_rng(n)
+    x = (rng.random(n, dtype=np.float32) * 12 - 4).astype(np.float32)
+    if n > 4:
+        x[:5] = [0.5 * scale, 1.5 * scale, 2.5 * scale, -0.5 * scale, 1e30]   # ties and saturation
+    got, want = ctx.quantize_linear(x, scale, zp, dt), oracle.quantize_linear(x, scale, zp, dt)
+    assert np.array_equal(got, want)
+    back_g, back_o = ctx.dequantize_linear(want, scale, zp), oracle.dequantize_linear(want, scale, zp)
+    assert np.array_equal(back_g.view(np.uint32), back_o.view(np.uint32))
+
+
+def test_dequantize_int32(ctx, oracle):
+    acc = np.random.default_rng(1).integers(-2**31, 2**31 - 1, 1000, dtype=np.int64).astype(np.int32)
+    a, b = ctx.dequantize_linear(acc, 0.0004, 0), oracle.dequantize_linear(acc, 0.0004, 0)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+QCONV = [
+    # N C H W M k stride pads dil group xdt ydt xzp yzp per_channel bias act
+    (2, 1, 28, 28, 32, 3, (1, 1), (0, 0, 0, 0), (1, 1), 1, U8, I8, 0, 0, True, True, "relu"),
+    (2, 32, 13, 13, 64, 3, (1, 1), (0, 0, 0, 0), (1, 1), 1, I8, I8, 0, 0, True, True, "relu"),
+    (1, 16, 9, 9, 24, 3, (1, 1), (1, 1, 1, 1), (1, 1), 1, I8, I8, 0, 0, False, False, None),
+    (2, 8, 10, 7, 12, 3, (2, 2), (1, 1, 1, 1), (1, 1), 1, U8, U8, 128, 3, True, True, "relu6"),
+    (1, 6, 8, 8, 9, 1, (1, 1), (0, 0, 0, 0), (1, 1), 3, I8, I8, -3, 5, True, True, None),
+    (2, 16, 11, 11, 16, 3, (1, 1), (1, 1, 1, 1), (1, 1), 16, I8, I8, 0, 0, True, True, "relu6"),   # depthwise
+    (1, 16, 12, 12, 16, 3, (2, 2), (0, 1, 1, 0), (1, 1), 16, I8, U8, 2, 10, False, False, "relu"),  # depthwise s2
+    (1, 4, 9, 9, 5, 2, (1, 1), (0, 0, 0, 0), (2, 2), 1, I8, I8, 0, 0, True, False, None),
+]
+
+
+@pytest.mark.parametrize("case", QCONV, ids=[f"qconv{i}" for i in range(len(QCONV))])
+def test_qlinearconv(ctx, oracle, case):
+    N, C, H, W, M, k, stride, pads, dil, group, xdt, ydt, xzp, yzp, per_ch, has_bias, act = case
+    rng = np.random.default_rng(N + C * 3 + M)
+    x = q(rng, (N, C, H, W), xdt)
+    w = rng.integers(-127, 128, (M, C // group, k, k), dtype=np.int8)
+    ws = (rng.random(M if per_ch else 1, dtype=np.float32) * 0.02 + 0.001).astype(np.float32)
+    wz = rng.integers(-3, 4, M if per_ch else 1).astype(np.int32) if xzp else None
+    bias = rng.integers(-2000, 2000, M).astype(np.int32) if has_bias else None
+    y_scale = 0.02 * np.sqrt(C // group * k * k)
+    kw = dict(bias=bias, y_dtype=ydt, stride=stride, pads=pads, dilations=dil, group=group, activation=act)
+    got = ctx.qlinearconv(x, 0.02, xzp, w, ws, wz, y_scale, yzp, **kw)
+    want = oracle.qlinearconv(x, 0.02, xzp, w, ws, wz, y_scale, yzp, **kw)
+    assert got.shape == want.shape and np.array_equal(got, want)
+    assert len(np.unique(want)) > 8   # the case is not saturated into triviality
+
+
+@pytest.mark.parametrize("auto_pad", ["SAME_UPPER", "SAME_LOWER", "VALID"])
+def test_qlinearconv_auto_pad(ctx, oracle, auto_pad):
+    rng = np.random.default_rng(3)
+    x = q(rng, (1, 4, 9, 10), I8)
+    w = rng.integers(-127, 128, (6, 4, 3, 3), dtype=np.int8)
+    kw = dict(stride=(2, 2), pads=(0, 0, 0, 0), auto_pad=auto_pad)
+    got = ctx.qlinearconv(x, 0.02, 0, w, [0.02], None, 0.3, 0, **kw)
+    want = oracle.qlinearconv(x, 0.02, 0, w, [0.02], None, 0.3, 0, **kw)
+    assert got.shape == want.shape and np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 1, 1), (3, 1600, 512), (5, 512, 10), (33, 70, 129), (128, 128, 128), (2, 17, 3)])
+@pytest.mark.parametrize("adt,ydt,azp,yzp,act", [(I8, I8, 0, 0, "relu"), (U8, U8, 128, 7, None), (I8, I32, 0, 0, None)])
+def test_qlinearmatmul(ctx, oracle, M, K, N, adt, ydt, azp, yzp, act):
+    rng = np.random.default_rng(M + K + N)
+    a = q(rng, (M, K), adt)
+    b = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    bs = (rng.random(N, dtype=np.float32) * 0.01 + 0.001).astype(np.float32)
+    bz = rng.integers(-2, 3, N).astype(np.int32) if azp else None
+    bias = rng.integers(-500, 500, N).astype(np.int32)
+    ys = 0.02 * np.sqrt(K)
+    got = ctx.qlinearmatmul(a, 0.02, azp, b, bs, bz, ys, yzp, bias, ydt, act)
+    want = oracle.qlinearmatmul(a, 0.02, azp, b, bs, bz, ys, yzp, bias, ydt, act)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("dt,act", [(I8, None), (U8, "relu"), (I8, "relu6")])
+def test_qlinearadd(ctx, oracle, dt, act):
+    rng = np.random.default_rng(17)
+    a, b = q(rng, (3, 24, 7, 7), dt), q(rng, (3, 24, 7, 7), dt)
+    zp = 0 if dt == I8 else 120
+    got = ctx.qlinearadd(a, 0.031, zp, b, 0.017, zp - 3 if dt == U8 else -4, 0.045, zp, act)
+    want = oracle.qlinearadd(a, 0.031, zp, b, 0.017, zp - 3 if dt == U8 else -4, 0.045, zp, act)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("dt", [I8, U8])
+@pytest.mark.parametrize("hw", [(7, 7), (1, 1), (5, 13)])
+def test_qlinear_global_avgpool(ctx, oracle, dt, hw):
+    x = q(np.random.default_rng(5), (3, 40) + hw, dt)
+    got = ctx.qlinear_global_avgpool(x, 0.05, 3, 0.02, -1 if dt == I8 else 9)
+    want = oracle.qlinear_global_avgpool(x, 0.05, 3, 0.02, -1 if dt == I8 else 9)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("dt", [I8, U8])
+def test_maxpool_q8(ctx, oracle, dt):
+    x = q(np.random.default_rng(6), (2, 16, 13, 13), dt)
+    for args in (((2, 2), (2, 2), (1, 1), (0, 0, 0, 0), "NOTSET"), ((2, 2), (1, 1), (1, 1), (0, 0, 0, 0), "SAME_UPPER"),
+                 ((3, 3), (2, 2), (1, 1), (1, 1, 1, 1), "NOTSET")):
+        assert np.array_equal(ctx.onnx_maxpool(x, *args), oracle.onnx_maxpool(x, *args))
+
+
+@pytest.mark.parametrize("dt", [I8, U8])
+@pytest.mark.parametrize("n", [1, 15, 16, 4097])
+def test_leaky_relu_lut(ctx, oracle, dt, n):
+    lut = oracle.build_leaky_lut(dt, 0.05, 3 if dt == U8 else 0, 0.1, 0.04, 5 if dt == U8 else 0)
+    x = q(np.random.default_rng(n), (n,), dt)
+    got, want = ctx.lut_q8(x, lut), oracle.lut_q8(x, lut)
+    assert np.array_equal(got, want)
+    # the table equals dequantise -> LeakyReLU -> quantise computed element by element
+    zi, zo = (3, 5) if dt == U8 else (0, 0)
+    ref = oracle.quantize_linear(oracle.leakyReLU(oracle.dequantize_linear(x, 0.05, zi), 0.1), 0.04, zo, dt)
+    assert np.array_equal(want, ref)

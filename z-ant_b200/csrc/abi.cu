@@ -1,0 +1,527 @@
+// extern "C" entry points declared in include/zant_b200.h: argument checks (host), staging of
+// host buffers, kernel launches.  No entry point has a CPU implementation: without a context
+// (i.e. without a usable GPU) every compute call returns ZANT_E_CUDA_UNAVAILABLE after its
+// arguments have been validated.
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/zant_b200.h"
+#include "context.cuh"
+#include "geometry.hpp"
+#include "ops.cuh"
+#include "status.hpp"
+
+using namespace zb;
+
+#define ZB_NEED(ptr, what) \
+    do { if ((ptr) == nullptr) return fail(ZANT_E_NULL_POINTER, "%s is NULL", what); } while (0)
+
+#define ZB_NEED_CTX(ctx)                                                                                     \
+    do {                                                                                                     \
+        if ((ctx) == nullptr) return fail(ZANT_E_CUDA_UNAVAILABLE, "no context (zant_b200_ctx_create failed or was not called); there is no CPU fallback"); \
+        ZB_CUDA(cudaSetDevice((ctx)->device));                                                               \
+    } while (0)
+
+#define ZB_TRY(expr) do { int32_t _s = (expr); if (_s != ZANT_OK) return _s; } while (0)
+
+extern "C" {
+
+// ------------------------------------------------------------------------------------ library / context
+const char* zant_b200_version(void) { return "zant-b200 0.1 (sm_100a)"; }
+const char* zant_b200_status_name(int32_t status) { return status_name(status); }
+const char* zant_b200_last_error(void) { return last_error_ref().c_str(); }
+void zant_b200_set_log(void (*fn)(char*)) { log_fn_ref() = fn; }
+
+int32_t zant_b200_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+int32_t zant_b200_ctx_create(int32_t device, size_t arena_bytes, zant_ctx** out) {
+    ZB_NEED(out, "out");
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        cudaGetLastError();
+        return fail(ZANT_E_CUDA_UNAVAILABLE, "no CUDA device (%s)", e != cudaSuccess ? cudaGetErrorString(e) : "count is 0");
+    }
+    if (device < 0 || device >= n) return fail(ZANT_E_INVALID_INPUT, "device %d of %d", device, n);
+    ZB_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    ZB_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) return fail(ZANT_E_CUDA_UNAVAILABLE, "device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
+    zant_ctx* c = new zant_ctx();
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { delete c; return fail(ZANT_E_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
+    const size_t want = arena_bytes ? arena_bytes : (size_t)256 << 20;
+    e = cudaMalloc((void**)&c->arena, want);
+    if (e != cudaSuccess) { cudaStreamDestroy(c->stream); delete c; return fail(ZANT_E_CUDA, "cudaMalloc(%zu): %s", want, cudaGetErrorString(e)); }
+    c->arena_bytes = want;
+    e = cudaMalloc((void**)&c->status_word, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(c->status_word, 0, sizeof(int));
+    if (e != cudaSuccess) { cudaFree(c->arena); cudaStreamDestroy(c->stream); delete c; return fail(ZANT_E_CUDA, "status word: %s", cudaGetErrorString(e)); }
+    *out = c;
+    log_line("zant_b200 context on device %d (%s, %d SMs)", device, prop.name, prop.multiProcessorCount);
+    return ZANT_OK;
+}
+
+int32_t zant_b200_ctx_destroy(zant_ctx* ctx) {
+    if (!ctx) return ZANT_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->arena) cudaFree(ctx->arena);
+    if (ctx->status_word) cudaFree(ctx->status_word);
+    if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return ZANT_OK;
+}
+
+int32_t zant_b200_ctx_set_stream(zant_ctx* ctx, void* cuda_stream) {
+    ZB_NEED_CTX(ctx);
+    ZB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->own_stream && ctx->stream) ZB_CUDA(cudaStreamDestroy(ctx->stream));
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    ctx->own_stream = false;
+    return ZANT_OK;
+}
+
+void* zant_b200_ctx_stream(zant_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int32_t zant_b200_ctx_synchronize(zant_ctx* ctx) {
+    ZB_NEED_CTX(ctx);
+    ZB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return ZANT_OK;
+}
+
+uint64_t zant_b200_ctx_launch_count(zant_ctx* ctx) { return ctx ? ctx->launches : 0; }
+void zant_b200_ctx_reset_launch_count(zant_ctx* ctx) { if (ctx) ctx->launches = 0; }
+
+// ------------------------------------------------------------------------------------ shape helpers
+int32_t zant_b200_conv_output_shape(const size_t* x_shape, size_t x_rank, const size_t* w_shape, size_t w_rank,
+                                    const size_t* stride, size_t n_stride, const size_t* pads, size_t n_pads,
+                                    const size_t* dilations, size_t n_dil, const char* auto_pad, size_t auto_pad_len,
+                                    size_t out_shape[4]) {
+    ZB_NEED(x_shape, "x_shape"); ZB_NEED(w_shape, "w_shape"); ZB_NEED(out_shape, "out_shape");
+    return conv_output_shape_ref(x_shape, x_rank, w_shape, w_rank, stride, n_stride, pads, n_pads, dilations, n_dil,
+                                 auto_pad, auto_pad_len, out_shape);
+}
+
+int32_t zant_b200_pooling_output_shape(const size_t* x_shape, size_t x_rank, const size_t kernel[2], const size_t stride[2],
+                                       size_t out_shape[4]) {
+    ZB_NEED(x_shape, "x_shape"); ZB_NEED(kernel, "kernel"); ZB_NEED(stride, "stride"); ZB_NEED(out_shape, "out_shape");
+    return pooling_output_shape(x_shape, x_rank, kernel, stride, out_shape);
+}
+
+int32_t zant_b200_maxpool_output_shape(const size_t* x_shape, size_t x_rank, const size_t* kernel_shape, const size_t* strides,
+                                       const size_t* dilations, const size_t* pads, int32_t auto_pad, int32_t ceil_mode,
+                                       size_t out_shape[4]) {
+    ZB_NEED(x_shape, "x_shape"); ZB_NEED(out_shape, "out_shape");
+    return maxpool_output_shape(x_shape, x_rank, kernel_shape, strides, dilations, pads, auto_pad, ceil_mode, out_shape);
+}
+
+int32_t zant_b200_resize_output_shape(const size_t* x_shape, size_t rank, const float* scales, size_t n_scales,
+                                      const size_t* sizes, size_t n_sizes, size_t* out_shape) {
+    ZB_NEED(x_shape, "x_shape"); ZB_NEED(out_shape, "out_shape");
+    return resize_output_shape(x_shape, rank, scales, n_scales, sizes, n_sizes, out_shape);
+}
+
+int32_t zant_b200_concat_output_shape(const size_t* const* shapes, const size_t* ranks, size_t n_tensors, int64_t axis,
+                                      size_t* out_shape, size_t* out_rank) {
+    ZB_NEED(out_shape, "out_shape"); ZB_NEED(out_rank, "out_rank");
+    if (n_tensors) { ZB_NEED(shapes, "shapes"); ZB_NEED(ranks, "ranks"); }
+    ConcatGeom g;
+    size_t tmp[8];
+    ZB_TRY(concat_resolve(shapes, ranks, n_tensors, axis, tmp, g));
+    for (size_t d = 0; d < g.rank; ++d) out_shape[d] = tmp[d];
+    *out_rank = g.rank;
+    return ZANT_OK;
+}
+
+int32_t zant_b200_get_concatenate_output_shape(const size_t* const* shapes, const size_t* ranks, size_t n_tensors,
+                                               int64_t axis, size_t* out_shape) {
+    ZB_NEED(out_shape, "out_shape");
+    if (n_tensors) { ZB_NEED(shapes, "shapes"); ZB_NEED(ranks, "ranks"); }
+    return concat_output_shape_strict(shapes, ranks, n_tensors, axis, out_shape);
+}
+
+int32_t zant_b200_shard_range(size_t total, size_t world, size_t rank, size_t* begin, size_t* count) {
+    ZB_NEED(begin, "begin"); ZB_NEED(count, "count");
+    return shard_range(total, world, rank, begin, count);
+}
+
+// ------------------------------------------------------------------------------------ fp32 operators
+int32_t zant_b200_conv_f32(zant_ctx* ctx, const float* x, const size_t* x_shape, size_t x_rank,
+                           const float* w, const size_t* w_shape, size_t w_rank, const float* bias, size_t bias_len,
+                           float* y, const size_t* y_shape, size_t y_rank,
+                           const size_t* stride, size_t n_stride, const size_t* pads, size_t n_pads,
+                           const size_t* dilations, size_t n_dil, size_t group, const char* auto_pad, size_t auto_pad_len) {
+    ZB_NEED(x, "x"); ZB_NEED(w, "w"); ZB_NEED(y, "y"); ZB_NEED(x_shape, "x_shape"); ZB_NEED(w_shape, "w_shape"); ZB_NEED(y_shape, "y_shape");
+    ConvGeom g;
+    ZB_TRY(conv_resolve_ref(x_shape, x_rank, w_shape, w_rank, y_shape, y_rank, stride, n_stride, pads, n_pads,
+                            dilations, n_dil, group, auto_pad, auto_pad_len, g));
+    if (bias && bias_len != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "bias holds %zu values for %d filters", bias_len, g.M);
+    ZB_NEED_CTX(ctx);
+    log_line("Running Conv [%d,%d,%d,%d] * [%d,%d,%d,%d]", g.N, g.C, g.H, g.W, g.M, g.Cg, g.KH, g.KW);
+    Stager s(ctx);
+    const int ix = s.in(x, numel(x_shape, 4) * 4), iw = s.in(w, numel(w_shape, 4) * 4);
+    const int ib = s.in(bias, (size_t)g.M * 4), iy = s.out(y, numel(y_shape, 4) * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_conv_f32(ctx, g, s.ptr<float>(ix), s.ptr<float>(iw), s.ptr<float>(ib), s.ptr<float>(iy)));
+    return s.finish();
+}
+
+int32_t zant_b200_mat_mul_f32(zant_ctx* ctx, const float* a, const size_t* a_shape, size_t a_rank,
+                              const float* b, const size_t* b_shape, size_t b_rank,
+                              float* y, const size_t* y_shape, size_t y_rank) {
+    ZB_NEED(a_shape, "a_shape"); ZB_NEED(b_shape, "b_shape"); ZB_NEED(y_shape, "y_shape");
+    MatGeom g;
+    ZB_TRY(matmul_check(a_shape, a_rank, b_shape, b_rank, y_shape, y_rank, g));
+    ZB_NEED(a, "a"); ZB_NEED(b, "b"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ia = s.in(a, g.M * g.K * 4), ib = s.in(b, g.K * g.N * 4), iy = s.out(y, g.M * g.N * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_matmul_f32(ctx, g, s.ptr<float>(ia), s.ptr<float>(ib), s.ptr<float>(iy)));
+    return s.finish();
+}
+
+int32_t zant_b200_gemm_f32(zant_ctx* ctx, const float* a, const size_t* a_shape, size_t a_rank,
+                           const float* b, const size_t* b_shape, size_t b_rank,
+                           const float* c, const size_t* c_shape, size_t c_rank,
+                           float alpha, float beta, int32_t trans_a, int32_t trans_b,
+                           float* y, const size_t* y_shape, size_t y_rank) {
+    ZB_NEED(a_shape, "a_shape"); ZB_NEED(b_shape, "b_shape");
+    GemmGeom g;
+    size_t auto_y[4];
+    // the checks that do not involve the output run first, as in gemm() (op_gemm.zig:22-61)
+    if (a_rank == 4 && b_rank == 4 && !y_shape) return fail(ZANT_E_NULL_POINTER, "y_shape is NULL");
+    if (a_rank != 4 || b_rank != 4) { auto_y[0] = auto_y[1] = auto_y[2] = auto_y[3] = 0; y_shape = auto_y; y_rank = 4; }
+    if (c && !c_shape) return fail(ZANT_E_NULL_POINTER, "c_shape is NULL");
+    ZB_TRY(gemm_check(a_shape, a_rank, b_shape, b_rank, c_shape, c_rank, c != nullptr, trans_a != 0, trans_b != 0, beta,
+                      y_shape, y_rank, g));
+    ZB_NEED(a, "a"); ZB_NEED(b, "b"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ia = s.in(a, numel(a_shape, 4) * 4), ib = s.in(b, numel(b_shape, 4) * 4);
+    const int ic = s.in(c, c ? numel(c_shape, 4) * 4 : 0), iy = s.out(y, numel(y_shape, 4) * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_gemm_f32(ctx, g, s.ptr<float>(ia), s.ptr<float>(ib), s.ptr<float>(ic), alpha, beta, trans_a != 0, trans_b != 0, s.ptr<float>(iy)));
+    return s.finish();
+}
+
+int32_t zant_b200_maxpool_f32(zant_ctx* ctx, const float* x, const size_t* x_shape, size_t x_rank,
+                              float* y, const size_t* y_shape, size_t y_rank,
+                              const size_t* kernel_shape, size_t n_kernel, const size_t* strides, size_t n_strides,
+                              const size_t* dilations, size_t n_dil, const size_t* pads, size_t n_pads, int32_t auto_pad) {
+    ZB_NEED(x_shape, "x_shape"); ZB_NEED(y_shape, "y_shape");
+    PoolGeom g;
+    ZB_TRY(pool_resolve(x_shape, x_rank, y_shape, y_rank, kernel_shape, n_kernel, strides, n_strides, dilations, n_dil, pads, n_pads, auto_pad, g));
+    ZB_NEED(x, "x"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ix = s.in(x, numel(x_shape, 4) * 4), iy = s.out(y, numel(y_shape, 4) * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_maxpool<float>(ctx, g, s.ptr<float>(ix), s.ptr<float>(iy)));
+    return s.finish();
+}
+
+}  // extern "C"
+
+template <typename F>
+static int32_t unary_entry(zant_ctx* ctx, const float* x, float* y, size_t n, F f, const char* name) {
+    if (n) { ZB_NEED(x, "x"); ZB_NEED(y, "y"); }
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ix = s.in(x, n * 4), iy = s.out(y, n * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_unary_f32(ctx, s.ptr<float>(ix), s.ptr<float>(iy), n, f, name));
+    return s.finish();
+}
+
+extern "C" {
+
+int32_t zant_b200_relu_f32(zant_ctx* ctx, const float* x, float* y, size_t n) { return unary_entry(ctx, x, y, n, ReluOp{}, "relu_f32"); }
+int32_t zant_b200_leaky_relu_f32(zant_ctx* ctx, const float* x, float slope, float* y, size_t n) { return unary_entry(ctx, x, y, n, LeakyOp{slope}, "leaky_relu_f32"); }
+int32_t zant_b200_clip_f32(zant_ctx* ctx, const float* x, float lo, float hi, float* y, size_t n) { return unary_entry(ctx, x, y, n, ClipOp{lo, hi}, "clip_f32"); }
+
+int32_t zant_b200_sum_tensors_f32(zant_ctx* ctx, const float* a, const size_t* a_shape, size_t a_rank,
+                                  const float* b, const size_t* b_shape, size_t b_rank,
+                                  float* y, const size_t* y_shape, size_t y_rank) {
+    ZB_NEED(a_shape, "a_shape"); ZB_NEED(b_shape, "b_shape"); ZB_NEED(y_shape, "y_shape");
+    BcastGeom g;
+    ZB_TRY(bcast_resolve(a_shape, a_rank, b_shape, b_rank, y_shape, y_rank, g));
+    ZB_NEED(a, "a"); ZB_NEED(b, "b"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ia = s.in(a, numel(a_shape, a_rank) * 4), ib = s.in(b, numel(b_shape, b_rank) * 4), iy = s.out(y, g.total * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_add_f32(ctx, g, s.ptr<float>(ia), s.ptr<float>(ib), s.ptr<float>(iy)));
+    return s.finish();
+}
+
+int32_t zant_b200_sum_tensor_list_f32(zant_ctx* ctx, const float* const* tensors, size_t n_tensors, float* y, size_t n) {
+    if (n_tensors == 0) return fail(ZANT_E_EMPTY_TENSOR_LIST, "empty tensor list");
+    ZB_NEED(tensors, "tensors"); ZB_NEED(y, "y");
+    for (size_t t = 0; t < n_tensors; ++t) ZB_NEED(tensors[t], "tensors[i]");
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    std::vector<int> idx(n_tensors);
+    for (size_t t = 0; t < n_tensors; ++t) idx[t] = s.in(tensors[t], n * 4);
+    const int iy = s.out(y, n * 4);
+    ZB_TRY(s.commit());
+    std::vector<const float*> dev(n_tensors);
+    for (size_t t = 0; t < n_tensors; ++t) dev[t] = s.ptr<float>(idx[t]);
+    ZB_TRY(run_sum_list_f32(ctx, dev.data(), n_tensors, s.ptr<float>(iy), n));
+    return s.finish();
+}
+
+int32_t zant_b200_concatenate(zant_ctx* ctx, int32_t dtype, const void* const* tensors, const size_t* const* shapes,
+                              const size_t* ranks, size_t n_tensors, int64_t axis, void* y, const size_t* y_shape, size_t y_rank) {
+    if (!dtype_valid(dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "dtype %d", dtype);
+    if (n_tensors) { ZB_NEED(shapes, "shapes"); ZB_NEED(ranks, "ranks"); }
+    ConcatGeom g;
+    size_t os[8];
+    ZB_TRY(concat_resolve(shapes, ranks, n_tensors, axis, os, g));
+    ZB_NEED(y_shape, "y_shape");
+    if (y_rank != g.rank) return fail(ZANT_E_MISMATCHED_RANK, "output rank %zu != %zu", y_rank, g.rank);
+    for (size_t d = 0; d < g.rank; ++d)
+        if (y_shape[d] != os[d]) return fail(ZANT_E_INDEX_OUT_OF_BOUNDS, "output dim %zu is %zu, expected %zu", d, y_shape[d], os[d]);
+    ZB_NEED(tensors, "tensors"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    const size_t esz = dtype_size(dtype);
+    Stager s(ctx);
+    std::vector<int> idx(n_tensors);
+    for (size_t t = 0; t < n_tensors; ++t) idx[t] = s.in(tensors[t], g.num_slices * g.axis_dim[t] * g.slice * esz);
+    const int iy = s.out(y, numel(os, g.rank) * esz);
+    ZB_TRY(s.commit());
+    std::vector<const void*> dev(n_tensors);
+    for (size_t t = 0; t < n_tensors; ++t) dev[t] = s.ptr<char>(idx[t]);
+    ZB_TRY(run_concat(ctx, g, esz, dev.data(), s.ptr<char>(iy)));
+    return s.finish();
+}
+
+int32_t zant_b200_resize(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t rank,
+                         const char* mode, size_t mode_len, const float* scales, size_t n_scales,
+                         const size_t* sizes, size_t n_sizes, const char* coord_mode, size_t coord_mode_len,
+                         void* y, const size_t* y_shape, size_t y_rank) {
+    if (!dtype_valid(dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "dtype %d", dtype);
+    ZB_NEED(x_shape, "x_shape");
+    if (rank == 0 || rank > 8) return fail(ZANT_E_UNSUPPORTED_DIMENSION, "rank %zu", rank);
+    size_t os[8];
+    ZB_TRY(resize_output_shape(x_shape, rank, scales, n_scales, sizes, n_sizes, os));
+    if (!bytes_eq(mode, mode_len, "nearest")) {
+        if (bytes_eq(mode, mode_len, "linear") || bytes_eq(mode, mode_len, "cubic"))
+            return fail(ZANT_E_UNSUPPORTED, "Resize mode linear/cubic is not implemented by this back end");
+        return fail(ZANT_E_UNSUPPORTED_MODE, "unknown Resize mode");
+    }
+    ZB_NEED(y_shape, "y_shape");
+    if (y_rank != rank) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "output rank");
+    for (size_t d = 0; d < rank; ++d) if (y_shape[d] != os[d]) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "output dim %zu is %zu, expected %zu", d, y_shape[d], os[d]);
+    for (size_t d = 0; d < rank; ++d) if (x_shape[d] == 0) return fail(ZANT_E_EMPTY_TENSOR, "empty input");
+    ZB_NEED(x, "x"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    std::vector<int32_t> table, axis_offset;
+    resize_index_table(x_shape, os, rank, coord_mode_code(coord_mode, coord_mode_len), table, axis_offset);
+    const size_t esz = dtype_size(dtype);
+    Stager s(ctx);
+    const int ix = s.in(x, numel(x_shape, rank) * esz), iy = s.out(y, numel(os, rank) * esz);
+    const int it = s.in(table.data(), std::max<size_t>(table.size(), 1) * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_resize(ctx, esz, s.ptr<char>(ix), s.ptr<char>(iy), s.ptr<int32_t>(it), x_shape, os, rank, axis_offset));
+    return s.finish();
+}
+
+int32_t zant_b200_reduce_mean_f32(zant_ctx* ctx, const float* x, const size_t* x_shape, size_t x_rank,
+                                  float* y, const size_t* y_shape, size_t y_rank,
+                                  const int64_t* axes, size_t n_axes, int32_t keepdims, int32_t noop_with_empty_axes) {
+    (void)keepdims;
+    ZB_NEED(x_shape, "x_shape"); ZB_NEED(y_shape, "y_shape");
+    ReduceGeom g;
+    ZB_TRY(reduce_resolve(x_shape, x_rank, y_shape, y_rank, axes, n_axes, noop_with_empty_axes != 0, g));
+    ZB_NEED(x, "x"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ix = s.in(x, g.total * 4), iy = s.out(y, g.out_total * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_reduce_mean_f32(ctx, g, s.ptr<float>(ix), s.ptr<float>(iy)));
+    return s.finish();
+}
+
+int32_t zant_b200_reshape(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                          const size_t* new_shape, size_t new_rank, void* y, size_t* y_shape_out) {
+    if (!dtype_valid(dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "dtype %d", dtype);
+    ZB_NEED(x_shape, "x_shape"); ZB_NEED(new_shape, "new_shape"); ZB_NEED(y_shape_out, "y_shape_out");
+    if (new_rank > 16) return fail(ZANT_E_UNSUPPORTED_DIMENSION, "rank %zu", new_rank);
+    size_t out[16];
+    ZB_TRY(reshape_resolve(x_shape, x_rank, new_shape, new_rank, out));
+    for (size_t i = 0; i < new_rank; ++i) y_shape_out[i] = out[i];
+    const size_t bytes = numel(x_shape, x_rank) * dtype_size(dtype);
+    if (bytes == 0) return ZANT_OK;
+    ZB_NEED(x, "x"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    // The reference copies (lib_shape_math.zig:1208); cudaMemcpyAsync picks the direction itself.
+    ZB_CUDA(cudaMemcpyAsync(y, x, bytes, cudaMemcpyDefault, ctx->stream));
+    if (!is_device_ptr(y) || !is_device_ptr(x)) ZB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return ZANT_OK;
+}
+
+// ------------------------------------------------------------------------------------ quantized operators
+static bool q8_dtype(int32_t dt) { return dt == ZANT_I8 || dt == ZANT_U8; }
+
+int32_t zant_b200_quantize_linear(zant_ctx* ctx, const float* x, size_t n, float scale, int32_t zero_point, int32_t out_dtype, void* y) {
+    if (!q8_dtype(out_dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QuantizeLinear output must be int8 or uint8");
+    if (n) { ZB_NEED(x, "x"); ZB_NEED(y, "y"); }
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ix = s.in(x, n * 4), iy = s.out(y, n);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_quantize(ctx, s.ptr<float>(ix), s.ptr<char>(iy), n, scale, zero_point, out_dtype));
+    return s.finish();
+}
+
+int32_t zant_b200_dequantize_linear(zant_ctx* ctx, int32_t in_dtype, const void* q, size_t n, float scale, int32_t zero_point, float* y) {
+    if (!q8_dtype(in_dtype) && in_dtype != ZANT_I32) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "DequantizeLinear input must be int8, uint8 or int32");
+    if (n) { ZB_NEED(q, "q"); ZB_NEED(y, "y"); }
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int iq = s.in(q, n * dtype_size(in_dtype)), iy = s.out(y, n * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_dequantize(ctx, in_dtype, s.ptr<char>(iq), s.ptr<float>(iy), n, scale, zero_point));
+    return s.finish();
+}
+
+int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                              float x_scale, int32_t x_zp, const int8_t* w, const size_t* w_shape, size_t w_rank,
+                              const float* w_scale, const int32_t* w_zp, size_t n_w_scale, float y_scale, int32_t y_zp,
+                              const int32_t* bias, size_t bias_len, int32_t y_dtype, void* y, const size_t* y_shape, size_t y_rank,
+                              const size_t* stride, size_t n_stride, const size_t* pads, size_t n_pads,
+                              const size_t* dilations, size_t n_dil, size_t group, int32_t auto_pad, int32_t activation) {
+    ZB_NEED(x_shape, "x_shape"); ZB_NEED(w_shape, "w_shape"); ZB_NEED(y_shape, "y_shape");
+    if (!q8_dtype(x_dtype) || !q8_dtype(y_dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearConv tensors must be int8 or uint8");
+    ConvGeom g;
+    ZB_TRY(conv_resolve_onnx(x_shape, x_rank, w_shape, w_rank, y_shape, y_rank, stride, n_stride, pads, n_pads, dilations, n_dil, group, auto_pad, g));
+    ZB_NEED(w_scale, "w_scale");
+    if (n_w_scale != 1 && n_w_scale != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "w_scale holds %zu values for %d filters", n_w_scale, g.M);
+    if (bias && bias_len != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "bias holds %zu values for %d filters", bias_len, g.M);
+    if (activation < ZANT_QACT_NONE || activation > ZANT_QACT_RELU6) return fail(ZANT_E_INVALID_INPUT, "activation %d", activation);
+    ZB_NEED(x, "x"); ZB_NEED(w, "w"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    std::vector<float> mult;
+    requant_multipliers(x_scale, w_scale, n_w_scale, y_scale, (size_t)g.M, mult);
+    std::vector<int32_t> wz((size_t)g.M, 0);
+    if (w_zp) for (int m = 0; m < g.M; ++m) wz[m] = w_zp[n_w_scale == 1 ? 0 : m];
+    Stager s(ctx);
+    const int ix = s.in(x, numel(x_shape, 4)), iw = s.in(w, numel(w_shape, 4)), iy = s.out(y, numel(y_shape, 4));
+    const int im = s.in(mult.data(), mult.size() * 4), iz = s.in(wz.data(), wz.size() * 4), ib = s.in(bias, (size_t)g.M * 4);
+    ZB_TRY(s.commit());
+    QConvArgs p{};
+    p.x = s.ptr<char>(ix); p.w = s.ptr<int8_t>(iw); p.y = s.ptr<char>(iy);
+    p.mult = s.ptr<float>(im); p.w_zp = s.ptr<int32_t>(iz); p.bias = s.ptr<int32_t>(ib);
+    p.x_zp = x_zp; p.rq = Requant{y_scale, y_zp, activation}; p.g = g;
+    ZB_TRY(run_qconv_generic(ctx, p, x_dtype, y_dtype));
+    return s.finish();
+}
+
+int32_t zant_b200_qlinearmatmul(zant_ctx* ctx, int32_t a_dtype, const void* a, const size_t* a_shape, size_t a_rank,
+                                float a_scale, int32_t a_zp, const int8_t* b, const size_t* b_shape, size_t b_rank,
+                                const float* b_scale, const int32_t* b_zp, size_t n_b_scale, float y_scale, int32_t y_zp,
+                                const int32_t* bias, size_t bias_len, int32_t y_dtype, void* y, const size_t* y_shape, size_t y_rank,
+                                int32_t activation) {
+    ZB_NEED(a_shape, "a_shape"); ZB_NEED(b_shape, "b_shape"); ZB_NEED(y_shape, "y_shape");
+    if (a_rank != 2 || b_rank != 2 || y_rank != 2) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearMatMul takes 2-D operands");
+    if (!q8_dtype(a_dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "A must be int8 or uint8");
+    if (!q8_dtype(y_dtype) && y_dtype != ZANT_I32) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "Y must be int8, uint8 or int32");
+    const size_t M = a_shape[0], K = a_shape[1], N = b_shape[1];
+    if (b_shape[0] != K) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "A cols %zu != B rows %zu", K, b_shape[0]);
+    if (M * N == 0 || K == 0) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "empty operand");
+    if (y_shape[0] != M || y_shape[1] != N) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "output is not [%zu,%zu]", M, N);
+    ZB_NEED(b_scale, "b_scale");
+    if (n_b_scale != 1 && n_b_scale != N) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "b_scale holds %zu values for %zu columns", n_b_scale, N);
+    if (bias && bias_len != N) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "bias holds %zu values for %zu columns", bias_len, N);
+    if (M > 0x7fffffffULL || N > 0x7fffffffULL || K > 0x7fffffffULL) return fail(ZANT_E_TOO_LARGE, "dims exceed int range");
+    ZB_NEED(a, "a"); ZB_NEED(b, "b"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    std::vector<float> mult;
+    requant_multipliers(a_scale, b_scale, n_b_scale, y_scale, N, mult);
+    std::vector<int32_t> bz(N, 0);
+    if (b_zp) for (size_t j = 0; j < N; ++j) bz[j] = b_zp[n_b_scale == 1 ? 0 : j];
+    Stager s(ctx);
+    const int ia = s.in(a, M * K), ib = s.in(b, K * N), iy = s.out(y, M * N * dtype_size(y_dtype));
+    const int im = s.in(mult.data(), N * 4), iz = s.in(bz.data(), N * 4), ibias = s.in(bias, N * 4);
+    ZB_TRY(s.commit());
+    QMatArgs p{};
+    p.a = s.ptr<char>(ia); p.b = s.ptr<int8_t>(ib); p.y = s.ptr<char>(iy);
+    p.mult = s.ptr<float>(im); p.b_zp = s.ptr<int32_t>(iz); p.bias = s.ptr<int32_t>(ibias);
+    p.a_zp = a_zp; p.rq = Requant{y_scale, y_zp, activation}; p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.y_i32 = y_dtype == ZANT_I32;
+    ZB_TRY(run_qmatmul_generic(ctx, p, a_dtype, y_dtype));
+    return s.finish();
+}
+
+int32_t zant_b200_qlinearadd(zant_ctx* ctx, int32_t dtype, const void* a, float a_scale, int32_t a_zp,
+                             const void* b, float b_scale, int32_t b_zp, float y_scale, int32_t y_zp, void* y, size_t n,
+                             int32_t activation) {
+    if (!q8_dtype(dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearAdd tensors must be int8 or uint8");
+    if (n) { ZB_NEED(a, "a"); ZB_NEED(b, "b"); ZB_NEED(y, "y"); }
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ia = s.in(a, n), ib = s.in(b, n), iy = s.out(y, n);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_qadd(ctx, dtype, s.ptr<char>(ia), a_scale, a_zp, s.ptr<char>(ib), b_scale, b_zp, y_scale, y_zp, activation, s.ptr<char>(iy), n));
+    return s.finish();
+}
+
+int32_t zant_b200_qlinear_global_avgpool(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                                         float x_scale, int32_t x_zp, float y_scale, int32_t y_zp, void* y) {
+    if (!q8_dtype(dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "tensors must be int8 or uint8");
+    ZB_NEED(x_shape, "x_shape");
+    if (x_rank != 4) return fail(ZANT_E_INVALID_DIMENSIONS, "GlobalAveragePool needs a 4-D input");
+    const size_t planes = x_shape[0] * x_shape[1], hw = x_shape[2] * x_shape[3];
+    if (hw == 0 || hw > 0x7fffffffULL) return fail(ZANT_E_INVALID_DIMENSIONS, "H*W = %zu", hw);
+    ZB_NEED(x, "x"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ix = s.in(x, planes * hw), iy = s.out(y, planes);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_qgap(ctx, dtype, s.ptr<char>(ix), s.ptr<char>(iy), planes, (int)hw, x_scale, x_zp, y_scale, y_zp));
+    return s.finish();
+}
+
+int32_t zant_b200_maxpool_q8(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                             void* y, const size_t* y_shape, size_t y_rank,
+                             const size_t* kernel_shape, size_t n_kernel, const size_t* strides, size_t n_strides,
+                             const size_t* dilations, size_t n_dil, const size_t* pads, size_t n_pads, int32_t auto_pad) {
+    if (!q8_dtype(dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "tensors must be int8 or uint8");
+    ZB_NEED(x_shape, "x_shape"); ZB_NEED(y_shape, "y_shape");
+    PoolGeom g;
+    ZB_TRY(pool_resolve(x_shape, x_rank, y_shape, y_rank, kernel_shape, n_kernel, strides, n_strides, dilations, n_dil, pads, n_pads, auto_pad, g));
+    ZB_NEED(x, "x"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
+    ZB_TRY(s.commit());
+    if (dtype == ZANT_U8) ZB_TRY(run_maxpool<uint8_t>(ctx, g, s.ptr<uint8_t>(ix), s.ptr<uint8_t>(iy)));
+    else ZB_TRY(run_maxpool<int8_t>(ctx, g, s.ptr<int8_t>(ix), s.ptr<int8_t>(iy)));
+    return s.finish();
+}
+
+int32_t zant_b200_lut_q8(zant_ctx* ctx, const void* x, const uint8_t lut[256], void* y, size_t n) {
+    ZB_NEED(lut, "lut");
+    if (n) { ZB_NEED(x, "x"); ZB_NEED(y, "y"); }
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ix = s.in(x, n), iy = s.out(y, n), il = s.in(lut, 256);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_lut(ctx, s.ptr<char>(ix), s.ptr<char>(iy), n, s.ptr<uint8_t>(il)));
+    return s.finish();
+}
+
+}  // extern "C"

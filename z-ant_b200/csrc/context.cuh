@@ -1,0 +1,139 @@
+// Device context, staging of host buffers, launch bookkeeping.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <vector>
+
+#include "status.hpp"
+
+struct zant_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = true;
+    char* arena = nullptr;        // staging arena for host-pointer calls and op workspaces
+    size_t arena_bytes = 0;
+    size_t arena_used = 0;
+    uint64_t launches = 0;
+    int sm_count = 148;
+    int* status_word = nullptr;   // device int: kernels with bounded waits report here
+};
+
+namespace zb {
+
+#define ZB_CUDA(expr)                                                                         \
+    do {                                                                                      \
+        cudaError_t _e = (expr);                                                              \
+        if (_e != cudaSuccess)                                                                \
+            return zb::fail(ZANT_E_CUDA, "%s -> %s", #expr, cudaGetErrorString(_e));          \
+    } while (0)
+
+inline int32_t check_launch(zant_ctx* ctx, const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(ZANT_E_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+    ctx->launches++;
+    return ZANT_OK;
+}
+
+inline bool is_device_ptr(const void* p) {
+    if (!p) return false;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+constexpr size_t kArenaAlign = 256;
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+inline int32_t arena_reserve(zant_ctx* ctx, size_t need_total) {
+    if (need_total <= ctx->arena_bytes) return ZANT_OK;
+    if (ctx->arena_used != 0) return fail(ZANT_E_ARENA_EXHAUSTED, "arena of %zu bytes exhausted (need %zu)", ctx->arena_bytes, need_total);
+    ZB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (ctx->arena) ZB_CUDA(cudaFree(ctx->arena));
+    ctx->arena = nullptr; ctx->arena_bytes = 0;
+    const size_t want = align_up(need_total + need_total / 4, 1 << 20);
+    ZB_CUDA(cudaMalloc((void**)&ctx->arena, want));
+    ctx->arena_bytes = want;
+    return ZANT_OK;
+}
+
+// Per-call staging: host inputs are copied into the arena, host outputs are copied back
+// when the call finishes; device pointers pass through.  All buffers of one call must be
+// declared (plan phase) before the first is materialised so the arena can grow once.
+class Stager {
+  public:
+    explicit Stager(zant_ctx* c) : ctx_(c) {}
+    ~Stager() { if (ctx_) ctx_->arena_used = 0; }
+
+    struct Slot { const void* host_in; void* host_out; size_t bytes; size_t off; void* dev; bool staged; };
+
+    int in(const void* p, size_t bytes) { return add(p, nullptr, bytes, true); }
+    int out(void* p, size_t bytes) { return add(nullptr, p, bytes, false); }
+    int scratch(size_t bytes) {
+        Slot s{nullptr, nullptr, bytes, 0, nullptr, true};
+        slots_.push_back(s);
+        return (int)slots_.size() - 1;
+    }
+
+    // Allocates arena space for every staged slot and issues the H2D copies.
+    int32_t commit() {
+        size_t total = 0;
+        for (auto& s : slots_) if (s.staged) { s.off = total; total += align_up(s.bytes ? s.bytes : 1, kArenaAlign); }
+        if (total) {
+            int32_t st = arena_reserve(ctx_, total);
+            if (st != ZANT_OK) return st;
+            ctx_->arena_used = total;
+        }
+        for (auto& s : slots_) {
+            if (!s.staged) continue;
+            s.dev = ctx_->arena + s.off;
+            if (s.host_in && s.bytes)
+                ZB_CUDA(cudaMemcpyAsync(s.dev, s.host_in, s.bytes, cudaMemcpyHostToDevice, ctx_->stream));
+        }
+        return ZANT_OK;
+    }
+
+    template <typename T> T* ptr(int i) { return reinterpret_cast<T*>(slots_[i].dev); }
+
+    // Copies staged outputs back and, if anything was staged, waits for the stream.
+    int32_t finish() {
+        bool any = false;
+        for (auto& s : slots_) {
+            if (!s.staged) continue;
+            any = true;
+            if (s.host_out && s.bytes)
+                ZB_CUDA(cudaMemcpyAsync(s.host_out, s.dev, s.bytes, cudaMemcpyDeviceToHost, ctx_->stream));
+        }
+        if (any) {
+            ZB_CUDA(cudaStreamSynchronize(ctx_->stream));
+            ctx_->arena_used = 0;
+        }
+        return ZANT_OK;
+    }
+
+  private:
+    int add(const void* pin, void* pout, size_t bytes, bool is_in) {
+        const void* p = is_in ? pin : pout;
+        Slot s{nullptr, nullptr, bytes, 0, nullptr, false};
+        if (p == nullptr) { s.dev = nullptr; }
+        else if (is_device_ptr(p)) { s.dev = const_cast<void*>(p); }
+        else { s.staged = true; s.host_in = pin; s.host_out = pout; }
+        slots_.push_back(s);
+        return (int)slots_.size() - 1;
+    }
+    zant_ctx* ctx_;
+    std::vector<Slot> slots_;
+};
+
+inline int grid_for(size_t work_items, int block, int sm_count, int waves = 8) {
+    size_t blocks = (work_items + block - 1) / block;
+    const size_t cap = (size_t)sm_count * waves;
+    if (blocks > cap) blocks = cap;
+    if (blocks == 0) blocks = 1;
+    return (int)blocks;
+}
+
+}  // namespace zb

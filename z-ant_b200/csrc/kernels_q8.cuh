@@ -1,0 +1,211 @@
+// Generic quantized kernels (NCHW, any geometry).  Exact int32 accumulation; requantisation in
+// fp32 with the operation order documented in include/zant_b200.h — each step is an explicitly
+// rounded intrinsic so the compiler cannot fuse or reorder it.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "geometry.hpp"
+
+namespace zb {
+
+__device__ __forceinline__ int rne_clamped(float v) {
+    // nearest-even of v clamped to [-512, 511]; fmaxf/fminf drop a NaN operand
+    v = fminf(fmaxf(v, -512.0f), 511.0f);
+    return __float2int_rn(v);
+}
+
+template <bool U8> __device__ __forceinline__ int sat_q(int t) {
+    return U8 ? min(max(t, 0), 255) : min(max(t, -128), 127);
+}
+
+struct Requant {
+    float y_scale; int y_zp; int act;   // zant_qact
+};
+
+template <bool YU8>
+__device__ __forceinline__ int requant_one(int acc, float M, const Requant& r) {
+    const float v = __fmul_rn(__int2float_rn(acc), M);
+    int t = sat_q<YU8>(rne_clamped(v) + r.y_zp);
+    if (r.act != ZANT_QACT_NONE) {
+        t = max(t, sat_q<YU8>(r.y_zp));
+        if (r.act == ZANT_QACT_RELU6) t = min(t, sat_q<YU8>(rne_clamped(__fdiv_rn(6.0f, r.y_scale)) + r.y_zp));
+    }
+    return t;
+}
+
+template <bool U8> __device__ __forceinline__ int load_q(const void* p, size_t i) {
+    return U8 ? (int)reinterpret_cast<const uint8_t*>(p)[i] : (int)reinterpret_cast<const int8_t*>(p)[i];
+}
+template <bool U8> __device__ __forceinline__ void store_q(void* p, size_t i, int v) {
+    if (U8) reinterpret_cast<uint8_t*>(p)[i] = (uint8_t)v; else reinterpret_cast<int8_t*>(p)[i] = (int8_t)v;
+}
+
+// ---------------------------------------------------------------------------- Quantize / Dequantize
+template <bool YU8>
+__global__ void quantize_linear_k(const float* __restrict__ x, void* __restrict__ y, size_t n, float scale, int zp, bool vec) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    size_t done = 0;
+    if (vec) {
+        const size_t n4 = n / 4;
+        const float4* x4 = reinterpret_cast<const float4*>(x);
+        uint32_t* y4 = reinterpret_cast<uint32_t*>(y);
+        for (size_t i = tid; i < n4; i += stride) {
+            const float4 v = x4[i];
+            const int a = sat_q<YU8>(rne_clamped(__fdiv_rn(v.x, scale)) + zp);
+            const int b = sat_q<YU8>(rne_clamped(__fdiv_rn(v.y, scale)) + zp);
+            const int c = sat_q<YU8>(rne_clamped(__fdiv_rn(v.z, scale)) + zp);
+            const int d = sat_q<YU8>(rne_clamped(__fdiv_rn(v.w, scale)) + zp);
+            y4[i] = (uint32_t)(a & 255) | ((uint32_t)(b & 255) << 8) | ((uint32_t)(c & 255) << 16) | ((uint32_t)(d & 255) << 24);
+        }
+        done = n4 * 4;
+    }
+    for (size_t i = done + tid; i < n; i += stride)
+        store_q<YU8>(y, i, sat_q<YU8>(rne_clamped(__fdiv_rn(x[i], scale)) + zp));
+}
+
+template <typename Q>
+__global__ void dequantize_linear_k(const Q* __restrict__ q, float* __restrict__ y, size_t n, float scale, int zp) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = __fmul_rn(__int2float_rn((int)q[i] - zp), scale);
+}
+
+// ---------------------------------------------------------------------------- QLinearConv, generic
+// One output per thread, ow fastest so that neighbouring threads read neighbouring inputs.
+struct QConvArgs {
+    const void* x; const int8_t* w; void* y;
+    const float* mult;        // per-output-channel multiplier M[m] (device, length g.M)
+    const int32_t* w_zp;      // per output channel (device, length g.M)
+    const int32_t* bias;      // nullable
+    int x_zp;
+    Requant rq;
+    ConvGeom g;
+};
+
+template <bool XU8, bool YU8>
+__global__ void qconv_nchw_generic(const QConvArgs p) {
+    const ConvGeom& g = p.g;
+    const size_t total = (size_t)g.N * g.M * g.OH * g.OW;
+    const int Mg = g.M / g.G;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int ow = (int)(i % g.OW); size_t t = i / g.OW;
+        const int oh = (int)(t % g.OH); t /= g.OH;
+        const int m = (int)(t % g.M); const int n = (int)(t / g.M);
+        const int grp = m / Mg;
+        const int wz = p.w_zp[m];
+        const int ih0 = oh * g.sh - g.pt, iw0 = ow * g.sw - g.pl;
+        int acc = 0;
+        for (int c = 0; c < g.Cg; ++c) {
+            const size_t xplane = ((size_t)n * g.C + (size_t)grp * g.Cg + c) * g.H;
+            const int8_t* wp = p.w + (((size_t)m * g.Cg + c) * g.KH) * g.KW;
+            for (int kh = 0; kh < g.KH; ++kh) {
+                const int ih = ih0 + kh * g.dh;
+                if (ih < 0 || ih >= g.H) continue;
+                for (int kw = 0; kw < g.KW; ++kw) {
+                    const int iw = iw0 + kw * g.dw;
+                    if (iw < 0 || iw >= g.W) continue;
+                    const int xv = load_q<XU8>(p.x, (xplane + ih) * g.W + iw) - p.x_zp;
+                    acc += xv * ((int)wp[kh * g.KW + kw] - wz);
+                }
+            }
+        }
+        if (p.bias) acc += p.bias[m];
+        store_q<YU8>(p.y, i, requant_one<YU8>(acc, p.mult[m], p.rq));
+    }
+}
+
+// ---------------------------------------------------------------------------- QLinearMatMul, generic
+struct QMatArgs {
+    const void* a; const int8_t* b; void* y;
+    const float* mult; const int32_t* b_zp; const int32_t* bias;
+    int a_zp; Requant rq;
+    int M, N, K;
+    int y_i32;   // store the raw accumulator
+};
+
+template <bool AU8, bool YU8>
+__global__ void qmatmul_generic(const QMatArgs p) {
+    const size_t total = (size_t)p.M * p.N;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int j = (int)(i % p.N); const size_t row = i / p.N;
+        const int bz = p.b_zp[j];
+        int acc = 0;
+        for (int k = 0; k < p.K; ++k)
+            acc += (load_q<AU8>(p.a, row * p.K + k) - p.a_zp) * ((int)p.b[(size_t)k * p.N + j] - bz);
+        if (p.bias) acc += p.bias[j];
+        if (p.y_i32) reinterpret_cast<int32_t*>(p.y)[i] = acc;
+        else store_q<YU8>(p.y, i, requant_one<YU8>(acc, p.mult[j], p.rq));
+    }
+}
+
+// ---------------------------------------------------------------------------- QLinearAdd
+template <bool U8>
+__global__ void qadd_k(const void* __restrict__ a, float a_s, int a_zp, const void* __restrict__ b, float b_s, int b_zp,
+                       float y_s, int y_zp, int act, void* __restrict__ y, size_t n) {
+    const int lo = sat_q<U8>(y_zp);
+    const int six = sat_q<U8>(rne_clamped(__fdiv_rn(6.0f, y_s)) + y_zp);
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float fa = __fmul_rn(__int2float_rn(load_q<U8>(a, i) - a_zp), a_s);
+        const float fb = __fmul_rn(__int2float_rn(load_q<U8>(b, i) - b_zp), b_s);
+        const float v = __fdiv_rn(__fadd_rn(fa, fb), y_s);
+        int t = sat_q<U8>(rne_clamped(v) + y_zp);
+        if (act != ZANT_QACT_NONE) t = max(t, lo);
+        if (act == ZANT_QACT_RELU6) t = min(t, six);
+        store_q<U8>(y, i, t);
+    }
+}
+
+// ---------------------------------------------------------------------------- Quantized GlobalAveragePool
+// One warp per (n,c) plane: exact int32 sum by shuffle reduction (integer addition is
+// associative, so the order is free), then the three rounded fp32 steps.
+template <bool U8>
+__global__ void qgap_k(const void* __restrict__ x, void* __restrict__ y, size_t planes, int hw,
+                       float x_s, int x_zp, float y_s, int y_zp) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+    const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t pidx = warp; pidx < planes; pidx += nwarps) {
+        int s = 0;
+        for (int j = lane; j < hw; j += 32) s += load_q<U8>(x, pidx * hw + j) - x_zp;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) {
+            const float f = __fmul_rn(__int2float_rn(s), x_s);
+            const float mean = __fdiv_rn(f, (float)hw);
+            const float v = __fdiv_rn(mean, y_s);
+            store_q<U8>(y, pidx, sat_q<U8>(rne_clamped(v) + y_zp));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------- 256-entry table lookup
+__global__ void lut_q8_k(const uint8_t* __restrict__ x, uint8_t* __restrict__ y, size_t n, const uint8_t* __restrict__ lut_g, bool vec) {
+    __shared__ uint8_t lut[256];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) lut[i] = lut_g[i];
+    __syncthreads();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    size_t done = 0;
+    if (vec) {
+        const size_t n16 = n / 16;
+        const uint4* x4 = reinterpret_cast<const uint4*>(x);
+        uint4* y4 = reinterpret_cast<uint4*>(y);
+        for (size_t i = tid; i < n16; i += stride) {
+            uint4 v = x4[i];
+            uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t u = w[k];
+                w[k] = (uint32_t)lut[u & 255] | ((uint32_t)lut[(u >> 8) & 255] << 8) |
+                       ((uint32_t)lut[(u >> 16) & 255] << 16) | ((uint32_t)lut[u >> 24] << 24);
+            }
+            y4[i] = v;
+        }
+        done = n16 * 16;
+    }
+    for (size_t i = done + tid; i < n; i += stride) y[i] = lut[x[i]];
+}
+
+}  // namespace zb

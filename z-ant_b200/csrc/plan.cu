@@ -1,0 +1,612 @@
+// Plan: the run-time form of a generated predict() — graph tensors at fixed offsets of one
+// cudaMalloc'd arena, constants uploaded once, nodes launched in insertion order.
+// (src/codeGen/predict.zig:23-70 emits the straight-line op calls this replays;
+//  :110-142, :265-272 is the one-static-array-per-tensor memory plan mirrored here.)
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+#include <functional>
+#include <string>
+#include <vector>
+
+#include "../../include/zant_b200.h"
+#include "context.cuh"
+#include "geometry.hpp"
+#include "ops.cuh"
+#include "status.hpp"
+
+using namespace zb;
+
+struct PlanTensor {
+    int32_t dtype = ZANT_F32;
+    std::vector<size_t> shape;
+    size_t bytes = 0;
+    bool is_const = false;
+    std::vector<char> host;     // initializer bytes (kept until finalize)
+    size_t offset = 0;          // arena offset
+    void* arena_ptr = nullptr;  // address inside the plan's arena
+    void* bound = nullptr;      // caller's device buffer bound for the current run (input/output)
+    int alias = -1;             // Reshape output: shares the buffer of this tensor
+};
+
+struct PlanNode {
+    int32_t op = 0;
+    std::vector<int> in, out;
+    zant_node_attrs a{};
+};
+
+struct zant_plan {
+    zant_ctx* ctx = nullptr;
+    std::vector<PlanTensor> t;
+    std::vector<PlanNode> nodes;
+    std::vector<std::vector<char>> aux_host;   // derived constants (multipliers, tables)
+    std::vector<size_t> aux_off;
+    int input = -1, output = -1;
+    bool finalized = false;
+    char* arena = nullptr;
+    size_t arena_bytes = 0;
+    std::vector<std::function<int32_t()>> steps;
+    std::vector<std::string> step_names;
+    int launches_per_run = 0;
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_events;   // pool, reused between reads
+    size_t prof_used = 0;                   // events recorded since the last read
+
+    void* ptr(int id) const {
+        int r = id;
+        while (t[r].alias >= 0) r = t[r].alias;
+        return t[r].bound ? t[r].bound : t[r].arena_ptr;
+    }
+    template <typename T> T* p(int id) const { return id < 0 ? nullptr : reinterpret_cast<T*>(ptr(id)); }
+    void* aux(int id) const { return arena + aux_off[id]; }
+    int add_aux(const void* data, size_t bytes) {
+        aux_host.emplace_back((const char*)data, (const char*)data + bytes);
+        return (int)aux_host.size() - 1;
+    }
+};
+
+namespace {
+
+const char* kAutoPadNames[] = {"NOTSET", "SAME_UPPER", "SAME_LOWER", "VALID"};
+
+int32_t need_inputs(const PlanNode& n, size_t lo, size_t hi, const char* name) {
+    if (n.in.size() < lo || n.in.size() > hi) return fail(ZANT_E_INVALID_INPUT, "%s takes %zu..%zu inputs, got %zu", name, lo, hi, n.in.size());
+    if (n.out.size() != 1) return fail(ZANT_E_INVALID_INPUT, "%s produces one output", name);
+    return ZANT_OK;
+}
+
+int opt_in(const PlanNode& n, size_t i) { return i < n.in.size() ? n.in[i] : -1; }
+
+int32_t want_dtype(const zant_plan* pl, int id, int32_t dt, const char* what) {
+    if (id >= 0 && pl->t[id].dtype != dt) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "%s: tensor %d has dtype %d, expected %d", what, id, pl->t[id].dtype, dt);
+    return ZANT_OK;
+}
+
+// Table for a unary function between two quantized tensors:
+//   lut[code] = sat(rne(f(float(q - zp_in) * s_in) / s_out) + zp_out)
+template <typename F>
+void build_unary_lut(int32_t dtype, float s_in, int zp_in, float s_out, int zp_out, F f, uint8_t lut[256]) {
+    for (int code = 0; code < 256; ++code) {
+        const int q = dtype == ZANT_U8 ? code : (int)(int8_t)(uint8_t)code;
+        volatile float x = (float)(q - zp_in) * s_in;
+        volatile float a = f((float)x);
+        volatile float v = a / s_out;
+        float c = std::fmin(std::fmax((float)v, -512.0f), 511.0f);
+        int t = (int)std::nearbyintf(c) + zp_out;
+        const int lo = dtype == ZANT_U8 ? 0 : -128, hi = dtype == ZANT_U8 ? 255 : 127;
+        t = std::min(std::max(t, lo), hi);
+        lut[code] = (uint8_t)t;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t zant_b200_plan_create(zant_ctx* ctx, zant_plan** out) {
+    if (!out) return fail(ZANT_E_NULL_POINTER, "out is NULL");
+    *out = nullptr;
+    if (!ctx) return fail(ZANT_E_CUDA_UNAVAILABLE, "no context; there is no CPU fallback");
+    zant_plan* p = new zant_plan();
+    p->ctx = ctx;
+    *out = p;
+    return ZANT_OK;
+}
+
+int32_t zant_b200_plan_destroy(zant_plan* plan) {
+    if (!plan) return ZANT_OK;
+    cudaSetDevice(plan->ctx->device);
+    cudaStreamSynchronize(plan->ctx->stream);
+    if (plan->arena) cudaFree(plan->arena);
+    for (cudaEvent_t e : plan->prof_events) cudaEventDestroy(e);
+    cudaGetLastError();
+    delete plan;
+    return ZANT_OK;
+}
+
+int32_t zant_b200_plan_tensor(zant_plan* plan, int32_t dtype, const size_t* shape, size_t rank, const void* const_data, int32_t* id) {
+    if (!plan) return fail(ZANT_E_BAD_HANDLE, "plan is NULL");
+    if (plan->finalized) return fail(ZANT_E_BAD_HANDLE, "plan already finalized");
+    if (!id || (rank && !shape)) return fail(ZANT_E_NULL_POINTER, "id/shape is NULL");
+    if (!dtype_valid(dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "dtype %d", dtype);
+    if (rank > 8) return fail(ZANT_E_UNSUPPORTED_DIMENSION, "rank %zu", rank);
+    PlanTensor t;
+    t.dtype = dtype;
+    t.shape.assign(shape, shape + rank);
+    t.bytes = numel(shape, rank) * dtype_size(dtype);
+    if (const_data) {
+        t.is_const = true;
+        t.host.assign((const char*)const_data, (const char*)const_data + t.bytes);
+    }
+    plan->t.push_back(std::move(t));
+    *id = (int32_t)plan->t.size() - 1;
+    return ZANT_OK;
+}
+
+int32_t zant_b200_plan_node(zant_plan* plan, int32_t op, const int32_t* inputs, size_t n_inputs,
+                            const int32_t* outputs, size_t n_outputs, const zant_node_attrs* attrs) {
+    if (!plan) return fail(ZANT_E_BAD_HANDLE, "plan is NULL");
+    if (plan->finalized) return fail(ZANT_E_BAD_HANDLE, "plan already finalized");
+    if ((n_inputs && !inputs) || (n_outputs && !outputs)) return fail(ZANT_E_NULL_POINTER, "inputs/outputs is NULL");
+    PlanNode n;
+    n.op = op;
+    const int nt = (int)plan->t.size();
+    for (size_t i = 0; i < n_inputs; ++i) {
+        if (inputs[i] < -1 || inputs[i] >= nt) return fail(ZANT_E_INVALID_INPUT, "input %zu: unknown tensor id %d", i, inputs[i]);
+        n.in.push_back(inputs[i]);
+    }
+    for (size_t i = 0; i < n_outputs; ++i) {
+        if (outputs[i] < 0 || outputs[i] >= nt) return fail(ZANT_E_INVALID_INPUT, "output %zu: unknown tensor id %d", i, outputs[i]);
+        if (plan->t[outputs[i]].is_const) return fail(ZANT_E_INVALID_INPUT, "output %zu is an initializer", i);
+        n.out.push_back(outputs[i]);
+    }
+    if (attrs) n.a = *attrs;
+    plan->nodes.push_back(std::move(n));
+    return ZANT_OK;
+}
+
+static int32_t build_node(zant_plan* pl, size_t node_index, int32_t fuse);
+static int32_t try_fuse(zant_plan* pl, size_t node_index, size_t& consumed);
+
+int32_t zant_b200_plan_finalize(zant_plan* plan, int32_t input_id, int32_t output_id, int32_t fuse) {
+    if (!plan) return fail(ZANT_E_BAD_HANDLE, "plan is NULL");
+    if (plan->finalized) return fail(ZANT_E_BAD_HANDLE, "plan already finalized");
+    const int nt = (int)plan->t.size();
+    if (input_id < 0 || input_id >= nt || output_id < 0 || output_id >= nt) return fail(ZANT_E_INVALID_INPUT, "input/output id out of range");
+    plan->input = input_id; plan->output = output_id;
+    zant_ctx* ctx = plan->ctx;
+    ZB_CUDA(cudaSetDevice(ctx->device));
+
+    // 1. validate nodes, derive constants, record launch closures
+    plan->steps.clear(); plan->step_names.clear();
+    size_t i = 0;
+    while (i < plan->nodes.size()) {
+        size_t consumed = 0;
+        if (fuse) {
+            int32_t st = try_fuse(plan, i, consumed);
+            if (st != ZANT_OK) return st;
+        }
+        if (consumed == 0) {
+            int32_t st = build_node(plan, i, fuse);
+            if (st != ZANT_OK) return st;
+            consumed = 1;
+        }
+        i += consumed;
+    }
+
+    // 2. arena layout: every non-aliased tensor and every derived constant at a fixed offset
+    size_t off = 0;
+    for (auto& t : plan->t) {
+        if (t.alias >= 0) continue;
+        t.offset = off;
+        off += align_up(t.bytes ? t.bytes : 1, kArenaAlign);
+    }
+    plan->aux_off.resize(plan->aux_host.size());
+    for (size_t a = 0; a < plan->aux_host.size(); ++a) {
+        plan->aux_off[a] = off;
+        off += align_up(plan->aux_host[a].size() ? plan->aux_host[a].size() : 1, kArenaAlign);
+    }
+    plan->arena_bytes = off;
+    ZB_CUDA(cudaMalloc((void**)&plan->arena, off));
+    for (auto& t : plan->t) {
+        if (t.alias >= 0) continue;
+        t.arena_ptr = plan->arena + t.offset;
+        if (t.is_const && t.bytes) ZB_CUDA(cudaMemcpyAsync(t.arena_ptr, t.host.data(), t.bytes, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    for (size_t a = 0; a < plan->aux_host.size(); ++a)
+        if (!plan->aux_host[a].empty())
+            ZB_CUDA(cudaMemcpyAsync(plan->arena + plan->aux_off[a], plan->aux_host[a].data(), plan->aux_host[a].size(), cudaMemcpyHostToDevice, ctx->stream));
+    ZB_CUDA(cudaStreamSynchronize(ctx->stream));
+    for (auto& t : plan->t) { t.host.clear(); t.host.shrink_to_fit(); }
+
+    // 3. one dry count of launches
+    plan->finalized = true;
+    const uint64_t before = ctx->launches;
+    for (auto& s : plan->steps) { int32_t st = s(); if (st != ZANT_OK) { plan->finalized = false; return st; } }
+    ZB_CUDA(cudaStreamSynchronize(ctx->stream));
+    plan->launches_per_run = (int)(ctx->launches - before);
+    ctx->launches = before;
+    log_line("zant_b200 plan: %zu tensors, %zu nodes, %zu steps, %d launches, arena %zu bytes", plan->t.size(), plan->nodes.size(), plan->steps.size(), plan->launches_per_run, plan->arena_bytes);
+    return ZANT_OK;
+}
+
+int32_t zant_b200_plan_run(zant_plan* plan, const void* input, void* output) {
+    if (!plan || !plan->finalized) return fail(ZANT_E_BAD_HANDLE, "plan is NULL or not finalized");
+    if (!input || !output) return fail(ZANT_E_NULL_POINTER, "input/output is NULL");
+    zant_ctx* ctx = plan->ctx;
+    ZB_CUDA(cudaSetDevice(ctx->device));
+    PlanTensor& ti = plan->t[plan->input];
+    PlanTensor& to = plan->t[plan->output];
+    int out_root = plan->output;
+    while (plan->t[out_root].alias >= 0) out_root = plan->t[out_root].alias;
+    PlanTensor& tor = plan->t[out_root];
+    const bool in_dev = is_device_ptr(input), out_dev = is_device_ptr(output);
+    ti.bound = in_dev ? const_cast<void*>(input) : nullptr;
+    tor.bound = out_dev ? output : nullptr;
+    if (!in_dev) ZB_CUDA(cudaMemcpyAsync(ti.arena_ptr, input, ti.bytes, cudaMemcpyHostToDevice, ctx->stream));
+    auto mark = [&]() -> int32_t {
+        if (plan->prof_used == plan->prof_events.size()) {
+            cudaEvent_t e;
+            ZB_CUDA(cudaEventCreate(&e));
+            plan->prof_events.push_back(e);
+        }
+        ZB_CUDA(cudaEventRecord(plan->prof_events[plan->prof_used++], ctx->stream));
+        return ZANT_OK;
+    };
+    for (size_t s = 0; s < plan->steps.size(); ++s) {
+        if (plan->profiling) { int32_t st = mark(); if (st != ZANT_OK) return st; }
+        int32_t st = plan->steps[s]();
+        if (st != ZANT_OK) { ti.bound = nullptr; tor.bound = nullptr; return st; }
+    }
+    if (plan->profiling) { int32_t st = mark(); if (st != ZANT_OK) return st; }
+    if (!out_dev) {
+        ZB_CUDA(cudaMemcpyAsync(output, tor.arena_ptr, to.bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        ZB_CUDA(cudaStreamSynchronize(ctx->stream));
+    }
+    ti.bound = nullptr; tor.bound = nullptr;
+    return ZANT_OK;
+}
+
+size_t zant_b200_plan_arena_bytes(zant_plan* plan) { return plan ? plan->arena_bytes : 0; }
+int32_t zant_b200_plan_launches_per_run(zant_plan* plan) { return plan ? plan->launches_per_run : 0; }
+void* zant_b200_plan_tensor_ptr(zant_plan* plan, int32_t id) {
+    if (!plan || !plan->finalized || id < 0 || id >= (int)plan->t.size()) return nullptr;
+    return plan->ptr(id);
+}
+
+int32_t zant_b200_plan_step_count(zant_plan* plan) { return (plan && plan->finalized) ? (int32_t)plan->steps.size() : 0; }
+const char* zant_b200_plan_step_name(zant_plan* plan, int32_t step) {
+    if (!plan || step < 0 || step >= (int32_t)plan->step_names.size()) return "";
+    return plan->step_names[step].c_str();
+}
+
+int32_t zant_b200_plan_profile(zant_plan* plan, int32_t enable) {
+    if (!plan || !plan->finalized) return fail(ZANT_E_BAD_HANDLE, "plan is NULL or not finalized");
+    plan->profiling = enable != 0;
+    plan->prof_used = 0;
+    return ZANT_OK;
+}
+
+int32_t zant_b200_plan_profile_read(zant_plan* plan, float* sum_ms, int32_t* runs) {
+    if (!plan || !plan->finalized) return fail(ZANT_E_BAD_HANDLE, "plan is NULL or not finalized");
+    if (!sum_ms || !runs) return fail(ZANT_E_NULL_POINTER, "sum_ms/runs is NULL");
+    ZB_CUDA(cudaSetDevice(plan->ctx->device));
+    ZB_CUDA(cudaStreamSynchronize(plan->ctx->stream));
+    const size_t per_run = plan->steps.size() + 1;
+    const size_t n_runs = plan->prof_used / per_run;
+    for (size_t r = 0; r < n_runs; ++r)
+        for (size_t s = 0; s + 1 < per_run; ++s) {
+            float ms = 0.0f;
+            ZB_CUDA(cudaEventElapsedTime(&ms, plan->prof_events[r * per_run + s], plan->prof_events[r * per_run + s + 1]));
+            sum_ms[s] += ms;
+        }
+    *runs = (int32_t)n_runs;
+    plan->prof_used = 0;
+    return ZANT_OK;
+}
+
+int32_t zant_b200_plan_read_tensor(zant_plan* plan, int32_t id, void* host_dst) {
+    if (!plan || !plan->finalized) return fail(ZANT_E_BAD_HANDLE, "plan is NULL or not finalized");
+    if (id < 0 || id >= (int)plan->t.size()) return fail(ZANT_E_INVALID_INPUT, "tensor id %d", id);
+    if (!host_dst) return fail(ZANT_E_NULL_POINTER, "host_dst is NULL");
+    ZB_CUDA(cudaSetDevice(plan->ctx->device));
+    ZB_CUDA(cudaStreamSynchronize(plan->ctx->stream));
+    ZB_CUDA(cudaMemcpy(host_dst, plan->ptr(id), plan->t[id].bytes, cudaMemcpyDeviceToHost));
+    return ZANT_OK;
+}
+
+}  // extern "C"
+
+// --------------------------------------------------------------------------------------------
+// One node -> one (or a few) kernel launches, using the same resolvers as the single-op ABI.
+// --------------------------------------------------------------------------------------------
+static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
+    const PlanNode& n = pl->nodes[node_index];
+    const zant_node_attrs& a = n.a;
+    zant_ctx* ctx = pl->ctx;
+    auto T = [&](int id) -> const PlanTensor& { return pl->t[id]; };
+    auto push = [&](const char* name, std::function<int32_t()> fn) { pl->steps.push_back(std::move(fn)); pl->step_names.push_back(name); };
+
+    switch (n.op) {
+        case ZANT_OP_CONV: {
+            ZB_TRY(need_inputs(n, 2, 3, "Conv"));
+            const int x = n.in[0], w = n.in[1], b = opt_in(n, 2), y = n.out[0];
+            ZB_TRY(want_dtype(pl, x, ZANT_F32, "Conv")); ZB_TRY(want_dtype(pl, w, ZANT_F32, "Conv")); ZB_TRY(want_dtype(pl, y, ZANT_F32, "Conv"));
+            ConvGeom g;
+            const char* ap = (a.auto_pad >= 0 && a.auto_pad <= 3) ? kAutoPadNames[a.auto_pad] : nullptr;
+            ZB_TRY(conv_resolve_ref(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(),
+                                    T(y).shape.data(), T(y).shape.size(), a.strides, a.n_strides,
+                                    a.n_pads ? a.pads : nullptr, a.n_pads, a.n_dilations ? a.dilations : nullptr, a.n_dilations,
+                                    a.group, ap, ap ? std::strlen(ap) : 0, g));
+            if (b >= 0 && numel(T(b).shape.data(), T(b).shape.size()) != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "Conv bias size");
+            push("Conv", [=]() { return run_conv_f32(ctx, g, pl->p<float>(x), pl->p<float>(w), pl->p<float>(b), pl->p<float>(y)); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_MATMUL: {
+            ZB_TRY(need_inputs(n, 2, 2, "MatMul"));
+            const int x = n.in[0], w = n.in[1], y = n.out[0];
+            MatGeom g;
+            ZB_TRY(matmul_check(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(), T(y).shape.data(), T(y).shape.size(), g));
+            push("MatMul", [=]() { return run_matmul_f32(ctx, g, pl->p<float>(x), pl->p<float>(w), pl->p<float>(y)); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_GEMM: {
+            ZB_TRY(need_inputs(n, 2, 3, "Gemm"));
+            const int x = n.in[0], w = n.in[1], c = opt_in(n, 2), y = n.out[0];
+            GemmGeom g;
+            ZB_TRY(gemm_check(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(),
+                              c >= 0 ? T(c).shape.data() : nullptr, c >= 0 ? T(c).shape.size() : 0, c >= 0,
+                              a.trans_a != 0, a.trans_b != 0, a.beta, T(y).shape.data(), T(y).shape.size(), g));
+            const float alpha = a.alpha, beta = a.beta; const bool ta = a.trans_a != 0, tb = a.trans_b != 0;
+            push("Gemm", [=]() { return run_gemm_f32(ctx, g, pl->p<float>(x), pl->p<float>(w), pl->p<float>(c), alpha, beta, ta, tb, pl->p<float>(y)); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_MAXPOOL: {
+            ZB_TRY(need_inputs(n, 1, 1, "MaxPool"));
+            const int x = n.in[0], y = n.out[0];
+            PoolGeom g;
+            const size_t ones[2] = {1, 1};
+            ZB_TRY(pool_resolve(T(x).shape.data(), T(x).shape.size(), T(y).shape.data(), T(y).shape.size(), a.kernel_shape, 2,
+                                a.n_strides ? a.strides : ones, 2, a.n_dilations ? a.dilations : ones, 2, a.pads, a.n_pads, a.auto_pad < 0 ? 0 : a.auto_pad, g));
+            const int32_t dt = T(x).dtype;
+            if (dt != T(y).dtype) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "MaxPool dtype mismatch");
+            if (dt == ZANT_F32) push("MaxPool", [=]() { return run_maxpool<float>(ctx, g, pl->p<float>(x), pl->p<float>(y)); });
+            else if (dt == ZANT_I8) push("MaxPool", [=]() { return run_maxpool<int8_t>(ctx, g, pl->p<int8_t>(x), pl->p<int8_t>(y)); });
+            else if (dt == ZANT_U8) push("MaxPool", [=]() { return run_maxpool<uint8_t>(ctx, g, pl->p<uint8_t>(x), pl->p<uint8_t>(y)); });
+            else return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "MaxPool on int32");
+            return ZANT_OK;
+        }
+        case ZANT_OP_RELU:
+        case ZANT_OP_LEAKY_RELU:
+        case ZANT_OP_CLIP: {
+            ZB_TRY(need_inputs(n, 1, 1, "activation"));
+            const int x = n.in[0], y = n.out[0];
+            const size_t cnt = numel(T(x).shape.data(), T(x).shape.size());
+            if (cnt != numel(T(y).shape.data(), T(y).shape.size())) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "activation sizes differ");
+            const int32_t dt = T(x).dtype;
+            if (dt != T(y).dtype) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "activation dtype mismatch");
+            const float p0 = a.alpha, p1 = a.beta;
+            if (dt == ZANT_F32) {
+                if (n.op == ZANT_OP_RELU) push("Relu", [=]() { return run_unary_f32(ctx, pl->p<float>(x), pl->p<float>(y), cnt, ReluOp{}, "relu_f32"); });
+                else if (n.op == ZANT_OP_LEAKY_RELU) push("LeakyRelu", [=]() { return run_unary_f32(ctx, pl->p<float>(x), pl->p<float>(y), cnt, LeakyOp{p0}, "leaky_relu_f32"); });
+                else push("Clip", [=]() { return run_unary_f32(ctx, pl->p<float>(x), pl->p<float>(y), cnt, ClipOp{p0, p1}, "clip_f32"); });
+                return ZANT_OK;
+            }
+            if (dt == ZANT_I32) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "activation on int32");
+            // Quantized tensors: dequantise, activate, requantise through a 256-entry table.
+            uint8_t lut[256];
+            if (n.op == ZANT_OP_RELU) build_unary_lut(dt, a.x_scale, a.x_zp, a.y_scale, a.y_zp, [](float v) { return v > 0.0f ? v : 0.0f; }, lut);
+            else if (n.op == ZANT_OP_LEAKY_RELU) build_unary_lut(dt, a.x_scale, a.x_zp, a.y_scale, a.y_zp, [p0](float v) { volatile float s = p0 * v; return v <= 0.0f ? (float)s : v; }, lut);
+            else build_unary_lut(dt, a.x_scale, a.x_zp, a.y_scale, a.y_zp, [p0, p1](float v) { return std::fmin(std::fmax(v, p0), p1); }, lut);
+            const int aux = pl->add_aux(lut, 256);
+            push("ActivationLut", [=]() { return run_lut(ctx, pl->p<char>(x), pl->p<char>(y), cnt, (const uint8_t*)pl->aux(aux)); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_ADD: {
+            ZB_TRY(need_inputs(n, 2, 2, "Add"));
+            const int x = n.in[0], w = n.in[1], y = n.out[0];
+            ZB_TRY(want_dtype(pl, x, ZANT_F32, "Add")); ZB_TRY(want_dtype(pl, w, ZANT_F32, "Add")); ZB_TRY(want_dtype(pl, y, ZANT_F32, "Add"));
+            BcastGeom g;
+            ZB_TRY(bcast_resolve(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(), T(y).shape.data(), T(y).shape.size(), g));
+            push("Add", [=]() { return run_add_f32(ctx, g, pl->p<float>(x), pl->p<float>(w), pl->p<float>(y)); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_CONCAT: {
+            if (n.in.empty() || n.out.size() != 1) return fail(ZANT_E_EMPTY_TENSOR_LIST, "Concat needs inputs and one output");
+            const int y = n.out[0];
+            std::vector<const size_t*> shapes; std::vector<size_t> ranks;
+            for (int id : n.in) {
+                if (id < 0) return fail(ZANT_E_INVALID_INPUT, "Concat input missing");
+                if (T(id).dtype != T(y).dtype) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "Concat dtype mismatch");
+                shapes.push_back(T(id).shape.data()); ranks.push_back(T(id).shape.size());
+            }
+            ConcatGeom g; size_t os[8];
+            ZB_TRY(concat_resolve(shapes.data(), ranks.data(), n.in.size(), a.axis, os, g));
+            if (T(y).shape.size() != g.rank) return fail(ZANT_E_MISMATCHED_RANK, "Concat output rank");
+            for (size_t d = 0; d < g.rank; ++d) if (T(y).shape[d] != os[d]) return fail(ZANT_E_MISMATCHED_SHAPE, "Concat output dim %zu", d);
+            const size_t esz = dtype_size(T(y).dtype);
+            const std::vector<int> ins = n.in;
+            push("Concat", [=]() {
+                std::vector<const void*> ptrs(ins.size());
+                for (size_t i = 0; i < ins.size(); ++i) ptrs[i] = pl->ptr(ins[i]);
+                return run_concat(ctx, g, esz, ptrs.data(), pl->ptr(y));
+            });
+            return ZANT_OK;
+        }
+        case ZANT_OP_RESIZE: {
+            ZB_TRY(need_inputs(n, 1, 1, "Resize"));
+            const int x = n.in[0], y = n.out[0];
+            const size_t r = T(x).shape.size();
+            if (r == 0 || r > 4 || a.n_scales != r) return fail(ZANT_E_INVALID_INPUT, "Resize scales length != rank");
+            if (T(x).dtype != T(y).dtype) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "Resize dtype mismatch");
+            std::vector<size_t> os(r);
+            ZB_TRY(resize_output_shape(T(x).shape.data(), r, a.scales, a.n_scales, nullptr, 0, os.data()));
+            if (T(y).shape != os) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "Resize output shape");
+            std::vector<int32_t> table, axis_offset;
+            resize_index_table(T(x).shape.data(), os.data(), r, a.coord_mode, table, axis_offset);
+            const int aux = pl->add_aux(table.data(), table.size() * 4);
+            const std::vector<size_t> xs = T(x).shape;
+            const size_t esz = dtype_size(T(x).dtype);
+            push("Resize", [=]() { return run_resize(ctx, esz, pl->ptr(x), pl->ptr(y), (const int32_t*)pl->aux(aux), xs.data(), os.data(), r, axis_offset); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_REDUCE_MEAN: {
+            ZB_TRY(need_inputs(n, 1, 1, "ReduceMean"));
+            const int x = n.in[0], y = n.out[0];
+            ZB_TRY(want_dtype(pl, x, ZANT_F32, "ReduceMean")); ZB_TRY(want_dtype(pl, y, ZANT_F32, "ReduceMean"));
+            ReduceGeom g;
+            ZB_TRY(reduce_resolve(T(x).shape.data(), T(x).shape.size(), T(y).shape.data(), T(y).shape.size(), a.n_axes ? a.axes : nullptr, a.n_axes, a.noop_with_empty_axes != 0, g));
+            push("ReduceMean", [=]() { return run_reduce_mean_f32(ctx, g, pl->p<float>(x), pl->p<float>(y)); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_RESHAPE: {
+            ZB_TRY(need_inputs(n, 1, 1, "Reshape"));
+            const int x = n.in[0], y = n.out[0];
+            if (T(x).dtype != T(y).dtype) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "Reshape dtype mismatch");
+            if (numel(T(x).shape.data(), T(x).shape.size()) != numel(T(y).shape.data(), T(y).shape.size()))
+                return fail(ZANT_E_INPUT_ARRAY_WRONG_SIZE, "Reshape changes the element count");
+            // Row-major order is preserved, so the output is a view: no kernel, no copy.
+            pl->t[y].alias = x;
+            return ZANT_OK;
+        }
+        case ZANT_OP_QUANTIZE_LINEAR: {
+            ZB_TRY(need_inputs(n, 1, 1, "QuantizeLinear"));
+            const int x = n.in[0], y = n.out[0];
+            ZB_TRY(want_dtype(pl, x, ZANT_F32, "QuantizeLinear"));
+            const int32_t dt = T(y).dtype;
+            if (dt != ZANT_I8 && dt != ZANT_U8) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QuantizeLinear output dtype");
+            const size_t cnt = numel(T(x).shape.data(), T(x).shape.size());
+            if (cnt != numel(T(y).shape.data(), T(y).shape.size())) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "QuantizeLinear sizes differ");
+            const float sc = a.y_scale; const int zp = a.y_zp;
+            push("QuantizeLinear", [=]() { return run_quantize(ctx, pl->p<float>(x), pl->ptr(y), cnt, sc, zp, dt); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_DEQUANTIZE_LINEAR: {
+            ZB_TRY(need_inputs(n, 1, 1, "DequantizeLinear"));
+            const int x = n.in[0], y = n.out[0];
+            ZB_TRY(want_dtype(pl, y, ZANT_F32, "DequantizeLinear"));
+            const int32_t dt = T(x).dtype;
+            if (dt == ZANT_F32) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "DequantizeLinear input dtype");
+            const size_t cnt = numel(T(x).shape.data(), T(x).shape.size());
+            if (cnt != numel(T(y).shape.data(), T(y).shape.size())) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "DequantizeLinear sizes differ");
+            const float sc = a.x_scale; const int zp = a.x_zp;
+            push("DequantizeLinear", [=]() { return run_dequantize(ctx, dt, pl->ptr(x), pl->p<float>(y), cnt, sc, zp); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_QLINEAR_CONV: {
+            ZB_TRY(need_inputs(n, 3, 5, "QLinearConv"));
+            const int x = n.in[0], w = n.in[1], ws = n.in[2], wz = opt_in(n, 3), b = opt_in(n, 4), y = n.out[0];
+            if (x < 0 || w < 0 || ws < 0) return fail(ZANT_E_INVALID_INPUT, "QLinearConv needs x, w, w_scale");
+            ZB_TRY(want_dtype(pl, w, ZANT_I8, "QLinearConv w")); ZB_TRY(want_dtype(pl, ws, ZANT_F32, "QLinearConv w_scale"));
+            ZB_TRY(want_dtype(pl, wz, ZANT_I32, "QLinearConv w_zp")); ZB_TRY(want_dtype(pl, b, ZANT_I32, "QLinearConv bias"));
+            const int32_t xd = T(x).dtype, yd = T(y).dtype;
+            if ((xd != ZANT_I8 && xd != ZANT_U8) || (yd != ZANT_I8 && yd != ZANT_U8)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearConv x/y dtype");
+            if (!T(w).is_const || !T(ws).is_const || (wz >= 0 && !T(wz).is_const)) return fail(ZANT_E_UNSUPPORTED, "QLinearConv weights and scales must be initializers");
+            ConvGeom g;
+            ZB_TRY(conv_resolve_onnx(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(), T(y).shape.data(), T(y).shape.size(),
+                                     a.strides, a.n_strides, a.pads, a.n_pads, a.dilations, a.n_dilations, a.group, a.auto_pad < 0 ? 0 : a.auto_pad, g));
+            const size_t nws = numel(T(ws).shape.data(), T(ws).shape.size());
+            if (nws != 1 && nws != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv w_scale size");
+            if (b >= 0 && numel(T(b).shape.data(), T(b).shape.size()) != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv bias size");
+            std::vector<float> mult;
+            requant_multipliers(a.x_scale, (const float*)T(ws).host.data(), nws, a.y_scale, (size_t)g.M, mult);
+            std::vector<int32_t> wzv((size_t)g.M, 0);
+            if (wz >= 0) {
+                const size_t nwz = numel(T(wz).shape.data(), T(wz).shape.size());
+                if (nwz != 1 && nwz != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv w_zp size");
+                for (int m = 0; m < g.M; ++m) wzv[m] = ((const int32_t*)T(wz).host.data())[nwz == 1 ? 0 : m];
+            }
+            const int am = pl->add_aux(mult.data(), mult.size() * 4), az = pl->add_aux(wzv.data(), wzv.size() * 4);
+            const int xzp = a.x_zp; const Requant rq{a.y_scale, a.y_zp, a.activation};
+            push("QLinearConv", [=]() {
+                QConvArgs q{};
+                q.x = pl->ptr(x); q.w = pl->p<int8_t>(w); q.y = pl->ptr(y);
+                q.mult = (const float*)pl->aux(am); q.w_zp = (const int32_t*)pl->aux(az); q.bias = pl->p<int32_t>(b);
+                q.x_zp = xzp; q.rq = rq; q.g = g;
+                return run_qconv_generic(ctx, q, xd, yd);
+            });
+            return ZANT_OK;
+        }
+        case ZANT_OP_QLINEAR_MATMUL: {
+            ZB_TRY(need_inputs(n, 3, 5, "QLinearMatMul"));
+            const int x = n.in[0], w = n.in[1], ws = n.in[2], wz = opt_in(n, 3), b = opt_in(n, 4), y = n.out[0];
+            if (x < 0 || w < 0 || ws < 0) return fail(ZANT_E_INVALID_INPUT, "QLinearMatMul needs a, b, b_scale");
+            ZB_TRY(want_dtype(pl, w, ZANT_I8, "QLinearMatMul b")); ZB_TRY(want_dtype(pl, ws, ZANT_F32, "QLinearMatMul b_scale"));
+            ZB_TRY(want_dtype(pl, wz, ZANT_I32, "QLinearMatMul b_zp")); ZB_TRY(want_dtype(pl, b, ZANT_I32, "QLinearMatMul bias"));
+            const int32_t xd = T(x).dtype, yd = T(y).dtype;
+            if (xd != ZANT_I8 && xd != ZANT_U8) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearMatMul a dtype");
+            if (yd == ZANT_F32) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearMatMul y dtype");
+            if (!T(w).is_const || !T(ws).is_const || (wz >= 0 && !T(wz).is_const)) return fail(ZANT_E_UNSUPPORTED, "QLinearMatMul weights and scales must be initializers");
+            if (T(x).shape.size() != 2 || T(w).shape.size() != 2 || T(y).shape.size() != 2) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearMatMul takes 2-D operands");
+            const size_t M = T(x).shape[0], K = T(x).shape[1], N = T(w).shape[1];
+            if (T(w).shape[0] != K || M * N == 0 || K == 0) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearMatMul inner dims");
+            if (T(y).shape[0] != M || T(y).shape[1] != N) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "QLinearMatMul output shape");
+            const size_t nws = numel(T(ws).shape.data(), T(ws).shape.size());
+            if (nws != 1 && nws != N) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearMatMul b_scale size");
+            if (b >= 0 && numel(T(b).shape.data(), T(b).shape.size()) != N) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearMatMul bias size");
+            std::vector<float> mult;
+            requant_multipliers(a.x_scale, (const float*)T(ws).host.data(), nws, a.y_scale, N, mult);
+            std::vector<int32_t> bz(N, 0);
+            if (wz >= 0) {
+                const size_t nwz = numel(T(wz).shape.data(), T(wz).shape.size());
+                if (nwz != 1 && nwz != N) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearMatMul b_zp size");
+                for (size_t j = 0; j < N; ++j) bz[j] = ((const int32_t*)T(wz).host.data())[nwz == 1 ? 0 : j];
+            }
+            const int am = pl->add_aux(mult.data(), mult.size() * 4), az = pl->add_aux(bz.data(), bz.size() * 4);
+            const int xzp = a.x_zp; const Requant rq{a.y_scale, a.y_zp, a.activation};
+            push("QLinearMatMul", [=]() {
+                QMatArgs q{};
+                q.a = pl->ptr(x); q.b = pl->p<int8_t>(w); q.y = pl->ptr(y);
+                q.mult = (const float*)pl->aux(am); q.b_zp = (const int32_t*)pl->aux(az); q.bias = pl->p<int32_t>(b);
+                q.a_zp = xzp; q.rq = rq; q.M = (int)M; q.N = (int)N; q.K = (int)K; q.y_i32 = yd == ZANT_I32;
+                return run_qmatmul_generic(ctx, q, xd, yd);
+            });
+            return ZANT_OK;
+        }
+        case ZANT_OP_QLINEAR_ADD: {
+            ZB_TRY(need_inputs(n, 2, 2, "QLinearAdd"));
+            const int x = n.in[0], w = n.in[1], y = n.out[0];
+            const int32_t dt = T(x).dtype;
+            if ((dt != ZANT_I8 && dt != ZANT_U8) || T(w).dtype != dt || T(y).dtype != dt) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearAdd dtypes");
+            const size_t cnt = numel(T(x).shape.data(), T(x).shape.size());
+            if (cnt != numel(T(w).shape.data(), T(w).shape.size()) || cnt != numel(T(y).shape.data(), T(y).shape.size()))
+                return fail(ZANT_E_INPUT_TENSOR_DIFFERENT_SIZE, "QLinearAdd sizes differ");
+            const zant_node_attrs aa = a;
+            push("QLinearAdd", [=]() { return run_qadd(ctx, dt, pl->ptr(x), aa.x_scale, aa.x_zp, pl->ptr(w), aa.b_scale, aa.b_zp, aa.y_scale, aa.y_zp, aa.activation, pl->ptr(y), cnt); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_QLINEAR_GLOBAL_AVGPOOL: {
+            ZB_TRY(need_inputs(n, 1, 1, "QLinearGlobalAveragePool"));
+            const int x = n.in[0], y = n.out[0];
+            const int32_t dt = T(x).dtype;
+            if ((dt != ZANT_I8 && dt != ZANT_U8) || T(y).dtype != dt) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearGlobalAveragePool dtypes");
+            if (T(x).shape.size() != 4) return fail(ZANT_E_INVALID_DIMENSIONS, "QLinearGlobalAveragePool needs a 4-D input");
+            const size_t planes = T(x).shape[0] * T(x).shape[1], hw = T(x).shape[2] * T(x).shape[3];
+            if (numel(T(y).shape.data(), T(y).shape.size()) != planes || hw == 0) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "QLinearGlobalAveragePool output size");
+            const zant_node_attrs aa = a;
+            push("QLinearGlobalAveragePool", [=]() { return run_qgap(ctx, dt, pl->ptr(x), pl->ptr(y), planes, (int)hw, aa.x_scale, aa.x_zp, aa.y_scale, aa.y_zp); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_LUT_Q8: {
+            ZB_TRY(need_inputs(n, 2, 2, "LutQ8"));
+            const int x = n.in[0], l = n.in[1], y = n.out[0];
+            if (T(l).bytes != 256) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "table must hold 256 bytes");
+            const size_t cnt = T(x).bytes;
+            if (dtype_size(T(x).dtype) != 1 || T(y).bytes != cnt) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "LutQ8 works on 8-bit tensors of equal size");
+            push("LutQ8", [=]() { return run_lut(ctx, pl->ptr(x), pl->ptr(y), cnt, pl->p<uint8_t>(l)); });
+            return ZANT_OK;
+        }
+        default:
+            return fail(ZANT_E_UNSUPPORTED, "operator %d is not supported", n.op);
+    }
+}
+
+// --------------------------------------------------------------------------------------------
+// Fusion: recognises chains starting at `node_index` and replaces them by one fused step.
+// `consumed` = number of nodes covered (0 = no pattern matched; the caller builds the node alone).
+// --------------------------------------------------------------------------------------------
+static int32_t try_fuse(zant_plan* /*pl*/, size_t /*node_index*/, size_t& consumed) {
+    consumed = 0;
+    return ZANT_OK;
+}
