@@ -97,8 +97,7 @@ void* zant_b200_ctx_stream(zant_ctx* ctx) { return ctx ? (void*)ctx->stream : nu
 
 int32_t zant_b200_ctx_synchronize(zant_ctx* ctx) {
     ZB_NEED_CTX(ctx);
-    ZB_CUDA(cudaStreamSynchronize(ctx->stream));
-    return ZANT_OK;
+    return drain_and_check_status(ctx);
 }
 
 uint64_t zant_b200_ctx_launch_count(zant_ctx* ctx) { return ctx ? ctx->launches : 0; }

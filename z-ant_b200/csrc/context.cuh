@@ -35,6 +35,19 @@ inline int32_t check_launch(zant_ctx* ctx, const char* what) {
     return ZANT_OK;
 }
 
+// Drains the stream and reads the device status word that kernels with bounded waits write when
+// they give up; a non-zero value is reported once and cleared.
+inline int32_t drain_and_check_status(zant_ctx* ctx) {
+    int h = 0;
+    ZB_CUDA(cudaMemcpyAsync(&h, ctx->status_word, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    ZB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (h != 0) {
+        ZB_CUDA(cudaMemsetAsync(ctx->status_word, 0, sizeof(int), ctx->stream));
+        return fail(ZANT_E_DEVICE_TIMEOUT, "a kernel gave up a bounded wait (device error %d)", h);
+    }
+    return ZANT_OK;
+}
+
 inline bool is_device_ptr(const void* p) {
     if (!p) return false;
     cudaPointerAttributes a;

@@ -1,0 +1,307 @@
+// Fused kernels for quantized 3x3 convolution stages followed by ReLU and a 2x2/2 MaxPool.
+//
+// Internal activation layout "C16 planar": [image][C/16][H*W positions][16 channels] int8, i.e.
+// every pixel of a 16-channel group is one 16-byte chunk and consecutive pixels are consecutive
+// chunks.  With that layout the A operand of an implicit-GEMM convolution needs no im2col at all:
+// for filter tap (kh,kw) the rows of A are the SAME chunks shifted by (kh*W + kw) positions, so the
+// tcgen05 shared-memory descriptor (K-major, no swizzle: 8 rows = 8 consecutive 16-byte chunks)
+// simply starts (kh*W + kw)*16 bytes further.  One bulk async copy brings an image into shared
+// memory once; nine (taps) x C/32 MMAs read it in place.
+//
+// MaxPool is applied to the int32 accumulators BEFORE requantisation.  That is exact because the
+// requantisation y = sat(rne(float(acc + bias) * M) + zp) is non-decreasing in acc whenever M > 0
+// (checked on the host), so max and requantise commute.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "kernels_q8.cuh"
+#include "ptx_sm100.cuh"
+
+namespace zb {
+
+enum DeviceError : int {
+    DEV_OK = 0,
+    DEV_ERR_WAIT_TIMEOUT = 1,   // a bounded mbarrier wait gave up
+};
+
+// =============================================================================================
+// Stage 1: QuantizeLinear(uint8) + QLinearConv(1 -> 32, 3x3, stride 1, no pad) + ReLU + MaxPool 2x2/2
+//          float [N,1,28,28]  ->  int8 C16-planar [N][2][13*13][16]
+// CUDA cores: the contraction is only 9 deep, too shallow for a 32-byte MMA K step.  Each thread
+// owns one pooled pixel: it holds the 4x4 input patch as four packed words and evaluates the four
+// conv windows of all 32 channels with dp4a against weights packed in the kernel parameters
+// (constant bank), three dp4a per window.
+// =============================================================================================
+struct Conv1Args {
+    const float* x;
+    int8_t* y;
+    int n_images;
+    float x_scale; int x_zp;            // QuantizeLinear of the input (uint8)
+    uint32_t wpack[32][3][2];           // [m][kh][dx]: dx=0 -> bytes (w0,w1,w2,0); dx=1 -> (0,w0,w1,w2)
+    float mult[32];                     // (x_scale * w_scale[m]) / y_scale
+    int32_t bias[32];                   // bias[m] - x_zp * sum(w[m])   (no padding: all 9 taps always valid)
+    float y_scale; int y_zp; int act;
+};
+
+__device__ __forceinline__ int dp4a_us(uint32_t a_u8x4, uint32_t b_s8x4, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_u8x4), "r"(b_s8x4), "r"(c));
+    return d;
+}
+
+constexpr int C1_G = 3;          // images per CTA iteration: 3*169 = 507 pooled pixels for 256 threads
+constexpr int C1_THREADS = 256;
+
+__global__ void __launch_bounds__(C1_THREADS) conv1_quant_relu_pool_kernel(const __grid_constant__ Conv1Args a) {
+    __shared__ uint32_t img[C1_G][28][8];   // rows of 32 bytes (28 pixels + 4 pad)
+    const int tid = threadIdx.x;
+    const Requant rq{a.y_scale, a.y_zp, a.act};
+    for (int base = blockIdx.x * C1_G; base < a.n_images; base += gridDim.x * C1_G) {
+        for (int i = tid; i < C1_G * 784; i += C1_THREADS) {
+            const int g = i / 784, p = i - g * 784;
+            int q = 0;
+            if (base + g < a.n_images) {
+                const float v = __ldg(a.x + (size_t)(base + g) * 784 + p);
+                q = sat_q<true>(rne_clamped(__fdiv_rn(v, a.x_scale)) + a.x_zp);
+            }
+            const int r = p / 28, c = p - r * 28;
+            reinterpret_cast<uint8_t*>(&img[g][r][0])[c] = (uint8_t)q;
+        }
+        __syncthreads();
+        for (int i = tid; i < C1_G * 169; i += C1_THREADS) {
+            const int g = i / 169, pp = i - g * 169;
+            if (base + g >= a.n_images) continue;
+            const int py = pp / 13, px = pp - py * 13;
+            uint32_t X[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const uint32_t* row = &img[g][2 * py + r][0];
+                const uint32_t w0 = row[px >> 1];
+                X[r] = (px & 1) ? __byte_perm(w0, row[(px >> 1) + 1], 0x5432) : w0;
+            }
+            uint32_t out[8];
+#pragma unroll
+            for (int m = 0; m < 32; ++m) {
+                const int a00 = dp4a_us(X[0], a.wpack[m][0][0], dp4a_us(X[1], a.wpack[m][1][0], dp4a_us(X[2], a.wpack[m][2][0], 0)));
+                const int a01 = dp4a_us(X[0], a.wpack[m][0][1], dp4a_us(X[1], a.wpack[m][1][1], dp4a_us(X[2], a.wpack[m][2][1], 0)));
+                const int a10 = dp4a_us(X[1], a.wpack[m][0][0], dp4a_us(X[2], a.wpack[m][1][0], dp4a_us(X[3], a.wpack[m][2][0], 0)));
+                const int a11 = dp4a_us(X[1], a.wpack[m][0][1], dp4a_us(X[2], a.wpack[m][1][1], dp4a_us(X[3], a.wpack[m][2][1], 0)));
+                const int mx = max(max(a00, a01), max(a10, a11)) + a.bias[m];
+                const int t = requant_one<false>(mx, a.mult[m], rq);
+                if ((m & 3) == 0) out[m >> 2] = (uint32_t)(t & 255);
+                else out[m >> 2] |= (uint32_t)(t & 255) << (8 * (m & 3));
+            }
+            int8_t* yo = a.y + ((size_t)(base + g) * 2 * 169 + pp) * 16;
+            *reinterpret_cast<uint4*>(yo) = make_uint4(out[0], out[1], out[2], out[3]);
+            *reinterpret_cast<uint4*>(yo + 169 * 16) = make_uint4(out[4], out[5], out[6], out[7]);
+        }
+        __syncthreads();
+    }
+}
+
+// =============================================================================================
+// Stage 2: QLinearConv(32 -> COUT, 3x3, stride 1, no pad) + ReLU + MaxPool 2x2/2 on tcgen05.
+//   input  int8 C16-planar [N][2][IH*IW][16]
+//   output int8, either row-major [N][PH*PW*COUT] in (h,w,c) order, or blocked for a following
+//          GEMM: [N/128][K/16][128 images][16]  (K = PH*PW*COUT)
+// One image per tile: the 128 MMA rows are the positions p = oh*IW + ow (0..127) of the input
+// grid, which cover every conv output that the 2x2 pool keeps.  Persistent CTAs, warp roles:
+//   warp 0   bulk-copy producer (one elected lane), STAGES-deep ring of images
+//   warp 1   TMEM owner + MMA issuer (one elected lane): 9 MMAs (K=32) per image into one of two
+//            TMEM accumulators
+//   warps 2-5  epilogue: TMEM -> registers -> shared staging (int32), 2x2 max, bias, requantise,
+//            ReLU, store
+// =============================================================================================
+struct TcConvPoolArgs {
+    const int8_t* x;
+    const int8_t* w;        // [9 taps][2 chunks][COUT][16] int8
+    const float* mult;      // [COUT]
+    const int32_t* bias;    // [COUT]  (already includes -x_zp * sum(w))
+    int8_t* y;
+    int n_images;
+    float y_scale; int y_zp; int act;
+    int out_blocked;        // 0 row-major, 1 GEMM-blocked
+    int* status;
+};
+
+template <int IH, int IW, int COUT>
+struct TcConvPoolCfg {
+    static constexpr int P = IH * IW;
+    static constexpr int PH = (IH - 2) / 2, PW = (IW - 2) / 2;
+    static constexpr int IMG_BYTES = 2 * P * 16;
+    static constexpr int STAGE_BYTES = (IMG_BYTES + 127) / 128 * 128;
+    static constexpr int STAGES = 4;
+    static constexpr int W_TAP_BYTES = 2 * COUT * 16;
+    static constexpr int W_BYTES = 9 * W_TAP_BYTES;
+    static constexpr int STG_ROW = COUT * 4 + 16;            // +16: rows land on distinct bank groups
+    static constexpr int STG_BYTES = 128 * STG_ROW;
+    static constexpr int OFF_W = 0;
+    static constexpr int OFF_A = OFF_W + W_BYTES;
+    static constexpr int OFF_STG = OFF_A + STAGES * STAGE_BYTES;
+    static constexpr int OFF_BAR = OFF_STG + STG_BYTES;
+    static constexpr int SMEM_BYTES = OFF_BAR + 256;
+    static constexpr int TMEM_COLS = 2 * COUT >= 32 ? 2 * COUT : 32;
+    static constexpr int KOUT = PH * PW * COUT;
+    static constexpr int THREADS = 192;
+    // every position the pool keeps must be one of the 128 MMA rows, and every shifted read must
+    // stay inside the image's planes
+    static_assert((2 * PH - 1) * IW + (2 * PW - 1) < 128, "pooled window exceeds one 128-row tile");
+    static_assert(127 + 2 * IW + 2 < 2 * P, "shifted A rows would leave the staged image");
+    static_assert(COUT % 32 == 0 && COUT <= 256, "COUT must be a multiple of 32 up to 256");
+    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
+    static_assert(128 % (COUT / 4) == 0, "channel quad of an epilogue thread must be loop invariant");
+};
+
+template <int IH, int IW, int COUT>
+__global__ void __launch_bounds__(192, 1) tc_conv3x3_relu_pool_kernel(const __grid_constant__ TcConvPoolArgs a) {
+    using Cfg = TcConvPoolCfg<IH, IW, COUT>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sW = smem + Cfg::OFF_W;
+    uint8_t* sA = smem + Cfg::OFF_A;
+    uint8_t* sStg = smem + Cfg::OFF_STG;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+    // barrier slots: full[STAGES], empty[STAGES], tfull[2], tempty[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 132);
+    volatile int* epi_ok = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 136);
+    const uint32_t bar0 = ptx::smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (Cfg::STAGES + s); };
+    auto tfull = [&](int b) { return bar0 + 8u * (2 * Cfg::STAGES + b); };
+    auto tempty = [&](int b) { return bar0 + 8u * (2 * Cfg::STAGES + 2 + b); };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) { ptx::mbar_init(full(s), 1); ptx::mbar_init(empty(s), 1); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 4); }
+        *abort_flag = 0;
+        *epi_ok = 1;
+        ptx::mbar_fence_init();
+    }
+    for (int i = tid; i < Cfg::W_BYTES / 16; i += Cfg::THREADS)
+        reinterpret_cast<uint4*>(sW)[i] = __ldg(reinterpret_cast<const uint4*>(a.w) + i);
+    ptx::fence_proxy_async_smem();
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), Cfg::TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (ptx::elect_one()) {
+            int it = 0;
+            for (int img = blockIdx.x; img < a.n_images; img += gridDim.x, ++it) {
+                const int s = it % Cfg::STAGES;
+                const uint32_t ph = (uint32_t)(it / Cfg::STAGES) & 1u;
+                if (!ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag)) break;
+                ptx::mbar_arrive_expect_tx(full(s), Cfg::IMG_BYTES);
+                ptx::bulk_g2s(ptx::smem_u32(sA + s * Cfg::STAGE_BYTES), a.x + (size_t)img * Cfg::IMG_BYTES, Cfg::IMG_BYTES, full(s));
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::idesc_i8(128, COUT, true, true);
+            const uint32_t w_addr = ptx::smem_u32(sW);
+            int it = 0;
+            for (int img = blockIdx.x; img < a.n_images; img += gridDim.x, ++it) {
+                const int s = it % Cfg::STAGES;
+                const uint32_t ph = (uint32_t)(it / Cfg::STAGES) & 1u;
+                const int b = it & 1;
+                const uint32_t bph = (uint32_t)(it >> 1) & 1u;
+                if (!ptx::mbar_wait(tempty(b), bph ^ 1u, abort_flag)) break;
+                if (!ptx::mbar_wait(full(s), ph, abort_flag)) break;
+                ptx::tc_fence_after();
+                const uint32_t a_addr = ptx::smem_u32(sA + s * Cfg::STAGE_BYTES);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * COUT);
+#pragma unroll
+                for (int tap = 0; tap < 9; ++tap) {
+                    const int kh = tap / 3, kw = tap - kh * 3;
+                    const uint64_t da = ptx::smem_desc_kmajor(a_addr + (uint32_t)((kh * IW + kw) * 16), Cfg::P * 16, 128);
+                    const uint64_t db = ptx::smem_desc_kmajor(w_addr + (uint32_t)(tap * Cfg::W_TAP_BYTES), COUT * 16, 128);
+                    ptx::mma_i8(d_tmem, da, db, idesc, tap > 0);
+                }
+                ptx::mma_commit(empty(s));    // the image's smem stage is free once these MMAs retire
+                ptx::mma_commit(tfull(b));    // ... and the accumulator is complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;               // TMEM lane quarter this warp may access
+        const int row = quarter * 32 + lane;        // MMA row = input-grid position
+        const int e = (warp - 2) * 32 + lane;       // 0..127 within the epilogue group
+        constexpr int QUADS = COUT / 4;
+        const int cq = e % QUADS;
+        float mult[4]; int bias[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { mult[j] = __ldg(a.mult + cq * 4 + j); bias[j] = __ldg(a.bias + cq * 4 + j); }
+        const Requant rq{a.y_scale, a.y_zp, a.act};
+        int it = 0;
+        for (int img = blockIdx.x; img < a.n_images; img += gridDim.x, ++it) {
+            const int b = it & 1;
+            const uint32_t bph = (uint32_t)(it >> 1) & 1u;
+            if (e == 0) *epi_ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
+            ptx::named_barrier_sync(1, 128);        // also: every thread finished reading the staging of the previous image
+            if (!*epi_ok) break;
+            ptx::tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * COUT);
+#pragma unroll
+            for (int h = 0; h < COUT / 32; ++h) {
+                uint32_t v[32];
+                ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
+                ptx::tmem_wait_ld();
+                uint4* dst = reinterpret_cast<uint4*>(sStg + row * Cfg::STG_ROW + h * 128);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) dst[k] = make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tempty(b));   // accumulator b may be overwritten
+            ptx::named_barrier_sync(1, 128);
+            for (int t = e; t < Cfg::PH * Cfg::PW * QUADS; t += 128) {
+                const int q = t / QUADS;
+                const int py = q / Cfg::PW, px = q - py * Cfg::PW;
+                const int p0 = 2 * py * IW + 2 * px;
+                const int4 r0 = *reinterpret_cast<const int4*>(sStg + p0 * Cfg::STG_ROW + cq * 16);
+                const int4 r1 = *reinterpret_cast<const int4*>(sStg + (p0 + 1) * Cfg::STG_ROW + cq * 16);
+                const int4 r2 = *reinterpret_cast<const int4*>(sStg + (p0 + IW) * Cfg::STG_ROW + cq * 16);
+                const int4 r3 = *reinterpret_cast<const int4*>(sStg + (p0 + IW + 1) * Cfg::STG_ROW + cq * 16);
+                const int m0 = max(max(r0.x, r1.x), max(r2.x, r3.x)) + bias[0];
+                const int m1 = max(max(r0.y, r1.y), max(r2.y, r3.y)) + bias[1];
+                const int m2 = max(max(r0.z, r1.z), max(r2.z, r3.z)) + bias[2];
+                const int m3 = max(max(r0.w, r1.w), max(r2.w, r3.w)) + bias[3];
+                const uint32_t packed = (uint32_t)(requant_one<false>(m0, mult[0], rq) & 255) |
+                                        ((uint32_t)(requant_one<false>(m1, mult[1], rq) & 255) << 8) |
+                                        ((uint32_t)(requant_one<false>(m2, mult[2], rq) & 255) << 16) |
+                                        ((uint32_t)(requant_one<false>(m3, mult[3], rq) & 255) << 24);
+                size_t off;
+                if (a.out_blocked) {
+                    const int chunk = q * (COUT / 16) + (cq >> 2);
+                    off = ((size_t)(img >> 7) * (Cfg::KOUT / 16) + chunk) * 2048 + (size_t)(img & 127) * 16 + (cq & 3) * 4;
+                } else {
+                    off = (size_t)img * Cfg::KOUT + q * COUT + cq * 4;
+                }
+                *reinterpret_cast<uint32_t*>(a.y + off) = packed;
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    if (*abort_flag) {
+        // give copies and MMAs that are still in flight time to land before the CTA's memory goes away
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) ptx::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (tid == 0 && *abort_flag) atomicExch(a.status, (int)DEV_ERR_WAIT_TIMEOUT);
+}
+
+}  // namespace zb

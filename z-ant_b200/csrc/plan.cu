@@ -14,6 +14,7 @@
 #include "context.cuh"
 #include "geometry.hpp"
 #include "ops.cuh"
+#include "fused_cnn.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -42,6 +43,8 @@ struct zant_plan {
     std::vector<PlanNode> nodes;
     std::vector<std::vector<char>> aux_host;   // derived constants (multipliers, tables)
     std::vector<size_t> aux_off;
+    std::vector<size_t> scratch_bytes;         // internal buffers of fused steps (private layouts)
+    std::vector<size_t> scratch_off;
     int input = -1, output = -1;
     bool finalized = false;
     char* arena = nullptr;
@@ -60,6 +63,8 @@ struct zant_plan {
     }
     template <typename T> T* p(int id) const { return id < 0 ? nullptr : reinterpret_cast<T*>(ptr(id)); }
     void* aux(int id) const { return arena + aux_off[id]; }
+    void* scratch(int id) const { return arena + scratch_off[id]; }
+    int add_scratch(size_t bytes) { scratch_bytes.push_back(bytes); return (int)scratch_bytes.size() - 1; }
     int add_aux(const void* data, size_t bytes) {
         aux_host.emplace_back((const char*)data, (const char*)data + bytes);
         return (int)aux_host.size() - 1;
@@ -207,6 +212,11 @@ int32_t zant_b200_plan_finalize(zant_plan* plan, int32_t input_id, int32_t outpu
         plan->aux_off[a] = off;
         off += align_up(plan->aux_host[a].size() ? plan->aux_host[a].size() : 1, kArenaAlign);
     }
+    plan->scratch_off.resize(plan->scratch_bytes.size());
+    for (size_t a = 0; a < plan->scratch_bytes.size(); ++a) {
+        plan->scratch_off[a] = off;
+        off += align_up(plan->scratch_bytes[a] ? plan->scratch_bytes[a] : 1, kArenaAlign);
+    }
     plan->arena_bytes = off;
     ZB_CUDA(cudaMalloc((void**)&plan->arena, off));
     for (auto& t : plan->t) {
@@ -262,7 +272,8 @@ int32_t zant_b200_plan_run(zant_plan* plan, const void* input, void* output) {
     if (plan->profiling) { int32_t st = mark(); if (st != ZANT_OK) return st; }
     if (!out_dev) {
         ZB_CUDA(cudaMemcpyAsync(output, tor.arena_ptr, to.bytes, cudaMemcpyDeviceToHost, ctx->stream));
-        ZB_CUDA(cudaStreamSynchronize(ctx->stream));
+        ti.bound = nullptr; tor.bound = nullptr;
+        return drain_and_check_status(ctx);
     }
     ti.bound = nullptr; tor.bound = nullptr;
     return ZANT_OK;
@@ -603,10 +614,240 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
 }
 
 // --------------------------------------------------------------------------------------------
-// Fusion: recognises chains starting at `node_index` and replaces them by one fused step.
-// `consumed` = number of nodes covered (0 = no pattern matched; the caller builds the node alone).
+// Fusion.  `try_fuse` looks for a known chain starting at `node_index` and, if every shape,
+// attribute and data-flow condition holds, emits fused steps and reports how many nodes they
+// cover (0 = nothing matched; the caller builds the node on its own).
+//
+// Chain recognised today (the reference's example CNN in QLinear form):
+//   QuantizeLinear(u8) -> QLinearConv(1->32,3x3) -> Relu -> MaxPool 2x2/2
+//                      -> QLinearConv(32->64,3x3) -> Relu -> MaxPool 2x2/2 -> Reshape
+//                      -> QLinearMatMul -> Relu -> QLinearMatMul -> DequantizeLinear
+// on [N,1,28,28] inputs.  Intermediate tensors of a fused chain are not materialised in their
+// graph layout: they live in private scratch buffers (C16-planar / GEMM-ordered).
 // --------------------------------------------------------------------------------------------
-static int32_t try_fuse(zant_plan* /*pl*/, size_t /*node_index*/, size_t& consumed) {
+namespace {
+
+struct ChainCtx {
+    zant_plan* pl;
+    std::vector<int> consumers;   // per tensor: number of nodes reading it
+};
+
+bool only_feeds_next(const ChainCtx& c, int tensor) {
+    return c.consumers[tensor] == 1 && tensor != c.pl->output && !c.pl->t[tensor].is_const;
+}
+
+bool shape_is(const PlanTensor& t, std::initializer_list<size_t> s) { return t.shape == std::vector<size_t>(s); }
+
+bool plain_conv3x3(const zant_node_attrs& a) {
+    auto one = [](const size_t* v, size_t n) { for (size_t i = 0; i < n; ++i) if (v[i] != 1) return false; return true; };
+    bool nopad = true;
+    for (size_t i = 0; i < a.n_pads; ++i) nopad = nopad && a.pads[i] == 0;
+    return one(a.strides, a.n_strides) && one(a.dilations, a.n_dilations) && nopad && (a.group == 0 || a.group == 1) &&
+           (a.auto_pad < 0 || a.auto_pad == ZANT_PAD_NOTSET || a.auto_pad == ZANT_PAD_VALID);
+}
+
+bool pool2x2(const zant_node_attrs& a) {
+    bool nopad = true;
+    for (size_t i = 0; i < a.n_pads; ++i) nopad = nopad && a.pads[i] == 0;
+    const bool d1 = a.n_dilations == 0 || (a.dilations[0] == 1 && a.dilations[1] == 1);
+    return a.kernel_shape[0] == 2 && a.kernel_shape[1] == 2 && a.n_strides == 2 && a.strides[0] == 2 && a.strides[1] == 2 && nopad && d1 &&
+           (a.auto_pad < 0 || a.auto_pad == ZANT_PAD_NOTSET || a.auto_pad == ZANT_PAD_VALID);
+}
+
+// A quantized Relu node that keeps scale and zero point is max(q, zp): foldable into the producer.
+bool identity_scale_relu(const PlanNode& n) {
+    return n.op == ZANT_OP_RELU && n.a.x_scale == n.a.y_scale && n.a.x_zp == n.a.y_zp;
+}
+
+bool all_zero_i32(const PlanTensor& t) {
+    const int32_t* v = (const int32_t*)t.host.data();
+    for (size_t i = 0; i < t.bytes / 4; ++i) if (v[i] != 0) return false;
+    return true;
+}
+
+bool positive_finite(const std::vector<float>& m) {
+    for (float v : m) if (!(v > 0.0f) || !std::isfinite(v)) return false;
+    return true;
+}
+
+}  // namespace
+
+static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
     consumed = 0;
+    if (i0 + 12 > pl->nodes.size()) return ZANT_OK;
+    const int kOps[12] = {ZANT_OP_QUANTIZE_LINEAR, ZANT_OP_QLINEAR_CONV, ZANT_OP_RELU, ZANT_OP_MAXPOOL, ZANT_OP_QLINEAR_CONV, ZANT_OP_RELU,
+                          ZANT_OP_MAXPOOL, ZANT_OP_RESHAPE, ZANT_OP_QLINEAR_MATMUL, ZANT_OP_RELU, ZANT_OP_QLINEAR_MATMUL, ZANT_OP_DEQUANTIZE_LINEAR};
+    for (int k = 0; k < 12; ++k) if (pl->nodes[i0 + k].op != kOps[k]) return ZANT_OK;
+    ChainCtx c{pl, std::vector<int>(pl->t.size(), 0)};
+    for (const PlanNode& n : pl->nodes) for (int id : n.in) if (id >= 0) c.consumers[id]++;
+    const PlanNode* N = &pl->nodes[i0];
+    auto T = [&](int id) -> const PlanTensor& { return pl->t[id]; };
+    // data flow: each node's first input is the previous node's only output, used nowhere else
+    for (int k = 1; k < 12; ++k) {
+        if (N[k].in.empty() || N[k - 1].out.size() != 1 || N[k].in[0] != N[k - 1].out[0]) return ZANT_OK;
+        if (!only_feeds_next(c, N[k - 1].out[0])) return ZANT_OK;
+    }
+    const int x = N[0].in[0], y = N[11].out[0];
+    if (T(x).dtype != ZANT_F32 || T(x).shape.size() != 4) return ZANT_OK;
+    const size_t B = T(x).shape[0];
+    if (B == 0 || B > 0x3fffffffULL) return ZANT_OK;
+    if (!shape_is(T(x), {B, 1, 28, 28}) || T(N[0].out[0]).dtype != ZANT_U8) return ZANT_OK;
+    // conv1
+    const PlanNode& c1 = N[1];
+    if (c1.in.size() < 3 || !plain_conv3x3(c1.a) || !shape_is(T(c1.in[1]), {32, 1, 3, 3}) || !shape_is(T(c1.out[0]), {B, 32, 26, 26})) return ZANT_OK;
+    if (T(c1.out[0]).dtype != ZANT_I8 || c1.a.activation == ZANT_QACT_RELU6) return ZANT_OK;
+    if (c1.a.x_scale != N[0].a.y_scale || c1.a.x_zp != N[0].a.y_zp) return ZANT_OK;
+    if (opt_in(c1, 3) >= 0 && !all_zero_i32(T(c1.in[3]))) return ZANT_OK;
+    if (!identity_scale_relu(N[2]) || N[2].a.x_scale != c1.a.y_scale || N[2].a.x_zp != c1.a.y_zp) return ZANT_OK;
+    if (!pool2x2(N[3].a) || !shape_is(T(N[3].out[0]), {B, 32, 13, 13})) return ZANT_OK;
+    // conv2
+    const PlanNode& c2 = N[4];
+    if (c2.in.size() < 3 || !plain_conv3x3(c2.a) || !shape_is(T(c2.in[1]), {64, 32, 3, 3}) || !shape_is(T(c2.out[0]), {B, 64, 11, 11})) return ZANT_OK;
+    if (T(c2.out[0]).dtype != ZANT_I8 || c2.a.activation == ZANT_QACT_RELU6) return ZANT_OK;
+    if (c2.a.x_scale != c1.a.y_scale || c2.a.x_zp != c1.a.y_zp) return ZANT_OK;
+    if (opt_in(c2, 3) >= 0 && !all_zero_i32(T(c2.in[3]))) return ZANT_OK;
+    if (!identity_scale_relu(N[5]) || N[5].a.x_scale != c2.a.y_scale || N[5].a.x_zp != c2.a.y_zp) return ZANT_OK;
+    if (!pool2x2(N[6].a) || !shape_is(T(N[6].out[0]), {B, 64, 5, 5})) return ZANT_OK;
+    if (!shape_is(T(N[7].out[0]), {B, 1600})) return ZANT_OK;
+    // fc1, fc2
+    const PlanNode& f1 = N[8];
+    const PlanNode& f2 = N[10];
+    if (f1.in.size() < 3 || f2.in.size() < 3) return ZANT_OK;
+    if (!shape_is(T(f1.in[1]), {1600, 512}) || !shape_is(T(f1.out[0]), {B, 512}) || T(f1.out[0]).dtype != ZANT_I8) return ZANT_OK;
+    if (f1.a.x_scale != c2.a.y_scale || f1.a.x_zp != c2.a.y_zp || f1.a.activation == ZANT_QACT_RELU6) return ZANT_OK;
+    if (opt_in(f1, 3) >= 0 && !all_zero_i32(T(f1.in[3]))) return ZANT_OK;
+    if (!identity_scale_relu(N[9]) || N[9].a.x_scale != f1.a.y_scale || N[9].a.x_zp != f1.a.y_zp) return ZANT_OK;
+    if (T(f2.in[1]).shape.size() != 2 || T(f2.in[1]).shape[0] != 512 || T(f2.out[0]).dtype != ZANT_I8) return ZANT_OK;
+    const size_t NCLS = T(f2.in[1]).shape[1];
+    if (NCLS == 0 || NCLS > 64 || !shape_is(T(f2.out[0]), {B, NCLS}) || !shape_is(T(y), {B, NCLS})) return ZANT_OK;
+    if (f2.a.x_scale != f1.a.y_scale || f2.a.x_zp != f1.a.y_zp || f2.a.activation != ZANT_QACT_NONE) return ZANT_OK;
+    if (opt_in(f2, 3) >= 0 && !all_zero_i32(T(f2.in[3]))) return ZANT_OK;
+    if (N[11].a.x_scale != f2.a.y_scale || N[11].a.x_zp != f2.a.y_zp || T(y).dtype != ZANT_F32) return ZANT_OK;
+    for (const PlanNode* q : {&c1, &c2, &f1, &f2})
+        for (size_t k = 1; k < q->in.size(); ++k)
+            if (q->in[k] >= 0 && !T(q->in[k]).is_const) return ZANT_OK;
+
+    zant_ctx* ctx = pl->ctx;
+    auto push = [&](const char* name, std::function<int32_t()> fn) { pl->steps.push_back(std::move(fn)); pl->step_names.push_back(name); };
+    auto scales_of = [&](const PlanNode& q, size_t M, std::vector<float>& mult) {
+        const PlanTensor& ws = T(q.in[2]);
+        const size_t nws = ws.bytes / 4;
+        if (ws.dtype != ZANT_F32 || (nws != 1 && nws != M)) return false;
+        requant_multipliers(q.a.x_scale, (const float*)ws.host.data(), nws, q.a.y_scale, M, mult);
+        return positive_finite(mult);
+    };
+    auto bias_of = [&](const PlanNode& q, size_t M, std::vector<int32_t>& bias) {
+        bias.assign(M, 0);
+        const int b = opt_in(q, 4);
+        if (b < 0) return true;
+        if (T(b).dtype != ZANT_I32 || T(b).bytes != M * 4) return false;
+        std::memcpy(bias.data(), T(b).host.data(), M * 4);
+        return true;
+    };
+
+    // ---- stage 1 parameters (weights travel as kernel parameters)
+    std::vector<float> m1; std::vector<int32_t> b1;
+    if (!scales_of(c1, 32, m1) || !bias_of(c1, 32, b1)) return ZANT_OK;
+    Conv1Args a1{};
+    {
+        const int8_t* w = (const int8_t*)T(c1.in[1]).host.data();
+        for (int m = 0; m < 32; ++m) {
+            int sum = 0;
+            for (int kh = 0; kh < 3; ++kh) {
+                const uint32_t w0 = (uint8_t)w[m * 9 + kh * 3 + 0], w1 = (uint8_t)w[m * 9 + kh * 3 + 1], w2 = (uint8_t)w[m * 9 + kh * 3 + 2];
+                a1.wpack[m][kh][0] = w0 | (w1 << 8) | (w2 << 16);
+                a1.wpack[m][kh][1] = (w0 << 8) | (w1 << 16) | (w2 << 24);
+                sum += w[m * 9 + kh * 3] + w[m * 9 + kh * 3 + 1] + w[m * 9 + kh * 3 + 2];
+            }
+            a1.mult[m] = m1[m];
+            a1.bias[m] = b1[m] - c1.a.x_zp * sum;
+        }
+        a1.n_images = (int)B; a1.x_scale = N[0].a.y_scale; a1.x_zp = N[0].a.y_zp;
+        a1.y_scale = c1.a.y_scale; a1.y_zp = c1.a.y_zp; a1.act = ZANT_QACT_RELU;
+    }
+    // ---- stage 2 parameters
+    std::vector<float> m2; std::vector<int32_t> b2;
+    if (!scales_of(c2, 64, m2) || !bias_of(c2, 64, b2)) return ZANT_OK;
+    std::vector<int8_t> w2arr(9 * 2 * 64 * 16);
+    {
+        const int8_t* w = (const int8_t*)T(c2.in[1]).host.data();   // [64][32][3][3]
+        for (int m = 0; m < 64; ++m) {
+            int sum = 0;
+            for (int ch = 0; ch < 32; ++ch)
+                for (int tap = 0; tap < 9; ++tap) {
+                    const int8_t v = w[(m * 32 + ch) * 9 + tap];
+                    w2arr[((tap * 2 + ch / 16) * 64 + m) * 16 + ch % 16] = v;
+                    sum += v;
+                }
+            b2[m] -= c2.a.x_zp * sum;
+        }
+    }
+    // ---- fc1: rows re-ordered from the graph's (c,h,w) flatten order to the (h,w,c) order stage 2 writes
+    std::vector<float> m3; std::vector<int32_t> b3;
+    if (!scales_of(f1, 512, m3) || !bias_of(f1, 512, b3)) return ZANT_OK;
+    std::vector<int8_t> w3p(1600 * 512);
+    {
+        const int8_t* w = (const int8_t*)T(f1.in[1]).host.data();   // [1600][512], row = c*25 + h*5 + w
+        for (int ch = 0; ch < 64; ++ch)
+            for (int hw = 0; hw < 25; ++hw)
+                std::memcpy(&w3p[(size_t)(hw * 64 + ch) * 512], &w[(size_t)(ch * 25 + hw) * 512], 512);
+    }
+    std::vector<float> m4; std::vector<int32_t> b4;
+    if (!scales_of(f2, NCLS, m4) || !bias_of(f2, NCLS, b4)) return ZANT_OK;
+
+    const int s_pool1 = pl->add_scratch(B * 2 * 169 * 16);
+    const int s_pool2 = pl->add_scratch(B * 1600);
+    const int s_fc1 = pl->add_scratch(B * 512);
+    const int s_fc2 = pl->add_scratch(B * NCLS);
+    const int a_w2 = pl->add_aux(w2arr.data(), w2arr.size());
+    const int a_m2 = pl->add_aux(m2.data(), m2.size() * 4), a_b2 = pl->add_aux(b2.data(), b2.size() * 4);
+    const int a_w3 = pl->add_aux(w3p.data(), w3p.size());
+    const int a_m3 = pl->add_aux(m3.data(), m3.size() * 4), a_b3 = pl->add_aux(b3.data(), b3.size() * 4);
+    const std::vector<int32_t> zeros(std::max<size_t>(512, NCLS), 0);
+    const int a_z = pl->add_aux(zeros.data(), zeros.size() * 4);
+    const int a_m4 = pl->add_aux(m4.data(), m4.size() * 4), a_b4 = pl->add_aux(b4.data(), b4.size() * 4);
+    const int w4 = f2.in[1];
+
+    push("Fused[QuantizeLinear+QLinearConv+Relu+MaxPool]", [=]() {
+        Conv1Args k = a1;
+        k.x = pl->p<float>(x); k.y = (int8_t*)pl->scratch(s_pool1);
+        const int blocks = std::min<int>((int)((B + C1_G - 1) / C1_G), ctx->sm_count * 8);
+        conv1_quant_relu_pool_kernel<<<blocks, C1_THREADS, 0, ctx->stream>>>(k);
+        return check_launch(ctx, "conv1_quant_relu_pool_kernel");
+    });
+    const zant_node_attrs c2a = c2.a;
+    push("Fused[QLinearConv+Relu+MaxPool] tcgen05", [=]() {
+        using Cfg = TcConvPoolCfg<13, 13, 64>;
+        static bool attr_set = false;
+        if (!attr_set) {
+            ZB_CUDA(cudaFuncSetAttribute(tc_conv3x3_relu_pool_kernel<13, 13, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+            attr_set = true;
+        }
+        TcConvPoolArgs k{};
+        k.x = (const int8_t*)pl->scratch(s_pool1); k.w = (const int8_t*)pl->aux(a_w2);
+        k.mult = (const float*)pl->aux(a_m2); k.bias = (const int32_t*)pl->aux(a_b2);
+        k.y = (int8_t*)pl->scratch(s_pool2); k.n_images = (int)B;
+        k.y_scale = c2a.y_scale; k.y_zp = c2a.y_zp; k.act = ZANT_QACT_RELU; k.out_blocked = 0; k.status = ctx->status_word;
+        const int blocks = std::min<int>((int)B, ctx->sm_count * 2);
+        tc_conv3x3_relu_pool_kernel<13, 13, 64><<<blocks, Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
+        return check_launch(ctx, "tc_conv3x3_relu_pool_kernel");
+    });
+    const zant_node_attrs f1a = f1.a, f2a = f2.a, dqa = N[11].a;
+    push("QLinearMatMul+Relu", [=]() {
+        QMatArgs q{};
+        q.a = pl->scratch(s_pool2); q.b = (const int8_t*)pl->aux(a_w3); q.y = pl->scratch(s_fc1);
+        q.mult = (const float*)pl->aux(a_m3); q.b_zp = (const int32_t*)pl->aux(a_z); q.bias = (const int32_t*)pl->aux(a_b3);
+        q.a_zp = f1a.x_zp; q.rq = Requant{f1a.y_scale, f1a.y_zp, ZANT_QACT_RELU}; q.M = (int)B; q.N = 512; q.K = 1600; q.y_i32 = 0;
+        return run_qmatmul_generic(ctx, q, ZANT_I8, ZANT_I8);
+    });
+    push("QLinearMatMul", [=]() {
+        QMatArgs q{};
+        q.a = pl->scratch(s_fc1); q.b = pl->p<int8_t>(w4); q.y = pl->scratch(s_fc2);
+        q.mult = (const float*)pl->aux(a_m4); q.b_zp = (const int32_t*)pl->aux(a_z); q.bias = (const int32_t*)pl->aux(a_b4);
+        q.a_zp = f2a.x_zp; q.rq = Requant{f2a.y_scale, f2a.y_zp, ZANT_QACT_NONE}; q.M = (int)B; q.N = (int)NCLS; q.K = 512; q.y_i32 = 0;
+        return run_qmatmul_generic(ctx, q, ZANT_I8, ZANT_I8);
+    });
+    push("DequantizeLinear", [=]() { return run_dequantize(ctx, ZANT_I8, pl->scratch(s_fc2), pl->p<float>(y), B * NCLS, dqa.x_scale, dqa.x_zp); });
+    consumed = 12;
     return ZANT_OK;
 }
