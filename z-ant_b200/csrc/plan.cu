@@ -15,6 +15,7 @@
 #include "geometry.hpp"
 #include "ops.cuh"
 #include "fused_cnn.cuh"
+#include "tc_gemm.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -785,26 +786,42 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
     // ---- fc1: rows re-ordered from the graph's (c,h,w) flatten order to the (h,w,c) order stage 2 writes
     std::vector<float> m3; std::vector<int32_t> b3;
     if (!scales_of(f1, 512, m3) || !bias_of(f1, 512, b3)) return ZANT_OK;
-    std::vector<int8_t> w3p(1600 * 512);
+    constexpr int FC_NT = 256, FC_KC = 4, FC_STAGES = 8;
+    std::vector<int8_t> w3blk(1600 * 512);      // [512/NT][100 chunks][NT][16], K in (h,w,c) order
     {
         const int8_t* w = (const int8_t*)T(f1.in[1]).host.data();   // [1600][512], row = c*25 + h*5 + w
+        std::vector<int> colsum(512, 0);
         for (int ch = 0; ch < 64; ++ch)
-            for (int hw = 0; hw < 25; ++hw)
-                std::memcpy(&w3p[(size_t)(hw * 64 + ch) * 512], &w[(size_t)(ch * 25 + hw) * 512], 512);
+            for (int hw = 0; hw < 25; ++hw) {
+                const int k = hw * 64 + ch;                         // position in the order stage 2 writes
+                const int8_t* src = &w[(size_t)(ch * 25 + hw) * 512];
+                for (int n = 0; n < 512; ++n) {
+                    w3blk[(((size_t)(n / FC_NT) * 100 + k / 16) * FC_NT + n % FC_NT) * 16 + k % 16] = src[n];
+                    colsum[n] += src[n];
+                }
+            }
+        for (int n = 0; n < 512; ++n) b3[n] -= f1.a.x_zp * colsum[n];
     }
     std::vector<float> m4; std::vector<int32_t> b4;
     if (!scales_of(f2, NCLS, m4) || !bias_of(f2, NCLS, b4)) return ZANT_OK;
+    if (NCLS > 16) return ZANT_OK;
+    {
+        const int8_t* w = (const int8_t*)T(f2.in[1]).host.data();   // [512][NCLS]
+        for (size_t n = 0; n < NCLS; ++n) {
+            int sum = 0;
+            for (int k = 0; k < 512; ++k) sum += w[(size_t)k * NCLS + n];
+            b4[n] -= f2.a.x_zp * sum;
+        }
+    }
 
     const int s_pool1 = pl->add_scratch(B * 2 * 169 * 16);
-    const int s_pool2 = pl->add_scratch(B * 1600);
+    const size_t Bpad = (B + 127) / 128 * 128;
+    const int s_pool2 = pl->add_scratch(Bpad * 1600);
     const int s_fc1 = pl->add_scratch(B * 512);
-    const int s_fc2 = pl->add_scratch(B * NCLS);
     const int a_w2 = pl->add_aux(w2arr.data(), w2arr.size());
     const int a_m2 = pl->add_aux(m2.data(), m2.size() * 4), a_b2 = pl->add_aux(b2.data(), b2.size() * 4);
-    const int a_w3 = pl->add_aux(w3p.data(), w3p.size());
+    const int a_w3 = pl->add_aux(w3blk.data(), w3blk.size());
     const int a_m3 = pl->add_aux(m3.data(), m3.size() * 4), a_b3 = pl->add_aux(b3.data(), b3.size() * 4);
-    const std::vector<int32_t> zeros(std::max<size_t>(512, NCLS), 0);
-    const int a_z = pl->add_aux(zeros.data(), zeros.size() * 4);
     const int a_m4 = pl->add_aux(m4.data(), m4.size() * 4), a_b4 = pl->add_aux(b4.data(), b4.size() * 4);
     const int w4 = f2.in[1];
 
@@ -827,27 +844,39 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
         k.x = (const int8_t*)pl->scratch(s_pool1); k.w = (const int8_t*)pl->aux(a_w2);
         k.mult = (const float*)pl->aux(a_m2); k.bias = (const int32_t*)pl->aux(a_b2);
         k.y = (int8_t*)pl->scratch(s_pool2); k.n_images = (int)B;
-        k.y_scale = c2a.y_scale; k.y_zp = c2a.y_zp; k.act = ZANT_QACT_RELU; k.out_blocked = 0; k.status = ctx->status_word;
+        k.y_scale = c2a.y_scale; k.y_zp = c2a.y_zp; k.act = ZANT_QACT_RELU; k.out_blocked = 1; k.status = ctx->status_word;
         const int blocks = std::min<int>((int)B, ctx->sm_count * 2);
         tc_conv3x3_relu_pool_kernel<13, 13, 64><<<blocks, Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
         return check_launch(ctx, "tc_conv3x3_relu_pool_kernel");
     });
     const zant_node_attrs f1a = f1.a, f2a = f2.a, dqa = N[11].a;
-    push("QLinearMatMul+Relu", [=]() {
-        QMatArgs q{};
-        q.a = pl->scratch(s_pool2); q.b = (const int8_t*)pl->aux(a_w3); q.y = pl->scratch(s_fc1);
-        q.mult = (const float*)pl->aux(a_m3); q.b_zp = (const int32_t*)pl->aux(a_z); q.bias = (const int32_t*)pl->aux(a_b3);
-        q.a_zp = f1a.x_zp; q.rq = Requant{f1a.y_scale, f1a.y_zp, ZANT_QACT_RELU}; q.M = (int)B; q.N = 512; q.K = 1600; q.y_i32 = 0;
-        return run_qmatmul_generic(ctx, q, ZANT_I8, ZANT_I8);
+    push("Fused[Reshape+QLinearMatMul+Relu] tcgen05", [=]() {
+        using Cfg = TcGemmCfg<FC_NT, FC_KC, FC_STAGES>;
+        static bool attr_set = false;
+        if (!attr_set) {
+            ZB_CUDA(cudaFuncSetAttribute(tc_gemm_i8_kernel<FC_NT, FC_KC, FC_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+            attr_set = true;
+        }
+        TcGemmArgs k{};
+        k.a = (const int8_t*)pl->scratch(s_pool2); k.w = (const int8_t*)pl->aux(a_w3);
+        k.mult = (const float*)pl->aux(a_m3); k.bias = (const int32_t*)pl->aux(a_b3);
+        k.y = (int8_t*)pl->scratch(s_fc1); k.M = (int)B; k.N = 512; k.K16 = 100;
+        k.y_scale = f1a.y_scale; k.y_zp = f1a.y_zp; k.act = ZANT_QACT_RELU; k.status = ctx->status_word;
+        const int tiles = (int)((B + 127) / 128) * (512 / FC_NT);
+        const int blocks = std::min(tiles, ctx->sm_count);
+        tc_gemm_i8_kernel<FC_NT, FC_KC, FC_STAGES><<<blocks, Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
+        return check_launch(ctx, "tc_gemm_i8_kernel");
     });
-    push("QLinearMatMul", [=]() {
-        QMatArgs q{};
-        q.a = pl->scratch(s_fc1); q.b = pl->p<int8_t>(w4); q.y = pl->scratch(s_fc2);
-        q.mult = (const float*)pl->aux(a_m4); q.b_zp = (const int32_t*)pl->aux(a_z); q.bias = (const int32_t*)pl->aux(a_b4);
-        q.a_zp = f2a.x_zp; q.rq = Requant{f2a.y_scale, f2a.y_zp, ZANT_QACT_NONE}; q.M = (int)B; q.N = (int)NCLS; q.K = 512; q.y_i32 = 0;
-        return run_qmatmul_generic(ctx, q, ZANT_I8, ZANT_I8);
+    push("Fused[QLinearMatMul+DequantizeLinear]", [=]() {
+        FcOutArgs k{};
+        k.a = (const int8_t*)pl->scratch(s_fc1); k.w = pl->p<int8_t>(w4);
+        k.mult = (const float*)pl->aux(a_m4); k.bias = (const int32_t*)pl->aux(a_b4);
+        k.y = pl->p<float>(y); k.M = (int)B; k.K = 512; k.NCLS = (int)NCLS;
+        k.y_scale = f2a.y_scale; k.y_zp = f2a.y_zp; k.dq_scale = dqa.x_scale; k.dq_zp = dqa.x_zp;
+        const int blocks = std::min<int>((int)((B + 127) / 128), ctx->sm_count * 8);
+        fc_out_dequant_kernel<16><<<blocks, 128, 16 * 512, ctx->stream>>>(k);
+        return check_launch(ctx, "fc_out_dequant_kernel");
     });
-    push("DequantizeLinear", [=]() { return run_dequantize(ctx, ZANT_I8, pl->scratch(s_fc2), pl->p<float>(y), B * NCLS, dqa.x_scale, dqa.x_zp); });
     consumed = 12;
     return ZANT_OK;
 }

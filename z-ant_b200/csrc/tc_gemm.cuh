@@ -1,0 +1,244 @@
+// int8 GEMM on tcgen05 for fully-connected layers:  Y[M,N] = requant(A[M,K] * W[K,N] + bias).
+//
+// Operand layout "GEMM-blocked": rows are grouped in tiles (128 rows of A, NT rows of W^T) and
+// inside a tile K is split into 16-byte chunks, chunk-major:  [tile][K/16][rows][16] int8.  A run
+// of chunks of one tile is therefore contiguous in global memory — one bulk async copy per
+// operand and pipeline stage, no tensor map — and lands in shared memory directly in the
+// K-major, no-swizzle form tcgen05 reads (8 rows = 8 consecutive 16-byte chunks; the second
+// chunk of a 32-byte MMA K step lies rows*16 bytes further).
+//
+// Persistent CTAs (one per SM, all 512 TMEM columns: two 128 x 256 int32 accumulators), warp roles:
+//   warp 0    producer: bulk copies of A and W stages (KC chunks of K each), STAGES-deep ring
+//   warp 1    TMEM owner + MMA issuer: KC/2 MMAs (128 x NT x 32) per stage
+//   warps 2-5 epilogue: TMEM -> registers, + bias, requantise (per-column multiplier), ReLU, store
+// Tile order: t -> (m = t / n_tiles, n = t % n_tiles), so CTAs that run at the same time share
+// their A tile through L2.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "fused_cnn.cuh"
+#include "kernels_q8.cuh"
+#include "ptx_sm100.cuh"
+
+namespace zb {
+
+struct TcGemmArgs {
+    const int8_t* a;       // [ceil(M/128)][K16][128][16]
+    const int8_t* w;       // [N/NT][K16][NT][16]
+    const float* mult;     // [N]
+    const int32_t* bias;   // [N]
+    int8_t* y;             // [M][N] row-major
+    int M, N, K16;         // K16 = K/16, a multiple of KC
+    float y_scale; int y_zp; int act;
+    int* status;
+};
+
+template <int NT, int KC, int STAGES>
+struct TcGemmCfg {
+    static constexpr int A_STAGE = KC * 128 * 16;
+    static constexpr int W_STAGE = KC * NT * 16;
+    static constexpr int STAGE = A_STAGE + W_STAGE;
+    static constexpr int OFF_STAGES = 0;
+    static constexpr int OFF_BAR = OFF_STAGES + STAGES * STAGE;
+    static constexpr int SMEM_BYTES = OFF_BAR + 512;
+    static constexpr int TMEM_COLS = 2 * NT;
+    static constexpr int THREADS = 192;
+    static_assert(KC % 2 == 0, "a stage must hold whole 32-byte MMA K steps");
+    static_assert(NT % 32 == 0 && NT <= 256, "tile width");
+    static_assert(TMEM_COLS == 32 || TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
+    static_assert(2 * STAGES + 4 <= 48, "barrier slots");
+};
+
+template <int NT, int KC, int STAGES>
+__global__ void __launch_bounds__(192, 1) tc_gemm_i8_kernel(const __grid_constant__ TcGemmArgs a) {
+    using Cfg = TcGemmCfg<NT, KC, STAGES>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sStages = smem + Cfg::OFF_STAGES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 400);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 404);
+    volatile int* epi_ok = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 408);
+    const uint32_t bar0 = ptx::smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto tfull = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+    auto tempty = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_tiles = a.N / NT;
+    const int m_tiles = (a.M + 127) / 128;
+    const int tiles = m_tiles * n_tiles;
+    const int k_stages = a.K16 / KC;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(full(s), 1); ptx::mbar_init(empty(s), 1); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 4); }
+        *abort_flag = 0;
+        *epi_ok = 1;
+        ptx::mbar_fence_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), Cfg::TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (ptx::elect_one()) {
+            int it = 0;
+            for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+                const int m = t / n_tiles, n = t - m * n_tiles;
+                const int8_t* ga = a.a + (size_t)m * a.K16 * 2048;
+                const int8_t* gw = a.w + (size_t)n * a.K16 * (NT * 16);
+                for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                    if (!ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag)) goto producer_done;
+                    ptx::mbar_arrive_expect_tx(full(s), Cfg::STAGE);
+                    const uint32_t dst = ptx::smem_u32(sStages + s * Cfg::STAGE);
+                    ptx::bulk_g2s(dst, ga + (size_t)ks * Cfg::A_STAGE, Cfg::A_STAGE, full(s));
+                    ptx::bulk_g2s(dst + Cfg::A_STAGE, gw + (size_t)ks * Cfg::W_STAGE, Cfg::W_STAGE, full(s));
+                }
+            }
+        producer_done:;
+        }
+    } else if (warp == 1) {
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::idesc_i8(128, NT, true, true);
+            int it = 0, tile_it = 0;
+            for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
+                const int b = tile_it & 1;
+                const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
+                if (!ptx::mbar_wait(tempty(b), bph ^ 1u, abort_flag)) goto mma_done;
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * NT);
+                for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                    if (!ptx::mbar_wait(full(s), ph, abort_flag)) goto mma_done;
+                    ptx::tc_fence_after();
+                    const uint32_t sa = ptx::smem_u32(sStages + s * Cfg::STAGE);
+                    const uint32_t sw = sa + Cfg::A_STAGE;
+#pragma unroll
+                    for (int kk = 0; kk < KC / 2; ++kk) {
+                        const uint64_t da = ptx::smem_desc_kmajor(sa + (uint32_t)(kk * 2 * 2048), 2048, 128);
+                        const uint64_t db = ptx::smem_desc_kmajor(sw + (uint32_t)(kk * 2 * NT * 16), NT * 16, 128);
+                        ptx::mma_i8(d_tmem, da, db, idesc, (ks | kk) != 0);
+                    }
+                    ptx::mma_commit(empty(s));
+                }
+                ptx::mma_commit(tfull(b));
+            }
+        mma_done:;
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int e = (warp - 2) * 32 + lane;
+        const Requant rq{a.y_scale, a.y_zp, a.act};
+        int tile_it = 0;
+        for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
+            const int m = t / n_tiles, n = t - m * n_tiles;
+            const int b = tile_it & 1;
+            const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
+            if (e == 0) *epi_ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
+            ptx::named_barrier_sync(1, 128);
+            if (!*epi_ok) break;
+            ptx::tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * NT);
+            const int grow = m * 128 + row;
+            int8_t* yrow = a.y + (size_t)grow * a.N + (size_t)n * NT;
+#pragma unroll 1
+            for (int h = 0; h < NT / 32; ++h) {
+                uint32_t v[32];
+                ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
+                ptx::tmem_wait_ld();
+                const int col0 = n * NT + h * 32;
+                uint32_t packed[8];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int acc = (int)v[j] + __ldg(a.bias + col0 + j);
+                    const int q = requant_one<false>(acc, __ldg(a.mult + col0 + j), rq);
+                    if ((j & 3) == 0) packed[j >> 2] = (uint32_t)(q & 255);
+                    else packed[j >> 2] |= (uint32_t)(q & 255) << (8 * (j & 3));
+                }
+                if (grow < a.M) {
+                    reinterpret_cast<uint4*>(yrow + h * 32)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    reinterpret_cast<uint4*>(yrow + h * 32)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tempty(b));
+        }
+    }
+
+    if (*abort_flag) {
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) ptx::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (tid == 0 && *abort_flag) atomicExch(a.status, (int)DEV_ERR_WAIT_TIMEOUT);
+}
+
+// =============================================================================================
+// Last layer: QLinearMatMul(K -> NCLS <= 64 classes) + DequantizeLinear, one row per thread.
+//   y[row][n] = float(sat(rne(float(acc + bias[n]) * mult[n]) + zp) - zp_dq) * scale_dq
+// The weight matrix (K x NCLS int8) is re-packed into shared memory as [NCLS][K/4] words so that
+// all threads of a warp read the same word (broadcast) while each walks its own row of A.
+// =============================================================================================
+struct FcOutArgs {
+    const int8_t* a;        // [M][K] row-major int8
+    const int8_t* w;        // [K][NCLS] int8 (graph layout)
+    const float* mult; const int32_t* bias;   // bias already holds -a_zp * sum_k w[k][n]
+    float* y;               // [M][NCLS]
+    int M, K, NCLS;
+    float y_scale; int y_zp;      // requantisation of the int8 logits
+    float dq_scale; int dq_zp;    // DequantizeLinear
+};
+
+template <int NC>   // compile-time bound on the number of classes
+__global__ void __launch_bounds__(128) fc_out_dequant_kernel(const FcOutArgs p) {
+    extern __shared__ uint32_t sw[];                     // [NC][K/4]
+    const int kw = p.K / 4;
+    for (int i = threadIdx.x; i < NC * kw; i += blockDim.x) {
+        const int n = i / kw, k4 = i - n * kw;
+        uint32_t word = 0;
+        if (n < p.NCLS)
+            for (int j = 0; j < 4; ++j) word |= (uint32_t)(uint8_t)p.w[(size_t)(k4 * 4 + j) * p.NCLS + n] << (8 * j);
+        sw[i] = word;
+    }
+    __syncthreads();
+    const Requant rq{p.y_scale, p.y_zp, ZANT_QACT_NONE};
+    for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < p.M; row += gridDim.x * blockDim.x) {
+        const uint4* ar = reinterpret_cast<const uint4*>(p.a + (size_t)row * p.K);
+        int acc[NC];
+#pragma unroll
+        for (int n = 0; n < NC; ++n) acc[n] = 0;
+        for (int k16 = 0; k16 < p.K / 16; ++k16) {
+            const uint4 av = __ldg(ar + k16);
+#pragma unroll
+            for (int n = 0; n < NC; ++n) {
+                const uint4 wv = *reinterpret_cast<const uint4*>(sw + n * kw + k16 * 4);
+                acc[n] = __dp4a((int)av.x, (int)wv.x, acc[n]);
+                acc[n] = __dp4a((int)av.y, (int)wv.y, acc[n]);
+                acc[n] = __dp4a((int)av.z, (int)wv.z, acc[n]);
+                acc[n] = __dp4a((int)av.w, (int)wv.w, acc[n]);
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < NC; ++n) {
+            if (n < p.NCLS) {
+                const int q = requant_one<false>(acc[n] + __ldg(p.bias + n), __ldg(p.mult + n), rq);
+                p.y[(size_t)row * p.NCLS + n] = __fmul_rn(__int2float_rn(q - p.dq_zp), p.dq_scale);
+            }
+        }
+    }
+}
+
+}  // namespace zb
