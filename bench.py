@@ -105,6 +105,17 @@ def step_costs(graph):
     return out
 
 
+def fused_step_costs(batch, n_classes=10):
+    """Algorithmic work of the four fused steps of the int8 CNN (per launch): every tensor that
+    crosses a kernel boundary counted once at its storage type, weights included."""
+    return [
+        dict(op="conv1 fused", out="pool1", macs=batch * 194688, bytes=batch * (784 * 4 + 13 * 13 * 32) + 32 * 9),
+        dict(op="conv2 fused tcgen05", out="pool2", macs=batch * 2230272, bytes=batch * (13 * 13 * 32 + 1600) + 64 * 288),
+        dict(op="fc1 tcgen05", out="relu3", macs=batch * 819200, bytes=batch * (1600 + 512) + 1600 * 512),
+        dict(op="fc2+dequant", out="logits", macs=batch * 512 * n_classes, bytes=batch * (512 + 4 * n_classes) + 512 * n_classes),
+    ]
+
+
 def cpu_reference_rate(batch_hint, scales, budget_s=12.0):
     """Times the CPU oracle (the reference's algorithm restated) on a bounded sample of the
     workload with every host core (independent sample shards, one thread each)."""
@@ -166,6 +177,7 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU per step")
     ap.add_argument("--no-fuse", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="chunks of the batch that the end-to-end path pipelines")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
 
@@ -229,7 +241,25 @@ def main():
         return ms, launches
 
     resident = lambda: plan.run(x_dev, out=y_dev)        # noqa: E731
-    end_to_end = lambda: plan.run(x_host, out=y_host)    # noqa: E731
+
+    # End to end: the same batch from pinned host memory, cut into chunks that alternate between two
+    # contexts (streams) so that the H2D copy of one chunk overlaps the kernels of the previous one.
+    n_chunks = args.e2e_chunks if batch % args.e2e_chunks == 0 else 1
+    cb = batch // n_chunks
+    if n_chunks > 1:
+        ctx2 = zb.Context(local)
+        chunk_graph = models.small_cnn_int8(cb, act_scales=scales)
+        chunk_plans = [zb.Plan(ctx, chunk_graph, fuse=not args.no_fuse), zb.Plan(ctx2, chunk_graph, fuse=not args.no_fuse)]
+        stream2 = torch.cuda.ExternalStream(ctx2.stream, device=torch.device("cuda", local))
+
+        def end_to_end():
+            # order the two streams behind the timing event's stream, run, and join them again
+            ev = torch.cuda.Event(); ev.record(stream); stream2.wait_event(ev)
+            for c in range(n_chunks):
+                chunk_plans[c % 2].run(x_host[c * cb:(c + 1) * cb], out=y_host[c * cb:(c + 1) * cb])
+            ev2 = torch.cuda.Event(); ev2.record(stream2); stream.wait_event(ev2)
+    else:
+        end_to_end = lambda: plan.run(x_host, out=y_host)    # noqa: E731
 
     for _ in range(args.warmup):
         resident()
@@ -244,6 +274,12 @@ def main():
     for _ in range(2):
         end_to_end()
     ms_e2e, _ = timed(end_to_end, args.steps)
+    torch.cuda.synchronize()
+    # the pipelined path must produce what the resident path produced
+    resident()
+    torch.cuda.synchronize()
+    if not torch.equal(y_dev.cpu(), y_host):
+        raise SystemExit("bench: end-to-end result differs from the device-resident result")
 
     if rank == 0:
         peaks = measured_peaks()
@@ -258,8 +294,9 @@ def main():
         node_ids = [i for i, n in enumerate(graph.nodes) if n["op"] != "Reshape"]
         shares = {f"{i}:{names[i]}": round(per_step[i] / max(sum(per_step), 1e-9), 4) for i in range(len(names))}
         roof = None
-        if len(names) == len(node_ids):
-            c = costs[node_ids[top]]
+        fused_costs = fused_step_costs(batch) if (len(names) == 4 and not args.no_fuse) else None
+        if len(names) == len(node_ids) or fused_costs:
+            c = fused_costs[top] if fused_costs else costs[node_ids[top]]
             int8_peak = 2.0 * peaks["bf16_tflops_sustained"]      # dense int8 = 2x dense bf16 on the same tensor pipes
             intensity = 2.0 * c["macs"] / max(c["bytes"], 1)
             ridge = int8_peak * 1e12 / (peaks["hbm_gbs"] * 1e9)
@@ -284,9 +321,11 @@ def main():
                                 batch_per_gpu=batch, global_batch=batch * world, fused=not args.no_fuse,
                                 l2="inputs larger than L2 (205 MB of float input per step)", calibration="256 seeded samples, FP32 plan on the GPU",
                                 macs_per_image=MACS_PER_IMAGE, parallelism=f"sample-sharded x{world}, no collective"),
-                    roofline=roof, step_share=shares, cpu_baseline=cpu,
+                    roofline=roof, step_share=shares, step_ms={f"{i}:{names[i]}": round(per_step[i], 5) for i in range(len(names))},
+                    cpu_baseline=cpu,
                     e2e=dict(value=total_images / (ms_e2e / 1e3), unit="images/s", h2d_bytes_per_step=batch * 784 * 4,
-                             d2h_bytes_per_step=batch * 10 * 4, ms_per_step=ms_e2e / args.steps),
+                             d2h_bytes_per_step=batch * 10 * 4, ms_per_step=ms_e2e / args.steps, chunks=n_chunks,
+                             how="plan.run on pinned host buffers, chunks alternate between two contexts (copy/compute overlap)"),
                     gpu_launches=int(launches) * world, clocks=clocks, arena_bytes=plan.arena_bytes)
         print(json.dumps(line), flush=True)
     plan.close()

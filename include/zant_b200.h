@@ -442,7 +442,10 @@ int32_t zant_b200_plan_node(zant_plan* plan, int32_t op,
 int32_t zant_b200_plan_finalize(zant_plan* plan, int32_t input_id, int32_t output_id, int32_t fuse);
 
 /* Runs the plan once: the analogue of predict(input, shape, len, &result)
- * (src/codeGen/predict.zig:34-40).  `input`/`output` may be host or device pointers. */
+ * (src/codeGen/predict.zig:34-40).  `input`/`output` may be host or device pointers.
+ * Pageable host buffers: the call returns when the result is in `output`.  Device buffers, or
+ * page-locked (pinned) host buffers on both sides: the call only enqueues work on the context's
+ * stream; zant_b200_ctx_synchronize waits for it and reports device-side errors. */
 int32_t zant_b200_plan_run(zant_plan* plan, const void* input, void* output);
 
 /* Bytes of the plan's arena and number of kernels one run launches. */

@@ -58,6 +58,18 @@ inline bool is_device_ptr(const void* p) {
     return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
 }
 
+// Page-locked host memory (cudaHostAlloc / cudaHostRegister): copies to and from it are truly
+// asynchronous, so calls that are handed such buffers do not wait for the stream.
+inline bool is_pinned_host_ptr(const void* p) {
+    if (!p) return false;
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeHost;
+}
+
 constexpr size_t kArenaAlign = 256;
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 

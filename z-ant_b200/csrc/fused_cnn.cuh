@@ -57,7 +57,6 @@ constexpr int C1_THREADS = 256;
 __global__ void __launch_bounds__(C1_THREADS) conv1_quant_relu_pool_kernel(const __grid_constant__ Conv1Args a) {
     __shared__ uint32_t img[C1_G][28][8];   // rows of 32 bytes (28 pixels + 4 pad)
     const int tid = threadIdx.x;
-    const Requant rq{a.y_scale, a.y_zp, a.act};
     for (int base = blockIdx.x * C1_G; base < a.n_images; base += gridDim.x * C1_G) {
         for (int i = tid; i < C1_G * 784; i += C1_THREADS) {
             const int g = i / 784, p = i - g * 784;
@@ -83,15 +82,19 @@ __global__ void __launch_bounds__(C1_THREADS) conv1_quant_relu_pool_kernel(const
             }
             uint32_t out[8];
 #pragma unroll
-            for (int m = 0; m < 32; ++m) {
-                const int a00 = dp4a_us(X[0], a.wpack[m][0][0], dp4a_us(X[1], a.wpack[m][1][0], dp4a_us(X[2], a.wpack[m][2][0], 0)));
-                const int a01 = dp4a_us(X[0], a.wpack[m][0][1], dp4a_us(X[1], a.wpack[m][1][1], dp4a_us(X[2], a.wpack[m][2][1], 0)));
-                const int a10 = dp4a_us(X[1], a.wpack[m][0][0], dp4a_us(X[2], a.wpack[m][1][0], dp4a_us(X[3], a.wpack[m][2][0], 0)));
-                const int a11 = dp4a_us(X[1], a.wpack[m][0][1], dp4a_us(X[2], a.wpack[m][1][1], dp4a_us(X[3], a.wpack[m][2][1], 0)));
-                const int mx = max(max(a00, a01), max(a10, a11)) + a.bias[m];
-                const int t = requant_one<false>(mx, a.mult[m], rq);
-                if ((m & 3) == 0) out[m >> 2] = (uint32_t)(t & 255);
-                else out[m >> 2] |= (uint32_t)(t & 255) << (8 * (m & 3));
+            for (int m4 = 0; m4 < 8; ++m4) {
+                int r[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int m = m4 * 4 + j;
+                    const int b = a.bias[m];    // max(acc_i) + b == max(acc_i + b): the bias seeds every window
+                    const int a00 = dp4a_us(X[0], a.wpack[m][0][0], dp4a_us(X[1], a.wpack[m][1][0], dp4a_us(X[2], a.wpack[m][2][0], b)));
+                    const int a01 = dp4a_us(X[0], a.wpack[m][0][1], dp4a_us(X[1], a.wpack[m][1][1], dp4a_us(X[2], a.wpack[m][2][1], b)));
+                    const int a10 = dp4a_us(X[1], a.wpack[m][0][0], dp4a_us(X[2], a.wpack[m][1][0], dp4a_us(X[3], a.wpack[m][2][0], b)));
+                    const int a11 = dp4a_us(X[1], a.wpack[m][0][1], dp4a_us(X[2], a.wpack[m][1][1], dp4a_us(X[3], a.wpack[m][2][1], b)));
+                    r[j] = rq_round(max(max(a00, a01), max(a10, a11)), a.mult[m]);
+                }
+                out[m4] = relu_s8x4(pack_sat_s8x4(r[0], r[1], r[2], r[3]));
             }
             int8_t* yo = a.y + ((size_t)(base + g) * 2 * 169 + pp) * 16;
             *reinterpret_cast<uint4*>(yo) = make_uint4(out[0], out[1], out[2], out[3]);
@@ -111,8 +114,9 @@ __global__ void __launch_bounds__(C1_THREADS) conv1_quant_relu_pool_kernel(const
 //   warp 0   bulk-copy producer (one elected lane), STAGES-deep ring of images
 //   warp 1   TMEM owner + MMA issuer (one elected lane): 9 MMAs (K=32) per image into one of two
 //            TMEM accumulators
-//   warps 2-5  epilogue: TMEM -> registers -> shared staging (int32), 2x2 max, bias, requantise,
-//            ReLU, store
+//   warps 2-9  epilogue, two groups of four warps that alternate images (group g owns TMEM
+//            accumulator g): TMEM -> registers -> shared staging (int32), 2x2 max, bias,
+//            requantise, ReLU, store
 // =============================================================================================
 struct TcConvPoolArgs {
     const int8_t* x;
@@ -139,33 +143,36 @@ struct TcConvPoolCfg {
     static constexpr int STG_BYTES = 128 * STG_ROW;
     static constexpr int OFF_W = 0;
     static constexpr int OFF_A = OFF_W + W_BYTES;
-    static constexpr int OFF_STG = OFF_A + STAGES * STAGE_BYTES;
-    static constexpr int OFF_BAR = OFF_STG + STG_BYTES;
+    static constexpr int OFF_STG = OFF_A + STAGES * STAGE_BYTES;   // two staging areas, one per epilogue group
+    static constexpr int OFF_BAR = OFF_STG + 2 * STG_BYTES;
     static constexpr int SMEM_BYTES = OFF_BAR + 256;
     static constexpr int TMEM_COLS = 2 * COUT >= 32 ? 2 * COUT : 32;
     static constexpr int KOUT = PH * PW * COUT;
-    static constexpr int THREADS = 192;
+    static constexpr int QUADS = COUT / 4;
+    static constexpr int TASKS = PH * PW * QUADS;
+    static constexpr int TASKS_PER_THREAD = (TASKS + 127) / 128;
+    static constexpr int THREADS = 320;                      // producer, MMA, 2 x 4 epilogue warps
     // every position the pool keeps must be one of the 128 MMA rows, and every shifted read must
     // stay inside the image's planes
     static_assert((2 * PH - 1) * IW + (2 * PW - 1) < 128, "pooled window exceeds one 128-row tile");
     static_assert(127 + 2 * IW + 2 < 2 * P, "shifted A rows would leave the staged image");
     static_assert(COUT % 32 == 0 && COUT <= 256, "COUT must be a multiple of 32 up to 256");
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
-    static_assert(128 % (COUT / 4) == 0, "channel quad of an epilogue thread must be loop invariant");
+    static_assert(128 % QUADS == 0, "channel quad of an epilogue thread must be loop invariant");
 };
 
+// Requires: int8 output with zero point 0, ReLU, positive finite multipliers (host-checked).
 template <int IH, int IW, int COUT>
-__global__ void __launch_bounds__(192, 1) tc_conv3x3_relu_pool_kernel(const __grid_constant__ TcConvPoolArgs a) {
+__global__ void __launch_bounds__(320, 1) tc_conv3x3_relu_pool_kernel(const __grid_constant__ TcConvPoolArgs a) {
     using Cfg = TcConvPoolCfg<IH, IW, COUT>;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sW = smem + Cfg::OFF_W;
     uint8_t* sA = smem + Cfg::OFF_A;
-    uint8_t* sStg = smem + Cfg::OFF_STG;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
     // barrier slots: full[STAGES], empty[STAGES], tfull[2], tempty[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 128);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 132);
-    volatile int* epi_ok = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 136);
+    volatile int* epi_ok = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 136);   // [2]
     const uint32_t bar0 = ptx::smem_u32(bars);
     auto full = [&](int s) { return bar0 + 8u * s; };
     auto empty = [&](int s) { return bar0 + 8u * (Cfg::STAGES + s); };
@@ -178,7 +185,7 @@ __global__ void __launch_bounds__(192, 1) tc_conv3x3_relu_pool_kernel(const __gr
         for (int s = 0; s < Cfg::STAGES; ++s) { ptx::mbar_init(full(s), 1); ptx::mbar_init(empty(s), 1); }
         for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 4); }
         *abort_flag = 0;
-        *epi_ok = 1;
+        epi_ok[0] = 1; epi_ok[1] = 1;
         ptx::mbar_fence_init();
     }
     for (int i = tid; i < Cfg::W_BYTES / 16; i += Cfg::THREADS)
@@ -233,25 +240,36 @@ __global__ void __launch_bounds__(192, 1) tc_conv3x3_relu_pool_kernel(const __gr
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------------------ epilogue: two groups of 4 warps;
+        // group g owns TMEM accumulator g and handles the images whose iteration index is g mod 2.
+        const int g = (warp - 2) >> 2;
         const int quarter = warp & 3;               // TMEM lane quarter this warp may access
         const int row = quarter * 32 + lane;        // MMA row = input-grid position
-        const int e = (warp - 2) * 32 + lane;       // 0..127 within the epilogue group
-        constexpr int QUADS = COUT / 4;
-        const int cq = e % QUADS;
+        const int e = ((warp - 2) & 3) * 32 + lane; // 0..127 within the group
+        uint8_t* sStg = smem + Cfg::OFF_STG + g * Cfg::STG_BYTES;
+        const int cq = e % Cfg::QUADS;
         float mult[4]; int bias[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) { mult[j] = __ldg(a.mult + cq * 4 + j); bias[j] = __ldg(a.bias + cq * 4 + j); }
-        const Requant rq{a.y_scale, a.y_zp, a.act};
-        int it = 0;
-        for (int img = blockIdx.x; img < a.n_images; img += gridDim.x, ++it) {
-            const int b = it & 1;
+        // this thread's pooled outputs: staging offset of the window's top-left row and output offset
+        int stg_off[Cfg::TASKS_PER_THREAD]; int out_off[Cfg::TASKS_PER_THREAD];
+#pragma unroll
+        for (int k = 0; k < Cfg::TASKS_PER_THREAD; ++k) {
+            const int t = e + 128 * k;
+            const int q = t / Cfg::QUADS;
+            const int py = q / Cfg::PW, px = q - py * Cfg::PW;
+            stg_off[k] = (t < Cfg::TASKS) ? (2 * py * IW + 2 * px) * Cfg::STG_ROW + cq * 16 : -1;
+            out_off[k] = a.out_blocked ? (q * (COUT / 16) + (cq >> 2)) * 2048 + (cq & 3) * 4 : q * COUT + cq * 4;
+        }
+        const uint32_t bar_id = 1u + (uint32_t)g;
+        int it = g;
+        for (int img = blockIdx.x + g * (int)gridDim.x; img < a.n_images; img += 2 * (int)gridDim.x, it += 2) {
             const uint32_t bph = (uint32_t)(it >> 1) & 1u;
-            if (e == 0) *epi_ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
-            ptx::named_barrier_sync(1, 128);        // also: every thread finished reading the staging of the previous image
-            if (!*epi_ok) break;
+            if (e == 0) epi_ok[g] = ptx::mbar_wait(tfull(g), bph, abort_flag) ? 1 : 0;
+            ptx::named_barrier_sync(bar_id, 128);   // also: the group finished reading the staging of its previous image
+            if (!epi_ok[g]) break;
             ptx::tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * COUT);
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(g * COUT);
 #pragma unroll
             for (int h = 0; h < COUT / 32; ++h) {
                 uint32_t v[32];
@@ -263,32 +281,23 @@ __global__ void __launch_bounds__(192, 1) tc_conv3x3_relu_pool_kernel(const __gr
             }
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(tempty(b));   // accumulator b may be overwritten
-            ptx::named_barrier_sync(1, 128);
-            for (int t = e; t < Cfg::PH * Cfg::PW * QUADS; t += 128) {
-                const int q = t / QUADS;
-                const int py = q / Cfg::PW, px = q - py * Cfg::PW;
-                const int p0 = 2 * py * IW + 2 * px;
-                const int4 r0 = *reinterpret_cast<const int4*>(sStg + p0 * Cfg::STG_ROW + cq * 16);
-                const int4 r1 = *reinterpret_cast<const int4*>(sStg + (p0 + 1) * Cfg::STG_ROW + cq * 16);
-                const int4 r2 = *reinterpret_cast<const int4*>(sStg + (p0 + IW) * Cfg::STG_ROW + cq * 16);
-                const int4 r3 = *reinterpret_cast<const int4*>(sStg + (p0 + IW + 1) * Cfg::STG_ROW + cq * 16);
-                const int m0 = max(max(r0.x, r1.x), max(r2.x, r3.x)) + bias[0];
-                const int m1 = max(max(r0.y, r1.y), max(r2.y, r3.y)) + bias[1];
-                const int m2 = max(max(r0.z, r1.z), max(r2.z, r3.z)) + bias[2];
-                const int m3 = max(max(r0.w, r1.w), max(r2.w, r3.w)) + bias[3];
-                const uint32_t packed = (uint32_t)(requant_one<false>(m0, mult[0], rq) & 255) |
-                                        ((uint32_t)(requant_one<false>(m1, mult[1], rq) & 255) << 8) |
-                                        ((uint32_t)(requant_one<false>(m2, mult[2], rq) & 255) << 16) |
-                                        ((uint32_t)(requant_one<false>(m3, mult[3], rq) & 255) << 24);
-                size_t off;
-                if (a.out_blocked) {
-                    const int chunk = q * (COUT / 16) + (cq >> 2);
-                    off = ((size_t)(img >> 7) * (Cfg::KOUT / 16) + chunk) * 2048 + (size_t)(img & 127) * 16 + (cq & 3) * 4;
-                } else {
-                    off = (size_t)img * Cfg::KOUT + q * COUT + cq * 4;
-                }
-                *reinterpret_cast<uint32_t*>(a.y + off) = packed;
+            if (lane == 0) ptx::mbar_arrive(tempty(g));   // accumulator g may be overwritten
+            ptx::named_barrier_sync(bar_id, 128);
+            int8_t* ybase = a.out_blocked ? a.y + (size_t)(img >> 7) * (Cfg::KOUT / 16) * 2048 + (size_t)(img & 127) * 16
+                                          : a.y + (size_t)img * Cfg::KOUT;
+#pragma unroll
+            for (int k = 0; k < Cfg::TASKS_PER_THREAD; ++k) {
+                if (stg_off[k] < 0) continue;
+                const uint8_t* s0 = sStg + stg_off[k];
+                const int4 r0 = *reinterpret_cast<const int4*>(s0);
+                const int4 r1 = *reinterpret_cast<const int4*>(s0 + Cfg::STG_ROW);
+                const int4 r2 = *reinterpret_cast<const int4*>(s0 + IW * Cfg::STG_ROW);
+                const int4 r3 = *reinterpret_cast<const int4*>(s0 + (IW + 1) * Cfg::STG_ROW);
+                const int q0 = rq_round(max(max(r0.x, r1.x), max(r2.x, r3.x)) + bias[0], mult[0]);
+                const int q1 = rq_round(max(max(r0.y, r1.y), max(r2.y, r3.y)) + bias[1], mult[1]);
+                const int q2 = rq_round(max(max(r0.z, r1.z), max(r2.z, r3.z)) + bias[2], mult[2]);
+                const int q3 = rq_round(max(max(r0.w, r1.w), max(r2.w, r3.w)) + bias[3], mult[3]);
+                *reinterpret_cast<uint32_t*>(ybase + out_off[k]) = relu_s8x4(pack_sat_s8x4(q0, q1, q2, q3));
             }
         }
     }

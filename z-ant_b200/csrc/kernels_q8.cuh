@@ -35,6 +35,24 @@ __device__ __forceinline__ int requant_one(int acc, float M, const Requant& r) {
     return t;
 }
 
+// ---------------------------------------------------------------------------- lean int8 requantisation
+// Fast form of requant_one for int8 outputs with zero point 0 and a positive finite multiplier
+// (the host checks both).  rni(float(acc) * M) saturates at the int32 range and the pack
+// instruction saturates to [-128,127]; for zero point 0 that equals
+// sat(rne(clamp(v,-512,511)) + 0) for every v, so the results are bit-identical.
+__device__ __forceinline__ int rq_round(int acc, float M) { return __float2int_rn(__fmul_rn(__int2float_rn(acc), M)); }
+
+// bytes (little endian) = sat8(a0), sat8(a1), sat8(a2), sat8(a3)
+__device__ __forceinline__ uint32_t pack_sat_s8x4(int a0, int a1, int a2, int a3) {
+    uint32_t hi, d;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(a3), "r"(a2));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a1), "r"(a0), "r"(hi));
+    return d;
+}
+
+// ReLU on four packed int8 values with zero point 0.
+__device__ __forceinline__ uint32_t relu_s8x4(uint32_t v) { return __vmaxs4(v, 0u); }
+
 template <bool U8> __device__ __forceinline__ int load_q(const void* p, size_t i) {
     return U8 ? (int)reinterpret_cast<const uint8_t*>(p)[i] : (int)reinterpret_cast<const int8_t*>(p)[i];
 }

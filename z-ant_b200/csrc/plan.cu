@@ -30,6 +30,7 @@ struct PlanTensor {
     void* arena_ptr = nullptr;  // address inside the plan's arena
     void* bound = nullptr;      // caller's device buffer bound for the current run (input/output)
     int alias = -1;             // Reshape output: shares the buffer of this tensor
+    bool elided = false;        // interior of a fused chain: never materialised, no arena space
 };
 
 struct PlanNode {
@@ -204,7 +205,7 @@ int32_t zant_b200_plan_finalize(zant_plan* plan, int32_t input_id, int32_t outpu
     // 2. arena layout: every non-aliased tensor and every derived constant at a fixed offset
     size_t off = 0;
     for (auto& t : plan->t) {
-        if (t.alias >= 0) continue;
+        if (t.alias >= 0 || t.elided) continue;
         t.offset = off;
         off += align_up(t.bytes ? t.bytes : 1, kArenaAlign);
     }
@@ -221,7 +222,7 @@ int32_t zant_b200_plan_finalize(zant_plan* plan, int32_t input_id, int32_t outpu
     plan->arena_bytes = off;
     ZB_CUDA(cudaMalloc((void**)&plan->arena, off));
     for (auto& t : plan->t) {
-        if (t.alias >= 0) continue;
+        if (t.alias >= 0 || t.elided) continue;
         t.arena_ptr = plan->arena + t.offset;
         if (t.is_const && t.bytes) ZB_CUDA(cudaMemcpyAsync(t.arena_ptr, t.host.data(), t.bytes, cudaMemcpyHostToDevice, ctx->stream));
     }
@@ -274,6 +275,10 @@ int32_t zant_b200_plan_run(zant_plan* plan, const void* input, void* output) {
     if (!out_dev) {
         ZB_CUDA(cudaMemcpyAsync(output, tor.arena_ptr, to.bytes, cudaMemcpyDeviceToHost, ctx->stream));
         ti.bound = nullptr; tor.bound = nullptr;
+        // Pinned host buffers on both sides: the whole run stays asynchronous on the stream (the
+        // caller overlaps it with other contexts and calls zant_b200_ctx_synchronize).  Pageable
+        // buffers: wait, so that the result is in place when the call returns.
+        if (is_pinned_host_ptr(output) && (in_dev || is_pinned_host_ptr(input))) return ZANT_OK;
         return drain_and_check_status(ctx);
     }
     ti.bound = nullptr; tor.bound = nullptr;
@@ -322,6 +327,11 @@ int32_t zant_b200_plan_read_tensor(zant_plan* plan, int32_t id, void* host_dst) 
     if (!plan || !plan->finalized) return fail(ZANT_E_BAD_HANDLE, "plan is NULL or not finalized");
     if (id < 0 || id >= (int)plan->t.size()) return fail(ZANT_E_INVALID_INPUT, "tensor id %d", id);
     if (!host_dst) return fail(ZANT_E_NULL_POINTER, "host_dst is NULL");
+    {
+        int r = id;
+        while (plan->t[r].alias >= 0) r = plan->t[r].alias;
+        if (plan->t[r].elided) return fail(ZANT_E_UNSUPPORTED, "tensor %d is interior to a fused chain and is not materialised", id);
+    }
     ZB_CUDA(cudaSetDevice(plan->ctx->device));
     ZB_CUDA(cudaStreamSynchronize(plan->ctx->stream));
     ZB_CUDA(cudaMemcpy(host_dst, plan->ptr(id), plan->t[id].bytes, cudaMemcpyDeviceToHost));
@@ -696,7 +706,7 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
     // conv1
     const PlanNode& c1 = N[1];
     if (c1.in.size() < 3 || !plain_conv3x3(c1.a) || !shape_is(T(c1.in[1]), {32, 1, 3, 3}) || !shape_is(T(c1.out[0]), {B, 32, 26, 26})) return ZANT_OK;
-    if (T(c1.out[0]).dtype != ZANT_I8 || c1.a.activation == ZANT_QACT_RELU6) return ZANT_OK;
+    if (T(c1.out[0]).dtype != ZANT_I8 || c1.a.activation == ZANT_QACT_RELU6 || c1.a.y_zp != 0) return ZANT_OK;
     if (c1.a.x_scale != N[0].a.y_scale || c1.a.x_zp != N[0].a.y_zp) return ZANT_OK;
     if (opt_in(c1, 3) >= 0 && !all_zero_i32(T(c1.in[3]))) return ZANT_OK;
     if (!identity_scale_relu(N[2]) || N[2].a.x_scale != c1.a.y_scale || N[2].a.x_zp != c1.a.y_zp) return ZANT_OK;
@@ -704,7 +714,7 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
     // conv2
     const PlanNode& c2 = N[4];
     if (c2.in.size() < 3 || !plain_conv3x3(c2.a) || !shape_is(T(c2.in[1]), {64, 32, 3, 3}) || !shape_is(T(c2.out[0]), {B, 64, 11, 11})) return ZANT_OK;
-    if (T(c2.out[0]).dtype != ZANT_I8 || c2.a.activation == ZANT_QACT_RELU6) return ZANT_OK;
+    if (T(c2.out[0]).dtype != ZANT_I8 || c2.a.activation == ZANT_QACT_RELU6 || c2.a.y_zp != 0) return ZANT_OK;
     if (c2.a.x_scale != c1.a.y_scale || c2.a.x_zp != c1.a.y_zp) return ZANT_OK;
     if (opt_in(c2, 3) >= 0 && !all_zero_i32(T(c2.in[3]))) return ZANT_OK;
     if (!identity_scale_relu(N[5]) || N[5].a.x_scale != c2.a.y_scale || N[5].a.x_zp != c2.a.y_zp) return ZANT_OK;
@@ -715,7 +725,7 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
     const PlanNode& f2 = N[10];
     if (f1.in.size() < 3 || f2.in.size() < 3) return ZANT_OK;
     if (!shape_is(T(f1.in[1]), {1600, 512}) || !shape_is(T(f1.out[0]), {B, 512}) || T(f1.out[0]).dtype != ZANT_I8) return ZANT_OK;
-    if (f1.a.x_scale != c2.a.y_scale || f1.a.x_zp != c2.a.y_zp || f1.a.activation == ZANT_QACT_RELU6) return ZANT_OK;
+    if (f1.a.x_scale != c2.a.y_scale || f1.a.x_zp != c2.a.y_zp || f1.a.activation == ZANT_QACT_RELU6 || f1.a.y_zp != 0) return ZANT_OK;
     if (opt_in(f1, 3) >= 0 && !all_zero_i32(T(f1.in[3]))) return ZANT_OK;
     if (!identity_scale_relu(N[9]) || N[9].a.x_scale != f1.a.y_scale || N[9].a.x_zp != f1.a.y_zp) return ZANT_OK;
     if (T(f2.in[1]).shape.size() != 2 || T(f2.in[1]).shape[0] != 512 || T(f2.out[0]).dtype != ZANT_I8) return ZANT_OK;
@@ -877,6 +887,7 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
         fc_out_dequant_kernel<16><<<blocks, 128, 16 * 512, ctx->stream>>>(k);
         return check_launch(ctx, "fc_out_dequant_kernel");
     });
+    for (int k = 0; k < 11; ++k) pl->t[N[k].out[0]].elided = true;   // interior tensors live only inside the fused kernels
     consumed = 12;
     return ZANT_OK;
 }

@@ -10,7 +10,9 @@
 // Persistent CTAs (one per SM, all 512 TMEM columns: two 128 x 256 int32 accumulators), warp roles:
 //   warp 0    producer: bulk copies of A and W stages (KC chunks of K each), STAGES-deep ring
 //   warp 1    TMEM owner + MMA issuer: KC/2 MMAs (128 x NT x 32) per stage
-//   warps 2-5 epilogue: TMEM -> registers, + bias, requantise (per-column multiplier), ReLU, store
+//   warps 2-9 epilogue (each lane quarter is served by two warps that split the tile's columns):
+//             TMEM -> registers, + bias, requantise (per-column constants from shared memory),
+//             ReLU, store
 // Tile order: t -> (m = t / n_tiles, n = t % n_tiles), so CTAs that run at the same time share
 // their A tile through L2.
 #pragma once
@@ -40,22 +42,29 @@ struct TcGemmCfg {
     static constexpr int A_STAGE = KC * 128 * 16;
     static constexpr int W_STAGE = KC * NT * 16;
     static constexpr int STAGE = A_STAGE + W_STAGE;
+    static constexpr int MAX_N = 1024;                       // per-column constants kept in shared memory
     static constexpr int OFF_STAGES = 0;
-    static constexpr int OFF_BAR = OFF_STAGES + STAGES * STAGE;
+    static constexpr int OFF_CONST = OFF_STAGES + STAGES * STAGE;   // float mult[MAX_N]; int bias[MAX_N]
+    static constexpr int OFF_BAR = OFF_CONST + 2 * MAX_N * 4;
     static constexpr int SMEM_BYTES = OFF_BAR + 512;
     static constexpr int TMEM_COLS = 2 * NT;
-    static constexpr int THREADS = 192;
+    static constexpr int THREADS = 320;                      // producer, MMA, 8 epilogue warps
+    static constexpr int COLS_PER_WARP = NT / 2;             // the two epilogue groups split the tile's columns
     static_assert(KC % 2 == 0, "a stage must hold whole 32-byte MMA K steps");
-    static_assert(NT % 32 == 0 && NT <= 256, "tile width");
-    static_assert(TMEM_COLS == 32 || TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
+    static_assert(NT % 64 == 0 && NT <= 256, "tile width");
+    static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
     static_assert(2 * STAGES + 4 <= 48, "barrier slots");
+    static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
+// Requires: int8 output with zero point 0, positive finite multipliers, N <= MAX_N (host-checked).
 template <int NT, int KC, int STAGES>
-__global__ void __launch_bounds__(192, 1) tc_gemm_i8_kernel(const __grid_constant__ TcGemmArgs a) {
+__global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constant__ TcGemmArgs a) {
     using Cfg = TcGemmCfg<NT, KC, STAGES>;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sStages = smem + Cfg::OFF_STAGES;
+    float* sMult = reinterpret_cast<float*>(smem + Cfg::OFF_CONST);
+    int* sBias = reinterpret_cast<int*>(smem + Cfg::OFF_CONST + Cfg::MAX_N * 4);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 400);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 404);
@@ -74,11 +83,12 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_i8_kernel(const __grid_constan
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(full(s), 1); ptx::mbar_init(empty(s), 1); }
-        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 4); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 8); }
         *abort_flag = 0;
         *epi_ok = 1;
         ptx::mbar_fence_init();
     }
+    for (int i = tid; i < a.N; i += Cfg::THREADS) { sMult[i] = __ldg(a.mult + i); sBias[i] = __ldg(a.bias + i); }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), Cfg::TMEM_COLS);
         ptx::tmem_relinquish();
@@ -136,35 +146,43 @@ __global__ void __launch_bounds__(192, 1) tc_gemm_i8_kernel(const __grid_constan
         mma_done:;
         }
     } else {
+        // ------------------------------------------------------------------ epilogue: 8 warps; warp (2+q) and (6+q)
+        // read lane quarter q; the first four warps take the tile's left half of the columns.
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int row = quarter * 32 + lane;
-        const int e = (warp - 2) * 32 + lane;
-        const Requant rq{a.y_scale, a.y_zp, a.act};
+        const int e = (warp - 2) * 32 + lane;     // 0..255
+        const bool relu = a.act == ZANT_QACT_RELU;
         int tile_it = 0;
         for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
             const int m = t / n_tiles, n = t - m * n_tiles;
             const int b = tile_it & 1;
             const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
             if (e == 0) *epi_ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
-            ptx::named_barrier_sync(1, 128);
+            ptx::named_barrier_sync(1, 256);
             if (!*epi_ok) break;
             ptx::tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * NT);
+            const int tcol0 = half * Cfg::COLS_PER_WARP;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * NT + tcol0);
             const int grow = m * 128 + row;
-            int8_t* yrow = a.y + (size_t)grow * a.N + (size_t)n * NT;
+            int8_t* yrow = a.y + (size_t)grow * a.N + (size_t)n * NT + tcol0;
 #pragma unroll 1
-            for (int h = 0; h < NT / 32; ++h) {
+            for (int h = 0; h < Cfg::COLS_PER_WARP / 32; ++h) {
                 uint32_t v[32];
                 ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
                 ptx::tmem_wait_ld();
-                const int col0 = n * NT + h * 32;
+                const int col0 = n * NT + tcol0 + h * 32;
                 uint32_t packed[8];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int acc = (int)v[j] + __ldg(a.bias + col0 + j);
-                    const int q = requant_one<false>(acc, __ldg(a.mult + col0 + j), rq);
-                    if ((j & 3) == 0) packed[j >> 2] = (uint32_t)(q & 255);
-                    else packed[j >> 2] |= (uint32_t)(q & 255) << (8 * (j & 3));
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
+                    const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
+                    const int q0 = rq_round((int)v[j4 * 4 + 0] + b4.x, m4.x);
+                    const int q1 = rq_round((int)v[j4 * 4 + 1] + b4.y, m4.y);
+                    const int q2 = rq_round((int)v[j4 * 4 + 2] + b4.z, m4.z);
+                    const int q3 = rq_round((int)v[j4 * 4 + 3] + b4.w, m4.w);
+                    const uint32_t pk = pack_sat_s8x4(q0, q1, q2, q3);
+                    packed[j4] = relu ? relu_s8x4(pk) : pk;
                 }
                 if (grow < a.M) {
                     reinterpret_cast<uint4*>(yrow + h * 32)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
