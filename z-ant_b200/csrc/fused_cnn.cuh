@@ -115,14 +115,15 @@ __global__ void __launch_bounds__(C1_THREADS) conv1_quant_relu_pool_kernel(const
 //   warp 1   TMEM owner + MMA issuer (one elected lane): 9 MMAs (K=32) per image into one of two
 //            TMEM accumulators
 //   warps 2-9  epilogue, two groups of four warps that alternate images (group g owns TMEM
-//            accumulator g): TMEM -> registers -> shared staging (int32), 2x2 max, bias,
-//            requantise, ReLU, store
+//            accumulator g): TMEM -> registers, + bias, requantise to int8, shared staging (int8),
+//            2x2 max and ReLU on packed bytes, 16-byte stores
 // =============================================================================================
+constexpr int TCCONV_MAX_COUT = 128;
 struct TcConvPoolArgs {
     const int8_t* x;
     const int8_t* w;        // [9 taps][2 chunks][COUT][16] int8
-    const float* mult;      // [COUT]
-    const int32_t* bias;    // [COUT]  (already includes -x_zp * sum(w))
+    float mult[TCCONV_MAX_COUT];     // per output channel; read as constant-bank operands (no loads)
+    int32_t bias[TCCONV_MAX_COUT];   // already includes -x_zp * sum(w)
     int8_t* y;
     int n_images;
     float y_scale; int y_zp; int act;
@@ -139,16 +140,17 @@ struct TcConvPoolCfg {
     static constexpr int STAGES = 4;
     static constexpr int W_TAP_BYTES = 2 * COUT * 16;
     static constexpr int W_BYTES = 9 * W_TAP_BYTES;
-    static constexpr int STG_ROW = COUT * 4 + 16;            // +16: rows land on distinct bank groups
+    static constexpr int STG_ROW = COUT + 16;                // int8 row + 16: 16-byte stores of 8 lanes hit distinct banks
     static constexpr int STG_BYTES = 128 * STG_ROW;
     static constexpr int OFF_W = 0;
     static constexpr int OFF_A = OFF_W + W_BYTES;
     static constexpr int OFF_STG = OFF_A + STAGES * STAGE_BYTES;   // two staging areas, one per epilogue group
-    static constexpr int OFF_BAR = OFF_STG + 2 * STG_BYTES;
+    static constexpr int OFF_CONST = OFF_STG + 2 * STG_BYTES;      // float mult[COUT]; int bias[COUT]
+    static constexpr int OFF_BAR = OFF_CONST + 2 * COUT * 4;
     static constexpr int SMEM_BYTES = OFF_BAR + 256;
     static constexpr int TMEM_COLS = 2 * COUT >= 32 ? 2 * COUT : 32;
     static constexpr int KOUT = PH * PW * COUT;
-    static constexpr int QUADS = COUT / 4;
+    static constexpr int QUADS = COUT / 16;                  // 16-channel groups: one 16-byte word of int8
     static constexpr int TASKS = PH * PW * QUADS;
     static constexpr int TASKS_PER_THREAD = (TASKS + 127) / 128;
     static constexpr int THREADS = 320;                      // producer, MMA, 2 x 4 epilogue warps
@@ -156,9 +158,8 @@ struct TcConvPoolCfg {
     // stay inside the image's planes
     static_assert((2 * PH - 1) * IW + (2 * PW - 1) < 128, "pooled window exceeds one 128-row tile");
     static_assert(127 + 2 * IW + 2 < 2 * P, "shifted A rows would leave the staged image");
-    static_assert(COUT % 32 == 0 && COUT <= 256, "COUT must be a multiple of 32 up to 256");
+    static_assert(COUT % 32 == 0 && COUT <= TCCONV_MAX_COUT, "COUT must be a multiple of 32 within the parameter block");
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
-    static_assert(128 % QUADS == 0, "channel quad of an epilogue thread must be loop invariant");
 };
 
 // Requires: int8 output with zero point 0, ReLU, positive finite multipliers (host-checked).
@@ -247,19 +248,16 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_relu_pool_kernel(const __gr
         const int row = quarter * 32 + lane;        // MMA row = input-grid position
         const int e = ((warp - 2) & 3) * 32 + lane; // 0..127 within the group
         uint8_t* sStg = smem + Cfg::OFF_STG + g * Cfg::STG_BYTES;
-        const int cq = e % Cfg::QUADS;
-        float mult[4]; int bias[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { mult[j] = __ldg(a.mult + cq * 4 + j); bias[j] = __ldg(a.bias + cq * 4 + j); }
-        // this thread's pooled outputs: staging offset of the window's top-left row and output offset
+        // this thread's pooled outputs (16 channels each): staging offset of the window's top-left
+        // row and output offset
         int stg_off[Cfg::TASKS_PER_THREAD]; int out_off[Cfg::TASKS_PER_THREAD];
 #pragma unroll
         for (int k = 0; k < Cfg::TASKS_PER_THREAD; ++k) {
             const int t = e + 128 * k;
-            const int q = t / Cfg::QUADS;
+            const int q = t / Cfg::QUADS, cg = t - q * Cfg::QUADS;
             const int py = q / Cfg::PW, px = q - py * Cfg::PW;
-            stg_off[k] = (t < Cfg::TASKS) ? (2 * py * IW + 2 * px) * Cfg::STG_ROW + cq * 16 : -1;
-            out_off[k] = a.out_blocked ? (q * (COUT / 16) + (cq >> 2)) * 2048 + (cq & 3) * 4 : q * COUT + cq * 4;
+            stg_off[k] = (t < Cfg::TASKS) ? (2 * py * IW + 2 * px) * Cfg::STG_ROW + cg * 16 : -1;
+            out_off[k] = a.out_blocked ? (q * Cfg::QUADS + cg) * 2048 : q * COUT + cg * 16;
         }
         const uint32_t bar_id = 1u + (uint32_t)g;
         int it = g;
@@ -270,14 +268,24 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_relu_pool_kernel(const __gr
             if (!epi_ok[g]) break;
             ptx::tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(g * COUT);
+            // requantise this row (max-pool and ReLU commute with it and are applied to the int8 values)
 #pragma unroll
             for (int h = 0; h < COUT / 32; ++h) {
                 uint32_t v[32];
                 ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
                 ptx::tmem_wait_ld();
-                uint4* dst = reinterpret_cast<uint4*>(sStg + row * Cfg::STG_ROW + h * 128);
+                uint32_t pk[8];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) dst[k] = make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    const int c = h * 32 + j4 * 4;     // compile-time after unrolling: constant-bank operands
+                    pk[j4] = pack_sat_s8x4(rq_round((int)v[j4 * 4 + 0] + a.bias[c + 0], a.mult[c + 0]),
+                                           rq_round((int)v[j4 * 4 + 1] + a.bias[c + 1], a.mult[c + 1]),
+                                           rq_round((int)v[j4 * 4 + 2] + a.bias[c + 2], a.mult[c + 2]),
+                                           rq_round((int)v[j4 * 4 + 3] + a.bias[c + 3], a.mult[c + 3]));
+                }
+                uint4* dst = reinterpret_cast<uint4*>(sStg + row * Cfg::STG_ROW + h * 32);
+                dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
             }
             ptx::tc_fence_before();
             __syncwarp();
@@ -289,15 +297,16 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_relu_pool_kernel(const __gr
             for (int k = 0; k < Cfg::TASKS_PER_THREAD; ++k) {
                 if (stg_off[k] < 0) continue;
                 const uint8_t* s0 = sStg + stg_off[k];
-                const int4 r0 = *reinterpret_cast<const int4*>(s0);
-                const int4 r1 = *reinterpret_cast<const int4*>(s0 + Cfg::STG_ROW);
-                const int4 r2 = *reinterpret_cast<const int4*>(s0 + IW * Cfg::STG_ROW);
-                const int4 r3 = *reinterpret_cast<const int4*>(s0 + (IW + 1) * Cfg::STG_ROW);
-                const int q0 = rq_round(max(max(r0.x, r1.x), max(r2.x, r3.x)) + bias[0], mult[0]);
-                const int q1 = rq_round(max(max(r0.y, r1.y), max(r2.y, r3.y)) + bias[1], mult[1]);
-                const int q2 = rq_round(max(max(r0.z, r1.z), max(r2.z, r3.z)) + bias[2], mult[2]);
-                const int q3 = rq_round(max(max(r0.w, r1.w), max(r2.w, r3.w)) + bias[3], mult[3]);
-                *reinterpret_cast<uint32_t*>(ybase + out_off[k]) = relu_s8x4(pack_sat_s8x4(q0, q1, q2, q3));
+                const uint4 r0 = *reinterpret_cast<const uint4*>(s0);
+                const uint4 r1 = *reinterpret_cast<const uint4*>(s0 + Cfg::STG_ROW);
+                const uint4 r2 = *reinterpret_cast<const uint4*>(s0 + IW * Cfg::STG_ROW);
+                const uint4 r3 = *reinterpret_cast<const uint4*>(s0 + (IW + 1) * Cfg::STG_ROW);
+                uint4 o;
+                o.x = relu_s8x4(__vmaxs4(__vmaxs4(r0.x, r1.x), __vmaxs4(r2.x, r3.x)));
+                o.y = relu_s8x4(__vmaxs4(__vmaxs4(r0.y, r1.y), __vmaxs4(r2.y, r3.y)));
+                o.z = relu_s8x4(__vmaxs4(__vmaxs4(r0.z, r1.z), __vmaxs4(r2.z, r3.z)));
+                o.w = relu_s8x4(__vmaxs4(__vmaxs4(r0.w, r1.w), __vmaxs4(r2.w, r3.w)));
+                *reinterpret_cast<uint4*>(ybase + out_off[k]) = o;
             }
         }
     }

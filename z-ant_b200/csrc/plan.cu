@@ -829,7 +829,6 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
     const int s_pool2 = pl->add_scratch(Bpad * 1600);
     const int s_fc1 = pl->add_scratch(B * 512);
     const int a_w2 = pl->add_aux(w2arr.data(), w2arr.size());
-    const int a_m2 = pl->add_aux(m2.data(), m2.size() * 4), a_b2 = pl->add_aux(b2.data(), b2.size() * 4);
     const int a_w3 = pl->add_aux(w3blk.data(), w3blk.size());
     const int a_m3 = pl->add_aux(m3.data(), m3.size() * 4), a_b3 = pl->add_aux(b3.data(), b3.size() * 4);
     const int a_m4 = pl->add_aux(m4.data(), m4.size() * 4), a_b4 = pl->add_aux(b4.data(), b4.size() * 4);
@@ -852,7 +851,7 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
         }
         TcConvPoolArgs k{};
         k.x = (const int8_t*)pl->scratch(s_pool1); k.w = (const int8_t*)pl->aux(a_w2);
-        k.mult = (const float*)pl->aux(a_m2); k.bias = (const int32_t*)pl->aux(a_b2);
+        for (int m = 0; m < 64; ++m) { k.mult[m] = m2[m]; k.bias[m] = b2[m]; }
         k.y = (int8_t*)pl->scratch(s_pool2); k.n_images = (int)B;
         k.y_scale = c2a.y_scale; k.y_zp = c2a.y_zp; k.act = ZANT_QACT_RELU; k.out_blocked = 1; k.status = ctx->status_word;
         const int blocks = std::min<int>((int)B, ctx->sm_count * 2);
