@@ -338,6 +338,35 @@ int32_t zant_b200_qlinearmatmul(zant_ctx* ctx,
                                 int32_t y_dtype, void* y, const size_t* y_shape, size_t y_rank,
                                 int32_t activation);
 
+/* QLinearConv for callers that cannot allocate device memory (no counterpart in the reference:
+ * its operators run on the CPU heap).  Think of an inference loop whose memory was handed out
+ * once at start-up, a latency-critical thread that must avoid cudaMalloc's device-wide
+ * synchronisation, or a port of Z-Ant's generated code, which owns only static arrays.  The
+ * regular entry point needs a context, and a context owns a cudaMalloc'd arena; this one takes
+ * a cudaStream_t (as void*, NULL = default stream) instead and allocates nothing.  The
+ * per-channel requantisation constants that the kernel reads besides x, w, bias and y are kept
+ * in a fixed device array inside the library (32 KiB per GPU, held until the process exits).
+ *   - same arithmetic, argument meaning and error codes as zant_b200_qlinearconv;
+ *   - x, w, bias, y: DEVICE pointers of the current device; w_scale, w_zp: host arrays;
+ *   - at most 4096 output channels, otherwise ZANT_E_TOO_LARGE;
+ *   - the first call on a device resolves the array's device address: issue it before any
+ *     stream capture starts;
+ *   - all calls on a device share the array, so calls whose kernels could overlap on the GPU
+ *     race: keep them on one stream or order them with events;
+ *   - asynchronous: returns after enqueueing on the stream. */
+int32_t zant_b200_qlinearconv_noalloc(void* cuda_stream,
+                                      int32_t x_dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                                      float x_scale, int32_t x_zp,
+                                      const int8_t* w, const size_t* w_shape, size_t w_rank,
+                                      const float* w_scale, const int32_t* w_zp, size_t n_w_scale,
+                                      float y_scale, int32_t y_zp,
+                                      const int32_t* bias, size_t bias_len,
+                                      int32_t y_dtype, void* y, const size_t* y_shape, size_t y_rank,
+                                      const size_t* stride, size_t n_stride,
+                                      const size_t* pads, size_t n_pads,
+                                      const size_t* dilations, size_t n_dil,
+                                      size_t group, int32_t auto_pad, int32_t activation);
+
 /* Quantized Add (QLinearAdd / QDQ residual), equal shapes:
  *   y = sat(rne((float(a - a_zp) * a_s + float(b - b_zp) * b_s) / y_s) + y_zp). */
 int32_t zant_b200_qlinearadd(zant_ctx* ctx, int32_t dtype,

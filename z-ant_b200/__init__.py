@@ -513,6 +513,24 @@ class Context:
         return y
 
 
+def qlinearconv_noalloc(x, x_scale, x_zp, w, w_scale, w_zp, y_scale, y_zp, out, bias=None, stride=(1, 1), pads=(0, 0, 0, 0),
+                        dilations=(1, 1), group=1, auto_pad="NOTSET", activation=None, stream=None):
+    """QLinearConv without any device allocation (zant_b200_qlinearconv_noalloc): no Context is
+    involved; x, w, bias and `out` are device tensors (objects with data_ptr()), `stream` is a raw
+    cudaStream_t value or None for the default stream.  Asynchronous."""
+    w_scale = np.atleast_1d(np.ascontiguousarray(w_scale, np.float32))
+    w_zp = None if w_zp is None else np.atleast_1d(np.ascontiguousarray(w_zp, np.int32))
+    xs, xr = _sz(_shape(x)); ws, wr = _sz(_shape(w)); ys, yr = _sz(_shape(out))
+    st, ns = _sz(stride); pd, npd = _sz(pads); dl, nd = _sz(dilations)
+    check(lib().zant_b200_qlinearconv_noalloc(
+        C.c_void_p(stream), C.c_int32(_dtype_code(x)), _ptr(x), xs, C.c_size_t(xr), C.c_float(x_scale), C.c_int32(x_zp),
+        _ptr(w), ws, C.c_size_t(wr), _ptr(w_scale), _ptr(w_zp), C.c_size_t(w_scale.size), C.c_float(y_scale), C.c_int32(y_zp),
+        _ptr(bias), C.c_size_t(0 if bias is None else _numel(_shape(bias))), C.c_int32(_dtype_code(out)), _ptr(out), ys,
+        C.c_size_t(yr), st, C.c_size_t(ns), pd, C.c_size_t(npd), dl, C.c_size_t(nd), C.c_size_t(group),
+        C.c_int32(AUTO_PAD[auto_pad]), C.c_int32(QACT[activation])))
+    return out
+
+
 def qconv_output_shape(x_shape, w_shape, stride, pads, dilations, auto_pad="NOTSET"):
     """ONNX output shape of QLinearConv (explicit pads unless auto_pad says otherwise)."""
     sh = stride[0] if len(stride) > 0 else 1

@@ -2,3 +2,4 @@
 // kernels defined in the .cuh headers.
 #include "abi.cu"
 #include "plan.cu"
+#include "noalloc.cu"
