@@ -116,6 +116,11 @@ def fused_step_costs(batch, n_classes=10):
     ]
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at batch 65536, from the ncu captures
+# summarised under profiles/ (index = fused step).
+NCU_DRAM_TRAFFIC_B65536 = [205.6e6 + 304.3e6, 355.0e6 + 84.0e6, 105.7e6 + 8.8e6, 33.6e6 + 0.0]
+
+
 def cpu_reference_rate(batch_hint, scales, budget_s=12.0):
     """Times the CPU oracle (the reference's algorithm restated) on a bounded sample of the
     workload with every host core (independent sample shards, one thread each)."""
@@ -307,7 +312,8 @@ def main():
             else:
                 ach = c["bytes"] / secs / 1e9
                 roof = dict(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"])
-            roof.update(traffic=None, kernel=f"{names[top]} -> {c['out']}", launch_ms=per_step[top], peak_source=peaks["source"] +
+            traffic = NCU_DRAM_TRAFFIC_B65536[top] * batch / 65536 if fused_costs else None
+            roof.update(traffic=traffic, traffic_source="ncu capture at batch 65536 (profiles/), scaled by batch" if traffic else None, kernel=f"{names[top]} -> {c['out']}", launch_ms=per_step[top], peak_source=peaks["source"] +
                         (" (int8 tensor peak taken as 2 x measured sustained bf16)" if roof["bound"] == "tensor" else ""),
                         algorithmic_bytes=c["bytes"], macs=c["macs"])
         else:
