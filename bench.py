@@ -208,6 +208,8 @@ def main():
     stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local))
     batch = args.batch
 
+    int8_peak_tops = ctx.measure_int8_peak(20000) if rank == 0 else None   # resident-tile tcgen05 probe, ~15 ms
+
     # calibration on the GPU through the FP32 plan (configuration 1 at batch 256), then the int8 graph
     scales = models.calibrate_on_gpu(ctx, models.small_cnn_fp32(256), models.small_cnn_input(256, models.DEFAULT_SEED + 1))
     graph = models.small_cnn_int8(batch, act_scales=scales)
@@ -302,7 +304,7 @@ def main():
         fused_costs = fused_step_costs(batch) if (len(names) == 4 and not args.no_fuse) else None
         if len(names) == len(node_ids) or fused_costs:
             c = fused_costs[top] if fused_costs else costs[node_ids[top]]
-            int8_peak = 2.0 * peaks["bf16_tflops_sustained"]      # dense int8 = 2x dense bf16 on the same tensor pipes
+            int8_peak = int8_peak_tops      # measured on this GPU by the resident-tile tcgen05 kind::i8 probe
             intensity = 2.0 * c["macs"] / max(c["bytes"], 1)
             ridge = int8_peak * 1e12 / (peaks["hbm_gbs"] * 1e9)
             secs = per_step[top] / 1e3
@@ -314,11 +316,20 @@ def main():
                 roof = dict(bound="hbm", achieved=ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=ach / peaks["hbm_gbs"])
             traffic = NCU_DRAM_TRAFFIC_B65536[top] * batch / 65536 if fused_costs else None
             roof.update(traffic=traffic, traffic_source="ncu capture at batch 65536 (profiles/), scaled by batch" if traffic else None, kernel=f"{names[top]} -> {c['out']}", launch_ms=per_step[top], peak_source=peaks["source"] +
-                        (" (int8 tensor peak taken as 2 x measured sustained bf16)" if roof["bound"] == "tensor" else ""),
+                        (" (int8 tensor peak measured in this run by zant_b200_measure_int8_peak)" if roof["bound"] == "tensor" else ""),
                         algorithmic_bytes=c["bytes"], macs=c["macs"])
         else:
             roof = dict(bound="hbm", achieved=None, peak=peaks["hbm_gbs"], unit="GB/s", frac=None, traffic=None,
                         kernel="fused plan: see step_share", peak_source=peaks["source"])
+        per_kernel = None
+        if fused_costs:
+            per_kernel = []
+            for i, c in enumerate(fused_costs):
+                secs = per_step[i] / 1e3
+                tens = 2.0 * c["macs"] / secs / 1e12
+                gbs = c["bytes"] / secs / 1e9
+                per_kernel.append(dict(kernel=names[i], ms=round(per_step[i], 5), tops=round(tens, 1), tops_frac=round(tens / int8_peak_tops, 4),
+                                       gbs=round(gbs, 1), hbm_frac=round(gbs / peaks["hbm_gbs"], 4)))
         cpu = None if args.skip_cpu else cpu_reference_rate(batch, scales)
         line = dict(metric=METRIC, value=value, unit="images/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
                     ms_per_step=ms / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="int8",
@@ -327,7 +338,7 @@ def main():
                                 batch_per_gpu=batch, global_batch=batch * world, fused=not args.no_fuse,
                                 l2="inputs larger than L2 (205 MB of float input per step)", calibration="256 seeded samples, FP32 plan on the GPU",
                                 macs_per_image=MACS_PER_IMAGE, parallelism=f"sample-sharded x{world}, no collective"),
-                    roofline=roof, step_share=shares, step_ms={f"{i}:{names[i]}": round(per_step[i], 5) for i in range(len(names))},
+                    roofline=roof, int8_peak_tops=int8_peak_tops, bf16_tflops_measured=peaks["bf16_tflops"], per_kernel=per_kernel, step_share=shares, step_ms={f"{i}:{names[i]}": round(per_step[i], 5) for i in range(len(names))},
                     cpu_baseline=cpu,
                     e2e=dict(value=total_images / (ms_e2e / 1e3), unit="images/s", h2d_bytes_per_step=batch * 784 * 4,
                              d2h_bytes_per_step=batch * 10 * 4, ms_per_step=ms_e2e / args.steps, chunks=n_chunks,

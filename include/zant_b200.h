@@ -136,6 +136,12 @@ int32_t zant_b200_ctx_synchronize(zant_ctx* ctx);
 uint64_t zant_b200_ctx_launch_count(zant_ctx* ctx);
 void zant_b200_ctx_reset_launch_count(zant_ctx* ctx);
 
+/* Attainable int8 tensor-core rate of the context's device in TOP/s: a resident-tile
+ * tcgen05.mma kind::i8 loop (128x256x32 per instruction, `iters` x 2 instructions per SM, no
+ * global traffic), best of four timed launches.  No reference counterpart; it is the
+ * denominator of the roofline fractions reported for tensor-bound kernels. */
+int32_t zant_b200_measure_int8_peak(zant_ctx* ctx, int32_t iters, double* tera_ops_per_s);
+
 /* ------------------------------------------------------------------------------------------
  * Shape helpers (host only; usable without a GPU)
  * ---------------------------------------------------------------------------------------- */

@@ -263,6 +263,12 @@ class Context:
     def set_stream(self, cuda_stream_ptr):
         check(lib().zant_b200_ctx_set_stream(self._h, C.c_void_p(cuda_stream_ptr)))
 
+    def measure_int8_peak(self, iters=20000):
+        """Attainable int8 tensor rate (TOP/s) from the resident-tile tcgen05 probe."""
+        v = C.c_double(0.0)
+        check(lib().zant_b200_measure_int8_peak(self._h, C.c_int32(iters), C.byref(v)))
+        return v.value
+
     def launch_count(self):
         return int(lib().zant_b200_ctx_launch_count(self._h))
 

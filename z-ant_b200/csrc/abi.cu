@@ -13,6 +13,7 @@
 #include "context.cuh"
 #include "geometry.hpp"
 #include "ops.cuh"
+#include "tc_peak.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -102,6 +103,31 @@ int32_t zant_b200_ctx_synchronize(zant_ctx* ctx) {
 
 uint64_t zant_b200_ctx_launch_count(zant_ctx* ctx) { return ctx ? ctx->launches : 0; }
 void zant_b200_ctx_reset_launch_count(zant_ctx* ctx) { if (ctx) ctx->launches = 0; }
+
+int32_t zant_b200_measure_int8_peak(zant_ctx* ctx, int32_t iters, double* tera_ops_per_s) {
+    ZB_NEED(tera_ops_per_s, "tera_ops_per_s");
+    ZB_NEED_CTX(ctx);
+    if (iters < 64) iters = 64;
+    if (iters > (1 << 20)) iters = 1 << 20;
+    ZB_CUDA(cudaFuncSetAttribute(tc_peak_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PEAK_SMEM));
+    cudaEvent_t e0, e1;
+    ZB_CUDA(cudaEventCreate(&e0)); ZB_CUDA(cudaEventCreate(&e1));
+    float best = 1e30f;
+    for (int rep = 0; rep < 5; ++rep) {      // first repetition is the warm-up
+        ZB_CUDA(cudaEventRecord(e0, ctx->stream));
+        tc_peak_i8_kernel<<<ctx->sm_count, 128, PEAK_SMEM, ctx->stream>>>(iters, ctx->status_word);
+        ZB_TRY(check_launch(ctx, "tc_peak_i8_kernel"));
+        ZB_CUDA(cudaEventRecord(e1, ctx->stream));
+        ZB_TRY(drain_and_check_status(ctx));
+        float ms = 0.0f;
+        ZB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        if (rep > 0 && ms < best) best = ms;
+    }
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    const double ops = (double)ctx->sm_count * iters * 2.0 * (2.0 * 128 * 256 * 32);
+    *tera_ops_per_s = ops / (best * 1e-3) / 1e12;
+    return ZANT_OK;
+}
 
 // ------------------------------------------------------------------------------------ shape helpers
 int32_t zant_b200_conv_output_shape(const size_t* x_shape, size_t x_rank, const size_t* w_shape, size_t w_rank,
