@@ -105,6 +105,117 @@ __global__ void __launch_bounds__(C1_THREADS) conv1_quant_relu_pool_kernel(const
 }
 
 // =============================================================================================
+// Stage 1, tensor-core form.  Same operator chain and output as conv1_quant_relu_pool_kernel, but
+// the 3x3 contraction runs on warp-level int8 MMAs (mma.sync m16n8k16, u8 x s8 -> s32):
+//   rows    = 16 pooled pixels (two per thread-row group g and g+8),
+//   K (16)  = the 4x4 input patch of a pooled pixel, byte (r,s) at k = 4r + s, so a thread's A
+//             register is simply patch row r = lane%4 as one packed word,
+//   columns = 8 output channels; the four members (dy,dx) of the 2x2 pool window are four
+//             MMAs with the filter shifted inside the patch (zero where it falls outside).
+// All four members of one pooled pixel and channel land in the same thread and register slot,
+// so the pool is three max instructions without any data exchange.  Channels are permuted
+// (group j, column n <-> channel 8*(n/2) + 2j + n%2) so that a thread ends up with eight
+// consecutive channels of its two pixels and stores them as one 8-byte word each.
+// =============================================================================================
+struct Conv1MmaArgs {
+    const float* x;
+    int8_t* y;
+    int n_images;
+    float x_scale; int x_zp;
+    const uint32_t* wfrag;   // [4 members][4 groups][32 lanes] B-fragment words
+    const int32_t* biasfrag; // [4 groups][32 lanes][2]  (bias - x_zp * sum(w)) of the lane's two columns
+    const float* multfrag;   // [4 groups][32 lanes][2]
+};
+
+__device__ __forceinline__ void mma_m16n8k16_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, const int (&c)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%9,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+
+constexpr int C1M_G = 3;               // images per CTA iteration: 507 pooled pixels = 32 units of 16
+constexpr int C1M_THREADS = 256;
+constexpr int C1M_UNITS = (C1M_G * 169 + 15) / 16;
+
+__global__ void __launch_bounds__(C1M_THREADS) conv1_mma_relu_pool_kernel(const Conv1MmaArgs a) {
+    __shared__ uint32_t img[C1M_G][28][8];   // quantized uint8 rows of 32 bytes (28 pixels + 4 pad)
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    uint32_t wf[4][4]; int bias[4][2]; float mult[4][2];
+#pragma unroll
+    for (int m = 0; m < 4; ++m)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wf[m][j] = __ldg(a.wfrag + (m * 4 + j) * 32 + lane);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int b = 0; b < 2; ++b) { bias[j][b] = __ldg(a.biasfrag + (j * 32 + lane) * 2 + b); mult[j][b] = __ldg(a.multfrag + (j * 32 + lane) * 2 + b); }
+
+    for (int base = blockIdx.x * C1M_G; base < a.n_images; base += gridDim.x * C1M_G) {
+        // ---- quantize C1M_G images: float4 in, four uint8 out
+        for (int i = tid; i < C1M_G * 196; i += C1M_THREADS) {
+            const int gi = i / 196, p4 = i - gi * 196;        // 196 float4 per image, 7 per row
+            uint32_t word = 0;
+            if (base + gi < a.n_images) {
+                const float4 v = __ldg(reinterpret_cast<const float4*>(a.x + (size_t)(base + gi) * 784) + p4);
+                const int q0 = sat_q<true>(rne_clamped(__fdiv_rn(v.x, a.x_scale)) + a.x_zp);
+                const int q1 = sat_q<true>(rne_clamped(__fdiv_rn(v.y, a.x_scale)) + a.x_zp);
+                const int q2 = sat_q<true>(rne_clamped(__fdiv_rn(v.z, a.x_scale)) + a.x_zp);
+                const int q3 = sat_q<true>(rne_clamped(__fdiv_rn(v.w, a.x_scale)) + a.x_zp);
+                word = (uint32_t)q0 | ((uint32_t)q1 << 8) | ((uint32_t)q2 << 16) | ((uint32_t)q3 << 24);
+            }
+            const int r = p4 / 7, c4 = p4 - r * 7;
+            img[gi][r][c4] = word;
+        }
+        __syncthreads();
+        // ---- 16 pooled pixels per warp iteration
+        for (int u = warp; u < C1M_UNITS; u += C1M_THREADS / 32) {
+            int pi[2]; bool ok[2]; uint32_t afrag[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                pi[h] = u * 16 + g + 8 * h;
+                const int gi = pi[h] / 169;
+                ok[h] = pi[h] < C1M_G * 169 && base + gi < a.n_images;
+                const int pc = ok[h] ? pi[h] : 0;
+                const int gi2 = pc / 169, pp = pc - gi2 * 169;
+                const int py = pp / 13, px = pp - py * 13;
+                const uint32_t* row = &img[gi2][2 * py + t][0];
+                const uint32_t w0 = row[px >> 1];
+                afrag[h] = (px & 1) ? __byte_perm(w0, row[(px >> 1) + 1], 0x5432) : w0;
+            }
+            uint32_t outw[2][2];
+#pragma unroll
+            for (int jp = 0; jp < 2; ++jp) {          // two channel groups at a time -> one packed word per pixel
+                int r[2][4];                          // [j in pair][row g: ch0, ch1 ; row g+8: ch0, ch1]
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj) {
+                    const int j = jp * 2 + jj;
+                    const int c[4] = {bias[j][0], bias[j][1], bias[j][0], bias[j][1]};
+                    int d0[4], d1[4], d2[4], d3[4];
+                    mma_m16n8k16_u8s8(d0, afrag[0], afrag[1], wf[0][j], c);
+                    mma_m16n8k16_u8s8(d1, afrag[0], afrag[1], wf[1][j], c);
+                    mma_m16n8k16_u8s8(d2, afrag[0], afrag[1], wf[2][j], c);
+                    mma_m16n8k16_u8s8(d3, afrag[0], afrag[1], wf[3][j], c);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        r[jj][k] = rq_round(max(max(d0[k], d1[k]), max(d2[k], d3[k])), mult[j][k & 1]);
+                }
+                outw[0][jp] = relu_s8x4(pack_sat_s8x4(r[0][0], r[0][1], r[1][0], r[1][1]));   // row g   : ch 8t+4jp .. +3
+                outw[1][jp] = relu_s8x4(pack_sat_s8x4(r[0][2], r[0][3], r[1][2], r[1][3]));   // row g+8
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                if (!ok[h]) continue;
+                const int gi = pi[h] / 169, pp = pi[h] - gi * 169;
+                int8_t* yo = a.y + (((size_t)(base + gi) * 2 + (t >> 1)) * 169 + pp) * 16 + (t & 1) * 8;
+                *reinterpret_cast<uint2*>(yo) = make_uint2(outw[h][0], outw[h][1]);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// =============================================================================================
 // Stage 2: QLinearConv(32 -> COUT, 3x3, stride 1, no pad) + ReLU + MaxPool 2x2/2 on tcgen05.
 //   input  int8 C16-planar [N][2][IH*IW][16]
 //   output int8, either row-major [N][PH*PW*COUT] in (h,w,c) order, or blocked for a following

@@ -834,12 +834,44 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
     const int a_m4 = pl->add_aux(m4.data(), m4.size() * 4), a_b4 = pl->add_aux(b4.data(), b4.size() * 4);
     const int w4 = f2.in[1];
 
-    push("Fused[QuantizeLinear+QLinearConv+Relu+MaxPool]", [=]() {
-        Conv1Args k = a1;
-        k.x = pl->p<float>(x); k.y = (int8_t*)pl->scratch(s_pool1);
-        const int blocks = std::min<int>((int)((B + C1_G - 1) / C1_G), ctx->sm_count * 8);
-        conv1_quant_relu_pool_kernel<<<blocks, C1_THREADS, 0, ctx->stream>>>(k);
-        return check_launch(ctx, "conv1_quant_relu_pool_kernel");
+    // B-fragment words, bias and multipliers in the per-lane order of the warp-level MMA
+    std::vector<uint32_t> wfrag(4 * 4 * 32);
+    std::vector<int32_t> biasfrag(4 * 32 * 2);
+    std::vector<float> multfrag(4 * 32 * 2);
+    {
+        const int8_t* w = (const int8_t*)T(c1.in[1]).host.data();   // [32][1][3][3]
+        for (int lane = 0; lane < 32; ++lane) {
+            const int g = lane >> 2, t = lane & 3;
+            for (int j = 0; j < 4; ++j) {
+                const int ch = 8 * (g / 2) + 2 * j + (g % 2);        // column g of channel group j
+                for (int m = 0; m < 4; ++m) {
+                    const int dy = m >> 1, dx = m & 1, kh = t - dy;
+                    uint32_t word = 0;
+                    for (int sx = 0; sx < 4; ++sx) {
+                        const int kw = sx - dx;
+                        if (kh >= 0 && kh < 3 && kw >= 0 && kw < 3) word |= (uint32_t)(uint8_t)w[ch * 9 + kh * 3 + kw] << (8 * sx);
+                    }
+                    wfrag[(m * 4 + j) * 32 + lane] = word;
+                }
+                for (int b = 0; b < 2; ++b) {
+                    const int cc = 8 * t + 2 * j + b;                // the lane's accumulator columns 2t, 2t+1
+                    biasfrag[(j * 32 + lane) * 2 + b] = a1.bias[cc];
+                    multfrag[(j * 32 + lane) * 2 + b] = a1.mult[cc];
+                }
+            }
+        }
+    }
+    const int a_wf = pl->add_aux(wfrag.data(), wfrag.size() * 4);
+    const int a_bf = pl->add_aux(biasfrag.data(), biasfrag.size() * 4);
+    const int a_mf = pl->add_aux(multfrag.data(), multfrag.size() * 4);
+    push("Fused[QuantizeLinear+QLinearConv+Relu+MaxPool] mma", [=]() {
+        Conv1MmaArgs k{};
+        k.x = pl->p<float>(x); k.y = (int8_t*)pl->scratch(s_pool1); k.n_images = (int)B;
+        k.x_scale = a1.x_scale; k.x_zp = a1.x_zp;
+        k.wfrag = (const uint32_t*)pl->aux(a_wf); k.biasfrag = (const int32_t*)pl->aux(a_bf); k.multfrag = (const float*)pl->aux(a_mf);
+        const int blocks = std::min<int>((int)((B + C1M_G - 1) / C1M_G), ctx->sm_count * 8);
+        conv1_mma_relu_pool_kernel<<<blocks, C1M_THREADS, 0, ctx->stream>>>(k);
+        return check_launch(ctx, "conv1_mma_relu_pool_kernel");
     });
     const zant_node_attrs c2a = c2.a;
     push("Fused[QLinearConv+Relu+MaxPool] tcgen05", [=]() {
