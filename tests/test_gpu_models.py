@@ -136,3 +136,74 @@ def test_qconv_sweep_reduced_batch(zb, ctx, oracle, models, name, batch):
     got = ctx.qlinearconv(c["x"], c["x_scale"], 0, c["w"], c["w_scale"], None, c["y_scale"], 0, **kw)
     want = oracle.qlinearconv(c["x"], c["x_scale"], 0, c["w"], c["w_scale"], None, c["y_scale"], 0, **kw)
     assert np.array_equal(got, want)
+
+
+# ------------------------------------------------------------------------------------------------
+# Configuration 4 (MobileNetV2-style int8) and configuration 5 (Tiny-YOLOv3-style FP32 + int8) at a
+# resolution the oracle finishes in seconds; the layer tables, channel counts and operator mix are
+# those of the full-size networks.
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("batch,res", [(1, 96), (2, 64)])
+def test_mobilenetv2_int8_bit_exact(zb, ctx, oracle, models, batch, res):
+    g = models.mobilenetv2_int8(batch, res=res, classes=1000)
+    x = models.mobilenetv2_input(batch, res)
+    want = graph_oracle.run(oracle, g, x)
+    plan = zb.Plan(ctx, g, fuse=True)
+    got = plan.run(x)
+    assert np.array_equal(got.view(np.uint32), want[g.output].view(np.uint32))
+    # spot-check intermediates of each operator kind: depthwise conv, residual add, global pool
+    kinds = {}
+    for n in g.nodes:
+        key = n["op"] + ("dw" if n["attrs"].get("group", 1) > 1 else "")
+        kinds.setdefault(key, n["outputs"][0])
+    for key, tid in kinds.items():
+        if g.tensors[tid]["data"] is None and tid != g.output:
+            assert np.array_equal(plan.read_tensor(tid), want[tid]), key
+    assert len(np.unique(want[g.output])) > 20
+    plan.close()
+
+
+def test_tiny_yolo_fp32_matches_oracle(zb, ctx, oracle, models):
+    g = models.tiny_yolo_fp32(1, res=96)
+    x = models.tiny_yolo_input(1, 96)
+    want = graph_oracle.run(oracle, g, x)
+    plan = zb.Plan(ctx, g, fuse=True)
+    got = plan.run(x)
+    for name, ref, out in (("head26", want[g.output], got), ("head13", want[g.meta["head13"]], plan.read_tensor(g.meta["head13"]))):
+        tol = 1e-4 * np.maximum(np.abs(ref), 1e-2 * np.abs(ref).max())     # the FP32 contract of the float path
+        assert np.all(np.abs(out - ref) <= tol), name
+        assert np.array_equal(out.view(np.uint32), ref.view(np.uint32)), name  # exact kernels: in fact bit-identical
+    plan.close()
+
+
+def test_tiny_yolo_int8_bit_exact(zb, ctx, oracle, models):
+    f = models.tiny_yolo_fp32(2, res=64)
+    x = models.tiny_yolo_input(2, 64)
+    scales = models.activation_scales_on_gpu(ctx, f, x)
+    q = models.tiny_yolo_int8(f, scales)
+    want = graph_oracle.run(oracle, q, x)
+    plan = zb.Plan(ctx, q, fuse=True)
+    got = plan.run(x)
+    assert np.array_equal(got.view(np.uint32), want[q.output].view(np.uint32))
+    assert np.array_equal(plan.read_tensor(q.meta["head13"]), want[q.meta["head13"]])
+    # the quantized detector tracks the FP32 one
+    ref = graph_oracle.run(oracle, f, x)[f.output]
+    assert np.abs(got - ref).max() <= 0.2 * np.abs(ref).max()
+    plan.close()
+
+
+def test_full_size_graphs_plan_and_run(zb, ctx, models):
+    """Full-size configurations 4 and 5 (224x224 and 416x416): the plans build, run and are
+    deterministic; sample 0 of a batch of 2 equals a batch-1 run (samples are independent)."""
+    g2, g1 = models.mobilenetv2_int8(2), models.mobilenetv2_int8(1)
+    x = models.mobilenetv2_input(2)
+    p2, p1 = zb.Plan(ctx, g2), zb.Plan(ctx, g1)
+    y2, y2b, y1 = p2.run(x), p2.run(x), p1.run(x[:1])
+    p2.close(); p1.close()
+    assert y2.shape == (2, 1000) and np.array_equal(y2, y2b) and np.array_equal(y2[:1], y1)
+    f = models.tiny_yolo_fp32(1)
+    pf = zb.Plan(ctx, f)
+    yf = pf.run(models.tiny_yolo_input(1))
+    assert yf.shape == (1, 255, 26, 26) and np.isfinite(yf).all()
+    assert pf.read_tensor(f.meta["head13"]).shape == (1, 255, 13, 13)
+    pf.close()

@@ -173,3 +173,255 @@ def qconv_case(name, batch=None, seed=DEFAULT_SEED):
     c["macs"] = c["N"] * c["K"] * oh * oh * (c["C"] // c["group"]) * c["k"] * c["k"]
     c["bytes"] = x.size + w.size + c["N"] * c["K"] * oh * oh
     return c
+
+
+# ------------------------------------------------------------------------------------------------
+# Small graph-building helpers for the larger synthetic networks below.
+# ------------------------------------------------------------------------------------------------
+class _Builder:
+    def __init__(self, name, seed):
+        self.g = Graph(name)
+        self.rng = np.random.default_rng(seed)
+        self.n = 0
+
+    def act(self, dtype, shape, name=None):
+        self.n += 1
+        return self.g.tensor(name or f"t{self.n}", dtype, shape)
+
+    def const(self, dtype, arr, name=None):
+        self.n += 1
+        arr = np.asarray(arr)
+        return self.g.tensor(name or f"c{self.n}", dtype, arr.shape, arr)
+
+    def shape(self, tid):
+        return list(self.g.tensors[tid]["shape"])
+
+
+def _conv_out(h, k, s, p):
+    return (h + 2 * p - k) // s + 1
+
+
+# ------------------------------------------------------------------------------------------------
+# Configuration 4: MobileNetV2-style int8 classifier (width 1.0).  Stem 3->32 3x3 s2, 17 inverted
+# residual blocks (1x1 expand x6, 3x3 depthwise, 1x1 project, residual Add where shapes match) with
+# ReLU6, channels 16/24/32/64/96/160/320 with repeats (1,2,3,4,3,3,1) and strides (1,2,2,2,1,2,1),
+# Conv 320->1280 1x1, GlobalAveragePool, 1280->classes, DequantizeLinear.  Weights: He-normal,
+# symmetric int8 per output channel.  Activation scales are fixed by construction instead of
+# calibrated: 6/127 after every ReLU6 (its exact range), 0.1 for the linear projection / residual
+# tensors, 0.05 for the pooled features and 0.1 for the logits; all zero points 0, int8 throughout.
+# ------------------------------------------------------------------------------------------------
+MBV2_STAGES = [(1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2), (6, 96, 3, 1), (6, 160, 3, 2), (6, 320, 1, 1)]
+
+
+def mobilenetv2_int8(batch, res=224, classes=1000, seed=DEFAULT_SEED):
+    b = _Builder("mobilenetv2_int8", seed + 4)
+    g = b.g
+    S6, SL = float(np.float32(6.0) / np.float32(127.0)), 0.1
+    sx = float(np.float32(1.0) / np.float32(255.0))
+    x = b.act(U8, (batch, 3, res, res), "x")
+    macs = 0
+
+    def qconv(src, s_in, cin, cout, k, stride, group, s_out, act, x_dtype_scale=None):
+        nonlocal macs
+        n, _, h, w_ = b.shape(src)
+        p = k // 2
+        oh, ow = _conv_out(h, k, stride, p), _conv_out(w_, k, stride, p)
+        wf = he_normal(b.rng, (cout, cin // group, k, k), (cin // group) * k * k)
+        wq, ws = quantize_weights(wf, 0)
+        out = b.act(I8, (n, cout, oh, ow))
+        g.node("QLinearConv", [src, b.const(I8, wq), b.const(F32, ws), -1, b.const(I32, np.zeros(cout, np.int32))], [out],
+               x_scale=s_in, x_zp=0, y_scale=s_out, y_zp=0, strides=(stride, stride), pads=(p, p, p, p), dilations=(1, 1),
+               group=group, auto_pad="NOTSET", activation=act)
+        macs += oh * ow * cout * (cin // group) * k * k
+        return out
+
+    cur = qconv(x, sx, 3, 32, 3, 2, 1, S6, "relu6")
+    s_cur, cin = S6, 32
+    for t, c, reps, stride in MBV2_STAGES:
+        for i in range(reps):
+            st = stride if i == 0 else 1
+            src, s_src = cur, s_cur
+            h = cur
+            if t != 1:
+                h = qconv(h, s_cur, cin, cin * t, 1, 1, 1, S6, "relu6")
+            h = qconv(h, S6, cin * t, cin * t, 3, st, cin * t, S6, "relu6")
+            h = qconv(h, S6, cin * t, c, 1, 1, 1, SL, None)
+            if st == 1 and cin == c:
+                o = b.act(I8, b.shape(h))
+                g.node("QLinearAdd", [src, h], [o], x_scale=s_src, x_zp=0, b_scale=SL, b_zp=0, y_scale=SL, y_zp=0)
+                h = o
+            cur, s_cur, cin = h, SL, c
+    cur = qconv(cur, s_cur, 320, 1280, 1, 1, 1, S6, "relu6")
+    n = b.shape(cur)[0]
+    gap = b.act(I8, (n, 1280, 1, 1))
+    g.node("QLinearGlobalAveragePool", [cur], [gap], x_scale=S6, x_zp=0, y_scale=0.05, y_zp=0)
+    flat = b.act(I8, (n, 1280))
+    g.node("Reshape", [gap], [flat])
+    wf = he_normal(b.rng, (1280, classes), 1280)
+    wq, ws = quantize_weights(wf, 1)
+    fc = b.act(I8, (n, classes))
+    g.node("QLinearMatMul", [flat, b.const(I8, wq), b.const(F32, ws), -1, b.const(I32, np.zeros(classes, np.int32))], [fc],
+           x_scale=0.05, x_zp=0, y_scale=0.1, y_zp=0)
+    y = b.act(F32, (n, classes), "logits")
+    g.node("DequantizeLinear", [fc], [y], x_scale=0.1, x_zp=0)
+    g.input, g.output = x, y
+    g.meta = dict(macs_per_image=macs + 1280 * classes)
+    return g
+
+
+def mobilenetv2_input(batch, res=224, seed=DEFAULT_SEED + 5):
+    return np.random.default_rng(seed).integers(0, 256, (batch, 3, res, res), dtype=np.uint8)
+
+
+# ------------------------------------------------------------------------------------------------
+# Configuration 5: Tiny-YOLOv3-style detector.  Backbone: [Conv 3x3 + LeakyReLU(0.1) + MaxPool 2/2]
+# with channels 16/32/64/128/256, then 512 with a stride-1 2x2 MaxPool (SAME_UPPER), then Conv 1024.
+# Heads: Conv 1x1 1024->256; head 1 = Conv 3x3 256->512, Conv 1x1 ->255 on the 13x13 grid; head 2 =
+# Conv 1x1 256->128, Resize x2 nearest, Concat with the 26x26x256 feature, Conv 3x3 ->256, 1x1 ->255.
+# (The 1x1 1024->256 in front of both heads is the choice made where the description is ambiguous.)
+# The graph has two outputs; the plan returns head 2 (26x26) and head 1 is read as an intermediate.
+# ------------------------------------------------------------------------------------------------
+def tiny_yolo_fp32(batch, res=416, seed=DEFAULT_SEED, out_ch=255):
+    b = _Builder("tiny_yolo_fp32", seed + 6)
+    g = b.g
+    x = b.act(F32, (batch, 3, res, res), "x")
+    macs = 0
+
+    def conv(src, cout, k, act=True, name=None):
+        nonlocal macs
+        n, cin, h, w_ = b.shape(src)
+        p = k // 2
+        wf = he_normal(b.rng, (cout, cin, k, k), cin * k * k)
+        c = b.act(F32, (n, cout, h, w_))
+        g.node("Conv", [src, b.const(F32, wf), b.const(F32, np.zeros(cout, np.float32))], [c], strides=(1, 1), pads=(p, p, p, p),
+               dilations=(1, 1), group=1, auto_pad="NOTSET")
+        macs += h * w_ * cout * cin * k * k
+        if not act:
+            g.tensors[c]["name"] = name or g.tensors[c]["name"]
+            return c
+        a = b.act(F32, (n, cout, h, w_), name)
+        g.node("LeakyRelu", [c], [a], alpha=0.1)
+        return a
+
+    def pool(src, stride):
+        n, c, h, w_ = b.shape(src)
+        if stride == 2:
+            o = b.act(F32, (n, c, h // 2, w_ // 2))
+            g.node("MaxPool", [src], [o], kernel_shape=(2, 2), strides=(2, 2), dilations=(1, 1), pads=(0, 0, 0, 0), auto_pad="NOTSET")
+        else:
+            o = b.act(F32, (n, c, h, w_))
+            g.node("MaxPool", [src], [o], kernel_shape=(2, 2), strides=(1, 1), dilations=(1, 1), pads=(0, 0, 0, 0), auto_pad="SAME_UPPER")
+        return o
+
+    cur = x
+    feat26 = None
+    for i, ch in enumerate((16, 32, 64, 128, 256)):
+        cur = conv(cur, ch, 3)
+        if ch == 256:
+            feat26 = cur
+        cur = pool(cur, 2)
+    cur = pool(conv(cur, 512, 3), 1)
+    cur = conv(cur, 1024, 3)
+    neck = conv(cur, 256, 1)
+    head1 = conv(conv(neck, 512, 3), out_ch, 1, act=False, name="head13")
+    up_in = conv(neck, 128, 1)
+    n, c, h, w_ = b.shape(up_in)
+    up = b.act(F32, (n, c, 2 * h, 2 * w_))
+    g.node("Resize", [up_in], [up], scales=(1.0, 1.0, 2.0, 2.0), coord_mode="half_pixel")
+    cat = b.act(F32, (n, c + 256, 2 * h, 2 * w_))
+    g.node("Concat", [up, feat26], [cat], axis=1)
+    head2 = conv(conv(cat, 256, 3), out_ch, 1, act=False, name="head26")
+    g.input, g.output = x, head2
+    g.meta = dict(macs_per_image=macs, head13=head1, head26=head2)
+    return g
+
+
+def tiny_yolo_input(batch, res=416, seed=DEFAULT_SEED + 7):
+    return np.random.default_rng(seed).random((batch, 3, res, res), dtype=np.float32)
+
+
+def tiny_yolo_int8(fp32_graph, act_scales):
+    """QDQ/QLinear form of a tiny_yolo_fp32 graph: QuantizeLinear(uint8, 1/255) on the input, every
+    Conv -> QLinearConv (int8 per-channel weights from the FP32 graph's own weights), LeakyReLU as a
+    requantising 256-entry table, MaxPool / Resize / Concat on int8 codes (Concat inputs are brought
+    to one scale by the producer's y_scale), DequantizeLinear on the 26x26 head.
+    `act_scales`: tensor name -> scale for every FP32 activation tensor (zero point 0)."""
+    f = fp32_graph
+    b = _Builder("tiny_yolo_int8", 0)
+    g = b.g
+    sx = float(np.float32(1.0) / np.float32(255.0))
+    m = {}            # fp32 tensor id -> (int8 tensor id, scale)
+    xin = b.act(F32, f.tensors[f.input]["shape"], "x")
+    xq = b.act(U8, f.tensors[f.input]["shape"], "xq")
+    g.node("QuantizeLinear", [xin], [xq], y_scale=sx, y_zp=0)
+    m[f.input] = (xq, sx)
+    # Concat needs equal scales on its inputs: give both producers the larger of the two scales.
+    forced = {}
+    for n in f.nodes:
+        if n["op"] == "Concat":
+            s = max(act_scales[f.tensors[i]["name"]] for i in n["inputs"])
+            for i in n["inputs"]:
+                forced[i] = s
+            forced[n["outputs"][0]] = s
+    # Resize / MaxPool keep the scale of their input; propagate forced scales backwards through them.
+    changed = True
+    while changed:
+        changed = False
+        for n in f.nodes:
+            if n["op"] in ("Resize", "MaxPool") and n["outputs"][0] in forced and n["inputs"][0] not in forced:
+                forced[n["inputs"][0]] = forced[n["outputs"][0]]
+                changed = True
+
+    def scale_of(tid):
+        return forced.get(tid, act_scales[f.tensors[tid]["name"]])
+
+    for n in f.nodes:
+        op, a = n["op"], n["attrs"]
+        out_t = f.tensors[n["outputs"][0]]
+        o = n["outputs"][0]
+        if op == "Conv":
+            src, s_in = m[n["inputs"][0]]
+            wf = f.tensors[n["inputs"][1]]["data"]
+            wq, ws = quantize_weights(wf, 0)
+            s_out = scale_of(o)
+            q = b.act(I8, out_t["shape"], out_t["name"])
+            g.node("QLinearConv", [src, b.const(I8, wq), b.const(F32, ws), -1, b.const(I32, np.zeros(wq.shape[0], np.int32))], [q],
+                   x_scale=s_in, x_zp=0, y_scale=s_out, y_zp=0, strides=a["strides"], pads=a["pads"], dilations=a["dilations"],
+                   group=1, auto_pad="NOTSET")
+            m[o] = (q, s_out)
+        elif op == "LeakyRelu":
+            src, s_in = m[n["inputs"][0]]
+            s_out = scale_of(o)
+            q = b.act(I8, out_t["shape"], out_t["name"])
+            g.node("LeakyRelu", [src], [q], alpha=a["alpha"], x_scale=s_in, x_zp=0, y_scale=s_out, y_zp=0)
+            m[o] = (q, s_out)
+        elif op in ("MaxPool", "Resize"):
+            src, s_in = m[n["inputs"][0]]
+            q = b.act(I8, out_t["shape"], out_t["name"])
+            g.node(op, [src], [q], **a)
+            m[o] = (q, s_in)
+        elif op == "Concat":
+            srcs = [m[i] for i in n["inputs"]]
+            assert len({s for _, s in srcs}) == 1
+            q = b.act(I8, out_t["shape"], out_t["name"])
+            g.node("Concat", [s for s, _ in srcs], [q], **a)
+            m[o] = (q, srcs[0][1])
+        else:
+            raise NotImplementedError(op)
+    last, s_last = m[f.output]
+    y = b.act(F32, f.tensors[f.output]["shape"], "head26_f32")
+    g.node("DequantizeLinear", [last], [y], x_scale=s_last, x_zp=0)
+    g.input, g.output = xin, y
+    g.meta = dict(macs_per_image=f.meta["macs_per_image"], head13=m[f.meta["head13"]][0], head13_scale=m[f.meta["head13"]][1])
+    return g
+
+
+def activation_scales_on_gpu(ctx, fp32_graph, calib_x):
+    """max|a|/127 of every non-constant tensor of an FP32 graph, from one run of its plan."""
+    plan = Plan(ctx, fp32_graph, fuse=False)
+    try:
+        plan.run(calib_x)
+        acts = {t["name"]: plan.read_tensor(i) for i, t in enumerate(fp32_graph.tensors) if t["data"] is None and i != fp32_graph.input}
+    finally:
+        plan.close()
+    return act_scales_from(acts)
