@@ -128,3 +128,49 @@ def test_leaky_relu_lut(ctx, oracle, dt, n):
     zi, zo = (3, 5) if dt == U8 else (0, 0)
     ref = oracle.quantize_linear(oracle.leakyReLU(oracle.dequantize_linear(x, 0.05, zi), 0.1), 0.04, zo, dt)
     assert np.array_equal(want, ref)
+
+
+# ---- tensor-core path (im2col into the GEMM-blocked layout + tcgen05 GEMM): taken for group 1,
+# ---- zero weight zero points and at least 256 output positions
+TC_QCONV = [
+    # N C H W M k stride pads dil xdt ydt xzp yzp per_channel bias act
+    (2, 64, 20, 20, 64, 3, (1, 1), (1, 1, 1, 1), (1, 1), I8, I8, 0, 0, False, False, None),
+    (4, 24, 17, 19, 40, 3, (2, 2), (1, 0, 2, 1), (1, 1), U8, U8, 128, 7, True, True, "relu6"),
+    (2, 7, 23, 23, 130, 5, (1, 2), (2, 2, 2, 2), (2, 1), I8, I8, -5, 3, True, True, "relu"),
+    (2, 256, 16, 16, 300, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, U8, 0, 100, True, True, None),
+    (4, 3, 32, 32, 32, 3, (2, 2), (1, 1, 1, 1), (1, 1), U8, I8, 0, 0, True, False, "relu6"),
+]
+
+
+@pytest.mark.parametrize("case", TC_QCONV, ids=[f"tcqconv{i}" for i in range(len(TC_QCONV))])
+def test_qlinearconv_tensor_core_path(ctx, oracle, case):
+    N, C, H, W, M, k, stride, pads, dil, xdt, ydt, xzp, yzp, per_ch, has_bias, act = case
+    rng = np.random.default_rng(N * 31 + C + M)
+    x = q(rng, (N, C, H, W), xdt)
+    w = rng.integers(-127, 128, (M, C, k, k), dtype=np.int8)
+    ws = (rng.random(M if per_ch else 1, dtype=np.float32) * 0.02 + 0.001).astype(np.float32)
+    bias = rng.integers(-3000, 3000, M).astype(np.int32) if has_bias else None
+    y_scale = 0.015 * np.sqrt(C * k * k)
+    kw = dict(bias=bias, y_dtype=ydt, stride=stride, pads=pads, dilations=dil, group=1, activation=act)
+    before = ctx.launch_count()
+    got = ctx.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
+    assert ctx.launch_count() - before == 2          # im2col + GEMM, not the generic kernel
+    want = oracle.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
+    assert got.shape == want.shape and np.array_equal(got, want)
+    assert len(np.unique(want)) > 8
+
+
+@pytest.mark.parametrize("M,K,N", [(256, 64, 64), (1000, 1600, 512), (300, 70, 10), (513, 1280, 1000)])
+@pytest.mark.parametrize("adt,ydt,azp,yzp,act", [(I8, I8, 0, 0, "relu"), (U8, U8, 128, 7, None), (I8, I8, 9, -4, "relu6")])
+def test_qlinearmatmul_tensor_core_path(ctx, oracle, M, K, N, adt, ydt, azp, yzp, act):
+    rng = np.random.default_rng(M + K + N)
+    a = q(rng, (M, K), adt)
+    b = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    bs = (rng.random(N, dtype=np.float32) * 0.01 + 0.001).astype(np.float32)
+    bias = rng.integers(-500, 500, N).astype(np.int32)
+    ys = 0.02 * np.sqrt(K)
+    before = ctx.launch_count()
+    got = ctx.qlinearmatmul(a, 0.02, azp, b, bs, None, ys, yzp, bias, ydt, act)
+    assert ctx.launch_count() - before == 2
+    want = oracle.qlinearmatmul(a, 0.02, azp, b, bs, None, ys, yzp, bias, ydt, act)
+    assert np.array_equal(got, want)

@@ -14,6 +14,7 @@
 #include "geometry.hpp"
 #include "ops.cuh"
 #include "tc_peak.cuh"
+#include "tc_conv_generic.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -27,7 +28,6 @@ using namespace zb;
         ZB_CUDA(cudaSetDevice((ctx)->device));                                                               \
     } while (0)
 
-#define ZB_TRY(expr) do { int32_t _s = (expr); if (_s != ZANT_OK) return _s; } while (0)
 
 extern "C" {
 
@@ -443,6 +443,22 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
     requant_multipliers(x_scale, w_scale, n_w_scale, y_scale, (size_t)g.M, mult);
     std::vector<int32_t> wz((size_t)g.M, 0);
     if (w_zp) for (int m = 0; m < g.M; ++m) wz[m] = w_zp[n_w_scale == 1 ? 0 : m];
+    bool wz_zero = true;
+    for (int32_t v : wz) wz_zero = wz_zero && v == 0;
+    if (qconv_tc_eligible(g, wz_zero) && !is_device_ptr(w) && !(bias && is_device_ptr(bias))) {
+        // tensor-core path: im2col into the GEMM-blocked layout, tcgen05 GEMM, NCHW requantised store
+        QGemmPrep prep;
+        qgemm_prepare(w, g.M, g.Cg * g.KH * g.KW, mult.data(), bias, x_zp, prep);
+        Stager s(ctx);
+        const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
+        const int iw = s.in(prep.w_blk.data(), prep.w_blk.size()), im = s.in(prep.mult.data(), prep.mult.size() * 4);
+        const int ib = s.in(prep.bias.data(), prep.bias.size() * 4);
+        const int ia = s.scratch(qgemm_a_bytes((size_t)g.N * g.OH * g.OW, prep));
+        ZB_TRY(s.commit());
+        ZB_TRY(run_qconv_tc(ctx, g, s.ptr<char>(ix), x_dtype == ZANT_U8, x_zp, prep, s.ptr<int8_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
+                            s.ptr<uint8_t>(ia), s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}));
+        return s.finish();
+    }
     Stager s(ctx);
     const int ix = s.in(x, numel(x_shape, 4)), iw = s.in(w, numel(w_shape, 4)), iy = s.out(y, numel(y_shape, 4));
     const int im = s.in(mult.data(), mult.size() * 4), iz = s.in(wz.data(), wz.size() * 4), ib = s.in(bias, (size_t)g.M * 4);
@@ -478,6 +494,28 @@ int32_t zant_b200_qlinearmatmul(zant_ctx* ctx, int32_t a_dtype, const void* a, c
     requant_multipliers(a_scale, b_scale, n_b_scale, y_scale, N, mult);
     std::vector<int32_t> bz(N, 0);
     if (b_zp) for (size_t j = 0; j < N; ++j) bz[j] = b_zp[n_b_scale == 1 ? 0 : j];
+    bool bz_zero = true;
+    for (int32_t v : bz) bz_zero = bz_zero && v == 0;
+    {
+        ConvGeom g{};   // a matrix product is a 1x1 convolution over M "images" of one pixel
+        g.N = (int)M; g.C = (int)K; g.H = g.W = 1; g.M = (int)N; g.Cg = (int)K; g.KH = g.KW = 1;
+        g.sh = g.sw = g.dh = g.dw = 1; g.OH = g.OW = 1; g.G = 1;
+        if (y_dtype != ZANT_I32 && qconv_tc_eligible(g, bz_zero) && !is_device_ptr(b) && !(bias && is_device_ptr(bias))) {
+            std::vector<int8_t> bt(K * N);
+            for (size_t k = 0; k < K; ++k) for (size_t j = 0; j < N; ++j) bt[j * K + k] = b[k * N + j];
+            QGemmPrep prep;
+            qgemm_prepare(bt.data(), (int)N, (int)K, mult.data(), bias, a_zp, prep);
+            Stager s(ctx);
+            const int ix = s.in(a, M * K), iy = s.out(y, M * N);
+            const int iw = s.in(prep.w_blk.data(), prep.w_blk.size()), im = s.in(prep.mult.data(), prep.mult.size() * 4);
+            const int ibb = s.in(prep.bias.data(), prep.bias.size() * 4);
+            const int isc = s.scratch(qgemm_a_bytes(M, prep));
+            ZB_TRY(s.commit());
+            ZB_TRY(run_qconv_tc(ctx, g, s.ptr<char>(ix), a_dtype == ZANT_U8, a_zp, prep, s.ptr<int8_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ibb),
+                                s.ptr<uint8_t>(isc), s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}));
+            return s.finish();
+        }
+    }
     Stager s(ctx);
     const int ia = s.in(a, M * K), ib = s.in(b, K * N), iy = s.out(y, M * N * dtype_size(y_dtype));
     const int im = s.in(mult.data(), N * 4), iz = s.in(bz.data(), N * 4), ibias = s.in(bias, N * 4);

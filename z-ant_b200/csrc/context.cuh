@@ -28,6 +28,10 @@ namespace zb {
             return zb::fail(ZANT_E_CUDA, "%s -> %s", #expr, cudaGetErrorString(_e));          \
     } while (0)
 
+#ifndef ZB_TRY
+#define ZB_TRY(expr) do { int32_t _s = (expr); if (_s != ZANT_OK) return _s; } while (0)
+#endif
+
 inline int32_t check_launch(zant_ctx* ctx, const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(ZANT_E_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));

@@ -1,0 +1,133 @@
+// Tensor-core path for QLinearConv of any geometry with group 1 (and for QLinearMatMul):
+//   1. im2col_blocked_kernel gathers the NCHW input into the GEMM-blocked A layout
+//      [row tile of 128][K/16][128 rows][16], rows = (image, oh, ow), K = (c, kh, kw) in the
+//      weight's own order, padded taps filled with the input zero point, K padded with zeros;
+//   2. tc_gemm_i8_kernel<NT, 4, 8, MODE|2> multiplies by the re-blocked weights on tcgen05 and
+//      requantises straight into the NCHW output.
+// The zero point of x is folded into the bias (bias - x_zp * sum(w)), which is exact because
+// padded taps hold x_zp; weight zero points other than 0 are not handled here (generic kernel).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <vector>
+
+#include "context.cuh"
+#include "geometry.hpp"
+#include "tc_gemm.cuh"
+
+namespace zb {
+
+struct Im2colArgs {
+    const uint8_t* x; uint8_t* a;
+    ConvGeom g;
+    int K, K16, M;       // K = C*KH*KW, K16 = padded K / 16, M = N*OH*OW
+    int pad_value;       // raw byte written for padded taps (the input zero point)
+};
+
+__global__ void im2col_blocked_kernel(const Im2colArgs p) {
+    const ConvGeom& g = p.g;
+    const size_t total = (size_t)((p.M + 127) / 128) * p.K16 * 128;
+    const int khw = g.KH * g.KW, ohw = g.OH * g.OW;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i & 127);
+        const size_t t = i >> 7;
+        const int k16 = (int)(t % p.K16);
+        const int m = (int)(t / p.K16) * 128 + r;
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+        if (m < p.M) {
+            const int n = m / ohw, pos = m - n * ohw;
+            const int oh = pos / g.OW, ow = pos - oh * g.OW;
+            const int ih0 = oh * g.sh - g.pt, iw0 = ow * g.sw - g.pl;
+            const uint8_t* xn = p.x + (size_t)n * g.C * g.H * g.W;
+            int k = k16 * 16;
+            int c = k / khw, rem = k - c * khw;
+            int kh = rem / g.KW, kw = rem - kh * g.KW;
+#pragma unroll
+            for (int j = 0; j < 16; ++j, ++k) {
+                uint32_t v = 0;
+                if (k < p.K) {
+                    const int ih = ih0 + kh * g.dh, iw = iw0 + kw * g.dw;
+                    v = (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) ? (uint32_t)__ldg(xn + ((size_t)c * g.H + ih) * g.W + iw) : (uint32_t)(p.pad_value & 255);
+                    if (++kw == g.KW) { kw = 0; if (++kh == g.KH) { kh = 0; ++c; } }
+                }
+                w[j >> 2] |= v << (8 * (j & 3));
+            }
+        }
+        reinterpret_cast<uint4*>(p.a)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// Host-side preparation of one convolution / matrix product for the tensor-core path.
+struct QGemmPrep {
+    int NT = 0, N_pad = 0, K = 0, K16 = 0;
+    std::vector<int8_t> w_blk;     // [N_pad/NT][K16][NT][16]
+    std::vector<float> mult;       // [N_pad]
+    std::vector<int32_t> bias;     // [N_pad], includes -x_zp * sum(w)
+};
+
+// w: [n_out][K] int8 row-major (a convolution's [M][C][KH][KW] weight is exactly that).
+inline void qgemm_prepare(const int8_t* w, int n_out, int K, const float* mult, const int32_t* bias, int x_zp, QGemmPrep& p) {
+    p.NT = n_out <= 64 ? 64 : (n_out <= 128 ? 128 : 256);
+    p.N_pad = (n_out + p.NT - 1) / p.NT * p.NT;
+    p.K = K;
+    p.K16 = (K + 63) / 64 * 4;
+    p.w_blk.assign((size_t)p.N_pad * p.K16 * 16, 0);
+    p.mult.assign(p.N_pad, 1.0f);
+    p.bias.assign(p.N_pad, 0);
+    for (int n = 0; n < n_out; ++n) {
+        int sum = 0;
+        const int8_t* wr = w + (size_t)n * K;
+        int8_t* dst_tile = p.w_blk.data() + (size_t)(n / p.NT) * p.K16 * p.NT * 16 + (size_t)(n % p.NT) * 16;
+        for (int k = 0; k < K; ++k) {
+            dst_tile[(size_t)(k >> 4) * p.NT * 16 + (k & 15)] = wr[k];
+            sum += wr[k];
+        }
+        p.mult[n] = mult[n];
+        p.bias[n] = (bias ? bias[n] : 0) - x_zp * sum;
+    }
+}
+
+inline size_t qgemm_a_bytes(size_t rows, const QGemmPrep& p) { return (rows + 127) / 128 * 128 * (size_t)p.K16 * 16; }
+
+template <int NT, int MODE>
+inline int32_t launch_tc_gemm(zant_ctx* ctx, const TcGemmArgs& k, int tiles) {
+    using Cfg = TcGemmCfg<NT, 4, 8>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        ZB_CUDA(cudaFuncSetAttribute(tc_gemm_i8_kernel<NT, 4, 8, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    tc_gemm_i8_kernel<NT, 4, 8, MODE><<<std::min(tiles, ctx->sm_count), Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
+    return check_launch(ctx, "tc_gemm_i8_kernel");
+}
+
+// im2col + GEMM on device buffers.  `a_blk` is scratch of qgemm_a_bytes(N*OH*OW) bytes.
+inline int32_t run_qconv_tc(zant_ctx* ctx, const ConvGeom& g, const void* x, bool x_u8, int x_zp, const QGemmPrep& p,
+                            const int8_t* w_blk_dev, const float* mult_dev, const int32_t* bias_dev, uint8_t* a_blk,
+                            void* y, bool y_u8, const Requant& rq) {
+    const long long M = (long long)g.N * g.OH * g.OW;
+    if (M <= 0 || M > 0x7fffff00LL) return fail(ZANT_E_TOO_LARGE, "too many output positions for the tensor-core path");
+    Im2colArgs ia{};
+    ia.x = (const uint8_t*)x; ia.a = a_blk; ia.g = g; ia.K = p.K; ia.K16 = p.K16; ia.M = (int)M; ia.pad_value = x_zp;
+    const size_t chunks = (size_t)((M + 127) / 128) * p.K16 * 128;
+    im2col_blocked_kernel<<<grid_for(chunks, 256, ctx->sm_count, 16), 256, 0, ctx->stream>>>(ia);
+    ZB_TRY(check_launch(ctx, "im2col_blocked_kernel"));
+    TcGemmArgs k{};
+    k.a = (const int8_t*)a_blk; k.w = w_blk_dev; k.mult = mult_dev; k.bias = bias_dev; k.y = (int8_t*)y;
+    k.M = (int)M; k.N = p.N_pad; k.K16 = p.K16; k.y_scale = rq.y_scale; k.y_zp = rq.y_zp; k.act = rq.act; k.status = ctx->status_word;
+    k.n_valid = g.M; k.ohw = g.OH * g.OW; k.out_u8 = y_u8 ? 1 : 0;
+    const int tiles = (int)((M + 127) / 128) * (p.N_pad / p.NT);
+    if (p.NT == 64) return x_u8 ? launch_tc_gemm<64, 3>(ctx, k, tiles) : launch_tc_gemm<64, 2>(ctx, k, tiles);
+    if (p.NT == 128) return x_u8 ? launch_tc_gemm<128, 3>(ctx, k, tiles) : launch_tc_gemm<128, 2>(ctx, k, tiles);
+    return x_u8 ? launch_tc_gemm<256, 3>(ctx, k, tiles) : launch_tc_gemm<256, 2>(ctx, k, tiles);
+}
+
+// Work is worth the tensor-core path when there is at least one full row tile and the operands fit.
+inline bool qconv_tc_eligible(const ConvGeom& g, bool w_zp_all_zero) {
+    const long long M = (long long)g.N * g.OH * g.OW;
+    const long long K = (long long)g.Cg * g.KH * g.KW;
+    return g.G == 1 && w_zp_all_zero && M >= 256 && g.M <= 1024 && K <= 65536 && (M + 127) / 128 * 128 * ((K + 63) / 64 * 64) <= (8LL << 30);
+}
+
+}  // namespace zb

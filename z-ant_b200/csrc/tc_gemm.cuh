@@ -32,9 +32,12 @@ struct TcGemmArgs {
     const float* mult;     // [N]
     const int32_t* bias;   // [N]
     int8_t* y;             // [M][N] row-major
-    int M, N, K16;         // K16 = K/16, a multiple of KC
+    int M, N, K16;         // N = padded column count (multiple of NT), K16 = K/16, a multiple of KC
     float y_scale; int y_zp; int act;
     int* status;
+    // MODE & 2 (convolution output): valid columns (output channels), positions per image (OH*OW)
+    // and output type; rows are (image, position) and the result is stored NCHW.
+    int n_valid; int ohw; int out_u8;
 };
 
 template <int NT, int KC, int STAGES>
@@ -58,7 +61,10 @@ struct TcGemmCfg {
 };
 
 // Requires: int8 output with zero point 0, positive finite multipliers, N <= MAX_N (host-checked).
-template <int NT, int KC, int STAGES>
+// MODE bit 0: A holds uint8 (else int8).  MODE bit 1: general requantisation (any zero point,
+// int8 or uint8, ReLU / ReLU6) and NCHW store; otherwise the lean int8 / zero-point-0 form with a
+// row-major [M][N] store.
+template <int NT, int KC, int STAGES, int MODE = 0>
 __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constant__ TcGemmArgs a) {
     using Cfg = TcGemmCfg<NT, KC, STAGES>;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -119,7 +125,7 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constan
         }
     } else if (warp == 1) {
         if (ptx::elect_one()) {
-            constexpr uint32_t idesc = ptx::idesc_i8(128, NT, true, true);
+            constexpr uint32_t idesc = ptx::idesc_i8(128, NT, (MODE & 1) == 0, true);
             int it = 0, tile_it = 0;
             for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
                 const int b = tile_it & 1;
@@ -165,28 +171,50 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constan
             const int tcol0 = half * Cfg::COLS_PER_WARP;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * NT + tcol0);
             const int grow = m * 128 + row;
-            int8_t* yrow = a.y + (size_t)grow * a.N + (size_t)n * NT + tcol0;
+            if constexpr ((MODE & 2) == 0) {
+                int8_t* yrow = a.y + (size_t)grow * a.N + (size_t)n * NT + tcol0;
 #pragma unroll 1
-            for (int h = 0; h < Cfg::COLS_PER_WARP / 32; ++h) {
-                uint32_t v[32];
-                ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
-                ptx::tmem_wait_ld();
-                const int col0 = n * NT + tcol0 + h * 32;
-                uint32_t packed[8];
+                for (int h = 0; h < Cfg::COLS_PER_WARP / 32; ++h) {
+                    uint32_t v[32];
+                    ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
+                    ptx::tmem_wait_ld();
+                    const int col0 = n * NT + tcol0 + h * 32;
+                    uint32_t packed[8];
 #pragma unroll
-                for (int j4 = 0; j4 < 8; ++j4) {
-                    const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
-                    const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
-                    const int q0 = rq_round((int)v[j4 * 4 + 0] + b4.x, m4.x);
-                    const int q1 = rq_round((int)v[j4 * 4 + 1] + b4.y, m4.y);
-                    const int q2 = rq_round((int)v[j4 * 4 + 2] + b4.z, m4.z);
-                    const int q3 = rq_round((int)v[j4 * 4 + 3] + b4.w, m4.w);
-                    const uint32_t pk = pack_sat_s8x4(q0, q1, q2, q3);
-                    packed[j4] = relu ? relu_s8x4(pk) : pk;
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
+                        const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
+                        const int q0 = rq_round((int)v[j4 * 4 + 0] + b4.x, m4.x);
+                        const int q1 = rq_round((int)v[j4 * 4 + 1] + b4.y, m4.y);
+                        const int q2 = rq_round((int)v[j4 * 4 + 2] + b4.z, m4.z);
+                        const int q3 = rq_round((int)v[j4 * 4 + 3] + b4.w, m4.w);
+                        const uint32_t pk = pack_sat_s8x4(q0, q1, q2, q3);
+                        packed[j4] = relu ? relu_s8x4(pk) : pk;
+                    }
+                    if (grow < a.M) {
+                        reinterpret_cast<uint4*>(yrow + h * 32)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        reinterpret_cast<uint4*>(yrow + h * 32)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    }
                 }
-                if (grow < a.M) {
-                    reinterpret_cast<uint4*>(yrow + h * 32)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    reinterpret_cast<uint4*>(yrow + h * 32)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {
+                // rows are (image, position): consecutive lanes hold consecutive positions, so for a
+                // fixed channel a warp writes 32 consecutive bytes of the NCHW output
+                const Requant rq{a.y_scale, a.y_zp, a.act};
+                const int img = grow / a.ohw, pos = grow - img * a.ohw;
+                uint8_t* ybase = reinterpret_cast<uint8_t*>(a.y) + (size_t)img * a.n_valid * a.ohw + pos;
+#pragma unroll 1
+                for (int h = 0; h < Cfg::COLS_PER_WARP / 32; ++h) {
+                    uint32_t v[32];
+                    ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
+                    ptx::tmem_wait_ld();
+                    const int col0 = n * NT + tcol0 + h * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = col0 + j;
+                        const int acc = (int)v[j] + sBias[col];
+                        const int q = a.out_u8 ? requant_one<true>(acc, sMult[col], rq) : requant_one<false>(acc, sMult[col], rq);
+                        if (grow < a.M && col < a.n_valid) ybase[(size_t)col * a.ohw] = (uint8_t)q;
+                    }
                 }
             }
             ptx::tc_fence_before();
