@@ -6,7 +6,9 @@
 
 #include <cstdint>
 #include <cstring>
+#include <algorithm>
 #include <functional>
+#include <memory>
 #include <string>
 #include <vector>
 
@@ -16,6 +18,7 @@
 #include "ops.cuh"
 #include "fused_cnn.cuh"
 #include "tc_gemm.cuh"
+#include "tc_conv_generic.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -67,6 +70,14 @@ struct zant_plan {
     void* aux(int id) const { return arena + aux_off[id]; }
     void* scratch(int id) const { return arena + scratch_off[id]; }
     int add_scratch(size_t bytes) { scratch_bytes.push_back(bytes); return (int)scratch_bytes.size() - 1; }
+    // One buffer for the im2col matrices of all tensor-core steps: steps run one after another on
+    // one stream, so they can share it; it is as large as the largest request.
+    int im2col_scratch = -1;
+    int shared_im2col_scratch(size_t bytes) {
+        if (im2col_scratch < 0) im2col_scratch = add_scratch(bytes);
+        else scratch_bytes[im2col_scratch] = std::max(scratch_bytes[im2col_scratch], bytes);
+        return im2col_scratch;
+    }
     int add_aux(const void* data, size_t bytes) {
         aux_host.emplace_back((const char*)data, (const char*)data + bytes);
         return (int)aux_host.size() - 1;
@@ -539,8 +550,24 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
                 if (nwz != 1 && nwz != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv w_zp size");
                 for (int m = 0; m < g.M; ++m) wzv[m] = ((const int32_t*)T(wz).host.data())[nwz == 1 ? 0 : m];
             }
-            const int am = pl->add_aux(mult.data(), mult.size() * 4), az = pl->add_aux(wzv.data(), wzv.size() * 4);
             const int xzp = a.x_zp; const Requant rq{a.y_scale, a.y_zp, a.activation};
+            bool wz_zero = true;
+            for (int32_t v : wzv) wz_zero = wz_zero && v == 0;
+            if (qconv_tc_eligible(g, wz_zero) && (b < 0 || T(b).is_const)) {
+                // tensor-core path: weights re-blocked once here, im2col + tcgen05 GEMM per run
+                auto prep = std::make_shared<QGemmPrep>();
+                qgemm_prepare((const int8_t*)T(w).host.data(), g.M, g.Cg * g.KH * g.KW, mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, *prep);
+                const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size()), am = pl->add_aux(prep->mult.data(), prep->mult.size() * 4);
+                const int ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
+                const int sa = pl->shared_im2col_scratch(qgemm_a_bytes((size_t)g.N * g.OH * g.OW, *prep));
+                prep->w_blk.clear(); prep->w_blk.shrink_to_fit();
+                push("QLinearConv(tc)", [=]() {
+                    return run_qconv_tc(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, *prep, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
+                                        (const int32_t*)pl->aux(ab), (uint8_t*)pl->scratch(sa), pl->ptr(y), yd == ZANT_U8, rq);
+                });
+                return ZANT_OK;
+            }
+            const int am = pl->add_aux(mult.data(), mult.size() * 4), az = pl->add_aux(wzv.data(), wzv.size() * 4);
             push("QLinearConv", [=]() {
                 QConvArgs q{};
                 q.x = pl->ptr(x); q.w = pl->p<int8_t>(w); q.y = pl->ptr(y);
@@ -575,8 +602,31 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
                 if (nwz != 1 && nwz != N) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearMatMul b_zp size");
                 for (size_t j = 0; j < N; ++j) bz[j] = ((const int32_t*)T(wz).host.data())[nwz == 1 ? 0 : j];
             }
-            const int am = pl->add_aux(mult.data(), mult.size() * 4), az = pl->add_aux(bz.data(), bz.size() * 4);
             const int xzp = a.x_zp; const Requant rq{a.y_scale, a.y_zp, a.activation};
+            bool bz_zero = true;
+            for (int32_t v : bz) bz_zero = bz_zero && v == 0;
+            if (M <= 0x7fffffffULL && N <= 0x7fffffffULL && K <= 0x7fffffffULL) {
+                ConvGeom g{};   // a matrix product is a 1x1 convolution over M "images" of one pixel
+                g.N = (int)M; g.C = (int)K; g.H = g.W = 1; g.M = (int)N; g.Cg = (int)K; g.KH = g.KW = 1;
+                g.sh = g.sw = g.dh = g.dw = 1; g.OH = g.OW = 1; g.G = 1;
+                if (yd != ZANT_I32 && qconv_tc_eligible(g, bz_zero) && (b < 0 || T(b).is_const)) {
+                    std::vector<int8_t> bt(K * N);
+                    const int8_t* bw = (const int8_t*)T(w).host.data();
+                    for (size_t k = 0; k < K; ++k) for (size_t j = 0; j < N; ++j) bt[j * K + k] = bw[k * N + j];
+                    auto prep = std::make_shared<QGemmPrep>();
+                    qgemm_prepare(bt.data(), (int)N, (int)K, mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, *prep);
+                    const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size()), am = pl->add_aux(prep->mult.data(), prep->mult.size() * 4);
+                    const int ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
+                    const int sa = pl->shared_im2col_scratch(qgemm_a_bytes(M, *prep));
+                    prep->w_blk.clear(); prep->w_blk.shrink_to_fit();
+                    push("QLinearMatMul(tc)", [=]() {
+                        return run_qconv_tc(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, *prep, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
+                                            (const int32_t*)pl->aux(ab), (uint8_t*)pl->scratch(sa), pl->ptr(y), yd == ZANT_U8, rq);
+                    });
+                    return ZANT_OK;
+                }
+            }
+            const int am = pl->add_aux(mult.data(), mult.size() * 4), az = pl->add_aux(bz.data(), bz.size() * 4);
             push("QLinearMatMul", [=]() {
                 QMatArgs q{};
                 q.a = pl->ptr(x); q.b = pl->p<int8_t>(w); q.y = pl->ptr(y);
