@@ -173,6 +173,60 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_qconv_workload(args, zb, ctx, models, torch, stream, rank, world, local, int8_peak_tops):
+    """One case of the standalone QLinearConv sweep (--workload qconv3a..3d): the batch of 256
+    NCHW int8 images resident in HBM, one plan step per pass; images/s plus the op's roofline."""
+    name = args.workload[len("qconv"):]
+    graph, c = models.qconv_graph(name)
+    plan = zb.Plan(ctx, graph, fuse=not args.no_fuse)
+    x_dev = torch.from_numpy(c["x"]).cuda()
+    y_dev = torch.empty(tuple(graph.tensors[graph.output]["shape"]), dtype=torch.int8, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")      # larger than L2
+    run = lambda: plan.run(x_dev, out=y_dev)    # noqa: E731
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            run()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local) if rank == 0 else None
+        if sampler:
+            sampler.start()
+        ctx.reset_launch_count()
+        times = []
+        for _ in range(args.steps):
+            flush.fill_(1)                                                # evict x, w and y from L2 between passes
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream); run(); e1.record(stream)
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        launches = ctx.launch_count()
+        clocks = sampler.stop() if sampler else None
+    ms = float(np.mean(times))
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        peaks = measured_peaks()
+        ridge = int8_peak_tops * 1e12 / (peaks["hbm_gbs"] * 1e9)
+        tops, gbs = 2.0 * c["macs"] / (ms / 1e3) / 1e12, c["bytes"] / (ms / 1e3) / 1e9
+        if 2.0 * c["macs"] / c["bytes"] > ridge:
+            roof = dict(bound="tensor", achieved=tops, peak=int8_peak_tops, unit="TFLOP/s", frac=tops / int8_peak_tops)
+        else:
+            roof = dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"])
+        roof.update(traffic=None, kernel=" + ".join(plan.step_names()), launch_ms=ms, algorithmic_bytes=c["bytes"], macs=c["macs"],
+                    peak_source=peaks["source"], tops=tops, gbs=gbs)
+        shape = {k: c[k] for k in ("N", "C", "H", "W", "K", "k", "s", "p", "group")}
+        line = dict(metric=f"int8 images/sec (standalone QLinearConv, sweep case {name})", value=c["N"] * world / (ms / 1e3), unit="images/s",
+                    n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="weak",
+                    vs_baseline=None, dtype="int8", data="synthetic",
+                    config=dict(workload=f"QLinearConv sweep case {name}", layout="NCHW int8 in and out", l2="256 MiB written between passes",
+                                parallelism=f"replicas x{world}, no collective", **shape),
+                    roofline=roof, int8_peak_tops=int8_peak_tops, cpu_baseline=None, e2e=None, gpu_launches=int(launches) * world, clocks=clocks)
+        print(json.dumps(line), flush=True)
+    plan.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -182,6 +236,8 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU per step")
     ap.add_argument("--no-fuse", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--workload", default="small_cnn_int8", choices=["small_cnn_int8", "qconv3a", "qconv3b", "qconv3c", "qconv3d"],
+                    help="small_cnn_int8 is the headline workload; the qconv cases time one standalone operator")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="chunks of the batch that the end-to-end path pipelines")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
@@ -209,6 +265,13 @@ def main():
     batch = args.batch
 
     int8_peak_tops = ctx.measure_int8_peak(20000) if rank == 0 else None   # resident-tile tcgen05 probe, ~15 ms
+
+    if args.workload.startswith("qconv"):
+        run_qconv_workload(args, zb, ctx, models, torch, stream, rank, world, local, ctx.measure_int8_peak(20000))
+        ctx.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # calibration on the GPU through the FP32 plan (configuration 1 at batch 256), then the int8 graph
     scales = models.calibrate_on_gpu(ctx, models.small_cnn_fp32(256), models.small_cnn_input(256, models.DEFAULT_SEED + 1))

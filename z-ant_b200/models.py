@@ -178,6 +178,21 @@ def qconv_case(name, batch=None, seed=DEFAULT_SEED):
 # ------------------------------------------------------------------------------------------------
 # Small graph-building helpers for the larger synthetic networks below.
 # ------------------------------------------------------------------------------------------------
+def qconv_graph(name, batch=None, seed=DEFAULT_SEED):
+    """One sweep case as a one-node graph (int8 NCHW in, int8 NCHW out); returns (graph, case)."""
+    c = qconv_case(name, batch, seed)
+    g = Graph("qconv_" + name)
+    oh = (c["H"] + 2 * c["p"] - c["k"]) // c["s"] + 1
+    x = g.tensor("x", I8, c["x"].shape)
+    w = g.tensor("w", I8, c["w"].shape, c["w"])
+    ws = g.tensor("w_scale", F32, (1,), c["w_scale"])
+    y = g.tensor("y", I8, (c["N"], c["K"], oh, oh))
+    g.node("QLinearConv", [x, w, ws, -1, -1], [y], x_scale=c["x_scale"], x_zp=0, y_scale=c["y_scale"], y_zp=0,
+           strides=c["stride"], pads=c["pads"], dilations=c["dilations"], group=c["group"], auto_pad="NOTSET", activation=None)
+    g.input, g.output = x, y
+    return g, c
+
+
 class _Builder:
     def __init__(self, name, seed):
         self.g = Graph(name)
