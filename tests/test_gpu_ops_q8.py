@@ -142,8 +142,43 @@ TC_QCONV = [
 ]
 
 
-@pytest.mark.parametrize("case", TC_QCONV, ids=[f"tcqconv{i}" for i in range(len(TC_QCONV))])
-def test_qlinearconv_tensor_core_path(ctx, oracle, case):
+# stride-1 cases run the implicit-GEMM kernel (one launch), the others im2col + GEMM (two launches)
+TC_QCONV_LAUNCHES = [1, 2, 2, 1, 2]
+
+IMPLICIT_QCONV = [
+    # N C H W M k stride pads dil xdt ydt xzp yzp per_channel bias act
+    (2, 64, 56, 56, 64, 3, (1, 1), (1, 1, 1, 1), (1, 1), I8, I8, 0, 0, False, False, None),         # sweep case 3a, 8-byte rows
+    (3, 3, 32, 32, 32, 3, (1, 1), (1, 1, 1, 1), (1, 1), U8, I8, 0, 0, True, True, "relu6"),          # 3 channels of a 32-channel stage
+    (2, 40, 24, 28, 72, 3, (1, 1), (1, 0, 1, 2), (1, 1), U8, U8, 128, 7, True, True, "relu"),        # partial second block, odd pads, zero points
+    (1, 16, 40, 140, 24, 3, (1, 1), (1, 1, 1, 1), (1, 1), I8, I8, -3, 5, True, True, None),          # two width segments
+    (2, 32, 36, 36, 48, 5, (1, 1), (4, 4, 4, 4), (2, 2), I8, I8, 0, -4, True, False, "relu"),        # 5x5 dilated
+    (2, 96, 20, 20, 300, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, U8, 0, 100, True, True, None),         # pointwise, 256-wide filter tiles
+    (5, 256, 8, 8, 64, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, I8, 2, 0, False, True, "relu6"),          # pointwise, 64 pixels per image
+    (2, 33, 12, 16, 130, 3, (1, 1), (0, 0, 0, 0), (1, 1), I8, I8, 0, 0, True, True, None),           # no padding, 2 filter tiles
+]
+
+
+@pytest.mark.parametrize("case", IMPLICIT_QCONV, ids=[f"implicit{i}" for i in range(len(IMPLICIT_QCONV))])
+def test_qlinearconv_implicit_gemm(ctx, oracle, case):
+    N, C, H, W, M, k, stride, pads, dil, xdt, ydt, xzp, yzp, per_ch, has_bias, act = case
+    rng = np.random.default_rng(N * 37 + C + M + W)
+    x = q(rng, (N, C, H, W), xdt)
+    w = rng.integers(-127, 128, (M, C, k, k), dtype=np.int8)
+    ws = (rng.random(M if per_ch else 1, dtype=np.float32) * 0.02 + 0.001).astype(np.float32)
+    bias = rng.integers(-3000, 3000, M).astype(np.int32) if has_bias else None
+    y_scale = 0.015 * np.sqrt(C * k * k)
+    kw = dict(bias=bias, y_dtype=ydt, stride=stride, pads=pads, dilations=dil, group=1, activation=act)
+    before = ctx.launch_count()
+    got = ctx.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
+    launches = ctx.launch_count() - before
+    want = oracle.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
+    assert np.array_equal(got, want)
+    assert launches == 1
+    assert len(np.unique(want)) > 16
+
+
+@pytest.mark.parametrize("case,launches", list(zip(TC_QCONV, TC_QCONV_LAUNCHES)), ids=[f"tcqconv{i}" for i in range(len(TC_QCONV))])
+def test_qlinearconv_tensor_core_path(ctx, oracle, case, launches):
     N, C, H, W, M, k, stride, pads, dil, xdt, ydt, xzp, yzp, per_ch, has_bias, act = case
     rng = np.random.default_rng(N * 31 + C + M)
     x = q(rng, (N, C, H, W), xdt)
@@ -154,7 +189,7 @@ def test_qlinearconv_tensor_core_path(ctx, oracle, case):
     kw = dict(bias=bias, y_dtype=ydt, stride=stride, pads=pads, dilations=dil, group=1, activation=act)
     before = ctx.launch_count()
     got = ctx.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
-    assert ctx.launch_count() - before == 2          # im2col + GEMM, not the generic kernel
+    assert ctx.launch_count() - before == launches    # a tensor-core path, not the generic kernel
     want = oracle.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
     assert got.shape == want.shape and np.array_equal(got, want)
     assert len(np.unique(want)) > 8

@@ -15,6 +15,7 @@
 #include "ops.cuh"
 #include "tc_peak.cuh"
 #include "tc_conv_generic.cuh"
+#include "tc_conv_nchw.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -445,7 +446,21 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
     if (w_zp) for (int m = 0; m < g.M; ++m) wz[m] = w_zp[n_w_scale == 1 ? 0 : m];
     bool wz_zero = true;
     for (int32_t v : wz) wz_zero = wz_zero && v == 0;
-    if (qconv_tc_eligible(g, wz_zero) && !is_device_ptr(w) && !(bias && is_device_ptr(bias))) {
+    const bool host_consts = !is_device_ptr(w) && !(bias && is_device_ptr(bias));
+    TcConvPlan tcp;
+    if (host_consts && (long long)g.N * g.OH * g.OW >= 256 && (!is_device_ptr(x) || tc_conv_ptr_ok(x)) && tc_conv_plan(g, wz_zero, tcp)) {
+        // implicit GEMM straight from NCHW (stride 1): no im2col matrix
+        std::vector<int8_t> w_blk; std::vector<float> mp; std::vector<int32_t> bp;
+        tc_conv_prepare(tcp, w, mult.data(), bias, x_zp, w_blk, mp, bp);
+        Stager s(ctx);
+        const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
+        const int iw = s.in(w_blk.data(), w_blk.size()), im = s.in(mp.data(), mp.size() * 4), ib = s.in(bp.data(), bp.size() * 4);
+        ZB_TRY(s.commit());
+        ZB_TRY(tc_conv_run(ctx, tcp, s.ptr<char>(ix), x_dtype == ZANT_U8, x_zp, s.ptr<int8_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
+                           s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}));
+        return s.finish();
+    }
+    if (qconv_tc_eligible(g, wz_zero) && host_consts) {
         // tensor-core path: im2col into the GEMM-blocked layout, tcgen05 GEMM, NCHW requantised store
         QGemmPrep prep;
         qgemm_prepare(w, g.M, g.Cg * g.KH * g.KW, mult.data(), bias, x_zp, prep);
