@@ -152,7 +152,8 @@ def test_mobilenetv2_int8_bit_exact(zb, ctx, oracle, models, batch, res):
     got = plan.run(x)
     assert np.array_equal(got.view(np.uint32), want[g.output].view(np.uint32))
     names = plan.step_names()
-    assert "QLinearConv(tc)" in names and "QLinearConv" in names     # pointwise convs on tensor cores, depthwise ones not
+    # pointwise convs: implicit GEMM; the stride-2 stem: im2col + GEMM; depthwise: the generic kernel
+    assert "QLinearConv(tc-implicit)" in names and "QLinearConv(tc)" in names and "QLinearConv" in names
     # spot-check intermediates of each operator kind: depthwise conv, residual add, global pool
     kinds = {}
     for n in g.nodes:
@@ -188,7 +189,7 @@ def test_tiny_yolo_int8_bit_exact(zb, ctx, oracle, models):
     got = plan.run(x)
     assert np.array_equal(got.view(np.uint32), want[q.output].view(np.uint32))
     assert np.array_equal(plan.read_tensor(q.meta["head13"]), want[q.meta["head13"]])
-    assert "QLinearConv(tc)" in plan.step_names()
+    assert "QLinearConv(tc-implicit)" in plan.step_names()
     # the quantized detector tracks the FP32 one
     ref = graph_oracle.run(oracle, f, x)[f.output]
     assert np.abs(got - ref).max() <= 0.2 * np.abs(ref).max()

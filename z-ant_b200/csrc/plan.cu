@@ -19,6 +19,7 @@
 #include "fused_cnn.cuh"
 #include "tc_gemm.cuh"
 #include "tc_conv_generic.cuh"
+#include "tc_conv_nchw.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -553,6 +554,21 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
             const int xzp = a.x_zp; const Requant rq{a.y_scale, a.y_zp, a.activation};
             bool wz_zero = true;
             for (int32_t v : wzv) wz_zero = wz_zero && v == 0;
+            TcConvPlan tcp;
+            if ((b < 0 || T(b).is_const) && (long long)g.N * g.OH * g.OW >= 256 && tc_conv_plan(g, wz_zero, tcp)) {
+                // implicit GEMM from NCHW (stride 1): weights blocked once here, one launch per run.
+                // Arena tensors are 256-byte aligned; a caller-bound input that is not 16-byte aligned is refused at run time.
+                std::vector<int8_t> w_blk; std::vector<float> mp; std::vector<int32_t> bp;
+                tc_conv_prepare(tcp, (const int8_t*)T(w).host.data(), mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, w_blk, mp, bp);
+                const int aw = pl->add_aux(w_blk.data(), w_blk.size()), am = pl->add_aux(mp.data(), mp.size() * 4), ab = pl->add_aux(bp.data(), bp.size() * 4);
+                const bool finite = all_finite(mult);
+                push("QLinearConv(tc-implicit)", [=]() {
+                    if (!tc_conv_ptr_ok(pl->ptr(x))) return fail(ZANT_E_INVALID_INPUT, "QLinearConv input buffer must be 16-byte aligned");
+                    return tc_conv_run(ctx, tcp, pl->ptr(x), xd == ZANT_U8, xzp, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
+                                       (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq, finite);
+                });
+                return ZANT_OK;
+            }
             if (qconv_tc_eligible(g, wz_zero) && (b < 0 || T(b).is_const)) {
                 // tensor-core path: weights re-blocked once here, im2col + tcgen05 GEMM per run
                 auto prep = std::make_shared<QGemmPrep>();

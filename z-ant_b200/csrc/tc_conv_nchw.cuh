@@ -22,6 +22,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdint>
 #include <vector>
 
@@ -38,17 +39,22 @@ struct TcConvArgs {
     int KH, KW, dh, dw, pt, pl;
     int BH, BW, PH, PW, PR;           // tile, patch, allocated patch pixels per 16-channel group
     int hseg, wseg, c_stages, n_tiles;
-    int G, SP;                        // cp.async granule (4, 8 or 16 bytes); staging row pitch
-    int stages, stage_bytes, off_patch, off_stg;   // a stage = weights | patch | staging
+    int CB;                           // 16-channel groups per stage (2 or 4)
+    int G, NG, SP;                    // cp.async granule (4, 8 or 16 bytes), granules per staging row, staging row pitch
+    int KN;                           // staging words per patch row that the transpose visits (upper bound over tiles)
+    int stages, stage_bytes, off_patch, off_stg, off_out;   // a stage = weights | patch | staging; off_out: output staging
+    int V;                            // bytes per global store of the epilogue's copy-out (1, 2, 4, 8 or 16)
     uint32_t pad_word;                // the input zero point in all four bytes
     float y_scale; int y_zp; int act; int out_u8;
+    int six;                          // lean epilogue: sat8(rne(6 / y_scale)), used by ReLU6
     int m_pad;                        // filters rounded up to the tile width
     int* status;
 };
 
 constexpr int kTcConvMaxStages = 6;
 constexpr int kTcConvMaxFilters = 1024;
-constexpr int kTcConvThreads = 448;
+constexpr int kTcConvThreads = 576;                             // 2 + 8 producer + 8 epilogue warps
+constexpr int kTcConvOutPitch = 128;                            // bytes per filter in the output staging buffer
 constexpr int kTcConvTail = 2 * kTcConvMaxFilters * 4 + 512;   // constants + barriers after the stages
 
 __device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
@@ -71,7 +77,12 @@ __device__ __forceinline__ void transpose_4x4_bytes(uint32_t a, uint32_t b, uint
     out[2] = __byte_perm(t2, t3, 0x5410); out[3] = __byte_perm(t2, t3, 0x7632);
 }
 
-struct TcConvTile { int img, h0, w0, nt; };
+// Where a tile sits: image, first output row / column, filter tile, and the producer's view of
+// its input patch (first input row / column, loaded column range, staging alignment).
+struct TcConvTile {
+    int img, h0, w0, nt;
+    int h_in0, w_in0, iw_lo, iw_hi, seg_base, n_gran;
+};
 
 __device__ __forceinline__ TcConvTile tc_conv_decode(const TcConvArgs& a, int t) {
     TcConvTile r;
@@ -80,14 +91,20 @@ __device__ __forceinline__ TcConvTile tc_conv_decode(const TcConvArgs& a, int t)
     const int ws = sp % a.wseg; sp /= a.wseg;
     const int hs = sp % a.hseg;
     r.img = sp / a.hseg; r.h0 = hs * a.BH; r.w0 = ws * a.BW;
+    r.h_in0 = r.h0 - a.pt; r.w_in0 = r.w0 - a.pl;
+    r.iw_lo = max(r.w_in0, 0); r.iw_hi = min(r.w_in0 + a.PW, a.W);
+    r.seg_base = r.iw_lo & ~(a.G - 1);
+    r.n_gran = r.iw_hi > r.iw_lo ? (r.iw_hi - r.seg_base + a.G - 1) / a.G : 0;
     return r;
 }
 
-template <int NT, bool XU8>
+// LEAN: int8 output with zero point 0 and finite multipliers (requantisation by rni + saturating pack).
+template <int NT, bool XU8, bool LEAN>
 __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const __grid_constant__ TcConvArgs a) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sStages = smem;
-    uint8_t* tail = smem + (size_t)a.stages * a.stage_bytes;
+    uint8_t* sOut = smem + a.off_out;
+    uint8_t* tail = sOut + 2 * NT * kTcConvOutPitch;
     float* sMult = reinterpret_cast<float*>(tail);
     int* sBias = reinterpret_cast<int*>(tail + kTcConvMaxFilters * 4);
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2 * kTcConvMaxFilters * 4);
@@ -104,7 +121,8 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles = a.N * a.hseg * a.wseg * a.n_tiles;
     const int taps = a.KH * a.KW;
-    const uint32_t w_stage_bytes = (uint32_t)taps * 2u * NT * 16u;
+    const uint32_t w_tap_bytes = (uint32_t)a.CB * NT * 16u;
+    const uint32_t w_stage_bytes = (uint32_t)taps * w_tap_bytes;
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), 2); ptx::mbar_init(empty(s), 1); }
@@ -145,6 +163,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         if (ptx::elect_one()) {
             constexpr uint32_t idesc = ptx::idesc_i8(128, NT, !XU8, true);
             const uint32_t a_lbo = (uint32_t)a.PR * 16u;
+            const int ksteps = a.CB / 2;
             int it = 0, tile_it = 0;
             for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
                 const int b = tile_it & 1;
@@ -162,9 +181,11 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                     for (int kh = 0; kh < a.KH; ++kh)
                         for (int kw = 0; kw < a.KW; ++kw, ++tap) {
                             const uint32_t off = (uint32_t)(kh * a.dh * a.PW + kw * a.dw) * 16u;
-                            const uint64_t da = ptx::smem_desc_kmajor(sp + off, a_lbo, 128);
-                            const uint64_t db = ptx::smem_desc_kmajor(sw + (uint32_t)tap * (2u * NT * 16u), NT * 16, 128);
-                            ptx::mma_i8(d_tmem, da, db, idesc, (cs | tap) != 0);
+                            for (int kk = 0; kk < ksteps; ++kk) {
+                                const uint64_t da = ptx::smem_desc_kmajor(sp + off + (uint32_t)kk * 2u * a_lbo, a_lbo, 128);
+                                const uint64_t db = ptx::smem_desc_kmajor(sw + (uint32_t)tap * w_tap_bytes + (uint32_t)kk * (2u * NT * 16u), NT * 16, 128);
+                                ptx::mma_i8(d_tmem, da, db, idesc, (cs | tap | kk) != 0);
+                            }
                         }
                     ptx::mma_commit(empty(s));
                 }
@@ -172,119 +193,153 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             }
         mma_done:;
         }
-    } else if (warp < 6) {
-        // ------------------------------------------------------------------ activation producers (128 threads)
-        const int p = tid - 64;
-        const int GP = (a.SP - 32) / a.G;                       // granules per staging row (data region)
-        const int runs = 32 * a.PH;
-        const int slots = runs * GP;
+    } else if (warp < 10) {
+        // ------------------------------------------------------------------ activation producers (256 threads)
+        const int p = tid - 64, pw = p >> 5;
+        const int CH = a.CB * 16;
+        const int chan_pitch = a.PH * a.SP;                    // staging bytes per channel
         const int my_tiles = (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
         const int total_it = my_tiles * a.c_stages;
         const size_t plane = (size_t)a.H * a.W;
 
-        auto issue_loads = [&](int it) {
-            if (it < total_it) {
-                const int tl = it / a.c_stages, cs = it - tl * a.c_stages;
-                const TcConvTile T = tc_conv_decode(a, (int)blockIdx.x + tl * (int)gridDim.x);
-                const int s = it % S;
+        // Tile-independent work lists, decoded once: cp.async slots of one channel (per lane) and
+        // transpose items of one stage (per thread).
+        int ld_src[4], ld_dst[4], ld_hh[4], ld_gi[4];
+        {
+            const int row_slots = a.PH * a.NG;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int idx = lane + 32 * r;
+                const int hh = idx / a.NG, gi = idx - hh * a.NG;
+                const bool ok = idx < row_slots;
+                ld_hh[r] = ok ? hh : 0; ld_gi[r] = ok ? gi : 0x7fff;
+                ld_src[r] = ok ? hh * a.W + gi * a.G : 0;
+                ld_dst[r] = ok ? hh * a.SP + 16 + gi * a.G : 0;
+            }
+        }
+        int t_stg[4], t_pat[4], t_hh[4], t_kk[4];
+        {
+            const int row_items = a.PH * a.KN, items = a.CB * row_items;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int i = p + 256 * r;
+                const int blk = i / row_items, rem = i - blk * row_items;
+                const int hh = rem / a.KN, kk = rem - hh * a.KN;
+                const bool ok = i < items;
+                t_hh[r] = ok ? hh : 0; t_kk[r] = ok ? kk : 0x7fff;
+                t_stg[r] = ok ? (blk * 16 * a.PH + hh) * a.SP + kk * 4 : 0;
+                t_pat[r] = ok ? (blk * a.PR + hh * a.PW + kk * 4) * 16 : 0;
+            }
+        }
+
+        // two cursors over the same (tile, channel stage) sequence: `li` issues loads S-1 stages ahead of `ci`
+        int li = 0, l_cs = 0, l_tl = 0;
+        TcConvTile LT = tc_conv_decode(a, (int)blockIdx.x);
+        auto issue_loads = [&]() {
+            if (li < total_it) {
+                const int s = li % S;
                 const uint32_t stg = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes + a.off_stg);
-                const int w_in0 = T.w0 - a.pl, h_in0 = T.h0 - a.pt;
-                const int iw_lo = max(w_in0, 0), iw_hi = min(w_in0 + a.PW, a.W);
-                const int seg_base = iw_lo & ~(a.G - 1);
-                const int n_gran = iw_hi > iw_lo ? (iw_hi - seg_base + a.G - 1) / a.G : 0;
-                const uint8_t* ximg = a.x + ((size_t)T.img * a.C + (size_t)cs * 32) * plane + seg_base;
-                for (int sl = p; sl < slots; sl += 128) {
-                    const int run = sl / GP, gi = sl - run * GP;
-                    const int cc = run / a.PH, hh = run - cc * a.PH;
-                    const int ih = h_in0 + hh;
-                    if (gi < n_gran && cs * 32 + cc < a.C && ih >= 0 && ih < a.H) {
-                        const uint8_t* src = ximg + (size_t)cc * plane + (size_t)ih * a.W + (size_t)gi * a.G;
-                        const uint32_t dst = stg + (uint32_t)(run * a.SP + 16 + gi * a.G);
-                        if (a.G == 16) cp_async_16(dst, src);
-                        else if (a.G == 8) cp_async_8(dst, src);
-                        else cp_async_4(dst, src);
+                const uint8_t* xb = a.x + ((size_t)LT.img * a.C + (size_t)l_cs * CH) * plane + (ptrdiff_t)LT.h_in0 * a.W + LT.seg_base;
+                bool v[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) v[r] = ld_gi[r] < LT.n_gran && (unsigned)(LT.h_in0 + ld_hh[r]) < (unsigned)a.H;
+                const int cmax = min(CH, a.C - l_cs * CH);
+                for (int cc = pw; cc < cmax; cc += 8) {
+                    const uint8_t* xc = xb + (size_t)cc * plane;
+                    const uint32_t dc = stg + (uint32_t)(cc * chan_pitch);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        if (v[r]) {
+                            if (a.G == 16) cp_async_16(dc + ld_dst[r], xc + ld_src[r]);
+                            else if (a.G == 8) cp_async_8(dc + ld_dst[r], xc + ld_src[r]);
+                            else cp_async_4(dc + ld_dst[r], xc + ld_src[r]);
+                        }
                     }
                 }
-                // halo columns that no copy covers hold the input zero point
-                const int left = iw_lo - w_in0, right = w_in0 + a.PW - iw_hi;     // pixels outside the image on either side
-                if (left + right > 0) {
-                    const int per_run = left + right;
-                    uint8_t* stg_g = sStages + (size_t)s * a.stage_bytes + a.off_stg;
-                    for (int i = p; i < runs * per_run; i += 128) {
-                        const int run = i / per_run, j = i - run * per_run;
-                        const int col = j < left ? (16 + (iw_lo - seg_base) - left + j) : (16 + (iw_hi - seg_base) + (j - left));
-                        stg_g[run * a.SP + col] = (uint8_t)a.pad_word;
-                    }
+                ++li;
+                if (++l_cs == a.c_stages) {
+                    l_cs = 0; ++l_tl;
+                    if (li < total_it) LT = tc_conv_decode(a, (int)blockIdx.x + l_tl * (int)gridDim.x);
                 }
             }
             cp_async_commit();
         };
 
-        for (int d = 0; d < S - 1; ++d) issue_loads(d);
-        for (int it = 0; it < total_it; ++it) {
-            issue_loads(it + S - 1);
-            // all but the S-1 newest groups of this thread are complete
-            switch (S - 1) {
+        for (int d = 0; d < S - 1; ++d) issue_loads();
+        int c_cs = 0, c_tl = 0;
+        TcConvTile CT = tc_conv_decode(a, (int)blockIdx.x);
+        for (int ci = 0; ci < total_it; ++ci) {
+            issue_loads();
+            switch (S - 1) {       // all but the S-1 newest groups of this thread are complete
                 case 1: cp_async_wait<1>(); break;
                 case 2: cp_async_wait<2>(); break;
                 case 3: cp_async_wait<3>(); break;
                 case 4: cp_async_wait<4>(); break;
                 default: cp_async_wait<5>(); break;
             }
-            const int s = it % S;
-            const uint32_t ph = (uint32_t)(it / S) & 1u;
+            const int s = ci % S;
+            const uint32_t ph = (uint32_t)(ci / S) & 1u;
             const bool ok = ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag);
-            ptx::named_barrier_sync(2, 128);                    // every thread's copies of this stage have landed
+            ptx::named_barrier_sync(2, 256);                    // every thread's copies of this stage have landed
             if (!ok || *abort_flag) break;
 
-            const int tl = it / a.c_stages, cs = it - tl * a.c_stages;
-            const TcConvTile T = tc_conv_decode(a, (int)blockIdx.x + tl * (int)gridDim.x);
-            const int w_in0 = T.w0 - a.pl, h_in0 = T.h0 - a.pt;
-            const int iw_lo = max(w_in0, 0);
-            const int seg_base = iw_lo & ~(a.G - 1);
-            const int S0 = w_in0 - seg_base + 16;               // staging column of patch column 0
-            const int k_lo = S0 >> 2, k_hi = (S0 + a.PW - 1) >> 2;
-            const int kn = k_hi - k_lo + 1;
-            const uint8_t* stg = sStages + (size_t)s * a.stage_bytes + a.off_stg;
-            uint8_t* patch = sStages + (size_t)s * a.stage_bytes + a.off_patch;
-            const int items = 2 * a.PH * kn;
-            for (int i = p; i < items; i += 128) {
-                const int k = k_lo + i % kn;
-                const int rest = i / kn;
-                const int hh = rest % a.PH, blk = rest / a.PH;
-                const int ih = h_in0 + hh;
-                const bool row_ok = ih >= 0 && ih < a.H;
-                const int c_base = cs * 32 + blk * 16;
-                uint32_t wv[16];
+            const int S0 = CT.w_in0 - CT.seg_base + 16;         // staging column of patch column 0
+            const int k_lo = S0 >> 2;
+            const int kn = ((S0 + a.PW - 1) >> 2) - k_lo + 1;
+            const uint8_t* stg = sStages + (size_t)s * a.stage_bytes + a.off_stg + k_lo * 4;
+            uint8_t* patch = sStages + (size_t)s * a.stage_bytes + a.off_patch + (k_lo * 4 - S0) * 16;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const uint32_t v = *reinterpret_cast<const uint32_t*>(stg + (size_t)((blk * 16 + j) * a.PH + hh) * a.SP + k * 4);
-                    wv[j] = (row_ok && c_base + j < a.C) ? v : a.pad_word;
-                }
-                uint32_t o[4][4];    // o[group of 4 channels][pixel]
+            for (int r = 0; r < 4; ++r) {
+                if (t_kk[r] < kn) {
+                    const uint8_t* sp = stg + t_stg[r];
+                    uint32_t wv[16];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) transpose_4x4_bytes(wv[4 * q], wv[4 * q + 1], wv[4 * q + 2], wv[4 * q + 3], o[q]);
-                uint8_t* dst_row = patch + (size_t)blk * a.PR * 16 + (size_t)hh * a.PW * 16;
+                    for (int j = 0; j < 16; ++j) wv[j] = *reinterpret_cast<const uint32_t*>(sp + j * chan_pitch);
+                    const int ww0 = (k_lo + t_kk[r]) * 4 - S0;   // patch column of byte 0
+                    const int iw0 = CT.w_in0 + ww0;
+                    const bool row_ok = (unsigned)(CT.h_in0 + t_hh[r]) < (unsigned)a.H;
+                    if (!row_ok || iw0 < 0 || iw0 + 3 >= a.W) {
+                        // pixels outside the image hold the input zero point
+                        uint32_t mask = 0;
 #pragma unroll
-                for (int px = 0; px < 4; ++px) {
-                    const int ww = k * 4 + px - S0;
-                    if (ww >= 0 && ww < a.PW) *reinterpret_cast<uint4*>(dst_row + (size_t)ww * 16) = make_uint4(o[0][px], o[1][px], o[2][px], o[3][px]);
+                        for (int px = 0; px < 4; ++px) mask |= ((unsigned)(iw0 + px) < (unsigned)a.W) ? (0xffu << (8 * px)) : 0u;
+                        if (!row_ok) mask = 0;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) wv[j] = (wv[j] & mask) | (a.pad_word & ~mask);
+                    }
+                    uint32_t o[4][4];    // o[group of 4 channels][pixel]
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) transpose_4x4_bytes(wv[4 * q], wv[4 * q + 1], wv[4 * q + 2], wv[4 * q + 3], o[q]);
+                    uint8_t* dst = patch + t_pat[r];
+#pragma unroll
+                    for (int px = 0; px < 4; ++px) {
+                        const int ww = ww0 + px;
+                        if (ww >= 0 && ww < a.PW) *reinterpret_cast<uint4*>(dst + px * 16) = make_uint4(o[0][px], o[1][px], o[2][px], o[3][px]);
+                    }
                 }
             }
             ptx::fence_proxy_async_smem();
-            ptx::named_barrier_sync(2, 128);
+            ptx::named_barrier_sync(2, 256);
             if (p == 0) ptx::mbar_arrive(full(s));
+            if (++c_cs == a.c_stages) {
+                c_cs = 0; ++c_tl;
+                if (ci + 1 < total_it) CT = tc_conv_decode(a, (int)blockIdx.x + c_tl * (int)gridDim.x);
+            }
         }
         cp_async_wait<0>();
     } else {
-        // ------------------------------------------------------------------ epilogue: warps 6..13
+        // ------------------------------------------------------------------ epilogue: warps 10..17
         const int quarter = warp & 3;
-        const int half = (warp - 6) >> 2;
+        const int half = (warp - 10) >> 2;
+        const int ew = warp - 10;
         const int row = quarter * 32 + lane;
-        const int e = (warp - 6) * 32 + lane;
+        const int e = tid - 320;
         const Requant rq{a.y_scale, a.y_zp, a.act};
         const int oh_l = row / a.PW, ow_l = row - oh_l * a.PW;
+        const bool row_live = oh_l < a.BH && ow_l < a.BW;        // this MMA row is an output of the tile
+        const int pix_off = oh_l * a.BW + ow_l;
         const size_t ohw = (size_t)a.OH * a.OW;
+        const uint32_t six4 = 0x01010101u * (uint32_t)(a.six & 255);
         int tile_it = 0;
         for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
             const TcConvTile T = tc_conv_decode(a, t);
@@ -296,26 +351,76 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             ptx::tc_fence_after();
             const int tcol0 = half * (NT / 2);
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * NT + tcol0);
-            const int oh = T.h0 + oh_l, ow = T.w0 + ow_l;
-            const bool row_ok = oh_l < a.BH && ow_l < a.BW && oh < a.OH && ow < a.OW;
-            uint8_t* ybase = a.y + (size_t)T.img * a.M * ohw + (size_t)oh * a.OW + ow;
+            uint8_t* ob = sOut + (size_t)b * NT * kTcConvOutPitch;
+            uint8_t* orow = ob + (size_t)tcol0 * kTcConvOutPitch + pix_off;
 #pragma unroll 1
             for (int h = 0; h < NT / 64; ++h) {
                 uint32_t v[32];
                 ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
                 ptx::tmem_wait_ld();
                 const int col0 = T.nt * NT + tcol0 + h * 32;
+                uint8_t* oc = orow + (size_t)h * 32 * kTcConvOutPitch;
+                if constexpr (LEAN) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int col = col0 + j;
-                    const int acc = (int)v[j] + sBias[col];
-                    const int q = a.out_u8 ? requant_one<true>(acc, sMult[col], rq) : requant_one<false>(acc, sMult[col], rq);
-                    if (row_ok && col < a.M) ybase[(size_t)col * ohw] = (uint8_t)q;
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
+                        const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
+                        const int q0 = rq_round((int)v[j4 * 4 + 0] + b4.x, m4.x);
+                        const int q1 = rq_round((int)v[j4 * 4 + 1] + b4.y, m4.y);
+                        const int q2 = rq_round((int)v[j4 * 4 + 2] + b4.z, m4.z);
+                        const int q3 = rq_round((int)v[j4 * 4 + 3] + b4.w, m4.w);
+                        uint32_t pk = pack_sat_s8x4(q0, q1, q2, q3);
+                        if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
+                        if (a.act == ZANT_QACT_RELU6) pk = __vmins4(pk, six4);
+                        if (row_live) {
+                            oc[(j4 * 4 + 0) * kTcConvOutPitch] = (uint8_t)pk;
+                            oc[(j4 * 4 + 1) * kTcConvOutPitch] = (uint8_t)(pk >> 8);
+                            oc[(j4 * 4 + 2) * kTcConvOutPitch] = (uint8_t)(pk >> 16);
+                            oc[(j4 * 4 + 3) * kTcConvOutPitch] = (uint8_t)(pk >> 24);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int acc = (int)v[j] + sBias[col0 + j];
+                        const int q = a.out_u8 ? requant_one<true>(acc, sMult[col0 + j], rq) : requant_one<false>(acc, sMult[col0 + j], rq);
+                        if (row_live) oc[j * kTcConvOutPitch] = (uint8_t)q;
+                    }
                 }
             }
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(tempty(b));
+            if (lane == 0) ptx::mbar_arrive(tempty(b));          // the accumulator is free again
+            ptx::named_barrier_sync(1, 256);                     // the tile's bytes are staged
+
+            // copy-out: per filter one contiguous run of the NCHW output
+            const int ncv = min(NT, a.M - T.nt * NT);
+            const int L = a.wseg == 1 ? min(a.BH, a.OH - T.h0) * a.OW : min(a.BW, a.OW - T.w0);
+            const int nvec = L / a.V, tail_bytes = L - nvec * a.V;
+            const int slots = nvec + (tail_bytes ? 1 : 0);
+            int shift = 0;
+            while ((1 << shift) < slots && shift < 5) ++shift;
+            const int lpc = 1 << shift, cpp = 32 >> shift;       // lanes per filter, filters per pass of a warp
+            uint8_t* yrun = a.y + ((size_t)T.img * a.M + (size_t)T.nt * NT) * ohw + (size_t)T.h0 * a.OW + T.w0;
+            for (int c0 = ew * cpp; c0 < ncv; c0 += 8 * cpp) {
+                const int c = c0 + (lane >> shift);
+                if (c < ncv) {
+                    const uint8_t* src = ob + (size_t)c * kTcConvOutPitch;
+                    uint8_t* dst = yrun + (size_t)c * ohw;
+                    for (int vv = lane & (lpc - 1); vv < slots; vv += lpc) {
+                        const int o = vv * a.V;
+                        if (vv < nvec) {
+                            if (a.V == 16) *reinterpret_cast<uint4*>(dst + o) = *reinterpret_cast<const uint4*>(src + o);
+                            else if (a.V == 8) *reinterpret_cast<uint2*>(dst + o) = *reinterpret_cast<const uint2*>(src + o);
+                            else if (a.V == 4) *reinterpret_cast<uint32_t*>(dst + o) = *reinterpret_cast<const uint32_t*>(src + o);
+                            else if (a.V == 2) *reinterpret_cast<uint16_t*>(dst + o) = *reinterpret_cast<const uint16_t*>(src + o);
+                            else dst[o] = src[o];
+                        } else {
+                            for (int i = 0; i < tail_bytes; ++i) dst[o + i] = src[o + i];
+                        }
+                    }
+                }
+            }
         }
     }
 
@@ -338,6 +443,8 @@ struct TcConvPlan {
     size_t w_bytes = 0;        // blocked weights
     double row_efficiency = 0; // useful MMA rows / issued MMA rows
 };
+
+inline int tc_gcd(int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; }
 
 // Chooses tiling for `g`.  Returns false when the kernel does not apply (the caller then uses the
 // im2col path or the generic kernel).
@@ -365,36 +472,47 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
     a.PR = (128 + halo_h * a.PW + halo_w + 7) / 8 * 8;
     a.wseg = (a.OW + a.BW - 1) / a.BW;
     a.hseg = (a.OH + a.BH - 1) / a.BH;
-    a.c_stages = (a.C + 31) / 32;
+    a.NG = (a.PW + 2 * a.G - 2) / a.G;
+    a.KN = (a.PW + 2) / 4 + 1;
+    a.SP = 32 + (a.PW + a.G + 15) / 16 * 16;
     p.NT = g.M <= 64 ? 64 : 128;
     if (pointwise && g.M > 128) p.NT = 256;
     a.m_pad = (g.M + p.NT - 1) / p.NT * p.NT;
     a.n_tiles = a.m_pad / p.NT;
-    a.SP = 32 + (a.PW + 15 + 15) / 16 * 16;
     const int taps = a.KH * a.KW;
-    const int w_stage = taps * 2 * p.NT * 16;
-    a.off_patch = w_stage;
-    a.off_stg = a.off_patch + 2 * a.PR * 16;
-    a.stage_bytes = (a.off_stg + 32 * a.PH * a.SP + 127) / 128 * 128;
-    const int budget = 232448 - kTcConvTail - 1024;
-    a.stages = std::min(kTcConvMaxStages, budget / a.stage_bytes);
-    if (a.stages < 2) return false;
-    p.smem_bytes = (size_t)a.stages * a.stage_bytes + kTcConvTail;
-    p.w_bytes = (size_t)a.n_tiles * a.c_stages * w_stage;
-    const double useful = (double)a.OH * a.OW;
-    const double issued = (double)a.hseg * a.wseg * 128.0;
-    p.row_efficiency = useful / issued;
+    const int out_bytes = 2 * p.NT * kTcConvOutPitch;
+    const int budget = 232448 - kTcConvTail - out_bytes - 1024;
+    // 64 channels per stage when three stages of that size fit (fewer barriers per byte), else 32
+    for (a.CB = (a.C > 32 ? 4 : 2); a.CB >= 2; a.CB -= 2) {
+        const int w_stage = taps * a.CB * p.NT * 16;
+        a.off_patch = w_stage;
+        a.off_stg = a.off_patch + a.CB * a.PR * 16;
+        a.stage_bytes = (a.off_stg + a.CB * 16 * a.PH * a.SP + 127) / 128 * 128;
+        a.stages = std::min(kTcConvMaxStages, budget / a.stage_bytes);
+        if (a.stages >= 3 || (a.CB == 2 && a.stages >= 2)) break;
+    }
+    if (a.CB < 2 || a.stages < 2) return false;
+    if (a.PH * a.NG > 128 || a.CB * a.PH * a.KN > 1024) return false;   // the producers' per-thread work lists hold 4 entries
+    a.c_stages = (a.C + a.CB * 16 - 1) / (a.CB * 16);
+    a.off_out = a.stages * a.stage_bytes;
+    p.smem_bytes = (size_t)a.off_out + out_bytes + kTcConvTail;
+    p.w_bytes = (size_t)a.n_tiles * a.c_stages * taps * a.CB * p.NT * 16;
+    // one contiguous output run per filter and tile; V = widest store that every run start and length allows
+    const int ohw_gcd = tc_gcd(16, (int)(((long long)a.OH * a.OW) % 16 == 0 ? 16 : ((long long)a.OH * a.OW) % 16));
+    a.V = a.wseg == 1 ? tc_gcd(ohw_gcd, tc_gcd(16, (a.BH * a.OW) % 16 == 0 ? 16 : (a.BH * a.OW) % 16))
+                      : tc_gcd(ohw_gcd, tc_gcd(tc_gcd(16, a.OW % 16 == 0 ? 16 : a.OW % 16), tc_gcd(16, a.BW % 16 == 0 ? 16 : a.BW % 16)));
+    p.row_efficiency = (double)a.OH * a.OW / ((double)a.hseg * a.wseg * 128.0);
     const long long tiles = (long long)a.N * a.hseg * a.wseg * a.n_tiles;
     if (tiles > 0x7fffffffLL || p.row_efficiency < 0.5) return false;
     return true;
 }
 
-// Blocks `w` ([M][C][KH][KW] int8) as [filter tile][channel stage][tap][2][NT][16] and pads the
+// Blocks `w` ([M][C][KH][KW] int8) as [filter tile][channel stage][tap][CB][NT][16] and pads the
 // per-filter constants; the input zero point is folded into the bias (halo pixels hold x_zp).
 inline void tc_conv_prepare(const TcConvPlan& p, const int8_t* w, const float* mult, const int32_t* bias, int x_zp,
                             std::vector<int8_t>& w_blk, std::vector<float>& mult_pad, std::vector<int32_t>& bias_pad) {
     const TcConvArgs& a = p.a;
-    const int taps = a.KH * a.KW, NT = p.NT;
+    const int taps = a.KH * a.KW, NT = p.NT, CH = a.CB * 16;
     w_blk.assign(p.w_bytes, 0);
     mult_pad.assign(a.m_pad, 1.0f);
     bias_pad.assign(a.m_pad, 0);
@@ -402,10 +520,10 @@ inline void tc_conv_prepare(const TcConvPlan& p, const int8_t* w, const float* m
         const int nt = m / NT, mm = m % NT;
         long long sum = 0;
         for (int c = 0; c < a.C; ++c) {
-            const int cs = c / 32, blk = (c % 32) / 16, j = c % 16;
+            const int cs = c / CH, blk = (c % CH) / 16, j = c % 16;
             for (int tap = 0; tap < taps; ++tap) {
                 const int8_t v = w[((size_t)m * a.C + c) * taps + tap];
-                w_blk[((((size_t)nt * a.c_stages + cs) * taps + tap) * 2 + blk) * NT * 16 + (size_t)mm * 16 + j] = v;
+                w_blk[((((size_t)nt * a.c_stages + cs) * taps + tap) * a.CB + blk) * NT * 16 + (size_t)mm * 16 + j] = v;
                 sum += v;
             }
         }
@@ -414,32 +532,51 @@ inline void tc_conv_prepare(const TcConvPlan& p, const int8_t* w, const float* m
     }
 }
 
-template <int NT, bool XU8>
+template <int NT, bool XU8, bool LEAN>
 inline int32_t tc_conv_launch_t(zant_ctx* ctx, const TcConvPlan& p, const TcConvArgs& a, int grid) {
     static bool attr_set = false;
     if (!attr_set) {
-        ZB_CUDA(cudaFuncSetAttribute(tc_conv_nchw_kernel<NT, XU8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+        ZB_CUDA(cudaFuncSetAttribute(tc_conv_nchw_kernel<NT, XU8, LEAN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
         attr_set = true;
     }
-    tc_conv_nchw_kernel<NT, XU8><<<grid, kTcConvThreads, p.smem_bytes, ctx->stream>>>(a);
+    tc_conv_nchw_kernel<NT, XU8, LEAN><<<grid, kTcConvThreads, p.smem_bytes, ctx->stream>>>(a);
     return check_launch(ctx, "tc_conv_nchw_kernel");
 }
 
-// x must be 16-byte aligned (checked by the caller through tc_conv_ptr_ok).
+template <int NT>
+inline int32_t tc_conv_launch_nt(zant_ctx* ctx, const TcConvPlan& p, const TcConvArgs& a, int grid, bool x_u8, bool lean) {
+    if (x_u8) return lean ? tc_conv_launch_t<NT, true, true>(ctx, p, a, grid) : tc_conv_launch_t<NT, true, false>(ctx, p, a, grid);
+    return lean ? tc_conv_launch_t<NT, false, true>(ctx, p, a, grid) : tc_conv_launch_t<NT, false, false>(ctx, p, a, grid);
+}
+
+// x must be 16-byte aligned (cp.async granules); a y that is not falls back to byte stores.
 inline bool tc_conv_ptr_ok(const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) == 0; }
 
+// `mult_finite`: every requantisation multiplier is finite (checked by the caller on the host copy).
 inline int32_t tc_conv_run(zant_ctx* ctx, const TcConvPlan& p, const void* x, bool x_u8, int x_zp, const int8_t* w_blk_dev,
-                           const float* mult_dev, const int32_t* bias_dev, void* y, bool y_u8, const Requant& rq) {
+                           const float* mult_dev, const int32_t* bias_dev, void* y, bool y_u8, const Requant& rq, bool mult_finite) {
     TcConvArgs a = p.a;
     a.x = (const uint8_t*)x; a.y = (uint8_t*)y; a.w = w_blk_dev; a.mult = mult_dev; a.bias = bias_dev;
     a.pad_word = 0x01010101u * (uint32_t)(x_zp & 255);
     a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0;
+    if (!tc_conv_ptr_ok(y)) a.V = 1;
+    const bool lean = !y_u8 && rq.y_zp == 0 && mult_finite;
+    if (lean) {
+        float v = 6.0f / rq.y_scale;
+        v = std::fmin(std::fmax(v, -512.0f), 511.0f);
+        a.six = std::min(std::max((int)std::nearbyintf(v), -128), 127);
+    }
     a.status = ctx->status_word;
     const long long tiles = (long long)a.N * a.hseg * a.wseg * a.n_tiles;
     const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
-    if (p.NT == 64) return x_u8 ? tc_conv_launch_t<64, true>(ctx, p, a, grid) : tc_conv_launch_t<64, false>(ctx, p, a, grid);
-    if (p.NT == 128) return x_u8 ? tc_conv_launch_t<128, true>(ctx, p, a, grid) : tc_conv_launch_t<128, false>(ctx, p, a, grid);
-    return x_u8 ? tc_conv_launch_t<256, true>(ctx, p, a, grid) : tc_conv_launch_t<256, false>(ctx, p, a, grid);
+    if (p.NT == 64) return tc_conv_launch_nt<64>(ctx, p, a, grid, x_u8, lean);
+    if (p.NT == 128) return tc_conv_launch_nt<128>(ctx, p, a, grid, x_u8, lean);
+    return tc_conv_launch_nt<256>(ctx, p, a, grid, x_u8, lean);
+}
+
+inline bool all_finite(const std::vector<float>& v) {
+    for (float f : v) if (!std::isfinite(f)) return false;
+    return true;
 }
 
 }  // namespace zb
