@@ -24,6 +24,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
+#include <type_traits>
 #include <vector>
 
 #include "context.cuh"
@@ -39,8 +40,12 @@ struct TcConvArgs {
     int KH, KW, dh, dw, pt, pl;
     int BH, BW, PH, PW, PR;           // tile, patch, allocated patch pixels per 16-channel group
     int hseg, wseg, c_stages, n_tiles;
-    int CB;                           // 16-channel groups per stage (2 or 4)
-    int G, NG, SP;                    // cp.async granule (4, 8 or 16 bytes), granules per staging row, staging row pitch
+    int CB;                           // 16-channel groups per stage (2, 4 or 8)
+    int G, NG, SP;                    // cp.async granule (4, 8 or 16 bytes), granules per staging row (max over tiles), staging row pitch
+    int log2G, log2V;
+    int w_resident;                   // all weights of the (single) filter tile stay in shared memory at off_wres
+    int off_wres;
+    int LQ;                           // lanes that one channel's granules occupy in a cp.async instruction (power of two <= 32)
     int KN;                           // staging words per patch row that the transpose visits (upper bound over tiles)
     int stages, stage_bytes, off_patch, off_stg, off_out;   // a stage = weights | patch | staging; off_out: output staging
     int V;                            // bytes per global store of the epilogue's copy-out (1, 2, 4, 8 or 16)
@@ -57,14 +62,15 @@ constexpr int kTcConvThreads = 576;                             // 2 + 8 produce
 constexpr int kTcConvOutPitch = 128;                            // bytes per filter in the output staging buffer
 constexpr int kTcConvTail = 2 * kTcConvMaxFilters * 4 + 512;   // constants + barriers after the stages
 
-__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_8(uint32_t dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+// cp.async of BYTES (4, 8 or 16) bytes, skipped when `on` is false (predicated inside the asm: no branch)
+template <int BYTES>
+__device__ __forceinline__ void cp_async_pred(uint32_t dst, const void* src, bool on) {
+    if constexpr (BYTES == 16)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.cg.shared.global [%0], [%1], 16;\n\t}\n" ::"r"(dst), "l"(src), "r"((int)on) : "memory");
+    else if constexpr (BYTES == 8)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.ca.shared.global [%0], [%1], 8;\n\t}\n" ::"r"(dst), "l"(src), "r"((int)on) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.ca.shared.global [%0], [%1], 4;\n\t}\n" ::"r"(dst), "l"(src), "r"((int)on) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -77,6 +83,30 @@ __device__ __forceinline__ void transpose_4x4_bytes(uint32_t a, uint32_t b, uint
     out[2] = __byte_perm(t2, t3, 0x5410); out[3] = __byte_perm(t2, t3, 0x7632);
 }
 
+// Optional per-role cycle counters (debug builds with -DZB_TC_CONV_TIMERS only).
+#ifdef ZB_TC_CONV_TIMERS
+__device__ unsigned long long g_tc_conv_timers[256 * 32];
+#define ZB_T0() long long zb_t_ = clock64()
+#define ZB_TACC(slot) do { const long long n_ = clock64(); zb_acc_[slot] += n_ - zb_t_; zb_t_ = n_; } while (0)
+#define ZB_TDECL() long long zb_acc_[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define ZB_TDUMP(base) do { for (int i_ = 0; i_ < 8; ++i_) g_tc_conv_timers[blockIdx.x * 32 + (base) + i_] = (unsigned long long)zb_acc_[i_]; } while (0)
+#else
+#define ZB_T0() do {} while (0)
+#define ZB_TACC(slot) do {} while (0)
+#define ZB_TDECL() do {} while (0)
+#define ZB_TDUMP(base) do {} while (0)
+#endif
+
+// Round-to-nearest-even of float(acc) * m for the lean epilogue, without the conversion unit:
+// adding 1.5 * 2^23 leaves the rounded integer in the low mantissa bits.  Exact for products in
+// [-512, 2^22); larger products stay large and positive (the saturating pack turns them into 127,
+// as the clamp of the reference formula does), smaller ones are clamped to -512 first.  The
+// multiplier is finite (host-checked), so no NaN arrives here.
+__device__ __forceinline__ int tc_conv_round(int acc, float m) {
+    const float t = fmaxf(__fmul_rn(__int2float_rn(acc), m), -512.0f);
+    return __float_as_int(__fadd_rn(t, 12582912.0f)) - 0x4B400000;
+}
+
 // Where a tile sits: image, first output row / column, filter tile, and the producer's view of
 // its input patch (first input row / column, loaded column range, staging alignment).
 struct TcConvTile {
@@ -84,17 +114,32 @@ struct TcConvTile {
     int h_in0, w_in0, iw_lo, iw_hi, seg_base, n_gran;
 };
 
-__device__ __forceinline__ TcConvTile tc_conv_decode(const TcConvArgs& a, int t) {
+// Mixed-radix counter over (image, row segment, column segment, filter tile) that advances by the
+// grid size without dividing: the per-tile paths of every role stay free of integer division.
+struct TcConvCursor {
+    int nt, ws, hs, img;
+    int d_nt, d_ws, d_hs, d_img;
+};
+
+__device__ __forceinline__ void tc_conv_cursor_init(const TcConvArgs& a, int t0, int step, TcConvCursor& c) {
+    c.nt = t0 % a.n_tiles; t0 /= a.n_tiles; c.ws = t0 % a.wseg; t0 /= a.wseg; c.hs = t0 % a.hseg; c.img = t0 / a.hseg;
+    c.d_nt = step % a.n_tiles; step /= a.n_tiles; c.d_ws = step % a.wseg; step /= a.wseg; c.d_hs = step % a.hseg; c.d_img = step / a.hseg;
+}
+
+__device__ __forceinline__ void tc_conv_cursor_next(const TcConvArgs& a, TcConvCursor& c) {
+    c.nt += c.d_nt; int carry = c.nt >= a.n_tiles ? 1 : 0; c.nt -= carry ? a.n_tiles : 0;
+    c.ws += c.d_ws + carry; carry = c.ws >= a.wseg ? 1 : 0; c.ws -= carry ? a.wseg : 0;
+    c.hs += c.d_hs + carry; carry = c.hs >= a.hseg ? 1 : 0; c.hs -= carry ? a.hseg : 0;
+    c.img += c.d_img + carry;
+}
+
+__device__ __forceinline__ TcConvTile tc_conv_tile(const TcConvArgs& a, const TcConvCursor& c) {
     TcConvTile r;
-    r.nt = t % a.n_tiles;
-    int sp = t / a.n_tiles;
-    const int ws = sp % a.wseg; sp /= a.wseg;
-    const int hs = sp % a.hseg;
-    r.img = sp / a.hseg; r.h0 = hs * a.BH; r.w0 = ws * a.BW;
+    r.nt = c.nt; r.img = c.img; r.h0 = c.hs * a.BH; r.w0 = c.ws * a.BW;
     r.h_in0 = r.h0 - a.pt; r.w_in0 = r.w0 - a.pl;
     r.iw_lo = max(r.w_in0, 0); r.iw_hi = min(r.w_in0 + a.PW, a.W);
     r.seg_base = r.iw_lo & ~(a.G - 1);
-    r.n_gran = r.iw_hi > r.iw_lo ? (r.iw_hi - r.seg_base + a.G - 1) / a.G : 0;
+    r.n_gran = r.iw_hi > r.iw_lo ? (r.iw_hi - r.seg_base + a.G - 1) >> a.log2G : 0;
     return r;
 }
 
@@ -117,6 +162,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     auto empty = [&](int s) { return bar0 + 8u * (kTcConvMaxStages + s); };
     auto tfull = [&](int b) { return bar0 + 8u * (2 * kTcConvMaxStages + b); };
     auto tempty = [&](int b) { return bar0 + 8u * (2 * kTcConvMaxStages + 2 + b); };
+    const uint32_t wfull = bar0 + 8u * (2 * kTcConvMaxStages + 4);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles = a.N * a.hseg * a.wseg * a.n_tiles;
@@ -125,8 +171,9 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     const uint32_t w_stage_bytes = (uint32_t)taps * w_tap_bytes;
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), 2); ptx::mbar_init(empty(s), 1); }
+        for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), a.w_resident ? 1 : 2); ptx::mbar_init(empty(s), 1); }
         for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 8); }
+        ptx::mbar_init(wfull, 1);
         *abort_flag = 0;
         *epi_ok = 1;
         ptx::mbar_fence_init();
@@ -144,16 +191,24 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     if (warp == 0) {
         // ------------------------------------------------------------------ weights: one bulk copy per stage
         if (ptx::elect_one()) {
-            int it = 0;
-            for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
-                const int nt = t % a.n_tiles;
-                const int8_t* gw = a.w + (size_t)nt * a.c_stages * w_stage_bytes;
-                for (int cs = 0; cs < a.c_stages; ++cs, ++it) {
-                    const int s = it % S;
-                    const uint32_t ph = (uint32_t)(it / S) & 1u;
-                    if (!ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag)) goto weights_done;
-                    ptx::mbar_arrive_expect_tx(full(s), w_stage_bytes);
-                    ptx::bulk_g2s(ptx::smem_u32(sStages + (size_t)s * a.stage_bytes), gw + (size_t)cs * w_stage_bytes, w_stage_bytes, full(s));
+            if (a.w_resident) {
+                // every tile uses the same weights: load them once
+                ptx::mbar_arrive_expect_tx(wfull, (uint32_t)a.c_stages * w_stage_bytes);
+                for (int cs = 0; cs < a.c_stages; ++cs)
+                    ptx::bulk_g2s(ptx::smem_u32(smem + a.off_wres) + (uint32_t)cs * w_stage_bytes, a.w + (size_t)cs * w_stage_bytes, w_stage_bytes, wfull);
+            } else {
+                TcConvCursor cur;
+                tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, cur);
+                int s = 0; uint32_t ph = 0;
+                for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+                    const int8_t* gw = a.w + (size_t)cur.nt * a.c_stages * w_stage_bytes;
+                    for (int cs = 0; cs < a.c_stages; ++cs) {
+                        if (!ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag)) goto weights_done;
+                        ptx::mbar_arrive_expect_tx(full(s), w_stage_bytes);
+                        ptx::bulk_g2s(ptx::smem_u32(sStages + (size_t)s * a.stage_bytes), gw + (size_t)cs * w_stage_bytes, w_stage_bytes, full(s));
+                        if (++s == S) { s = 0; ph ^= 1u; }
+                    }
+                    tc_conv_cursor_next(a, cur);
                 }
             }
         weights_done:;
@@ -164,33 +219,44 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             constexpr uint32_t idesc = ptx::idesc_i8(128, NT, !XU8, true);
             const uint32_t a_lbo = (uint32_t)a.PR * 16u;
             const int ksteps = a.CB / 2;
-            int it = 0, tile_it = 0;
+            // descriptors advance by adding 16-byte units to their address field (shared memory is < 256 KiB, no carry)
+            const uint64_t a_kstep = (uint64_t)((2u * a_lbo) >> 4), b_kstep = (uint64_t)((2u * NT * 16u) >> 4);
+            const uint64_t a_col = (uint64_t)a.dw, a_rowstep = (uint64_t)(a.dh * a.PW);
+            const uint64_t b_tap = (uint64_t)(w_tap_bytes >> 4);
+            int s = 0; uint32_t ph = 0;
+            int tile_it = 0;
+            ZB_TDECL(); ZB_T0();
+            if (a.w_resident && !ptx::mbar_wait(wfull, 0, abort_flag)) goto mma_done;
             for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
                 const int b = tile_it & 1;
                 const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
                 if (!ptx::mbar_wait(tempty(b), bph ^ 1u, abort_flag)) goto mma_done;
+                ZB_TACC(0);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * NT);
-                for (int cs = 0; cs < a.c_stages; ++cs, ++it) {
-                    const int s = it % S;
-                    const uint32_t ph = (uint32_t)(it / S) & 1u;
+                for (int cs = 0; cs < a.c_stages; ++cs) {
                     if (!ptx::mbar_wait(full(s), ph, abort_flag)) goto mma_done;
+                    ZB_TACC(1);
                     ptx::tc_fence_after();
-                    const uint32_t sw = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
-                    const uint32_t sp = sw + (uint32_t)a.off_patch;
-                    int tap = 0;
-                    for (int kh = 0; kh < a.KH; ++kh)
-                        for (int kw = 0; kw < a.KW; ++kw, ++tap) {
-                            const uint32_t off = (uint32_t)(kh * a.dh * a.PW + kw * a.dw) * 16u;
-                            for (int kk = 0; kk < ksteps; ++kk) {
-                                const uint64_t da = ptx::smem_desc_kmajor(sp + off + (uint32_t)kk * 2u * a_lbo, a_lbo, 128);
-                                const uint64_t db = ptx::smem_desc_kmajor(sw + (uint32_t)tap * w_tap_bytes + (uint32_t)kk * (2u * NT * 16u), NT * 16, 128);
-                                ptx::mma_i8(d_tmem, da, db, idesc, (cs | tap | kk) != 0);
-                            }
+                    const uint32_t stage0 = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
+                    const uint32_t sw = a.w_resident ? ptx::smem_u32(smem + a.off_wres) + (uint32_t)cs * w_stage_bytes : stage0;
+                    uint64_t da_row = ptx::smem_desc_kmajor(stage0 + (uint32_t)a.off_patch, a_lbo, 128);
+                    uint64_t db = ptx::smem_desc_kmajor(sw, NT * 16, 128);
+                    uint32_t acc = cs != 0 ? 1u : 0u;
+                    for (int kh = 0; kh < a.KH; ++kh, da_row += a_rowstep) {
+                        uint64_t da = da_row;
+                        for (int kw = 0; kw < a.KW; ++kw, da += a_col, db += b_tap) {
+                            ptx::mma_i8(d_tmem, da, db, idesc, acc != 0);
+                            acc = 1u;
+                            for (int kk = 1; kk < ksteps; ++kk) ptx::mma_i8(d_tmem, da + (uint64_t)kk * a_kstep, db + (uint64_t)kk * b_kstep, idesc, true);
                         }
+                    }
                     ptx::mma_commit(empty(s));
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                    ZB_TACC(2);
                 }
                 ptx::mma_commit(tfull(b));
             }
+            ZB_TDUMP(0);
         mma_done:;
         }
     } else if (warp < 10) {
@@ -198,78 +264,98 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         const int p = tid - 64, pw = p >> 5;
         const int CH = a.CB * 16;
         const int chan_pitch = a.PH * a.SP;                    // staging bytes per channel
+        const int skew = 128 / a.CB;                           // each 16-channel group starts `skew` bytes later: conflict-free transposes
         const int my_tiles = (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
         const int total_it = my_tiles * a.c_stages;
         const size_t plane = (size_t)a.H * a.W;
 
         // Tile-independent work lists, decoded once: cp.async slots of one channel (per lane) and
         // transpose items of one stage (per thread).
+        // A cp.async instruction of a warp covers 32 / LQ channels x LQ (row, granule) slots; a channel
+        // with more than 32 slots takes several rounds.
+        const int lsub = lane / a.LQ, lslot = lane - lsub * a.LQ;
+        const int ch_per_instr = 32 / a.LQ;
         int ld_src[4], ld_dst[4], ld_hh[4], ld_gi[4];
         {
             const int row_slots = a.PH * a.NG;
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
-                const int idx = lane + 32 * r;
+                const int idx = lslot + 32 * r;
                 const int hh = idx / a.NG, gi = idx - hh * a.NG;
-                const bool ok = idx < row_slots;
+                const bool ok = idx < row_slots && (r == 0 || a.LQ == 32);
                 ld_hh[r] = ok ? hh : 0; ld_gi[r] = ok ? gi : 0x7fff;
                 ld_src[r] = ok ? hh * a.W + gi * a.G : 0;
                 ld_dst[r] = ok ? hh * a.SP + 16 + gi * a.G : 0;
             }
         }
+        const int rounds = a.LQ == 32 ? (a.PH * a.NG + 31) / 32 : 1;
+        // transpose items: 16 channels x 4 pixels each; consecutive threads take consecutive channel groups
+        // of the same pixels, so that a quarter warp's 16-byte stores and a warp's word loads spread over all banks
         int t_stg[4], t_pat[4], t_hh[4], t_kk[4];
         {
             const int row_items = a.PH * a.KN, items = a.CB * row_items;
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 const int i = p + 256 * r;
-                const int blk = i / row_items, rem = i - blk * row_items;
+                const int rem = i / a.CB, blk = i - rem * a.CB;
                 const int hh = rem / a.KN, kk = rem - hh * a.KN;
                 const bool ok = i < items;
                 t_hh[r] = ok ? hh : 0; t_kk[r] = ok ? kk : 0x7fff;
-                t_stg[r] = ok ? (blk * 16 * a.PH + hh) * a.SP + kk * 4 : 0;
+                t_stg[r] = ok ? (blk * 16 * a.PH + hh) * a.SP + kk * 4 + blk * skew : 0;
                 t_pat[r] = ok ? (blk * a.PR + hh * a.PW + kk * 4) * 16 : 0;
             }
         }
 
         // two cursors over the same (tile, channel stage) sequence: `li` issues loads S-1 stages ahead of `ci`
-        int li = 0, l_cs = 0, l_tl = 0;
-        TcConvTile LT = tc_conv_decode(a, (int)blockIdx.x);
+        int li = 0, l_cs = 0, l_s = 0;
+        TcConvCursor lcur;
+        tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, lcur);
+        TcConvTile LT = tc_conv_tile(a, lcur);
         auto issue_loads = [&]() {
             if (li < total_it) {
-                const int s = li % S;
-                const uint32_t stg = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes + a.off_stg);
+                const uint32_t stg = ptx::smem_u32(sStages + (size_t)l_s * a.stage_bytes + a.off_stg);
                 const uint8_t* xb = a.x + ((size_t)LT.img * a.C + (size_t)l_cs * CH) * plane + (ptrdiff_t)LT.h_in0 * a.W + LT.seg_base;
                 bool v[4];
 #pragma unroll
                 for (int r = 0; r < 4; ++r) v[r] = ld_gi[r] < LT.n_gran && (unsigned)(LT.h_in0 + ld_hh[r]) < (unsigned)a.H;
                 const int cmax = min(CH, a.C - l_cs * CH);
-                for (int cc = pw; cc < cmax; cc += 8) {
-                    const uint8_t* xc = xb + (size_t)cc * plane;
-                    const uint32_t dc = stg + (uint32_t)(cc * chan_pitch);
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        if (v[r]) {
-                            if (a.G == 16) cp_async_16(dc + ld_dst[r], xc + ld_src[r]);
-                            else if (a.G == 8) cp_async_8(dc + ld_dst[r], xc + ld_src[r]);
-                            else cp_async_4(dc + ld_dst[r], xc + ld_src[r]);
-                        }
+                auto copy_all = [&](auto granule) {
+                    constexpr int GB = decltype(granule)::value;
+                    for (int c0 = pw * ch_per_instr; c0 < cmax; c0 += 8 * ch_per_instr) {
+                        const int cc = c0 + lsub;
+                        const bool c_ok = cc < cmax;
+                        const uint8_t* xc = xb + (size_t)cc * plane;
+                        const uint32_t dc = stg + (uint32_t)(cc * chan_pitch + (cc >> 4) * skew);
+                        cp_async_pred<GB>(dc + ld_dst[0], xc + ld_src[0], c_ok && v[0]);
+                        if (rounds > 1) cp_async_pred<GB>(dc + ld_dst[1], xc + ld_src[1], c_ok && v[1]);
+                        if (rounds > 2) cp_async_pred<GB>(dc + ld_dst[2], xc + ld_src[2], c_ok && v[2]);
+                        if (rounds > 3) cp_async_pred<GB>(dc + ld_dst[3], xc + ld_src[3], c_ok && v[3]);
                     }
-                }
+                };
+                if (a.G == 16) copy_all(std::integral_constant<int, 16>{});
+                else if (a.G == 8) copy_all(std::integral_constant<int, 8>{});
+                else copy_all(std::integral_constant<int, 4>{});
                 ++li;
+                if (++l_s == S) l_s = 0;
                 if (++l_cs == a.c_stages) {
-                    l_cs = 0; ++l_tl;
-                    if (li < total_it) LT = tc_conv_decode(a, (int)blockIdx.x + l_tl * (int)gridDim.x);
+                    l_cs = 0;
+                    tc_conv_cursor_next(a, lcur);
+                    LT = tc_conv_tile(a, lcur);
                 }
             }
             cp_async_commit();
         };
 
         for (int d = 0; d < S - 1; ++d) issue_loads();
-        int c_cs = 0, c_tl = 0;
-        TcConvTile CT = tc_conv_decode(a, (int)blockIdx.x);
+        int c_cs = 0, s = 0;
+        uint32_t ph = 0;
+        TcConvCursor ccur;
+        tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, ccur);
+        TcConvTile CT = tc_conv_tile(a, ccur);
+        ZB_TDECL(); ZB_T0();
         for (int ci = 0; ci < total_it; ++ci) {
             issue_loads();
+            ZB_TACC(0);
             switch (S - 1) {       // all but the S-1 newest groups of this thread are complete
                 case 1: cp_async_wait<1>(); break;
                 case 2: cp_async_wait<2>(); break;
@@ -277,11 +363,12 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                 case 4: cp_async_wait<4>(); break;
                 default: cp_async_wait<5>(); break;
             }
-            const int s = ci % S;
-            const uint32_t ph = (uint32_t)(ci / S) & 1u;
-            const bool ok = ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag);
-            ptx::named_barrier_sync(2, 256);                    // every thread's copies of this stage have landed
-            if (!ok || *abort_flag) break;
+            ZB_TACC(1);
+            if (p == 0) ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag);   // a time-out raises the abort flag
+            ZB_TACC(2);
+            ptx::named_barrier_sync(2, 256);                    // the patch slot is free and every thread's copies have landed
+            if (*abort_flag) break;
+            ZB_TACC(3);
 
             const int S0 = CT.w_in0 - CT.seg_base + 16;         // staging column of patch column 0
             const int k_lo = S0 >> 2;
@@ -318,15 +405,20 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                     }
                 }
             }
+            ZB_TACC(4);
             ptx::fence_proxy_async_smem();
             ptx::named_barrier_sync(2, 256);
             if (p == 0) ptx::mbar_arrive(full(s));
+            ZB_TACC(5);
+            if (++s == S) { s = 0; ph ^= 1u; }
             if (++c_cs == a.c_stages) {
-                c_cs = 0; ++c_tl;
-                if (ci + 1 < total_it) CT = tc_conv_decode(a, (int)blockIdx.x + c_tl * (int)gridDim.x);
+                c_cs = 0;
+                tc_conv_cursor_next(a, ccur);
+                CT = tc_conv_tile(a, ccur);
             }
         }
         cp_async_wait<0>();
+        if (p == 0) ZB_TDUMP(8);
     } else {
         // ------------------------------------------------------------------ epilogue: warps 10..17
         const int quarter = warp & 3;
@@ -341,13 +433,19 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         const size_t ohw = (size_t)a.OH * a.OW;
         const uint32_t six4 = 0x01010101u * (uint32_t)(a.six & 255);
         int tile_it = 0;
+        TcConvCursor ecur;
+        tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, ecur);
+        ZB_TDECL(); ZB_T0();
         for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
-            const TcConvTile T = tc_conv_decode(a, t);
+            const TcConvTile T = tc_conv_tile(a, ecur);
+            tc_conv_cursor_next(a, ecur);
             const int b = tile_it & 1;
             const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
+            ZB_TACC(0);
             if (e == 0) *epi_ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
             ptx::named_barrier_sync(1, 256);
             if (!*epi_ok) break;
+            ZB_TACC(1);
             ptx::tc_fence_after();
             const int tcol0 = half * (NT / 2);
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * NT + tcol0);
@@ -365,10 +463,10 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                     for (int j4 = 0; j4 < 8; ++j4) {
                         const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
                         const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
-                        const int q0 = rq_round((int)v[j4 * 4 + 0] + b4.x, m4.x);
-                        const int q1 = rq_round((int)v[j4 * 4 + 1] + b4.y, m4.y);
-                        const int q2 = rq_round((int)v[j4 * 4 + 2] + b4.z, m4.z);
-                        const int q3 = rq_round((int)v[j4 * 4 + 3] + b4.w, m4.w);
+                        const int q0 = tc_conv_round((int)v[j4 * 4 + 0] + b4.x, m4.x);
+                        const int q1 = tc_conv_round((int)v[j4 * 4 + 1] + b4.y, m4.y);
+                        const int q2 = tc_conv_round((int)v[j4 * 4 + 2] + b4.z, m4.z);
+                        const int q3 = tc_conv_round((int)v[j4 * 4 + 3] + b4.w, m4.w);
                         uint32_t pk = pack_sat_s8x4(q0, q1, q2, q3);
                         if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
                         if (a.act == ZANT_QACT_RELU6) pk = __vmins4(pk, six4);
@@ -391,12 +489,14 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(tempty(b));          // the accumulator is free again
+            ZB_TACC(2);
             ptx::named_barrier_sync(1, 256);                     // the tile's bytes are staged
+            ZB_TACC(3);
 
             // copy-out: per filter one contiguous run of the NCHW output
             const int ncv = min(NT, a.M - T.nt * NT);
             const int L = a.wseg == 1 ? min(a.BH, a.OH - T.h0) * a.OW : min(a.BW, a.OW - T.w0);
-            const int nvec = L / a.V, tail_bytes = L - nvec * a.V;
+            const int nvec = L >> a.log2V, tail_bytes = L - (nvec << a.log2V);
             const int slots = nvec + (tail_bytes ? 1 : 0);
             int shift = 0;
             while ((1 << shift) < slots && shift < 5) ++shift;
@@ -408,7 +508,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                     const uint8_t* src = ob + (size_t)c * kTcConvOutPitch;
                     uint8_t* dst = yrun + (size_t)c * ohw;
                     for (int vv = lane & (lpc - 1); vv < slots; vv += lpc) {
-                        const int o = vv * a.V;
+                        const int o = vv << a.log2V;
                         if (vv < nvec) {
                             if (a.V == 16) *reinterpret_cast<uint4*>(dst + o) = *reinterpret_cast<const uint4*>(src + o);
                             else if (a.V == 8) *reinterpret_cast<uint2*>(dst + o) = *reinterpret_cast<const uint2*>(src + o);
@@ -421,7 +521,9 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                     }
                 }
             }
+            ZB_TACC(4);
         }
+        if (e == 32) ZB_TDUMP(16);
     }
 
     if (*abort_flag) {
@@ -469,11 +571,21 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
     a.PW = a.BW + halo_w;
     a.BH = std::max(1, std::min(a.OH, 128 / a.PW));
     a.PH = a.BH + halo_h;
-    a.PR = (128 + halo_h * a.PW + halo_w + 7) / 8 * 8;
+    a.PR = (128 + halo_h * a.PW + halo_w + 7) / 8 * 8 + 1;   // 1 mod 8: the channel groups of a pixel fall into different banks
     a.wseg = (a.OW + a.BW - 1) / a.BW;
     a.hseg = (a.OH + a.BH - 1) / a.BH;
-    a.NG = (a.PW + 2 * a.G - 2) / a.G;
-    a.KN = (a.PW + 2) / 4 + 1;
+    a.NG = 1;
+    for (int ws = 0; ws < a.wseg; ++ws) {       // most granules any tile's patch row needs
+        const int w_in0 = ws * a.BW - a.pl;
+        const int lo = std::max(w_in0, 0), hi = std::min(w_in0 + a.PW, a.W);
+        if (hi > lo) a.NG = std::max(a.NG, (hi - (lo & ~(a.G - 1)) + a.G - 1) / a.G);
+    }
+    a.KN = 1;
+    for (int ws = 0; ws < a.wseg; ++ws) {       // most staging words any tile's patch row spans
+        const int w_in0 = ws * a.BW - a.pl;
+        const int s0 = w_in0 - (std::max(w_in0, 0) & ~(a.G - 1)) + 16;
+        a.KN = std::max(a.KN, ((s0 + a.PW - 1) >> 2) - (s0 >> 2) + 1);
+    }
     a.SP = 32 + (a.PW + a.G + 15) / 16 * 16;
     p.NT = g.M <= 64 ? 64 : 128;
     if (pointwise && g.M > 128) p.NT = 256;
@@ -482,25 +594,39 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
     const int taps = a.KH * a.KW;
     const int out_bytes = 2 * p.NT * kTcConvOutPitch;
     const int budget = 232448 - kTcConvTail - out_bytes - 1024;
-    // 64 channels per stage when three stages of that size fit (fewer barriers per byte), else 32
-    for (a.CB = (a.C > 32 ? 4 : 2); a.CB >= 2; a.CB -= 2) {
-        const int w_stage = taps * a.CB * p.NT * 16;
-        a.off_patch = w_stage;
-        a.off_stg = a.off_patch + a.CB * a.PR * 16;
-        a.stage_bytes = (a.off_stg + a.CB * 16 * a.PH * a.SP + 127) / 128 * 128;
-        a.stages = std::min(kTcConvMaxStages, budget / a.stage_bytes);
-        if (a.stages >= 3 || (a.CB == 2 && a.stages >= 2)) break;
-    }
-    if (a.CB < 2 || a.stages < 2) return false;
+    // Shared-memory plan.  Preference: 64 channels per stage over 32 (fewer hand-offs per byte), weights
+    // resident over streamed (possible when there is one filter tile: no re-fetch per tile), at least 3 stages.
+    bool placed = false;
+    for (int min_stages = 3; min_stages >= 2 && !placed; --min_stages)
+        for (int cb = (a.C > 64 ? 8 : (a.C > 32 ? 4 : 2)); cb >= 2 && !placed; cb /= 2)
+            for (int resident = 1; resident >= 0 && !placed; --resident) {
+                const int c_stages = (a.C + cb * 16 - 1) / (cb * 16);
+                const int w_stage = taps * cb * p.NT * 16;
+                const long long w_all = (long long)c_stages * w_stage;
+                if (resident && (a.n_tiles != 1 || w_all > 112 * 1024)) continue;
+                const int off_patch = resident ? 0 : w_stage;
+                const int off_stg = off_patch + cb * a.PR * 16;
+                const int stage_bytes = (off_stg + cb * 16 * a.PH * a.SP + 128 + 127) / 128 * 128;   // + 128: room for the staging skew
+                const int stages = std::min<long long>(kTcConvMaxStages, (budget - (resident ? w_all : 0)) / stage_bytes);
+                if (stages < min_stages) continue;
+                a.CB = cb; a.c_stages = c_stages; a.w_resident = resident; a.off_patch = off_patch; a.off_stg = off_stg;
+                a.stage_bytes = stage_bytes; a.stages = stages;
+                a.off_wres = stages * stage_bytes;
+                a.off_out = a.off_wres + (resident ? (int)w_all : 0);
+                placed = true;
+            }
+    if (!placed) return false;
+    a.LQ = 1;
+    while (a.LQ < 32 && a.LQ < a.PH * a.NG) a.LQ *= 2;
     if (a.PH * a.NG > 128 || a.CB * a.PH * a.KN > 1024) return false;   // the producers' per-thread work lists hold 4 entries
-    a.c_stages = (a.C + a.CB * 16 - 1) / (a.CB * 16);
-    a.off_out = a.stages * a.stage_bytes;
+    for (a.log2G = 0; (1 << a.log2G) < a.G; ++a.log2G) {}
     p.smem_bytes = (size_t)a.off_out + out_bytes + kTcConvTail;
     p.w_bytes = (size_t)a.n_tiles * a.c_stages * taps * a.CB * p.NT * 16;
     // one contiguous output run per filter and tile; V = widest store that every run start and length allows
     const int ohw_gcd = tc_gcd(16, (int)(((long long)a.OH * a.OW) % 16 == 0 ? 16 : ((long long)a.OH * a.OW) % 16));
     a.V = a.wseg == 1 ? tc_gcd(ohw_gcd, tc_gcd(16, (a.BH * a.OW) % 16 == 0 ? 16 : (a.BH * a.OW) % 16))
                       : tc_gcd(ohw_gcd, tc_gcd(tc_gcd(16, a.OW % 16 == 0 ? 16 : a.OW % 16), tc_gcd(16, a.BW % 16 == 0 ? 16 : a.BW % 16)));
+    for (a.log2V = 0; (1 << a.log2V) < a.V; ++a.log2V) {}
     p.row_efficiency = (double)a.OH * a.OW / ((double)a.hseg * a.wseg * 128.0);
     const long long tiles = (long long)a.N * a.hseg * a.wseg * a.n_tiles;
     if (tiles > 0x7fffffffLL || p.row_efficiency < 0.5) return false;
@@ -559,7 +685,7 @@ inline int32_t tc_conv_run(zant_ctx* ctx, const TcConvPlan& p, const void* x, bo
     a.x = (const uint8_t*)x; a.y = (uint8_t*)y; a.w = w_blk_dev; a.mult = mult_dev; a.bias = bias_dev;
     a.pad_word = 0x01010101u * (uint32_t)(x_zp & 255);
     a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0;
-    if (!tc_conv_ptr_ok(y)) a.V = 1;
+    if (!tc_conv_ptr_ok(y)) { a.V = 1; a.log2V = 0; }
     const bool lean = !y_u8 && rq.y_zp == 0 && mult_finite;
     if (lean) {
         float v = 6.0f / rq.y_scale;
