@@ -150,7 +150,7 @@ IMPLICIT_QCONV = [
     (2, 64, 56, 56, 64, 3, (1, 1), (1, 1, 1, 1), (1, 1), I8, I8, 0, 0, False, False, None),         # sweep case 3a, 8-byte rows
     (3, 3, 32, 32, 32, 3, (1, 1), (1, 1, 1, 1), (1, 1), U8, I8, 0, 0, True, True, "relu6"),          # 3 channels of a 32-channel stage
     (2, 40, 24, 28, 72, 3, (1, 1), (1, 0, 1, 2), (1, 1), U8, U8, 128, 7, True, True, "relu"),        # partial second block, odd pads, zero points
-    (1, 16, 40, 140, 24, 3, (1, 1), (1, 1, 1, 1), (1, 1), I8, I8, -3, 5, True, True, None),          # two width segments
+    (1, 16, 40, 144, 24, 3, (1, 1), (1, 1, 1, 1), (1, 1), I8, I8, -3, 5, True, True, None),          # two width segments
     (2, 32, 36, 36, 48, 5, (1, 1), (4, 4, 4, 4), (2, 2), I8, I8, 0, -4, True, False, "relu"),        # 5x5 dilated
     (2, 96, 20, 20, 300, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, U8, 0, 100, True, True, None),         # pointwise, 256-wide filter tiles
     (5, 256, 8, 8, 64, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, I8, 2, 0, False, True, "relu6"),          # pointwise, 64 pixels per image

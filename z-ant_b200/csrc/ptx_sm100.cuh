@@ -78,6 +78,19 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src_gmem
                  ::"r"(dst_smem), "l"(src_gmem), "r"(bytes), "r"(bar) : "memory");
 }
 
+// ---------------------------------------------------------------------------- tiled TMA loads
+// Box of a tensor map -> this CTA's shared memory (128-byte aligned), completion counted in bytes
+// on an mbarrier.  The innermost coordinate times the element size must be a multiple of 16 bytes.
+// No cluster multicast.  `tmap` is the generic address of a CUtensorMap kernel parameter.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap, int x, int y, int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, int x, int y, int z, int w, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar) : "memory");
+}
+
 // ---------------------------------------------------------------------------- TMEM
 // One full warp allocates `cols` (power of two >= 32) columns; the base address lands in smem.
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {

@@ -2,23 +2,30 @@
 // (group 1, stride 1, any kernel size / dilation / padding, weight zero points 0).
 //
 // A tile is BH output rows x BW output columns of one image; its input patch (PH x PW pixels, halo
-// included) is brought in 32 channels at a time:
-//   1. producer warps copy the patch rows of the 32 channel planes with cp.async into a staging
-//      buffer (rows stay rows: [channel][patch row][bytes], every input column at the same byte
-//      offset in every row);
-//   2. the same warps transpose staging -> "patch" [16-channel group][patch pixel][16 channels],
-//      one 16-byte chunk per pixel, pixels in row-major order of the patch (4x4 byte transposes
-//      with prmt); pixels outside the image hold the input zero point.
+// included) is brought in CB*16 channels at a time:
+//   1. the loader warp copies, for every channel of the stage, the run of input bytes that holds
+//      the patch rows (one run per channel when the tile spans the image width, else one per row)
+//      with 1-D bulk async copies (TMA engine) into a staging buffer.  A run starts at the 16-byte
+//      boundary below its first byte, so the data sits `shift` bytes into its slot; the host admits
+//      only shapes for which `shift` is the same for every channel of a stage (H*W % 16 == 0, and
+//      W % 16 == 0 when rows are separate runs);
+//   2. eight warps transpose staging -> "patch" [16-channel group][patch pixel][16 channels], one
+//      16-byte chunk per pixel, pixels in row-major order of the patch (4x4 byte transposes with
+//      prmt); pixels outside the image are replaced by the input zero point on the way.
 // In that form filter tap (kh,kw) of the implicit GEMM is the same shared memory shifted by
 // (kh*dh*PW + kw*dw) chunks, which a K-major no-swizzle shared-memory descriptor expresses
 // directly: MMA row r stands for patch pixel r, i.e. output (r / PW, r % PW) of the tile; rows
 // with r % PW >= BW or r / PW >= BH are computed and dropped.  No im2col matrix exists anywhere.
-// Weights arrive pre-blocked [filter tile][channel stage][tap][2][NT][16] by one bulk copy per stage.
+// Weights are pre-blocked [filter tile][channel stage][tap][CB][NT][16]; they stay resident in
+// shared memory when there is a single filter tile, else one bulk copy per stage streams them.
+// The epilogue requantises into a shared-memory image of the tile's NCHW bytes and copies it out
+// as one contiguous run per filter.
 //
-// Warp roles (448 threads, one persistent CTA per SM):
-//   warp 0      weight bulk copies          warp 1      TMEM owner + MMA issuer (taps MMAs per stage)
-//   warps 2-5   cp.async + transpose        warps 6-13  epilogue: TMEM -> requantise -> NCHW bytes
+// Warp roles (576 threads, one persistent CTA per SM):
+//   warp 0       loader (bulk copies)          warp 1        TMEM owner + MMA issuer
+//   warps 2-9    transpose                     warps 10-17   epilogue
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -41,12 +48,13 @@ struct TcConvArgs {
     int BH, BW, PH, PW, PR;           // tile, patch, allocated patch pixels per 16-channel group
     int hseg, wseg, c_stages, n_tiles;
     int CB;                           // 16-channel groups per stage (2, 4 or 8)
-    int G, NG, SP;                    // cp.async granule (4, 8 or 16 bytes), granules per staging row (max over tiles), staging row pitch
-    int log2G, log2V;
+    int full_width;                   // 1: a tile spans the image width and a channel's patch rows are one run; 0: one run per row
+    int RP;                           // staging bytes between two patch rows of a channel (W, or the run pitch when rows are separate runs)
+    int CP;                           // staging bytes per channel
+    int KN;                           // staging words per patch row that the transpose visits (upper bound over tiles)
+    int log2V;
     int w_resident;                   // all weights of the (single) filter tile stay in shared memory at off_wres
     int off_wres;
-    int LQ;                           // lanes that one channel's granules occupy in a cp.async instruction (power of two <= 32)
-    int KN;                           // staging words per patch row that the transpose visits (upper bound over tiles)
     int stages, stage_bytes, off_patch, off_stg, off_out;   // a stage = weights | patch | staging; off_out: output staging
     int V;                            // bytes per global store of the epilogue's copy-out (1, 2, 4, 8 or 16)
     uint32_t pad_word;                // the input zero point in all four bytes
@@ -62,19 +70,6 @@ constexpr int kTcConvThreads = 576;                             // 2 + 8 produce
 constexpr int kTcConvOutPitch = 128;                            // bytes per filter in the output staging buffer
 constexpr int kTcConvTail = 2 * kTcConvMaxFilters * 4 + 512;   // constants + barriers after the stages
 
-// cp.async of BYTES (4, 8 or 16) bytes, skipped when `on` is false (predicated inside the asm: no branch)
-template <int BYTES>
-__device__ __forceinline__ void cp_async_pred(uint32_t dst, const void* src, bool on) {
-    if constexpr (BYTES == 16)
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.cg.shared.global [%0], [%1], 16;\n\t}\n" ::"r"(dst), "l"(src), "r"((int)on) : "memory");
-    else if constexpr (BYTES == 8)
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.ca.shared.global [%0], [%1], 8;\n\t}\n" ::"r"(dst), "l"(src), "r"((int)on) : "memory");
-    else
-        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.ca.shared.global [%0], [%1], 4;\n\t}\n" ::"r"(dst), "l"(src), "r"((int)on) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 // out[p] = bytes (a[p], b[p], c[p], d[p]) for p = 0..3
 __device__ __forceinline__ void transpose_4x4_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t out[4]) {
     const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);
@@ -89,11 +84,15 @@ __device__ unsigned long long g_tc_conv_timers[256 * 32];
 #define ZB_T0() long long zb_t_ = clock64()
 #define ZB_TACC(slot) do { const long long n_ = clock64(); zb_acc_[slot] += n_ - zb_t_; zb_t_ = n_; } while (0)
 #define ZB_TDECL() long long zb_acc_[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define ZB_TSUB0() long long zb_q_ = clock64()
+#define ZB_TSUB(slot) do { const long long n_ = clock64(); zb_acc_[slot] += n_ - zb_q_; zb_q_ = n_; } while (0)
 #define ZB_TDUMP(base) do { for (int i_ = 0; i_ < 8; ++i_) g_tc_conv_timers[blockIdx.x * 32 + (base) + i_] = (unsigned long long)zb_acc_[i_]; } while (0)
 #else
 #define ZB_T0() do {} while (0)
 #define ZB_TACC(slot) do {} while (0)
 #define ZB_TDECL() do {} while (0)
+#define ZB_TSUB0() do {} while (0)
+#define ZB_TSUB(slot) do {} while (0)
 #define ZB_TDUMP(base) do {} while (0)
 #endif
 
@@ -107,11 +106,16 @@ __device__ __forceinline__ int tc_conv_round(int acc, float m) {
     return __float_as_int(__fadd_rn(t, 12582912.0f)) - 0x4B400000;
 }
 
-// Where a tile sits: image, first output row / column, filter tile, and the producer's view of
-// its input patch (first input row / column, loaded column range, staging alignment).
+// Where a tile sits: image, first output row / column, filter tile, and the loader's view of its
+// input patch: first input row / column, the patch rows and image columns that exist, and where
+// the data of a run lands in its staging slot.
 struct TcConvTile {
     int img, h0, w0, nt;
-    int h_in0, w_in0, iw_lo, iw_hi, seg_base, n_gran;
+    int h_in0, w_in0;
+    int hh_lo, hh_hi;        // patch rows [hh_lo, hh_hi) lie inside the image
+    int iw_lo, iw_hi;        // image columns [iw_lo, iw_hi) are loaded
+    int shift;               // bytes between the 16-byte boundary a run is copied from and its first wanted byte
+    int S0;                  // staging byte (within a row of a run) that holds patch column 0
 };
 
 // Mixed-radix counter over (image, row segment, column segment, filter tile) that advances by the
@@ -137,15 +141,21 @@ __device__ __forceinline__ TcConvTile tc_conv_tile(const TcConvArgs& a, const Tc
     TcConvTile r;
     r.nt = c.nt; r.img = c.img; r.h0 = c.hs * a.BH; r.w0 = c.ws * a.BW;
     r.h_in0 = r.h0 - a.pt; r.w_in0 = r.w0 - a.pl;
-    r.iw_lo = max(r.w_in0, 0); r.iw_hi = min(r.w_in0 + a.PW, a.W);
-    r.seg_base = r.iw_lo & ~(a.G - 1);
-    r.n_gran = r.iw_hi > r.iw_lo ? (r.iw_hi - r.seg_base + a.G - 1) >> a.log2G : 0;
+    r.hh_lo = max(0, -r.h_in0); r.hh_hi = min(a.PH, a.H - r.h_in0);
+    if (a.full_width) {
+        r.iw_lo = 0; r.iw_hi = a.W;
+        r.shift = ((r.h_in0 + r.hh_lo) * a.W) & 15;      // H*W % 16 == 0: the same for every channel
+    } else {
+        r.iw_lo = max(r.w_in0, 0); r.iw_hi = min(r.w_in0 + a.PW, a.W);
+        r.shift = r.iw_lo & 15;                          // W % 16 == 0: the same for every row and channel
+    }
+    r.S0 = r.shift + r.w_in0 - r.iw_lo;
     return r;
 }
 
 // LEAN: int8 output with zero point 0 and finite multipliers (requantisation by rni + saturating pack).
 template <int NT, bool XU8, bool LEAN>
-__global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const __grid_constant__ TcConvArgs a) {
+__global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const __grid_constant__ TcConvArgs a, const __grid_constant__ CUtensorMap x_map) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sStages = smem;
     uint8_t* sOut = smem + a.off_out;
@@ -163,6 +173,8 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     auto tfull = [&](int b) { return bar0 + 8u * (2 * kTcConvMaxStages + b); };
     auto tempty = [&](int b) { return bar0 + 8u * (2 * kTcConvMaxStages + 2 + b); };
     const uint32_t wfull = bar0 + 8u * (2 * kTcConvMaxStages + 4);
+    auto ld_full = [&](int s) { return bar0 + 8u * (2 * kTcConvMaxStages + 5 + s); };    // staging slot filled (bytes)
+    auto ld_empty = [&](int s) { return bar0 + 8u * (3 * kTcConvMaxStages + 5 + s); };   // staging slot read by all 8 transpose warps
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tiles = a.N * a.hseg * a.wseg * a.n_tiles;
@@ -173,6 +185,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), a.w_resident ? 1 : 2); ptx::mbar_init(empty(s), 1); }
         for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 8); }
+        for (int s = 0; s < S; ++s) { ptx::mbar_init(ld_full(s), 1); ptx::mbar_init(ld_empty(s), 8); }
         ptx::mbar_init(wfull, 1);
         *abort_flag = 0;
         *epi_ok = 1;
@@ -189,29 +202,44 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ weights: one bulk copy per stage
-        if (ptx::elect_one()) {
-            if (a.w_resident) {
-                // every tile uses the same weights: load them once
-                ptx::mbar_arrive_expect_tx(wfull, (uint32_t)a.c_stages * w_stage_bytes);
-                for (int cs = 0; cs < a.c_stages; ++cs)
-                    ptx::bulk_g2s(ptx::smem_u32(smem + a.off_wres) + (uint32_t)cs * w_stage_bytes, a.w + (size_t)cs * w_stage_bytes, w_stage_bytes, wfull);
-            } else {
-                TcConvCursor cur;
-                tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, cur);
-                int s = 0; uint32_t ph = 0;
-                for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
-                    const int8_t* gw = a.w + (size_t)cur.nt * a.c_stages * w_stage_bytes;
-                    for (int cs = 0; cs < a.c_stages; ++cs) {
-                        if (!ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag)) goto weights_done;
+        // ------------------------------------------------------------------ loader: bulk copies of activations (and weights)
+        if (a.w_resident && lane == 0) {
+            // every tile uses the same weights: load them once
+            ptx::mbar_arrive_expect_tx(wfull, (uint32_t)a.c_stages * w_stage_bytes);
+            for (int cs = 0; cs < a.c_stages; ++cs)
+                ptx::bulk_g2s(ptx::smem_u32(smem + a.off_wres) + (uint32_t)cs * w_stage_bytes, a.w + (size_t)cs * w_stage_bytes, w_stage_bytes, wfull);
+        }
+        // One tiled TMA load per stage: the box holds CB*16 channels x the bytes of the patch rows.  With
+        // full-width tiles the image plane is addressed as one row of H*W bytes (4-byte elements) and the
+        // box starts at the 16-byte boundary below the first wanted byte; otherwise the map is (W, H, C, N)
+        // and rows above or below the image arrive as zero fill.
+        const int CH = a.CB * 16;
+        const uint32_t box_bytes = (uint32_t)(CH * a.CP);
+        TcConvCursor cur;
+        tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, cur);
+        int s = 0; uint32_t ph = 0;
+        bool alive = true;
+        for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
+            const TcConvTile T = tc_conv_tile(a, cur);
+            tc_conv_cursor_next(a, cur);
+            for (int cs = 0; cs < a.c_stages; ++cs) {
+                // the slot's previous contents have been transposed (and, for streamed weights, multiplied)
+                bool ok = ptx::mbar_wait(ld_empty(s), ph ^ 1u, abort_flag);
+                if (ok && !a.w_resident) ok = ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag);
+                if (!ok) { alive = false; break; }
+                if (lane == 0) {
+                    const uint32_t stage0 = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
+                    ptx::mbar_arrive_expect_tx(ld_full(s), box_bytes);
+                    if (a.full_width) ptx::tma_load_3d(stage0 + (uint32_t)a.off_stg, &x_map, (((T.h_in0 + T.hh_lo) * a.W) - T.shift) >> 2, cs * CH, T.img, ld_full(s));
+                    else ptx::tma_load_4d(stage0 + (uint32_t)a.off_stg, &x_map, (T.iw_lo - T.shift) >> 2, T.h_in0, cs * CH, T.img, ld_full(s));
+                    if (!a.w_resident) {
                         ptx::mbar_arrive_expect_tx(full(s), w_stage_bytes);
-                        ptx::bulk_g2s(ptx::smem_u32(sStages + (size_t)s * a.stage_bytes), gw + (size_t)cs * w_stage_bytes, w_stage_bytes, full(s));
-                        if (++s == S) { s = 0; ph ^= 1u; }
+                        ptx::bulk_g2s(stage0, a.w + ((size_t)T.nt * a.c_stages + cs) * w_stage_bytes, w_stage_bytes, full(s));
                     }
-                    tc_conv_cursor_next(a, cur);
                 }
+                __syncwarp();
+                if (++s == S) { s = 0; ph ^= 1u; }
             }
-        weights_done:;
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -260,93 +288,31 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         mma_done:;
         }
     } else if (warp < 10) {
-        // ------------------------------------------------------------------ activation producers (256 threads)
-        const int p = tid - 64, pw = p >> 5;
-        const int CH = a.CB * 16;
-        const int chan_pitch = a.PH * a.SP;                    // staging bytes per channel
-        const int skew = 128 / a.CB;                           // each 16-channel group starts `skew` bytes later: conflict-free transposes
+        // ------------------------------------------------------------------ transpose: staging -> patch (256 threads)
+        const int p = tid - 64;
         const int my_tiles = (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
         const int total_it = my_tiles * a.c_stages;
-        const size_t plane = (size_t)a.H * a.W;
 
-        // Tile-independent work lists, decoded once: cp.async slots of one channel (per lane) and
-        // transpose items of one stage (per thread).
-        // A cp.async instruction of a warp covers 32 / LQ channels x LQ (row, granule) slots; a channel
-        // with more than 32 slots takes several rounds.
-        const int lsub = lane / a.LQ, lslot = lane - lsub * a.LQ;
-        const int ch_per_instr = 32 / a.LQ;
-        int ld_src[4], ld_dst[4], ld_hh[4], ld_gi[4];
-        {
-            const int row_slots = a.PH * a.NG;
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                const int idx = lslot + 32 * r;
-                const int hh = idx / a.NG, gi = idx - hh * a.NG;
-                const bool ok = idx < row_slots && (r == 0 || a.LQ == 32);
-                ld_hh[r] = ok ? hh : 0; ld_gi[r] = ok ? gi : 0x7fff;
-                ld_src[r] = ok ? hh * a.W + gi * a.G : 0;
-                ld_dst[r] = ok ? hh * a.SP + 16 + gi * a.G : 0;
-            }
-        }
-        const int rounds = a.LQ == 32 ? (a.PH * a.NG + 31) / 32 : 1;
-        // transpose items: 16 channels x 4 pixels each; consecutive threads take consecutive channel groups
-        // of the same pixels, so that a quarter warp's 16-byte stores and a warp's word loads spread over all banks
+        // transpose items: 16 channels x 4 pixels each, decoded once; consecutive threads take consecutive
+        // words of a patch row (conflict-free loads).  The 16-byte stores of a quarter warp would all fall
+        // into two bank groups; each lane therefore rotates its four pixels by (lane / 2) % 4 before the
+        // transposes and stores them in the rotated order, which spreads the stores over all banks.
         int t_stg[4], t_pat[4], t_hh[4], t_kk[4];
         {
             const int row_items = a.PH * a.KN, items = a.CB * row_items;
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 const int i = p + 256 * r;
-                const int rem = i / a.CB, blk = i - rem * a.CB;
+                const int blk = i / row_items, rem = i - blk * row_items;
                 const int hh = rem / a.KN, kk = rem - hh * a.KN;
                 const bool ok = i < items;
                 t_hh[r] = ok ? hh : 0; t_kk[r] = ok ? kk : 0x7fff;
-                t_stg[r] = ok ? (blk * 16 * a.PH + hh) * a.SP + kk * 4 + blk * skew : 0;
+                t_stg[r] = ok ? blk * 16 * a.CP + hh * a.RP + kk * 4 : 0;
                 t_pat[r] = ok ? (blk * a.PR + hh * a.PW + kk * 4) * 16 : 0;
             }
         }
-
-        // two cursors over the same (tile, channel stage) sequence: `li` issues loads S-1 stages ahead of `ci`
-        int li = 0, l_cs = 0, l_s = 0;
-        TcConvCursor lcur;
-        tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, lcur);
-        TcConvTile LT = tc_conv_tile(a, lcur);
-        auto issue_loads = [&]() {
-            if (li < total_it) {
-                const uint32_t stg = ptx::smem_u32(sStages + (size_t)l_s * a.stage_bytes + a.off_stg);
-                const uint8_t* xb = a.x + ((size_t)LT.img * a.C + (size_t)l_cs * CH) * plane + (ptrdiff_t)LT.h_in0 * a.W + LT.seg_base;
-                bool v[4];
-#pragma unroll
-                for (int r = 0; r < 4; ++r) v[r] = ld_gi[r] < LT.n_gran && (unsigned)(LT.h_in0 + ld_hh[r]) < (unsigned)a.H;
-                const int cmax = min(CH, a.C - l_cs * CH);
-                auto copy_all = [&](auto granule) {
-                    constexpr int GB = decltype(granule)::value;
-                    for (int c0 = pw * ch_per_instr; c0 < cmax; c0 += 8 * ch_per_instr) {
-                        const int cc = c0 + lsub;
-                        const bool c_ok = cc < cmax;
-                        const uint8_t* xc = xb + (size_t)cc * plane;
-                        const uint32_t dc = stg + (uint32_t)(cc * chan_pitch + (cc >> 4) * skew);
-                        cp_async_pred<GB>(dc + ld_dst[0], xc + ld_src[0], c_ok && v[0]);
-                        if (rounds > 1) cp_async_pred<GB>(dc + ld_dst[1], xc + ld_src[1], c_ok && v[1]);
-                        if (rounds > 2) cp_async_pred<GB>(dc + ld_dst[2], xc + ld_src[2], c_ok && v[2]);
-                        if (rounds > 3) cp_async_pred<GB>(dc + ld_dst[3], xc + ld_src[3], c_ok && v[3]);
-                    }
-                };
-                if (a.G == 16) copy_all(std::integral_constant<int, 16>{});
-                else if (a.G == 8) copy_all(std::integral_constant<int, 8>{});
-                else copy_all(std::integral_constant<int, 4>{});
-                ++li;
-                if (++l_s == S) l_s = 0;
-                if (++l_cs == a.c_stages) {
-                    l_cs = 0;
-                    tc_conv_cursor_next(a, lcur);
-                    LT = tc_conv_tile(a, lcur);
-                }
-            }
-            cp_async_commit();
-        };
-
-        for (int d = 0; d < S - 1; ++d) issue_loads();
+        const int rot = (lane >> 1) & 3;
+        const uint32_t rot_sel = rot == 0 ? 0x3210u : (rot == 1 ? 0x0321u : (rot == 2 ? 0x1032u : 0x2103u));
         int c_cs = 0, s = 0;
         uint32_t ph = 0;
         TcConvCursor ccur;
@@ -354,37 +320,29 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         TcConvTile CT = tc_conv_tile(a, ccur);
         ZB_TDECL(); ZB_T0();
         for (int ci = 0; ci < total_it; ++ci) {
-            issue_loads();
-            ZB_TACC(0);
-            switch (S - 1) {       // all but the S-1 newest groups of this thread are complete
-                case 1: cp_async_wait<1>(); break;
-                case 2: cp_async_wait<2>(); break;
-                case 3: cp_async_wait<3>(); break;
-                case 4: cp_async_wait<4>(); break;
-                default: cp_async_wait<5>(); break;
-            }
+            const bool loaded = ptx::mbar_wait(ld_full(s), ph, abort_flag);        // this stage's runs have landed
             ZB_TACC(1);
-            if (p == 0) ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag);   // a time-out raises the abort flag
+            if (p == 0) ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag);              // a time-out raises the abort flag
             ZB_TACC(2);
-            ptx::named_barrier_sync(2, 256);                    // the patch slot is free and every thread's copies have landed
-            if (*abort_flag) break;
+            ptx::named_barrier_sync(2, 256);                                        // the patch slot is free
+            if (!loaded || *abort_flag) break;
             ZB_TACC(3);
 
-            const int S0 = CT.w_in0 - CT.seg_base + 16;         // staging column of patch column 0
-            const int k_lo = S0 >> 2;
-            const int kn = ((S0 + a.PW - 1) >> 2) - k_lo + 1;
-            const uint8_t* stg = sStages + (size_t)s * a.stage_bytes + a.off_stg + k_lo * 4;
-            uint8_t* patch = sStages + (size_t)s * a.stage_bytes + a.off_patch + (k_lo * 4 - S0) * 16;
+            const int k_lo = CT.S0 >> 2;                                             // S0 may be negative: floor
+            const int kn = ((CT.S0 + a.PW - 1) >> 2) - k_lo + 1;
+            // full-width tiles: the run starts with patch row hh_lo; otherwise the box holds every patch row
+            const uint8_t* stg = sStages + (size_t)s * a.stage_bytes + a.off_stg + k_lo * 4 - (a.full_width ? CT.hh_lo * a.RP : 0);
+            uint8_t* patch = sStages + (size_t)s * a.stage_bytes + a.off_patch + (k_lo * 4 - CT.S0) * 16;
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
                 if (t_kk[r] < kn) {
                     const uint8_t* sp = stg + t_stg[r];
                     uint32_t wv[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) wv[j] = *reinterpret_cast<const uint32_t*>(sp + j * chan_pitch);
-                    const int ww0 = (k_lo + t_kk[r]) * 4 - S0;   // patch column of byte 0
+                    for (int j = 0; j < 16; ++j) wv[j] = *reinterpret_cast<const uint32_t*>(sp + j * a.CP);
+                    const int ww0 = (k_lo + t_kk[r]) * 4 - CT.S0;   // patch column of byte 0
                     const int iw0 = CT.w_in0 + ww0;
-                    const bool row_ok = (unsigned)(CT.h_in0 + t_hh[r]) < (unsigned)a.H;
+                    const bool row_ok = t_hh[r] >= CT.hh_lo && t_hh[r] < CT.hh_hi;
                     if (!row_ok || iw0 < 0 || iw0 + 3 >= a.W) {
                         // pixels outside the image hold the input zero point
                         uint32_t mask = 0;
@@ -394,18 +352,23 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
 #pragma unroll
                         for (int j = 0; j < 16; ++j) wv[j] = (wv[j] & mask) | (a.pad_word & ~mask);
                     }
-                    uint32_t o[4][4];    // o[group of 4 channels][pixel]
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) wv[j] = __byte_perm(wv[j], wv[j], rot_sel);
+                    uint32_t o[4][4];    // o[group of 4 channels][i] = pixel (i + rot) % 4
 #pragma unroll
                     for (int q = 0; q < 4; ++q) transpose_4x4_bytes(wv[4 * q], wv[4 * q + 1], wv[4 * q + 2], wv[4 * q + 3], o[q]);
                     uint8_t* dst = patch + t_pat[r];
 #pragma unroll
-                    for (int px = 0; px < 4; ++px) {
+                    for (int i = 0; i < 4; ++i) {
+                        const int px = (i + rot) & 3;
                         const int ww = ww0 + px;
-                        if (ww >= 0 && ww < a.PW) *reinterpret_cast<uint4*>(dst + px * 16) = make_uint4(o[0][px], o[1][px], o[2][px], o[3][px]);
+                        if (ww >= 0 && ww < a.PW) *reinterpret_cast<uint4*>(dst + px * 16) = make_uint4(o[0][i], o[1][i], o[2][i], o[3][i]);
                     }
                 }
             }
             ZB_TACC(4);
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ld_empty(s));                           // this warp is done reading the staging slot
             ptx::fence_proxy_async_smem();
             ptx::named_barrier_sync(2, 256);
             if (p == 0) ptx::mbar_arrive(full(s));
@@ -417,7 +380,6 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                 CT = tc_conv_tile(a, ccur);
             }
         }
-        cp_async_wait<0>();
         if (p == 0) ZB_TDUMP(8);
     } else {
         // ------------------------------------------------------------------ epilogue: warps 10..17
@@ -562,8 +524,7 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
     } else {
         a.H = g.H; a.W = g.W; a.OH = g.OH; a.OW = g.OW; a.pt = g.pt; a.pl = g.pl;
     }
-    if (a.W % 4 != 0 || a.pl > 16) return false;
-    a.G = a.W % 16 == 0 ? 16 : (a.W % 8 == 0 ? 8 : 4);
+    if (a.W % 4 != 0) return false;
     const int halo_w = (a.KW - 1) * a.dw, halo_h = (a.KH - 1) * a.dh;
     if (halo_w > 32 || halo_h > 32) return false;
     if (!pointwise && (g.pl > halo_w || g.pr > halo_w || g.pt > halo_h || g.pb > halo_h)) return false;   // every tile overlaps the image
@@ -574,19 +535,27 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
     a.PR = (128 + halo_h * a.PW + halo_w + 7) / 8 * 8 + 1;   // 1 mod 8: the channel groups of a pixel fall into different banks
     a.wseg = (a.OW + a.BW - 1) / a.BW;
     a.hseg = (a.OH + a.BH - 1) / a.BH;
-    a.NG = 1;
-    for (int ws = 0; ws < a.wseg; ++ws) {       // most granules any tile's patch row needs
-        const int w_in0 = ws * a.BW - a.pl;
-        const int lo = std::max(w_in0, 0), hi = std::min(w_in0 + a.PW, a.W);
-        if (hi > lo) a.NG = std::max(a.NG, (hi - (lo & ~(a.G - 1)) + a.G - 1) / a.G);
+    a.full_width = a.wseg == 1 ? 1 : 0;
+    // the bulk copies start at 16-byte boundaries; every channel of a stage must see the same offset
+    if (((long long)a.H * a.W) % 16 != 0) return false;
+    if (!a.full_width && a.W % 16 != 0) return false;
+    if (a.full_width) {
+        a.RP = a.W;
+        a.CP = (a.PH * a.W + 15 + 15) / 16 * 16;        // box row: the run plus its alignment slack
+        if (a.CP > 1024) return false;                  // box rows hold at most 256 four-byte elements
+        const int s0 = ((-a.pl) % 4 + 4) % 4;
+        a.KN = ((s0 + a.PW - 1) >> 2) + 1;
+    } else {
+        a.RP = (a.PW + 15 + 15) / 16 * 16;
+        a.CP = a.PH * a.RP;
+        if (a.PH > 256) return false;
+        a.KN = 1;
+        for (int ws = 0; ws < a.wseg; ++ws) {   // most staging words any tile's patch row spans
+            const int w_in0 = ws * a.BW - a.pl, lo = std::max(w_in0, 0);
+            const int s0 = (lo & 15) + w_in0 - lo;
+            a.KN = std::max(a.KN, ((s0 + a.PW - 1) >> 2) - (s0 >> 2) + 1);
+        }
     }
-    a.KN = 1;
-    for (int ws = 0; ws < a.wseg; ++ws) {       // most staging words any tile's patch row spans
-        const int w_in0 = ws * a.BW - a.pl;
-        const int s0 = w_in0 - (std::max(w_in0, 0) & ~(a.G - 1)) + 16;
-        a.KN = std::max(a.KN, ((s0 + a.PW - 1) >> 2) - (s0 >> 2) + 1);
-    }
-    a.SP = 32 + (a.PW + a.G + 15) / 16 * 16;
     p.NT = g.M <= 64 ? 64 : 128;
     if (pointwise && g.M > 128) p.NT = 256;
     a.m_pad = (g.M + p.NT - 1) / p.NT * p.NT;
@@ -605,8 +574,8 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
                 const long long w_all = (long long)c_stages * w_stage;
                 if (resident && (a.n_tiles != 1 || w_all > 112 * 1024)) continue;
                 const int off_patch = resident ? 0 : w_stage;
-                const int off_stg = off_patch + cb * a.PR * 16;
-                const int stage_bytes = (off_stg + cb * 16 * a.PH * a.SP + 128 + 127) / 128 * 128;   // + 128: room for the staging skew
+                const int off_stg = (off_patch + cb * a.PR * 16 + 127) / 128 * 128;   // TMA destination
+                const int stage_bytes = (off_stg + cb * 16 * a.CP + 128 + 127) / 128 * 128;   // + 128: the transposes may read a few bytes past the last channel
                 const int stages = std::min<long long>(kTcConvMaxStages, (budget - (resident ? w_all : 0)) / stage_bytes);
                 if (stages < min_stages) continue;
                 a.CB = cb; a.c_stages = c_stages; a.w_resident = resident; a.off_patch = off_patch; a.off_stg = off_stg;
@@ -616,10 +585,7 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
                 placed = true;
             }
     if (!placed) return false;
-    a.LQ = 1;
-    while (a.LQ < 32 && a.LQ < a.PH * a.NG) a.LQ *= 2;
-    if (a.PH * a.NG > 128 || a.CB * a.PH * a.KN > 1024) return false;   // the producers' per-thread work lists hold 4 entries
-    for (a.log2G = 0; (1 << a.log2G) < a.G; ++a.log2G) {}
+    if (a.CB * a.PH * a.KN > 1024) return false;   // the transposers' per-thread work lists hold 4 entries
     p.smem_bytes = (size_t)a.off_out + out_bytes + kTcConvTail;
     p.w_bytes = (size_t)a.n_tiles * a.c_stages * taps * a.CB * p.NT * 16;
     // one contiguous output run per filter and tile; V = widest store that every run start and length allows
@@ -659,20 +625,45 @@ inline void tc_conv_prepare(const TcConvPlan& p, const int8_t* w, const float* m
 }
 
 template <int NT, bool XU8, bool LEAN>
-inline int32_t tc_conv_launch_t(zant_ctx* ctx, const TcConvPlan& p, const TcConvArgs& a, int grid) {
+inline int32_t tc_conv_launch_t(zant_ctx* ctx, const TcConvPlan& p, const TcConvArgs& a, const CUtensorMap& x_map, int grid) {
     static bool attr_set = false;
     if (!attr_set) {
         ZB_CUDA(cudaFuncSetAttribute(tc_conv_nchw_kernel<NT, XU8, LEAN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
         attr_set = true;
     }
-    tc_conv_nchw_kernel<NT, XU8, LEAN><<<grid, kTcConvThreads, p.smem_bytes, ctx->stream>>>(a);
+    tc_conv_nchw_kernel<NT, XU8, LEAN><<<grid, kTcConvThreads, p.smem_bytes, ctx->stream>>>(a, x_map);
     return check_launch(ctx, "tc_conv_nchw_kernel");
 }
 
 template <int NT>
-inline int32_t tc_conv_launch_nt(zant_ctx* ctx, const TcConvPlan& p, const TcConvArgs& a, int grid, bool x_u8, bool lean) {
-    if (x_u8) return lean ? tc_conv_launch_t<NT, true, true>(ctx, p, a, grid) : tc_conv_launch_t<NT, true, false>(ctx, p, a, grid);
-    return lean ? tc_conv_launch_t<NT, false, true>(ctx, p, a, grid) : tc_conv_launch_t<NT, false, false>(ctx, p, a, grid);
+inline int32_t tc_conv_launch_nt(zant_ctx* ctx, const TcConvPlan& p, const TcConvArgs& a, const CUtensorMap& m, int grid, bool x_u8, bool lean) {
+    if (x_u8) return lean ? tc_conv_launch_t<NT, true, true>(ctx, p, a, m, grid) : tc_conv_launch_t<NT, true, false>(ctx, p, a, m, grid);
+    return lean ? tc_conv_launch_t<NT, false, true>(ctx, p, a, m, grid) : tc_conv_launch_t<NT, false, false>(ctx, p, a, m, grid);
+}
+
+// Tensor map over the NCHW input in 4-byte elements: (H*W/4, C, N) for full-width tiles (an image plane
+// is one row), (W/4, H, C, N) otherwise; box = the bytes of a stage.  Out-of-range elements read as zero.
+inline int32_t tc_conv_encode_map(const TcConvArgs& a, const void* x, CUtensorMap* map) {
+    const cuuint64_t W = (cuuint64_t)a.W, H = (cuuint64_t)a.H, C = (cuuint64_t)a.C, N = (cuuint64_t)a.N;
+    cuuint64_t dims[4], strides[3];
+    cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+    cuuint32_t rank;
+    if (a.full_width) {
+        rank = 3;
+        dims[0] = H * W / 4; dims[1] = C; dims[2] = N;
+        strides[0] = H * W; strides[1] = C * H * W;
+        box[0] = (cuuint32_t)(a.CP / 4); box[1] = (cuuint32_t)(a.CB * 16); box[2] = 1;
+    } else {
+        rank = 4;
+        dims[0] = W / 4; dims[1] = H; dims[2] = C; dims[3] = N;
+        strides[0] = W; strides[1] = H * W; strides[2] = C * H * W;
+        box[0] = (cuuint32_t)(a.RP / 4); box[1] = (cuuint32_t)a.PH; box[2] = (cuuint32_t)(a.CB * 16); box[3] = 1;
+    }
+    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, rank, const_cast<void*>(x), dims, strides, box, estr,
+                                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ZANT_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return ZANT_OK;
 }
 
 // x must be 16-byte aligned (cp.async granules); a y that is not falls back to byte stores.
@@ -695,9 +686,11 @@ inline int32_t tc_conv_run(zant_ctx* ctx, const TcConvPlan& p, const void* x, bo
     a.status = ctx->status_word;
     const long long tiles = (long long)a.N * a.hseg * a.wseg * a.n_tiles;
     const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
-    if (p.NT == 64) return tc_conv_launch_nt<64>(ctx, p, a, grid, x_u8, lean);
-    if (p.NT == 128) return tc_conv_launch_nt<128>(ctx, p, a, grid, x_u8, lean);
-    return tc_conv_launch_nt<256>(ctx, p, a, grid, x_u8, lean);
+    alignas(64) CUtensorMap x_map;
+    ZB_TRY(tc_conv_encode_map(a, x, &x_map));
+    if (p.NT == 64) return tc_conv_launch_nt<64>(ctx, p, a, x_map, grid, x_u8, lean);
+    if (p.NT == 128) return tc_conv_launch_nt<128>(ctx, p, a, x_map, grid, x_u8, lean);
+    return tc_conv_launch_nt<256>(ctx, p, a, x_map, grid, x_u8, lean);
 }
 
 inline bool all_finite(const std::vector<float>& v) {
