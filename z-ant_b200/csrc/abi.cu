@@ -457,7 +457,7 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
         const int iw = s.in(w_blk.data(), w_blk.size()), im = s.in(mp.data(), mp.size() * 4), ib = s.in(bp.data(), bp.size() * 4);
         ZB_TRY(s.commit());
         ZB_TRY(tc_conv_run(ctx, tcp, s.ptr<char>(ix), x_dtype == ZANT_U8, x_zp, s.ptr<int8_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
-                           s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, all_finite(mult)));
+                           s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, tc_conv_max_product(mp, bp, (long long)g.Cg * g.KH * g.KW)));
         return s.finish();
     }
     if (qconv_tc_eligible(g, wz_zero) && host_consts) {

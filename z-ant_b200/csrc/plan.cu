@@ -561,11 +561,11 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
                 std::vector<int8_t> w_blk; std::vector<float> mp; std::vector<int32_t> bp;
                 tc_conv_prepare(tcp, (const int8_t*)T(w).host.data(), mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, w_blk, mp, bp);
                 const int aw = pl->add_aux(w_blk.data(), w_blk.size()), am = pl->add_aux(mp.data(), mp.size() * 4), ab = pl->add_aux(bp.data(), bp.size() * 4);
-                const bool finite = all_finite(mult);
+                const double max_product = tc_conv_max_product(mp, bp, (long long)g.Cg * g.KH * g.KW);
                 push("QLinearConv(tc-implicit)", [=]() {
                     if (!tc_conv_ptr_ok(pl->ptr(x))) return fail(ZANT_E_INVALID_INPUT, "QLinearConv input buffer must be 16-byte aligned");
                     return tc_conv_run(ctx, tcp, pl->ptr(x), xd == ZANT_U8, xzp, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
-                                       (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq, finite);
+                                       (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq, max_product);
                 });
                 return ZANT_OK;
             }

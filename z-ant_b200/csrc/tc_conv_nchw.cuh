@@ -60,6 +60,7 @@ struct TcConvArgs {
     uint32_t pad_word;                // the input zero point in all four bytes
     float y_scale; int y_zp; int act; int out_u8;
     int six;                          // lean epilogue: sat8(rne(6 / y_scale)), used by ReLU6
+    int small_products;               // lean epilogue: every |accumulator * multiplier| is below 2^22 (host-checked bound)
     int m_pad;                        // filters rounded up to the tile width
     int* status;
 };
@@ -101,8 +102,10 @@ __device__ unsigned long long g_tc_conv_timers[256 * 32];
 // [-512, 2^22); larger products stay large and positive (the saturating pack turns them into 127,
 // as the clamp of the reference formula does), smaller ones are clamped to -512 first.  The
 // multiplier is finite (host-checked), so no NaN arrives here.
+template <bool CLAMP>
 __device__ __forceinline__ int tc_conv_round(int acc, float m) {
-    const float t = fmaxf(__fmul_rn(__int2float_rn(acc), m), -512.0f);
+    float t = __fmul_rn(__int2float_rn(acc), m);
+    if (CLAMP) t = fmaxf(t, -512.0f);
     return __float_as_int(__fadd_rn(t, 12582912.0f)) - 0x4B400000;
 }
 
@@ -394,6 +397,17 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         const int pix_off = oh_l * a.BW + ow_l;
         const size_t ohw = (size_t)a.OH * a.OW;
         const uint32_t six4 = 0x01010101u * (uint32_t)(a.six & 255);
+        // copy-out work split, fixed for the launch: a warp pass covers co_cpp filters x co_lpc lanes
+        // (a power of two that holds the vectors of a full tile's run)
+        int co_shift = 0;
+        {
+            const int l_full = a.wseg == 1 ? a.BH * a.OW : a.BW;
+            const int slots_full = (l_full >> a.log2V) + ((l_full & (a.V - 1)) ? 1 : 0);
+            while ((1 << co_shift) < slots_full && co_shift < 5) ++co_shift;
+        }
+        const int co_lpc = 1 << co_shift, co_cpp = 32 >> co_shift;
+        const int co_c0 = ew * co_cpp + (lane >> co_shift), co_v0 = lane & (co_lpc - 1);
+        const size_t co_dst_step = (size_t)(8 * co_cpp) * ohw;
         int tile_it = 0;
         TcConvCursor ecur;
         tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, ecur);
@@ -421,24 +435,29 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                 const int col0 = T.nt * NT + tcol0 + h * 32;
                 uint8_t* oc = orow + (size_t)h * 32 * kTcConvOutPitch;
                 if constexpr (LEAN) {
+                    auto lean_chunk = [&](auto clamp) {
+                        constexpr bool CL = decltype(clamp)::value;
 #pragma unroll
-                    for (int j4 = 0; j4 < 8; ++j4) {
-                        const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
-                        const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
-                        const int q0 = tc_conv_round((int)v[j4 * 4 + 0] + b4.x, m4.x);
-                        const int q1 = tc_conv_round((int)v[j4 * 4 + 1] + b4.y, m4.y);
-                        const int q2 = tc_conv_round((int)v[j4 * 4 + 2] + b4.z, m4.z);
-                        const int q3 = tc_conv_round((int)v[j4 * 4 + 3] + b4.w, m4.w);
-                        uint32_t pk = pack_sat_s8x4(q0, q1, q2, q3);
-                        if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
-                        if (a.act == ZANT_QACT_RELU6) pk = __vmins4(pk, six4);
-                        if (row_live) {
-                            oc[(j4 * 4 + 0) * kTcConvOutPitch] = (uint8_t)pk;
-                            oc[(j4 * 4 + 1) * kTcConvOutPitch] = (uint8_t)(pk >> 8);
-                            oc[(j4 * 4 + 2) * kTcConvOutPitch] = (uint8_t)(pk >> 16);
-                            oc[(j4 * 4 + 3) * kTcConvOutPitch] = (uint8_t)(pk >> 24);
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
+                            const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
+                            const int q0 = tc_conv_round<CL>((int)v[j4 * 4 + 0] + b4.x, m4.x);
+                            const int q1 = tc_conv_round<CL>((int)v[j4 * 4 + 1] + b4.y, m4.y);
+                            const int q2 = tc_conv_round<CL>((int)v[j4 * 4 + 2] + b4.z, m4.z);
+                            const int q3 = tc_conv_round<CL>((int)v[j4 * 4 + 3] + b4.w, m4.w);
+                            uint32_t pk = pack_sat_s8x4(q0, q1, q2, q3);
+                            if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
+                            if (a.act == ZANT_QACT_RELU6) pk = __vmins4(pk, six4);
+                            if (row_live) {
+                                oc[(j4 * 4 + 0) * kTcConvOutPitch] = (uint8_t)pk;
+                                oc[(j4 * 4 + 1) * kTcConvOutPitch] = (uint8_t)(pk >> 8);
+                                oc[(j4 * 4 + 2) * kTcConvOutPitch] = (uint8_t)(pk >> 16);
+                                oc[(j4 * 4 + 3) * kTcConvOutPitch] = (uint8_t)(pk >> 24);
+                            }
                         }
-                    }
+                    };
+                    if (a.small_products) lean_chunk(std::false_type{});
+                    else lean_chunk(std::true_type{});
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -460,26 +479,19 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             const int L = a.wseg == 1 ? min(a.BH, a.OH - T.h0) * a.OW : min(a.BW, a.OW - T.w0);
             const int nvec = L >> a.log2V, tail_bytes = L - (nvec << a.log2V);
             const int slots = nvec + (tail_bytes ? 1 : 0);
-            int shift = 0;
-            while ((1 << shift) < slots && shift < 5) ++shift;
-            const int lpc = 1 << shift, cpp = 32 >> shift;       // lanes per filter, filters per pass of a warp
-            uint8_t* yrun = a.y + ((size_t)T.img * a.M + (size_t)T.nt * NT) * ohw + (size_t)T.h0 * a.OW + T.w0;
-            for (int c0 = ew * cpp; c0 < ncv; c0 += 8 * cpp) {
-                const int c = c0 + (lane >> shift);
-                if (c < ncv) {
-                    const uint8_t* src = ob + (size_t)c * kTcConvOutPitch;
-                    uint8_t* dst = yrun + (size_t)c * ohw;
-                    for (int vv = lane & (lpc - 1); vv < slots; vv += lpc) {
-                        const int o = vv << a.log2V;
-                        if (vv < nvec) {
-                            if (a.V == 16) *reinterpret_cast<uint4*>(dst + o) = *reinterpret_cast<const uint4*>(src + o);
-                            else if (a.V == 8) *reinterpret_cast<uint2*>(dst + o) = *reinterpret_cast<const uint2*>(src + o);
-                            else if (a.V == 4) *reinterpret_cast<uint32_t*>(dst + o) = *reinterpret_cast<const uint32_t*>(src + o);
-                            else if (a.V == 2) *reinterpret_cast<uint16_t*>(dst + o) = *reinterpret_cast<const uint16_t*>(src + o);
-                            else dst[o] = src[o];
-                        } else {
-                            for (int i = 0; i < tail_bytes; ++i) dst[o + i] = src[o + i];
-                        }
+            uint8_t* dst = a.y + ((size_t)T.img * a.M + (size_t)(T.nt * NT + co_c0)) * ohw + (size_t)T.h0 * a.OW + T.w0;
+            const uint8_t* src = ob + co_c0 * kTcConvOutPitch;
+            for (int c = co_c0; c < ncv; c += 8 * co_cpp, dst += co_dst_step, src += 8 * co_cpp * kTcConvOutPitch) {
+                for (int vv = co_v0; vv < slots; vv += co_lpc) {
+                    const int o = vv << a.log2V;
+                    if (vv < nvec) {
+                        if (a.V == 16) *reinterpret_cast<uint4*>(dst + o) = *reinterpret_cast<const uint4*>(src + o);
+                        else if (a.V == 8) *reinterpret_cast<uint2*>(dst + o) = *reinterpret_cast<const uint2*>(src + o);
+                        else if (a.V == 4) *reinterpret_cast<uint32_t*>(dst + o) = *reinterpret_cast<const uint32_t*>(src + o);
+                        else if (a.V == 2) *reinterpret_cast<uint16_t*>(dst + o) = *reinterpret_cast<const uint16_t*>(src + o);
+                        else dst[o] = src[o];
+                    } else {
+                        for (int i = 0; i < tail_bytes; ++i) dst[o + i] = src[o + i];
                     }
                 }
             }
@@ -669,15 +681,18 @@ inline int32_t tc_conv_encode_map(const TcConvArgs& a, const void* x, CUtensorMa
 // x must be 16-byte aligned (cp.async granules); a y that is not falls back to byte stores.
 inline bool tc_conv_ptr_ok(const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) == 0; }
 
-// `mult_finite`: every requantisation multiplier is finite (checked by the caller on the host copy).
+// `max_product`: upper bound of |accumulator * multiplier| over all filters (tc_conv_max_product), infinity if
+// some multiplier is not finite.
 inline int32_t tc_conv_run(zant_ctx* ctx, const TcConvPlan& p, const void* x, bool x_u8, int x_zp, const int8_t* w_blk_dev,
-                           const float* mult_dev, const int32_t* bias_dev, void* y, bool y_u8, const Requant& rq, bool mult_finite) {
+                           const float* mult_dev, const int32_t* bias_dev, void* y, bool y_u8, const Requant& rq, double max_product) {
+    const bool mult_finite = std::isfinite(max_product);
     TcConvArgs a = p.a;
     a.x = (const uint8_t*)x; a.y = (uint8_t*)y; a.w = w_blk_dev; a.mult = mult_dev; a.bias = bias_dev;
     a.pad_word = 0x01010101u * (uint32_t)(x_zp & 255);
     a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0;
     if (!tc_conv_ptr_ok(y)) { a.V = 1; a.log2V = 0; }
     const bool lean = !y_u8 && rq.y_zp == 0 && mult_finite;
+    a.small_products = max_product < 4194304.0 ? 1 : 0;
     if (lean) {
         float v = 6.0f / rq.y_scale;
         v = std::fmin(std::fmax(v, -512.0f), 511.0f);
@@ -693,9 +708,15 @@ inline int32_t tc_conv_run(zant_ctx* ctx, const TcConvPlan& p, const void* x, bo
     return tc_conv_launch_nt<256>(ctx, p, a, x_map, grid, x_u8, lean);
 }
 
-inline bool all_finite(const std::vector<float>& v) {
-    for (float f : v) if (!std::isfinite(f)) return false;
-    return true;
+// Bound of |accumulator * multiplier|: an accumulator is at most 255 * 128 * K in magnitude plus the bias.
+inline double tc_conv_max_product(const std::vector<float>& mult, const std::vector<int32_t>& bias_folded, long long K) {
+    double worst = 0.0;
+    for (size_t m = 0; m < mult.size(); ++m) {
+        if (!std::isfinite(mult[m])) return INFINITY;
+        const double acc = 255.0 * 128.0 * (double)K + std::fabs((double)(m < bias_folded.size() ? bias_folded[m] : 0));
+        worst = std::max(worst, acc * std::fabs((double)mult[m]));
+    }
+    return worst;
 }
 
 }  // namespace zb
