@@ -142,6 +142,33 @@ TC_QCONV = [
 ]
 
 
+DW_QCONV = [
+    # N C H W stride xdt ydt xzp yzp per_channel bias act
+    (2, 128, 56, 56, 1, I8, I8, 0, 0, False, False, None),        # sweep case 3d
+    (3, 24, 28, 28, 1, U8, U8, 128, 9, True, True, "relu6"),      # four planes per warp, zero points
+    (2, 40, 8, 8, 1, I8, I8, -4, 0, True, True, "relu"),          # 16 planes per warp
+    (1, 7, 20, 112, 1, I8, U8, 3, 120, True, False, None),        # 28 of 32 lanes
+    (2, 96, 112, 112, 2, I8, I8, 0, 0, True, True, "relu6"),      # stride 2
+    (3, 18, 16, 24, 2, U8, I8, 7, -3, True, True, None),          # stride 2, uint8 input
+    (1, 5, 4, 8, 2, I8, I8, 0, 0, False, False, "relu"),          # smallest stride-2 plane
+]
+
+
+@pytest.mark.parametrize("case", DW_QCONV, ids=[f"dw{i}" for i in range(len(DW_QCONV))])
+def test_qlinearconv_depthwise3x3(zb, ctx, oracle, case):
+    N, C, H, W, stride, xdt, ydt, xzp, yzp, per_ch, has_bias, act = case
+    rng = np.random.default_rng(N * 41 + C + H + W)
+    x = q(rng, (N, C, H, W), xdt)
+    w = rng.integers(-127, 128, (C, 1, 3, 3), dtype=np.int8)
+    ws = (rng.random(C if per_ch else 1, dtype=np.float32) * 0.02 + 0.001).astype(np.float32)
+    bias = rng.integers(-3000, 3000, C).astype(np.int32) if has_bias else None
+    kw = dict(bias=bias, y_dtype=ydt, stride=(stride, stride), pads=(1, 1, 1, 1), dilations=(1, 1), group=C, activation=act)
+    got = ctx.qlinearconv(x, 0.02, xzp, w, ws, None, 0.045, yzp, **kw)
+    want = oracle.qlinearconv(x, 0.02, xzp, w, ws, None, 0.045, yzp, **kw)
+    assert np.array_equal(got, want)
+    assert len(np.unique(want)) > 16
+
+
 # stride-1 cases run the implicit-GEMM kernel (one launch), the others im2col + GEMM (two launches)
 TC_QCONV_LAUNCHES = [1, 2, 2, 1, 2]
 

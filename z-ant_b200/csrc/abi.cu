@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cmath>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -16,6 +17,7 @@
 #include "tc_peak.cuh"
 #include "tc_conv_generic.cuh"
 #include "tc_conv_nchw.cuh"
+#include "dwconv_q8.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -458,6 +460,20 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
         ZB_TRY(s.commit());
         ZB_TRY(tc_conv_run(ctx, tcp, s.ptr<char>(ix), x_dtype == ZANT_U8, x_zp, s.ptr<int8_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
                            s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, tc_conv_max_product(mp, bp, (long long)g.Cg * g.KH * g.KW)));
+        return s.finish();
+    }
+    if (host_consts && qdwconv_eligible(g, wz_zero) && (!is_device_ptr(x) || qdwconv_ptr_ok(x)) && (!is_device_ptr(y) || qdwconv_ptr_ok(y))) {
+        // depthwise 3x3: one HBM-bound pass
+        std::vector<uint32_t> wrow; std::vector<int32_t> bf;
+        qdwconv_prepare(g, w, bias, x_zp, wrow, bf);
+        bool finite = true;
+        for (float f : mult) finite = finite && std::isfinite(f);
+        Stager s(ctx);
+        const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
+        const int iw = s.in(wrow.data(), wrow.size() * 4), im = s.in(mult.data(), mult.size() * 4), ib = s.in(bf.data(), bf.size() * 4);
+        ZB_TRY(s.commit());
+        ZB_TRY(run_qdwconv(ctx, g, s.ptr<char>(ix), x_dtype == ZANT_U8, x_zp, s.ptr<uint32_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
+                           s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, finite));
         return s.finish();
     }
     if (qconv_tc_eligible(g, wz_zero) && host_consts) {

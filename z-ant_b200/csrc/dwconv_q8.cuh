@@ -1,0 +1,226 @@
+// Depthwise 3x3 QLinearConv (group == channels == filters, pads 1, dilation 1, stride 1 or 2) on
+// NCHW int8/uint8: an HBM-bound kernel, one pass over the input and one over the output.
+//
+// A lane owns a strip of a plane: 4 output columns, all rows.  It walks down the input rows with one
+// aligned 4-byte load per row (stride 2: two loads, 8 input columns); the neighbouring columns come
+// from the adjacent lanes by shuffle.  For each input row it forms the four 3-pixel windows with prmt and
+// feeds them to dp4a against the three filter rows (the fourth dp4a weight is 0), accumulating into
+// the output rows the input row belongs to; an output row is requantised, packed and stored as one
+// 4-byte word once its last input row has been seen.  Several narrow planes share a warp (LW lanes per
+// plane).  Pixels outside the image hold the input zero point, which is folded into the bias
+// (bias - x_zp * sum(w)) exactly as in the tensor-core paths.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <vector>
+
+#include "context.cuh"
+#include "geometry.hpp"
+#include "kernels_q8.cuh"
+
+namespace zb {
+
+struct QDwArgs {
+    const uint8_t* x; uint8_t* y;
+    const uint32_t* wrow;      // [C][3] filter rows packed for dp4a: bytes (w[kh][0], w[kh][1], w[kh][2], 0)
+    const float* mult; const int32_t* bias;   // [C]; bias already holds -x_zp * sum(w)
+    int planes, C, H, W, OH, OW;
+    int log2LW;                // lanes per plane = 1 << log2LW (covers OW / 4 columns of 4 outputs)
+    uint32_t pad_word;
+    float y_scale; int y_zp; int act; int out_u8;
+    int six;
+};
+
+template <bool XU8>
+__device__ __forceinline__ int dw_dp4a(uint32_t x, uint32_t w, int acc) {
+    int d;
+    if (XU8) asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    else asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(acc));
+    return d;
+}
+
+// Requantises four accumulators of one channel and packs them (little endian = ascending columns).
+template <bool LEAN>
+__device__ __forceinline__ uint32_t dw_requant4(const int acc[4], float m, const QDwArgs& p) {
+    if (LEAN) {
+        uint32_t pk = pack_sat_s8x4(rq_round(acc[0], m), rq_round(acc[1], m), rq_round(acc[2], m), rq_round(acc[3], m));
+        if (p.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
+        if (p.act == ZANT_QACT_RELU6) pk = __vmins4(pk, 0x01010101u * (uint32_t)(p.six & 255));
+        return pk;
+    }
+    const Requant rq{p.y_scale, p.y_zp, p.act};
+    uint32_t pk = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int q = p.out_u8 ? requant_one<true>(acc[i], m, rq) : requant_one<false>(acc[i], m, rq);
+        pk |= (uint32_t)(q & 255) << (8 * i);
+    }
+    return pk;
+}
+
+// STRIDE 1: lane = 4 input columns = 4 output columns.  STRIDE 2: lane = 8 input columns = 4 output columns.
+template <int STRIDE, bool XU8, bool LEAN>
+__global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
+    const int lane = threadIdx.x & 31;
+    const int LW = 1 << p.log2LW;
+    const int ppw = 32 >> p.log2LW;                          // planes per warp
+    const int sub = lane >> p.log2LW, col = lane & (LW - 1);
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int groups = (p.planes + ppw - 1) / ppw;
+    const int in_words = p.W >> 2;                           // 4-byte words per input row
+    const bool col_ok = col * 4 < p.OW;
+    for (int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; g < groups; g += warps) {
+        const int plane = g * ppw + sub;
+        const bool live = plane < p.planes && col_ok;
+        const int c = live ? plane % p.C : 0;
+        const uint32_t k0 = __ldg(p.wrow + c * 3), k1 = __ldg(p.wrow + c * 3 + 1), k2 = __ldg(p.wrow + c * 3 + 2);
+        const float m = __ldg(p.mult + c);
+        const int b = __ldg(p.bias + c);
+        const uint32_t* xin = reinterpret_cast<const uint32_t*>(p.x + (size_t)(live ? plane : 0) * p.H * p.W);
+        uint32_t* yout = reinterpret_cast<uint32_t*>(p.y + (size_t)(live ? plane : 0) * p.OH * p.OW) + col;
+        const int ow_words = p.OW >> 2;
+
+        if (STRIDE == 1) {
+            // acc[r]: output row (ih - 1 + r) while input row ih is being added; rows rotate through the three slots
+            int acc[3][4];
+#pragma unroll
+            for (int r = 0; r < 3; ++r)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[r][i] = b;
+            // input rows -1 .. H (the first and last are padding)
+            for (int base = -1; base <= p.H; base += 3) {
+#pragma unroll
+                for (int r = 0; r < 3; ++r) {
+                    const int ih = base + r;
+                    if (ih > p.H) break;
+                    const bool in_img = ih >= 0 && ih < p.H;
+                    const uint32_t M = (live && in_img) ? __ldg(xin + (size_t)ih * in_words + col) : p.pad_word;
+                    uint32_t L = __shfl_up_sync(0xffffffffu, M, 1), R = __shfl_down_sync(0xffffffffu, M, 1);
+                    if (col == 0) L = p.pad_word;
+                    if (col * 4 + 4 >= p.W) R = p.pad_word;
+                    const uint32_t w0 = __byte_perm(L, M, 0x6543), w1 = M, w2 = __byte_perm(M, R, 0x4321), w3 = __byte_perm(M, R, 0x5432);
+                    // slots: row ih-1 is (r+2)%3 [filter row 2], row ih is r%3... expressed with r compile-time:
+                    int* a_prev = acc[(r + 2) % 3];   // output row ih - 1: this input row is its filter row 2
+                    int* a_cur = acc[r % 3];          // output row ih: filter row 1
+                    int* a_next = acc[(r + 1) % 3];   // output row ih + 1: filter row 0
+                    a_prev[0] = dw_dp4a<XU8>(w0, k2, a_prev[0]); a_prev[1] = dw_dp4a<XU8>(w1, k2, a_prev[1]);
+                    a_prev[2] = dw_dp4a<XU8>(w2, k2, a_prev[2]); a_prev[3] = dw_dp4a<XU8>(w3, k2, a_prev[3]);
+                    a_cur[0] = dw_dp4a<XU8>(w0, k1, a_cur[0]); a_cur[1] = dw_dp4a<XU8>(w1, k1, a_cur[1]);
+                    a_cur[2] = dw_dp4a<XU8>(w2, k1, a_cur[2]); a_cur[3] = dw_dp4a<XU8>(w3, k1, a_cur[3]);
+                    a_next[0] = dw_dp4a<XU8>(w0, k0, a_next[0]); a_next[1] = dw_dp4a<XU8>(w1, k0, a_next[1]);
+                    a_next[2] = dw_dp4a<XU8>(w2, k0, a_next[2]); a_next[3] = dw_dp4a<XU8>(w3, k0, a_next[3]);
+                    // output row ih - 1 has now seen its three input rows
+                    const int oh = ih - 1;
+                    if (oh >= 0 && oh < p.OH) {
+                        const uint32_t pk = dw_requant4<LEAN>(a_prev, m, p);
+                        if (live) yout[(size_t)oh * ow_words] = pk;
+                    }
+                    a_prev[0] = a_prev[1] = a_prev[2] = a_prev[3] = b;   // the slot becomes output row ih + 2
+                }
+            }
+        } else {
+            // stride 2: output row oh reads input rows 2oh-1, 2oh, 2oh+1; lane holds input columns 8col .. 8col+7
+            int nxt[4] = {b, b, b, b};      // output row oh+1 so far (its filter row 0 = input row 2oh+1)
+            const int in_pairs = in_words;  // words per input row
+            for (int oh = 0; oh < p.OH; ++oh) {
+                int cur[4] = {nxt[0], nxt[1], nxt[2], nxt[3]};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) nxt[i] = b;
+                if (oh == 0) {
+                    // input row -1 is padding: filter row 0 sees the zero point everywhere
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) cur[i] = dw_dp4a<XU8>(p.pad_word, k0, cur[i]);
+                }
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                    const int ih = 2 * oh + rr;
+                    const bool in_img = ih < p.H;
+                    const bool ld0 = live && in_img && (col * 2) < in_pairs, ld1 = live && in_img && (col * 2 + 1) < in_pairs;
+                    const uint32_t M0 = ld0 ? __ldg(xin + (size_t)ih * in_words + col * 2) : p.pad_word;
+                    const uint32_t M1 = ld1 ? __ldg(xin + (size_t)ih * in_words + col * 2 + 1) : p.pad_word;
+                    uint32_t L = __shfl_up_sync(0xffffffffu, M1, 1);
+                    if (col == 0) L = p.pad_word;
+                    // windows centred on input columns 8col, 8col+2, 8col+4, 8col+6
+                    const uint32_t w0 = __byte_perm(L, M0, 0x6543), w1 = __byte_perm(M0, M0, 0x0321);
+                    const uint32_t w2 = __byte_perm(M0, M1, 0x6543), w3 = __byte_perm(M1, M1, 0x0321);
+                    if (rr == 0) {          // input row 2oh: filter row 1 of this output row
+                        cur[0] = dw_dp4a<XU8>(w0, k1, cur[0]); cur[1] = dw_dp4a<XU8>(w1, k1, cur[1]);
+                        cur[2] = dw_dp4a<XU8>(w2, k1, cur[2]); cur[3] = dw_dp4a<XU8>(w3, k1, cur[3]);
+                    } else {                // input row 2oh+1: filter row 2 of this output row, filter row 0 of the next
+                        cur[0] = dw_dp4a<XU8>(w0, k2, cur[0]); cur[1] = dw_dp4a<XU8>(w1, k2, cur[1]);
+                        cur[2] = dw_dp4a<XU8>(w2, k2, cur[2]); cur[3] = dw_dp4a<XU8>(w3, k2, cur[3]);
+                        nxt[0] = dw_dp4a<XU8>(w0, k0, nxt[0]); nxt[1] = dw_dp4a<XU8>(w1, k0, nxt[1]);
+                        nxt[2] = dw_dp4a<XU8>(w2, k0, nxt[2]); nxt[3] = dw_dp4a<XU8>(w3, k0, nxt[3]);
+                    }
+                }
+                const uint32_t pk = dw_requant4<LEAN>(cur, m, p);
+                if (live) yout[(size_t)oh * ow_words] = pk;
+            }
+        }
+    }
+}
+
+// Shapes the kernel covers: 3x3, group == channels == filters, pads 1 on every side, dilation 1,
+// stride 1 or 2 on both axes, rows that are whole 4-byte words on both sides, weight zero points 0.
+inline bool qdwconv_eligible(const ConvGeom& g, bool w_zp_all_zero) {
+    if (!w_zp_all_zero || g.G != g.C || g.M != g.C || g.Cg != 1 || g.KH != 3 || g.KW != 3) return false;
+    if (g.dh != 1 || g.dw != 1 || g.pt != 1 || g.pl != 1 || g.pb != 1 || g.pr != 1) return false;
+    if (g.sh != g.sw || (g.sh != 1 && g.sh != 2)) return false;
+    if (g.W % 4 != 0 || g.OW % 4 != 0 || g.OW > 128) return false;
+    if (g.sh == 2 && (g.W != 2 * g.OW || g.H != 2 * g.OH)) return false;   // even sizes: no pixel right of / below the last window
+    return (long long)g.N * g.C <= 0x7fffffffLL;
+}
+
+// Host constants: filter rows packed for dp4a and the bias with the input zero point folded in.
+inline void qdwconv_prepare(const ConvGeom& g, const int8_t* w, const int32_t* bias, int x_zp, std::vector<uint32_t>& wrow, std::vector<int32_t>& bias_f) {
+    wrow.assign((size_t)g.C * 3, 0);
+    bias_f.assign(g.C, 0);
+    for (int c = 0; c < g.C; ++c) {
+        int sum = 0;
+        for (int kh = 0; kh < 3; ++kh) {
+            uint32_t word = 0;
+            for (int kw = 0; kw < 3; ++kw) {
+                const int8_t v = w[(size_t)c * 9 + kh * 3 + kw];
+                word |= (uint32_t)(uint8_t)v << (8 * kw);
+                sum += v;
+            }
+            wrow[(size_t)c * 3 + kh] = word;
+        }
+        bias_f[c] = (bias ? bias[c] : 0) - x_zp * sum;
+    }
+}
+
+template <int STRIDE>
+inline int32_t qdwconv_launch_s(zant_ctx* ctx, const QDwArgs& a, int grid, bool x_u8, bool lean) {
+    if (x_u8) { if (lean) qdwconv3x3_kernel<STRIDE, true, true><<<grid, 256, 0, ctx->stream>>>(a); else qdwconv3x3_kernel<STRIDE, true, false><<<grid, 256, 0, ctx->stream>>>(a); }
+    else { if (lean) qdwconv3x3_kernel<STRIDE, false, true><<<grid, 256, 0, ctx->stream>>>(a); else qdwconv3x3_kernel<STRIDE, false, false><<<grid, 256, 0, ctx->stream>>>(a); }
+    return check_launch(ctx, "qdwconv3x3_kernel");
+}
+
+// x and y must be 4-byte aligned (the caller checks with qdwconv_ptr_ok).
+inline bool qdwconv_ptr_ok(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
+
+inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool x_u8, int x_zp, const uint32_t* wrow_dev, const float* mult_dev,
+                           const int32_t* bias_dev, void* y, bool y_u8, const Requant& rq, bool mult_finite) {
+    QDwArgs a{};
+    a.x = (const uint8_t*)x; a.y = (uint8_t*)y; a.wrow = wrow_dev; a.mult = mult_dev; a.bias = bias_dev;
+    a.planes = g.N * g.C; a.C = g.C; a.H = g.H; a.W = g.W; a.OH = g.OH; a.OW = g.OW;
+    const int cols = g.OW / 4;
+    for (a.log2LW = 0; (1 << a.log2LW) < cols; ++a.log2LW) {}
+    a.pad_word = 0x01010101u * (uint32_t)(x_zp & 255);
+    a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0;
+    const bool lean = !y_u8 && rq.y_zp == 0 && mult_finite;
+    if (lean) {
+        float v = 6.0f / rq.y_scale;
+        v = std::fmin(std::fmax(v, -512.0f), 511.0f);
+        a.six = std::min(std::max((int)std::nearbyintf(v), -128), 127);
+    }
+    const int ppw = 32 >> a.log2LW;
+    const long long groups = ((long long)a.planes + ppw - 1) / ppw;
+    const int grid = (int)std::min<long long>((groups + 7) / 8, (long long)ctx->sm_count * 16);
+    if (grid == 0) return ZANT_OK;
+    return g.sh == 1 ? qdwconv_launch_s<1>(ctx, a, grid, x_u8, lean) : qdwconv_launch_s<2>(ctx, a, grid, x_u8, lean);
+}
+
+}  // namespace zb

@@ -7,6 +7,7 @@
 #include <cstdint>
 #include <cstring>
 #include <algorithm>
+#include <cmath>
 #include <functional>
 #include <memory>
 #include <string>
@@ -20,6 +21,7 @@
 #include "tc_gemm.cuh"
 #include "tc_conv_generic.cuh"
 #include "tc_conv_nchw.cuh"
+#include "dwconv_q8.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -566,6 +568,20 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
                     if (!tc_conv_ptr_ok(pl->ptr(x))) return fail(ZANT_E_INVALID_INPUT, "QLinearConv input buffer must be 16-byte aligned");
                     return tc_conv_run(ctx, tcp, pl->ptr(x), xd == ZANT_U8, xzp, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
                                        (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq, max_product);
+                });
+                return ZANT_OK;
+            }
+            if ((b < 0 || T(b).is_const) && qdwconv_eligible(g, wz_zero)) {
+                // depthwise 3x3: one HBM-bound pass; arena tensors are 256-byte aligned
+                std::vector<uint32_t> wrow; std::vector<int32_t> bf;
+                qdwconv_prepare(g, (const int8_t*)T(w).host.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, wrow, bf);
+                bool finite = true;
+                for (float f : mult) finite = finite && std::isfinite(f);
+                const int aw = pl->add_aux(wrow.data(), wrow.size() * 4), am = pl->add_aux(mult.data(), mult.size() * 4), ab = pl->add_aux(bf.data(), bf.size() * 4);
+                push("QLinearConv(depthwise)", [=]() {
+                    if (!qdwconv_ptr_ok(pl->ptr(x)) || !qdwconv_ptr_ok(pl->ptr(y))) return fail(ZANT_E_INVALID_INPUT, "depthwise QLinearConv buffers must be 4-byte aligned");
+                    return run_qdwconv(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, (const uint32_t*)pl->aux(aw), (const float*)pl->aux(am),
+                                       (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq, finite);
                 });
                 return ZANT_OK;
             }
