@@ -88,19 +88,25 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
             for (int r = 0; r < 3; ++r)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[r][i] = b;
-            // input rows -1 .. H (the first and last are padding)
+            // input rows -1 .. H (the first and last are padding), three per trip; the loads of the next trip
+            // are issued before this trip's arithmetic so that their latency is covered
+            auto load_row = [&](int ih) -> uint32_t {
+                return (live && ih >= 0 && ih < p.H) ? __ldg(xin + (size_t)ih * in_words + col) : p.pad_word;
+            };
+            uint32_t nx0 = load_row(-1), nx1 = load_row(0), nx2 = load_row(1);
             for (int base = -1; base <= p.H; base += 3) {
+                const uint32_t cur_rows[3] = {nx0, nx1, nx2};
+                nx0 = load_row(base + 3); nx1 = load_row(base + 4); nx2 = load_row(base + 5);
 #pragma unroll
                 for (int r = 0; r < 3; ++r) {
                     const int ih = base + r;
                     if (ih > p.H) break;
-                    const bool in_img = ih >= 0 && ih < p.H;
-                    const uint32_t M = (live && in_img) ? __ldg(xin + (size_t)ih * in_words + col) : p.pad_word;
+                    const uint32_t M = cur_rows[r];
                     uint32_t L = __shfl_up_sync(0xffffffffu, M, 1), R = __shfl_down_sync(0xffffffffu, M, 1);
                     if (col == 0) L = p.pad_word;
                     if (col * 4 + 4 >= p.W) R = p.pad_word;
                     const uint32_t w0 = __byte_perm(L, M, 0x6543), w1 = M, w2 = __byte_perm(M, R, 0x4321), w3 = __byte_perm(M, R, 0x5432);
-                    // slots: row ih-1 is (r+2)%3 [filter row 2], row ih is r%3... expressed with r compile-time:
+                    // base is -1 mod 3, so r is (ih + 1) % 3 at compile time and names the slots of the three output rows
                     int* a_prev = acc[(r + 2) % 3];   // output row ih - 1: this input row is its filter row 2
                     int* a_cur = acc[r % 3];          // output row ih: filter row 1
                     int* a_next = acc[(r + 1) % 3];   // output row ih + 1: filter row 0
@@ -122,7 +128,12 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
         } else {
             // stride 2: output row oh reads input rows 2oh-1, 2oh, 2oh+1; lane holds input columns 8col .. 8col+7
             int nxt[4] = {b, b, b, b};      // output row oh+1 so far (its filter row 0 = input row 2oh+1)
-            const int in_pairs = in_words;  // words per input row
+            const bool c0 = live && (col * 2) < in_words, c1 = live && (col * 2 + 1) < in_words;
+            auto load_w = [&](int ih, int k, bool on) -> uint32_t {
+                return (on && ih < p.H) ? __ldg(xin + (size_t)ih * in_words + col * 2 + k) : p.pad_word;
+            };
+            // the four words of the next output row are loaded while this one is computed
+            uint32_t n00 = load_w(0, 0, c0), n01 = load_w(0, 1, c1), n10 = load_w(1, 0, c0), n11 = load_w(1, 1, c1);
             for (int oh = 0; oh < p.OH; ++oh) {
                 int cur[4] = {nxt[0], nxt[1], nxt[2], nxt[3]};
 #pragma unroll
@@ -132,13 +143,12 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) cur[i] = dw_dp4a<XU8>(p.pad_word, k0, cur[i]);
                 }
+                const uint32_t rows[2][2] = {{n00, n01}, {n10, n11}};
+                n00 = load_w(2 * oh + 2, 0, c0); n01 = load_w(2 * oh + 2, 1, c1);
+                n10 = load_w(2 * oh + 3, 0, c0); n11 = load_w(2 * oh + 3, 1, c1);
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
-                    const int ih = 2 * oh + rr;
-                    const bool in_img = ih < p.H;
-                    const bool ld0 = live && in_img && (col * 2) < in_pairs, ld1 = live && in_img && (col * 2 + 1) < in_pairs;
-                    const uint32_t M0 = ld0 ? __ldg(xin + (size_t)ih * in_words + col * 2) : p.pad_word;
-                    const uint32_t M1 = ld1 ? __ldg(xin + (size_t)ih * in_words + col * 2 + 1) : p.pad_word;
+                    const uint32_t M0 = rows[rr][0], M1 = rows[rr][1];
                     uint32_t L = __shfl_up_sync(0xffffffffu, M1, 1);
                     if (col == 0) L = p.pad_word;
                     // windows centred on input columns 8col, 8col+2, 8col+4, 8col+6
