@@ -227,6 +227,76 @@ def run_qconv_workload(args, zb, ctx, models, torch, stream, rank, world, local,
     plan.close()
 
 
+def run_graph_workload(args, zb, ctx, models, torch, stream, rank, world, local, int8_peak_tops):
+    """Whole-network workloads beside the headline one (--workload mobilenetv2_int8 | tinyyolo_int8 |
+    tinyyolo_fp32): device-resident images/s of one plan pass per step, with the per-step time table."""
+    if args.workload == "mobilenetv2_int8":
+        batch = args.batch if args.batch != BATCH_PER_GPU else 1024
+        graph = models.mobilenetv2_int8(batch)
+        x = models.mobilenetv2_input(batch)
+        name = "MobileNetV2-style int8 classifier, 224x224"
+    else:
+        batch = args.batch if args.batch != BATCH_PER_GPU else 32
+        fp32 = models.tiny_yolo_fp32(batch)
+        x = models.tiny_yolo_input(batch)
+        if args.workload == "tinyyolo_int8":
+            small = models.tiny_yolo_fp32(2)
+            scales = models.activation_scales_on_gpu(ctx, small, models.tiny_yolo_input(2))
+            graph = models.tiny_yolo_int8(fp32, scales)
+        else:
+            graph = fp32
+        name = "Tiny-YOLOv3-style detector, 416x416, " + ("int8" if args.workload == "tinyyolo_int8" else "FP32")
+    plan = zb.Plan(ctx, graph, fuse=not args.no_fuse)
+    x_dev = torch.from_numpy(x).cuda()
+    out_shape = tuple(graph.tensors[graph.output]["shape"])
+    y_dev = torch.empty(out_shape, dtype=torch.float32, device="cuda")
+    run = lambda: plan.run(x_dev, out=y_dev)    # noqa: E731
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            run()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local) if rank == 0 else None
+        if sampler:
+            sampler.start()
+        plan.profile(True)
+        ctx.reset_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            run()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        launches = ctx.launch_count()
+        step_ms, runs = plan.profile_read()
+        plan.profile(False)
+        clocks = sampler.stop() if sampler else None
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        names = plan.step_names()
+        per = [m / max(runs, 1) for m in step_ms]
+        by_kind = {}
+        for n, m in zip(names, per):
+            by_kind[n] = by_kind.get(n, 0.0) + m
+        top = sorted(range(len(per)), key=lambda i: -per[i])[:8]
+        macs = graph.meta.get("macs_per_image") if hasattr(graph, "meta") else None
+        line = dict(metric=f"images/sec ({name})", value=batch * world / (ms / 1e3), unit="images/s", n_gpus=world, steps=args.steps,
+                    warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
+                    dtype="f32" if args.workload == "tinyyolo_fp32" else "int8", data="synthetic",
+                    config=dict(workload=name, batch_per_gpu=batch, l2="activations larger than L2", parallelism=f"sample-sharded x{world}, no collective"),
+                    roofline=None, int8_peak_tops=int8_peak_tops, macs_per_image=macs,
+                    tops=(2.0 * macs * batch / (ms / 1e3) / 1e12) if macs else None,
+                    ms_by_step_kind={k: round(v, 4) for k, v in sorted(by_kind.items(), key=lambda kv: -kv[1])},
+                    top_steps=[dict(step=i, kind=names[i], ms=round(per[i], 4)) for i in top],
+                    cpu_baseline=None, e2e=None, gpu_launches=int(launches) * world, clocks=clocks, arena_bytes=plan.arena_bytes)
+        print(json.dumps(line), flush=True)
+    plan.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -236,7 +306,7 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU per step")
     ap.add_argument("--no-fuse", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
-    ap.add_argument("--workload", default="small_cnn_int8", choices=["small_cnn_int8", "qconv3a", "qconv3b", "qconv3c", "qconv3d"],
+    ap.add_argument("--workload", default="small_cnn_int8", choices=["small_cnn_int8", "qconv3a", "qconv3b", "qconv3c", "qconv3d", "mobilenetv2_int8", "tinyyolo_int8", "tinyyolo_fp32"],
                     help="small_cnn_int8 is the headline workload; the qconv cases time one standalone operator")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="chunks of the batch that the end-to-end path pipelines")
     args = ap.parse_args()
@@ -266,8 +336,9 @@ def main():
 
     int8_peak_tops = ctx.measure_int8_peak(20000) if rank == 0 else None   # resident-tile tcgen05 probe, ~15 ms
 
-    if args.workload.startswith("qconv"):
-        run_qconv_workload(args, zb, ctx, models, torch, stream, rank, world, local, ctx.measure_int8_peak(20000))
+    if args.workload != "small_cnn_int8":
+        fn = run_qconv_workload if args.workload.startswith("qconv") else run_graph_workload
+        fn(args, zb, ctx, models, torch, stream, rank, world, local, ctx.measure_int8_peak(20000))
         ctx.close()
         if world > 1:
             dist.destroy_process_group()
