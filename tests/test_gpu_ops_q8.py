@@ -118,6 +118,15 @@ def test_maxpool_q8(ctx, oracle, dt):
 
 
 @pytest.mark.parametrize("dt", [I8, U8])
+@pytest.mark.parametrize("shape", [(2, 5, 16, 24), (1, 3, 2, 8), (3, 16, 52, 104)])
+def test_maxpool_q8_2x2_stride2_rows_of_whole_words(ctx, oracle, dt, shape):
+    """The packed-byte kernel (even H, W % 8 == 0) against the oracle."""
+    x = q(np.random.default_rng(shape[3]), shape, dt)
+    args = ((2, 2), (2, 2), (1, 1), (0, 0, 0, 0), "NOTSET")
+    assert np.array_equal(ctx.onnx_maxpool(x, *args), oracle.onnx_maxpool(x, *args))
+
+
+@pytest.mark.parametrize("dt", [I8, U8])
 @pytest.mark.parametrize("n", [1, 15, 16, 4097])
 def test_leaky_relu_lut(ctx, oracle, dt, n):
     lut = oracle.build_leaky_lut(dt, 0.05, 3 if dt == U8 else 0, 0.1, 0.04, 5 if dt == U8 else 0)
@@ -151,6 +160,11 @@ DW_QCONV = [
     (2, 96, 112, 112, 2, I8, I8, 0, 0, True, True, "relu6"),      # stride 2
     (3, 18, 16, 24, 2, U8, I8, 7, -3, True, True, None),          # stride 2, uint8 input
     (1, 5, 4, 8, 2, I8, I8, 0, 0, False, False, "relu"),          # smallest stride-2 plane
+    (3, 48, 14, 14, 1, I8, I8, 0, 0, True, True, "relu6"),        # rows that are not whole words
+    (5, 21, 7, 7, 1, U8, U8, 100, 3, True, True, None),           # 49-byte planes, tensor size not a multiple of 4
+    (2, 36, 14, 14, 2, I8, I8, -2, 0, True, True, "relu6"),       # stride 2 onto 7x7
+    (1, 3, 5, 9, 1, I8, U8, 0, 17, False, False, None),           # odd sizes
+    (2, 8, 6, 10, 2, U8, I8, 9, 0, True, False, "relu"),          # stride 2, 10 -> 5 columns
 ]
 
 

@@ -9,6 +9,9 @@
 // 4-byte word once its last input row has been seen.  Several narrow planes share a warp (LW lanes per
 // plane).  Pixels outside the image hold the input zero point, which is folded into the bias
 // (bias - x_zp * sum(w)) exactly as in the tensor-core paths.
+// ALIGNED: rows are whole 4-byte words (W % 4 == 0 and OW % 4 == 0).  Otherwise the four bytes of a lane
+// are cut out of the two aligned words that hold them and the outputs are stored bytewise, which covers
+// any width (the 14x14 and 7x7 planes of mobile networks).
 #pragma once
 #include <cuda_runtime.h>
 
@@ -26,6 +29,7 @@ struct QDwArgs {
     const uint32_t* wrow;      // [C][3] filter rows packed for dp4a: bytes (w[kh][0], w[kh][1], w[kh][2], 0)
     const float* mult; const int32_t* bias;   // [C]; bias already holds -x_zp * sum(w)
     int planes, C, H, W, OH, OW;
+    long long x_bytes;         // size of x (the unaligned variant never reads a word that extends past it)
     int log2LW;                // lanes per plane = 1 << log2LW (covers OW / 4 columns of 4 outputs)
     uint32_t pad_word;
     float y_scale; int y_zp; int act; int out_u8;
@@ -60,7 +64,27 @@ __device__ __forceinline__ uint32_t dw_requant4(const int acc[4], float m, const
 }
 
 // STRIDE 1: lane = 4 input columns = 4 output columns.  STRIDE 2: lane = 8 input columns = 4 output columns.
-template <int STRIDE, bool XU8, bool LEAN>
+// Four consecutive bytes of x starting at byte offset `off` (any alignment); bytes at or beyond `limit`
+// (the end of the row) are replaced by the padding byte.
+__device__ __forceinline__ uint32_t dw_load_unaligned(const QDwArgs& p, long long off, int n_valid) {
+    uint32_t v;
+    if (off + 8 <= p.x_bytes) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(p.x) + (off >> 2);
+        const uint32_t a = __ldg(w), b = __ldg(w + 1);
+        v = __byte_perm(a, b, 0x3210u + 0x1111u * (uint32_t)(off & 3));
+    } else {                   // the last bytes of the tensor: one by one
+        v = 0;
+        for (int i = 0; i < 4; ++i)
+            if (off + i < p.x_bytes) v |= (uint32_t)__ldg(p.x + off + i) << (8 * i);
+    }
+    if (n_valid < 4) {
+        const uint32_t mask = n_valid <= 0 ? 0u : (0xffffffffu >> (8 * (4 - n_valid)));
+        v = (v & mask) | (p.pad_word & ~mask);
+    }
+    return v;
+}
+
+template <int STRIDE, bool XU8, bool LEAN, bool ALIGNED>
 __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
     const int lane = threadIdx.x & 31;
     const int LW = 1 << p.log2LW;
@@ -70,6 +94,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
     const int groups = (p.planes + ppw - 1) / ppw;
     const int in_words = p.W >> 2;                           // 4-byte words per input row
     const bool col_ok = col * 4 < p.OW;
+    const int out_valid = p.OW - col * 4;                    // output columns of this lane (>= 4: all)
     for (int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; g < groups; g += warps) {
         const int plane = g * ppw + sub;
         const bool live = plane < p.planes && col_ok;
@@ -80,6 +105,16 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
         const uint32_t* xin = reinterpret_cast<const uint32_t*>(p.x + (size_t)(live ? plane : 0) * p.H * p.W);
         uint32_t* yout = reinterpret_cast<uint32_t*>(p.y + (size_t)(live ? plane : 0) * p.OH * p.OW) + col;
         const int ow_words = p.OW >> 2;
+        const long long xplane = (long long)(live ? plane : 0) * p.H * p.W;
+        uint8_t* yplane = p.y + (size_t)(live ? plane : 0) * p.OH * p.OW + col * 4;
+        auto store_row = [&](int oh, uint32_t pk) {
+            if (!live) return;
+            if (ALIGNED) { yout[(size_t)oh * ow_words] = pk; return; }
+            uint8_t* d = yplane + (size_t)oh * p.OW;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (i < out_valid) d[i] = (uint8_t)(pk >> (8 * i));
+        };
 
         if (STRIDE == 1) {
             // acc[r]: output row (ih - 1 + r) while input row ih is being added; rows rotate through the three slots
@@ -91,7 +126,9 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
             // input rows -1 .. H (the first and last are padding), three per trip; the loads of the next trip
             // are issued before this trip's arithmetic so that their latency is covered
             auto load_row = [&](int ih) -> uint32_t {
-                return (live && ih >= 0 && ih < p.H) ? __ldg(xin + (size_t)ih * in_words + col) : p.pad_word;
+                if (!(live && ih >= 0 && ih < p.H)) return p.pad_word;
+                if (ALIGNED) return __ldg(xin + (size_t)ih * in_words + col);
+                return dw_load_unaligned(p, xplane + (long long)ih * p.W + col * 4, p.W - col * 4);
             };
             uint32_t nx0 = load_row(-1), nx1 = load_row(0), nx2 = load_row(1);
             for (int base = -1; base <= p.H; base += 3) {
@@ -119,8 +156,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
                     // output row ih - 1 has now seen its three input rows
                     const int oh = ih - 1;
                     if (oh >= 0 && oh < p.OH) {
-                        const uint32_t pk = dw_requant4<LEAN>(a_prev, m, p);
-                        if (live) yout[(size_t)oh * ow_words] = pk;
+                        store_row(oh, dw_requant4<LEAN>(a_prev, m, p));
                     }
                     a_prev[0] = a_prev[1] = a_prev[2] = a_prev[3] = b;   // the slot becomes output row ih + 2
                 }
@@ -128,9 +164,11 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
         } else {
             // stride 2: output row oh reads input rows 2oh-1, 2oh, 2oh+1; lane holds input columns 8col .. 8col+7
             int nxt[4] = {b, b, b, b};      // output row oh+1 so far (its filter row 0 = input row 2oh+1)
-            const bool c0 = live && (col * 2) < in_words, c1 = live && (col * 2 + 1) < in_words;
+            const bool c0 = live && col * 8 < p.W, c1 = live && col * 8 + 4 < p.W;
             auto load_w = [&](int ih, int k, bool on) -> uint32_t {
-                return (on && ih < p.H) ? __ldg(xin + (size_t)ih * in_words + col * 2 + k) : p.pad_word;
+                if (!(on && ih < p.H)) return p.pad_word;
+                if (ALIGNED) return __ldg(xin + (size_t)ih * in_words + col * 2 + k);
+                return dw_load_unaligned(p, xplane + (long long)ih * p.W + col * 8 + k * 4, p.W - col * 8 - k * 4);
             };
             // the four words of the next output row are loaded while this one is computed
             uint32_t n00 = load_w(0, 0, c0), n01 = load_w(0, 1, c1), n10 = load_w(1, 0, c0), n11 = load_w(1, 1, c1);
@@ -164,20 +202,19 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
                         nxt[2] = dw_dp4a<XU8>(w2, k0, nxt[2]); nxt[3] = dw_dp4a<XU8>(w3, k0, nxt[3]);
                     }
                 }
-                const uint32_t pk = dw_requant4<LEAN>(cur, m, p);
-                if (live) yout[(size_t)oh * ow_words] = pk;
+                store_row(oh, dw_requant4<LEAN>(cur, m, p));
             }
         }
     }
 }
 
 // Shapes the kernel covers: 3x3, group == channels == filters, pads 1 on every side, dilation 1,
-// stride 1 or 2 on both axes, rows that are whole 4-byte words on both sides, weight zero points 0.
+// stride 1 or 2 on both axes (even sizes for stride 2), at most 128 output columns, weight zero points 0.
 inline bool qdwconv_eligible(const ConvGeom& g, bool w_zp_all_zero) {
     if (!w_zp_all_zero || g.G != g.C || g.M != g.C || g.Cg != 1 || g.KH != 3 || g.KW != 3) return false;
     if (g.dh != 1 || g.dw != 1 || g.pt != 1 || g.pl != 1 || g.pb != 1 || g.pr != 1) return false;
     if (g.sh != g.sw || (g.sh != 1 && g.sh != 2)) return false;
-    if (g.W % 4 != 0 || g.OW % 4 != 0 || g.OW > 128) return false;
+    if (g.OW > 128) return false;
     if (g.sh == 2 && (g.W != 2 * g.OW || g.H != 2 * g.OH)) return false;   // even sizes: no pixel right of / below the last window
     return (long long)g.N * g.C <= 0x7fffffffLL;
 }
@@ -201,10 +238,10 @@ inline void qdwconv_prepare(const ConvGeom& g, const int8_t* w, const int32_t* b
     }
 }
 
-template <int STRIDE>
+template <int STRIDE, bool ALIGNED>
 inline int32_t qdwconv_launch_s(zant_ctx* ctx, const QDwArgs& a, int grid, bool x_u8, bool lean) {
-    if (x_u8) { if (lean) qdwconv3x3_kernel<STRIDE, true, true><<<grid, 256, 0, ctx->stream>>>(a); else qdwconv3x3_kernel<STRIDE, true, false><<<grid, 256, 0, ctx->stream>>>(a); }
-    else { if (lean) qdwconv3x3_kernel<STRIDE, false, true><<<grid, 256, 0, ctx->stream>>>(a); else qdwconv3x3_kernel<STRIDE, false, false><<<grid, 256, 0, ctx->stream>>>(a); }
+    if (x_u8) { if (lean) qdwconv3x3_kernel<STRIDE, true, true, ALIGNED><<<grid, 256, 0, ctx->stream>>>(a); else qdwconv3x3_kernel<STRIDE, true, false, ALIGNED><<<grid, 256, 0, ctx->stream>>>(a); }
+    else { if (lean) qdwconv3x3_kernel<STRIDE, false, true, ALIGNED><<<grid, 256, 0, ctx->stream>>>(a); else qdwconv3x3_kernel<STRIDE, false, false, ALIGNED><<<grid, 256, 0, ctx->stream>>>(a); }
     return check_launch(ctx, "qdwconv3x3_kernel");
 }
 
@@ -216,7 +253,8 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
     QDwArgs a{};
     a.x = (const uint8_t*)x; a.y = (uint8_t*)y; a.wrow = wrow_dev; a.mult = mult_dev; a.bias = bias_dev;
     a.planes = g.N * g.C; a.C = g.C; a.H = g.H; a.W = g.W; a.OH = g.OH; a.OW = g.OW;
-    const int cols = g.OW / 4;
+    a.x_bytes = (long long)g.N * g.C * g.H * g.W;
+    const int cols = (g.OW + 3) / 4;
     for (a.log2LW = 0; (1 << a.log2LW) < cols; ++a.log2LW) {}
     a.pad_word = 0x01010101u * (uint32_t)(x_zp & 255);
     a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0;
@@ -230,7 +268,9 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
     const long long groups = ((long long)a.planes + ppw - 1) / ppw;
     const int grid = (int)std::min<long long>((groups + 7) / 8, (long long)ctx->sm_count * 16);
     if (grid == 0) return ZANT_OK;
-    return g.sh == 1 ? qdwconv_launch_s<1>(ctx, a, grid, x_u8, lean) : qdwconv_launch_s<2>(ctx, a, grid, x_u8, lean);
+    const bool aligned = g.W % 4 == 0 && g.OW % 4 == 0;
+    if (g.sh == 1) return aligned ? qdwconv_launch_s<1, true>(ctx, a, grid, x_u8, lean) : qdwconv_launch_s<1, false>(ctx, a, grid, x_u8, lean);
+    return aligned ? qdwconv_launch_s<2, true>(ctx, a, grid, x_u8, lean) : qdwconv_launch_s<2, false>(ctx, a, grid, x_u8, lean);
 }
 
 }  // namespace zb

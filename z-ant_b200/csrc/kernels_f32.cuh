@@ -212,6 +212,24 @@ __global__ void maxpool_nchw(const T* __restrict__ x, T* __restrict__ y, const P
     }
 }
 
+// 2x2 / stride 2 / no padding on 8-bit planes whose rows are whole 8-byte groups (W % 8 == 0, even H):
+// a thread reads 8 bytes of two input rows, takes the row-wise maximum with one packed byte-max, then
+// the maximum of neighbouring bytes, and stores 4 outputs.  Same values as maxpool_nchw.
+template <bool SIGNED>
+__global__ void maxpool2x2s2_q8(const uint2* __restrict__ x, uint32_t* __restrict__ y, size_t planes_rows, int ow4, int w8) {
+    // planes_rows = NC * OH output rows; an output row has ow4 words, its two input rows have w8 (= ow4) uint2 each
+    const size_t total = planes_rows * (size_t)ow4;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / ow4;
+        const int c = (int)(i - row * ow4);
+        const uint2 a = __ldg(x + (row * 2) * (size_t)w8 + c), b = __ldg(x + (row * 2 + 1) * (size_t)w8 + c);
+        const uint32_t m0 = SIGNED ? __vmaxs4(a.x, b.x) : __vmaxu4(a.x, b.x);
+        const uint32_t m1 = SIGNED ? __vmaxs4(a.y, b.y) : __vmaxu4(a.y, b.y);
+        const uint32_t even = __byte_perm(m0, m1, 0x6420), odd = __byte_perm(m0, m1, 0x7531);
+        y[i] = SIGNED ? __vmaxs4(even, odd) : __vmaxu4(even, odd);
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // Element-wise activations: float4 body when both pointers are 16-byte aligned, scalar tail.
 // ------------------------------------------------------------------------------------------

@@ -1,6 +1,7 @@
 // Device-level operator launchers: resolved geometry + device pointers -> kernel launches on
 // the context's stream.  Shared by the single-operator C entry points and by the plan.
 #pragma once
+#include <type_traits>
 #include "context.cuh"
 #include "geometry.hpp"
 #include "kernels_f32.cuh"
@@ -64,6 +65,20 @@ template <typename T>
 inline int32_t run_maxpool(zant_ctx* ctx, const PoolGeom& g, const T* x, T* y) {
     const size_t total = (size_t)g.NC * g.OH * g.OW;
     if (total == 0) return ZANT_OK;
+    if constexpr (sizeof(T) == 1) {
+        const bool fast = g.KH == 2 && g.KW == 2 && g.sh == 2 && g.sw == 2 && g.dh == 1 && g.dw == 1 && g.pt == 0 && g.pl == 0 &&
+                          g.W % 8 == 0 && g.H == 2 * g.OH && g.W == 2 * g.OW &&
+                          (reinterpret_cast<uintptr_t>(x) & 7u) == 0 && (reinterpret_cast<uintptr_t>(y) & 3u) == 0;
+        if (fast) {
+            const size_t words = total / 4;
+            const int grid = grid_for(words, 256, ctx->sm_count, 16);
+            if (std::is_signed<T>::value)
+                maxpool2x2s2_q8<true><<<grid, 256, 0, ctx->stream>>>((const uint2*)x, (uint32_t*)y, (size_t)g.NC * g.OH, g.OW / 4, g.W / 8);
+            else
+                maxpool2x2s2_q8<false><<<grid, 256, 0, ctx->stream>>>((const uint2*)x, (uint32_t*)y, (size_t)g.NC * g.OH, g.OW / 4, g.W / 8);
+            return check_launch(ctx, "maxpool2x2s2_q8");
+        }
+    }
     maxpool_nchw<T><<<grid_for(total, 256, ctx->sm_count), 256, 0, ctx->stream>>>(x, y, g);
     return check_launch(ctx, "maxpool_nchw");
 }

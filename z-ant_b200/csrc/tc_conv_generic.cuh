@@ -127,7 +127,7 @@ inline int32_t run_qconv_tc(zant_ctx* ctx, const ConvGeom& g, const void* x, boo
 inline bool qconv_tc_eligible(const ConvGeom& g, bool w_zp_all_zero) {
     const long long M = (long long)g.N * g.OH * g.OW;
     const long long K = (long long)g.Cg * g.KH * g.KW;
-    return g.G == 1 && w_zp_all_zero && M >= 256 && g.M <= 1024 && K <= 65536 && (M + 127) / 128 * 128 * ((K + 63) / 64 * 64) <= (8LL << 30);
+    return g.G == 1 && w_zp_all_zero && M >= 256 && g.M <= 2048 && K <= 65536 && (M + 127) / 128 * 128 * ((K + 63) / 64 * 64) <= (8LL << 30);
 }
 
 }  // namespace zb

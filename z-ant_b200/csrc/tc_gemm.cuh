@@ -45,7 +45,7 @@ struct TcGemmCfg {
     static constexpr int A_STAGE = KC * 128 * 16;
     static constexpr int W_STAGE = KC * NT * 16;
     static constexpr int STAGE = A_STAGE + W_STAGE;
-    static constexpr int MAX_N = 1024;                       // per-column constants kept in shared memory
+    static constexpr int MAX_N = 2048;                       // per-column constants kept in shared memory
     static constexpr int OFF_STAGES = 0;
     static constexpr int OFF_CONST = OFF_STAGES + STAGES * STAGE;   // float mult[MAX_N]; int bias[MAX_N]
     static constexpr int OFF_BAR = OFF_CONST + 2 * MAX_N * 4;
