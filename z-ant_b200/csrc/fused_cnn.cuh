@@ -29,10 +29,8 @@ enum DeviceError : int {
 // =============================================================================================
 // Stage 1: QuantizeLinear(uint8) + QLinearConv(1 -> 32, 3x3, stride 1, no pad) + ReLU + MaxPool 2x2/2
 //          float [N,1,28,28]  ->  int8 C16-planar [N][2][13*13][16]
-// CUDA cores: the contraction is only 9 deep, too shallow for a 32-byte MMA K step.  Each thread
-// owns one pooled pixel: it holds the 4x4 input patch as four packed words and evaluates the four
-// conv windows of all 32 channels with dp4a against weights packed in the kernel parameters
-// (constant bank), three dp4a per window.
+// Host-side description of the stage (the plan fills it from the graph; the kernel below takes its
+// own argument block derived from it).
 // =============================================================================================
 struct Conv1Args {
     const float* x;
@@ -45,68 +43,9 @@ struct Conv1Args {
     float y_scale; int y_zp; int act;
 };
 
-__device__ __forceinline__ int dp4a_us(uint32_t a_u8x4, uint32_t b_s8x4, int c) {
-    int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_u8x4), "r"(b_s8x4), "r"(c));
-    return d;
-}
-
-constexpr int C1_G = 3;          // images per CTA iteration: 3*169 = 507 pooled pixels for 256 threads
-constexpr int C1_THREADS = 256;
-
-__global__ void __launch_bounds__(C1_THREADS) conv1_quant_relu_pool_kernel(const __grid_constant__ Conv1Args a) {
-    __shared__ uint32_t img[C1_G][28][8];   // rows of 32 bytes (28 pixels + 4 pad)
-    const int tid = threadIdx.x;
-    for (int base = blockIdx.x * C1_G; base < a.n_images; base += gridDim.x * C1_G) {
-        for (int i = tid; i < C1_G * 784; i += C1_THREADS) {
-            const int g = i / 784, p = i - g * 784;
-            int q = 0;
-            if (base + g < a.n_images) {
-                const float v = __ldg(a.x + (size_t)(base + g) * 784 + p);
-                q = sat_q<true>(rne_clamped(__fdiv_rn(v, a.x_scale)) + a.x_zp);
-            }
-            const int r = p / 28, c = p - r * 28;
-            reinterpret_cast<uint8_t*>(&img[g][r][0])[c] = (uint8_t)q;
-        }
-        __syncthreads();
-        for (int i = tid; i < C1_G * 169; i += C1_THREADS) {
-            const int g = i / 169, pp = i - g * 169;
-            if (base + g >= a.n_images) continue;
-            const int py = pp / 13, px = pp - py * 13;
-            uint32_t X[4];
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                const uint32_t* row = &img[g][2 * py + r][0];
-                const uint32_t w0 = row[px >> 1];
-                X[r] = (px & 1) ? __byte_perm(w0, row[(px >> 1) + 1], 0x5432) : w0;
-            }
-            uint32_t out[8];
-#pragma unroll
-            for (int m4 = 0; m4 < 8; ++m4) {
-                int r[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int m = m4 * 4 + j;
-                    const int b = a.bias[m];    // max(acc_i) + b == max(acc_i + b): the bias seeds every window
-                    const int a00 = dp4a_us(X[0], a.wpack[m][0][0], dp4a_us(X[1], a.wpack[m][1][0], dp4a_us(X[2], a.wpack[m][2][0], b)));
-                    const int a01 = dp4a_us(X[0], a.wpack[m][0][1], dp4a_us(X[1], a.wpack[m][1][1], dp4a_us(X[2], a.wpack[m][2][1], b)));
-                    const int a10 = dp4a_us(X[1], a.wpack[m][0][0], dp4a_us(X[2], a.wpack[m][1][0], dp4a_us(X[3], a.wpack[m][2][0], b)));
-                    const int a11 = dp4a_us(X[1], a.wpack[m][0][1], dp4a_us(X[2], a.wpack[m][1][1], dp4a_us(X[3], a.wpack[m][2][1], b)));
-                    r[j] = rq_round(max(max(a00, a01), max(a10, a11)), a.mult[m]);
-                }
-                out[m4] = relu_s8x4(pack_sat_s8x4(r[0], r[1], r[2], r[3]));
-            }
-            int8_t* yo = a.y + ((size_t)(base + g) * 2 * 169 + pp) * 16;
-            *reinterpret_cast<uint4*>(yo) = make_uint4(out[0], out[1], out[2], out[3]);
-            *reinterpret_cast<uint4*>(yo + 169 * 16) = make_uint4(out[4], out[5], out[6], out[7]);
-        }
-        __syncthreads();
-    }
-}
-
 // =============================================================================================
-// Stage 1, tensor-core form.  Same operator chain and output as conv1_quant_relu_pool_kernel, but
-// the 3x3 contraction runs on warp-level int8 MMAs (mma.sync m16n8k16, u8 x s8 -> s32):
+// Stage 1 kernel.  The contraction is only 9 deep and the input has one channel, so the 128-row
+// tcgen05 shape has nothing to contract over; the 3x3 contraction runs on warp-level int8 MMAs (mma.sync m16n8k16, u8 x s8 -> s32):
 //   rows    = 16 pooled pixels (two per thread-row group g and g+8),
 //   K (16)  = the 4x4 input patch of a pooled pixel, byte (r,s) at k = 4r + s, so a thread's A
 //             register is simply patch row r = lane%4 as one packed word,
