@@ -671,7 +671,22 @@ inline int32_t tc_conv_encode_map(const TcConvArgs& a, const void* x, CUtensorMa
         strides[0] = W; strides[1] = H * W; strides[2] = C * H * W;
         box[0] = (cuuint32_t)(a.RP / 4); box[1] = (cuuint32_t)a.PH; box[2] = (cuuint32_t)(a.CB * 16); box[3] = 1;
     }
-    const CUresult r = cuTensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, rank, const_cast<void*>(x), dims, strides, box, estr,
+    // The driver entry point is looked up at run time, so that the library itself does not link against
+    // libcuda (it must load on machines without a driver, where only its symbols are inspected).
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+            cudaGetLastError();
+            return fail(ZANT_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        }
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, rank, const_cast<void*>(x), dims, strides, box, estr,
                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(ZANT_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
