@@ -323,12 +323,14 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         TcConvTile CT = tc_conv_tile(a, ccur);
         ZB_TDECL(); ZB_T0();
         for (int ci = 0; ci < total_it; ++ci) {
-            const bool loaded = ptx::mbar_wait(ld_full(s), ph, abort_flag);        // this stage's runs have landed
-            ZB_TACC(1);
-            if (p == 0) ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag);              // a time-out raises the abort flag
+            // one thread polls (a time-out raises the abort flag); the others park at the barrier
+            if (p == 0) {
+                if (ptx::mbar_wait(ld_full(s), ph, abort_flag))                     // this stage's box has landed
+                    ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag);                  // the patch slot is free
+            }
             ZB_TACC(2);
-            ptx::named_barrier_sync(2, 256);                                        // the patch slot is free
-            if (!loaded || *abort_flag) break;
+            ptx::named_barrier_sync(2, 256);
+            if (*abort_flag) break;
             ZB_TACC(3);
 
             const int k_lo = CT.S0 >> 2;                                             // S0 may be negative: floor
