@@ -431,10 +431,11 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             uint8_t* orow = ob + (size_t)tcol0 * kTcConvOutPitch + pix_off;
 #pragma unroll 1
             for (int h = 0; h < NT / 64; ++h) {
+                const int col0 = T.nt * NT + tcol0 + h * 32;
+                if (col0 >= a.M) break;                              // the rest of the tile is filter padding
                 uint32_t v[32];
                 ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
                 ptx::tmem_wait_ld();
-                const int col0 = T.nt * NT + tcol0 + h * 32;
                 uint8_t* oc = orow + (size_t)h * 32 * kTcConvOutPitch;
                 if constexpr (LEAN) {
                     auto lean_chunk = [&](auto clamp) {
