@@ -422,6 +422,29 @@ def main():
     if not torch.equal(y_dev.cpu(), y_host):
         raise SystemExit("bench: end-to-end result differs from the device-resident result")
 
+    latency = None
+    if rank == 0:
+        # batch-1 latency of one predict() call on pinned host buffers (host clock around run + synchronize),
+        # with separate launches and with the plan's captured CUDA graph
+        g1 = models.small_cnn_int8(1, act_scales=scales)
+        p1 = zb.Plan(ctx, g1, fuse=not args.no_fuse)
+        x1, y1 = x_host[:1], torch.empty((1, 10), dtype=torch.float32).pin_memory()
+        latency = {}
+        for mode in ("launches", "graph"):
+            p1.use_graph(mode == "graph")
+            for _ in range(50):
+                p1.run(x1, out=y1)
+            ctx.synchronize()
+            samples = []
+            for _ in range(300):
+                t0 = time.perf_counter()
+                p1.run(x1, out=y1)
+                ctx.synchronize()
+                samples.append((time.perf_counter() - t0) * 1e6)
+            latency[mode + "_us_median"] = round(float(np.median(samples)), 2)
+        latency["kernels_per_call"] = p1.launches_per_run
+        p1.close()
+
     if rank == 0:
         peaks = measured_peaks()
         total_images = batch * world * args.steps
@@ -477,7 +500,7 @@ def main():
                     e2e=dict(value=total_images / (ms_e2e / 1e3), unit="images/s", h2d_bytes_per_step=batch * 784 * 4,
                              d2h_bytes_per_step=batch * 10 * 4, ms_per_step=ms_e2e / args.steps, chunks=n_chunks,
                              how="plan.run on pinned host buffers, chunks alternate between two contexts (copy/compute overlap)"),
-                    gpu_launches=int(launches) * world, clocks=clocks, arena_bytes=plan.arena_bytes)
+                    gpu_launches=int(launches) * world, clocks=clocks, arena_bytes=plan.arena_bytes, batch1_latency=latency)
         print(json.dumps(line), flush=True)
     plan.close()
     ctx.close()

@@ -483,6 +483,14 @@ int32_t zant_b200_plan_finalize(zant_plan* plan, int32_t input_id, int32_t outpu
  * stream; zant_b200_ctx_synchronize waits for it and reports device-side errors. */
 int32_t zant_b200_plan_run(zant_plan* plan, const void* input, void* output);
 
+/* Captures the plan's launches into a CUDA graph (enable != 0) or drops it (enable == 0).  With a
+ * graph, zant_b200_plan_run replays all steps with one cudaGraphLaunch: what the reference's
+ * generated predict() does with a fixed sequence of calls, minus the per-launch cost, which is
+ * what batch-1 latency consists of.  Inputs and outputs always pass through the arena's own input and
+ * output buffers then (device buffers are copied in and out).  Results are identical to the
+ * un-captured run; per-step profiling falls back to separate launches while it is enabled. */
+int32_t zant_b200_plan_use_graph(zant_plan* plan, int32_t enable);
+
 /* Bytes of the plan's arena and number of kernels one run launches. */
 size_t zant_b200_plan_arena_bytes(zant_plan* plan);
 int32_t zant_b200_plan_launches_per_run(zant_plan* plan);

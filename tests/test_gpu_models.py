@@ -211,3 +211,29 @@ def test_full_size_graphs_plan_and_run(zb, ctx, models):
     assert yf.shape == (1, 255, 26, 26) and np.isfinite(yf).all()
     assert pf.read_tensor(f.meta["head13"]).shape == (1, 255, 13, 13)
     pf.close()
+
+
+def test_plan_graph_replay_matches_separate_launches(zb, ctx, models, scales):
+    """One captured CUDA graph per run: same bytes as the step-by-step run, host and device buffers."""
+    import torch
+    for g, x in ((models.small_cnn_int8(4, act_scales=scales), models.small_cnn_input(4)),
+                 (models.mobilenetv2_int8(1, res=96, classes=1000), models.mobilenetv2_input(1, 96))):
+        plan = zb.Plan(ctx, g, fuse=True)
+        want = plan.run(x).copy()
+        plan.use_graph(True)
+        before = ctx.launch_count()
+        got = plan.run(x)
+        assert ctx.launch_count() - before == plan.launches_per_run
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        xd = torch.from_numpy(x).cuda()
+        yd = torch.empty(tuple(want.shape), dtype=torch.float32, device="cuda")
+        plan.run(xd, out=yd)
+        ctx.synchronize()
+        assert np.array_equal(yd.cpu().numpy().view(np.uint32), want.view(np.uint32))
+        # a second input through the same graph
+        x2 = np.ascontiguousarray(x[::-1]) if x.shape[0] > 1 else (255 - x if x.dtype == np.uint8 else 1.0 - x)
+        plan.use_graph(False)
+        want2 = plan.run(x2).copy()
+        plan.use_graph(True)
+        assert np.array_equal(plan.run(x2).view(np.uint32), want2.view(np.uint32))
+        plan.close()

@@ -673,6 +673,10 @@ class Plan:
         L = lib()
         return [L.zant_b200_plan_step_name(self._h, C.c_int32(i)).decode() for i in range(L.zant_b200_plan_step_count(self._h))]
 
+    def use_graph(self, enable=True):
+        """Replays all steps as one captured CUDA graph per run (batch-1 latency)."""
+        check(lib().zant_b200_plan_use_graph(self._h, C.c_int32(int(enable))))
+
     def profile(self, enable=True):
         check(lib().zant_b200_plan_profile(self._h, C.c_int32(int(enable))))
 

@@ -61,6 +61,7 @@ struct zant_plan {
     std::vector<std::string> step_names;
     int launches_per_run = 0;
     bool profiling = false;
+    cudaGraphExec_t graph_exec = nullptr;   // replay of all steps on arena buffers
     std::vector<cudaEvent_t> prof_events;   // pool, reused between reads
     size_t prof_used = 0;                   // events recorded since the last read
 
@@ -139,6 +140,7 @@ int32_t zant_b200_plan_destroy(zant_plan* plan) {
     if (!plan) return ZANT_OK;
     cudaSetDevice(plan->ctx->device);
     cudaStreamSynchronize(plan->ctx->stream);
+    if (plan->graph_exec) cudaGraphExecDestroy(plan->graph_exec);
     if (plan->arena) cudaFree(plan->arena);
     for (cudaEvent_t e : plan->prof_events) cudaEventDestroy(e);
     cudaGetLastError();
@@ -268,6 +270,15 @@ int32_t zant_b200_plan_run(zant_plan* plan, const void* input, void* output) {
     while (plan->t[out_root].alias >= 0) out_root = plan->t[out_root].alias;
     PlanTensor& tor = plan->t[out_root];
     const bool in_dev = is_device_ptr(input), out_dev = is_device_ptr(output);
+    if (plan->graph_exec && !plan->profiling) {
+        // replay: everything runs on the arena's own buffers
+        ZB_CUDA(cudaMemcpyAsync(ti.arena_ptr, input, ti.bytes, in_dev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, ctx->stream));
+        ZB_CUDA(cudaGraphLaunch(plan->graph_exec, ctx->stream));
+        ctx->launches += (uint64_t)plan->launches_per_run;
+        ZB_CUDA(cudaMemcpyAsync(output, tor.arena_ptr, to.bytes, out_dev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, ctx->stream));
+        if (out_dev || (is_pinned_host_ptr(output) && (in_dev || is_pinned_host_ptr(input)))) return ZANT_OK;
+        return drain_and_check_status(ctx);
+    }
     ti.bound = in_dev ? const_cast<void*>(input) : nullptr;
     tor.bound = out_dev ? output : nullptr;
     if (!in_dev) ZB_CUDA(cudaMemcpyAsync(ti.arena_ptr, input, ti.bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -296,6 +307,35 @@ int32_t zant_b200_plan_run(zant_plan* plan, const void* input, void* output) {
         return drain_and_check_status(ctx);
     }
     ti.bound = nullptr; tor.bound = nullptr;
+    return ZANT_OK;
+}
+
+int32_t zant_b200_plan_use_graph(zant_plan* plan, int32_t enable) {
+    if (!plan || !plan->finalized) return fail(ZANT_E_BAD_HANDLE, "plan is NULL or not finalized");
+    zant_ctx* ctx = plan->ctx;
+    ZB_CUDA(cudaSetDevice(ctx->device));
+    ZB_CUDA(cudaStreamSynchronize(ctx->stream));
+    if (plan->graph_exec) { cudaGraphExecDestroy(plan->graph_exec); plan->graph_exec = nullptr; }
+    if (!enable) return ZANT_OK;
+    // every step has run at least once (the dry run of finalize), so one-time function attributes are set
+    plan->t[plan->input].bound = nullptr;
+    {
+        int r = plan->output;
+        while (plan->t[r].alias >= 0) r = plan->t[r].alias;
+        plan->t[r].bound = nullptr;
+    }
+    const uint64_t before = ctx->launches;
+    ZB_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    int32_t st = ZANT_OK;
+    for (auto& step : plan->steps) { st = step(); if (st != ZANT_OK) break; }
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    ctx->launches = before;
+    if (st != ZANT_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+    if (e != cudaSuccess || !graph) { cudaGetLastError(); return fail(ZANT_E_CUDA, "stream capture failed: %s", cudaGetErrorString(e)); }
+    const cudaError_t ei = cudaGraphInstantiate(&plan->graph_exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ei != cudaSuccess) { plan->graph_exec = nullptr; cudaGetLastError(); return fail(ZANT_E_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(ei)); }
     return ZANT_OK;
 }
 
