@@ -249,6 +249,20 @@ int32_t zant_b200_leaky_relu_f32(zant_ctx* ctx, const float* x, float slope, flo
 /* ONNX Clip on f32 (ReLU6 = clip(0,6)).  Not present in the reference. */
 int32_t zant_b200_clip_f32(zant_ctx* ctx, const float* x, float lo, float hi, float* y, size_t n);
 
+/* tensMath.sigmoid_lean (lib_activation_function_math.zig:107-122): 1 / (1 + exp(-x)). */
+int32_t zant_b200_sigmoid_f32(zant_ctx* ctx, const float* x, float* y, size_t n);
+/* tensMath.softmax_lean = lean_softmax (lib_activation_function_math.zig:154-187): x is [rows][cols];
+ * per row: maximum, exp(x - max) summed in index order, division by the sum. */
+int32_t zant_b200_softmax_f32(zant_ctx* ctx, const float* x, float* y, size_t rows, size_t cols);
+/* tensMath.tanh_lean / ceil_lean (lib_elementWise_math.zig:452-456, 471-480; ceil passes NaN and
+ * infinities through). */
+int32_t zant_b200_tanh_f32(zant_ctx* ctx, const float* x, float* y, size_t n);
+int32_t zant_b200_ceil_f32(zant_ctx* ctx, const float* x, float* y, size_t n);
+/* tensMath.mul_lean / div_lean (lib_elementWise_math.zig:392-427): element-wise on tensors of equal
+ * size; different sizes return MismatchedShape as TensMath.mul / div do. */
+int32_t zant_b200_mul_f32(zant_ctx* ctx, const float* a, size_t n_a, const float* b, size_t n_b, float* y);
+int32_t zant_b200_div_f32(zant_ctx* ctx, const float* a, size_t n_a, const float* b, size_t n_b, float* y);
+
 /* tensMath.sum_tensors_lean = lean_sum_tensors (lib_elementWise_math.zig:70-210): equal
  * sizes add element-wise; otherwise NumPy right-aligned broadcasting up to rank 4. */
 int32_t zant_b200_sum_tensors_f32(zant_ctx* ctx,
@@ -423,6 +437,12 @@ typedef enum zant_op {
     ZANT_OP_REDUCE_MEAN = 10,
     ZANT_OP_RESHAPE = 11,
     ZANT_OP_CLIP = 12,
+    ZANT_OP_SIGMOID = 13,
+    ZANT_OP_SOFTMAX = 14,           /* 2-D input, rows normalised */
+    ZANT_OP_TANH = 15,
+    ZANT_OP_CEIL = 16,
+    ZANT_OP_MUL = 17,               /* equal sizes */
+    ZANT_OP_DIV = 18,
     ZANT_OP_QUANTIZE_LINEAR = 20,
     ZANT_OP_DEQUANTIZE_LINEAR = 21,
     ZANT_OP_QLINEAR_CONV = 22,

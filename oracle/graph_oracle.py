@@ -37,6 +37,12 @@ def run(zo, g, x):
                 y = zo.quantize_linear(f, a["y_scale"], a["y_zp"], dt)
         elif op == "Add":
             y = zo.sum_tensors(ins[0], ins[1])
+        elif op in ("Sigmoid", "Tanh", "Ceil"):
+            y = {"Sigmoid": zo.sigmoid, "Tanh": zo.tanh, "Ceil": zo.ceil}[op](ins[0])
+        elif op == "Softmax":
+            y = zo.softmax(ins[0])
+        elif op in ("Mul", "Div"):
+            y = (zo.mul if op == "Mul" else zo.div)(ins[0], ins[1]).reshape(oshape)
         elif op == "Concat":
             y = zo.concatenate(ins, a["axis"])
         elif op == "Resize":

@@ -513,9 +513,54 @@ int32_t zo_clip_f32(const float* x, float lo, float hi, float* y, usize n) {
     return ZANT_OK;
 }
 
+// sigmoid_lean, lib_activation_function_math.zig:107-122: 1 / (1 + exp(-x)) element by element.
+int32_t zo_sigmoid_f32(const float* x, float* y, usize n) {
+    for (usize i = 0; i < n; ++i) y[i] = 1.0f / (1.0f + std::exp(-x[i]));
+    return ZANT_OK;
+}
+
+// lean_softmax, lib_activation_function_math.zig:154-187: rows of a 2-D tensor; row maximum, exp(x - max)
+// stored and summed in index order, then every entry divided by the sum.
+int32_t zo_softmax_f32(const float* x, float* y, usize rows, usize cols) {
+    for (usize i = 0; i < rows; ++i) {
+        if (cols == 0) continue;
+        float max_val = x[i * cols];
+        for (usize j = 0; j < cols; ++j) { const float v = x[i * cols + j]; if (v > max_val) max_val = v; }
+        float sum = 0.0f;
+        for (usize j = 0; j < cols; ++j) { const float v = std::exp(x[i * cols + j] - max_val); y[i * cols + j] = v; sum += v; }
+        for (usize j = 0; j < cols; ++j) y[i * cols + j] /= sum;
+    }
+    return ZANT_OK;
+}
+
+// tanh_lean, lib_elementWise_math.zig:452-456.
+int32_t zo_tanh_f32(const float* x, float* y, usize n) {
+    for (usize i = 0; i < n; ++i) y[i] = std::tanh(x[i]);
+    return ZANT_OK;
+}
+
+// ceil_lean, lib_elementWise_math.zig:471-480: NaN and infinities pass through.
+int32_t zo_ceil_f32(const float* x, float* y, usize n) {
+    for (usize i = 0; i < n; ++i) y[i] = (std::isnan(x[i]) || std::isinf(x[i])) ? x[i] : std::ceil(x[i]);
+    return ZANT_OK;
+}
+
 // ---------------------------------------------------------------------------------------
 // Element-wise
 // ---------------------------------------------------------------------------------------
+
+// mul_lean / div_lean, lib_elementWise_math.zig:404-408 and 422-426; the callers mul / div reject
+// operands of different sizes with MismatchedShape (:393-395, :411-413).
+int32_t zo_mul_f32(const float* a, usize na, const float* b, usize nb, float* y) {
+    if (na != nb) return ZANT_E_MISMATCHED_SHAPE;
+    for (usize i = 0; i < na; ++i) y[i] = a[i] * b[i];
+    return ZANT_OK;
+}
+int32_t zo_div_f32(const float* a, usize na, const float* b, usize nb, float* y) {
+    if (na != nb) return ZANT_E_MISMATCHED_SHAPE;
+    for (usize i = 0; i < na; ++i) y[i] = a[i] / b[i];
+    return ZANT_OK;
+}
 
 // lean_sum_tensors, lib_elementWise_math.zig:70-210.
 // The broadcasting branch of the reference derives BOTH operands' strides from the OUTPUT

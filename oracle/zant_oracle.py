@@ -235,6 +235,53 @@ def leakyReLU(x, slope):
     return y
 
 
+def sigmoid(x):
+    """TensorMath.sigmoid / sigmoid_lean."""
+    x = _c(x, np.float32)
+    y = np.empty_like(x)
+    _check(lib().zo_sigmoid_f32(_p(x), _p(y), C.c_size_t(x.size)))
+    return y
+
+
+def softmax(x):
+    """TensorMath.softmax / lean_softmax on a 2-D tensor (rows are normalised)."""
+    x = _c(x, np.float32)
+    if x.ndim != 2:
+        raise ValueError("softmax takes a 2-D tensor")
+    y = np.empty_like(x)
+    _check(lib().zo_softmax_f32(_p(x), _p(y), C.c_size_t(x.shape[0]), C.c_size_t(x.shape[1])))
+    return y
+
+
+def tanh(x):
+    x = _c(x, np.float32)
+    y = np.empty_like(x)
+    _check(lib().zo_tanh_f32(_p(x), _p(y), C.c_size_t(x.size)))
+    return y
+
+
+def ceil(x):
+    x = _c(x, np.float32)
+    y = np.empty_like(x)
+    _check(lib().zo_ceil_f32(_p(x), _p(y), C.c_size_t(x.size)))
+    return y
+
+
+def mul(a, b):
+    """TensorMath.mul: element-wise product of tensors of equal size (result takes a's shape)."""
+    a, b = _c(a, np.float32), _c(b, np.float32)
+    y = np.empty_like(a)
+    _check(lib().zo_mul_f32(_p(a), C.c_size_t(a.size), _p(b), C.c_size_t(b.size), _p(y)))
+    return y
+
+
+def div(a, b):
+    a, b = _c(a, np.float32), _c(b, np.float32)
+    y = np.empty_like(a)
+    _check(lib().zo_div_f32(_p(a), C.c_size_t(a.size), _p(b), C.c_size_t(b.size), _p(y)))
+    return y
+
+
 def clip(x, lo, hi):
     x = _c(x, np.float32)
     y = np.empty_like(x)

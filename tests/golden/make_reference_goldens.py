@@ -120,8 +120,17 @@ add(op="leakyReLU", cite=A + ":265-287", x=[1, -2, -4, 5], slope=0.01, y=[1, -0.
 add(op="leakyReLU", cite=A + ":289-310", x=[-1, -2, -4, -5], slope=0.01, y=[-0.01, -0.02, -0.04, -0.05], atol=1e-5)
 add(op="leakyReLU", cite=A + ":312-333", x=[1, 2, 4, 5], slope=0.01, y=[1, 2, 4, 5], atol=0)
 
+add(op="sigmoid", cite=A + ":210-227", x=[0.0, 2.0, -2.0], y=[0.5, 0.880797, 0.119203], atol=1e-6,
+    note="the Zig test runs on f64; the f32 kernel meets the same 1e-6 bound")
+add(op="softmax_rows_sum_to_one", cite=A + ":126-151", x_shape=[2, 2], x=[1.0, 2.0, 4.0, 5.0], lo=0.9, hi=1.1)
+add(op="softmax_equal_entries", cite=A + ":153-175", x_shape=[2, 2], x=[0.0, 0.0, 0.0, 0.0])
+
 # ----------------------------------------------------------------------------- element-wise
 E = T + "test_lib_elementWise_math.zig"
+add(op="div", cite=E + ":234-262", a=[2, 4, 6, 8, 10, 12], b=[1, 2, 3, 4, 5, 6], y=[2, 2, 2, 2, 2, 2],
+    note="the Zig test divides u8 tensors; the quotients are exact, so the f32 operator gives the same values")
+add(op="tanh_matches_libm", cite=E + ":387-409", x=[0.0, 1.0, -1.0, 0.5, -0.5, 2.0], atol=1e-6)
+add(op="ceil", cite=E + ":411-434", x=[0.0, 1.2, -1.2, 0.5, -0.5, 2.0], y=[0.0, 2.0, -1.0, 1.0, 0.0, 2.0], atol=1e-6)
 add(op="sum_tensors", cite=E + ":10-32", a_shape=[2, 2], a=[1, 2, 4, 5], b_shape=[2, 2], b=[1, 2, 4, 5],
     y_shape=[2, 2], y_at={"0": 2, "1": 4})
 add(op="add_bias", cite=E + ":90-115", t_shape=[2, 3], t=[1, 2, 3, 4, 5, 6], bias=[1, 1, 1], y=[2, 3, 4, 5, 6, 7])

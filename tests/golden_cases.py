@@ -78,6 +78,26 @@ def run_case(impl, c, err_type):
     elif op == "leakyReLU":
         y = impl.leakyReLU(np.asarray(c["x"], np.float32), c["slope"])
         assert np.all(np.abs(y.astype(np.float64) - np.asarray(c["y"])) <= c["atol"])
+    elif op == "sigmoid":
+        y = impl.sigmoid(np.asarray(c["x"], np.float32))
+        assert np.all(np.abs(y.astype(np.float64) - np.asarray(c["y"])) < c["atol"])
+    elif op == "softmax_rows_sum_to_one":
+        y = impl.softmax(arr("x"))
+        sums = y.astype(np.float64).sum(axis=1)
+        assert np.all(sums > c["lo"]) and np.all(sums < c["hi"])
+    elif op == "softmax_equal_entries":
+        y = impl.softmax(arr("x"))
+        assert np.all(y[:, 0] == y[:, 1])
+    elif op == "div":
+        y = impl.div(np.asarray(c["a"], np.float32), np.asarray(c["b"], np.float32))
+        assert np.array_equal(y, np.asarray(c["y"], np.float32))
+    elif op == "tanh_matches_libm":
+        import math
+        y = impl.tanh(np.asarray(c["x"], np.float32))
+        assert np.all(np.abs(y.astype(np.float64) - np.array([math.tanh(v) for v in c["x"]])) <= c["atol"])
+    elif op == "ceil":
+        y = impl.ceil(np.asarray(c["x"], np.float32))
+        assert np.all(np.abs(y.astype(np.float64) - np.asarray(c["y"])) <= c["atol"])
     elif op == "sum_tensors":
         _expect(c, impl.sum_tensors(arr("a"), arr("b")))
     elif op == "add_bias":

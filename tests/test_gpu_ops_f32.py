@@ -216,3 +216,77 @@ def test_device_pointers_are_used_in_place(ctx, oracle):
     ctx.ReLU(xd, out=yd)
     ctx.synchronize()
     same(yd.cpu().numpy(), oracle.ReLU(x))
+
+
+# ------------------------------------------------------------------------------------------------
+# Sigmoid / Softmax / Tanh / Ceil / Mul / Div (the next operators the code generator can emit).
+# Mul, Div and Ceil are single rounded operations: bit-identical.  The others go through exp / tanh
+# of two different math libraries: the FP32 contract (1e-4 relative) with a much tighter bound in fact.
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [0, 1, 7, 1024, 100003])
+def test_mul_div_ceil_bit_identical(ctx, oracle, n):
+    rng = np.random.default_rng(n + 3)
+    a = (rng.standard_normal(n) * 50).astype(np.float32)
+    b = (rng.standard_normal(n) * 3 + 0.5).astype(np.float32)
+    for name in ("mul", "div"):
+        got, want = getattr(ctx, name)(a, b), getattr(oracle, name)(a, b)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), name
+    x = np.concatenate([a, np.array([np.inf, -np.inf, np.nan, -0.0, 2.0], np.float32)])
+    assert np.array_equal(ctx.ceil(x).view(np.uint32), oracle.ceil(x).view(np.uint32))
+
+
+def test_mul_div_reject_different_sizes(zb, ctx):
+    for fn in (ctx.mul, ctx.div):
+        with pytest.raises(zb.ZantError) as e:
+            fn(np.zeros((2, 3), np.float32), np.zeros((3, 3), np.float32))
+        assert e.value.name == "MismatchedShape"
+
+
+@pytest.mark.parametrize("n", [1, 33, 4096, 70001])
+def test_sigmoid_tanh(ctx, oracle, n):
+    x = (np.random.default_rng(n).standard_normal(n) * 6).astype(np.float32)
+    for name in ("sigmoid", "tanh"):
+        got, want = getattr(ctx, name)(x), getattr(oracle, name)(x)
+        tol = 1e-4 * np.maximum(np.abs(want), 1e-2 * np.abs(want).max())
+        assert np.all(np.abs(got - want) <= tol), name
+        assert np.abs(got - want).max() <= 4e-7, name          # a few units in the last place of values below 1
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (3, 10), (257, 1000), (4096, 7)])
+def test_softmax_rows(ctx, oracle, rows, cols):
+    x = (np.random.default_rng(rows * cols).standard_normal((rows, cols)) * 8).astype(np.float32)
+    got, want = ctx.softmax(x), oracle.softmax(x)
+    tol = 1e-4 * np.maximum(np.abs(want), 1e-2 * np.abs(want).max())
+    assert np.all(np.abs(got - want) <= tol)
+    assert np.all(np.abs(got.astype(np.float64).sum(axis=1) - 1.0) < 1e-5)
+
+
+def test_next_operators_in_a_plan(zb, ctx, oracle):
+    """MatMul -> Sigmoid -> Mul -> Div -> Tanh -> Ceil -> Softmax as plan nodes against the graph oracle."""
+    import graph_oracle
+    rng = np.random.default_rng(5)
+    g = zb.Graph("next_ops")
+    F32 = zb.F32
+    x = g.tensor("x", F32, (6, 16))
+    w = g.tensor("w", F32, (16, 12), rng.standard_normal((16, 12)).astype(np.float32))
+    s = g.tensor("s", F32, (6, 12), (rng.standard_normal((6, 12)) * 4).astype(np.float32))
+    d = g.tensor("d", F32, (6, 12), (rng.random((6, 12)) + 0.5).astype(np.float32))
+    ids = [g.tensor(n, F32, (6, 12)) for n in ("mm", "sig", "mul", "div", "tanh", "ceil", "soft")]
+    g.node("MatMul", [x, w], [ids[0]])
+    g.node("Sigmoid", [ids[0]], [ids[1]])
+    g.node("Mul", [ids[1], s], [ids[2]])
+    g.node("Div", [ids[2], d], [ids[3]])
+    g.node("Tanh", [ids[3]], [ids[4]])
+    g.node("Ceil", [ids[3]], [ids[5]])
+    g.node("Softmax", [ids[4]], [ids[6]])
+    g.input, g.output = x, ids[6]
+    xin = rng.standard_normal((6, 16)).astype(np.float32)
+    want = graph_oracle.run(oracle, g, xin)
+    plan = zb.Plan(ctx, g)
+    got = plan.run(xin)
+    assert np.abs(got - want[ids[6]]).max() <= 1e-5
+    assert np.abs(plan.read_tensor(ids[3]) - want[ids[3]]).max() <= 1e-4 * np.abs(want[ids[3]]).max()
+    # ceil of nearly equal inputs can differ by one where the input sits on an integer; compare where it does not
+    far = np.abs(want[ids[3]] - np.round(want[ids[3]])) > 1e-3
+    assert np.array_equal(plan.read_tensor(ids[5])[far], want[ids[5]][far])
+    plan.close()

@@ -29,7 +29,7 @@ COORD_MODE = {"half_pixel": 0, "align_corners": 1, "asymmetric": 2}
 SIZE_MAX = (1 << 64) - 1
 
 OP = dict(Conv=1, MatMul=2, Gemm=3, MaxPool=4, Relu=5, LeakyRelu=6, Add=7, Concat=8, Resize=9, ReduceMean=10,
-          Reshape=11, Clip=12, QuantizeLinear=20, DequantizeLinear=21, QLinearConv=22, QLinearMatMul=23,
+          Reshape=11, Clip=12, Sigmoid=13, Softmax=14, Tanh=15, Ceil=16, Mul=17, Div=18, QuantizeLinear=20, DequantizeLinear=21, QLinearConv=22, QLinearMatMul=23,
           QLinearAdd=24, QLinearGlobalAveragePool=25, LutQ8=26)
 
 
@@ -353,6 +353,42 @@ class Context:
         y = self._out(out, _shape(x), F32)
         check(lib().zant_b200_clip_f32(self._h, _ptr(x), C.c_float(lo), C.c_float(hi), _ptr(y), C.c_size_t(_numel(_shape(x)))))
         return y
+
+    def _unary(self, fn, x, out=None):
+        x = _host(x, np.float32)
+        y = self._out(out, _shape(x), F32)
+        check(fn(self._h, _ptr(x), _ptr(y), C.c_size_t(_numel(_shape(x)))))
+        return y
+
+    def sigmoid(self, x, out=None):
+        return self._unary(lib().zant_b200_sigmoid_f32, x, out)
+
+    def tanh(self, x, out=None):
+        return self._unary(lib().zant_b200_tanh_f32, x, out)
+
+    def ceil(self, x, out=None):
+        return self._unary(lib().zant_b200_ceil_f32, x, out)
+
+    def softmax(self, x, out=None):
+        x = _host(x, np.float32)
+        sh = _shape(x)
+        if len(sh) != 2:
+            raise ZantError(-1, "InvalidDimensions", "softmax takes a 2-D tensor")
+        y = self._out(out, sh, F32)
+        check(lib().zant_b200_softmax_f32(self._h, _ptr(x), _ptr(y), C.c_size_t(sh[0]), C.c_size_t(sh[1])))
+        return y
+
+    def _binary(self, fn, a, b, out=None):
+        a = _host(a, np.float32); b = _host(b, np.float32)
+        y = self._out(out, _shape(a), F32)
+        check(fn(self._h, _ptr(a), C.c_size_t(_numel(_shape(a))), _ptr(b), C.c_size_t(_numel(_shape(b))), _ptr(y)))
+        return y
+
+    def mul(self, a, b, out=None):
+        return self._binary(lib().zant_b200_mul_f32, a, b, out)
+
+    def div(self, a, b, out=None):
+        return self._binary(lib().zant_b200_div_f32, a, b, out)
 
     def sum_tensors(self, a, b, out=None):
         a = _host(a, np.float32); b = _host(b, np.float32)

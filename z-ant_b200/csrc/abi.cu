@@ -280,6 +280,34 @@ int32_t zant_b200_relu_f32(zant_ctx* ctx, const float* x, float* y, size_t n) { 
 int32_t zant_b200_leaky_relu_f32(zant_ctx* ctx, const float* x, float slope, float* y, size_t n) { return unary_entry(ctx, x, y, n, LeakyOp{slope}, "leaky_relu_f32"); }
 int32_t zant_b200_clip_f32(zant_ctx* ctx, const float* x, float lo, float hi, float* y, size_t n) { return unary_entry(ctx, x, y, n, ClipOp{lo, hi}, "clip_f32"); }
 
+int32_t zant_b200_sigmoid_f32(zant_ctx* ctx, const float* x, float* y, size_t n) { return unary_entry(ctx, x, y, n, SigmoidOp{}, "sigmoid_f32"); }
+int32_t zant_b200_tanh_f32(zant_ctx* ctx, const float* x, float* y, size_t n) { return unary_entry(ctx, x, y, n, TanhOp{}, "tanh_f32"); }
+int32_t zant_b200_ceil_f32(zant_ctx* ctx, const float* x, float* y, size_t n) { return unary_entry(ctx, x, y, n, CeilOp{}, "ceil_f32"); }
+
+int32_t zant_b200_softmax_f32(zant_ctx* ctx, const float* x, float* y, size_t rows, size_t cols) {
+    const size_t n = rows * cols;
+    if (n) { ZB_NEED(x, "x"); ZB_NEED(y, "y"); }
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ix = s.in(x, n * 4), iy = s.out(y, n * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_softmax_f32(ctx, s.ptr<float>(ix), s.ptr<float>(iy), rows, cols));
+    return s.finish();
+}
+
+static int32_t binary_entry(zant_ctx* ctx, const float* a, size_t n_a, const float* b, size_t n_b, float* y, bool divide) {
+    if (n_a != n_b) return fail(ZANT_E_MISMATCHED_SHAPE, "operands hold %zu and %zu elements", n_a, n_b);
+    if (n_a) { ZB_NEED(a, "a"); ZB_NEED(b, "b"); ZB_NEED(y, "y"); }
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ia = s.in(a, n_a * 4), ib = s.in(b, n_b * 4), iy = s.out(y, n_a * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_binary_same_f32(ctx, s.ptr<float>(ia), s.ptr<float>(ib), s.ptr<float>(iy), n_a, divide));
+    return s.finish();
+}
+int32_t zant_b200_mul_f32(zant_ctx* ctx, const float* a, size_t n_a, const float* b, size_t n_b, float* y) { return binary_entry(ctx, a, n_a, b, n_b, y, false); }
+int32_t zant_b200_div_f32(zant_ctx* ctx, const float* a, size_t n_a, const float* b, size_t n_b, float* y) { return binary_entry(ctx, a, n_a, b, n_b, y, true); }
+
 int32_t zant_b200_sum_tensors_f32(zant_ctx* ctx, const float* a, const size_t* a_shape, size_t a_rank,
                                   const float* b, const size_t* b_shape, size_t b_rank,
                                   float* y, const size_t* y_shape, size_t y_rank) {

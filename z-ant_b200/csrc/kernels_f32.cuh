@@ -236,6 +236,33 @@ __global__ void maxpool2x2s2_q8(const uint2* __restrict__ x, uint32_t* __restric
 struct ReluOp { __device__ float operator()(float v) const { return v > 0.0f ? v : 0.0f; } };
 struct LeakyOp { float slope; __device__ float operator()(float v) const { return v <= 0.0f ? __fmul_rn(slope, v) : v; } };
 struct ClipOp { float lo, hi; __device__ float operator()(float v) const { return fminf(fmaxf(v, lo), hi); } };
+// sigmoid_lean, tanh_lean, ceil_lean: exp / tanh are the CUDA library's accurate single-precision forms
+// (they agree with the reference's within a few units in the last place, inside the FP32 tolerance).
+struct SigmoidOp { __device__ float operator()(float v) const { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-v))); } };
+struct TanhOp { __device__ float operator()(float v) const { return tanhf(v); } };
+struct CeilOp { __device__ float operator()(float v) const { return (isnan(v) || isinf(v)) ? v : ceilf(v); } };
+
+// mul_lean / div_lean: equal sizes, one rounded operation per element.
+template <bool DIV>
+__global__ void binary_same_f32(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ y, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = DIV ? __fdiv_rn(a[i], b[i]) : __fmul_rn(a[i], b[i]);
+}
+
+// lean_softmax: one thread per row walks it three times in index order (maximum; exp and running sum;
+// division), which reproduces the reference's summation order.
+__global__ void softmax_rows_f32(const float* __restrict__ x, float* __restrict__ y, size_t rows, size_t cols) {
+    for (size_t r = blockIdx.x * (size_t)blockDim.x + threadIdx.x; r < rows; r += (size_t)gridDim.x * blockDim.x) {
+        if (cols == 0) continue;
+        const float* xr = x + r * cols;
+        float* yr = y + r * cols;
+        float m = xr[0];
+        for (size_t j = 0; j < cols; ++j) m = xr[j] > m ? xr[j] : m;
+        float sum = 0.0f;
+        for (size_t j = 0; j < cols; ++j) { const float v = expf(__fsub_rn(xr[j], m)); yr[j] = v; sum = __fadd_rn(sum, v); }
+        for (size_t j = 0; j < cols; ++j) yr[j] = __fdiv_rn(yr[j], sum);
+    }
+}
 
 template <typename F>
 __global__ void unary_f32(const float* __restrict__ x, float* __restrict__ y, size_t n, bool vec, F f) {

@@ -91,6 +91,20 @@ inline int32_t run_unary_f32(zant_ctx* ctx, const float* x, float* y, size_t n, 
     return check_launch(ctx, name);
 }
 
+inline int32_t run_binary_same_f32(zant_ctx* ctx, const float* a, const float* b, float* y, size_t n, bool divide) {
+    if (n == 0) return ZANT_OK;
+    const int grid = grid_for(n, 256, ctx->sm_count);
+    if (divide) binary_same_f32<true><<<grid, 256, 0, ctx->stream>>>(a, b, y, n);
+    else binary_same_f32<false><<<grid, 256, 0, ctx->stream>>>(a, b, y, n);
+    return check_launch(ctx, divide ? "div_f32" : "mul_f32");
+}
+
+inline int32_t run_softmax_f32(zant_ctx* ctx, const float* x, float* y, size_t rows, size_t cols) {
+    if (rows == 0 || cols == 0) return ZANT_OK;
+    softmax_rows_f32<<<grid_for(rows, 128, ctx->sm_count), 128, 0, ctx->stream>>>(x, y, rows, cols);
+    return check_launch(ctx, "softmax_rows_f32");
+}
+
 inline int32_t run_add_f32(zant_ctx* ctx, const BcastGeom& g, const float* a, const float* b, float* y) {
     if (g.total == 0) return ZANT_OK;
     if (g.same_size) {

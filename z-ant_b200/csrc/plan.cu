@@ -453,6 +453,41 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
             else return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "MaxPool on int32");
             return ZANT_OK;
         }
+        case ZANT_OP_SIGMOID:
+        case ZANT_OP_TANH:
+        case ZANT_OP_CEIL: {
+            ZB_TRY(need_inputs(n, 1, 1, "unary"));
+            const int x = n.in[0], y = n.out[0];
+            ZB_TRY(want_dtype(pl, x, ZANT_F32, "unary")); ZB_TRY(want_dtype(pl, y, ZANT_F32, "unary"));
+            const size_t cnt = numel(T(x).shape.data(), T(x).shape.size());
+            if (cnt != numel(T(y).shape.data(), T(y).shape.size())) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "unary sizes differ");
+            if (n.op == ZANT_OP_SIGMOID) push("Sigmoid", [=]() { return run_unary_f32(ctx, pl->p<float>(x), pl->p<float>(y), cnt, SigmoidOp{}, "sigmoid_f32"); });
+            else if (n.op == ZANT_OP_TANH) push("Tanh", [=]() { return run_unary_f32(ctx, pl->p<float>(x), pl->p<float>(y), cnt, TanhOp{}, "tanh_f32"); });
+            else push("Ceil", [=]() { return run_unary_f32(ctx, pl->p<float>(x), pl->p<float>(y), cnt, CeilOp{}, "ceil_f32"); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_SOFTMAX: {
+            ZB_TRY(need_inputs(n, 1, 1, "Softmax"));
+            const int x = n.in[0], y = n.out[0];
+            ZB_TRY(want_dtype(pl, x, ZANT_F32, "Softmax")); ZB_TRY(want_dtype(pl, y, ZANT_F32, "Softmax"));
+            if (T(x).shape.size() != 2) return fail(ZANT_E_INVALID_DIMENSIONS, "Softmax takes a 2-D tensor");
+            if (T(y).shape != T(x).shape) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "Softmax shapes differ");
+            const size_t rows = T(x).shape[0], cols = T(x).shape[1];
+            push("Softmax", [=]() { return run_softmax_f32(ctx, pl->p<float>(x), pl->p<float>(y), rows, cols); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_MUL:
+        case ZANT_OP_DIV: {
+            ZB_TRY(need_inputs(n, 2, 2, "Mul/Div"));
+            const int x = n.in[0], w = n.in[1], y = n.out[0];
+            ZB_TRY(want_dtype(pl, x, ZANT_F32, "Mul/Div")); ZB_TRY(want_dtype(pl, w, ZANT_F32, "Mul/Div")); ZB_TRY(want_dtype(pl, y, ZANT_F32, "Mul/Div"));
+            const size_t cnt = numel(T(x).shape.data(), T(x).shape.size());
+            if (cnt != numel(T(w).shape.data(), T(w).shape.size())) return fail(ZANT_E_MISMATCHED_SHAPE, "Mul/Div operands differ in size");
+            if (cnt != numel(T(y).shape.data(), T(y).shape.size())) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "Mul/Div output size");
+            const bool divide = n.op == ZANT_OP_DIV;
+            push(divide ? "Div" : "Mul", [=]() { return run_binary_same_f32(ctx, pl->p<float>(x), pl->p<float>(w), pl->p<float>(y), cnt, divide); });
+            return ZANT_OK;
+        }
         case ZANT_OP_RELU:
         case ZANT_OP_LEAKY_RELU:
         case ZANT_OP_CLIP: {

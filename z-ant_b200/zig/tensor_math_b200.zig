@@ -17,6 +17,12 @@ extern fn zant_b200_gemm_f32(ctx: ?*Ctx, a: [*]const f32, as: [*]const usize, ar
 extern fn zant_b200_maxpool_f32(ctx: ?*Ctx, x: [*]const f32, xs: [*]const usize, xr: usize, y: [*]f32, ys: [*]const usize, yr: usize, k: [*]const usize, nk: usize, s: [*]const usize, ns: usize, d: [*]const usize, nd: usize, p: [*]const usize, np: usize, auto_pad: i32) i32;
 extern fn zant_b200_relu_f32(ctx: ?*Ctx, x: [*]const f32, y: [*]f32, n: usize) i32;
 extern fn zant_b200_leaky_relu_f32(ctx: ?*Ctx, x: [*]const f32, slope: f32, y: [*]f32, n: usize) i32;
+extern fn zant_b200_sigmoid_f32(ctx: ?*Ctx, x: [*]const f32, y: [*]f32, n: usize) i32;
+extern fn zant_b200_softmax_f32(ctx: ?*Ctx, x: [*]const f32, y: [*]f32, rows: usize, cols: usize) i32;
+extern fn zant_b200_tanh_f32(ctx: ?*Ctx, x: [*]const f32, y: [*]f32, n: usize) i32;
+extern fn zant_b200_ceil_f32(ctx: ?*Ctx, x: [*]const f32, y: [*]f32, n: usize) i32;
+extern fn zant_b200_mul_f32(ctx: ?*Ctx, a: [*]const f32, na: usize, b: [*]const f32, nb: usize, y: [*]f32) i32;
+extern fn zant_b200_div_f32(ctx: ?*Ctx, a: [*]const f32, na: usize, b: [*]const f32, nb: usize, y: [*]f32) i32;
 extern fn zant_b200_sum_tensors_f32(ctx: ?*Ctx, a: [*]const f32, as: [*]const usize, ar: usize, b: [*]const f32, bs: [*]const usize, br: usize, y: [*]f32, ys: [*]const usize, yr: usize) i32;
 
 pub const AutoPadType = enum { NOTSET, SAME_UPPER, SAME_LOWER, VALID };
@@ -69,6 +75,30 @@ pub fn ReLU_lean(comptime T: type, input: *Tensor(T), output: *Tensor(T)) !void 
 
 pub fn leakyReLU_lean(comptime T: type, input: *Tensor(T), slope: T, output: *Tensor(T)) !void {
     try check(zant_b200_leaky_relu_f32(context(), input.data.ptr, slope, output.data.ptr, input.size));
+}
+
+pub fn sigmoid_lean(comptime T: type, input: *Tensor(T), output: *Tensor(T)) !void {
+    try check(zant_b200_sigmoid_f32(context(), input.data.ptr, output.data.ptr, input.size));
+}
+
+pub fn softmax_lean(comptime T: type, input: *Tensor(T), output: *Tensor(T)) !void {
+    try check(zant_b200_softmax_f32(context(), input.data.ptr, output.data.ptr, input.shape[0], input.shape[1]));
+}
+
+pub fn tanh_lean(comptime T: type, input: *Tensor(T), output: *Tensor(T)) !void {
+    try check(zant_b200_tanh_f32(context(), input.data.ptr, output.data.ptr, input.size));
+}
+
+pub fn ceil_lean(comptime T: type, input: *Tensor(T), output: *Tensor(T)) !void {
+    try check(zant_b200_ceil_f32(context(), input.data.ptr, output.data.ptr, input.size));
+}
+
+pub fn mul_lean(comptime T: type, lhs: *Tensor(T), rhs: *Tensor(T), result: *Tensor(T)) !void {
+    try check(zant_b200_mul_f32(context(), lhs.data.ptr, lhs.size, rhs.data.ptr, rhs.size, result.data.ptr));
+}
+
+pub fn div_lean(comptime T: type, lhs: *Tensor(T), rhs: *Tensor(T), result: *Tensor(T)) !void {
+    try check(zant_b200_div_f32(context(), lhs.data.ptr, lhs.size, rhs.data.ptr, rhs.size, result.data.ptr));
 }
 
 pub fn sum_tensors_lean(comptime inT: type, comptime outT: type, t1: *Tensor(inT), t2: *Tensor(inT), out: *Tensor(outT)) !void {
