@@ -59,13 +59,19 @@ typedef enum zant_status {
     ZANT_E_INPUT_ARRAY_WRONG_SIZE = -35,
     ZANT_E_EMPTY_TENSOR = -36,
     ZANT_E_ZERO_SIZE_TENSOR = -37,
+    ZANT_E_INVALID_SLICE_INDICES = -43,
+    ZANT_E_INVALID_SLICE_STEP = -46,
     ZANT_E_AXIS_OUT_OF_BOUNDS = -49,
     ZANT_E_MISMATCHED_RANK = -50,
     ZANT_E_MISMATCHED_SHAPE = -51,
     ZANT_E_INDEX_OUT_OF_BOUNDS = -52,
+    ZANT_E_INVALID_AXIS = -53,
+    ZANT_E_DUPLICATE_AXIS = -54,
     ZANT_E_INVALID_INPUT = -55,
     ZANT_E_UNSUPPORTED_MODE = -56,
     ZANT_E_UNSUPPORTED_DIMENSION = -57,
+    ZANT_E_INVALID_RANK = -59,
+    ZANT_E_INVALID_PERMUTATION = -60,
     /* backend */
     ZANT_E_CUDA = -100,             /* a CUDA runtime call failed; see zant_b200_last_error() */
     ZANT_E_CUDA_UNAVAILABLE = -101, /* no usable sm_100 device / driver */
@@ -248,6 +254,38 @@ int32_t zant_b200_leaky_relu_f32(zant_ctx* ctx, const float* x, float slope, flo
 
 /* ONNX Clip on f32 (ReLU6 = clip(0,6)).  Not present in the reference. */
 int32_t zant_b200_clip_f32(zant_ctx* ctx, const float* x, float lo, float hi, float* y, size_t n);
+
+/* tensMath.transpose_onnx_lean (lib_shape_math.zig:1628-1753): y[out coords] = x[coords permuted];
+ * `perm` NULL reverses the dimensions.  A perm of the wrong length, with an entry >= rank or with a
+ * repeated entry is InvalidPermutation; an output of another rank InvalidRank.  Unlike the reference,
+ * which overwrites the output's shape, the caller's y_shape must already be the permuted shape
+ * (OutputTensorDifferentSize otherwise).  Any dtype (elements are moved, not interpreted). */
+int32_t zant_b200_transpose_onnx(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                                 const size_t* perm, size_t n_perm, void* y, const size_t* y_shape, size_t y_rank);
+
+/* tensMath.get_slice_output_shape / lean_slice_onnx (lib_shape_math.zig:1378-1495): ONNX Slice with
+ * optional axes and steps (NULL = all axes in order / step 1).  starts/ends are clamped as the
+ * reference does; starts.len != ends.len (here: one count `n` for all arrays) or an axis out of range is
+ * InvalidSliceIndices, a zero step InvalidSliceStep.  `out_shape` receives x_rank entries. */
+int32_t zant_b200_slice_output_shape(const size_t* x_shape, size_t x_rank, const int64_t* starts, const int64_t* ends, size_t n,
+                                     const int64_t* axes, const int64_t* steps, size_t* out_shape);
+/* The dimensions lean_slice_onnx itself writes into its output (lib_shape_math.zig:1445-1462).  They equal
+ * get_slice_output_shape for positive steps; for a negative step the reference's two functions count
+ * differently ((start - end) / |step| + 1 in the shape function, ceil((start - end - 1) / |step|) in the
+ * operator), and zant_b200_slice_onnx follows the operator: its y_shape must be these dimensions. */
+int32_t zant_b200_slice_lean_dims(const size_t* x_shape, size_t x_rank, const int64_t* starts, const int64_t* ends, size_t n,
+                                  const int64_t* axes, const int64_t* steps, size_t* out_shape);
+int32_t zant_b200_slice_onnx(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                             const int64_t* starts, const int64_t* ends, size_t n, const int64_t* axes, const int64_t* steps,
+                             void* y, const size_t* y_shape, size_t y_rank);
+
+/* tensMath.gather / lean_gather (lib_shape_math.zig:1217-1330): output shape = data.shape[:axis] ++
+ * indices.shape ++ data.shape[axis+1:].  `indices` is a HOST array (the reference's Tensor(usize)).  Rank 0
+ * data is InvalidRank, an axis outside [-rank, rank) InvalidAxis, an index >= the axis length
+ * IndexOutOfBounds. */
+int32_t zant_b200_gather(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                         const size_t* indices, const size_t* idx_shape, size_t idx_rank, int64_t axis,
+                         void* y, const size_t* y_shape, size_t y_rank);
 
 /* tensMath.sigmoid_lean (lib_activation_function_math.zig:107-122): 1 / (1 + exp(-x)). */
 int32_t zant_b200_sigmoid_f32(zant_ctx* ctx, const float* x, float* y, size_t n);
@@ -443,6 +481,9 @@ typedef enum zant_op {
     ZANT_OP_CEIL = 16,
     ZANT_OP_MUL = 17,               /* equal sizes */
     ZANT_OP_DIV = 18,
+    ZANT_OP_TRANSPOSE = 19,         /* attrs.perm */
+    ZANT_OP_SLICE = 27,             /* attrs.slice_* */
+    ZANT_OP_GATHER = 28,            /* inputs: data, indices (I32 initializer); attrs.axis */
     ZANT_OP_QUANTIZE_LINEAR = 20,
     ZANT_OP_DEQUANTIZE_LINEAR = 21,
     ZANT_OP_QLINEAR_CONV = 22,
@@ -473,6 +514,11 @@ typedef struct zant_node_attrs {
     float b_scale;  int32_t b_zp;   /* second operand of QLinearAdd */
     float y_scale;  int32_t y_zp;
     int32_t activation;             /* zant_qact */
+    /* Transpose */
+    int64_t perm[8];     size_t n_perm;          /* n_perm = 0: reverse the dimensions */
+    /* Slice: n_slice entries; has_* = 0 means the optional ONNX input is absent */
+    int64_t slice_starts[8], slice_ends[8], slice_axes[8], slice_steps[8];
+    size_t n_slice; int32_t slice_has_axes, slice_has_steps;
 } zant_node_attrs;
 
 int32_t zant_b200_plan_create(zant_ctx* ctx, zant_plan** out);

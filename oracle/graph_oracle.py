@@ -41,6 +41,12 @@ def run(zo, g, x):
             y = {"Sigmoid": zo.sigmoid, "Tanh": zo.tanh, "Ceil": zo.ceil}[op](ins[0])
         elif op == "Softmax":
             y = zo.softmax(ins[0])
+        elif op == "Transpose":
+            y = zo.transpose_onnx(ins[0], a.get("perm"))
+        elif op == "Slice":
+            y = zo.slice_onnx(ins[0], a["starts"], a["ends"], a.get("slice_axes"), a.get("steps"))
+        elif op == "Gather":
+            y = zo.gather(ins[0], ins[1], a["axis"])
         elif op in ("Mul", "Div"):
             y = (zo.mul if op == "Mul" else zo.div)(ins[0], ins[1]).reshape(oshape)
         elif op == "Concat":

@@ -546,6 +546,142 @@ int32_t zo_ceil_f32(const float* x, float* y, usize n) {
 }
 
 // ---------------------------------------------------------------------------------------
+// Transpose / Slice / Gather (lib_shape_math.zig): elements are moved, never interpreted, so the
+// functions take the element size in bytes.
+// ---------------------------------------------------------------------------------------
+
+// transpose_onnx_lean, lib_shape_math.zig:1628-1753: the output index is decomposed by the output strides and
+// coordinate d walks input dimension perm[d]; a missing perm reverses the dimensions.
+int32_t zo_transpose_onnx(usize esz, const void* x, const usize* xs, usize xr, const usize* perm, usize np, void* y, const usize* ys, usize yr) {
+    if (yr != xr) return ZANT_E_INVALID_RANK;
+    std::vector<usize> rp(xr);
+    if (perm) {
+        if (np != xr) return ZANT_E_INVALID_PERMUTATION;
+        std::vector<bool> used(xr, false);
+        for (usize i = 0; i < xr; ++i) {
+            if (perm[i] >= xr || used[perm[i]]) return ZANT_E_INVALID_PERMUTATION;
+            used[perm[i]] = true;
+            rp[i] = perm[i];
+        }
+    } else {
+        for (usize i = 0; i < xr; ++i) rp[i] = xr - 1 - i;
+    }
+    std::vector<usize> istr(xr), oshape(xr), ostr(xr);
+    usize st = 1;
+    for (usize i = xr; i-- > 0;) { istr[i] = st; st *= xs[i]; }
+    for (usize j = 0; j < xr; ++j) oshape[j] = xs[rp[j]];
+    st = 1;
+    for (usize i = xr; i-- > 0;) { ostr[i] = st; st *= oshape[i]; }
+    for (usize j = 0; j < xr; ++j) if (ys[j] != oshape[j]) return ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE;
+    const usize total = st;
+    for (usize flat = 0; flat < total; ++flat) {
+        usize tmp = flat, in_idx = 0;
+        for (usize d = 0; d < xr; ++d) { const usize c = tmp / ostr[d]; tmp %= ostr[d]; in_idx += c * istr[rp[d]]; }
+        std::memcpy((char*)y + flat * esz, (const char*)x + in_idx * esz, esz);
+    }
+    return ZANT_OK;
+}
+
+// The start / end / step normalisation shared by get_slice_output_shape and lean_slice_onnx
+// (lib_shape_math.zig:1378-1443).
+// `shape_rule`: count the elements of a negative step as get_slice_output_shape does (:1546-1550:
+// (start - end) / |step| + 1) instead of as lean_slice_onnx does (:1452-1456).
+static int32_t slice_normalise(const usize* xs, usize xr, const int64_t* starts, const int64_t* ends, usize n, const int64_t* axes,
+                               const int64_t* steps, std::vector<int64_t>& a_start, std::vector<int64_t>& a_step, std::vector<usize>& odims,
+                               bool shape_rule) {
+    a_start.assign(xr, 0); a_step.assign(xr, 1); odims.assign(xr, 0);
+    std::vector<int64_t> a_end(xr);
+    for (usize i = 0; i < xr; ++i) a_end[i] = (int64_t)xs[i];
+    for (usize i = 0; i < n; ++i) {
+        const int64_t axis = axes ? axes[i] : (int64_t)i;
+        const int64_t ax = axis < 0 ? axis + (int64_t)xr : axis;
+        if (ax < 0 || (usize)ax >= xr) return ZANT_E_INVALID_SLICE_INDICES;
+        const int64_t dim = (int64_t)xs[ax];
+        int64_t s0 = starts[i] < 0 ? starts[i] + dim : starts[i];
+        s0 = std::max<int64_t>(0, std::min(s0, dim));
+        a_start[ax] = s0;
+        int64_t e0 = ends[i] < 0 ? ends[i] + dim : ends[i];
+        if (steps && steps[i] < 0) e0 = ends[i] < 0 ? -1 : e0;
+        else e0 = std::max<int64_t>(0, std::min(e0, dim));
+        a_end[ax] = e0;
+        if (steps) {
+            if (steps[i] == 0) return ZANT_E_INVALID_SLICE_STEP;
+            a_step[ax] = steps[i];
+        }
+    }
+    for (usize i = 0; i < xr; ++i) {
+        const int64_t st = a_start[i], en = a_end[i], sp = a_step[i];
+        usize d = 0;
+        if (sp > 0) { if (en > st) d = (usize)(((en - st) + sp - 1) / sp); }
+        else if (st > en) {
+            const int64_t as = -sp;
+            if (shape_rule) d = (usize)((st - en) / as + 1);
+            else { const int64_t range = st - (en + 1); d = (usize)((range + as - 1) / as); }
+        }
+        odims[i] = d;
+    }
+    return ZANT_OK;
+}
+
+// get_slice_output_shape (shape_rule != 0), or the dimensions lean_slice_onnx writes into its output.
+int32_t zo_slice_output_shape(const usize* xs, usize xr, const int64_t* starts, const int64_t* ends, usize n, const int64_t* axes,
+                              const int64_t* steps, usize* out, int32_t shape_rule) {
+    std::vector<int64_t> a, b; std::vector<usize> od;
+    const int32_t st = slice_normalise(xs, xr, starts, ends, n, axes, steps, a, b, od, shape_rule != 0);
+    if (st != ZANT_OK) return st;
+    for (usize i = 0; i < xr; ++i) out[i] = od[i];
+    return ZANT_OK;
+}
+
+// lean_slice_onnx, lib_shape_math.zig:1445-1495: output coordinates (last dimension fastest) map to
+// start + coord * step in every dimension.
+int32_t zo_slice_onnx(usize esz, const void* x, const usize* xs, usize xr, const int64_t* starts, const int64_t* ends, usize n,
+                      const int64_t* axes, const int64_t* steps, void* y, const usize* ys, usize yr) {
+    std::vector<int64_t> a_start, a_step; std::vector<usize> od;
+    const int32_t st = slice_normalise(xs, xr, starts, ends, n, axes, steps, a_start, a_step, od, false);
+    if (st != ZANT_OK) return st;
+    if (yr != xr) return ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE;
+    usize total = 1;
+    for (usize i = 0; i < xr; ++i) { if (ys[i] != od[i]) return ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE; total *= od[i]; }
+    std::vector<usize> istr(xr);
+    usize s = 1;
+    for (usize i = xr; i-- > 0;) { istr[i] = s; s *= xs[i]; }
+    for (usize o = 0; o < total; ++o) {
+        usize tmp = o, in_idx = 0;
+        for (usize i = 0; i < xr; ++i) {
+            const usize d = xr - 1 - i;
+            const usize c = tmp % od[d]; tmp /= od[d];
+            in_idx += (usize)(a_start[d] + (int64_t)c * a_step[d]) * istr[d];
+        }
+        std::memcpy((char*)y + o * esz, (const char*)x + in_idx * esz, esz);
+    }
+    return ZANT_OK;
+}
+
+// gather + lean_gather, lib_shape_math.zig:1217-1330.
+int32_t zo_gather(usize esz, const void* x, const usize* xs, usize xr, const usize* indices, const usize* is, usize ir, int64_t axis_in,
+                  void* y, const usize* ys, usize yr) {
+    if (xr == 0) return ZANT_E_INVALID_RANK;
+    const int64_t nd = (int64_t)xr;
+    if (axis_in >= nd || axis_in < -nd) return ZANT_E_INVALID_AXIS;
+    const usize axis = (usize)(axis_in < 0 ? nd + axis_in : axis_in);
+    usize n_idx = 1;
+    for (usize i = 0; i < ir; ++i) n_idx *= is[i];
+    for (usize i = 0; i < n_idx; ++i) if (indices[i] >= xs[axis]) return ZANT_E_INDEX_OUT_OF_BOUNDS;
+    if (yr != xr + ir - 1) return ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE;
+    for (usize i = 0; i < axis; ++i) if (ys[i] != xs[i]) return ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE;
+    for (usize i = 0; i < ir; ++i) if (ys[axis + i] != is[i]) return ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE;
+    for (usize i = axis + 1; i < xr; ++i) if (ys[axis + ir + (i - axis - 1)] != xs[i]) return ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE;
+    usize outer = 1, inner = 1;
+    for (usize i = 0; i < axis; ++i) outer *= xs[i];
+    for (usize i = axis + 1; i < xr; ++i) inner *= xs[i];
+    for (usize o = 0; o < outer; ++o)
+        for (usize k = 0; k < n_idx; ++k)
+            std::memcpy((char*)y + ((o * n_idx + k) * inner) * esz, (const char*)x + ((o * xs[axis] + indices[k]) * inner) * esz, inner * esz);
+    return ZANT_OK;
+}
+
+// ---------------------------------------------------------------------------------------
 // Element-wise
 // ---------------------------------------------------------------------------------------
 

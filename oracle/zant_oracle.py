@@ -28,9 +28,10 @@ STATUS_NAMES = {
     -7: "TooSmallOutputType", -8: "InputTensorDimensionMismatch", -9: "WrongStride",
     -10: "IncompatibleBroadcastShapes", -11: "EmptyTensorList", -12: "DivisionError",
     -13: "InvalidPadding", -14: "InvalidAxes", -33: "TensorNotInitialized", -34: "InputArrayWrongType",
-    -35: "InputArrayWrongSize", -36: "EmptyTensor", -37: "ZeroSizeTensor", -49: "AxisOutOfBounds",
-    -50: "MismatchedRank", -51: "MismatchedShape", -52: "IndexOutOfBounds", -55: "InvalidInput",
-    -56: "UnsupportedMode", -57: "UnsupportedDimension", -100: "Cuda", -101: "CudaUnavailable",
+    -35: "InputArrayWrongSize", -36: "EmptyTensor", -37: "ZeroSizeTensor", -43: "InvalidSliceIndices",
+    -46: "InvalidSliceStep", -49: "AxisOutOfBounds",
+    -50: "MismatchedRank", -51: "MismatchedShape", -52: "IndexOutOfBounds", -53: "InvalidAxis", -54: "DuplicateAxis",
+    -55: "InvalidInput", -56: "UnsupportedMode", -57: "UnsupportedDimension", -59: "InvalidRank", -60: "InvalidPermutation", -100: "Cuda", -101: "CudaUnavailable",
     -102: "NullPointer", -103: "Unsupported", -104: "ArenaExhausted", -105: "BadHandle",
     -106: "DeviceTimeout", -107: "TooLarge",
 }
@@ -342,6 +343,63 @@ def concatenate(tensors, axis):
     ys, yr = _sz(y.shape)
     _check(lib().zo_concatenate(C.c_size_t(ts[0].itemsize), data, ptrs, ranks, C.c_size_t(len(ts)), C.c_int64(axis),
                                 _p(y), ys, C.c_size_t(yr)))
+    return y
+
+
+def _i64(v):
+    if v is None:
+        return None
+    return (C.c_int64 * len(v))(*[int(a) for a in v])
+
+
+def transpose_onnx(x, perm=None):
+    """TensMath.transpose_onnx: `perm` None reverses the dimensions."""
+    x = np.ascontiguousarray(x)
+    if perm is not None and (len(perm) != x.ndim or sorted(int(p) for p in perm) != list(range(x.ndim))):
+        raise OracleError(-60)
+    oshape = [x.shape[i] for i in (perm if perm is not None else range(x.ndim - 1, -1, -1))]
+    y = np.zeros(oshape, x.dtype)
+    xs, r = _sz(x.shape); ys, yr = _sz(y.shape)
+    pm, npm = _sz(perm)
+    _check(lib().zo_transpose_onnx(C.c_size_t(x.itemsize), _p(x), xs, C.c_size_t(r), pm, C.c_size_t(npm), _p(y), ys, C.c_size_t(yr)))
+    return y
+
+
+def get_slice_output_shape(x_shape, starts, ends, axes=None, steps=None, lean=False):
+    """TensMath.get_slice_output_shape; `lean` = the dimensions lean_slice_onnx gives its output (they
+    differ from the shape function's for negative steps)."""
+    if len(starts) != len(ends) or (axes is not None and len(axes) != len(starts)) or (steps is not None and len(steps) != len(starts)):
+        raise OracleError(-43)
+    xs, r = _sz(x_shape)
+    out = (C.c_size_t * max(r, 1))()
+    _check(lib().zo_slice_output_shape(xs, C.c_size_t(r), _i64(starts), _i64(ends), C.c_size_t(len(starts)), _i64(axes), _i64(steps), out,
+                                       C.c_int32(0 if lean else 1)))
+    return [int(out[i]) for i in range(r)]
+
+
+def slice_onnx(x, starts, ends, axes=None, steps=None):
+    x = np.ascontiguousarray(x)
+    oshape = get_slice_output_shape(x.shape, starts, ends, axes, steps, lean=True)
+    y = np.zeros(oshape, x.dtype)
+    xs, r = _sz(x.shape); ys, yr = _sz(y.shape)
+    _check(lib().zo_slice_onnx(C.c_size_t(x.itemsize), _p(x), xs, C.c_size_t(r), _i64(starts), _i64(ends), C.c_size_t(len(starts)),
+                               _i64(axes), _i64(steps), _p(y), ys, C.c_size_t(yr)))
+    return y
+
+
+def gather(x, indices, axis):
+    x = np.ascontiguousarray(x)
+    idx = np.ascontiguousarray(np.asarray(indices), dtype=np.uint64)
+    if x.ndim == 0:
+        raise OracleError(-59)
+    if axis >= x.ndim or axis < -x.ndim:
+        raise OracleError(-53)
+    ax = axis + x.ndim if axis < 0 else axis
+    oshape = list(x.shape[:ax]) + list(idx.shape) + list(x.shape[ax + 1:])
+    y = np.zeros(oshape, x.dtype)
+    xs, r = _sz(x.shape); ys, yr = _sz(y.shape); is_, ir = _sz(idx.shape)
+    _check(lib().zo_gather(C.c_size_t(x.itemsize), _p(x), xs, C.c_size_t(r), _p(idx), is_, C.c_size_t(ir), C.c_int64(axis),
+                           _p(y), ys, C.c_size_t(yr)))
     return y
 
 

@@ -209,6 +209,34 @@ add(op="reshape", cite=S + ":1838-1866", dtype="u8", x_shape=[2, 3], x=[1, 2, 3,
     y_shape=[2, 3], y=[1, 2, 3, 4, 5, 6])
 add(op="reshape_error", cite=S + ":1868-1885", x_shape=[2, 3], new_shape=[NEG1, NEG1], error="InvalidInput")
 
+# ----------------------------------------------------------------------------- transpose / slice / gather
+add(op="transpose_onnx", cite=S + ":1172-1206", dtype="f32", x_shape=[2, 3], x=[1, 2, 3, 4, 5, 6], perm=None,
+    y_shape=[3, 2], y=[1, 4, 2, 5, 3, 6])
+add(op="transpose_onnx", cite=S + ":1208-1255", dtype="f32", x_shape=[2, 2, 3], x=list(range(1, 13)), perm=[2, 1, 0],
+    y_shape=[3, 2, 2], y=[1, 7, 4, 10, 2, 8, 5, 11, 3, 9, 6, 12])
+add(op="transpose_onnx_error", cite=S + ":1257-1285", x_shape=[2, 3], perm=[0, 1, 2], error="InvalidPermutation")
+add(op="slice_output_shape", cite=S + ":1033-1048", x_shape=[5, 5, 5], starts=[1, 1, 1], ends=[4, 4, 4], axes=None, steps=None, y=[3, 3, 3])
+add(op="slice_output_shape", cite=S + ":1050-1059", x_shape=[5, 5, 5], starts=[1, 1, 1], ends=[4, 4, 4], axes=None, steps=[2, 2, 2], y=[2, 2, 2])
+add(op="slice_output_shape", cite=S + ":1061-1076", x_shape=[5, 5, 5], starts=[-3, -3, -3], ends=[-1, -1, -1], axes=None, steps=None, y=[2, 2, 2])
+add(op="slice_output_shape", cite=S + ":1078-1102", x_shape=[5, 5, 5], starts=[1], ends=[4], axes=[1], steps=None, y=[5, 3, 5])
+add(op="slice_output_shape", cite=S + ":1104-1133", x_shape=[5, 5, 5], starts=[4, 4, 4], ends=[1, 1, 1], axes=None, steps=[-1, -1, -1], y=[4, 4, 4],
+    note="the shape function counts (start - end) / |step| + 1 for a negative step")
+add(op="slice_output_shape_error", cite=S + ":1135-1145", x_shape=[5, 5, 5], starts=[1, 2], ends=[4], axes=None, steps=None, error="InvalidSliceIndices")
+add(op="slice_output_shape_error", cite=S + ":1147-1153", x_shape=[5, 5, 5], starts=[1, 2], ends=[4, 5], axes=[1], steps=None, error="InvalidSliceIndices")
+add(op="slice_output_shape_error", cite=S + ":1155-1161", x_shape=[5, 5, 5], starts=[1], ends=[4], axes=None, steps=[0], error="InvalidSliceStep")
+add(op="slice_output_shape_error", cite=S + ":1163-1169", x_shape=[5, 5, 5], starts=[1], ends=[4], axes=[5], steps=None, error="InvalidSliceIndices")
+add(op="gather", cite=S + ":929-975", dtype="u8", x_shape=[3, 3], x=[1, 2, 3, 4, 5, 6, 7, 8, 9], idx_shape=[2], idx=[0, 2], axis=0,
+    y_shape=[2, 3], y=[1, 2, 3, 7, 8, 9])
+add(op="gather", cite=S + ":977-1025", dtype="u8", x_shape=[2, 4], x=[10, 20, 30, 40, 50, 60, 70, 80], idx_shape=[2, 2], idx=[1, 3, 0, 2], axis=1,
+    y_shape=[2, 2, 2], y=[20, 40, 10, 30, 60, 80, 50, 70])
+add(op="gather", cite=S + ":1887-1916", dtype="u8", x_shape=[2, 3], x=[1, 2, 3, 4, 5, 6], idx_shape=[1], idx=[1], axis=-2,
+    y_shape=[1, 3], y=[4, 5, 6])
+add(op="gather", cite=S + ":1941-1988", dtype="u8", x_shape=[3, 3], x=[1, 2, 3, 4, 5, 6, 7, 8, 9], idx_shape=[2, 2], idx=[0, 2, 1, 1], axis=0,
+    y_shape=[2, 2, 3], y=[1, 2, 3, 7, 8, 9, 4, 5, 6, 4, 5, 6])
+add(op="gather_error", cite=S + ":1918-1939", x_shape=[2, 2], idx_shape=[1], idx=[2], axis=0, error="IndexOutOfBounds")
+add(op="gather_error", cite=S + ":1027-1031", x_shape=[3, 3], idx_shape=[2], idx=[0, 2], axis=5, error="InvalidAxis",
+    note="the Zig test passes an axis beyond the rank")
+
 if __name__ == "__main__":
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_goldens.json")
     with open(out, "w") as f:

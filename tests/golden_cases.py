@@ -78,6 +78,20 @@ def run_case(impl, c, err_type):
     elif op == "leakyReLU":
         y = impl.leakyReLU(np.asarray(c["x"], np.float32), c["slope"])
         assert np.all(np.abs(y.astype(np.float64) - np.asarray(c["y"])) <= c["atol"])
+    elif op == "transpose_onnx":
+        _expect(c, impl.transpose_onnx(arr("x", NP[c["dtype"]]), c["perm"]))
+    elif op == "transpose_onnx_error":
+        raises(lambda: impl.transpose_onnx(np.zeros(c["x_shape"], np.float32), c["perm"]))
+    elif op == "slice_output_shape":
+        assert list(impl.get_slice_output_shape(c["x_shape"], c["starts"], c["ends"], c["axes"], c["steps"])) == c["y"]
+    elif op == "slice_output_shape_error":
+        raises(lambda: impl.get_slice_output_shape(c["x_shape"], c["starts"], c["ends"], c["axes"], c["steps"]))
+    elif op == "gather":
+        idx = np.asarray(c["idx"], np.uint64).reshape(c["idx_shape"])
+        _expect(c, impl.gather(arr("x", NP[c["dtype"]]), idx, c["axis"]))
+    elif op == "gather_error":
+        idx = np.asarray(c["idx"], np.uint64).reshape(c["idx_shape"])
+        raises(lambda: impl.gather(np.zeros(c["x_shape"], np.uint8), idx, c["axis"]))
     elif op == "sigmoid":
         y = impl.sigmoid(np.asarray(c["x"], np.float32))
         assert np.all(np.abs(y.astype(np.float64) - np.asarray(c["y"])) < c["atol"])

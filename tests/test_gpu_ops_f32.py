@@ -290,3 +290,105 @@ def test_next_operators_in_a_plan(zb, ctx, oracle):
     far = np.abs(want[ids[3]] - np.round(want[ids[3]])) > 1e-3
     assert np.array_equal(plan.read_tensor(ids[5])[far], want[ids[5]][far])
     plan.close()
+
+
+# ------------------------------------------------------------------------------------------------
+# Transpose / Slice / Gather: elements are moved, so every dtype is bit-identical to the oracle.
+# ------------------------------------------------------------------------------------------------
+def same_bytes(a, b):
+    assert a.shape == b.shape and a.dtype == b.dtype, (a.shape, b.shape, a.dtype, b.dtype)
+    assert a.tobytes() == b.tobytes()
+
+
+@pytest.mark.parametrize("shape,perm", [((7,), None), ((5, 9), None), ((3, 4, 5), [1, 2, 0]), ((2, 3, 4, 5), [0, 2, 3, 1]),
+                                        ((2, 3, 4, 5), [3, 2, 1, 0]), ((4, 1, 6), [2, 0, 1]), ((2, 64, 17, 9), [0, 2, 3, 1])])
+@pytest.mark.parametrize("dt", [np.float32, np.int8, np.uint8, np.int32])
+def test_transpose_onnx(ctx, oracle, shape, perm, dt):
+    x = np.random.default_rng(len(shape)).integers(-100, 100, shape).astype(dt)
+    same_bytes(ctx.transpose_onnx(x, perm), oracle.transpose_onnx(x, perm))
+    assert np.array_equal(ctx.transpose_onnx(x, perm), np.transpose(x, perm))
+
+
+def test_transpose_onnx_errors(zb, ctx):
+    x = np.zeros((2, 3), np.float32)
+    for perm in ([0, 1, 2], [0, 0], [0, 2]):
+        with pytest.raises(zb.ZantError) as e:
+            ctx.transpose_onnx(x, perm)
+        assert e.value.name == "InvalidPermutation"
+
+
+SLICES = [
+    ((10,), [2], [8], None, None), ((10,), [-3], [100], None, None), ((6, 7), [1, 2], [5, 6], None, [2, 3]),
+    ((4, 5, 6), [1], [4], [1], None), ((4, 5, 6), [0, 1], [4, 6], [0, -1], [3, 2]), ((8,), [6], [1], [0], [-2]),
+    ((5, 5), [4, 4], [-6, 0], None, [-1, -2]), ((3, 4), [2], [2], [0], None), ((2, 3, 4, 5), [1, 0], [2, 5], [0, 3], [1, 4]),
+]
+
+
+@pytest.mark.parametrize("shape,starts,ends,axes,steps", SLICES)
+@pytest.mark.parametrize("dt", [np.float32, np.uint8])
+def test_slice_onnx(ctx, oracle, shape, starts, ends, axes, steps, dt):
+    x = np.arange(int(np.prod(shape))).reshape(shape).astype(dt)
+    got, want = ctx.slice_onnx(x, starts, ends, axes, steps), oracle.slice_onnx(x, starts, ends, axes, steps)
+    same_bytes(got, want)
+    for lean in (False, True):
+        assert ctx.get_slice_output_shape(shape, starts, ends, axes, steps, lean=lean) == oracle.get_slice_output_shape(shape, starts, ends, axes, steps, lean=lean)
+    if steps is None or all(s > 0 for s in steps):
+        # positive steps: the reference agrees with NumPy slicing
+        sl = [slice(None)] * len(shape)
+        for i, (s0, e0) in enumerate(zip(starts, ends)):
+            ax = axes[i] if axes is not None else i
+            sl[ax] = slice(s0, e0, steps[i] if steps is not None else 1)
+        assert np.array_equal(got, x[tuple(sl)])
+
+
+def test_slice_onnx_errors(zb, ctx):
+    x = np.zeros((5, 5, 5), np.float32)
+    for args, name in ((([1], [4], [5], None), "InvalidSliceIndices"), (([1], [4], None, [0]), "InvalidSliceStep"),
+                       (([1, 2], [4], None, None), "InvalidSliceIndices")):
+        with pytest.raises(zb.ZantError) as e:
+            ctx.slice_onnx(x, *args)
+        assert e.value.name == name
+
+
+@pytest.mark.parametrize("shape,idx_shape,axis", [((9,), (4,), 0), ((3, 3), (2,), 0), ((2, 4), (2, 2), 1), ((5, 6, 7), (3,), -2),
+                                                  ((4, 5, 6), (2, 3), 0), ((1000, 64), (128,), 0), ((2, 3, 4, 5), (1,), 3)])
+@pytest.mark.parametrize("dt", [np.float32, np.int8])
+def test_gather(ctx, oracle, shape, idx_shape, axis, dt):
+    rng = np.random.default_rng(sum(shape))
+    x = rng.integers(-100, 100, shape).astype(dt)
+    idx = rng.integers(0, shape[axis], idx_shape).astype(np.uint64)
+    got = ctx.gather(x, idx, axis)
+    same_bytes(got, oracle.gather(x, idx, axis))
+    assert np.array_equal(got, np.take(x, idx.astype(np.int64), axis=axis))
+
+
+def test_gather_errors(zb, ctx):
+    x = np.zeros((2, 2), np.uint8)
+    with pytest.raises(zb.ZantError) as e:
+        ctx.gather(x, np.array([2], np.uint64), 0)
+    assert e.value.name == "IndexOutOfBounds"
+    for axis in (2, -3):
+        with pytest.raises(zb.ZantError) as e:
+            ctx.gather(x, np.array([0], np.uint64), axis)
+        assert e.value.name == "InvalidAxis"
+
+
+def test_movement_operators_in_a_plan(zb, ctx, oracle):
+    import graph_oracle
+    g = zb.Graph("moves")
+    x = g.tensor("x", zb.F32, (2, 6, 4, 5))
+    t = g.tensor("t", zb.F32, (2, 4, 5, 6))
+    s = g.tensor("s", zb.F32, (2, 2, 5, 3))
+    idx = g.tensor("idx", zb.I32, (2, 2), np.array([[2, 0], [1, 1]], np.int32))
+    y = g.tensor("y", zb.F32, (2, 2, 2, 2, 3))
+    g.node("Transpose", [x], [t], perm=[0, 2, 3, 1])
+    g.node("Slice", [t], [s], starts=[1, 0], ends=[3, 6], slice_axes=[1, 3], steps=[1, 2])
+    g.node("Gather", [s, idx], [y], axis=2)
+    g.input, g.output = x, y
+    xin = np.random.default_rng(8).standard_normal((2, 6, 4, 5)).astype(np.float32)
+    want = graph_oracle.run(oracle, g, xin)
+    plan = zb.Plan(ctx, g)
+    same_bytes(plan.run(xin), want[y])
+    ref = np.take(np.transpose(xin, (0, 2, 3, 1))[:, 1:3, :, 0:6:2], np.array([[2, 0], [1, 1]]), axis=2)
+    assert np.array_equal(want[y], ref)
+    plan.close()

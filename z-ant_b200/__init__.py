@@ -29,8 +29,15 @@ COORD_MODE = {"half_pixel": 0, "align_corners": 1, "asymmetric": 2}
 SIZE_MAX = (1 << 64) - 1
 
 OP = dict(Conv=1, MatMul=2, Gemm=3, MaxPool=4, Relu=5, LeakyRelu=6, Add=7, Concat=8, Resize=9, ReduceMean=10,
-          Reshape=11, Clip=12, Sigmoid=13, Softmax=14, Tanh=15, Ceil=16, Mul=17, Div=18, QuantizeLinear=20, DequantizeLinear=21, QLinearConv=22, QLinearMatMul=23,
+          Reshape=11, Clip=12, Sigmoid=13, Softmax=14, Tanh=15, Ceil=16, Mul=17, Div=18, Transpose=19, Slice=27, Gather=28,
+          QuantizeLinear=20, DequantizeLinear=21, QLinearConv=22, QLinearMatMul=23,
           QLinearAdd=24, QLinearGlobalAveragePool=25, LutQ8=26)
+
+
+def _i64(v):
+    if v is None:
+        return None
+    return (C.c_int64 * max(len(v), 1))(*[int(a) for a in v])
 
 
 class ZantError(Exception):
@@ -61,6 +68,9 @@ class NodeAttrs(C.Structure):
         ("b_scale", C.c_float), ("b_zp", C.c_int32),
         ("y_scale", C.c_float), ("y_zp", C.c_int32),
         ("activation", C.c_int32),
+        ("perm", C.c_int64 * 8), ("n_perm", C.c_size_t),
+        ("slice_starts", C.c_int64 * 8), ("slice_ends", C.c_int64 * 8), ("slice_axes", C.c_int64 * 8), ("slice_steps", C.c_int64 * 8),
+        ("n_slice", C.c_size_t), ("slice_has_axes", C.c_int32), ("slice_has_steps", C.c_int32),
     ]
 
 
@@ -448,6 +458,54 @@ class Context:
     def get_concatenate_output_shape(self, shapes, axis):
         return get_concatenate_output_shape(shapes, axis)
 
+    def transpose_onnx(self, x, perm=None, out=None):
+        x = _host(x)
+        sh = _shape(x)
+        if perm is not None and len(perm) == len(sh) and sorted(int(p) for p in perm) == list(range(len(sh))):
+            oshape = [sh[int(p)] for p in perm]
+        else:
+            oshape = list(reversed(sh))       # a bad perm is reported by the library
+        dt = _dtype_code(x)
+        y = self._out(out, oshape, dt)
+        xs, r = _sz(sh); ys, yr = _sz(oshape); pm, npm = _sz(perm)
+        check(lib().zant_b200_transpose_onnx(self._h, C.c_int32(dt), _ptr(x), xs, C.c_size_t(r), pm, C.c_size_t(npm), _ptr(y), ys, C.c_size_t(yr)))
+        return y
+
+    def get_slice_output_shape(self, x_shape, starts, ends, axes=None, steps=None, lean=False):
+        n = len(starts)
+        if len(ends) != n or (axes is not None and len(axes) != n) or (steps is not None and len(steps) != n):
+            raise ZantError(-43, "InvalidSliceIndices")
+        xs, r = _sz(x_shape)
+        out = (C.c_size_t * max(r, 1))()
+        fn = lib().zant_b200_slice_lean_dims if lean else lib().zant_b200_slice_output_shape
+        check(fn(xs, C.c_size_t(r), _i64(starts), _i64(ends), C.c_size_t(n), _i64(axes), _i64(steps), out))
+        return [int(out[i]) for i in range(r)]
+
+    def slice_onnx(self, x, starts, ends, axes=None, steps=None, out=None):
+        x = _host(x)
+        sh = _shape(x)
+        oshape = self.get_slice_output_shape(sh, starts, ends, axes, steps, lean=True)
+        dt = _dtype_code(x)
+        y = self._out(out, oshape, dt)
+        xs, r = _sz(sh); ys, yr = _sz(oshape)
+        check(lib().zant_b200_slice_onnx(self._h, C.c_int32(dt), _ptr(x), xs, C.c_size_t(r), _i64(starts), _i64(ends), C.c_size_t(len(starts)),
+                                         _i64(axes), _i64(steps), _ptr(y), ys, C.c_size_t(yr)))
+        return y
+
+    def gather(self, x, indices, axis, out=None):
+        x = _host(x)
+        sh = _shape(x)
+        idx = np.ascontiguousarray(np.asarray(indices), dtype=np.uint64)
+        nd = len(sh)
+        ax = axis + nd if -nd <= axis < 0 else (axis if 0 <= axis < nd else 0)
+        oshape = (list(sh[:ax]) + list(idx.shape) + list(sh[ax + 1:])) if nd else [1]
+        dt = _dtype_code(x)
+        y = self._out(out, oshape, dt)
+        xs, r = _sz(sh); ys, yr = _sz(oshape); is_, ir = _sz(idx.shape)
+        check(lib().zant_b200_gather(self._h, C.c_int32(dt), _ptr(x), xs, C.c_size_t(r), idx.ctypes.data_as(C.c_void_p), is_, C.c_size_t(ir),
+                                     C.c_int64(axis), _ptr(y), ys, C.c_size_t(yr)))
+        return y
+
     def resize(self, x, mode, scales=None, sizes=None, coord_mode="half_pixel", out=None):
         x = _host(x)
         dt = _dtype_code(x)
@@ -642,6 +700,17 @@ def _fill_attrs(attrs):
         elif k == "scales":
             for i, s in enumerate(v): a.scales[i] = s
             a.n_scales = len(v)
+        elif k == "perm":
+            if v is not None:
+                for i, s in enumerate(v): a.perm[i] = s
+                a.n_perm = len(v)
+        elif k in ("starts", "ends", "slice_axes", "steps"):
+            if v is not None:
+                arr = {"starts": a.slice_starts, "ends": a.slice_ends, "slice_axes": a.slice_axes, "steps": a.slice_steps}[k]
+                for i, s in enumerate(v): arr[i] = s
+                a.n_slice = len(v)
+                if k == "slice_axes": a.slice_has_axes = 1
+                if k == "steps": a.slice_has_steps = 1
         elif k == "coord_mode":
             a.coord_mode = COORD_MODE[v]
         elif k == "activation":

@@ -364,6 +364,85 @@ int32_t zant_b200_concatenate(zant_ctx* ctx, int32_t dtype, const void* const* t
     return s.finish();
 }
 
+int32_t zant_b200_transpose_onnx(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                                 const size_t* perm, size_t n_perm, void* y, const size_t* y_shape, size_t y_rank) {
+    if (!dtype_valid(dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "dtype %d", dtype);
+    if (x_rank) { ZB_NEED(x_shape, "x_shape"); ZB_NEED(y_shape, "y_shape"); }
+    StridedMap m;
+    ZB_TRY(transpose_resolve(x_shape, x_rank, perm, n_perm, y_shape, y_rank, m));
+    if (m.total) { ZB_NEED(x, "x"); ZB_NEED(y, "y"); }
+    ZB_NEED_CTX(ctx);
+    const size_t esz = dtype_size(dtype);
+    Stager s(ctx);
+    const int ix = s.in(x, m.total * esz), iy = s.out(y, m.total * esz);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_strided_copy(ctx, esz, s.ptr<char>(ix), s.ptr<char>(iy), m));
+    return s.finish();
+}
+
+int32_t zant_b200_slice_output_shape(const size_t* x_shape, size_t x_rank, const int64_t* starts, const int64_t* ends, size_t n,
+                                     const int64_t* axes, const int64_t* steps, size_t* out_shape) {
+    if (x_rank) { ZB_NEED(x_shape, "x_shape"); ZB_NEED(out_shape, "out_shape"); }
+    if (n) { ZB_NEED(starts, "starts"); ZB_NEED(ends, "ends"); }
+    return slice_resolve(x_shape, x_rank, starts, ends, n, axes, steps, out_shape, nullptr, true);
+}
+
+int32_t zant_b200_slice_lean_dims(const size_t* x_shape, size_t x_rank, const int64_t* starts, const int64_t* ends, size_t n,
+                                  const int64_t* axes, const int64_t* steps, size_t* out_shape) {
+    if (x_rank) { ZB_NEED(x_shape, "x_shape"); ZB_NEED(out_shape, "out_shape"); }
+    if (n) { ZB_NEED(starts, "starts"); ZB_NEED(ends, "ends"); }
+    return slice_resolve(x_shape, x_rank, starts, ends, n, axes, steps, out_shape, nullptr, false);
+}
+
+int32_t zant_b200_slice_onnx(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                             const int64_t* starts, const int64_t* ends, size_t n, const int64_t* axes, const int64_t* steps,
+                             void* y, const size_t* y_shape, size_t y_rank) {
+    if (!dtype_valid(dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "dtype %d", dtype);
+    if (x_rank) { ZB_NEED(x_shape, "x_shape"); ZB_NEED(y_shape, "y_shape"); }
+    if (n) { ZB_NEED(starts, "starts"); ZB_NEED(ends, "ends"); }
+    StridedMap m;
+    size_t od[8];
+    ZB_TRY(slice_resolve(x_shape, x_rank, starts, ends, n, axes, steps, od, &m));
+    if (y_rank != x_rank) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "output rank %zu, input rank %zu", y_rank, x_rank);
+    for (size_t d = 0; d < x_rank; ++d)
+        if (y_shape[d] != od[d]) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "output dim %zu is %zu, expected %zu", d, y_shape[d], od[d]);
+    if (m.total) { ZB_NEED(x, "x"); ZB_NEED(y, "y"); }
+    ZB_NEED_CTX(ctx);
+    const size_t esz = dtype_size(dtype);
+    Stager s(ctx);
+    const int ix = s.in(x, numel(x_shape, x_rank) * esz), iy = s.out(y, m.total * esz);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_strided_copy(ctx, esz, s.ptr<char>(ix), s.ptr<char>(iy), m));
+    return s.finish();
+}
+
+int32_t zant_b200_gather(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                         const size_t* indices, const size_t* idx_shape, size_t idx_rank, int64_t axis,
+                         void* y, const size_t* y_shape, size_t y_rank) {
+    if (!dtype_valid(dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "dtype %d", dtype);
+    if (x_rank) ZB_NEED(x_shape, "x_shape");
+    if (idx_rank) ZB_NEED(idx_shape, "idx_shape");
+    ZB_NEED(y_shape, "y_shape");
+    size_t n_idx = 1;
+    for (size_t i = 0; i < idx_rank; ++i) n_idx *= idx_shape[i];
+    if (n_idx) ZB_NEED(indices, "indices");
+    if (is_device_ptr(indices)) return fail(ZANT_E_INVALID_INPUT, "gather indices must be a host array");
+    GatherGeom g;
+    ZB_TRY(gather_resolve(x_shape, x_rank, indices, idx_shape, idx_rank, axis, y_shape, y_rank, g));
+    if (g.axis_dim > 0x7fffffffULL) return fail(ZANT_E_TOO_LARGE, "gather axis of %zu entries", g.axis_dim);
+    const size_t total = g.outer * g.n_idx * g.inner;
+    if (total) { ZB_NEED(x, "x"); ZB_NEED(y, "y"); }
+    ZB_NEED_CTX(ctx);
+    std::vector<int32_t> idx32(g.n_idx);
+    for (size_t i = 0; i < g.n_idx; ++i) idx32[i] = (int32_t)indices[i];
+    const size_t esz = dtype_size(dtype);
+    Stager s(ctx);
+    const int ix = s.in(x, numel(x_shape, x_rank) * esz), ii = s.in(idx32.data(), idx32.size() * 4), iy = s.out(y, total * esz);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_gather(ctx, esz, s.ptr<char>(ix), s.ptr<int32_t>(ii), s.ptr<char>(iy), g));
+    return s.finish();
+}
+
 int32_t zant_b200_resize(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t rank,
                          const char* mode, size_t mode_len, const float* scales, size_t n_scales,
                          const size_t* sizes, size_t n_sizes, const char* coord_mode, size_t coord_mode_len,

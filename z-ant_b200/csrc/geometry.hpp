@@ -541,4 +541,111 @@ inline int32_t shard_range(size_t total, size_t world, size_t rank, size_t* begi
     return ZANT_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// Transpose / Slice / Gather: all three are "output element i comes from input element f(i)" with f
+// affine in the output coordinates (plus one table look-up for Gather).
+// ------------------------------------------------------------------------------------------
+struct StridedMap {
+    int rank = 0;
+    long long out_dims[8] = {0};
+    long long in_stride[8] = {0};   // elements; may be negative (Slice with a negative step)
+    long long base = 0;
+    size_t total = 0;
+};
+
+// transpose_onnx_lean, lib_shape_math.zig:1628-1700.
+inline int32_t transpose_resolve(const size_t* xs, size_t xr, const size_t* perm, size_t np, const size_t* ys, size_t yr, StridedMap& m) {
+    if (xr > 8) return fail(ZANT_E_UNSUPPORTED_DIMENSION, "rank %zu", xr);
+    if (yr != xr) return fail(ZANT_E_INVALID_RANK, "output rank %zu, input rank %zu", yr, xr);
+    size_t rp[8];
+    if (perm) {
+        if (np != xr) return fail(ZANT_E_INVALID_PERMUTATION, "perm holds %zu entries for rank %zu", np, xr);
+        bool used[8] = {false};
+        for (size_t i = 0; i < xr; ++i) {
+            if (perm[i] >= xr || used[perm[i]]) return fail(ZANT_E_INVALID_PERMUTATION, "perm[%zu] = %zu", i, perm[i]);
+            used[perm[i]] = true;
+            rp[i] = perm[i];
+        }
+    } else {
+        for (size_t i = 0; i < xr; ++i) rp[i] = xr - 1 - i;
+    }
+    long long istr[8], st = 1;
+    for (size_t i = xr; i-- > 0;) { istr[i] = st; st *= (long long)xs[i]; }
+    m.rank = (int)xr; m.base = 0; m.total = 1;
+    for (size_t d = 0; d < xr; ++d) {
+        m.out_dims[d] = (long long)xs[rp[d]];
+        m.in_stride[d] = istr[rp[d]];
+        if (ys[d] != xs[rp[d]]) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "output dim %zu is %zu, expected %zu", d, ys[d], xs[rp[d]]);
+        m.total *= xs[rp[d]];
+    }
+    return ZANT_OK;
+}
+
+// get_slice_output_shape (lib_shape_math.zig:1497-1560) and lean_slice_onnx (:1378-1443) normalise
+// starts / ends / steps identically but count the elements of a NEGATIVE step differently: the shape
+// function takes (start - end) / |step| + 1, the operator ceil((start - end - 1) / |step|) and then writes
+// its own count into the output's shape.  `shape_rule` selects the former.  `out_dims` gets xr entries.
+inline int32_t slice_resolve(const size_t* xs, size_t xr, const int64_t* starts, const int64_t* ends, size_t n, const int64_t* axes,
+                             const int64_t* steps, size_t* out_dims, StridedMap* m, bool shape_rule = false) {
+    if (xr > 8) return fail(ZANT_E_UNSUPPORTED_DIMENSION, "rank %zu", xr);
+    long long a_start[8], a_end[8], a_step[8];
+    for (size_t i = 0; i < xr; ++i) { a_start[i] = 0; a_end[i] = (long long)xs[i]; a_step[i] = 1; }
+    for (size_t i = 0; i < n; ++i) {
+        const long long axis = axes ? axes[i] : (long long)i;
+        const long long ax = axis < 0 ? axis + (long long)xr : axis;
+        if (ax < 0 || (size_t)ax >= xr) return fail(ZANT_E_INVALID_SLICE_INDICES, "axis %lld for rank %zu", axis, xr);
+        const long long dim = (long long)xs[ax];
+        long long s0 = starts[i] < 0 ? starts[i] + dim : starts[i];
+        s0 = std::max(0LL, std::min(s0, dim));
+        long long e0 = ends[i] < 0 ? ends[i] + dim : ends[i];
+        if (steps && steps[i] < 0) e0 = ends[i] < 0 ? -1 : e0;
+        else e0 = std::max(0LL, std::min(e0, dim));
+        a_start[ax] = s0; a_end[ax] = e0;
+        if (steps) {
+            if (steps[i] == 0) return fail(ZANT_E_INVALID_SLICE_STEP, "step 0 on axis %lld", axis);
+            a_step[ax] = steps[i];
+        }
+    }
+    long long istr[8], st = 1;
+    for (size_t i = xr; i-- > 0;) { istr[i] = st; st *= (long long)xs[i]; }
+    if (m) { m->rank = (int)xr; m->base = 0; m->total = 1; }
+    for (size_t i = 0; i < xr; ++i) {
+        long long d = 0;
+        if (a_step[i] > 0) { if (a_end[i] > a_start[i]) d = ((a_end[i] - a_start[i]) + a_step[i] - 1) / a_step[i]; }
+        else if (a_start[i] > a_end[i]) {
+            const long long as = -a_step[i];
+            if (shape_rule) d = (a_start[i] - a_end[i]) / as + 1;
+            else { const long long range = a_start[i] - (a_end[i] + 1); d = (range + as - 1) / as; }
+        }
+        out_dims[i] = (size_t)d;
+        if (m) { m->out_dims[i] = d; m->in_stride[i] = a_step[i] * istr[i]; m->base += a_start[i] * istr[i]; m->total *= (size_t)d; }
+    }
+    return ZANT_OK;
+}
+
+struct GatherGeom { size_t outer = 0, n_idx = 0, inner = 0, axis_dim = 0; };
+
+// gather, lib_shape_math.zig:1217-1277 (validation and output shape) over host indices.
+inline int32_t gather_resolve(const size_t* xs, size_t xr, const size_t* indices, const size_t* is, size_t ir, int64_t axis_in,
+                              const size_t* ys, size_t yr, GatherGeom& g) {
+    if (xr == 0) return fail(ZANT_E_INVALID_RANK, "gather on a rank-0 tensor");
+    const long long nd = (long long)xr;
+    if (axis_in >= nd || axis_in < -nd) return fail(ZANT_E_INVALID_AXIS, "axis %lld for rank %zu", (long long)axis_in, xr);
+    const size_t axis = (size_t)(axis_in < 0 ? nd + axis_in : axis_in);
+    g.n_idx = 1;
+    for (size_t i = 0; i < ir; ++i) g.n_idx *= is[i];
+    for (size_t i = 0; i < g.n_idx; ++i)
+        if (indices[i] >= xs[axis]) return fail(ZANT_E_INDEX_OUT_OF_BOUNDS, "index %zu on an axis of %zu", indices[i], xs[axis]);
+    if (yr != xr + ir - 1) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "output rank %zu, expected %zu", yr, xr + ir - 1);
+    bool ok = true;
+    for (size_t i = 0; i < axis; ++i) ok = ok && ys[i] == xs[i];
+    for (size_t i = 0; i < ir; ++i) ok = ok && ys[axis + i] == is[i];
+    for (size_t i = axis + 1; i < xr; ++i) ok = ok && ys[axis + ir + (i - axis - 1)] == xs[i];
+    if (!ok) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "gather output shape");
+    g.outer = 1; g.inner = 1; g.axis_dim = xs[axis];
+    for (size_t i = 0; i < axis; ++i) g.outer *= xs[i];
+    for (size_t i = axis + 1; i < xr; ++i) g.inner *= xs[i];
+    return ZANT_OK;
+}
+
 }  // namespace zb

@@ -396,4 +396,36 @@ __global__ void reduce_all_mean_f32(const float* __restrict__ x, float* __restri
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Transpose / Slice: y[i] = x[base + sum_d coord_d(i) * in_stride[d]], coordinates of the row-major
+// output index.  Gather: y[(o * n_idx + k) * inner + j] = x[(o * axis_dim + idx[k]) * inner + j].
+// T is an unsigned type of the element's size.
+// ------------------------------------------------------------------------------------------
+struct StridedMapDev { int rank; long long out_dims[8]; long long in_stride[8]; long long base; size_t total; };
+
+template <typename T>
+__global__ void strided_copy_k(const T* __restrict__ x, T* __restrict__ y, const StridedMapDev m) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < m.total; i += (size_t)gridDim.x * blockDim.x) {
+        size_t t = i;
+        long long src = m.base;
+        for (int d = m.rank - 1; d >= 0; --d) {
+            const size_t c = t % (size_t)m.out_dims[d];
+            t /= (size_t)m.out_dims[d];
+            src += (long long)c * m.in_stride[d];
+        }
+        y[i] = x[src];
+    }
+}
+
+template <typename T>
+__global__ void gather_axis_k(const T* __restrict__ x, const int32_t* __restrict__ idx, T* __restrict__ y,
+                              size_t outer, size_t n_idx, size_t inner, size_t axis_dim) {
+    const size_t total = outer * n_idx * inner;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t j = i % inner, t = i / inner;
+        const size_t k = t % n_idx, o = t / n_idx;
+        y[i] = x[(o * axis_dim + (size_t)idx[k]) * inner + j];
+    }
+}
+
 }  // namespace zb

@@ -270,4 +270,24 @@ inline void requant_multipliers(float x_scale, const float* w_scale, size_t nws,
     }
 }
 
+inline int32_t run_strided_copy(zant_ctx* ctx, size_t esz, const void* x, void* y, const StridedMap& m) {
+    if (m.total == 0) return ZANT_OK;
+    StridedMapDev d{};
+    d.rank = m.rank; d.base = m.base; d.total = m.total;
+    for (int i = 0; i < 8; ++i) { d.out_dims[i] = m.out_dims[i]; d.in_stride[i] = m.in_stride[i]; }
+    const int grid = grid_for(m.total, 256, ctx->sm_count);
+    if (esz == 4) strided_copy_k<uint32_t><<<grid, 256, 0, ctx->stream>>>((const uint32_t*)x, (uint32_t*)y, d);
+    else strided_copy_k<uint8_t><<<grid, 256, 0, ctx->stream>>>((const uint8_t*)x, (uint8_t*)y, d);
+    return check_launch(ctx, "strided_copy_k");
+}
+
+inline int32_t run_gather(zant_ctx* ctx, size_t esz, const void* x, const int32_t* idx_dev, void* y, const GatherGeom& g) {
+    const size_t total = g.outer * g.n_idx * g.inner;
+    if (total == 0) return ZANT_OK;
+    const int grid = grid_for(total, 256, ctx->sm_count);
+    if (esz == 4) gather_axis_k<uint32_t><<<grid, 256, 0, ctx->stream>>>((const uint32_t*)x, idx_dev, (uint32_t*)y, g.outer, g.n_idx, g.inner, g.axis_dim);
+    else gather_axis_k<uint8_t><<<grid, 256, 0, ctx->stream>>>((const uint8_t*)x, idx_dev, (uint8_t*)y, g.outer, g.n_idx, g.inner, g.axis_dim);
+    return check_launch(ctx, "gather_axis_k");
+}
+
 }  // namespace zb

@@ -453,6 +453,49 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
             else return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "MaxPool on int32");
             return ZANT_OK;
         }
+        case ZANT_OP_TRANSPOSE:
+        case ZANT_OP_SLICE: {
+            ZB_TRY(need_inputs(n, 1, 1, "Transpose/Slice"));
+            const int x = n.in[0], y = n.out[0];
+            if (T(x).dtype != T(y).dtype) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "Transpose/Slice dtype mismatch");
+            StridedMap m;
+            const std::vector<size_t>& xs = T(x).shape; const std::vector<size_t>& ys = T(y).shape;
+            if (n.op == ZANT_OP_TRANSPOSE) {
+                size_t perm[8];
+                if (a.n_perm > 8) return fail(ZANT_E_INVALID_PERMUTATION, "perm holds %zu entries", a.n_perm);
+                for (size_t i = 0; i < a.n_perm; ++i) perm[i] = a.perm[i] < 0 ? (size_t)-1 : (size_t)a.perm[i];
+                ZB_TRY(transpose_resolve(xs.data(), xs.size(), a.n_perm ? perm : nullptr, a.n_perm, ys.data(), ys.size(), m));
+            } else {
+                if (a.n_slice > 8) return fail(ZANT_E_INVALID_SLICE_INDICES, "%zu slice entries", a.n_slice);
+                size_t od[8];
+                ZB_TRY(slice_resolve(xs.data(), xs.size(), a.slice_starts, a.slice_ends, a.n_slice, a.slice_has_axes ? a.slice_axes : nullptr,
+                                     a.slice_has_steps ? a.slice_steps : nullptr, od, &m));
+                if (ys.size() != xs.size()) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "Slice output rank");
+                for (size_t d = 0; d < xs.size(); ++d) if (ys[d] != od[d]) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "Slice output dim %zu", d);
+            }
+            const size_t esz = dtype_size(T(x).dtype);
+            push(n.op == ZANT_OP_TRANSPOSE ? "Transpose" : "Slice", [=]() { return run_strided_copy(ctx, esz, pl->ptr(x), pl->ptr(y), m); });
+            return ZANT_OK;
+        }
+        case ZANT_OP_GATHER: {
+            ZB_TRY(need_inputs(n, 2, 2, "Gather"));
+            const int x = n.in[0], ind = n.in[1], y = n.out[0];
+            if (T(x).dtype != T(y).dtype) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "Gather dtype mismatch");
+            ZB_TRY(want_dtype(pl, ind, ZANT_I32, "Gather indices"));
+            if (!T(ind).is_const) return fail(ZANT_E_UNSUPPORTED, "Gather indices must be an initializer");
+            const size_t ni = numel(T(ind).shape.data(), T(ind).shape.size());
+            std::vector<size_t> idx(ni);
+            for (size_t i = 0; i < ni; ++i) {
+                const int32_t v = ((const int32_t*)T(ind).host.data())[i];
+                idx[i] = v < 0 ? (size_t)-1 : (size_t)v;      // a negative index is out of bounds, as for the reference's usize
+            }
+            GatherGeom g;
+            ZB_TRY(gather_resolve(T(x).shape.data(), T(x).shape.size(), idx.data(), T(ind).shape.data(), T(ind).shape.size(), a.axis,
+                                  T(y).shape.data(), T(y).shape.size(), g));
+            const size_t esz = dtype_size(T(x).dtype);
+            push("Gather", [=]() { return run_gather(ctx, esz, pl->ptr(x), pl->p<int32_t>(ind), pl->ptr(y), g); });
+            return ZANT_OK;
+        }
         case ZANT_OP_SIGMOID:
         case ZANT_OP_TANH:
         case ZANT_OP_CEIL: {

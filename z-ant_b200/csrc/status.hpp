@@ -31,6 +31,12 @@ inline const char* status_name(int32_t s) {
         case ZANT_E_INPUT_ARRAY_WRONG_SIZE: return "InputArrayWrongSize";
         case ZANT_E_EMPTY_TENSOR: return "EmptyTensor";
         case ZANT_E_ZERO_SIZE_TENSOR: return "ZeroSizeTensor";
+        case ZANT_E_INVALID_SLICE_INDICES: return "InvalidSliceIndices";
+        case ZANT_E_INVALID_SLICE_STEP: return "InvalidSliceStep";
+        case ZANT_E_INVALID_AXIS: return "InvalidAxis";
+        case ZANT_E_DUPLICATE_AXIS: return "DuplicateAxis";
+        case ZANT_E_INVALID_RANK: return "InvalidRank";
+        case ZANT_E_INVALID_PERMUTATION: return "InvalidPermutation";
         case ZANT_E_AXIS_OUT_OF_BOUNDS: return "AxisOutOfBounds";
         case ZANT_E_MISMATCHED_RANK: return "MismatchedRank";
         case ZANT_E_MISMATCHED_SHAPE: return "MismatchedShape";
