@@ -120,12 +120,29 @@ __device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t addr, uint32_t lbo
     return d;                  // base_offset 0, lbo_mode 0, layout type 0 (no swizzle)
 }
 
+// Shared-memory matrix descriptor, MN-major with the 128-byte swizzle: the operand's M (or N) index
+// runs along 128-byte rows (128 int8 elements, their 16-byte chunks XOR-swizzled with the row number
+// as a TMA load with SWIZZLE_128B writes them), eight consecutive K indices are eight consecutive rows,
+// and the next group of eight K indices lies SBO bytes further; LBO is the distance to the next
+// 128-element block along M/N.  The tile must start at a 1024-byte boundary.
+__device__ __forceinline__ uint64_t smem_desc_mnmajor_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;   // descriptor version for sm_100
+    d |= (uint64_t)2 << 61;   // layout type: 128-byte swizzle
+    return d;
+}
+
 // Instruction descriptor for kind::i8: int32 accumulator, K-major A and B.
 // a_unsigned / b_unsigned choose uint8 (0) or int8 (1) in the format fields.
 __host__ __device__ constexpr uint32_t idesc_i8(int M, int N, bool a_signed, bool b_signed) {
     return (2u << 4) | ((a_signed ? 1u : 0u) << 7) | ((b_signed ? 1u : 0u) << 10) |
            ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// Bit 15 of the instruction descriptor: A is MN-major (its M index is the contiguous one).
+constexpr uint32_t kIdescAMnMajor = 1u << 15;
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
 __device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {

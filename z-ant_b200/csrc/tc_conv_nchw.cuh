@@ -16,6 +16,9 @@
 // (kh*dh*PW + kw*dw) chunks, which a K-major no-swizzle shared-memory descriptor expresses
 // directly: MMA row r stands for patch pixel r, i.e. output (r / PW, r % PW) of the tile; rows
 // with r % PW >= BW or r / PW >= BH are computed and dropped.  No im2col matrix exists anywhere.
+// 1x1 convolutions skip steps 1-2: a box of 128 pixels x CB*16 channels, loaded with the 128-byte swizzle,
+// is already a valid MMA operand (MN-major: the pixel index is the contiguous one), so the loader
+// signals the MMA issuer directly and the transposing warps stay idle.
 // Weights are pre-blocked [filter tile][channel stage][tap][CB][NT][16]; they stay resident in
 // shared memory when there is a single filter tile, else one bulk copy per stage streams them.
 // The epilogue requantises into a shared-memory image of the tile's NCHW bytes and copies it out
@@ -48,6 +51,7 @@ struct TcConvArgs {
     int BH, BW, PH, PW, PR;           // tile, patch, allocated patch pixels per 16-channel group
     int hseg, wseg, c_stages, n_tiles;
     int CB;                           // 16-channel groups per stage (2, 4 or 8)
+    int direct;                       // 1x1 convolution: the TMA box is the MMA operand itself (MN-major, 128-byte swizzle); no transposes
     int full_width;                   // 1: a tile spans the image width and a channel's patch rows are one run; 0: one run per row
     int RP;                           // staging bytes between two patch rows of a channel (W, or the run pitch when rows are separate runs)
     int CP;                           // staging bytes per channel
@@ -186,7 +190,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     const uint32_t w_stage_bytes = (uint32_t)taps * w_tap_bytes;
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), a.w_resident ? 1 : 2); ptx::mbar_init(empty(s), 1); }
+        for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), (a.direct || a.w_resident) ? 1 : 2); ptx::mbar_init(empty(s), 1); }
         for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 8); }
         for (int s = 0; s < S; ++s) { ptx::mbar_init(ld_full(s), 1); ptx::mbar_init(ld_empty(s), 8); }
         ptx::mbar_init(wfull, 1);
@@ -226,6 +230,19 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             const TcConvTile T = tc_conv_tile(a, cur);
             tc_conv_cursor_next(a, cur);
             for (int cs = 0; cs < a.c_stages; ++cs) {
+                if (a.direct) {
+                    // 1x1: the box of 128 pixels x CB*16 channels lands where the MMA reads it
+                    if (!ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag)) { alive = false; break; }
+                    if (lane == 0) {
+                        const uint32_t stage0 = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
+                        ptx::mbar_arrive_expect_tx(full(s), box_bytes + (a.w_resident ? 0u : w_stage_bytes));
+                        ptx::tma_load_3d(stage0 + (uint32_t)a.off_patch, &x_map, T.w0 >> 2, cs * CH, T.img, full(s));
+                        if (!a.w_resident) ptx::bulk_g2s(stage0, a.w + ((size_t)T.nt * a.c_stages + cs) * w_stage_bytes, w_stage_bytes, full(s));
+                    }
+                    __syncwarp();
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                    continue;
+                }
                 // the slot's previous contents have been transposed (and, for streamed weights, multiplied)
                 bool ok = ptx::mbar_wait(ld_empty(s), ph ^ 1u, abort_flag);
                 if (ok && !a.w_resident) ok = ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag);
@@ -270,9 +287,20 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                     ptx::tc_fence_after();
                     const uint32_t stage0 = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
                     const uint32_t sw = a.w_resident ? ptx::smem_u32(smem + a.off_wres) + (uint32_t)cs * w_stage_bytes : stage0;
-                    uint64_t da_row = ptx::smem_desc_kmajor(stage0 + (uint32_t)a.off_patch, a_lbo, 128);
                     uint64_t db = ptx::smem_desc_kmajor(sw, NT * 16, 128);
                     uint32_t acc = cs != 0 ? 1u : 0u;
+                    if (a.direct) {
+                        // A = [channel][128 pixels] rows of 128 bytes: MN-major; a K step of 32 channels is 4096 bytes
+                        const uint64_t da0 = ptx::smem_desc_mnmajor_sw128(stage0 + (uint32_t)a.off_patch, (uint32_t)(a.CB * 16 * 128), 1024);
+                        for (int kk = 0; kk < ksteps; ++kk) {
+                            ptx::mma_i8(d_tmem, da0 + (uint64_t)kk * 256u, db + (uint64_t)kk * b_kstep, idesc | ptx::kIdescAMnMajor, (acc | (uint32_t)kk) != 0);
+                        }
+                        ptx::mma_commit(empty(s));
+                        if (++s == S) { s = 0; ph ^= 1u; }
+                        ZB_TACC(2);
+                        continue;
+                    }
+                    uint64_t da_row = ptx::smem_desc_kmajor(stage0 + (uint32_t)a.off_patch, a_lbo, 128);
                     for (int kh = 0; kh < a.KH; ++kh, da_row += a_rowstep) {
                         uint64_t da = da_row;
                         for (int kw = 0; kw < a.KW; ++kw, da += a_col, db += b_tap) {
@@ -294,7 +322,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         // ------------------------------------------------------------------ transpose: staging -> patch (256 threads)
         const int p = tid - 64;
         const int my_tiles = (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-        const int total_it = my_tiles * a.c_stages;
+        const int total_it = a.direct ? 0 : my_tiles * a.c_stages;   // 1x1 convolutions need no transposes
 
         // transpose items: 16 channels x 4 pixels each, decoded once; consecutive threads take consecutive
         // words of a patch row (conflict-free loads).  The 16-byte stores of a quarter warp would all fall
@@ -551,10 +579,13 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
     a.wseg = (a.OW + a.BW - 1) / a.BW;
     a.hseg = (a.OH + a.BH - 1) / a.BH;
     a.full_width = a.wseg == 1 ? 1 : 0;
+    a.direct = pointwise ? 1 : 0;
     // the bulk copies start at 16-byte boundaries; every channel of a stage must see the same offset
     if (((long long)a.H * a.W) % 16 != 0) return false;
     if (!a.full_width && a.W % 16 != 0) return false;
-    if (a.full_width) {
+    if (a.direct) {
+        a.RP = 128; a.CP = 128; a.KN = 1;               // the box row is the operand row: 128 pixels of one channel
+    } else if (a.full_width) {
         a.RP = a.W;
         a.CP = (a.PH * a.W + 15 + 15) / 16 * 16;        // box row: the run plus its alignment slack
         if (a.CP > 1024) return false;                  // box rows hold at most 256 four-byte elements
@@ -589,8 +620,14 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
                 const long long w_all = (long long)c_stages * w_stage;
                 if (resident && (a.n_tiles != 1 || w_all > 112 * 1024)) continue;
                 const int off_patch = resident ? 0 : w_stage;
-                const int off_stg = (off_patch + cb * a.PR * 16 + 127) / 128 * 128;   // TMA destination
-                const int stage_bytes = (off_stg + cb * 16 * a.CP + 128 + 127) / 128 * 128;   // + 128: the transposes may read a few bytes past the last channel
+                int off_stg, stage_bytes;
+                if (a.direct) {       // operand tile = TMA destination: 1024-byte aligned, no staging
+                    off_stg = off_patch;
+                    stage_bytes = (off_patch + cb * 16 * 128 + 1023) / 1024 * 1024;
+                } else {
+                    off_stg = (off_patch + cb * a.PR * 16 + 127) / 128 * 128;   // TMA destination
+                    stage_bytes = (off_stg + cb * 16 * a.CP + 128 + 127) / 128 * 128;   // + 128: the transposes may read a few bytes past the last channel
+                }
                 const int stages = std::min<long long>(kTcConvMaxStages, (budget - (resident ? w_all : 0)) / stage_bytes);
                 if (stages < min_stages) continue;
                 a.CB = cb; a.c_stages = c_stages; a.w_resident = resident; a.off_patch = off_patch; a.off_stg = off_stg;
@@ -600,7 +637,7 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
                 placed = true;
             }
     if (!placed) return false;
-    if (a.CB * a.PH * a.KN > 1024) return false;   // the transposers' per-thread work lists hold 4 entries
+    if (!a.direct && a.CB * a.PH * a.KN > 1024) return false;   // the transposers' per-thread work lists hold 4 entries
     p.smem_bytes = (size_t)a.off_out + out_bytes + kTcConvTail;
     p.w_bytes = (size_t)a.n_tiles * a.c_stages * taps * a.CB * p.NT * 16;
     // one contiguous output run per filter and tile; V = widest store that every run start and length allows
@@ -663,7 +700,14 @@ inline int32_t tc_conv_encode_map(const TcConvArgs& a, const void* x, CUtensorMa
     cuuint64_t dims[4], strides[3];
     cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
     cuuint32_t rank;
-    if (a.full_width) {
+    CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_NONE;
+    if (a.direct) {
+        rank = 3;
+        dims[0] = H * W / 4; dims[1] = C; dims[2] = N;
+        strides[0] = H * W; strides[1] = C * H * W;
+        box[0] = 32; box[1] = (cuuint32_t)(a.CB * 16); box[2] = 1;     // 128 pixels x the stage's channels
+        swizzle = CU_TENSOR_MAP_SWIZZLE_128B;
+    } else if (a.full_width) {
         rank = 3;
         dims[0] = H * W / 4; dims[1] = C; dims[2] = N;
         strides[0] = H * W; strides[1] = C * H * W;
@@ -690,7 +734,7 @@ inline int32_t tc_conv_encode_map(const TcConvArgs& a, const void* x, CUtensorMa
         encode = reinterpret_cast<EncodeFn>(fn);
     }
     const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, rank, const_cast<void*>(x), dims, strides, box, estr,
-                                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(ZANT_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return ZANT_OK;
