@@ -26,7 +26,7 @@
 //
 // Warp roles (576 threads, one persistent CTA per SM):
 //   warp 0       loader (bulk copies)          warp 1        TMEM owner + MMA issuer
-//   warps 2-9    transpose                     warps 10-17   epilogue
+//   warps 2-9    transpose (1x1: epilogue)     warps 10-17   epilogue
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), (a.direct || a.w_resident) ? 1 : 2); ptx::mbar_init(empty(s), 1); }
-        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 8); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), a.direct ? 16 : 8); }
         for (int s = 0; s < S; ++s) { ptx::mbar_init(ld_full(s), 1); ptx::mbar_init(ld_empty(s), 8); }
         ptx::mbar_init(wfull, 1);
         *abort_flag = 0;
@@ -318,11 +318,11 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             ZB_TDUMP(0);
         mma_done:;
         }
-    } else if (warp < 10) {
+    } else if (warp < 10 && !a.direct) {
         // ------------------------------------------------------------------ transpose: staging -> patch (256 threads)
         const int p = tid - 64;
         const int my_tiles = (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-        const int total_it = a.direct ? 0 : my_tiles * a.c_stages;   // 1x1 convolutions need no transposes
+        const int total_it = my_tiles * a.c_stages;
 
         // transpose items: 16 channels x 4 pixels each, decoded once; consecutive threads take consecutive
         // words of a patch row (conflict-free loads).  The 16-byte stores of a quarter warp would all fall
@@ -415,12 +415,16 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         }
         if (p == 0) ZB_TDUMP(8);
     } else {
-        // ------------------------------------------------------------------ epilogue: warps 10..17
+        // ------------------------------------------------------------------ epilogue: warps 10..17, and for 1x1
+        // convolutions also warps 2..9, which have nothing to transpose.  Each TMEM lane quarter is served by
+        // n_epi / 4 warps that split the tile's filters.
+        const int n_epi = a.direct ? 16 : 8;
+        const int ew = warp >= 10 ? warp - 10 : warp + 6;     // 0..7, then 8..15
         const int quarter = warp & 3;
-        const int half = (warp - 10) >> 2;
-        const int ew = warp - 10;
+        const int part = ew >> 2;
+        const int cols = NT / (n_epi >> 2);                    // filters of this warp: 16 .. 128
         const int row = quarter * 32 + lane;
-        const int e = tid - 320;
+        const int e = ew * 32 + lane;
         const Requant rq{a.y_scale, a.y_zp, a.act};
         const int oh_l = row / a.PW, ow_l = row - oh_l * a.PW;
         const bool row_live = oh_l < a.BH && ow_l < a.BW;        // this MMA row is an output of the tile
@@ -437,7 +441,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         }
         const int co_lpc = 1 << co_shift, co_cpp = 32 >> co_shift;
         const int co_c0 = ew * co_cpp + (lane >> co_shift), co_v0 = lane & (co_lpc - 1);
-        const size_t co_dst_step = (size_t)(8 * co_cpp) * ohw;
+        const size_t co_dst_step = (size_t)(n_epi * co_cpp) * ohw;
         int tile_it = 0;
         TcConvCursor ecur;
         tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, ecur);
@@ -449,27 +453,27 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
             ZB_TACC(0);
             if (e == 0) *epi_ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
-            ptx::named_barrier_sync(1, 256);
+            ptx::named_barrier_sync(1, n_epi * 32);
             if (!*epi_ok) break;
             ZB_TACC(1);
             ptx::tc_fence_after();
-            const int tcol0 = half * (NT / 2);
+            const int tcol0 = part * cols;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * NT + tcol0);
             uint8_t* ob = sOut + (size_t)b * NT * kTcConvOutPitch;
             uint8_t* orow = ob + (size_t)tcol0 * kTcConvOutPitch + pix_off;
 #pragma unroll 1
-            for (int h = 0; h < NT / 64; ++h) {
-                const int col0 = T.nt * NT + tcol0 + h * 32;
+            for (int h = 0; h < cols / 16; ++h) {
+                const int col0 = T.nt * NT + tcol0 + h * 16;
                 if (col0 >= a.M) break;                              // the rest of the tile is filter padding
-                uint32_t v[32];
-                ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
+                uint32_t v[16];
+                ptx::tmem_ld16(taddr + (uint32_t)(h * 16), v);
                 ptx::tmem_wait_ld();
-                uint8_t* oc = orow + (size_t)h * 32 * kTcConvOutPitch;
+                uint8_t* oc = orow + (size_t)h * 16 * kTcConvOutPitch;
                 if constexpr (LEAN) {
                     auto lean_chunk = [&](auto clamp) {
                         constexpr bool CL = decltype(clamp)::value;
 #pragma unroll
-                        for (int j4 = 0; j4 < 8; ++j4) {
+                        for (int j4 = 0; j4 < 4; ++j4) {
                             const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
                             const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
                             const int q0 = tc_conv_round<CL>((int)v[j4 * 4 + 0] + b4.x, m4.x);
@@ -491,7 +495,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                     else lean_chunk(std::true_type{});
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
+                    for (int j = 0; j < 16; ++j) {
                         const int acc = (int)v[j] + sBias[col0 + j];
                         const int q = a.out_u8 ? requant_one<true>(acc, sMult[col0 + j], rq) : requant_one<false>(acc, sMult[col0 + j], rq);
                         if (row_live) oc[j * kTcConvOutPitch] = (uint8_t)q;
@@ -502,7 +506,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(tempty(b));          // the accumulator is free again
             ZB_TACC(2);
-            ptx::named_barrier_sync(1, 256);                     // the tile's bytes are staged
+            ptx::named_barrier_sync(1, n_epi * 32);              // the tile's bytes are staged
             ZB_TACC(3);
 
             // copy-out: per filter one contiguous run of the NCHW output
@@ -512,7 +516,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             const int slots = nvec + (tail_bytes ? 1 : 0);
             uint8_t* dst = a.y + ((size_t)T.img * a.M + (size_t)(T.nt * NT + co_c0)) * ohw + (size_t)T.h0 * a.OW + T.w0;
             const uint8_t* src = ob + co_c0 * kTcConvOutPitch;
-            for (int c = co_c0; c < ncv; c += 8 * co_cpp, dst += co_dst_step, src += 8 * co_cpp * kTcConvOutPitch) {
+            for (int c = co_c0; c < ncv; c += n_epi * co_cpp, dst += co_dst_step, src += n_epi * co_cpp * kTcConvOutPitch) {
                 for (int vv = co_v0; vv < slots; vv += co_lpc) {
                     const int o = vv << a.log2V;
                     if (vv < nvec) {
