@@ -148,6 +148,8 @@ TC_QCONV = [
     (2, 7, 23, 23, 130, 5, (1, 2), (2, 2, 2, 2), (2, 1), I8, I8, -5, 3, True, True, "relu"),
     (2, 256, 16, 16, 300, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, U8, 0, 100, True, True, None),
     (4, 3, 32, 32, 32, 3, (2, 2), (1, 1, 1, 1), (1, 1), U8, I8, 0, 0, True, False, "relu6"),
+    (4, 40, 14, 14, 72, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, I8, 3, 0, True, True, "relu6"),     # 1x1 on 14x14: pixel/channel swap + GEMM
+    (8, 200, 6, 6, 130, 1, (1, 1), (0, 0, 0, 0), (1, 1), U8, U8, 128, 4, True, True, None),      # 1x1, 200 channels (4 K groups, last partial)
 ]
 
 
@@ -184,7 +186,7 @@ def test_qlinearconv_depthwise3x3(zb, ctx, oracle, case):
 
 
 # stride-1 cases run the implicit-GEMM kernel (one launch), the others im2col + GEMM (two launches)
-TC_QCONV_LAUNCHES = [1, 2, 2, 1, 2]
+TC_QCONV_LAUNCHES = [1, 2, 2, 1, 2, 2, 2]
 
 IMPLICIT_QCONV = [
     # N C H W M k stride pads dil xdt ydt xzp yzp per_channel bias act

@@ -58,6 +58,54 @@ __global__ void im2col_blocked_kernel(const Im2colArgs p) {
     }
 }
 
+// 1x1 convolutions (stride 1, no padding) with H*W % 4 == 0: the im2col matrix is the NCHW tensor with
+// pixels and channels swapped.  A CTA turns 64 channels x 128 consecutive pixels (image after image) into
+// four [128 rows][16] chunks of the GEMM-blocked layout: coalesced 4-byte loads along the pixels into
+// shared memory, 4x4 byte transposes with prmt, 16-byte stores.  Rows beyond the last pixel and
+// channels beyond C are zero.
+struct PwBlockArgs {
+    const uint8_t* x; uint8_t* a;
+    int C, HW, M, K16;        // M = N * HW rows
+};
+
+__global__ void __launch_bounds__(256) pointwise_blocked_kernel(const PwBlockArgs p) {
+    __shared__ uint32_t tile[64][33];                 // [channel][32 words of 4 pixels], padded against bank conflicts
+    const int tid = threadIdx.x, lane = tid & 31, wrp = tid >> 5;
+    const int mt = blockIdx.x, kg = blockIdx.y;       // row tile, group of 4 K chunks (64 channels)
+    const int m4 = mt * 128 + lane * 4;               // first of this lane's 4 rows; never straddles an image (H*W % 4 == 0)
+    const int n = m4 / p.HW, pix = m4 - n * p.HW;
+    const bool row_ok = m4 < p.M;
+    const uint8_t* src = p.x + ((size_t)n * p.C) * p.HW + pix;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int cl = wrp * 8 + i, c = kg * 64 + cl;
+        tile[cl][lane] = (row_ok && c < p.C) ? __ldg(reinterpret_cast<const uint32_t*>(src + (size_t)c * p.HW)) : 0u;
+    }
+    __syncthreads();
+    // thread = (K chunk q of 4, word w of 32): 16 channels x 4 pixels -> four 16-byte chunks; two rounds cover 4 x 32
+    const int q = tid >> 6, w = (tid & 63) >> 1, half = tid & 1;     // half: which 2 of the word's 4 pixels this thread stores
+    uint32_t wv[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) wv[j] = tile[q * 16 + j][w];
+    uint32_t o[4][4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const uint32_t t0 = __byte_perm(wv[4 * g], wv[4 * g + 1], 0x5140), t1 = __byte_perm(wv[4 * g + 2], wv[4 * g + 3], 0x5140);
+        const uint32_t t2 = __byte_perm(wv[4 * g], wv[4 * g + 1], 0x7362), t3 = __byte_perm(wv[4 * g + 2], wv[4 * g + 3], 0x7362);
+        o[g][0] = __byte_perm(t0, t1, 0x5410); o[g][1] = __byte_perm(t0, t1, 0x7632);
+        o[g][2] = __byte_perm(t2, t3, 0x5410); o[g][3] = __byte_perm(t2, t3, 0x7632);
+    }
+    const int k16 = kg * 4 + q;
+    if (k16 < p.K16) {
+        uint4* dst = reinterpret_cast<uint4*>(p.a) + ((size_t)mt * p.K16 + k16) * 128 + w * 4;
+#pragma unroll
+        for (int px = 0; px < 2; ++px) {
+            const int r = half * 2 + px;
+            dst[r] = make_uint4(o[0][r], o[1][r], o[2][r], o[3][r]);
+        }
+    }
+}
+
 // Host-side preparation of one convolution / matrix product for the tensor-core path.
 struct QGemmPrep {
     int NT = 0, N_pad = 0, K = 0, K16 = 0;
@@ -110,9 +158,18 @@ inline int32_t run_qconv_tc(zant_ctx* ctx, const ConvGeom& g, const void* x, boo
     if (M <= 0 || M > 0x7fffff00LL) return fail(ZANT_E_TOO_LARGE, "too many output positions for the tensor-core path");
     Im2colArgs ia{};
     ia.x = (const uint8_t*)x; ia.a = a_blk; ia.g = g; ia.K = p.K; ia.K16 = p.K16; ia.M = (int)M; ia.pad_value = x_zp;
-    const size_t chunks = (size_t)((M + 127) / 128) * p.K16 * 128;
-    im2col_blocked_kernel<<<grid_for(chunks, 256, ctx->sm_count, 16), 256, 0, ctx->stream>>>(ia);
-    ZB_TRY(check_launch(ctx, "im2col_blocked_kernel"));
+    const bool pointwise = g.KH == 1 && g.KW == 1 && g.sh == 1 && g.sw == 1 && g.pt == 0 && g.pl == 0 && g.pb == 0 && g.pr == 0;
+    const int m_tiles = (int)((M + 127) / 128);
+    if (pointwise && (g.H * g.W) % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 3u) == 0 && m_tiles <= 0x7fffffff / 128 && (p.K16 + 3) / 4 <= 65535) {
+        PwBlockArgs pa{};
+        pa.x = (const uint8_t*)x; pa.a = a_blk; pa.C = g.C; pa.HW = g.H * g.W; pa.M = (int)M; pa.K16 = p.K16;
+        pointwise_blocked_kernel<<<dim3((unsigned)m_tiles, (unsigned)((p.K16 + 3) / 4)), 256, 0, ctx->stream>>>(pa);
+        ZB_TRY(check_launch(ctx, "pointwise_blocked_kernel"));
+    } else {
+        const size_t chunks = (size_t)m_tiles * p.K16 * 128;
+        im2col_blocked_kernel<<<grid_for(chunks, 256, ctx->sm_count, 16), 256, 0, ctx->stream>>>(ia);
+        ZB_TRY(check_launch(ctx, "im2col_blocked_kernel"));
+    }
     TcGemmArgs k{};
     k.a = (const int8_t*)a_blk; k.w = w_blk_dev; k.mult = mult_dev; k.bias = bias_dev; k.y = (int8_t*)y;
     k.M = (int)M; k.N = p.N_pad; k.K16 = p.K16; k.y_scale = rq.y_scale; k.y_zp = rq.y_zp; k.act = rq.act; k.status = ctx->status_word;
