@@ -150,6 +150,9 @@ TC_QCONV = [
     (4, 3, 32, 32, 32, 3, (2, 2), (1, 1, 1, 1), (1, 1), U8, I8, 0, 0, True, False, "relu6"),
     (4, 40, 14, 14, 72, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, I8, 3, 0, True, True, "relu6"),     # 1x1 on 14x14: pixel/channel swap + GEMM
     (8, 200, 6, 6, 130, 1, (1, 1), (0, 0, 0, 0), (1, 1), U8, U8, 128, 4, True, True, None),      # 1x1, 200 channels (4 K groups, last partial)
+    (8, 64, 14, 14, 96, 3, (2, 2), (1, 1, 1, 1), (1, 1), I8, I8, 0, 0, True, True, "relu"),      # sweep case 3b in small: tap-major im2col
+    (6, 80, 13, 11, 40, 3, (1, 2), (2, 0, 1, 1), (2, 1), U8, I8, 77, -5, True, False, None),     # tap-major, 80 channels, odd geometry
+    (3, 16, 30, 30, 24, 5, (3, 3), (2, 2, 2, 2), (1, 1), I8, U8, -9, 30, False, True, "relu6"),  # tap-major, 25 taps of 16 channels
 ]
 
 
@@ -186,7 +189,7 @@ def test_qlinearconv_depthwise3x3(zb, ctx, oracle, case):
 
 
 # stride-1 cases run the implicit-GEMM kernel (one launch), the others im2col + GEMM (two launches)
-TC_QCONV_LAUNCHES = [1, 2, 2, 1, 2, 2, 2]
+TC_QCONV_LAUNCHES = [1, 2, 2, 1, 2, 2, 2, 2, 2, 2]
 
 IMPLICIT_QCONV = [
     # N C H W M k stride pads dil xdt ydt xzp yzp per_channel bias act

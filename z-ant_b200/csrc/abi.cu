@@ -586,7 +586,7 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
     if (qconv_tc_eligible(g, wz_zero) && host_consts) {
         // tensor-core path: im2col into the GEMM-blocked layout, tcgen05 GEMM, NCHW requantised store
         QGemmPrep prep;
-        qgemm_prepare(w, g.M, g.Cg * g.KH * g.KW, mult.data(), bias, x_zp, prep);
+        qconv_gemm_prepare(g, w, mult.data(), bias, x_zp, prep);
         Stager s(ctx);
         const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
         const int iw = s.in(prep.w_blk.data(), prep.w_blk.size()), im = s.in(prep.mult.data(), prep.mult.size() * 4);

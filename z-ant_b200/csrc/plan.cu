@@ -706,7 +706,7 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
             if (qconv_tc_eligible(g, wz_zero) && (b < 0 || T(b).is_const)) {
                 // tensor-core path: weights re-blocked once here, im2col + tcgen05 GEMM per run
                 auto prep = std::make_shared<QGemmPrep>();
-                qgemm_prepare((const int8_t*)T(w).host.data(), g.M, g.Cg * g.KH * g.KW, mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, *prep);
+                qconv_gemm_prepare(g, (const int8_t*)T(w).host.data(), mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, *prep);
                 const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size()), am = pl->add_aux(prep->mult.data(), prep->mult.size() * 4);
                 const int ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
                 const int sa = pl->shared_im2col_scratch(qgemm_a_bytes((size_t)g.N * g.OH * g.OW, *prep));

@@ -106,12 +106,75 @@ __global__ void __launch_bounds__(256) pointwise_blocked_kernel(const PwBlockArg
     }
 }
 
+// Convolutions whose channel count is a multiple of 16 use the K order (tap, channel) instead of the
+// weight tensor's (channel, tap): a 16-byte K chunk is then 16 channels of ONE tap, and the im2col
+// matrix is built like the 1x1 case, tap by tap.  A CTA takes one tap, 64 channels and 128 output
+// pixels: byte loads that are contiguous (or stride-s) along the pixels, out-of-image taps replaced by
+// the input zero point, into shared memory, then the same 4x4 byte transposes and 16-byte stores.
+struct TapMajorArgs {
+    const uint8_t* x; uint8_t* a;
+    ConvGeom g;
+    int M, K16, cgroups;      // rows, K chunks per row, groups of 64 channels
+    int pad_value;
+};
+
+__global__ void __launch_bounds__(256) im2col_tapmajor_kernel(const TapMajorArgs p) {
+    __shared__ uint32_t tile[64][33];
+    uint8_t (*tile8)[132] = reinterpret_cast<uint8_t (*)[132]>(&tile[0][0]);   // the same rows, byte view (33 words = 132 bytes)
+    const ConvGeom& g = p.g;
+    const int tid = threadIdx.x;
+    const int mt = blockIdx.x;
+    const int tap = blockIdx.y / p.cgroups, kg = blockIdx.y - tap * p.cgroups;
+    const int kh = tap / g.KW, kw = tap - kh * g.KW;
+    {
+        const int r = tid & 127, half = tid >> 7;
+        const int m = mt * 128 + r;
+        const int ohw = g.OH * g.OW;
+        const int n = m / ohw, pos = m - n * ohw;
+        const int oh = pos / g.OW, ow = pos - oh * g.OW;
+        const int ih = oh * g.sh - g.pt + kh * g.dh, iw = ow * g.sw - g.pl + kw * g.dw;
+        const bool ok = m < p.M && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W;
+        const size_t plane = (size_t)g.H * g.W;
+        const int c0 = kg * 64 + half * 32;
+        const uint8_t* src = p.x + ((size_t)n * g.C + c0) * plane + (size_t)(ok ? ih : 0) * g.W + (ok ? iw : 0);
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i) {
+            uint8_t v = (uint8_t)p.pad_value;
+            if (ok && c0 + i < g.C) v = __ldg(src + (size_t)i * plane);
+            tile8[half * 32 + i][r] = v;
+        }
+    }
+    __syncthreads();
+    const int q = tid >> 6, w = (tid & 63) >> 1, half = tid & 1;
+    uint32_t wv[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) wv[j] = tile[q * 16 + j][w];
+    uint32_t o[4][4];
+#pragma unroll
+    for (int gq = 0; gq < 4; ++gq) {
+        const uint32_t t0 = __byte_perm(wv[4 * gq], wv[4 * gq + 1], 0x5140), t1 = __byte_perm(wv[4 * gq + 2], wv[4 * gq + 3], 0x5140);
+        const uint32_t t2 = __byte_perm(wv[4 * gq], wv[4 * gq + 1], 0x7362), t3 = __byte_perm(wv[4 * gq + 2], wv[4 * gq + 3], 0x7362);
+        o[gq][0] = __byte_perm(t0, t1, 0x5410); o[gq][1] = __byte_perm(t0, t1, 0x7632);
+        o[gq][2] = __byte_perm(t2, t3, 0x5410); o[gq][3] = __byte_perm(t2, t3, 0x7632);
+    }
+    if (kg * 64 + q * 16 < g.C) {
+        const int k16 = tap * (g.C / 16) + kg * 4 + q;
+        uint4* dst = reinterpret_cast<uint4*>(p.a) + ((size_t)mt * p.K16 + k16) * 128 + w * 4;
+#pragma unroll
+        for (int px = 0; px < 2; ++px) {
+            const int r = half * 2 + px;
+            dst[r] = make_uint4(o[0][r], o[1][r], o[2][r], o[3][r]);
+        }
+    }
+}
+
 // Host-side preparation of one convolution / matrix product for the tensor-core path.
 struct QGemmPrep {
     int NT = 0, N_pad = 0, K = 0, K16 = 0;
     std::vector<int8_t> w_blk;     // [N_pad/NT][K16][NT][16]
     std::vector<float> mult;       // [N_pad]
     std::vector<int32_t> bias;     // [N_pad], includes -x_zp * sum(w)
+    bool tap_major = false;        // K order (tap, channel) instead of the weight tensor's (channel, tap)
 };
 
 // w: [n_out][K] int8 row-major (a convolution's [M][C][KH][KW] weight is exactly that).
@@ -134,6 +197,20 @@ inline void qgemm_prepare(const int8_t* w, int n_out, int K, const float* mult, 
         p.mult[n] = mult[n];
         p.bias[n] = (bias ? bias[n] : 0) - x_zp * sum;
     }
+}
+
+// Convolution weights [M][C][KH][KW]: channel counts that are multiples of 16 (and more than one tap)
+// get the (tap, channel) K order that im2col_tapmajor_kernel produces; everything else keeps the
+// tensor's own order.
+inline void qconv_gemm_prepare(const ConvGeom& g, const int8_t* w, const float* mult, const int32_t* bias, int x_zp, QGemmPrep& p) {
+    const int taps = g.KH * g.KW, C = g.Cg, K = C * taps;
+    if (taps == 1 || C % 16 != 0) { qgemm_prepare(w, g.M, K, mult, bias, x_zp, p); return; }
+    std::vector<int8_t> wt((size_t)g.M * K);
+    for (int m = 0; m < g.M; ++m)
+        for (int c = 0; c < C; ++c)
+            for (int t = 0; t < taps; ++t) wt[(size_t)m * K + (size_t)t * C + c] = w[((size_t)m * C + c) * taps + t];
+    qgemm_prepare(wt.data(), g.M, K, mult, bias, x_zp, p);
+    p.tap_major = true;
 }
 
 inline size_t qgemm_a_bytes(size_t rows, const QGemmPrep& p) { return (rows + 127) / 128 * 128 * (size_t)p.K16 * 16; }
@@ -165,7 +242,13 @@ inline int32_t run_qconv_tc(zant_ctx* ctx, const ConvGeom& g, const void* x, boo
         pa.x = (const uint8_t*)x; pa.a = a_blk; pa.C = g.C; pa.HW = g.H * g.W; pa.M = (int)M; pa.K16 = p.K16;
         pointwise_blocked_kernel<<<dim3((unsigned)m_tiles, (unsigned)((p.K16 + 3) / 4)), 256, 0, ctx->stream>>>(pa);
         ZB_TRY(check_launch(ctx, "pointwise_blocked_kernel"));
+    } else if (p.tap_major && (long long)g.KH * g.KW * ((g.C + 63) / 64) <= 65535) {
+        TapMajorArgs ta{};
+        ta.x = (const uint8_t*)x; ta.a = a_blk; ta.g = g; ta.M = (int)M; ta.K16 = p.K16; ta.cgroups = (g.C + 63) / 64; ta.pad_value = x_zp;
+        im2col_tapmajor_kernel<<<dim3((unsigned)m_tiles, (unsigned)(g.KH * g.KW * ta.cgroups)), 256, 0, ctx->stream>>>(ta);
+        ZB_TRY(check_launch(ctx, "im2col_tapmajor_kernel"));
     } else {
+        if (p.tap_major) return fail(ZANT_E_TOO_LARGE, "too many taps x channel groups for the tap-major gather");
         const size_t chunks = (size_t)m_tiles * p.K16 * 128;
         im2col_blocked_kernel<<<grid_for(chunks, 256, ctx->sm_count, 16), 256, 0, ctx->stream>>>(ia);
         ZB_TRY(check_launch(ctx, "im2col_blocked_kernel"));
