@@ -170,6 +170,12 @@ DW_QCONV = [
     (2, 36, 14, 14, 2, I8, I8, -2, 0, True, True, "relu6"),       # stride 2 onto 7x7
     (1, 3, 5, 9, 1, I8, U8, 0, 17, False, False, None),           # odd sizes
     (2, 8, 6, 10, 2, U8, I8, 9, 0, True, False, "relu"),          # stride 2, 10 -> 5 columns
+    (3, 5, 1, 8, 1, I8, I8, 4, 0, True, True, None),              # 8 columns per lane: one row
+    (2, 6, 2, 16, 1, U8, U8, 11, 2, True, True, "relu"),          # two rows
+    (2, 7, 3, 24, 1, I8, I8, 0, 0, False, True, None),            # three rows
+    (1, 9, 4, 40, 1, I8, I8, -1, 0, True, False, "relu6"),        # four rows, 5 lanes of 8 per plane
+    (2, 3, 5, 64, 1, I8, U8, 0, 9, True, True, None),             # five rows
+    (1, 2, 9, 128, 1, U8, I8, 200, 0, True, True, None),          # widest plane the kernel takes
 ]
 
 

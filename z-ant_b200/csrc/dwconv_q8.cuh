@@ -208,6 +208,82 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
     }
 }
 
+// Stride 1 on planes whose rows are whole 8-byte groups (W % 8 == 0): a lane owns 8 columns (one 8-byte
+// load per row), which halves the per-output share of loads, shuffles and address arithmetic; the padding
+// rows and the first output row are peeled off so that the row loop carries no range checks.
+template <bool XU8, bool LEAN>
+__global__ void __launch_bounds__(256) qdwconv3x3_s1w8_kernel(const QDwArgs p) {
+    const int lane = threadIdx.x & 31;
+    const int LW = 1 << p.log2LW;                            // lanes per plane, each 8 columns
+    const int ppw = 32 >> p.log2LW;
+    const int sub = lane >> p.log2LW, col = lane & (LW - 1);
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int groups = (p.planes + ppw - 1) / ppw;
+    const int wu2 = p.W >> 3;                                // 8-byte groups per row
+    const bool col_ok = col < wu2;
+    const bool first_col = col == 0, last_col = col == wu2 - 1;
+    const uint2 padrow = make_uint2(p.pad_word, p.pad_word);
+    for (int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; g < groups; g += warps) {
+        const int plane = g * ppw + sub;
+        const bool live = plane < p.planes && col_ok;
+        const int c = live ? plane % p.C : 0;
+        const uint32_t k0 = __ldg(p.wrow + c * 3), k1 = __ldg(p.wrow + c * 3 + 1), k2 = __ldg(p.wrow + c * 3 + 2);
+        const float m = __ldg(p.mult + c);
+        const int b = __ldg(p.bias + c);
+        const uint2* xr = reinterpret_cast<const uint2*>(p.x + (size_t)(live ? plane : 0) * p.H * p.W) + (live ? col : 0);
+        uint2* yr = reinterpret_cast<uint2*>(p.y + (size_t)(live ? plane : 0) * p.H * p.W) + (live ? col : 0);
+        int A[8], B[8], C[8];                                // three output rows in flight
+#pragma unroll
+        for (int i = 0; i < 8; ++i) A[i] = B[i] = C[i] = b;
+        // adds input row M to the output rows above (filter row 2), at (1) and below (0) it
+        auto step = [&](const uint2 M, int* up, int* at, int* dn) {
+            uint32_t L = __shfl_up_sync(0xffffffffu, M.y, 1), R = __shfl_down_sync(0xffffffffu, M.x, 1);
+            if (first_col) L = p.pad_word;
+            if (last_col) R = p.pad_word;
+            const uint32_t w[8] = {__byte_perm(L, M.x, 0x6543), M.x, __byte_perm(M.x, M.y, 0x4321), __byte_perm(M.x, M.y, 0x5432),
+                                   __byte_perm(M.x, M.y, 0x6543), M.y, __byte_perm(M.y, R, 0x4321), __byte_perm(M.y, R, 0x5432)};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (up) up[i] = dw_dp4a<XU8>(w[i], k2, up[i]);
+                if (at) at[i] = dw_dp4a<XU8>(w[i], k1, at[i]);
+                if (dn) dn[i] = dw_dp4a<XU8>(w[i], k0, dn[i]);
+            }
+        };
+        auto emit = [&](int* row) {                          // requantise, store, and recycle the slot
+            const uint2 pk = make_uint2(dw_requant4<LEAN>(row, m, p), dw_requant4<LEAN>(row + 4, m, p));
+            if (live) *yr = pk;
+            yr += wu2;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) row[i] = b;
+        };
+        auto load = [&]() -> uint2 { const uint2 v = live ? __ldg(xr) : padrow; xr += wu2; return v; };
+        // rows -1 (padding) and 0: nothing to emit yet.  A = output row 0, B = row 1, C = row 2.
+        step(padrow, nullptr, nullptr, A);
+        step(load(), nullptr, A, B);
+        int ih = 1;
+        for (; ih + 2 < p.H; ih += 3) {                      // three input rows per trip: the slots return to their roles
+            const uint2 r0 = load(), r1 = load(), r2 = load();
+            step(r0, A, B, C); emit(A);                      // A becomes output row ih + 2
+            step(r1, B, C, A); emit(B);
+            step(r2, C, A, B); emit(C);
+        }
+        // up to two more input rows, then the padding row below the image
+        int left = p.H - ih;                                 // 0, 1 or 2 rows (H >= 1)
+        if (left == 2) {
+            const uint2 r0 = load(), r1 = load();
+            step(r0, A, B, C); emit(A);
+            step(r1, B, C, nullptr); emit(B);
+            step(padrow, C, nullptr, nullptr); emit(C);
+        } else if (left == 1) {
+            const uint2 r0 = load();
+            step(r0, A, B, nullptr); emit(A);
+            step(padrow, B, nullptr, nullptr); emit(B);
+        } else if (p.H >= 1) {
+            step(padrow, A, nullptr, nullptr); emit(A);
+        }
+    }
+}
+
 // Shapes the kernel covers: 3x3, group == channels == filters, pads 1 on every side, dilation 1,
 // stride 1 or 2 on both axes (even sizes for stride 2), at most 128 output columns, weight zero points 0.
 inline bool qdwconv_eligible(const ConvGeom& g, bool w_zp_all_zero) {
@@ -268,6 +344,19 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
     const long long groups = ((long long)a.planes + ppw - 1) / ppw;
     const int grid = (int)std::min<long long>((groups + 7) / 8, (long long)ctx->sm_count * 16);
     if (grid == 0) return ZANT_OK;
+    if (g.sh == 1 && g.W % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 7u) == 0 && (reinterpret_cast<uintptr_t>(y) & 7u) == 0) {
+        // 8 columns per lane
+        const int cols8 = g.W / 8;
+        for (a.log2LW = 0; (1 << a.log2LW) < cols8; ++a.log2LW) {}
+        if (a.log2LW <= 5) {
+            const int ppw8 = 32 >> a.log2LW;
+            const long long groups8 = ((long long)a.planes + ppw8 - 1) / ppw8;
+            const int grid8 = (int)std::min<long long>((groups8 + 7) / 8, (long long)ctx->sm_count * 16);
+            if (x_u8) { if (lean) qdwconv3x3_s1w8_kernel<true, true><<<grid8, 256, 0, ctx->stream>>>(a); else qdwconv3x3_s1w8_kernel<true, false><<<grid8, 256, 0, ctx->stream>>>(a); }
+            else { if (lean) qdwconv3x3_s1w8_kernel<false, true><<<grid8, 256, 0, ctx->stream>>>(a); else qdwconv3x3_s1w8_kernel<false, false><<<grid8, 256, 0, ctx->stream>>>(a); }
+            return check_launch(ctx, "qdwconv3x3_s1w8_kernel");
+        }
+    }
     const bool aligned = g.W % 4 == 0 && g.OW % 4 == 0;
     if (g.sh == 1) return aligned ? qdwconv_launch_s<1, true>(ctx, a, grid, x_u8, lean) : qdwconv_launch_s<1, false>(ctx, a, grid, x_u8, lean);
     return aligned ? qdwconv_launch_s<2, true>(ctx, a, grid, x_u8, lean) : qdwconv_launch_s<2, false>(ctx, a, grid, x_u8, lean);

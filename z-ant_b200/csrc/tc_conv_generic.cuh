@@ -178,8 +178,16 @@ struct QGemmPrep {
 };
 
 // w: [n_out][K] int8 row-major (a convolution's [M][C][KH][KW] weight is exactly that).
-inline void qgemm_prepare(const int8_t* w, int n_out, int K, const float* mult, const int32_t* bias, int x_zp, QGemmPrep& p) {
+// `rows` (when known) lets wide outputs pick the tile width that wastes the least of the last wave of
+// 148 persistent CTAs: 256-wide tiles halve the number of tiles but a partly filled wave costs a full one.
+inline void qgemm_prepare(const int8_t* w, int n_out, int K, const float* mult, const int32_t* bias, int x_zp, QGemmPrep& p, long long rows = 0) {
     p.NT = n_out <= 64 ? 64 : (n_out <= 128 ? 128 : 256);
+    if (p.NT == 256 && rows > 0) {
+        const long long mt = (rows + 127) / 128;
+        const long long t256 = mt * ((n_out + 255) / 256), t128 = mt * ((n_out + 127) / 128);
+        const long long c256 = (t256 + 147) / 148 * 256, c128 = (t128 + 147) / 148 * 128;
+        if (c128 < c256) p.NT = 128;
+    }
     p.N_pad = (n_out + p.NT - 1) / p.NT * p.NT;
     p.K = K;
     p.K16 = (K + 63) / 64 * 4;
@@ -204,12 +212,13 @@ inline void qgemm_prepare(const int8_t* w, int n_out, int K, const float* mult, 
 // tensor's own order.
 inline void qconv_gemm_prepare(const ConvGeom& g, const int8_t* w, const float* mult, const int32_t* bias, int x_zp, QGemmPrep& p) {
     const int taps = g.KH * g.KW, C = g.Cg, K = C * taps;
-    if (taps == 1 || C % 16 != 0) { qgemm_prepare(w, g.M, K, mult, bias, x_zp, p); return; }
+    const long long rows = (long long)g.N * g.OH * g.OW;
+    if (taps == 1 || C % 16 != 0) { qgemm_prepare(w, g.M, K, mult, bias, x_zp, p, rows); return; }
     std::vector<int8_t> wt((size_t)g.M * K);
     for (int m = 0; m < g.M; ++m)
         for (int c = 0; c < C; ++c)
             for (int t = 0; t < taps; ++t) wt[(size_t)m * K + (size_t)t * C + c] = w[((size_t)m * C + c) * taps + t];
-    qgemm_prepare(wt.data(), g.M, K, mult, bias, x_zp, p);
+    qgemm_prepare(wt.data(), g.M, K, mult, bias, x_zp, p, rows);
     p.tap_major = true;
 }
 
