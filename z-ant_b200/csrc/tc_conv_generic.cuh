@@ -190,7 +190,7 @@ inline void qgemm_prepare(const int8_t* w, int n_out, int K, const float* mult, 
     }
     p.N_pad = (n_out + p.NT - 1) / p.NT * p.NT;
     p.K = K;
-    p.K16 = (K + 63) / 64 * 4;
+    p.K16 = K <= 32 ? 2 : (K + 63) / 64 * 4;      // a stage holds 4 chunks of K (2 when K fits 32: first layers with 3 channels)
     p.w_blk.assign((size_t)p.N_pad * p.K16 * 16, 0);
     p.mult.assign(p.N_pad, 1.0f);
     p.bias.assign(p.N_pad, 0);
@@ -224,16 +224,22 @@ inline void qconv_gemm_prepare(const ConvGeom& g, const int8_t* w, const float* 
 
 inline size_t qgemm_a_bytes(size_t rows, const QGemmPrep& p) { return (rows + 127) / 128 * 128 * (size_t)p.K16 * 16; }
 
-template <int NT, int MODE>
-inline int32_t launch_tc_gemm(zant_ctx* ctx, const TcGemmArgs& k, int tiles) {
-    using Cfg = TcGemmCfg<NT, 4, 8>;
+template <int NT, int KC, int MODE>
+inline int32_t launch_tc_gemm_kc(zant_ctx* ctx, const TcGemmArgs& k, int tiles) {
+    using Cfg = TcGemmCfg<NT, KC, 8>;
     static bool attr_set = false;
     if (!attr_set) {
-        ZB_CUDA(cudaFuncSetAttribute(tc_gemm_i8_kernel<NT, 4, 8, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        ZB_CUDA(cudaFuncSetAttribute(tc_gemm_i8_kernel<NT, KC, 8, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set = true;
     }
-    tc_gemm_i8_kernel<NT, 4, 8, MODE><<<std::min(tiles, ctx->sm_count), Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
+    tc_gemm_i8_kernel<NT, KC, 8, MODE><<<std::min(tiles, ctx->sm_count), Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
     return check_launch(ctx, "tc_gemm_i8_kernel");
+}
+
+template <int NT, int MODE>
+inline int32_t launch_tc_gemm(zant_ctx* ctx, const TcGemmArgs& k, int tiles) {
+    if (k.K16 == 2) return launch_tc_gemm_kc<NT, 2, MODE>(ctx, k, tiles);
+    return launch_tc_gemm_kc<NT, 4, MODE>(ctx, k, tiles);
 }
 
 // im2col + GEMM on device buffers.  `a_blk` is scratch of qgemm_a_bytes(N*OH*OW) bytes.
