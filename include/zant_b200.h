@@ -287,6 +287,20 @@ int32_t zant_b200_gather(zant_ctx* ctx, int32_t dtype, const void* x, const size
                          const size_t* indices, const size_t* idx_shape, size_t idx_rank, int64_t axis,
                          void* y, const size_t* y_shape, size_t y_rank);
 
+/* tensMath.get_unsqueeze_output_shape / unsqueeze_lean (lib_shape_math.zig:1933-2030): inserts
+ * dimensions of size 1 at `axes` (positions in the OUTPUT; negative values count from its end).  An axis
+ * outside the output rank is AxisOutOfBounds, a repeated one DuplicateAxis.  `out_shape` receives
+ * x_rank + n_axes entries.  The data is copied unchanged. */
+int32_t zant_b200_unsqueeze_output_shape(const size_t* x_shape, size_t x_rank, const int64_t* axes, size_t n_axes, size_t* out_shape);
+int32_t zant_b200_unsqueeze(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                            const int64_t* axes, size_t n_axes, void* y, const size_t* y_shape, size_t y_rank);
+
+/* tensMath.shape_onnx / lean_shape_onnx / get_shape_output_shape (lib_shape_math.zig:1836-1931): the
+ * dimensions [start, end) of a shape as int64 values, written to the HOST array `out` (x_rank entries of
+ * room); no device work.  has_start / has_end = 0 stand for the absent ONNX attributes. */
+int32_t zant_b200_shape_onnx(const size_t* x_shape, size_t x_rank, int32_t has_start, int64_t start, int32_t has_end, int64_t end,
+                             int64_t* out, size_t* out_len);
+
 /* tensMath.sigmoid_lean (lib_activation_function_math.zig:107-122): 1 / (1 + exp(-x)). */
 int32_t zant_b200_sigmoid_f32(zant_ctx* ctx, const float* x, float* y, size_t n);
 /* tensMath.softmax_lean = lean_softmax (lib_activation_function_math.zig:154-187): x is [rows][cols];

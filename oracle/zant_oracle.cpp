@@ -681,6 +681,42 @@ int32_t zo_gather(usize esz, const void* x, const usize* xs, usize xr, const usi
     return ZANT_OK;
 }
 
+// get_unsqueeze_output_shape, lib_shape_math.zig:1983-2030: axes refer to the OUTPUT rank; negative axes
+// count from its end; out of range -> AxisOutOfBounds, repeated -> DuplicateAxis.
+int32_t zo_unsqueeze_output_shape(const usize* xs, usize xr, const int64_t* axes, usize na, usize* out) {
+    const usize orank = xr + na;
+    std::vector<bool> is_new(orank, false);
+    std::vector<usize> seen;
+    for (usize i = 0; i < na; ++i) {
+        int64_t a = axes[i];
+        if (a < 0) a += (int64_t)orank;
+        if (a < 0 || a >= (int64_t)orank) return ZANT_E_AXIS_OUT_OF_BOUNDS;
+        for (usize j : seen) if (j == (usize)a) return ZANT_E_DUPLICATE_AXIS;
+        seen.push_back((usize)a);
+        is_new[(usize)a] = true;
+    }
+    usize k = 0;
+    for (usize i = 0; i < orank; ++i) out[i] = is_new[i] ? 1 : xs[k++];
+    return ZANT_OK;
+}
+
+// get_shape_output_shape (:1903-1931) gives the length; lean_shape_onnx (:1869-1901) the values.  The
+// latter clamps the start to rank - 1 (the former to rank); both are restated as they are.
+int32_t zo_shape_onnx(const usize* xs, usize xr, int32_t has_start, int64_t start, int32_t has_end, int64_t end, int64_t* out, usize* out_len) {
+    if (xr == 0) { *out_len = 0; return ZANT_OK; }
+    const int64_t r = (int64_t)xr;
+    int64_t s0 = has_start ? start : 0; if (s0 < 0) s0 += r;
+    int64_t e0 = has_end ? end : r; if (e0 < 0) e0 += r;
+    const int64_t s_len = std::max<int64_t>(0, std::min(s0, r));
+    const int64_t e_len = std::max(s_len, std::min(e0, r));
+    *out_len = (usize)std::max<int64_t>(0, e_len - s_len);
+    const int64_t s_val = std::max<int64_t>(0, std::min(s0, r - 1));
+    const int64_t e_val = std::max(s_val, std::min(e0, r));
+    if ((usize)std::max<int64_t>(0, e_val - s_val) != *out_len) return ZANT_E_MISMATCHED_SHAPE;   // the reference's ShapeMismatch
+    for (usize i = 0; i < *out_len; ++i) out[i] = (int64_t)xs[(usize)s_val + i];
+    return ZANT_OK;
+}
+
 // ---------------------------------------------------------------------------------------
 // Element-wise
 // ---------------------------------------------------------------------------------------

@@ -403,6 +403,28 @@ def gather(x, indices, axis):
     return y
 
 
+def get_unsqueeze_output_shape(x_shape, axes):
+    xs, r = _sz(x_shape)
+    out = (C.c_size_t * max(r + len(axes), 1))()
+    _check(lib().zo_unsqueeze_output_shape(xs, C.c_size_t(r), _i64(axes), C.c_size_t(len(axes)), out))
+    return [int(out[i]) for i in range(r + len(axes))]
+
+
+def unsqueeze(x, axes):
+    x = np.ascontiguousarray(x)
+    return x.reshape(get_unsqueeze_output_shape(x.shape, axes)).copy()
+
+
+def shape_onnx(x_shape, start=None, end=None):
+    """TensMath.shape_onnx on a tensor of shape `x_shape`: int64 values of dimensions [start, end)."""
+    xs, r = _sz(x_shape)
+    out = (C.c_int64 * max(r, 1))()
+    n = C.c_size_t(0)
+    _check(lib().zo_shape_onnx(xs, C.c_size_t(r), C.c_int32(start is not None), C.c_int64(start or 0), C.c_int32(end is not None),
+                               C.c_int64(end or 0), out, C.byref(n)))
+    return np.array([out[i] for i in range(n.value)], np.int64)
+
+
 def resize(x, mode, scales=None, sizes=None, coord_mode="half_pixel"):
     x = np.ascontiguousarray(x)
     oshape = get_resize_output_shape(x.shape, scales, sizes)

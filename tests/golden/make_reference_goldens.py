@@ -237,6 +237,28 @@ add(op="gather_error", cite=S + ":1918-1939", x_shape=[2, 2], idx_shape=[1], idx
 add(op="gather_error", cite=S + ":1027-1031", x_shape=[3, 3], idx_shape=[2], idx=[0, 2], axis=5, error="InvalidAxis",
     note="the Zig test passes an axis beyond the rank")
 
+# ----------------------------------------------------------------------------- unsqueeze / shape
+add(op="unsqueeze_shape", cite=S + ":2016-2048", x_shape=[2, 3], axes=[1], y=[2, 1, 3])
+add(op="unsqueeze_shape", cite=S + ":2050-2083", x_shape=[2, 2], axes=[0, 2], y=[1, 2, 1, 2])
+add(op="unsqueeze_shape", cite=S + ":2085-2117", x_shape=[2, 3], axes=[-1], y=[2, 3, 1])
+add(op="unsqueeze_shape", cite=S + ":2119-2146", x_shape=[1, 1], axes=[0, 2, 3], y=[1, 1, 1, 1, 1],
+    note="the Zig test checks the rank (5); every dimension is 1")
+add(op="unsqueeze_error", cite=S + ":1644-1666", x_shape=[2, 3], axes=[3], error="AxisOutOfBounds")
+add(op="unsqueeze_error", cite=S + ":1668-1688", x_shape=[2, 3], axes=[0, 0], error="DuplicateAxis")
+add(op="unsqueeze_error", cite=S + ":2148-2180", x_shape=[2, 2], axes=[5], error="AxisOutOfBounds")
+add(op="unsqueeze_error", cite=S + ":2148-2180", x_shape=[2, 2], axes=[-5], error="AxisOutOfBounds")
+add(op="shape_onnx", cite=S + ":1324-1350", x_shape=[2, 2, 3], start=None, end=None, y=[2, 2, 3])
+add(op="shape_onnx", cite=S + ":1352-1376", x_shape=[2, 2, 3], start=1, end=3, y=[2, 3])
+add(op="shape_onnx", cite=S + ":1378-1402", x_shape=[2, 2, 3], start=-2, end=None, y=[2, 3])
+add(op="shape_onnx", cite=S + ":1404-1430", x_shape=[4], start=None, end=None, y=[4])
+add(op="shape_onnx", cite=S + ":1404-1430", x_shape=[4], start=-5, end=5, y=[4])
+add(op="shape_onnx_len", cite=S + ":1521-1606", x_shape=[2, 3, 4, 5], start=1, end=None, n=3)
+add(op="shape_onnx_len", cite=S + ":1521-1606", x_shape=[2, 3, 4, 5, 6], start=1, end=3, n=2)
+add(op="shape_onnx_len", cite=S + ":1521-1606", x_shape=[2, 3, 4, 5], start=-2, end=-1, n=1)
+add(op="shape_onnx_len", cite=S + ":1521-1606", x_shape=[2, 3, 4], start=2, end=1, n=0)
+add(op="shape_onnx_len", cite=S + ":1521-1606", x_shape=[], start=None, end=None, n=0)
+add(op="shape_onnx_len", cite=S + ":1521-1606", x_shape=[2, 3, 4], start=-5, end=5, n=3)
+
 if __name__ == "__main__":
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_goldens.json")
     with open(out, "w") as f:

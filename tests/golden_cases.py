@@ -92,6 +92,17 @@ def run_case(impl, c, err_type):
     elif op == "gather_error":
         idx = np.asarray(c["idx"], np.uint64).reshape(c["idx_shape"])
         raises(lambda: impl.gather(np.zeros(c["x_shape"], np.uint8), idx, c["axis"]))
+    elif op == "unsqueeze_shape":
+        assert list(impl.get_unsqueeze_output_shape(c["x_shape"], c["axes"])) == c["y"]
+        x = np.arange(int(np.prod(c["x_shape"])), dtype=np.float32).reshape(c["x_shape"])
+        y = impl.unsqueeze(x, c["axes"])
+        assert list(y.shape) == c["y"] and np.array_equal(y.reshape(-1), x.reshape(-1))
+    elif op == "unsqueeze_error":
+        raises(lambda: impl.get_unsqueeze_output_shape(c["x_shape"], c["axes"]))
+    elif op == "shape_onnx":
+        assert impl.shape_onnx(c["x_shape"], c["start"], c["end"]).tolist() == c["y"]
+    elif op == "shape_onnx_len":
+        assert len(impl.shape_onnx(c["x_shape"], c["start"], c["end"])) == c["n"]
     elif op == "sigmoid":
         y = impl.sigmoid(np.asarray(c["x"], np.float32))
         assert np.all(np.abs(y.astype(np.float64) - np.asarray(c["y"])) < c["atol"])

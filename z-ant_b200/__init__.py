@@ -458,6 +458,30 @@ class Context:
     def get_concatenate_output_shape(self, shapes, axis):
         return get_concatenate_output_shape(shapes, axis)
 
+    def get_unsqueeze_output_shape(self, x_shape, axes):
+        xs, r = _sz(x_shape)
+        out = (C.c_size_t * max(r + len(axes), 1))()
+        check(lib().zant_b200_unsqueeze_output_shape(xs, C.c_size_t(r), _i64(axes), C.c_size_t(len(axes)), out))
+        return [int(out[i]) for i in range(r + len(axes))]
+
+    def unsqueeze(self, x, axes, out=None):
+        x = _host(x)
+        sh = _shape(x)
+        oshape = self.get_unsqueeze_output_shape(sh, axes)
+        dt = _dtype_code(x)
+        y = self._out(out, oshape, dt)
+        xs, r = _sz(sh); ys, yr = _sz(oshape)
+        check(lib().zant_b200_unsqueeze(self._h, C.c_int32(dt), _ptr(x), xs, C.c_size_t(r), _i64(axes), C.c_size_t(len(axes)), _ptr(y), ys, C.c_size_t(yr)))
+        return y
+
+    def shape_onnx(self, x_shape, start=None, end=None):
+        xs, r = _sz(x_shape)
+        out = (C.c_int64 * max(r, 1))()
+        n = C.c_size_t(0)
+        check(lib().zant_b200_shape_onnx(xs, C.c_size_t(r), C.c_int32(start is not None), C.c_int64(start or 0), C.c_int32(end is not None),
+                                         C.c_int64(end or 0), out, C.byref(n)))
+        return np.array([out[i] for i in range(n.value)], np.int64)
+
     def transpose_onnx(self, x, perm=None, out=None):
         x = _host(x)
         sh = _shape(x)

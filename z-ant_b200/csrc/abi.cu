@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <string>
@@ -362,6 +363,61 @@ int32_t zant_b200_concatenate(zant_ctx* ctx, int32_t dtype, const void* const* t
     for (size_t t = 0; t < n_tensors; ++t) dev[t] = s.ptr<char>(idx[t]);
     ZB_TRY(run_concat(ctx, g, esz, dev.data(), s.ptr<char>(iy)));
     return s.finish();
+}
+
+int32_t zant_b200_unsqueeze_output_shape(const size_t* x_shape, size_t x_rank, const int64_t* axes, size_t n_axes, size_t* out_shape) {
+    if (x_rank) ZB_NEED(x_shape, "x_shape");
+    if (n_axes) ZB_NEED(axes, "axes");
+    ZB_NEED(out_shape, "out_shape");
+    const size_t orank = x_rank + n_axes;
+    if (orank > 16) return fail(ZANT_E_UNSUPPORTED_DIMENSION, "output rank %zu", orank);
+    bool is_new[16] = {false};
+    for (size_t i = 0; i < n_axes; ++i) {
+        long long a = axes[i];
+        if (a < 0) a += (long long)orank;
+        if (a < 0 || a >= (long long)orank) return fail(ZANT_E_AXIS_OUT_OF_BOUNDS, "axis %lld for output rank %zu", (long long)axes[i], orank);
+        if (is_new[a]) return fail(ZANT_E_DUPLICATE_AXIS, "axis %lld given twice", (long long)axes[i]);
+        is_new[a] = true;
+    }
+    size_t k = 0;
+    for (size_t i = 0; i < orank; ++i) out_shape[i] = is_new[i] ? 1 : x_shape[k++];
+    return ZANT_OK;
+}
+
+int32_t zant_b200_unsqueeze(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                            const int64_t* axes, size_t n_axes, void* y, const size_t* y_shape, size_t y_rank) {
+    if (!dtype_valid(dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "dtype %d", dtype);
+    size_t os[16];
+    ZB_TRY(zant_b200_unsqueeze_output_shape(x_shape, x_rank, axes, n_axes, os));
+    ZB_NEED(y_shape, "y_shape");
+    if (y_rank != x_rank + n_axes) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "output rank %zu, expected %zu", y_rank, x_rank + n_axes);
+    for (size_t d = 0; d < y_rank; ++d)
+        if (y_shape[d] != os[d]) return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "output dim %zu is %zu, expected %zu", d, y_shape[d], os[d]);
+    const size_t bytes = numel(x_shape, x_rank) * dtype_size(dtype);
+    if (bytes) { ZB_NEED(x, "x"); ZB_NEED(y, "y"); }
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ix = s.in(x, bytes), iy = s.out(y, bytes);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_copy2d(ctx, s.ptr<char>(ix), bytes, s.ptr<char>(iy), bytes, bytes, 1));
+    return s.finish();
+}
+
+int32_t zant_b200_shape_onnx(const size_t* x_shape, size_t x_rank, int32_t has_start, int64_t start, int32_t has_end, int64_t end,
+                             int64_t* out, size_t* out_len) {
+    ZB_NEED(out_len, "out_len");
+    if (x_rank == 0) { *out_len = 0; return ZANT_OK; }
+    ZB_NEED(x_shape, "x_shape"); ZB_NEED(out, "out");
+    const long long r = (long long)x_rank;
+    long long s0 = has_start ? start : 0; if (s0 < 0) s0 += r;
+    long long e0 = has_end ? end : r; if (e0 < 0) e0 += r;
+    // length as get_shape_output_shape counts it, values as lean_shape_onnx reads them (start clamped to rank - 1)
+    const long long s_len = std::max(0LL, std::min(s0, r)), e_len = std::max(s_len, std::min(e0, r));
+    const long long s_val = std::max(0LL, std::min(s0, r - 1)), e_val = std::max(s_val, std::min(e0, r));
+    *out_len = (size_t)std::max(0LL, e_len - s_len);
+    if ((size_t)std::max(0LL, e_val - s_val) != *out_len) return fail(ZANT_E_MISMATCHED_SHAPE, "shape_onnx: the reference's two clamps disagree (ShapeMismatch)");
+    for (size_t i = 0; i < *out_len; ++i) out[i] = (int64_t)x_shape[(size_t)s_val + i];
+    return ZANT_OK;
 }
 
 int32_t zant_b200_transpose_onnx(zant_ctx* ctx, int32_t dtype, const void* x, const size_t* x_shape, size_t x_rank,

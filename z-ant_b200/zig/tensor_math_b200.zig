@@ -25,6 +25,8 @@ extern fn zant_b200_mul_f32(ctx: ?*Ctx, a: [*]const f32, na: usize, b: [*]const 
 extern fn zant_b200_div_f32(ctx: ?*Ctx, a: [*]const f32, na: usize, b: [*]const f32, nb: usize, y: [*]f32) i32;
 extern fn zant_b200_transpose_onnx(ctx: ?*Ctx, dtype: i32, x: *const anyopaque, xs: [*]const usize, xr: usize, perm: ?[*]const usize, np: usize, y: *anyopaque, ys: [*]const usize, yr: usize) i32;
 extern fn zant_b200_slice_onnx(ctx: ?*Ctx, dtype: i32, x: *const anyopaque, xs: [*]const usize, xr: usize, starts: [*]const i64, ends: [*]const i64, n: usize, axes: ?[*]const i64, steps: ?[*]const i64, y: *anyopaque, ys: [*]const usize, yr: usize) i32;
+extern fn zant_b200_unsqueeze(ctx: ?*Ctx, dtype: i32, x: *const anyopaque, xs: [*]const usize, xr: usize, axes: [*]const i64, na: usize, y: *anyopaque, ys: [*]const usize, yr: usize) i32;
+extern fn zant_b200_shape_onnx(xs: [*]const usize, xr: usize, has_start: i32, start: i64, has_end: i32, end: i64, out: [*]i64, out_len: *usize) i32;
 extern fn zant_b200_gather(ctx: ?*Ctx, dtype: i32, x: *const anyopaque, xs: [*]const usize, xr: usize, indices: [*]const usize, is: [*]const usize, ir: usize, axis: i64, y: *anyopaque, ys: [*]const usize, yr: usize) i32;
 extern fn zant_b200_sum_tensors_f32(ctx: ?*Ctx, a: [*]const f32, as: [*]const usize, ar: usize, b: [*]const f32, bs: [*]const usize, br: usize, y: [*]f32, ys: [*]const usize, yr: usize) i32;
 
