@@ -113,3 +113,38 @@ def test_shard_range_partitions_every_sample(zb):
         assert pos == total
     with pytest.raises(zb.ZantError):
         zb.shard_range(10, 2, 2)
+
+
+def test_slice_unsqueeze_shape_helpers_match_oracle(zb, nogpu, oracle):
+    """Host-only shape rules of Slice, Unsqueeze and Shape against the oracle over many parameter sets."""
+    rng = np.random.default_rng(11)
+    for _ in range(300):
+        rank = int(rng.integers(1, 5))
+        shape = [int(v) for v in rng.integers(1, 9, rank)]
+        n = int(rng.integers(1, rank + 1))
+        axes = [int(a) - (rank if rng.random() < 0.3 else 0) for a in rng.permutation(rank)[:n]]
+        starts = [int(v) for v in rng.integers(-10, 10, n)]
+        ends = [int(v) for v in rng.integers(-10, 12, n)]
+        steps = [int(v) for v in rng.choice([-3, -2, -1, 1, 2, 3], n)]
+        for use_axes, use_steps in itertools.product((False, True), (False, True)):
+            if not use_axes and n != rank and False:
+                continue
+            a = axes if use_axes else None
+            s = steps if use_steps else None
+            st, en = (starts, ends) if use_axes else (starts[:n], ends[:n])
+            for lean in (False, True):
+                assert nogpu.get_slice_output_shape(shape, st, en, a, s, lean=lean) == oracle.get_slice_output_shape(shape, st, en, a, s, lean=lean)
+        k = int(rng.integers(1, 4))
+        orank = rank + k
+        ax = [int(v) - (orank if rng.random() < 0.5 else 0) for v in rng.permutation(orank)[:k]]
+        assert nogpu.get_unsqueeze_output_shape(shape, ax) == oracle.get_unsqueeze_output_shape(shape, ax)
+        s0 = None if rng.random() < 0.3 else int(rng.integers(-6, 6))
+        e0 = None if rng.random() < 0.3 else int(rng.integers(-6, 7))
+        try:
+            want = oracle.shape_onnx(shape, s0, e0).tolist()
+        except oracle.OracleError as e:
+            with pytest.raises(zb.ZantError) as got:
+                nogpu.shape_onnx(shape, s0, e0)
+            assert got.value.name == e.name
+        else:
+            assert nogpu.shape_onnx(shape, s0, e0).tolist() == want
