@@ -177,7 +177,8 @@ def run_qconv_workload(args, zb, ctx, models, torch, stream, rank, world, local,
     """One case of the standalone QLinearConv sweep (--workload qconv3a..3d): the batch of 256
     NCHW int8 images resident in HBM, one plan step per pass; images/s plus the op's roofline."""
     name = args.workload[len("qconv"):]
-    graph, c = models.qconv_graph(name)
+    channels_last = name.endswith("_nhwc")
+    graph, c = models.qconv_graph(name[:2], channels_last=channels_last)
     plan = zb.Plan(ctx, graph, fuse=not args.no_fuse)
     x_dev = torch.from_numpy(c["x"]).cuda()
     y_dev = torch.empty(tuple(graph.tensors[graph.output]["shape"]), dtype=torch.int8, device="cuda")
@@ -220,7 +221,7 @@ def run_qconv_workload(args, zb, ctx, models, torch, stream, rank, world, local,
         line = dict(metric=f"int8 images/sec (standalone QLinearConv, sweep case {name})", value=c["N"] * world / (ms / 1e3), unit="images/s",
                     n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True, scaling="weak",
                     vs_baseline=None, dtype="int8", data="synthetic",
-                    config=dict(workload=f"QLinearConv sweep case {name}", layout="NCHW int8 in and out", l2="256 MiB written between passes",
+                    config=dict(workload=f"QLinearConv sweep case {name}", layout="NHWC int8 in and out (channels-last entry point)" if channels_last else "NCHW int8 in and out", l2="256 MiB written between passes",
                                 parallelism=f"replicas x{world}, no collective", **shape),
                     roofline=roof, int8_peak_tops=int8_peak_tops, cpu_baseline=None, e2e=None, gpu_launches=int(launches) * world, clocks=clocks)
         print(json.dumps(line), flush=True)
@@ -306,7 +307,7 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH_PER_GPU, help="images per GPU per step")
     ap.add_argument("--no-fuse", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
-    ap.add_argument("--workload", default="small_cnn_int8", choices=["small_cnn_int8", "qconv3a", "qconv3b", "qconv3c", "qconv3d", "mobilenetv2_int8", "tinyyolo_int8", "tinyyolo_fp32"],
+    ap.add_argument("--workload", default="small_cnn_int8", choices=["small_cnn_int8", "qconv3a", "qconv3b", "qconv3c", "qconv3d", "qconv3a_nhwc", "qconv3c_nhwc", "mobilenetv2_int8", "tinyyolo_int8", "tinyyolo_fp32"],
                     help="small_cnn_int8 is the headline workload; the qconv cases time one standalone operator")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="chunks of the batch that the end-to-end path pipelines")
     args = ap.parse_args()

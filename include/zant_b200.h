@@ -410,6 +410,27 @@ int32_t zant_b200_qlinearmatmul(zant_ctx* ctx,
                                 int32_t y_dtype, void* y, const size_t* y_shape, size_t y_rank,
                                 int32_t activation);
 
+/* QLinearConv on channels-last tensors: x is [N, H, W, C], y is [N, OH, OW, M]; w stays the ONNX
+ * [M, C, KH, KW].  The reference has no channels-last operator (its tensors are NCHW,
+ * src/Core/Tensor/TensorMath/op_convolution.zig:42); this entry point serves callers that keep
+ * activations channels-last between layers, the layout in which a TMA box of the input is a tensor-core
+ * operand as it lands.  Arithmetic, remaining arguments and error codes are those of
+ * zant_b200_qlinearconv.  Shapes the channels-last kernel does not take (group != 1, stride != 1,
+ * C % 64 != 0, M % 16 != 0, non-zero weight zero points, padding together with x_zp != 0) return
+ * ZANT_E_UNSUPPORTED: there is no second code path behind this entry point. */
+int32_t zant_b200_qlinearconv_nhwc(zant_ctx* ctx,
+                                   int32_t x_dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                                   float x_scale, int32_t x_zp,
+                                   const int8_t* w, const size_t* w_shape, size_t w_rank,
+                                   const float* w_scale, const int32_t* w_zp, size_t n_w_scale,
+                                   float y_scale, int32_t y_zp,
+                                   const int32_t* bias, size_t bias_len,
+                                   int32_t y_dtype, void* y, const size_t* y_shape, size_t y_rank,
+                                   const size_t* stride, size_t n_stride,
+                                   const size_t* pads, size_t n_pads,
+                                   const size_t* dilations, size_t n_dil,
+                                   size_t group, int32_t auto_pad, int32_t activation);
+
 /* QLinearConv for callers that cannot allocate device memory (no counterpart in the reference:
  * its operators run on the CPU heap).  Think of an inference loop whose memory was handed out
  * once at start-up, a latency-critical thread that must avoid cudaMalloc's device-wide
@@ -533,6 +554,9 @@ typedef struct zant_node_attrs {
     /* Slice: n_slice entries; has_* = 0 means the optional ONNX input is absent */
     int64_t slice_starts[8], slice_ends[8], slice_axes[8], slice_steps[8];
     size_t n_slice; int32_t slice_has_axes, slice_has_steps;
+    /* QLinearConv: 1 = x is [N,H,W,C] and y is [N,OH,OW,M] (w stays [M,C,KH,KW]); shapes the
+     * channels-last kernel does not take make zant_b200_plan_finalize return ZANT_E_UNSUPPORTED */
+    int32_t channels_last;
 } zant_node_attrs;
 
 int32_t zant_b200_plan_create(zant_ctx* ctx, zant_plan** out);

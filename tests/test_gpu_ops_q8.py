@@ -148,7 +148,7 @@ TC_QCONV = [
     (2, 7, 23, 23, 130, 5, (1, 2), (2, 2, 2, 2), (2, 1), I8, I8, -5, 3, True, True, "relu"),
     (2, 256, 16, 16, 300, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, U8, 0, 100, True, True, None),
     (4, 3, 32, 32, 32, 3, (2, 2), (1, 1, 1, 1), (1, 1), U8, I8, 0, 0, True, False, "relu6"),
-    (4, 40, 14, 14, 72, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, I8, 3, 0, True, True, "relu6"),     # 1x1 on 14x14: pixel/channel swap + GEMM
+    (4, 40, 14, 14, 72, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, I8, 3, 0, True, True, "relu6"),     # 1x1 on 14x14 (196-byte planes): implicit GEMM, rows copied by warps
     (8, 200, 6, 6, 130, 1, (1, 1), (0, 0, 0, 0), (1, 1), U8, U8, 128, 4, True, True, None),      # 1x1, 200 channels (4 K groups, last partial)
     (8, 64, 14, 14, 96, 3, (2, 2), (1, 1, 1, 1), (1, 1), I8, I8, 0, 0, True, True, "relu"),      # sweep case 3b in small: tap-major im2col
     (6, 80, 13, 11, 40, 3, (1, 2), (2, 0, 1, 1), (2, 1), U8, I8, 77, -5, True, False, None),     # tap-major, 80 channels, odd geometry
@@ -195,7 +195,7 @@ def test_qlinearconv_depthwise3x3(zb, ctx, oracle, case):
 
 
 # stride-1 cases run the implicit-GEMM kernel (one launch), the others im2col + GEMM (two launches)
-TC_QCONV_LAUNCHES = [1, 2, 2, 1, 2, 2, 2, 2, 2, 2]
+TC_QCONV_LAUNCHES = [1, 2, 2, 1, 2, 1, 2, 2, 2, 2]
 
 IMPLICIT_QCONV = [
     # N C H W M k stride pads dil xdt ydt xzp yzp per_channel bias act
@@ -207,6 +207,12 @@ IMPLICIT_QCONV = [
     (2, 96, 20, 20, 300, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, U8, 0, 100, True, True, None),         # pointwise, 256-wide filter tiles
     (5, 256, 8, 8, 64, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, I8, 2, 0, False, True, "relu6"),          # pointwise, 64 pixels per image
     (2, 33, 12, 16, 130, 3, (1, 1), (0, 0, 0, 0), (1, 1), I8, I8, 0, 0, True, True, None),           # no padding, 2 filter tiles
+    (3, 32, 30, 56, 64, 3, (1, 1), (1, 1, 1, 1), (1, 1), I8, I8, 0, 0, True, True, "relu"),          # 4 row blocks per tile, 3 in the last tile
+    (1, 16, 9, 144, 24, 3, (1, 1), (1, 1, 1, 1), (1, 1), U8, I8, 5, 0, True, True, None),            # width segments, 2 row blocks, 1 in the last tile
+    (2, 128, 28, 28, 128, 3, (1, 1), (1, 1, 1, 1), (1, 1), I8, U8, 0, 3, True, False, None),         # 128-wide filter tile: 2 row blocks
+    (3, 96, 14, 14, 160, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, I8, 0, 0, True, True, "relu6"),        # pointwise, 196-byte planes: rows copied by warps, channel padding
+    (3, 40, 10, 10, 24, 1, (1, 1), (0, 0, 0, 0), (1, 1), U8, U8, 9, 5, True, True, None),            # pointwise, 100-byte planes, one tile per image
+    (2, 192, 14, 14, 300, 1, (1, 1), (0, 0, 0, 0), (1, 1), I8, I8, -2, 0, False, True, "relu"),      # pointwise, 196-byte planes, streamed weights, 2 channel stages
 ]
 
 
@@ -229,6 +235,91 @@ def test_qlinearconv_implicit_gemm(ctx, oracle, case):
     assert len(np.unique(want)) > 16
 
 
+NHWC_QCONV = [
+    # N C H W M k pads dil xdt ydt xzp yzp per_channel bias act        (channels-last in and out)
+    (2, 64, 56, 56, 64, 3, (1, 1, 1, 1), (1, 1), I8, I8, 0, 0, True, True, "relu"),        # sweep case 3a: 64-byte rows, 4 row blocks, resident weights
+    (2, 128, 28, 28, 128, 3, (1, 1, 1, 1), (1, 1), I8, U8, 0, 3, True, False, None),       # 128-byte rows, 128-wide filter tile, general requantisation
+    (1, 64, 40, 144, 32, 3, (1, 1, 1, 1), (1, 1), I8, I8, 0, 0, False, True, "relu6"),     # two width segments
+    (2, 256, 20, 20, 320, 1, (0, 0, 0, 0), (1, 1), U8, I8, 128, 0, True, True, None),      # 1x1, two channel stages, two filter tiles (streamed weights)
+    (2, 64, 36, 36, 48, 5, (4, 4, 4, 4), (2, 2), I8, I8, 0, -4, True, False, "relu"),      # 5x5 dilated
+    (3, 192, 14, 14, 64, 3, (0, 0, 0, 0), (1, 1), U8, U8, 7, 9, True, True, None),         # three 64-channel stages, no padding with an input zero point
+    (1, 64, 30, 56, 64, 3, (1, 1, 1, 1), (1, 1), I8, I8, 0, 0, True, True, None),          # 3 row blocks in the last tile
+]
+
+
+@pytest.mark.parametrize("case", NHWC_QCONV, ids=[f"nhwc{i}" for i in range(len(NHWC_QCONV))])
+def test_qlinearconv_channels_last(ctx, oracle, case):
+    N, C, H, W, M, k, pads, dil, xdt, ydt, xzp, yzp, per_ch, has_bias, act = case
+    rng = np.random.default_rng(N * 43 + C + M + W)
+    x = q(rng, (N, H, W, C), xdt)
+    w = rng.integers(-127, 128, (M, C, k, k), dtype=np.int8)
+    ws = (rng.random(M if per_ch else 1, dtype=np.float32) * 0.02 + 0.001).astype(np.float32)
+    bias = rng.integers(-3000, 3000, M).astype(np.int32) if has_bias else None
+    y_scale = 0.015 * np.sqrt(C * k * k)
+    kw = dict(bias=bias, y_dtype=ydt, stride=(1, 1), pads=pads, dilations=dil, group=1, activation=act)
+    before = ctx.launch_count()
+    got = ctx.qlinearconv_nhwc(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
+    assert ctx.launch_count() - before == 1
+    want = oracle.qlinearconv(np.ascontiguousarray(x.transpose(0, 3, 1, 2)), 0.02, xzp, w, ws, None, y_scale, yzp, **kw).transpose(0, 2, 3, 1)
+    assert got.shape == want.shape and np.array_equal(got, want)
+    assert len(np.unique(want)) > 16
+
+
+def test_qlinearconv_channels_last_as_a_plan_node(ctx, zb, oracle):
+    """The sweep case 3a, small batch, as a one-node plan with channels_last=1."""
+    import torch
+    from zant_b200 import models
+    graph, c = models.qconv_graph("3a", batch=4, channels_last=True)
+    plan = zb.Plan(ctx, graph)
+    assert plan.step_names() == ["QLinearConv(tc-nhwc)"]
+    x = torch.from_numpy(c["x"]).cuda()
+    y = torch.empty(tuple(graph.tensors[graph.output]["shape"]), dtype=torch.int8, device="cuda")
+    plan.run(x, out=y)
+    want = oracle.qlinearconv(np.ascontiguousarray(c["x"].transpose(0, 3, 1, 2)), c["x_scale"], 0, c["w"], c["w_scale"], None, c["y_scale"], 0,
+                              y_dtype=I8, stride=c["stride"], pads=c["pads"], dilations=c["dilations"], group=1, activation=None)
+    assert np.array_equal(y.cpu().numpy(), want.transpose(0, 2, 3, 1))
+    plan.close()
+
+
+def test_qlinearconv_channels_last_refuses_other_shapes(ctx, zb):
+    rng = np.random.default_rng(5)
+    x = q(rng, (1, 8, 8, 32), I8)                              # 32 channels: not a whole 64-byte operand row
+    w = rng.integers(-127, 128, (16, 32, 3, 3), dtype=np.int8)
+    with pytest.raises(zb.ZantError) as e:
+        ctx.qlinearconv_nhwc(x, 0.02, 0, w, np.float32(0.01), None, 0.5, 0)
+    assert e.value.name == "Unsupported" or e.value.status == -103
+
+
+SMALLC_QCONV = [
+    # N C H W M stride pads xdt ydt xzp yzp per_channel bias act        (3x3 on at most four channels: network stems)
+    (5, 3, 64, 64, 32, 2, (1, 1, 1, 1), U8, I8, 0, 0, True, True, "relu6"),       # MobileNet-style stem, 32-pixel units
+    (1, 3, 48, 112, 16, 1, (1, 1, 1, 1), U8, I8, 3, 0, True, True, None),         # detector-style stem, 16-pixel units
+    (2, 1, 40, 60, 48, 1, (0, 1, 1, 0), I8, U8, 0, 7, True, True, "relu"),        # one channel, odd output width: byte stores, partial units
+    (4, 4, 66, 72, 64, 2, (0, 0, 0, 0), I8, I8, -5, -3, False, False, None),      # four channels, 64 filters, no padding, general requantisation
+    (8, 3, 50, 52, 32, 2, (1, 0, 0, 1), U8, U8, 128, 100, True, True, "relu6"),   # asymmetric pads
+    (1, 2, 20, 512, 16, 1, (1, 1, 1, 1), I8, I8, 0, 0, True, False, "relu"),      # wide rows, one band per few rows
+]
+
+
+@pytest.mark.parametrize("case", SMALLC_QCONV, ids=[f"smallc{i}" for i in range(len(SMALLC_QCONV))])
+def test_qlinearconv_small_channel_count(ctx, oracle, case):
+    N, C, H, W, M, s, pads, xdt, ydt, xzp, yzp, per_ch, has_bias, act = case
+    rng = np.random.default_rng(N * 41 + C + M + W)
+    x = q(rng, (N, C, H, W), xdt)
+    w = rng.integers(-127, 128, (M, C, 3, 3), dtype=np.int8)
+    ws = (rng.random(M if per_ch else 1, dtype=np.float32) * 0.02 + 0.001).astype(np.float32)
+    bias = rng.integers(-3000, 3000, M).astype(np.int32) if has_bias else None
+    y_scale = 0.03 * np.sqrt(C * 9)
+    kw = dict(bias=bias, y_dtype=ydt, stride=(s, s), pads=pads, dilations=(1, 1), group=1, activation=act)
+    before = ctx.launch_count()
+    got = ctx.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
+    launches = ctx.launch_count() - before
+    want = oracle.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
+    assert got.shape == want.shape and np.array_equal(got, want)
+    assert launches == 1
+    assert len(np.unique(want)) > 16
+
+
 @pytest.mark.parametrize("case,launches", list(zip(TC_QCONV, TC_QCONV_LAUNCHES)), ids=[f"tcqconv{i}" for i in range(len(TC_QCONV))])
 def test_qlinearconv_tensor_core_path(ctx, oracle, case, launches):
     N, C, H, W, M, k, stride, pads, dil, xdt, ydt, xzp, yzp, per_ch, has_bias, act = case
@@ -241,9 +332,10 @@ def test_qlinearconv_tensor_core_path(ctx, oracle, case, launches):
     kw = dict(bias=bias, y_dtype=ydt, stride=stride, pads=pads, dilations=dil, group=1, activation=act)
     before = ctx.launch_count()
     got = ctx.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
-    assert ctx.launch_count() - before == launches    # a tensor-core path, not the generic kernel
+    n_launches = ctx.launch_count() - before
     want = oracle.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
     assert got.shape == want.shape and np.array_equal(got, want)
+    assert n_launches == launches    # a tensor-core path, not the generic kernel
     assert len(np.unique(want)) > 8
 
 

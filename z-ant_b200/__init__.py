@@ -71,6 +71,7 @@ class NodeAttrs(C.Structure):
         ("perm", C.c_int64 * 8), ("n_perm", C.c_size_t),
         ("slice_starts", C.c_int64 * 8), ("slice_ends", C.c_int64 * 8), ("slice_axes", C.c_int64 * 8), ("slice_steps", C.c_int64 * 8),
         ("n_slice", C.c_size_t), ("slice_has_axes", C.c_int32), ("slice_has_steps", C.c_int32),
+        ("channels_last", C.c_int32),
     ]
 
 
@@ -597,6 +598,28 @@ class Context:
                                           C.c_size_t(group), C.c_int32(AUTO_PAD[auto_pad]), C.c_int32(QACT[activation])))
         return y
 
+    def qlinearconv_nhwc(self, x, x_scale, x_zp, w, w_scale, w_zp, y_scale, y_zp, bias=None, y_dtype=I8, stride=(1, 1),
+                         pads=(0, 0, 0, 0), dilations=(1, 1), group=1, auto_pad="NOTSET", activation=None, out=None):
+        """QLinearConv on channels-last tensors (zant_b200_qlinearconv_nhwc): x [N,H,W,C] -> y [N,OH,OW,M],
+        w in the ONNX [M,C,KH,KW] order; everything else as qlinearconv."""
+        x = _host(x); w = _host(w, np.int8)
+        w_scale = np.atleast_1d(np.ascontiguousarray(w_scale, np.float32))
+        w_zp = None if w_zp is None else np.atleast_1d(np.ascontiguousarray(w_zp, np.int32))
+        bias = _host(bias, np.int32)
+        n, h, wd, c = _shape(x)
+        yn, ym, yh, yw = qconv_output_shape((n, c, h, wd), _shape(w), stride, pads, dilations, auto_pad)
+        y_shape = (yn, yh, yw, ym)
+        y = self._out(out, y_shape, y_dtype)
+        xs, xr = _sz(_shape(x)); ws, wr = _sz(_shape(w)); ys, yr = _sz(y_shape)
+        st, ns = _sz(stride); pd, npd = _sz(pads); dl, nd = _sz(dilations)
+        check(lib().zant_b200_qlinearconv_nhwc(self._h, C.c_int32(_dtype_code(x)), _ptr(x), xs, C.c_size_t(xr), C.c_float(x_scale),
+                                               C.c_int32(x_zp), _ptr(w), ws, C.c_size_t(wr), _ptr(w_scale), _ptr(w_zp),
+                                               C.c_size_t(w_scale.size), C.c_float(y_scale), C.c_int32(y_zp), _ptr(bias),
+                                               C.c_size_t(0 if bias is None else bias.size), C.c_int32(y_dtype), _ptr(y), ys,
+                                               C.c_size_t(yr), st, C.c_size_t(ns), pd, C.c_size_t(npd), dl, C.c_size_t(nd),
+                                               C.c_size_t(group), C.c_int32(AUTO_PAD[auto_pad]), C.c_int32(QACT[activation])))
+        return y
+
     def qlinearmatmul(self, a, a_scale, a_zp, b, b_scale, b_zp, y_scale, y_zp, bias=None, y_dtype=I8, activation=None, out=None):
         a = _host(a); b = _host(b, np.int8)
         b_scale = np.atleast_1d(np.ascontiguousarray(b_scale, np.float32))
@@ -741,7 +764,7 @@ def _fill_attrs(attrs):
             a.activation = QACT[v]
         elif k in ("alpha", "beta", "x_scale", "b_scale", "y_scale"):
             setattr(a, k, float(v))
-        elif k in ("group", "trans_a", "trans_b", "axis", "keepdims", "noop_with_empty_axes", "x_zp", "b_zp", "y_zp"):
+        elif k in ("group", "trans_a", "trans_b", "axis", "keepdims", "noop_with_empty_axes", "x_zp", "b_zp", "y_zp", "channels_last"):
             setattr(a, k, int(v))
         else:
             raise KeyError(f"unknown node attribute {k}")

@@ -19,6 +19,8 @@
 #include "tc_conv_generic.cuh"
 #include "tc_conv_nchw.cuh"
 #include "dwconv_q8.cuh"
+#include "smallc_conv_q8.cuh"
+#include "tc_conv_nhwc.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -589,6 +591,44 @@ int32_t zant_b200_dequantize_linear(zant_ctx* ctx, int32_t in_dtype, const void*
     return s.finish();
 }
 
+int32_t zant_b200_qlinearconv_nhwc(zant_ctx* ctx, int32_t x_dtype, const void* x, const size_t* x_shape, size_t x_rank,
+                                   float x_scale, int32_t x_zp, const int8_t* w, const size_t* w_shape, size_t w_rank,
+                                   const float* w_scale, const int32_t* w_zp, size_t n_w_scale, float y_scale, int32_t y_zp,
+                                   const int32_t* bias, size_t bias_len, int32_t y_dtype, void* y, const size_t* y_shape, size_t y_rank,
+                                   const size_t* stride, size_t n_stride, const size_t* pads, size_t n_pads,
+                                   const size_t* dilations, size_t n_dil, size_t group, int32_t auto_pad, int32_t activation) {
+    ZB_NEED(x_shape, "x_shape"); ZB_NEED(w_shape, "w_shape"); ZB_NEED(y_shape, "y_shape");
+    if (!q8_dtype(x_dtype) || !q8_dtype(y_dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearConv tensors must be int8 or uint8");
+    if (x_rank != 4 || y_rank != 4) return fail(ZANT_E_INVALID_DIMENSIONS, "channels-last QLinearConv takes rank-4 tensors");
+    // the geometry is that of the NCHW operator on the permuted shapes
+    const size_t xs[4] = {x_shape[0], x_shape[3], x_shape[1], x_shape[2]}, ys[4] = {y_shape[0], y_shape[3], y_shape[1], y_shape[2]};
+    ConvGeom g;
+    ZB_TRY(conv_resolve_onnx(xs, 4, w_shape, w_rank, ys, 4, stride, n_stride, pads, n_pads, dilations, n_dil, group, auto_pad, g));
+    ZB_NEED(w_scale, "w_scale");
+    if (n_w_scale != 1 && n_w_scale != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "w_scale holds %zu values for %d filters", n_w_scale, g.M);
+    if (bias && bias_len != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "bias holds %zu values for %d filters", bias_len, g.M);
+    if (activation < ZANT_QACT_NONE || activation > ZANT_QACT_RELU6) return fail(ZANT_E_INVALID_INPUT, "activation %d", activation);
+    ZB_NEED(x, "x"); ZB_NEED(w, "w"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    if (is_device_ptr(w) || (bias && is_device_ptr(bias))) return fail(ZANT_E_UNSUPPORTED, "channels-last QLinearConv takes weights and bias from host memory");
+    if ((is_device_ptr(x) && !tc_conv_ptr_ok(x)) || (is_device_ptr(y) && !tc_conv_ptr_ok(y))) return fail(ZANT_E_INVALID_INPUT, "channels-last QLinearConv buffers must be 16-byte aligned");
+    std::vector<float> mult;
+    requant_multipliers(x_scale, w_scale, n_w_scale, y_scale, (size_t)g.M, mult);
+    bool wz_zero = true;
+    if (w_zp) for (size_t i = 0; i < n_w_scale; ++i) wz_zero = wz_zero && w_zp[i] == 0;
+    TcConvPlan tcp;
+    if (!tc_conv_nhwc_plan(g, wz_zero, x_zp, tcp)) return fail(ZANT_E_UNSUPPORTED, "shape not taken by the channels-last QLinearConv kernel");
+    std::vector<int8_t> w_blk; std::vector<float> mp; std::vector<int32_t> bp;
+    tc_conv_nhwc_prepare(tcp, w, mult.data(), bias, x_zp, w_blk, mp, bp);
+    Stager s(ctx);
+    const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
+    const int iw = s.in(w_blk.data(), w_blk.size()), im = s.in(mp.data(), mp.size() * 4), ib = s.in(bp.data(), bp.size() * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(tc_conv_nhwc_run(ctx, tcp, s.ptr<char>(ix), x_dtype == ZANT_U8, s.ptr<int8_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
+                            s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, tc_conv_max_product(mp, bp, (long long)g.Cg * g.KH * g.KW)));
+    return s.finish();
+}
+
 int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, const size_t* x_shape, size_t x_rank,
                               float x_scale, int32_t x_zp, const int8_t* w, const size_t* w_shape, size_t w_rank,
                               const float* w_scale, const int32_t* w_zp, size_t n_w_scale, float y_scale, int32_t y_zp,
@@ -612,6 +652,18 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
     bool wz_zero = true;
     for (int32_t v : wz) wz_zero = wz_zero && v == 0;
     const bool host_consts = !is_device_ptr(w) && !(bias && is_device_ptr(bias));
+    if (host_consts && qconv_smallc_eligible(g, wz_zero) && (!is_device_ptr(x) || qconv_smallc_ptr_ok(x))) {
+        // 3x3 on at most four input channels (network stems): warp-level MMAs with the filters as rows
+        std::vector<uint32_t> wfrag; std::vector<int32_t> bf;
+        qconv_smallc_prepare(g, w, bias, x_zp, wfrag, bf);
+        Stager s(ctx);
+        const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
+        const int iw = s.in(wfrag.data(), wfrag.size() * 4), im = s.in(mult.data(), mult.size() * 4), ib = s.in(bf.data(), bf.size() * 4);
+        ZB_TRY(s.commit());
+        ZB_TRY(run_qconv_smallc(ctx, g, s.ptr<char>(ix), x_dtype == ZANT_U8, x_zp, s.ptr<uint32_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
+                                s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, tc_conv_max_product(mult, bf, (long long)g.C * 9)));
+        return s.finish();
+    }
     TcConvPlan tcp;
     if (host_consts && (long long)g.N * g.OH * g.OW >= 256 && (!is_device_ptr(x) || tc_conv_ptr_ok(x)) && tc_conv_plan(g, wz_zero, tcp)) {
         // implicit GEMM straight from NCHW (stride 1): no im2col matrix

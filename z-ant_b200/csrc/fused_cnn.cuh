@@ -78,8 +78,20 @@ constexpr int C1M_UNITS = (C1M_G * 169 + 15) / 16;
 
 __global__ void __launch_bounds__(C1M_THREADS) conv1_mma_relu_pool_kernel(const Conv1MmaArgs a) {
     __shared__ uint32_t img[C1M_G][28][8];   // quantized uint8 rows of 32 bytes (28 pixels + 4 pad)
+    // Per pooled pixel of an iteration (the same in every iteration): x = word of img that holds the patch's
+    // first byte | odd column << 16 | image within the group << 17 | exists << 19; y = byte offset of the
+    // pixel's first 16-channel chunk from the group's first image.  Keeps divisions out of the main loop.
+    __shared__ uint2 pix_tab[C1M_UNITS * 16];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
+    for (int i = tid; i < C1M_UNITS * 16; i += C1M_THREADS) {
+        const bool exists = i < C1M_G * 169;
+        const int pc = exists ? i : 0;
+        const int gi = pc / 169, pp = pc - gi * 169;
+        const int py = pp / 13, px = pp - py * 13;
+        pix_tab[i] = make_uint2((uint32_t)(gi * 224 + 2 * py * 8 + (px >> 1)) | ((uint32_t)(px & 1) << 16) | ((uint32_t)gi << 17) | ((uint32_t)exists << 19),
+                                (uint32_t)(gi * 2 * 169 * 16 + pp * 16));
+    }
     uint32_t wf[4][4]; int bias[4][2]; float mult[4][2];
 #pragma unroll
     for (int m = 0; m < 4; ++m)
@@ -109,18 +121,14 @@ __global__ void __launch_bounds__(C1M_THREADS) conv1_mma_relu_pool_kernel(const 
         __syncthreads();
         // ---- 16 pooled pixels per warp iteration
         for (int u = warp; u < C1M_UNITS; u += C1M_THREADS / 32) {
-            int pi[2]; bool ok[2]; uint32_t afrag[2];
+            bool ok[2]; uint32_t afrag[2], out_off[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                pi[h] = u * 16 + g + 8 * h;
-                const int gi = pi[h] / 169;
-                ok[h] = pi[h] < C1M_G * 169 && base + gi < a.n_images;
-                const int pc = ok[h] ? pi[h] : 0;
-                const int gi2 = pc / 169, pp = pc - gi2 * 169;
-                const int py = pp / 13, px = pp - py * 13;
-                const uint32_t* row = &img[gi2][2 * py + t][0];
-                const uint32_t w0 = row[px >> 1];
-                afrag[h] = (px & 1) ? __byte_perm(w0, row[(px >> 1) + 1], 0x5432) : w0;
+                const uint2 e = pix_tab[u * 16 + g + 8 * h];
+                ok[h] = (e.x >> 19) != 0 && base + (int)((e.x >> 17) & 3u) < a.n_images;
+                out_off[h] = e.y;
+                const uint32_t* row = &img[0][0][0] + (e.x & 0xffffu) + t * 8;       // patch row t of the pooled pixel
+                afrag[h] = __byte_perm(row[0], row[1], (e.x & 0x10000u) ? 0x5432u : 0x3210u);
             }
             uint32_t outw[2][2];
 #pragma unroll
@@ -145,8 +153,7 @@ __global__ void __launch_bounds__(C1M_THREADS) conv1_mma_relu_pool_kernel(const 
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 if (!ok[h]) continue;
-                const int gi = pi[h] / 169, pp = pi[h] - gi * 169;
-                int8_t* yo = a.y + (((size_t)(base + gi) * 2 + (t >> 1)) * 169 + pp) * 16 + (t & 1) * 8;
+                int8_t* yo = a.y + (size_t)base * (2 * 169 * 16) + out_off[h] + (t >> 1) * (169 * 16) + (t & 1) * 8;
                 *reinterpret_cast<uint2*>(yo) = make_uint2(outw[h][0], outw[h][1]);
             }
         }

@@ -22,6 +22,8 @@
 #include "tc_conv_generic.cuh"
 #include "tc_conv_nchw.cuh"
 #include "dwconv_q8.cuh"
+#include "smallc_conv_q8.cuh"
+#include "tc_conv_nhwc.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -658,8 +660,16 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
             if ((xd != ZANT_I8 && xd != ZANT_U8) || (yd != ZANT_I8 && yd != ZANT_U8)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearConv x/y dtype");
             if (!T(w).is_const || !T(ws).is_const || (wz >= 0 && !T(wz).is_const)) return fail(ZANT_E_UNSUPPORTED, "QLinearConv weights and scales must be initializers");
             ConvGeom g;
-            ZB_TRY(conv_resolve_onnx(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(), T(y).shape.data(), T(y).shape.size(),
-                                     a.strides, a.n_strides, a.pads, a.n_pads, a.dilations, a.n_dilations, a.group, a.auto_pad < 0 ? 0 : a.auto_pad, g));
+            if (a.channels_last) {
+                // the geometry is that of the NCHW operator on the permuted shapes
+                if (T(x).shape.size() != 4 || T(y).shape.size() != 4) return fail(ZANT_E_INVALID_DIMENSIONS, "channels-last QLinearConv takes rank-4 tensors");
+                const size_t xs[4] = {T(x).shape[0], T(x).shape[3], T(x).shape[1], T(x).shape[2]}, ys[4] = {T(y).shape[0], T(y).shape[3], T(y).shape[1], T(y).shape[2]};
+                ZB_TRY(conv_resolve_onnx(xs, 4, T(w).shape.data(), T(w).shape.size(), ys, 4,
+                                         a.strides, a.n_strides, a.pads, a.n_pads, a.dilations, a.n_dilations, a.group, a.auto_pad < 0 ? 0 : a.auto_pad, g));
+            } else {
+                ZB_TRY(conv_resolve_onnx(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(), T(y).shape.data(), T(y).shape.size(),
+                                         a.strides, a.n_strides, a.pads, a.n_pads, a.dilations, a.n_dilations, a.group, a.auto_pad < 0 ? 0 : a.auto_pad, g));
+            }
             const size_t nws = numel(T(ws).shape.data(), T(ws).shape.size());
             if (nws != 1 && nws != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv w_scale size");
             if (b >= 0 && numel(T(b).shape.data(), T(b).shape.size()) != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv bias size");
@@ -674,6 +684,33 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
             const int xzp = a.x_zp; const Requant rq{a.y_scale, a.y_zp, a.activation};
             bool wz_zero = true;
             for (int32_t v : wzv) wz_zero = wz_zero && v == 0;
+            if (a.channels_last) {
+                TcConvPlan ncp;
+                if (!(b < 0 || T(b).is_const) || !tc_conv_nhwc_plan(g, wz_zero, xzp, ncp)) return fail(ZANT_E_UNSUPPORTED, "shape not taken by the channels-last QLinearConv kernel");
+                std::vector<int8_t> w_blk; std::vector<float> mp; std::vector<int32_t> bp;
+                tc_conv_nhwc_prepare(ncp, (const int8_t*)T(w).host.data(), mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, w_blk, mp, bp);
+                const int aw = pl->add_aux(w_blk.data(), w_blk.size()), am = pl->add_aux(mp.data(), mp.size() * 4), ab = pl->add_aux(bp.data(), bp.size() * 4);
+                const double max_product = tc_conv_max_product(mp, bp, (long long)g.Cg * g.KH * g.KW);
+                push("QLinearConv(tc-nhwc)", [=]() {
+                    if (!tc_conv_ptr_ok(pl->ptr(x)) || !tc_conv_ptr_ok(pl->ptr(y))) return fail(ZANT_E_INVALID_INPUT, "channels-last QLinearConv buffers must be 16-byte aligned");
+                    return tc_conv_nhwc_run(ctx, ncp, pl->ptr(x), xd == ZANT_U8, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
+                                            (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq, max_product);
+                });
+                return ZANT_OK;
+            }
+            if ((b < 0 || T(b).is_const) && qconv_smallc_eligible(g, wz_zero)) {
+                // 3x3 on at most four input channels (network stems); arena tensors are 256-byte aligned
+                std::vector<uint32_t> wfrag; std::vector<int32_t> bf;
+                qconv_smallc_prepare(g, (const int8_t*)T(w).host.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, wfrag, bf);
+                const int aw = pl->add_aux(wfrag.data(), wfrag.size() * 4), am = pl->add_aux(mult.data(), mult.size() * 4), ab = pl->add_aux(bf.data(), bf.size() * 4);
+                const double max_product = tc_conv_max_product(mult, bf, (long long)g.C * 9);
+                push("QLinearConv(small-c)", [=]() {
+                    if (!qconv_smallc_ptr_ok(pl->ptr(x))) return fail(ZANT_E_INVALID_INPUT, "QLinearConv input buffer must be 4-byte aligned");
+                    return run_qconv_smallc(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, (const uint32_t*)pl->aux(aw), (const float*)pl->aux(am),
+                                            (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq, max_product);
+                });
+                return ZANT_OK;
+            }
             TcConvPlan tcp;
             if ((b < 0 || T(b).is_const) && (long long)g.N * g.OH * g.OW >= 256 && tc_conv_plan(g, wz_zero, tcp)) {
                 // implicit GEMM from NCHW (stride 1): weights blocked once here, one launch per run.

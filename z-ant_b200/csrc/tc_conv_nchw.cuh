@@ -1,21 +1,24 @@
 // Implicit-GEMM QLinearConv on tcgen05 that reads and writes the reference's NCHW layout directly
 // (group 1, stride 1, any kernel size / dilation / padding, weight zero points 0).
 //
-// A tile is BH output rows x BW output columns of one image; its input patch (PH x PW pixels, halo
-// included) is brought in CB*16 channels at a time:
-//   1. the loader warp copies, for every channel of the stage, the run of input bytes that holds
-//      the patch rows (one run per channel when the tile spans the image width, else one per row)
-//      with 1-D bulk async copies (TMA engine) into a staging buffer.  A run starts at the 16-byte
-//      boundary below its first byte, so the data sits `shift` bytes into its slot; the host admits
-//      only shapes for which `shift` is the same for every channel of a stage (H*W % 16 == 0, and
-//      W % 16 == 0 when rows are separate runs);
+// A tile is RB row blocks of BH output rows x BW output columns of one image (a row block is what one
+// 128-row MMA covers); its input patch (PH x PW pixels, halo included, shared by the row blocks so that
+// the halo rows are fetched and transposed once per tile, not once per block) is brought in CB*16
+// channels at a time:
+//   1. the loader warp issues one tiled TMA load per stage: a box of CB*16 channels x the input bytes
+//      that hold the patch rows (one run per channel when the tile spans the image width, else one
+//      per row) into a staging buffer.  A box starts at the 16-byte boundary below its first wanted
+//      byte, so the data sits `shift` bytes into its slot; the host admits only shapes for which
+//      `shift` is the same for every channel of a stage (H*W % 16 == 0, and W % 16 == 0 when rows
+//      are separate runs);
 //   2. eight warps transpose staging -> "patch" [16-channel group][patch pixel][16 channels], one
 //      16-byte chunk per pixel, pixels in row-major order of the patch (4x4 byte transposes with
 //      prmt); pixels outside the image are replaced by the input zero point on the way.
 // In that form filter tap (kh,kw) of the implicit GEMM is the same shared memory shifted by
 // (kh*dh*PW + kw*dw) chunks, which a K-major no-swizzle shared-memory descriptor expresses
-// directly: MMA row r stands for patch pixel r, i.e. output (r / PW, r % PW) of the tile; rows
-// with r % PW >= BW or r / PW >= BH are computed and dropped.  No im2col matrix exists anywhere.
+// directly: MMA row r of row block b stands for patch pixel b*BH*PW + r, i.e. output
+// (b*BH + r / PW, r % PW) of the tile; rows with r % PW >= BW or r / PW >= BH are computed and
+// dropped.  Each row block accumulates in its own TMEM columns.  No im2col matrix exists anywhere.
 // 1x1 convolutions skip steps 1-2: a box of 128 pixels x CB*16 channels, loaded with the 128-byte swizzle,
 // is already a valid MMA operand (MN-major: the pixel index is the contiguous one), so the loader
 // signals the MMA issuer directly and the transposing warps stay idle.
@@ -48,10 +51,13 @@ struct TcConvArgs {
     const uint8_t* x; uint8_t* y; const int8_t* w; const float* mult; const int32_t* bias;
     int N, C, H, W, M, OH, OW;        // M = filters; for 1x1 convolutions the host passes H = 1, W = H*W
     int KH, KW, dh, dw, pt, pl;
-    int BH, BW, PH, PW, PR;           // tile, patch, allocated patch pixels per 16-channel group
+    int BH, BW, PH, PW, PR;           // row block, patch, allocated patch pixels per 16-channel group
+    int RB, BHT;                      // row blocks per tile (1, 2 or 4); output rows per tile = RB * BH
     int hseg, wseg, c_stages, n_tiles;
     int CB;                           // 16-channel groups per stage (2, 4 or 8)
-    int direct;                       // 1x1 convolution: the TMA box is the MMA operand itself (MN-major, 128-byte swizzle); no transposes
+    int direct;                       // 1x1 convolution: the MMA operand is the input itself (MN-major, 128-byte swizzle), no transposes.
+                                      // 1: a TMA box lands in that form; 2: image planes are not multiples of 16 bytes (no tensor map
+                                      // exists), warps 2-9 copy the rows with 4-byte loads into the same swizzled form
     int full_width;                   // 1: a tile spans the image width and a channel's patch rows are one run; 0: one run per row
     int RP;                           // staging bytes between two patch rows of a channel (W, or the run pitch when rows are separate runs)
     int CP;                           // staging bytes per channel
@@ -146,7 +152,7 @@ __device__ __forceinline__ void tc_conv_cursor_next(const TcConvArgs& a, TcConvC
 
 __device__ __forceinline__ TcConvTile tc_conv_tile(const TcConvArgs& a, const TcConvCursor& c) {
     TcConvTile r;
-    r.nt = c.nt; r.img = c.img; r.h0 = c.hs * a.BH; r.w0 = c.ws * a.BW;
+    r.nt = c.nt; r.img = c.img; r.h0 = c.hs * a.BHT; r.w0 = c.ws * a.BW;
     r.h_in0 = r.h0 - a.pt; r.w_in0 = r.w0 - a.pl;
     r.hh_lo = max(0, -r.h_in0); r.hh_hi = min(a.PH, a.H - r.h_in0);
     if (a.full_width) {
@@ -190,8 +196,8 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     const uint32_t w_stage_bytes = (uint32_t)taps * w_tap_bytes;
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), (a.direct || a.w_resident) ? 1 : 2); ptx::mbar_init(empty(s), 1); }
-        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), a.direct ? 16 : 8); }
+        for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), (a.direct == 1 || a.w_resident) ? 1 : 2); ptx::mbar_init(empty(s), 1); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), a.direct == 1 ? 16 : 8); }
         for (int s = 0; s < S; ++s) { ptx::mbar_init(ld_full(s), 1); ptx::mbar_init(ld_empty(s), 8); }
         ptx::mbar_init(wfull, 1);
         *abort_flag = 0;
@@ -200,7 +206,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     }
     for (int i = tid; i < a.m_pad; i += kTcConvThreads) { sMult[i] = __ldg(a.mult + i); sBias[i] = __ldg(a.bias + i); }
     if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), 2 * NT);
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), 2 * a.RB * NT);
         ptx::tmem_relinquish();
     }
     ptx::tc_fence_before();
@@ -230,6 +236,19 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             const TcConvTile T = tc_conv_tile(a, cur);
             tc_conv_cursor_next(a, cur);
             for (int cs = 0; cs < a.c_stages; ++cs) {
+                if (a.direct == 2) {
+                    // 1x1 without a tensor map: warps 2-9 copy the activations; only streamed weights are loaded here
+                    if (!a.w_resident) {
+                        if (!ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag)) { alive = false; break; }
+                        if (lane == 0) {
+                            ptx::mbar_arrive_expect_tx(full(s), w_stage_bytes);
+                            ptx::bulk_g2s(ptx::smem_u32(sStages + (size_t)s * a.stage_bytes), a.w + ((size_t)T.nt * a.c_stages + cs) * w_stage_bytes, w_stage_bytes, full(s));
+                        }
+                        __syncwarp();
+                    }
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                    continue;
+                }
                 if (a.direct) {
                     // 1x1: the box of 128 pixels x CB*16 channels lands where the MMA reads it
                     if (!ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag)) { alive = false; break; }
@@ -269,7 +288,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             const int ksteps = a.CB / 2;
             // descriptors advance by adding 16-byte units to their address field (shared memory is < 256 KiB, no carry)
             const uint64_t a_kstep = (uint64_t)((2u * a_lbo) >> 4), b_kstep = (uint64_t)((2u * NT * 16u) >> 4);
-            const uint64_t a_col = (uint64_t)a.dw, a_rowstep = (uint64_t)(a.dh * a.PW);
+            const uint64_t a_col = (uint64_t)a.dw, a_rowstep = (uint64_t)(a.dh * a.PW), a_blkstep = (uint64_t)(a.BH * a.PW);
             const uint64_t b_tap = (uint64_t)(w_tap_bytes >> 4);
             int s = 0; uint32_t ph = 0;
             int tile_it = 0;
@@ -280,7 +299,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                 const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
                 if (!ptx::mbar_wait(tempty(b), bph ^ 1u, abort_flag)) goto mma_done;
                 ZB_TACC(0);
-                const uint32_t d_tmem = tmem_base + (uint32_t)(b * NT);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * a.RB * NT);
                 for (int cs = 0; cs < a.c_stages; ++cs) {
                     if (!ptx::mbar_wait(full(s), ph, abort_flag)) goto mma_done;
                     ZB_TACC(1);
@@ -300,13 +319,19 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                         ZB_TACC(2);
                         continue;
                     }
+                    // Every row block multiplies its own window of the shared patch into its own accumulator.
+                    // The blocks' MMAs alternate: consecutive instructions are then independent of one another
+                    // (an MMA that accumulates onto the previous one's result waits for it).
                     uint64_t da_row = ptx::smem_desc_kmajor(stage0 + (uint32_t)a.off_patch, a_lbo, 128);
                     for (int kh = 0; kh < a.KH; ++kh, da_row += a_rowstep) {
                         uint64_t da = da_row;
                         for (int kw = 0; kw < a.KW; ++kw, da += a_col, db += b_tap) {
-                            ptx::mma_i8(d_tmem, da, db, idesc, acc != 0);
-                            acc = 1u;
-                            for (int kk = 1; kk < ksteps; ++kk) ptx::mma_i8(d_tmem, da + (uint64_t)kk * a_kstep, db + (uint64_t)kk * b_kstep, idesc, true);
+                            for (int kk = 0; kk < ksteps; ++kk) {
+                                uint64_t da_blk = da + (uint64_t)kk * a_kstep;
+                                for (int rb = 0; rb < a.RB; ++rb, da_blk += a_blkstep)
+                                    ptx::mma_i8(d_tmem + (uint32_t)(rb * NT), da_blk, db + (uint64_t)kk * b_kstep, idesc, acc != 0);
+                                acc = 1u;
+                            }
                         }
                     }
                     ptx::mma_commit(empty(s));
@@ -317,6 +342,39 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             }
             ZB_TDUMP(0);
         mma_done:;
+        }
+    } else if (warp < 10 && a.direct == 2) {
+        // ------------------------------------------------------------------ 1x1 without a tensor map: copy 128 pixels x CB*16
+        // channels per stage into the form a swizzled TMA box would have: one 128-byte row per channel, 16-byte
+        // chunk k of row r stored at chunk position k ^ (r % 8).  Pixels past the image and channels past C are zero.
+        const int p = tid - 64, lw = warp - 2;
+        const int CH = a.CB * 16;
+        const uint32_t lane_off = (uint32_t)((lane & 3) * 4);
+        TcConvCursor lcur;
+        tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, lcur);
+        int s = 0; uint32_t ph = 0;
+        bool alive = true;
+        for (int t = blockIdx.x; t < tiles && alive; t += gridDim.x) {
+            const TcConvTile T = tc_conv_tile(a, lcur);
+            tc_conv_cursor_next(a, lcur);
+            const bool px_ok = T.w0 + lane * 4 < a.W;          // W % 4 == 0: a word is inside the image or outside
+            for (int cs = 0; cs < a.c_stages; ++cs) {
+                if (p == 0) ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag);      // the MMAs that read this slot are done
+                ptx::named_barrier_sync(2, 256);
+                if (*abort_flag) { alive = false; break; }
+                uint8_t* dst = sStages + (size_t)s * a.stage_bytes + a.off_patch;
+                const uint8_t* src = a.x + ((size_t)T.img * a.C + (size_t)cs * CH) * a.W + T.w0 + lane * 4;
+#pragma unroll 4
+                for (int rr = lw; rr < CH; rr += 8) {
+                    uint32_t v = 0;
+                    if (px_ok && cs * CH + rr < a.C) v = __ldg(reinterpret_cast<const uint32_t*>(src + (size_t)rr * a.W));
+                    *reinterpret_cast<uint32_t*>(dst + rr * 128 + ((((uint32_t)lane >> 2) ^ ((uint32_t)rr & 7u)) << 4) + lane_off) = v;
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::named_barrier_sync(2, 256);
+                if (p == 0) ptx::mbar_arrive(full(s));
+                if (++s == S) { s = 0; ph ^= 1u; }
+            }
         }
     } else if (warp < 10 && !a.direct) {
         // ------------------------------------------------------------------ transpose: staging -> patch (256 threads)
@@ -418,7 +476,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         // ------------------------------------------------------------------ epilogue: warps 10..17, and for 1x1
         // convolutions also warps 2..9, which have nothing to transpose.  Each TMEM lane quarter is served by
         // n_epi / 4 warps that split the tile's filters.
-        const int n_epi = a.direct ? 16 : 8;
+        const int n_epi = a.direct == 1 ? 16 : 8;
         const int ew = warp >= 10 ? warp - 10 : warp + 6;     // 0..7, then 8..15
         const int quarter = warp & 3;
         const int part = ew >> 2;
@@ -443,6 +501,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         const int co_c0 = ew * co_cpp + (lane >> co_shift), co_v0 = lane & (co_lpc - 1);
         const size_t co_dst_step = (size_t)(n_epi * co_cpp) * ohw;
         int tile_it = 0;
+        int blk_it = 0;                                        // row blocks done: parity selects the output staging buffer
         TcConvCursor ecur;
         tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, ecur);
         ZB_TDECL(); ZB_T0();
@@ -458,8 +517,12 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             ZB_TACC(1);
             ptx::tc_fence_after();
             const int tcol0 = part * cols;
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * NT + tcol0);
-            uint8_t* ob = sOut + (size_t)b * NT * kTcConvOutPitch;
+            // row blocks of the tile, one after the other; those below the image's last row do not exist
+            const int n_blk = min(a.RB, (a.OH - T.h0 + a.BH - 1) / a.BH);
+            for (int rb = 0; rb < n_blk; ++rb, ++blk_it) {
+            const int hb = T.h0 + rb * a.BH;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((b * a.RB + rb) * NT + tcol0);
+            uint8_t* ob = sOut + (size_t)(blk_it & 1) * NT * kTcConvOutPitch;
             uint8_t* orow = ob + (size_t)tcol0 * kTcConvOutPitch + pix_off;
 #pragma unroll 1
             for (int h = 0; h < cols / 16; ++h) {
@@ -502,19 +565,23 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                     }
                 }
             }
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(tempty(b));          // the accumulator is free again
+            if (rb == n_blk - 1) {
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(tempty(b));      // the tile's accumulators are free again
+            }
             ZB_TACC(2);
-            ptx::named_barrier_sync(1, n_epi * 32);              // the tile's bytes are staged
+            // The block's bytes are staged.  The staging buffer written two blocks later is this one: every
+            // thread has left this block's copy-out before it reaches the next block's barrier.
+            ptx::named_barrier_sync(1, n_epi * 32);
             ZB_TACC(3);
 
             // copy-out: per filter one contiguous run of the NCHW output
             const int ncv = min(NT, a.M - T.nt * NT);
-            const int L = a.wseg == 1 ? min(a.BH, a.OH - T.h0) * a.OW : min(a.BW, a.OW - T.w0);
+            const int L = a.wseg == 1 ? min(a.BH, a.OH - hb) * a.OW : min(a.BW, a.OW - T.w0);
             const int nvec = L >> a.log2V, tail_bytes = L - (nvec << a.log2V);
             const int slots = nvec + (tail_bytes ? 1 : 0);
-            uint8_t* dst = a.y + ((size_t)T.img * a.M + (size_t)(T.nt * NT + co_c0)) * ohw + (size_t)T.h0 * a.OW + T.w0;
+            uint8_t* dst = a.y + ((size_t)T.img * a.M + (size_t)(T.nt * NT + co_c0)) * ohw + (size_t)hb * a.OW + T.w0;
             const uint8_t* src = ob + co_c0 * kTcConvOutPitch;
             for (int c = co_c0; c < ncv; c += n_epi * co_cpp, dst += co_dst_step, src += n_epi * co_cpp * kTcConvOutPitch) {
                 for (int vv = co_v0; vv < slots; vv += co_lpc) {
@@ -531,6 +598,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                 }
             }
             ZB_TACC(4);
+            }
         }
         if (e == 32) ZB_TDUMP(16);
     }
@@ -540,7 +608,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     }
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == 1) ptx::tmem_dealloc(tmem_base, 2 * NT);
+    if (warp == 1) ptx::tmem_dealloc(tmem_base, 2 * a.RB * NT);
     if (tid == 0 && *abort_flag) atomicExch(a.status, (int)DEV_ERR_WAIT_TIMEOUT);
 }
 
@@ -578,34 +646,15 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
     a.BW = std::min(a.OW, 128 - halo_w);
     a.PW = a.BW + halo_w;
     a.BH = std::max(1, std::min(a.OH, 128 / a.PW));
-    a.PH = a.BH + halo_h;
-    a.PR = (128 + halo_h * a.PW + halo_w + 7) / 8 * 8 + 1;   // 1 mod 8: the channel groups of a pixel fall into different banks
     a.wseg = (a.OW + a.BW - 1) / a.BW;
-    a.hseg = (a.OH + a.BH - 1) / a.BH;
     a.full_width = a.wseg == 1 ? 1 : 0;
     a.direct = pointwise ? 1 : 0;
-    // the bulk copies start at 16-byte boundaries; every channel of a stage must see the same offset
-    if (((long long)a.H * a.W) % 16 != 0) return false;
-    if (!a.full_width && a.W % 16 != 0) return false;
-    if (a.direct) {
-        a.RP = 128; a.CP = 128; a.KN = 1;               // the box row is the operand row: 128 pixels of one channel
-    } else if (a.full_width) {
-        a.RP = a.W;
-        a.CP = (a.PH * a.W + 15 + 15) / 16 * 16;        // box row: the run plus its alignment slack
-        if (a.CP > 1024) return false;                  // box rows hold at most 256 four-byte elements
-        const int s0 = ((-a.pl) % 4 + 4) % 4;
-        a.KN = ((s0 + a.PW - 1) >> 2) + 1;
-    } else {
-        a.RP = (a.PW + 15 + 15) / 16 * 16;
-        a.CP = a.PH * a.RP;
-        if (a.PH > 256) return false;
-        a.KN = 1;
-        for (int ws = 0; ws < a.wseg; ++ws) {   // most staging words any tile's patch row spans
-            const int w_in0 = ws * a.BW - a.pl, lo = std::max(w_in0, 0);
-            const int s0 = (lo & 15) + w_in0 - lo;
-            a.KN = std::max(a.KN, ((s0 + a.PW - 1) >> 2) - (s0 >> 2) + 1);
-        }
+    // the TMA boxes start at 16-byte boundaries; every channel of a stage must see the same offset
+    if (((long long)a.H * a.W) % 16 != 0) {
+        if (!pointwise) return false;
+        a.direct = 2;          // no tensor map over planes of such a size (W % 4 == 0 holds): the rows are copied with plain loads
     }
+    if (!a.direct && !a.full_width && a.W % 16 != 0) return false;
     p.NT = g.M <= 64 ? 64 : 128;
     if (pointwise && g.M > 128) p.NT = 256;
     a.m_pad = (g.M + p.NT - 1) / p.NT * p.NT;
@@ -613,35 +662,71 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
     const int taps = a.KH * a.KW;
     const int out_bytes = 2 * p.NT * kTcConvOutPitch;
     const int budget = 232448 - kTcConvTail - out_bytes - 1024;
-    // Shared-memory plan.  Preference: 64 channels per stage over 32 (fewer hand-offs per byte), weights
-    // resident over streamed (possible when there is one filter tile: no re-fetch per tile), at least 3 stages.
+    const int blocks_in_image = (a.OH + a.BH - 1) / a.BH;
+    const TcConvArgs base = a;
+    // Row blocks per tile: the more blocks share a patch, the fewer halo rows are fetched and transposed
+    // (a 3x3 filter on a 56-wide image: 4 input rows per 2 output rows with one block, 10 per 8 with four).
+    // The accumulators of a tile take RB * NT TMEM columns, twice (double buffering), out of 512.  A count
+    // that wastes more than an eighth of the last tile's blocks, or that does not fit, gives way to a smaller one.
     bool placed = false;
-    for (int min_stages = 3; min_stages >= 2 && !placed; --min_stages)
-        for (int cb = (a.C > 64 ? 8 : (a.C > 32 ? 4 : 2)); cb >= 2 && !placed; cb /= 2)
-            for (int resident = 1; resident >= 0 && !placed; --resident) {
-                const int c_stages = (a.C + cb * 16 - 1) / (cb * 16);
-                const int w_stage = taps * cb * p.NT * 16;
-                const long long w_all = (long long)c_stages * w_stage;
-                if (resident && (a.n_tiles != 1 || w_all > 112 * 1024)) continue;
-                const int off_patch = resident ? 0 : w_stage;
-                int off_stg, stage_bytes;
-                if (a.direct) {       // operand tile = TMA destination: 1024-byte aligned, no staging
-                    off_stg = off_patch;
-                    stage_bytes = (off_patch + cb * 16 * 128 + 1023) / 1024 * 1024;
-                } else {
-                    off_stg = (off_patch + cb * a.PR * 16 + 127) / 128 * 128;   // TMA destination
-                    stage_bytes = (off_stg + cb * 16 * a.CP + 128 + 127) / 128 * 128;   // + 128: the transposes may read a few bytes past the last channel
-                }
-                const int stages = std::min<long long>(kTcConvMaxStages, (budget - (resident ? w_all : 0)) / stage_bytes);
-                if (stages < min_stages) continue;
-                a.CB = cb; a.c_stages = c_stages; a.w_resident = resident; a.off_patch = off_patch; a.off_stg = off_stg;
-                a.stage_bytes = stage_bytes; a.stages = stages;
-                a.off_wres = stages * stage_bytes;
-                a.off_out = a.off_wres + (resident ? (int)w_all : 0);
-                placed = true;
+    for (int rb = (a.direct || halo_h == 0) ? 1 : 4; rb >= 1 && !placed; rb /= 2) {
+        if (2 * rb * p.NT > 512 || (rb > 1 && rb > blocks_in_image)) continue;
+        a = base;
+        a.RB = rb; a.BHT = rb * a.BH;
+        a.PH = a.BHT + halo_h;
+        a.hseg = (a.OH + a.BHT - 1) / a.BHT;
+        if (rb > 1 && (long long)a.hseg * rb * 7 > (long long)blocks_in_image * 8) continue;
+        // patch pixels a 16-channel group holds: the last block's 128 MMA rows plus the filter's reach;
+        // 1 mod 8, so that the channel groups of a pixel fall into different banks
+        a.PR = ((rb - 1) * a.BH * a.PW + 128 + halo_h * a.PW + halo_w + 7) / 8 * 8 + 1;
+        if (a.direct) {
+            a.RP = 128; a.CP = 128; a.KN = 1;               // the box row is the operand row: 128 pixels of one channel
+        } else if (a.full_width) {
+            a.RP = a.W;
+            a.CP = (a.PH * a.W + 15 + 15) / 16 * 16;        // box row: the run plus its alignment slack
+            if (a.CP > 1024) continue;                      // box rows hold at most 256 four-byte elements
+            const int s0 = ((-a.pl) % 4 + 4) % 4;
+            a.KN = ((s0 + a.PW - 1) >> 2) + 1;
+        } else {
+            a.RP = (a.PW + 15 + 15) / 16 * 16;
+            a.CP = a.PH * a.RP;
+            if (a.PH > 256) continue;
+            a.KN = 1;
+            for (int ws = 0; ws < a.wseg; ++ws) {   // most staging words any tile's patch row spans
+                const int w_in0 = ws * a.BW - a.pl, lo = std::max(w_in0, 0);
+                const int s0 = (lo & 15) + w_in0 - lo;
+                a.KN = std::max(a.KN, ((s0 + a.PW - 1) >> 2) - (s0 >> 2) + 1);
             }
+        }
+        // Shared-memory plan.  Preference: 64 channels per stage over 32 (fewer hand-offs per byte), weights
+        // resident over streamed (possible when there is one filter tile: no re-fetch per tile), at least 3 stages.
+        for (int min_stages = 3; min_stages >= 2 && !placed; --min_stages)
+            for (int cb = (a.C > 64 ? 8 : (a.C > 32 ? 4 : 2)); cb >= 2 && !placed; cb /= 2)
+                for (int resident = 1; resident >= 0 && !placed; --resident) {
+                    if (!a.direct && cb * a.PH * a.KN > 1024) continue;   // the transposers' per-thread work lists hold 4 entries
+                    const int c_stages = (a.C + cb * 16 - 1) / (cb * 16);
+                    const int w_stage = taps * cb * p.NT * 16;
+                    const long long w_all = (long long)c_stages * w_stage;
+                    if (resident && (a.n_tiles != 1 || w_all > 112 * 1024)) continue;
+                    const int off_patch = resident ? 0 : w_stage;
+                    int off_stg, stage_bytes;
+                    if (a.direct) {       // operand tile = TMA destination: 1024-byte aligned, no staging
+                        off_stg = off_patch;
+                        stage_bytes = (off_patch + cb * 16 * 128 + 1023) / 1024 * 1024;
+                    } else {
+                        off_stg = (off_patch + cb * a.PR * 16 + 127) / 128 * 128;   // TMA destination
+                        stage_bytes = (off_stg + cb * 16 * a.CP + 128 + 127) / 128 * 128;   // + 128: the transposes may read a few bytes past the last channel
+                    }
+                    const int stages = std::min<long long>(kTcConvMaxStages, (budget - (resident ? w_all : 0)) / stage_bytes);
+                    if (stages < min_stages) continue;
+                    a.CB = cb; a.c_stages = c_stages; a.w_resident = resident; a.off_patch = off_patch; a.off_stg = off_stg;
+                    a.stage_bytes = stage_bytes; a.stages = stages;
+                    a.off_wres = stages * stage_bytes;
+                    a.off_out = a.off_wres + (resident ? (int)w_all : 0);
+                    placed = true;
+                }
+    }
     if (!placed) return false;
-    if (!a.direct && a.CB * a.PH * a.KN > 1024) return false;   // the transposers' per-thread work lists hold 4 entries
     p.smem_bytes = (size_t)a.off_out + out_bytes + kTcConvTail;
     p.w_bytes = (size_t)a.n_tiles * a.c_stages * taps * a.CB * p.NT * 16;
     // one contiguous output run per filter and tile; V = widest store that every run start and length allows
@@ -649,7 +734,7 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
     a.V = a.wseg == 1 ? tc_gcd(ohw_gcd, tc_gcd(16, (a.BH * a.OW) % 16 == 0 ? 16 : (a.BH * a.OW) % 16))
                       : tc_gcd(ohw_gcd, tc_gcd(tc_gcd(16, a.OW % 16 == 0 ? 16 : a.OW % 16), tc_gcd(16, a.BW % 16 == 0 ? 16 : a.BW % 16)));
     for (a.log2V = 0; (1 << a.log2V) < a.V; ++a.log2V) {}
-    p.row_efficiency = (double)a.OH * a.OW / ((double)a.hseg * a.wseg * 128.0);
+    p.row_efficiency = (double)a.OH * a.OW / ((double)a.hseg * a.RB * a.wseg * 128.0);
     const long long tiles = (long long)a.N * a.hseg * a.wseg * a.n_tiles;
     if (tiles > 0x7fffffffLL || p.row_efficiency < 0.5) return false;
     return true;
@@ -767,8 +852,8 @@ inline int32_t tc_conv_run(zant_ctx* ctx, const TcConvPlan& p, const void* x, bo
     a.status = ctx->status_word;
     const long long tiles = (long long)a.N * a.hseg * a.wseg * a.n_tiles;
     const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
-    alignas(64) CUtensorMap x_map;
-    ZB_TRY(tc_conv_encode_map(a, x, &x_map));
+    alignas(64) CUtensorMap x_map{};
+    if (a.direct != 2) ZB_TRY(tc_conv_encode_map(a, x, &x_map));
     if (p.NT == 64) return tc_conv_launch_nt<64>(ctx, p, a, x_map, grid, x_u8, lean);
     if (p.NT == 128) return tc_conv_launch_nt<128>(ctx, p, a, x_map, grid, x_u8, lean);
     return tc_conv_launch_nt<256>(ctx, p, a, x_map, grid, x_u8, lean);

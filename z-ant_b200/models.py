@@ -178,17 +178,22 @@ def qconv_case(name, batch=None, seed=DEFAULT_SEED):
 # ------------------------------------------------------------------------------------------------
 # Small graph-building helpers for the larger synthetic networks below.
 # ------------------------------------------------------------------------------------------------
-def qconv_graph(name, batch=None, seed=DEFAULT_SEED):
-    """One sweep case as a one-node graph (int8 NCHW in, int8 NCHW out); returns (graph, case)."""
+def qconv_graph(name, batch=None, seed=DEFAULT_SEED, channels_last=False):
+    """One sweep case as a one-node graph (int8 in and out); returns (graph, case).  NCHW tensors as the
+    reference has them, or, with `channels_last`, the same values as [N,H,W,C] -> [N,OH,OW,K]
+    (case["x"] is then the transposed input)."""
     c = qconv_case(name, batch, seed)
-    g = Graph("qconv_" + name)
+    g = Graph("qconv_" + name + ("_nhwc" if channels_last else ""))
     oh = (c["H"] + 2 * c["p"] - c["k"]) // c["s"] + 1
+    if channels_last:
+        c["x"] = np.ascontiguousarray(c["x"].transpose(0, 2, 3, 1))
     x = g.tensor("x", I8, c["x"].shape)
     w = g.tensor("w", I8, c["w"].shape, c["w"])
     ws = g.tensor("w_scale", F32, (1,), c["w_scale"])
-    y = g.tensor("y", I8, (c["N"], c["K"], oh, oh))
+    y = g.tensor("y", I8, (c["N"], oh, oh, c["K"]) if channels_last else (c["N"], c["K"], oh, oh))
     g.node("QLinearConv", [x, w, ws, -1, -1], [y], x_scale=c["x_scale"], x_zp=0, y_scale=c["y_scale"], y_zp=0,
-           strides=c["stride"], pads=c["pads"], dilations=c["dilations"], group=c["group"], auto_pad="NOTSET", activation=None)
+           strides=c["stride"], pads=c["pads"], dilations=c["dilations"], group=c["group"], auto_pad="NOTSET", activation=None,
+           channels_last=1 if channels_last else 0)
     g.input, g.output = x, y
     return g, c
 

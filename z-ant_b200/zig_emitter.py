@@ -48,7 +48,7 @@ def emit_static_parameters(graph):
 _ATTR_FIELDS = ("kernel_shape", "strides", "n_strides", "dilations", "n_dilations", "pads", "n_pads", "group", "auto_pad", "alpha", "beta",
                 "trans_a", "trans_b", "axis", "axes", "n_axes", "keepdims", "noop_with_empty_axes", "scales", "n_scales", "coord_mode",
                 "x_scale", "x_zp", "b_scale", "b_zp", "y_scale", "y_zp", "activation", "perm", "n_perm", "slice_starts", "slice_ends",
-                "slice_axes", "slice_steps", "n_slice", "slice_has_axes", "slice_has_steps")
+                "slice_axes", "slice_steps", "n_slice", "slice_has_axes", "slice_has_steps", "channels_last")
 
 
 def _attrs_literal(attrs):
@@ -92,6 +92,7 @@ def emit_lib(graph, model_name="model", fuse=True):
     w("    perm: [8]i64 = [_]i64{0} ** 8, n_perm: usize = 0,")
     w("    slice_starts: [8]i64 = [_]i64{0} ** 8, slice_ends: [8]i64 = [_]i64{0} ** 8, slice_axes: [8]i64 = [_]i64{0} ** 8,")
     w("    slice_steps: [8]i64 = [_]i64{0} ** 8, n_slice: usize = 0, slice_has_axes: i32 = 0, slice_has_steps: i32 = 0,")
+    w("    channels_last: i32 = 0,")
     w("};")
     w("extern fn zant_b200_ctx_create(device: i32, arena_bytes: usize, out: *?*Ctx) i32;")
     w("extern fn zant_b200_plan_create(ctx: ?*Ctx, out: *?*Plan) i32;")
