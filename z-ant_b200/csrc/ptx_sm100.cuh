@@ -154,6 +154,21 @@ __device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc), "r"(zero) : "memory");
 }
 
+// The same with the descriptors given as 32-bit halves.  The low half holds the start address (bits 0-13,
+// in 16-byte units) and the leading-dimension offset; the issuing thread of a loop over taps, K steps and
+// row blocks only ever changes the start address, so it keeps the high halves fixed and advances the low
+// ones with single 32-bit adds (shared memory is smaller than 256 KiB: the address field cannot overflow).
+// That keeps the instruction count per MMA of a data-dependent loop at a handful; 64-bit descriptor
+// arithmetic in such a loop costs more issue time than a 128x64x32 MMA takes to execute.
+__device__ __forceinline__ void mma_i8_halves(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t zero = 0u;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, {%7, %7, %7, %7}, p;\n\t}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(zero) : "memory");
+}
+
 // Arrives on the mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

@@ -197,11 +197,11 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), (a.direct == 1 || a.w_resident) ? 1 : 2); ptx::mbar_init(empty(s), 1); }
-        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), a.direct == 1 ? 16 : 8); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 8); }
         for (int s = 0; s < S; ++s) { ptx::mbar_init(ld_full(s), 1); ptx::mbar_init(ld_empty(s), 8); }
         ptx::mbar_init(wfull, 1);
         *abort_flag = 0;
-        *epi_ok = 1;
+        epi_ok[0] = 1; epi_ok[1] = 1;
         ptx::mbar_fence_init();
     }
     for (int i = tid; i < a.m_pad; i += kTcConvThreads) { sMult[i] = __ldg(a.mult + i); sBias[i] = __ldg(a.bias + i); }
@@ -287,9 +287,9 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             const uint32_t a_lbo = (uint32_t)a.PR * 16u;
             const int ksteps = a.CB / 2;
             // descriptors advance by adding 16-byte units to their address field (shared memory is < 256 KiB, no carry)
-            const uint64_t a_kstep = (uint64_t)((2u * a_lbo) >> 4), b_kstep = (uint64_t)((2u * NT * 16u) >> 4);
-            const uint64_t a_col = (uint64_t)a.dw, a_rowstep = (uint64_t)(a.dh * a.PW), a_blkstep = (uint64_t)(a.BH * a.PW);
-            const uint64_t b_tap = (uint64_t)(w_tap_bytes >> 4);
+            const uint32_t a_kstep = (2u * a_lbo) >> 4, b_kstep = (2u * NT * 16u) >> 4;
+            const uint32_t a_col = (uint32_t)a.dw, a_rowstep = (uint32_t)(a.dh * a.PW), a_blkstep = (uint32_t)(a.BH * a.PW);
+            const uint32_t b_tap = w_tap_bytes >> 4;
             int s = 0; uint32_t ph = 0;
             int tile_it = 0;
             ZB_TDECL(); ZB_T0();
@@ -306,13 +306,13 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                     ptx::tc_fence_after();
                     const uint32_t stage0 = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
                     const uint32_t sw = a.w_resident ? ptx::smem_u32(smem + a.off_wres) + (uint32_t)cs * w_stage_bytes : stage0;
-                    uint64_t db = ptx::smem_desc_kmajor(sw, NT * 16, 128);
+                    const uint64_t db0 = ptx::smem_desc_kmajor(sw, NT * 16, 128);
                     uint32_t acc = cs != 0 ? 1u : 0u;
                     if (a.direct) {
                         // A = [channel][128 pixels] rows of 128 bytes: MN-major; a K step of 32 channels is 4096 bytes
                         const uint64_t da0 = ptx::smem_desc_mnmajor_sw128(stage0 + (uint32_t)a.off_patch, (uint32_t)(a.CB * 16 * 128), 1024);
                         for (int kk = 0; kk < ksteps; ++kk) {
-                            ptx::mma_i8(d_tmem, da0 + (uint64_t)kk * 256u, db + (uint64_t)kk * b_kstep, idesc | ptx::kIdescAMnMajor, (acc | (uint32_t)kk) != 0);
+                            ptx::mma_i8(d_tmem, da0 + (uint64_t)kk * 256u, db0 + (uint64_t)(kk * b_kstep), idesc | ptx::kIdescAMnMajor, (acc | (uint32_t)kk) != 0);
                         }
                         ptx::mma_commit(empty(s));
                         if (++s == S) { s = 0; ph ^= 1u; }
@@ -322,14 +322,21 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                     // Every row block multiplies its own window of the shared patch into its own accumulator.
                     // The blocks' MMAs alternate: consecutive instructions are then independent of one another
                     // (an MMA that accumulates onto the previous one's result waits for it).
-                    uint64_t da_row = ptx::smem_desc_kmajor(stage0 + (uint32_t)a.off_patch, a_lbo, 128);
-                    for (int kh = 0; kh < a.KH; ++kh, da_row += a_rowstep) {
-                        uint64_t da = da_row;
-                        for (int kw = 0; kw < a.KW; ++kw, da += a_col, db += b_tap) {
-                            for (int kk = 0; kk < ksteps; ++kk) {
-                                uint64_t da_blk = da + (uint64_t)kk * a_kstep;
-                                for (int rb = 0; rb < a.RB; ++rb, da_blk += a_blkstep)
-                                    ptx::mma_i8(d_tmem + (uint32_t)(rb * NT), da_blk, db + (uint64_t)kk * b_kstep, idesc, acc != 0);
+                    // Only the start-address field of the descriptors changes inside the loops: 32-bit adds on the low halves.
+                    const uint64_t da0 = ptx::smem_desc_kmajor(stage0 + (uint32_t)a.off_patch, a_lbo, 128);
+                    const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+                    uint32_t a_row = (uint32_t)da0, b_lo = (uint32_t)db0;
+                    for (int kh = 0; kh < a.KH; ++kh, a_row += a_rowstep) {
+                        uint32_t a_tap = a_row;
+                        for (int kw = 0; kw < a.KW; ++kw, a_tap += a_col, b_lo += b_tap) {
+                            uint32_t a_k = a_tap, b_k = b_lo;
+                            for (int kk = 0; kk < ksteps; ++kk, a_k += a_kstep, b_k += b_kstep) {
+                                ptx::mma_i8_halves(d_tmem, a_k, a_hi, b_k, b_hi, idesc, acc);
+                                if (a.RB > 1) ptx::mma_i8_halves(d_tmem + NT, a_k + a_blkstep, a_hi, b_k, b_hi, idesc, acc);
+                                if (a.RB > 2) {
+                                    ptx::mma_i8_halves(d_tmem + 2 * NT, a_k + 2 * a_blkstep, a_hi, b_k, b_hi, idesc, acc);
+                                    ptx::mma_i8_halves(d_tmem + 3 * NT, a_k + 3 * a_blkstep, a_hi, b_k, b_hi, idesc, acc);
+                                }
                                 acc = 1u;
                             }
                         }
@@ -473,16 +480,21 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         }
         if (p == 0) ZB_TDUMP(8);
     } else {
-        // ------------------------------------------------------------------ epilogue: warps 10..17, and for 1x1
-        // convolutions also warps 2..9, which have nothing to transpose.  Each TMEM lane quarter is served by
-        // n_epi / 4 warps that split the tile's filters.
-        const int n_epi = a.direct == 1 ? 16 : 8;
-        const int ew = warp >= 10 ? warp - 10 : warp + 6;     // 0..7, then 8..15
+        // ------------------------------------------------------------------ epilogue: a group of 8 warps per tile (warps
+        // 10..17); each TMEM lane quarter is served by two warps that split the tile's filters.  In 1x1 convolutions
+        // with a TMA-fed operand warps 2..9 have nothing else to do and form a second group: the groups take
+        // alternate tiles (group g owns accumulator g and staging buffer g), so that one group's waits
+        // (accumulator ready, TMEM loads, barriers, stores) overlap the other's arithmetic.
+        constexpr int n_epi = 8;
+        const int n_grp = a.direct == 1 ? 2 : 1;
+        const int grp = warp >= 10 ? 0 : 1;
+        const int ew = warp >= 10 ? warp - 10 : warp - 2;     // 0..7 within the group
         const int quarter = warp & 3;
         const int part = ew >> 2;
-        const int cols = NT / (n_epi >> 2);                    // filters of this warp: 16 .. 128
         const int row = quarter * 32 + lane;
         const int e = ew * 32 + lane;
+        const uint32_t epi_bar = grp == 0 ? 1u : 3u;           // named barrier of the group (2 belongs to warps 2..9 in their other roles)
+        volatile int* grp_ok = epi_ok + grp;
         const Requant rq{a.y_scale, a.y_zp, a.act};
         const int oh_l = row / a.PW, ow_l = row - oh_l * a.PW;
         const bool row_live = oh_l < a.BH && ow_l < a.BW;        // this MMA row is an output of the tile
@@ -500,70 +512,94 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         const int co_lpc = 1 << co_shift, co_cpp = 32 >> co_shift;
         const int co_c0 = ew * co_cpp + (lane >> co_shift), co_v0 = lane & (co_lpc - 1);
         const size_t co_dst_step = (size_t)(n_epi * co_cpp) * ohw;
-        int tile_it = 0;
-        int blk_it = 0;                                        // row blocks done: parity selects the output staging buffer
+        int tile_it = grp;
+        int blk_it = grp;                                      // one group: row blocks done, parity selects the staging buffer; two groups: buffer = group
+        const int t_step = n_grp * (int)gridDim.x;
         TcConvCursor ecur;
-        tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, ecur);
+        tc_conv_cursor_init(a, (int)blockIdx.x + grp * (int)gridDim.x, t_step, ecur);
         ZB_TDECL(); ZB_T0();
-        for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
+        for (int t = (int)blockIdx.x + grp * (int)gridDim.x; t < tiles; t += t_step, tile_it += n_grp) {
             const TcConvTile T = tc_conv_tile(a, ecur);
             tc_conv_cursor_next(a, ecur);
             const int b = tile_it & 1;
             const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
             ZB_TACC(0);
-            if (e == 0) *epi_ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
-            ptx::named_barrier_sync(1, n_epi * 32);
-            if (!*epi_ok) break;
+            if (e == 0) *grp_ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
+            ptx::named_barrier_sync(epi_bar, n_epi * 32);       // also: the group's previous copy-out has left the staging buffer
+            if (!*grp_ok) break;
             ZB_TACC(1);
             ptx::tc_fence_after();
-            const int tcol0 = part * cols;
+            // the tile's real filters, in chunks of 16, split evenly between the two warps of a lane quarter
+            const int n_chunks = (min(NT, a.M - T.nt * NT) + 15) >> 4;
+            const int h_lo = part ? (n_chunks + 1) >> 1 : 0, h_hi = part ? n_chunks : (n_chunks + 1) >> 1;
             // row blocks of the tile, one after the other; those below the image's last row do not exist
             const int n_blk = min(a.RB, (a.OH - T.h0 + a.BH - 1) / a.BH);
-            for (int rb = 0; rb < n_blk; ++rb, ++blk_it) {
+            for (int rb = 0; rb < n_blk; ++rb, blk_it += (n_grp == 1 ? 1 : 0)) {
             const int hb = T.h0 + rb * a.BH;
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((b * a.RB + rb) * NT + tcol0);
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((b * a.RB + rb) * NT);
             uint8_t* ob = sOut + (size_t)(blk_it & 1) * NT * kTcConvOutPitch;
-            uint8_t* orow = ob + (size_t)tcol0 * kTcConvOutPitch + pix_off;
+            uint8_t* orow = ob + pix_off;
 #pragma unroll 1
-            for (int h = 0; h < cols / 16; ++h) {
-                const int col0 = T.nt * NT + tcol0 + h * 16;
-                if (col0 >= a.M) break;                              // the rest of the tile is filter padding
+            for (int h = h_lo; h < h_hi; ++h) {
+                const int col0 = T.nt * NT + h * 16;                 // filters past M in the last chunk are padding: staged, never copied out
                 uint32_t v[16];
+                ZB_TSUB0();
                 ptx::tmem_ld16(taddr + (uint32_t)(h * 16), v);
                 ptx::tmem_wait_ld();
+                ZB_TSUB(5);
                 uint8_t* oc = orow + (size_t)h * 16 * kTcConvOutPitch;
+                // All loads and arithmetic of the chunk come before its first store: the byte stores may alias anything
+                // in the compiler's eyes, and loads placed after them would wait for them, one group of four at a time.
+                uint32_t pk[4];
                 if constexpr (LEAN) {
+                    float4 m4[4]; int4 b4[4];
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; ++j4) {
+                        m4[j4] = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
+                        b4[j4] = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
+                    }
                     auto lean_chunk = [&](auto clamp) {
                         constexpr bool CL = decltype(clamp)::value;
 #pragma unroll
                         for (int j4 = 0; j4 < 4; ++j4) {
-                            const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
-                            const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
-                            const int q0 = tc_conv_round<CL>((int)v[j4 * 4 + 0] + b4.x, m4.x);
-                            const int q1 = tc_conv_round<CL>((int)v[j4 * 4 + 1] + b4.y, m4.y);
-                            const int q2 = tc_conv_round<CL>((int)v[j4 * 4 + 2] + b4.z, m4.z);
-                            const int q3 = tc_conv_round<CL>((int)v[j4 * 4 + 3] + b4.w, m4.w);
-                            uint32_t pk = pack_sat_s8x4(q0, q1, q2, q3);
-                            if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
-                            if (a.act == ZANT_QACT_RELU6) pk = __vmins4(pk, six4);
-                            if (row_live) {
-                                oc[(j4 * 4 + 0) * kTcConvOutPitch] = (uint8_t)pk;
-                                oc[(j4 * 4 + 1) * kTcConvOutPitch] = (uint8_t)(pk >> 8);
-                                oc[(j4 * 4 + 2) * kTcConvOutPitch] = (uint8_t)(pk >> 16);
-                                oc[(j4 * 4 + 3) * kTcConvOutPitch] = (uint8_t)(pk >> 24);
-                            }
+                            const int q0 = tc_conv_round<CL>((int)v[j4 * 4 + 0] + b4[j4].x, m4[j4].x);
+                            const int q1 = tc_conv_round<CL>((int)v[j4 * 4 + 1] + b4[j4].y, m4[j4].y);
+                            const int q2 = tc_conv_round<CL>((int)v[j4 * 4 + 2] + b4[j4].z, m4[j4].z);
+                            const int q3 = tc_conv_round<CL>((int)v[j4 * 4 + 3] + b4[j4].w, m4[j4].w);
+                            uint32_t w4 = pack_sat_s8x4(q0, q1, q2, q3);
+                            if (a.act != ZANT_QACT_NONE) w4 = relu_s8x4(w4);
+                            if (a.act == ZANT_QACT_RELU6) w4 = __vmins4(w4, six4);
+                            pk[j4] = w4;
                         }
                     };
                     if (a.small_products) lean_chunk(std::false_type{});
                     else lean_chunk(std::true_type{});
                 } else {
+                    float mv[16]; int bv[16];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int acc = (int)v[j] + sBias[col0 + j];
-                        const int q = a.out_u8 ? requant_one<true>(acc, sMult[col0 + j], rq) : requant_one<false>(acc, sMult[col0 + j], rq);
-                        if (row_live) oc[j * kTcConvOutPitch] = (uint8_t)q;
+                    for (int j = 0; j < 16; ++j) { mv[j] = sMult[col0 + j]; bv[j] = sBias[col0 + j]; }
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; ++j4) {
+                        uint32_t w4 = 0;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int acc = (int)v[j4 * 4 + j] + bv[j4 * 4 + j];
+                            const int q = a.out_u8 ? requant_one<true>(acc, mv[j4 * 4 + j], rq) : requant_one<false>(acc, mv[j4 * 4 + j], rq);
+                            w4 |= (uint32_t)(q & 255) << (8 * j);
+                        }
+                        pk[j4] = w4;
                     }
                 }
+                if (row_live) {
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; ++j4) {
+                        oc[(j4 * 4 + 0) * kTcConvOutPitch] = (uint8_t)pk[j4];
+                        oc[(j4 * 4 + 1) * kTcConvOutPitch] = (uint8_t)(pk[j4] >> 8);
+                        oc[(j4 * 4 + 2) * kTcConvOutPitch] = (uint8_t)(pk[j4] >> 16);
+                        oc[(j4 * 4 + 3) * kTcConvOutPitch] = (uint8_t)(pk[j4] >> 24);
+                    }
+                }
+                ZB_TSUB(6);
             }
             if (rb == n_blk - 1) {
                 ptx::tc_fence_before();
@@ -573,7 +609,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             ZB_TACC(2);
             // The block's bytes are staged.  The staging buffer written two blocks later is this one: every
             // thread has left this block's copy-out before it reaches the next block's barrier.
-            ptx::named_barrier_sync(1, n_epi * 32);
+            ptx::named_barrier_sync(epi_bar, n_epi * 32);
             ZB_TACC(3);
 
             // copy-out: per filter one contiguous run of the NCHW output

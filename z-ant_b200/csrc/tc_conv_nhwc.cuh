@@ -127,6 +127,9 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
             constexpr uint32_t idesc = ptx::idesc_i8(128, NT, !XU8, true);
             const int ksteps = KC / 32;
             const uint32_t row_bytes = (uint32_t)KC;
+            const uint32_t row_units = row_bytes >> 4;                          // descriptor address units per patch row
+            const uint32_t a_col = (uint32_t)a.dw * row_units, a_rowstep = (uint32_t)(a.dh * a.PW) * row_units;
+            const uint32_t a_blkstep = (uint32_t)(a.BH * a.PW) * row_units, b_tap = w_tap_bytes >> 4;
             int s = 0; uint32_t ph = 0;
             int tile_it = 0;
             if (a.w_resident && !ptx::mbar_wait(wfull, 0, abort_flag)) goto mma_done;
@@ -139,18 +142,24 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
                     if (!ptx::mbar_wait(full(s), ph, abort_flag)) goto mma_done;
                     ptx::tc_fence_after();
                     const uint32_t stage0 = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
-                    uint32_t sw = a.w_resident ? ptx::smem_u32(smem + a.off_wres) + (uint32_t)cs * w_stage_bytes : stage0;
-                    const uint32_t pa = stage0 + (uint32_t)a.off_patch;
+                    const uint32_t sw = a.w_resident ? ptx::smem_u32(smem + a.off_wres) + (uint32_t)cs * w_stage_bytes : stage0;
                     uint32_t acc = cs != 0 ? 1u : 0u;
-                    for (int kh = 0; kh < a.KH; ++kh) {
-                        for (int kw = 0; kw < a.KW; ++kw, sw += w_tap_bytes) {
-                            const uint32_t tap_row = (uint32_t)(kh * a.dh * a.PW + kw * a.dw);
-                            for (int kk = 0; kk < ksteps; ++kk) {
-                                const uint64_t db = smem_desc_kmajor_swizzled(sw + (uint32_t)kk * 32u, row_bytes);
-                                // the row blocks' MMAs alternate, so that consecutive instructions do not depend on one another
-                                for (int rb = 0; rb < a.RB; ++rb) {
-                                    const uint32_t addr = pa + (tap_row + (uint32_t)(rb * a.BH * a.PW)) * row_bytes + (uint32_t)kk * 32u;
-                                    ptx::mma_i8(d_tmem + (uint32_t)(rb * NT), smem_desc_kmajor_swizzled(addr, row_bytes), db, idesc, acc != 0);
+                    // Only the start-address field (16-byte units) of the descriptors changes inside the loops: 32-bit adds
+                    // on the low halves.  The row blocks' MMAs alternate, so that consecutive instructions are independent.
+                    const uint64_t da0 = smem_desc_kmajor_swizzled(stage0 + (uint32_t)a.off_patch, row_bytes);
+                    const uint64_t db0 = smem_desc_kmajor_swizzled(sw, row_bytes);
+                    const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+                    uint32_t a_row = (uint32_t)da0, b_lo = (uint32_t)db0;
+                    for (int kh = 0; kh < a.KH; ++kh, a_row += a_rowstep) {
+                        uint32_t a_tap = a_row;
+                        for (int kw = 0; kw < a.KW; ++kw, a_tap += a_col, b_lo += b_tap) {
+                            uint32_t a_k = a_tap, b_k = b_lo;
+                            for (int kk = 0; kk < ksteps; ++kk, a_k += 2u, b_k += 2u) {        // a K step is 32 bytes
+                                ptx::mma_i8_halves(d_tmem, a_k, a_hi, b_k, b_hi, idesc, acc);
+                                if (a.RB > 1) ptx::mma_i8_halves(d_tmem + NT, a_k + a_blkstep, a_hi, b_k, b_hi, idesc, acc);
+                                if (a.RB > 2) {
+                                    ptx::mma_i8_halves(d_tmem + 2 * NT, a_k + 2 * a_blkstep, a_hi, b_k, b_hi, idesc, acc);
+                                    ptx::mma_i8_halves(d_tmem + 3 * NT, a_k + 3 * a_blkstep, a_hi, b_k, b_hi, idesc, acc);
                                 }
                                 acc = 1u;
                             }
