@@ -132,14 +132,17 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
             const uint32_t a_blkstep = (uint32_t)(a.BH * a.PW) * row_units, b_tap = w_tap_bytes >> 4;
             int s = 0; uint32_t ph = 0;
             int tile_it = 0;
+            ZB_TDECL(); ZB_T0();
             if (a.w_resident && !ptx::mbar_wait(wfull, 0, abort_flag)) goto mma_done;
             for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
                 const int b = tile_it & 1;
                 const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
                 if (!ptx::mbar_wait(tempty(b), bph ^ 1u, abort_flag)) goto mma_done;
+                ZB_TACC(0);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * a.RB * NT);
                 for (int cs = 0; cs < a.c_stages; ++cs) {
                     if (!ptx::mbar_wait(full(s), ph, abort_flag)) goto mma_done;
+                    ZB_TACC(1);
                     ptx::tc_fence_after();
                     const uint32_t stage0 = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
                     const uint32_t sw = a.w_resident ? ptx::smem_u32(smem + a.off_wres) + (uint32_t)cs * w_stage_bytes : stage0;
@@ -167,9 +170,11 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
                     }
                     ptx::mma_commit(empty(s));
                     if (++s == S) { s = 0; ph ^= 1u; }
+                    ZB_TACC(2);
                 }
                 ptx::mma_commit(tfull(b));
             }
+            ZB_TDUMP(0);
         mma_done:;
         }
     } else {
@@ -185,16 +190,28 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
         const bool row_live = oh_l < a.BH && ow_l < a.BW;
         const uint32_t six4 = 0x01010101u * (uint32_t)(a.six & 255);
         const int tcol0 = part * cols;
+        // With one 64-filter tile a warp serves the same 16 filters in every tile: their constants stay in registers
+        // (as broadcast shared-memory loads they would take about a third of the shared-memory pipe's time, which the
+        // tensor core's operand fetches need).
+        constexpr bool kRegConsts = NT == 64 && LEAN;
+        float rm[kRegConsts ? 16 : 1]; int rbias[kRegConsts ? 16 : 1];
+        if constexpr (kRegConsts) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { rm[j] = sMult[tcol0 + j]; rbias[j] = sBias[tcol0 + j]; }
+        }
         int tile_it = 0;
         TcConvCursor ecur;
         tc_conv_cursor_init(a, (int)blockIdx.x, (int)gridDim.x, ecur);
+        ZB_TDECL(); ZB_T0();
         for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
             const TcConvTile T = tc_conv_tile(a, ecur);
             tc_conv_cursor_next(a, ecur);
             const int b = tile_it & 1;
             const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
+            ZB_TACC(0);
             const bool arrived = ptx::mbar_wait(tfull(b), bph, abort_flag);
             if (!__all_sync(0xffffffffu, arrived)) break;                // a time-out ends the whole warp together
+            ZB_TACC(1);
             ptx::tc_fence_after();
             const int n_blk = min(a.RB, (a.OH - T.h0 + a.BH - 1) / a.BH);
             const int ow = T.w0 + ow_l;
@@ -216,8 +233,14 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
                             constexpr bool CL = decltype(clamp)::value;
 #pragma unroll
                             for (int j4 = 0; j4 < 4; ++j4) {
-                                const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
-                                const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
+                                float4 m4; int4 b4;
+                                if constexpr (kRegConsts) {
+                                    m4 = make_float4(rm[j4 * 4], rm[j4 * 4 + 1], rm[j4 * 4 + 2], rm[j4 * 4 + 3]);
+                                    b4 = make_int4(rbias[j4 * 4], rbias[j4 * 4 + 1], rbias[j4 * 4 + 2], rbias[j4 * 4 + 3]);
+                                } else {
+                                    m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
+                                    b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
+                                }
                                 uint32_t pk = pack_sat_s8x4(tc_conv_round<CL>((int)v[j4 * 4 + 0] + b4.x, m4.x), tc_conv_round<CL>((int)v[j4 * 4 + 1] + b4.y, m4.y),
                                                             tc_conv_round<CL>((int)v[j4 * 4 + 2] + b4.z, m4.z), tc_conv_round<CL>((int)v[j4 * 4 + 3] + b4.w, m4.w));
                                 if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
@@ -247,7 +270,9 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(tempty(b));          // this warp has read its part of the tile's accumulators
+            ZB_TACC(2);
         }
+        if (warp == 2 && lane == 0) ZB_TDUMP(16);
     }
 
     if (*abort_flag) {
