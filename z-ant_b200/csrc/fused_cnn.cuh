@@ -64,6 +64,7 @@ struct Conv1MmaArgs {
     const uint32_t* wfrag;   // [4 members][4 groups][32 lanes] B-fragment words
     const int32_t* biasfrag; // [4 groups][32 lanes][2]  (bias - x_zp * sum(w)) of the lane's two columns
     const float* multfrag;   // [4 groups][32 lanes][2]
+    int* status;             // device status word: DEV_ERR_WAIT_TIMEOUT when a bounded wait gave up
 };
 
 __device__ __forceinline__ void mma_m16n8k16_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, const int (&c)[4]) {
@@ -76,14 +77,37 @@ constexpr int C1M_G = 3;               // images per CTA iteration: 507 pooled p
 constexpr int C1M_THREADS = 256;
 constexpr int C1M_UNITS = (C1M_G * 169 + 15) / 16;
 
-__global__ void __launch_bounds__(C1M_THREADS) conv1_mma_relu_pool_kernel(const Conv1MmaArgs a) {
-    __shared__ uint32_t img[C1M_G][28][8];   // quantized uint8 rows of 32 bytes (28 pixels + 4 pad)
+constexpr int C1M_IMG_FLOATS = 28 * 28;
+constexpr int C1M_GROUP_BYTES = C1M_G * C1M_IMG_FLOATS * 4;   // 9408: a multiple of 16, as the bulk copy wants
+
+// The float images of a group arrive by one bulk async copy into a two-deep shared-memory ring: the copy
+// of group i+1 is issued when the MMA phase of group i starts, so no thread waits on global loads.  The
+// quantized bytes are double-buffered too, which leaves one __syncthreads per group.
+// Four CTAs per SM (64 registers per thread): measured faster than three at 80 registers.
+__global__ void __launch_bounds__(C1M_THREADS, 4) conv1_mma_relu_pool_kernel(const Conv1MmaArgs a) {
+    __shared__ __align__(128) float stage[2][C1M_G * C1M_IMG_FLOATS];
+    __shared__ uint32_t img2[2][C1M_G][28][8];   // quantized uint8 rows of 32 bytes (28 pixels + 4 pad)
+    __shared__ __align__(8) uint64_t bars[2];
+    __shared__ int abort_flag;
     // Per pooled pixel of an iteration (the same in every iteration): x = word of img that holds the patch's
     // first byte | odd column << 16 | image within the group << 17 | exists << 19; y = byte offset of the
     // pixel's first 16-channel chunk from the group's first image.  Keeps divisions out of the main loop.
     __shared__ uint2 pix_tab[C1M_UNITS * 16];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
+    const int stride = gridDim.x * C1M_G;
+    const uint32_t bar0 = ptx::smem_u32(&bars[0]);
+    if (tid == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(bar0, 1); ptx::mbar_init(bar0 + 8, 1);
+        ptx::mbar_fence_init();
+        const int base = blockIdx.x * C1M_G;
+        if (base < a.n_images) {
+            const uint32_t bytes = (uint32_t)min(C1M_G, a.n_images - base) * (C1M_IMG_FLOATS * 4);
+            ptx::mbar_arrive_expect_tx(bar0, bytes);
+            ptx::bulk_g2s(ptx::smem_u32(&stage[0][0]), a.x + (size_t)base * C1M_IMG_FLOATS, bytes, bar0);
+        }
+    }
     for (int i = tid; i < C1M_UNITS * 16; i += C1M_THREADS) {
         const bool exists = i < C1M_G * 169;
         const int pc = exists ? i : 0;
@@ -101,14 +125,22 @@ __global__ void __launch_bounds__(C1M_THREADS) conv1_mma_relu_pool_kernel(const 
     for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int b = 0; b < 2; ++b) { bias[j][b] = __ldg(a.biasfrag + (j * 32 + lane) * 2 + b); mult[j][b] = __ldg(a.multfrag + (j * 32 + lane) * 2 + b); }
+    __syncthreads();                               // barriers and the abort flag are set up
 
-    for (int base = blockIdx.x * C1M_G; base < a.n_images; base += gridDim.x * C1M_G) {
+    int it = 0;
+    for (int base = blockIdx.x * C1M_G; base < a.n_images; base += stride, ++it) {
+        const int s = it & 1;
+        // ---- the group's floats have landed (bounded wait; after a time-out the results are void and the
+        //      status word says so)
+        ptx::mbar_wait(bar0 + 8 * s, (uint32_t)(it >> 1) & 1u, &abort_flag);
         // ---- quantize C1M_G images: float4 in, four uint8 out
+        uint32_t (*img)[28][8] = img2[s];
+        const int n_here = min(C1M_G, a.n_images - base);
         for (int i = tid; i < C1M_G * 196; i += C1M_THREADS) {
             const int gi = i / 196, p4 = i - gi * 196;        // 196 float4 per image, 7 per row
             uint32_t word = 0;
-            if (base + gi < a.n_images) {
-                const float4 v = __ldg(reinterpret_cast<const float4*>(a.x + (size_t)(base + gi) * 784) + p4);
+            if (gi < n_here) {
+                const float4 v = reinterpret_cast<const float4*>(stage[s])[i];
                 const int q0 = sat_q<true>(rne_clamped(__fdiv_rn(v.x, a.x_scale)) + a.x_zp);
                 const int q1 = sat_q<true>(rne_clamped(__fdiv_rn(v.y, a.x_scale)) + a.x_zp);
                 const int q2 = sat_q<true>(rne_clamped(__fdiv_rn(v.z, a.x_scale)) + a.x_zp);
@@ -119,6 +151,14 @@ __global__ void __launch_bounds__(C1M_THREADS) conv1_mma_relu_pool_kernel(const 
             img[gi][r][c4] = word;
         }
         __syncthreads();
+        // ---- every thread is done with the other ring slot (it was read one group ago): refill it
+        if (tid == 0 && base + stride < a.n_images) {
+            const int nb = base + stride;
+            const uint32_t bytes = (uint32_t)min(C1M_G, a.n_images - nb) * (C1M_IMG_FLOATS * 4);
+            const uint32_t bar = bar0 + 8 * (s ^ 1);
+            ptx::mbar_arrive_expect_tx(bar, bytes);
+            ptx::bulk_g2s(ptx::smem_u32(&stage[s ^ 1][0]), a.x + (size_t)nb * C1M_IMG_FLOATS, bytes, bar);
+        }
         // ---- 16 pooled pixels per warp iteration
         for (int u = warp; u < C1M_UNITS; u += C1M_THREADS / 32) {
             bool ok[2]; uint32_t afrag[2], out_off[2];
@@ -157,8 +197,8 @@ __global__ void __launch_bounds__(C1M_THREADS) conv1_mma_relu_pool_kernel(const 
                 *reinterpret_cast<uint2*>(yo) = make_uint2(outw[h][0], outw[h][1]);
             }
         }
-        __syncthreads();
     }
+    if (tid == 0 && abort_flag) atomicExch(a.status, (int)DEV_ERR_WAIT_TIMEOUT);
 }
 
 // =============================================================================================

@@ -1105,7 +1105,7 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
         Conv1MmaArgs k{};
         k.x = pl->p<float>(x); k.y = (int8_t*)pl->scratch(s_pool1); k.n_images = (int)B;
         k.x_scale = a1.x_scale; k.x_zp = a1.x_zp;
-        k.wfrag = (const uint32_t*)pl->aux(a_wf); k.biasfrag = (const int32_t*)pl->aux(a_bf); k.multfrag = (const float*)pl->aux(a_mf);
+        k.wfrag = (const uint32_t*)pl->aux(a_wf); k.biasfrag = (const int32_t*)pl->aux(a_bf); k.multfrag = (const float*)pl->aux(a_mf); k.status = ctx->status_word;
         const int blocks = std::min<int>((int)((B + C1M_G - 1) / C1M_G), ctx->sm_count * 8);
         conv1_mma_relu_pool_kernel<<<blocks, C1M_THREADS, 0, ctx->stream>>>(k);
         return check_launch(ctx, "conv1_mma_relu_pool_kernel");
