@@ -185,10 +185,10 @@ __global__ void __launch_bounds__(C1M_THREADS, 4) conv1_mma_relu_pool_kernel(con
                     mma_m16n8k16_u8s8(d3, afrag[0], afrag[1], wf[3][j], c);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        r[jj][k] = rq_round(max(max(d0[k], d1[k]), max(d2[k], d3[k])), mult[j][k & 1]);
+                        r[jj][k] = rq_round(__vimax_s32_relu(__vimax3_s32(d0[k], d1[k], d2[k]), d3[k]), mult[j][k & 1]);   // max of the window and ReLU: two instructions
                 }
-                outw[0][jp] = relu_s8x4(pack_sat_s8x4(r[0][0], r[0][1], r[1][0], r[1][1]));   // row g   : ch 8t+4jp .. +3
-                outw[1][jp] = relu_s8x4(pack_sat_s8x4(r[0][2], r[0][3], r[1][2], r[1][3]));   // row g+8
+                outw[0][jp] = pack_sat_s8x4(r[0][0], r[0][1], r[1][0], r[1][1]);   // row g   : ch 8t+4jp .. +3
+                outw[1][jp] = pack_sat_s8x4(r[0][2], r[0][3], r[1][2], r[1][3]);   // row g+8
             }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -237,7 +237,15 @@ struct TcConvPoolCfg {
     static constexpr int STAGES = 4;
     static constexpr int W_TAP_BYTES = 2 * COUT * 16;
     static constexpr int W_BYTES = 9 * W_TAP_BYTES;
-    static constexpr int STG_ROW = COUT + 16;                // int8 row + 16: 16-byte stores of 8 lanes hit distinct banks
+    // Staging of the requantised rows (int8).  COUT == 64: rows of 64 bytes, two per 128-byte line, the eight
+    // 16-byte slots of a line permuted per row pair (stg_chunk) so that both the row-wise stores (8 consecutive
+    // rows, one chunk index) and the pooling loads (two windows two rows apart, four chunks each) of a quarter
+    // warp touch eight distinct slots.  Otherwise rows padded by 16 bytes (conflict-free stores only).
+    static constexpr int STG_ROW = COUT == 64 ? 64 : COUT + 16;
+    __host__ __device__ static constexpr int stg_chunk(int row, int c) {     // byte offset of 16-byte chunk c of a staged row
+        if (COUT == 64) { const int k = row >> 1; return k * 128 + (((((row & 1) << 2) | c) ^ ((k & 3) | ((k & 1) << 2))) << 4); }
+        return row * STG_ROW + c * 16;
+    }
     static constexpr int STG_BYTES = 128 * STG_ROW;
     static constexpr int OFF_W = 0;
     static constexpr int OFF_A = OFF_W + W_BYTES;
@@ -261,7 +269,7 @@ struct TcConvPoolCfg {
 
 // Requires: int8 output with zero point 0, ReLU, positive finite multipliers (host-checked).
 template <int IH, int IW, int COUT>
-__global__ void __launch_bounds__(320, 1) tc_conv3x3_relu_pool_kernel(const __grid_constant__ TcConvPoolArgs a) {
+__global__ void __launch_bounds__(320, 2) tc_conv3x3_relu_pool_kernel(const __grid_constant__ TcConvPoolArgs a) {
     using Cfg = TcConvPoolCfg<IH, IW, COUT>;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sW = smem + Cfg::OFF_W;
@@ -347,13 +355,17 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_relu_pool_kernel(const __gr
         uint8_t* sStg = smem + Cfg::OFF_STG + g * Cfg::STG_BYTES;
         // this thread's pooled outputs (16 channels each): staging offset of the window's top-left
         // row and output offset
-        int stg_off[Cfg::TASKS_PER_THREAD]; int out_off[Cfg::TASKS_PER_THREAD];
+        int stg_off[Cfg::TASKS_PER_THREAD][4]; int out_off[Cfg::TASKS_PER_THREAD];   // the four members of the pool window
 #pragma unroll
         for (int k = 0; k < Cfg::TASKS_PER_THREAD; ++k) {
             const int t = e + 128 * k;
             const int q = t / Cfg::QUADS, cg = t - q * Cfg::QUADS;
             const int py = q / Cfg::PW, px = q - py * Cfg::PW;
-            stg_off[k] = (t < Cfg::TASKS) ? (2 * py * IW + 2 * px) * Cfg::STG_ROW + cg * 16 : -1;
+            const int p0 = 2 * py * IW + 2 * px;
+            stg_off[k][0] = (t < Cfg::TASKS) ? Cfg::stg_chunk(p0, cg) : -1;
+            stg_off[k][1] = Cfg::stg_chunk(p0 + 1, cg);
+            stg_off[k][2] = Cfg::stg_chunk(p0 + IW, cg);
+            stg_off[k][3] = Cfg::stg_chunk(p0 + IW + 1, cg);
             out_off[k] = a.out_blocked ? (q * Cfg::QUADS + cg) * 2048 : q * COUT + cg * 16;
         }
         const uint32_t bar_id = 1u + (uint32_t)g;
@@ -366,11 +378,13 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_relu_pool_kernel(const __gr
             ptx::tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(g * COUT);
             // requantise this row (max-pool and ReLU commute with it and are applied to the int8 values)
+            uint32_t vv[COUT / 32][32];
+#pragma unroll
+            for (int h = 0; h < COUT / 32; ++h) ptx::tmem_ld32(taddr + (uint32_t)(h * 32), vv[h]);   // all loads in flight before the one wait
+            ptx::tmem_wait_ld();
 #pragma unroll
             for (int h = 0; h < COUT / 32; ++h) {
-                uint32_t v[32];
-                ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
-                ptx::tmem_wait_ld();
+                const uint32_t (&v)[32] = vv[h];
                 uint32_t pk[8];
 #pragma unroll
                 for (int j4 = 0; j4 < 8; ++j4) {
@@ -380,9 +394,8 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_relu_pool_kernel(const __gr
                                            rq_round((int)v[j4 * 4 + 2] + a.bias[c + 2], a.mult[c + 2]),
                                            rq_round((int)v[j4 * 4 + 3] + a.bias[c + 3], a.mult[c + 3]));
                 }
-                uint4* dst = reinterpret_cast<uint4*>(sStg + row * Cfg::STG_ROW + h * 32);
-                dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                *reinterpret_cast<uint4*>(sStg + Cfg::stg_chunk(row, 2 * h)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(sStg + Cfg::stg_chunk(row, 2 * h + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
             }
             ptx::tc_fence_before();
             __syncwarp();
@@ -392,12 +405,11 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_relu_pool_kernel(const __gr
                                           : a.y + (size_t)img * Cfg::KOUT;
 #pragma unroll
             for (int k = 0; k < Cfg::TASKS_PER_THREAD; ++k) {
-                if (stg_off[k] < 0) continue;
-                const uint8_t* s0 = sStg + stg_off[k];
-                const uint4 r0 = *reinterpret_cast<const uint4*>(s0);
-                const uint4 r1 = *reinterpret_cast<const uint4*>(s0 + Cfg::STG_ROW);
-                const uint4 r2 = *reinterpret_cast<const uint4*>(s0 + IW * Cfg::STG_ROW);
-                const uint4 r3 = *reinterpret_cast<const uint4*>(s0 + (IW + 1) * Cfg::STG_ROW);
+                if (stg_off[k][0] < 0) continue;
+                const uint4 r0 = *reinterpret_cast<const uint4*>(sStg + stg_off[k][0]);
+                const uint4 r1 = *reinterpret_cast<const uint4*>(sStg + stg_off[k][1]);
+                const uint4 r2 = *reinterpret_cast<const uint4*>(sStg + stg_off[k][2]);
+                const uint4 r3 = *reinterpret_cast<const uint4*>(sStg + stg_off[k][3]);
                 uint4 o;
                 o.x = relu_s8x4(__vmaxs4(__vmaxs4(r0.x, r1.x), __vmaxs4(r2.x, r3.x)));
                 o.y = relu_s8x4(__vmaxs4(__vmaxs4(r0.y, r1.y), __vmaxs4(r2.y, r3.y)));
