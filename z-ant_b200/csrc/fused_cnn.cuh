@@ -127,6 +127,7 @@ __global__ void __launch_bounds__(C1M_THREADS, 4) conv1_mma_relu_pool_kernel(con
         for (int b = 0; b < 2; ++b) { bias[j][b] = __ldg(a.biasfrag + (j * 32 + lane) * 2 + b); mult[j][b] = __ldg(a.multfrag + (j * 32 + lane) * 2 + b); }
     __syncthreads();                               // barriers and the abort flag are set up
 
+    const float q_lo = (float)(-a.x_zp), q_hi = (float)(255 - a.x_zp);
     int it = 0;
     for (int base = blockIdx.x * C1M_G; base < a.n_images; base += stride, ++it) {
         const int s = it & 1;
@@ -141,10 +142,12 @@ __global__ void __launch_bounds__(C1M_THREADS, 4) conv1_mma_relu_pool_kernel(con
             uint32_t word = 0;
             if (gi < n_here) {
                 const float4 v = reinterpret_cast<const float4*>(stage[s])[i];
-                const int q0 = sat_q<true>(rne_clamped(__fdiv_rn(v.x, a.x_scale)) + a.x_zp);
-                const int q1 = sat_q<true>(rne_clamped(__fdiv_rn(v.y, a.x_scale)) + a.x_zp);
-                const int q2 = sat_q<true>(rne_clamped(__fdiv_rn(v.z, a.x_scale)) + a.x_zp);
-                const int q3 = sat_q<true>(rne_clamped(__fdiv_rn(v.w, a.x_scale)) + a.x_zp);
+                // sat_u8(rne(clamp(t, -512, 511)) + zp) == rne(clamp(t, -zp, 255 - zp)) + zp: the bounds are integers
+                // inside [-512, 511] and rounding is monotonic; a NaN becomes the lower bound either way.
+                const int q0 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.x, a.x_scale), q_lo), q_hi)) + a.x_zp;
+                const int q1 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.y, a.x_scale), q_lo), q_hi)) + a.x_zp;
+                const int q2 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.z, a.x_scale), q_lo), q_hi)) + a.x_zp;
+                const int q3 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.w, a.x_scale), q_lo), q_hi)) + a.x_zp;
                 word = (uint32_t)q0 | ((uint32_t)q1 << 8) | ((uint32_t)q2 << 16) | ((uint32_t)q3 << 24);
             }
             const int r = p4 / 7, c4 = p4 - r * 7;
@@ -218,9 +221,8 @@ __global__ void __launch_bounds__(C1M_THREADS, 4) conv1_mma_relu_pool_kernel(con
 constexpr int TCCONV_MAX_COUT = 128;
 struct TcConvPoolArgs {
     const int8_t* x;
-    const int8_t* w;        // [9 taps][2 chunks][COUT][16] int8
+    const int8_t* w;        // [9 taps + bias block][2 chunks][COUT][16] int8 (TcConvPoolCfg::W_BYTES)
     float mult[TCCONV_MAX_COUT];     // per output channel; read as constant-bank operands (no loads)
-    int32_t bias[TCCONV_MAX_COUT];   // already includes -x_zp * sum(w)
     int8_t* y;
     int n_images;
     float y_scale; int y_zp; int act;
@@ -236,7 +238,12 @@ struct TcConvPoolCfg {
     static constexpr int STAGE_BYTES = (IMG_BYTES + 127) / 128 * 128;
     static constexpr int STAGES = 4;
     static constexpr int W_TAP_BYTES = 2 * COUT * 16;
-    static constexpr int W_BYTES = 9 * W_TAP_BYTES;
+    // A tenth block after the nine taps holds the bias as int8 factors: the MMA issuer multiplies it with a
+    // constant block of (1, 127, 127, ...) rows, so the accumulators arrive with the bias already added and the
+    // epilogue saves one integer add per value.  Row m of the block: k = 0 the remainder r, k = 1..31 factors
+    // v with bias = r + 127 * sum(v)  (|bias| <= 127 + 31 * 127 * 127; the host checks).
+    static constexpr int W_BYTES = 10 * W_TAP_BYTES;
+    static constexpr int ONES_BYTES = 2 * 128 * 16;          // [2 chunks][128 rows][16]: K-major like an image
     // Staging of the requantised rows (int8).  COUT == 64: rows of 64 bytes, two per 128-byte line, the eight
     // 16-byte slots of a line permuted per row pair (stg_chunk) so that both the row-wise stores (8 consecutive
     // rows, one chunk index) and the pooling loads (two windows two rows apart, four chunks each) of a quarter
@@ -249,7 +256,8 @@ struct TcConvPoolCfg {
     static constexpr int STG_BYTES = 128 * STG_ROW;
     static constexpr int OFF_W = 0;
     static constexpr int OFF_A = OFF_W + W_BYTES;
-    static constexpr int OFF_STG = OFF_A + STAGES * STAGE_BYTES;   // two staging areas, one per epilogue group
+    static constexpr int OFF_ONES = OFF_A + STAGES * STAGE_BYTES;
+    static constexpr int OFF_STG = OFF_ONES + ONES_BYTES;          // two staging areas, one per epilogue group
     static constexpr int OFF_CONST = OFF_STG + 2 * STG_BYTES;      // float mult[COUT]; int bias[COUT]
     static constexpr int OFF_BAR = OFF_CONST + 2 * COUT * 4;
     static constexpr int SMEM_BYTES = OFF_BAR + 256;
@@ -267,9 +275,12 @@ struct TcConvPoolCfg {
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns must be a power of two");
 };
 
+// Three CTAs per SM (63 registers per thread, 3 x 64 KB of shared memory, 3 x 128 TMEM columns): six epilogue
+// groups per SM hide the waits of one another; measured 0.176 ms against 0.193 ms with two.
+constexpr int TCCONV_CTAS_PER_SM = 3;
 // Requires: int8 output with zero point 0, ReLU, positive finite multipliers (host-checked).
 template <int IH, int IW, int COUT>
-__global__ void __launch_bounds__(320, 2) tc_conv3x3_relu_pool_kernel(const __grid_constant__ TcConvPoolArgs a) {
+__global__ void __launch_bounds__(320, TCCONV_CTAS_PER_SM) tc_conv3x3_relu_pool_kernel(const __grid_constant__ TcConvPoolArgs a) {
     using Cfg = TcConvPoolCfg<IH, IW, COUT>;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sW = smem + Cfg::OFF_W;
@@ -296,6 +307,8 @@ __global__ void __launch_bounds__(320, 2) tc_conv3x3_relu_pool_kernel(const __gr
     }
     for (int i = tid; i < Cfg::W_BYTES / 16; i += Cfg::THREADS)
         reinterpret_cast<uint4*>(sW)[i] = __ldg(reinterpret_cast<const uint4*>(a.w) + i);
+    for (int i = tid; i < Cfg::ONES_BYTES / 16; i += Cfg::THREADS)     // the constant operand of the bias MMA
+        reinterpret_cast<uint4*>(smem + Cfg::OFF_ONES)[i] = make_uint4(i < 128 ? 0x7f7f7f01u : 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu, 0x7f7f7f7fu);
     ptx::fence_proxy_async_smem();
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -341,6 +354,8 @@ __global__ void __launch_bounds__(320, 2) tc_conv3x3_relu_pool_kernel(const __gr
                     const uint64_t db = ptx::smem_desc_kmajor(w_addr + (uint32_t)(tap * Cfg::W_TAP_BYTES), COUT * 16, 128);
                     ptx::mma_i8(d_tmem, da, db, idesc, tap > 0);
                 }
+                ptx::mma_i8(d_tmem, ptx::smem_desc_kmajor(ptx::smem_u32(smem + Cfg::OFF_ONES), 128 * 16, 128),
+                            ptx::smem_desc_kmajor(w_addr + (uint32_t)(9 * Cfg::W_TAP_BYTES), COUT * 16, 128), idesc, true);   // + bias
                 ptx::mma_commit(empty(s));    // the image's smem stage is free once these MMAs retire
                 ptx::mma_commit(tfull(b));    // ... and the accumulator is complete
             }
@@ -378,21 +393,19 @@ __global__ void __launch_bounds__(320, 2) tc_conv3x3_relu_pool_kernel(const __gr
             ptx::tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(g * COUT);
             // requantise this row (max-pool and ReLU commute with it and are applied to the int8 values)
-            uint32_t vv[COUT / 32][32];
-#pragma unroll
-            for (int h = 0; h < COUT / 32; ++h) ptx::tmem_ld32(taddr + (uint32_t)(h * 32), vv[h]);   // all loads in flight before the one wait
-            ptx::tmem_wait_ld();
 #pragma unroll
             for (int h = 0; h < COUT / 32; ++h) {
-                const uint32_t (&v)[32] = vv[h];
+                uint32_t v[32];
+                ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
+                ptx::tmem_wait_ld();
                 uint32_t pk[8];
 #pragma unroll
                 for (int j4 = 0; j4 < 8; ++j4) {
                     const int c = h * 32 + j4 * 4;     // compile-time after unrolling: constant-bank operands
-                    pk[j4] = pack_sat_s8x4(rq_round((int)v[j4 * 4 + 0] + a.bias[c + 0], a.mult[c + 0]),
-                                           rq_round((int)v[j4 * 4 + 1] + a.bias[c + 1], a.mult[c + 1]),
-                                           rq_round((int)v[j4 * 4 + 2] + a.bias[c + 2], a.mult[c + 2]),
-                                           rq_round((int)v[j4 * 4 + 3] + a.bias[c + 3], a.mult[c + 3]));
+                    pk[j4] = pack_sat_s8x4(rq_round((int)v[j4 * 4 + 0], a.mult[c + 0]),
+                                           rq_round((int)v[j4 * 4 + 1], a.mult[c + 1]),
+                                           rq_round((int)v[j4 * 4 + 2], a.mult[c + 2]),
+                                           rq_round((int)v[j4 * 4 + 3], a.mult[c + 3]));
                 }
                 *reinterpret_cast<uint4*>(sStg + Cfg::stg_chunk(row, 2 * h)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 *reinterpret_cast<uint4*>(sStg + Cfg::stg_chunk(row, 2 * h + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);

@@ -1016,7 +1016,7 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
     // ---- stage 2 parameters
     std::vector<float> m2; std::vector<int32_t> b2;
     if (!scales_of(c2, 64, m2) || !bias_of(c2, 64, b2)) return ZANT_OK;
-    std::vector<int8_t> w2arr(9 * 2 * 64 * 16);
+    std::vector<int8_t> w2arr(10 * 2 * 64 * 16);      // nine taps and the bias block (TcConvPoolCfg)
     {
         const int8_t* w = (const int8_t*)T(c2.in[1]).host.data();   // [64][32][3][3]
         for (int m = 0; m < 64; ++m) {
@@ -1028,6 +1028,17 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
                     sum += v;
                 }
             b2[m] -= c2.a.x_zp * sum;
+            // bias block: b = r + 127 * (v1 + ... + v31), every factor an int8 in [-127, 127]
+            const long long bq = (long long)std::llround((double)b2[m] / 127.0);
+            long long rest = bq;
+            const long long r = (long long)b2[m] - 127 * bq;
+            if (r < -127 || r > 127 || std::llabs(bq) > 31 * 127) return ZANT_OK;      // bias too large for the bias MMA: no fusion
+            w2arr[((9 * 2 + 0) * 64 + m) * 16 + 0] = (int8_t)r;
+            for (int k = 1; k < 32; ++k) {
+                const long long v = std::max(-127LL, std::min(127LL, rest));
+                w2arr[((9 * 2 + k / 16) * 64 + m) * 16 + k % 16] = (int8_t)v;
+                rest -= v;
+            }
         }
     }
     // ---- fc1: rows re-ordered from the graph's (c,h,w) flatten order to the (h,w,c) order stage 2 writes
@@ -1120,10 +1131,10 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
         }
         TcConvPoolArgs k{};
         k.x = (const int8_t*)pl->scratch(s_pool1); k.w = (const int8_t*)pl->aux(a_w2);
-        for (int m = 0; m < 64; ++m) { k.mult[m] = m2[m]; k.bias[m] = b2[m]; }
+        for (int m = 0; m < 64; ++m) k.mult[m] = m2[m];      // the bias travels in the weight array's tenth block
         k.y = (int8_t*)pl->scratch(s_pool2); k.n_images = (int)B;
         k.y_scale = c2a.y_scale; k.y_zp = c2a.y_zp; k.act = ZANT_QACT_RELU; k.out_blocked = 1; k.status = ctx->status_word;
-        const int blocks = std::min<int>((int)B, ctx->sm_count * 2);
+        const int blocks = std::min<int>((int)B, ctx->sm_count * TCCONV_CTAS_PER_SM);
         tc_conv3x3_relu_pool_kernel<13, 13, 64><<<blocks, Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
         return check_launch(ctx, "tc_conv3x3_relu_pool_kernel");
     });
