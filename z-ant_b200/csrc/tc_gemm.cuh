@@ -236,7 +236,8 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constan
 // Last layer: QLinearMatMul(K -> NCLS <= 64 classes) + DequantizeLinear, one row per thread.
 //   y[row][n] = float(sat(rne(float(acc + bias[n]) * mult[n]) + zp) - zp_dq) * scale_dq
 // The weight matrix (K x NCLS int8) is re-packed into shared memory as [NCLS][K/4] words so that
-// all threads of a warp read the same word (broadcast) while each walks its own row of A.
+// all threads of a warp read the same word (broadcast) while each walks its own row of A (staged in
+// shared memory by coalesced copies).
 // =============================================================================================
 struct FcOutArgs {
     const int8_t* a;        // [M][K] row-major int8
@@ -248,10 +249,22 @@ struct FcOutArgs {
     float dq_scale; int dq_zp;    // DequantizeLinear
 };
 
-template <int NC>   // compile-time bound on the number of classes
-__global__ void __launch_bounds__(128) fc_out_dequant_kernel(const FcOutArgs p) {
-    extern __shared__ uint32_t sw[];                     // [NC][K/4]
-    const int kw = p.K / 4;
+// One warp per tile of 32 rows: the tile (32 x K bytes, contiguous in global memory) is brought into the
+// warp's own shared-memory area with 16-byte cp.async copies (coalesced, all in flight at once), rows padded
+// by 16 bytes so that the 16-byte reads of the lanes, each walking its own row, hit distinct banks.  Only
+// __syncwarp between the phases: warps run independently and the grid balances at 32-row granularity.
+constexpr int FCOUT_THREADS = 128;
+template <int K> __host__ __device__ constexpr int fcout_pitch() { return K + 16; }
+template <int NC, int K> constexpr int fcout_smem_bytes() { return NC * K + (FCOUT_THREADS / 32) * 32 * fcout_pitch<K>(); }
+
+template <int NC, int K>   // NC: compile-time bound on the number of classes
+__global__ void __launch_bounds__(FCOUT_THREADS) fc_out_dequant_kernel(const FcOutArgs p) {
+    extern __shared__ __align__(16) uint8_t fc_smem[];
+    uint32_t* sw = reinterpret_cast<uint32_t*>(fc_smem);   // [NC][K/4]
+    constexpr int kw = K / 4, K16 = K / 16, PITCH = fcout_pitch<K>();
+    static_assert(K % 16 == 0 && K16 <= 32 && 32 % K16 == 0, "a row must be 1..32 chunks of 16 bytes, a divisor of 32");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* sa = fc_smem + NC * K + warp * 32 * PITCH;       // this warp's [32][PITCH]
     for (int i = threadIdx.x; i < NC * kw; i += blockDim.x) {
         const int n = i / kw, k4 = i - n * kw;
         uint32_t word = 0;
@@ -261,29 +274,47 @@ __global__ void __launch_bounds__(128) fc_out_dequant_kernel(const FcOutArgs p) 
     }
     __syncthreads();
     const Requant rq{p.y_scale, p.y_zp, ZANT_QACT_NONE};
-    for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < p.M; row += gridDim.x * blockDim.x) {
-        const uint4* ar = reinterpret_cast<const uint4*>(p.a + (size_t)row * p.K);
-        int acc[NC];
+    const int tiles = (p.M + 31) / 32;
+    const int warps_total = gridDim.x * (FCOUT_THREADS / 32);
+    constexpr int ROWS_PER_PASS = 32 / K16;                   // rows covered by one copy instruction of the warp
+    const int cr = lane / K16, cc = lane - cr * K16;
+    for (int tile = blockIdx.x * (FCOUT_THREADS / 32) + warp; tile < tiles; tile += warps_total) {
+        const int row0 = tile * 32, rows = min(32, p.M - row0);
+        const int8_t* src = p.a + (size_t)row0 * K;
+#pragma unroll 8
+        for (int r = cr; r < rows; r += ROWS_PER_PASS) {
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(sa + r * PITCH + cc * 16);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + (size_t)r * K + cc * 16) : "memory");
+        }
+        asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        if (lane < rows) {
+            const uint4* ar = reinterpret_cast<const uint4*>(sa + lane * PITCH);
+            int acc[NC];
 #pragma unroll
-        for (int n = 0; n < NC; ++n) acc[n] = 0;
-        for (int k16 = 0; k16 < p.K / 16; ++k16) {
-            const uint4 av = __ldg(ar + k16);
+            for (int n = 0; n < NC; ++n) acc[n] = 0;
+#pragma unroll 2
+            for (int k16 = 0; k16 < K16; ++k16) {
+                const uint4 av = ar[k16];
+#pragma unroll
+                for (int n = 0; n < NC; ++n) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(sw + n * kw + k16 * 4);
+                    acc[n] = __dp4a((int)av.x, (int)wv.x, acc[n]);
+                    acc[n] = __dp4a((int)av.y, (int)wv.y, acc[n]);
+                    acc[n] = __dp4a((int)av.z, (int)wv.z, acc[n]);
+                    acc[n] = __dp4a((int)av.w, (int)wv.w, acc[n]);
+                }
+            }
+            const int row = row0 + lane;
 #pragma unroll
             for (int n = 0; n < NC; ++n) {
-                const uint4 wv = *reinterpret_cast<const uint4*>(sw + n * kw + k16 * 4);
-                acc[n] = __dp4a((int)av.x, (int)wv.x, acc[n]);
-                acc[n] = __dp4a((int)av.y, (int)wv.y, acc[n]);
-                acc[n] = __dp4a((int)av.z, (int)wv.z, acc[n]);
-                acc[n] = __dp4a((int)av.w, (int)wv.w, acc[n]);
+                if (n < p.NCLS) {
+                    const int q = requant_one<false>(acc[n] + __ldg(p.bias + n), __ldg(p.mult + n), rq);
+                    p.y[(size_t)row * p.NCLS + n] = __fmul_rn(__int2float_rn(q - p.dq_zp), p.dq_scale);
+                }
             }
         }
-#pragma unroll
-        for (int n = 0; n < NC; ++n) {
-            if (n < p.NCLS) {
-                const int q = requant_one<false>(acc[n] + __ldg(p.bias + n), __ldg(p.mult + n), rq);
-                p.y[(size_t)row * p.NCLS + n] = __fmul_rn(__int2float_rn(q - p.dq_zp), p.dq_scale);
-            }
-        }
+        __syncwarp();      // the tile's reads are done before the next copy overwrites it
     }
 }
 
