@@ -107,10 +107,12 @@ def step_costs(graph):
 
 def fused_step_costs(batch, n_classes=10):
     """Algorithmic work of the four fused steps of the int8 CNN (per launch): every tensor that
-    crosses a kernel boundary counted once at its storage type, weights included."""
+    crosses a kernel boundary counted once at its storage type, weights included.  Of the 13 x 13 pooled
+    pixels of stage 1 the next stage's pool reads 12 x 12: only those are stored and counted (MACs stay the
+    layer's nominal ones)."""
     return [
-        dict(op="conv1 fused", out="pool1", macs=batch * 194688, bytes=batch * (784 * 4 + 13 * 13 * 32) + 32 * 9),
-        dict(op="conv2 fused tcgen05", out="pool2", macs=batch * 2230272, bytes=batch * (13 * 13 * 32 + 1600) + 64 * 288),
+        dict(op="conv1 fused", out="pool1", macs=batch * 194688, bytes=batch * (784 * 4 + 12 * 12 * 32) + 32 * 9),
+        dict(op="conv2 fused tcgen05", out="pool2", macs=batch * 2230272, bytes=batch * (12 * 12 * 32 + 1600) + 64 * 288),
         dict(op="fc1 tcgen05", out="relu3", macs=batch * 819200, bytes=batch * (1600 + 512) + 1600 * 512),
         dict(op="fc2+dequant", out="logits", macs=batch * 512 * n_classes, bytes=batch * (512 + 4 * n_classes) + 512 * n_classes),
     ]

@@ -69,9 +69,8 @@ def test_small_cnn_int8_bit_exact(zb, ctx, oracle, models, scales, batch, fuse):
 
 @pytest.mark.parametrize("amplitude", [(300, 3000, 20000, 500), (2000, 400000, 100000, 3000), (2000, 600000, 100000, 3000)])
 def test_small_cnn_int8_with_biases_bit_exact(zb, ctx, oracle, models, scales, amplitude):
-    """Non-zero int32 biases through the fused chain: conv1 adds them as the MMA's C operand, conv2 as a tenth
-    MMA over int8 factors of the bias (small, near its limit of about 500 000, and beyond it, where the plan
-    keeps one kernel per node)."""
+    """Non-zero int32 biases through the fused chain (conv1 adds them as the MMA's C operand, conv2 after the
+    window max, the two matrix products in their epilogues): small ones and ones that saturate most outputs."""
     batch = 7
     g = models.small_cnn_int8(batch, act_scales=scales, bias_amplitude=amplitude)
     x = models.small_cnn_input(batch, 123)
@@ -81,8 +80,7 @@ def test_small_cnn_int8_with_biases_bit_exact(zb, ctx, oracle, models, scales, a
         got = plan.run(x)
         assert np.array_equal(got.view(np.uint32), want[g.output].view(np.uint32)), fuse
         if fuse:
-            fused = any("Fused" in n for n in plan.step_names())
-            assert fused == (amplitude[1] <= 500000)
+            assert any("Fused" in n for n in plan.step_names())
         plan.close()
     if amplitude[1] <= 3000:      # the moderate biases leave the activations spread over many codes
         assert len(np.unique(want[g.id_of("pool2")])) > 16

@@ -1016,7 +1016,7 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
     // ---- stage 2 parameters
     std::vector<float> m2; std::vector<int32_t> b2;
     if (!scales_of(c2, 64, m2) || !bias_of(c2, 64, b2)) return ZANT_OK;
-    std::vector<int8_t> w2arr(10 * 2 * 64 * 16);      // nine taps and the bias block (TcConvPoolCfg)
+    std::vector<int8_t> w2arr(9 * 2 * 64 * 16);
     {
         const int8_t* w = (const int8_t*)T(c2.in[1]).host.data();   // [64][32][3][3]
         for (int m = 0; m < 64; ++m) {
@@ -1028,17 +1028,6 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
                     sum += v;
                 }
             b2[m] -= c2.a.x_zp * sum;
-            // bias block: b = r + 127 * (v1 + ... + v31), every factor an int8 in [-127, 127]
-            const long long bq = (long long)std::llround((double)b2[m] / 127.0);
-            long long rest = bq;
-            const long long r = (long long)b2[m] - 127 * bq;
-            if (r < -127 || r > 127 || std::llabs(bq) > 31 * 127) return ZANT_OK;      // bias too large for the bias MMA: no fusion
-            w2arr[((9 * 2 + 0) * 64 + m) * 16 + 0] = (int8_t)r;
-            for (int k = 1; k < 32; ++k) {
-                const long long v = std::max(-127LL, std::min(127LL, rest));
-                w2arr[((9 * 2 + k / 16) * 64 + m) * 16 + k % 16] = (int8_t)v;
-                rest -= v;
-            }
         }
     }
     // ---- fc1: rows re-ordered from the graph's (c,h,w) flatten order to the (h,w,c) order stage 2 writes
@@ -1072,7 +1061,11 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
         }
     }
 
-    const int s_pool1 = pl->add_scratch(B * 2 * 169 * 16);
+    // stage 1 -> stage 2 hand-over: parity planes (TcConvParityCfg), every tile of stage 2 copies 136 rows of each plane
+    if (B > (1u << 20)) return ZANT_OK;                     // 32-bit plane offsets in stage 1
+    const long long c2_tiles = ((long long)B * 36 + 127) / 128;
+    const long long plane_bytes = (TcConvParityCfg::plane_rows(c2_tiles) * 16 + 255) / 256 * 256;
+    const int s_pool1 = pl->add_scratch((size_t)(8 * plane_bytes));
     const size_t Bpad = (B + 127) / 128 * 128;
     const int s_pool2 = pl->add_scratch(Bpad * 1600);
     const int s_fc1 = pl->add_scratch(B * 512);
@@ -1116,27 +1109,25 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
         Conv1MmaArgs k{};
         k.x = pl->p<float>(x); k.y = (int8_t*)pl->scratch(s_pool1); k.n_images = (int)B;
         k.x_scale = a1.x_scale; k.x_zp = a1.x_zp;
-        k.wfrag = (const uint32_t*)pl->aux(a_wf); k.biasfrag = (const int32_t*)pl->aux(a_bf); k.multfrag = (const float*)pl->aux(a_mf); k.status = ctx->status_word;
+        k.wfrag = (const uint32_t*)pl->aux(a_wf); k.biasfrag = (const int32_t*)pl->aux(a_bf); k.multfrag = (const float*)pl->aux(a_mf); k.status = ctx->status_word; k.plane_bytes = plane_bytes;
         const int blocks = std::min<int>((int)((B + C1M_G - 1) / C1M_G), ctx->sm_count * 8);
         conv1_mma_relu_pool_kernel<<<blocks, C1M_THREADS, 0, ctx->stream>>>(k);
         return check_launch(ctx, "conv1_mma_relu_pool_kernel");
     });
-    const zant_node_attrs c2a = c2.a;
     push("Fused[QLinearConv+Relu+MaxPool] tcgen05", [=]() {
-        using Cfg = TcConvPoolCfg<13, 13, 64>;
+        using Cfg = TcConvParityCfg;
         static bool attr_set = false;
         if (!attr_set) {
-            ZB_CUDA(cudaFuncSetAttribute(tc_conv3x3_relu_pool_kernel<13, 13, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+            ZB_CUDA(cudaFuncSetAttribute(tc_conv3x3_pool_parity_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
             attr_set = true;
         }
-        TcConvPoolArgs k{};
-        k.x = (const int8_t*)pl->scratch(s_pool1); k.w = (const int8_t*)pl->aux(a_w2);
-        for (int m = 0; m < 64; ++m) k.mult[m] = m2[m];      // the bias travels in the weight array's tenth block
-        k.y = (int8_t*)pl->scratch(s_pool2); k.n_images = (int)B;
-        k.y_scale = c2a.y_scale; k.y_zp = c2a.y_zp; k.act = ZANT_QACT_RELU; k.out_blocked = 1; k.status = ctx->status_word;
-        const int blocks = std::min<int>((int)B, ctx->sm_count * TCCONV_CTAS_PER_SM);
-        tc_conv3x3_relu_pool_kernel<13, 13, 64><<<blocks, Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
-        return check_launch(ctx, "tc_conv3x3_relu_pool_kernel");
+        TcConvParityArgs k{};
+        k.x = (const int8_t*)pl->scratch(s_pool1); k.plane_bytes = plane_bytes; k.w = (const int8_t*)pl->aux(a_w2);
+        for (int m = 0; m < 64; ++m) { k.mult[m] = m2[m]; k.bias[m] = b2[m]; }
+        k.y = (int8_t*)pl->scratch(s_pool2); k.n_images = (int)B; k.n_tiles = (int)c2_tiles; k.status = ctx->status_word;
+        const int blocks = std::min<int>((int)c2_tiles, ctx->sm_count);
+        tc_conv3x3_pool_parity_kernel<<<blocks, Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
+        return check_launch(ctx, "tc_conv3x3_pool_parity_kernel");
     });
     const zant_node_attrs f1a = f1.a, f2a = f2.a, dqa = N[11].a;
     push("Fused[Reshape+QLinearMatMul+Relu] tcgen05", [=]() {
