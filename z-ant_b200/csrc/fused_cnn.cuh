@@ -235,16 +235,17 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
 // accumulators (TMEM columns m*64 ..): member (dy, dx), tap (kh, kw) reads input pixel
 // (2py + dy + kh, 2px + dx + kw), which lies in parity plane ((dy+kh)&1, (dx+kw)&1) at row
 // R + ((dy+kh)>>1)*6 + ((dx+kw)>>1) -- the same 128 consecutive rows of that plane, shifted.  So a tile is
-// eight bulk copies (2 chunks x 4 planes, 136 rows of 16 bytes each) and 36 MMAs (128x64x32), and a thread
+// eight bulk copies (2 chunks x 4 planes, 136 rows of 16 bytes each) and 24 MMAs (12 of 128x128x32 that serve two
+// members at once, 12 of 128x64x32), and a thread
 // of the epilogue holds all four members of its window: max, bias, ReLU and requantisation happen in
 // registers on a quarter of the values, with no staging; a window's 64 channels leave as four 16-byte stores
 // into the GEMM-blocked layout [N/128][1600/16][128 images][16].
-//   warp 0 producer, warp 1 MMA issuer (TMEM: two sets of 4 x 64 columns), warps 2-9 two epilogue groups that
-//   alternate tiles.
+//   warp 0 producer, warp 1 MMA issuer (TMEM: two sets of 4 x 64 columns, so the epilogue of a tile overlaps the
+//   MMAs of the next), warps 2-17 epilogue.
 // =============================================================================================
 struct TcConvParityArgs {
     const int8_t* x; long long plane_bytes;
-    const int8_t* w;                 // [9 taps][2 chunks][64][16] int8 (a longer array is fine)
+    const int8_t* w;                 // [9 taps][2 chunks][64][16] int8, then the paired blocks (TcConvParityCfg::W_ALL_BYTES)
     float mult[64]; int32_t bias[64];   // per filter; bias includes -x_zp * sum(w); constant-bank operands
     int8_t* y;
     int n_images, n_tiles;           // n_tiles = ceil(n_images * 36 / 128)
@@ -258,17 +259,21 @@ struct TcConvParityCfg {
     static constexpr int STAGES = 6;                         // 104 KB of stages: also keeps a second CTA (which would wait for TMEM) off the SM
     static constexpr int W_TAP_BYTES = 2 * 64 * 16;
     static constexpr int W_BYTES = 9 * W_TAP_BYTES;
+    // paired blocks after the nine taps: [kh][j][2 chunks][128 rows][16]; j = 0: rows 0-63 tap (kh,1), rows 64-127 tap
+    // (kh,0); j = 1: rows 0-63 tap (kh,2), rows 64-127 tap (kh,1)   (member dx = 0 first, then dx = 1)
+    static constexpr int W_PAIR_BYTES = 2 * 128 * 16;
+    static constexpr int W_ALL_BYTES = W_BYTES + 6 * W_PAIR_BYTES;
     static constexpr int OFF_W = 0;
-    static constexpr int OFF_A = OFF_W + W_BYTES;
+    static constexpr int OFF_A = OFF_W + W_ALL_BYTES;
     static constexpr int OFF_BAR = OFF_A + STAGES * STAGE_BYTES;
     static constexpr int SMEM_BYTES = OFF_BAR + 256;
     static constexpr int TMEM_COLS = 512;                    // 2 sets x 4 members x 64 filters
-    static constexpr int THREADS = 320;
+    static constexpr int THREADS = 576;                      // producer, MMA issuer, 16 epilogue warps
     // rows of a plane that a batch needs: every tile copies ROWS rows from its first row
     static long long plane_rows(long long n_tiles) { return n_tiles * 128 + (ROWS - 128); }
 };
 
-__global__ void __launch_bounds__(320, 1) tc_conv3x3_pool_parity_kernel(const __grid_constant__ TcConvParityArgs a) {
+__global__ void __launch_bounds__(576, 1) tc_conv3x3_pool_parity_kernel(const __grid_constant__ TcConvParityArgs a) {
     using Cfg = TcConvParityCfg;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sW = smem + Cfg::OFF_W;
@@ -276,7 +281,6 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_pool_parity_kernel(const __
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + Cfg::OFF_BAR + 128);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 132);
-    volatile int* epi_ok = reinterpret_cast<volatile int*>(smem + Cfg::OFF_BAR + 136);   // [2]
     const uint32_t bar0 = ptx::smem_u32(bars);
     auto full = [&](int s) { return bar0 + 8u * s; };
     auto empty = [&](int s) { return bar0 + 8u * (Cfg::STAGES + s); };
@@ -286,12 +290,11 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_pool_parity_kernel(const __
 
     if (tid == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { ptx::mbar_init(full(s), 1); ptx::mbar_init(empty(s), 1); }
-        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 4); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 16); }
         *abort_flag = 0;
-        epi_ok[0] = 1; epi_ok[1] = 1;
         ptx::mbar_fence_init();
     }
-    for (int i = tid; i < Cfg::W_BYTES / 16; i += Cfg::THREADS)
+    for (int i = tid; i < Cfg::W_ALL_BYTES / 16; i += Cfg::THREADS)
         reinterpret_cast<uint4*>(sW)[i] = __ldg(reinterpret_cast<const uint4*>(a.w) + i);
     ptx::fence_proxy_async_smem();
     if (warp == 1) {
@@ -322,7 +325,7 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_pool_parity_kernel(const __
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (ptx::elect_one()) {
-            constexpr uint32_t idesc = ptx::idesc_i8(128, 64, true, true);
+            constexpr uint32_t idesc64 = ptx::idesc_i8(128, 64, true, true), idesc128 = ptx::idesc_i8(128, 128, true, true);
             const uint32_t w_addr = ptx::smem_u32(sW);
             int it = 0;
             for (int t = blockIdx.x; t < a.n_tiles; t += gridDim.x, ++it) {
@@ -334,16 +337,26 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_pool_parity_kernel(const __
                 if (!ptx::mbar_wait(full(s), ph, abort_flag)) break;
                 ptx::tc_fence_after();
                 const uint32_t a_addr = ptx::smem_u32(sA + s * Cfg::STAGE_BYTES);
+                // Input pixel (2py + ry, 2px + rx), ry = dy + kh, rx = dx + kw, 0..3 each: one shifted view of one plane.
+                // The view (ry, rx = 1 or 2) serves both members dx = 0 (kw = rx) and dx = 1 (kw = rx - 1) of a row dy:
+                // one MMA of 128 filters-times-members over the paired weight block instead of two of 64 (an N = 64
+                // MMA is bound by its 6 KB of shared-memory operands, not by its 32 cycles of math).
 #pragma unroll
-                for (int tap = 0; tap < 9; ++tap) {
-                    const int kh = tap / 3, kw = tap - kh * 3;
-                    const uint64_t db = ptx::smem_desc_kmajor(w_addr + (uint32_t)(tap * Cfg::W_TAP_BYTES), 64 * 16, 128);
+                for (int kh = 0; kh < 3; ++kh) {
 #pragma unroll
-                    for (int m = 0; m < 4; ++m) {          // consecutive MMAs write different accumulators
-                        const int ry = (m >> 1) + kh, rx = (m & 1) + kw;
-                        const int plane = (ry & 1) * 2 + (rx & 1), shift = (ry >> 1) * 6 + (rx >> 1);
-                        const uint64_t da = ptx::smem_desc_kmajor(a_addr + (uint32_t)(plane * Cfg::PLANE_BYTES + shift * 16), 4 * Cfg::PLANE_BYTES, 128);
-                        ptx::mma_i8(tmem_base + (uint32_t)(b * 256 + m * 64), da, db, idesc, tap > 0);
+                    for (int dy = 0; dy < 2; ++dy) {
+                        const int ry = dy + kh;
+                        auto view = [&](int rx) {
+                            const int plane = (ry & 1) * 2 + (rx & 1), shift = (ry >> 1) * 6 + (rx >> 1);
+                            return ptx::smem_desc_kmajor(a_addr + (uint32_t)(plane * Cfg::PLANE_BYTES + shift * 16), 4 * Cfg::PLANE_BYTES, 128);
+                        };
+                        auto w64 = [&](int kw) { return ptx::smem_desc_kmajor(w_addr + (uint32_t)((kh * 3 + kw) * Cfg::W_TAP_BYTES), 64 * 16, 128); };
+                        auto w128 = [&](int j) { return ptx::smem_desc_kmajor(w_addr + (uint32_t)(Cfg::W_BYTES + (kh * 2 + j) * Cfg::W_PAIR_BYTES), 128 * 16, 128); };
+                        const uint32_t d = tmem_base + (uint32_t)(b * 256 + dy * 128);     // members (dy, 0) and (dy, 1): 2 x 64 columns
+                        ptx::mma_i8(d, view(1), w128(0), idesc128, kh > 0);               // the first MMA of a set initialises both members
+                        ptx::mma_i8(d, view(2), w128(1), idesc128, true);
+                        ptx::mma_i8(d, view(0), w64(0), idesc64, true);
+                        ptx::mma_i8(d + 64u, view(3), w64(2), idesc64, true);
                     }
                 }
                 ptx::mma_commit(empty(s));
@@ -351,49 +364,50 @@ __global__ void __launch_bounds__(320, 1) tc_conv3x3_pool_parity_kernel(const __
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue: two groups of 4 warps;
-        // group g owns accumulator set g and handles the tiles whose iteration index is g mod 2.
-        const int g = (warp - 2) >> 2;
+        // ------------------------------------------------------------------ epilogue: 16 warps, four per TMEM lane
+        // quarter; each takes 16 of the 64 filters of its quarter's 32 windows, in every tile (a single warp per
+        // quarter and tile would be latency-bound and slower than the MMAs of the next tile).
         const int quarter = warp & 3;               // TMEM lane quarter this warp may access
+        const int cg = (warp - 2) >> 2;             // 16-filter group of this warp
         const int row = quarter * 32 + lane;        // MMA row = pool window within the tile
-        const int e = ((warp - 2) & 3) * 32 + lane; // 0..127 within the group
-        const uint32_t bar_id = 1u + (uint32_t)g;
-        int it = g;
-        for (int t = blockIdx.x + g * (int)gridDim.x; t < a.n_tiles; t += 2 * (int)gridDim.x, it += 2) {
+        float mult[16]; int bias[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { mult[j] = a.mult[cg * 16 + j]; bias[j] = a.bias[cg * 16 + j]; }
+        int it = 0;
+        for (int t = blockIdx.x; t < a.n_tiles; t += gridDim.x, ++it) {
+            const int b = it & 1;
             const uint32_t bph = (uint32_t)(it >> 1) & 1u;
-            if (e == 0) epi_ok[g] = ptx::mbar_wait(tfull(g), bph, abort_flag) ? 1 : 0;
-            ptx::named_barrier_sync(bar_id, 128);
-            if (!epi_ok[g]) break;
+            int ok = 1;
+            if (lane == 0) ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
             ptx::tc_fence_after();
             const int R = t * 128 + row;
             const int n = R / 36, q = R - 36 * n;
             const int py = q / 6, px = q - py * 6;
             const bool live = n < a.n_images && py < 5 && px < 5;
-            int8_t* yw = a.y + (size_t)(n >> 7) * (1600 / 16) * 2048 + (size_t)(n & 127) * 16 + (size_t)((py * 5 + px) * 4) * 2048;
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(g * 256);
+            int8_t* yw = a.y + (size_t)(n >> 7) * (1600 / 16) * 2048 + (size_t)(n & 127) * 16 + (size_t)((py * 5 + px) * 4 + cg) * 2048;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * 256 + cg * 16);
+            uint32_t v[4][16];
 #pragma unroll
-            for (int cg = 0; cg < 4; ++cg) {
-                uint32_t v[4][16];
-#pragma unroll
-                for (int m = 0; m < 4; ++m) ptx::tmem_ld16(taddr + (uint32_t)(m * 64 + cg * 16), v[m]);
-                ptx::tmem_wait_ld();
-                uint32_t pk[4];
-#pragma unroll
-                for (int j4 = 0; j4 < 4; ++j4) {
-                    int r[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int c = cg * 16 + j4 * 4 + j;      // compile-time after unrolling: constant-bank operands
-                        const int mx = max(__vimax3_s32((int)v[0][j4 * 4 + j], (int)v[1][j4 * 4 + j], (int)v[2][j4 * 4 + j]), (int)v[3][j4 * 4 + j]);
-                        r[j] = rq_round(mx + a.bias[c], a.mult[c]);
-                    }
-                    pk[j4] = relu_s8x4(pack_sat_s8x4(r[0], r[1], r[2], r[3]));
-                }
-                if (live) *reinterpret_cast<uint4*>(yw + (size_t)cg * 2048) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
+            for (int m = 0; m < 4; ++m) ptx::tmem_ld16(taddr + (uint32_t)(m * 64), v[m]);
+            ptx::tmem_wait_ld();
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(tempty(g));   // accumulator set g may be overwritten
+            if (lane == 0) ptx::mbar_arrive(tempty(b));   // this warp has its values: the set may be overwritten once all 16 arrived
+            uint32_t pk[4];
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) {
+                int r[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = j4 * 4 + j;
+                    const int mx = max(__vimax3_s32((int)v[0][c], (int)v[1][c], (int)v[2][c]), (int)v[3][c]);
+                    r[j] = rq_round(mx + bias[c], mult[c]);
+                }
+                pk[j4] = relu_s8x4(pack_sat_s8x4(r[0], r[1], r[2], r[3]));
+            }
+            if (live) *reinterpret_cast<uint4*>(yw) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
     }
 

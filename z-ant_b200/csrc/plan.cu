@@ -1016,7 +1016,7 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
     // ---- stage 2 parameters
     std::vector<float> m2; std::vector<int32_t> b2;
     if (!scales_of(c2, 64, m2) || !bias_of(c2, 64, b2)) return ZANT_OK;
-    std::vector<int8_t> w2arr(9 * 2 * 64 * 16);
+    std::vector<int8_t> w2arr(TcConvParityCfg::W_ALL_BYTES);      // nine taps, then the paired blocks
     {
         const int8_t* w = (const int8_t*)T(c2.in[1]).host.data();   // [64][32][3][3]
         for (int m = 0; m < 64; ++m) {
@@ -1029,6 +1029,15 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
                 }
             b2[m] -= c2.a.x_zp * sum;
         }
+        // paired blocks [kh][j][chunk][128 rows][16]: rows 0-63 tap (kh, j + 1), rows 64-127 tap (kh, j)
+        for (int kh = 0; kh < 3; ++kh)
+            for (int j = 0; j < 2; ++j)
+                for (int chunk = 0; chunk < 2; ++chunk)
+                    for (int r = 0; r < 128; ++r) {
+                        const int tap = kh * 3 + (r < 64 ? j + 1 : j), m = r & 63;
+                        std::memcpy(&w2arr[TcConvParityCfg::W_BYTES + (size_t)(((kh * 2 + j) * 2 + chunk) * 128 + r) * 16],
+                                    &w2arr[(size_t)((tap * 2 + chunk) * 64 + m) * 16], 16);
+                    }
     }
     // ---- fc1: rows re-ordered from the graph's (c,h,w) flatten order to the (h,w,c) order stage 2 writes
     std::vector<float> m3; std::vector<int32_t> b3;
