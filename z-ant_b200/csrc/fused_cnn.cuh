@@ -29,7 +29,7 @@ enum DeviceError : int {
 
 // =============================================================================================
 // Stage 1: QuantizeLinear(uint8) + QLinearConv(1 -> 32, 3x3, stride 1, no pad) + ReLU + MaxPool 2x2/2
-//          float [N,1,28,28]  ->  int8 parity planes (Conv1MmaArgs::plane_bytes) or C16-planar [N][2][13*13][16]
+//          float [N,1,28,28]  ->  int8 parity planes (Conv1MmaArgs::plane_bytes)
 // Host-side description of the stage (the plan fills it from the graph; the kernel below takes its
 // own argument block derived from it).
 // =============================================================================================
@@ -66,10 +66,10 @@ struct Conv1MmaArgs {
     const int32_t* biasfrag; // [4 groups][32 lanes][2]  (bias - x_zp * sum(w)) of the lane's two columns
     const float* multfrag;   // [4 groups][32 lanes][2]
     int* status;             // device status word: DEV_ERR_WAIT_TIMEOUT when a bounded wait gave up
-    // Output layout.  0: C16-planar [N][2][13*13][16].  > 0: parity planes for tc_conv3x3_pool_parity_kernel,
-    // [2 chunks][4 parities][N*36 rows (+ padding)][16], `plane_bytes` apart: pooled pixel (y, x), y and x below
-    // 12, lies in plane (y&1)*2 + (x&1) at row n*36 + (y>>1)*6 + (x>>1); row and column 12 are not stored
-    // (the next stage's pool never reads them).
+    // Output layout: parity planes for tc_conv3x3_pool_parity_kernel, [2 chunks][4 parities][N*36 rows (+ padding)][16],
+    // `plane_bytes` apart: pooled pixel (y, x), y and x below 12, lies in plane (y&1)*2 + (x&1) at row
+    // n*36 + (y>>1)*6 + (x>>1); row and column 12 are neither computed nor stored (the next stage's pool never
+    // reads them).
     long long plane_bytes;
 };
 
@@ -79,9 +79,11 @@ __device__ __forceinline__ void mma_m16n8k16_u8s8(int (&d)[4], uint32_t a0, uint
                  : "r"(a0), "r"(a1), "r"(b0), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 
-constexpr int C1M_G = 3;               // images per CTA iteration: 507 pooled pixels = 32 units of 16
+// Images per CTA iteration: 4 x 144 pooled pixels = 36 units of 16.  Measured (batch 65536): 0.212 ms with groups of
+// three, 0.197 ms with four, 0.199 ms with five; 384 threads x 2 CTAs and 288 x 3 were slower than 256 x 3.
+constexpr int C1M_G = 4;
 constexpr int C1M_THREADS = 256;
-constexpr int C1M_UNITS = (C1M_G * 169 + 15) / 16;
+constexpr int C1M_UNITS = (C1M_G * 144 + 15) / 16;
 
 constexpr int C1M_IMG_FLOATS = 28 * 28;
 constexpr int C1M_GROUP_BYTES = C1M_G * C1M_IMG_FLOATS * 4;   // 9408: a multiple of 16, as the bulk copy wants
@@ -96,7 +98,7 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
     __shared__ __align__(8) uint64_t bars[2];
     __shared__ int abort_flag;
     // Per pooled pixel of an iteration (the same in every iteration): x = word of img that holds the patch's
-    // first byte | odd column << 16 | image within the group << 17 | stored << 19; y = byte offset of the
+    // first byte | odd column << 16 | image within the group << 17 (3 bits) | exists << 20; y = byte offset of the
     // pixel's first 16-channel chunk from the group's first image (and, with parity planes, from plane 0).  Keeps divisions out of the main loop.
     __shared__ uint2 pix_tab[C1M_UNITS * 16];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -116,23 +118,15 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
     }
     // Parity planes: only the 12 x 12 pooled pixels that the next stage reads are computed, enumerated plane by
     // plane (a unit's 16 pixels are 16 consecutive rows of one plane: contiguous stores).
-    const int n_pix = a.plane_bytes == 0 ? C1M_G * 169 : C1M_G * 144;
-    const int n_units = (n_pix + 15) / 16;
+    constexpr int n_pix = C1M_G * 144, n_units = (n_pix + 15) / 16;
     for (int i = tid; i < C1M_UNITS * 16; i += C1M_THREADS) {
         const bool exists = i < n_pix;
         const int pc = exists ? i : 0;
-        int gi, py, px; uint32_t off;
-        if (a.plane_bytes == 0) {
-            gi = pc / 169; const int pp = pc - gi * 169;
-            py = pp / 13; px = pp - py * 13;
-            off = (uint32_t)(gi * 2 * 169 * 16 + pp * 16);
-        } else {
-            gi = pc / 144; const int rem = pc - gi * 144;
-            const int plane = rem / 36, rloc = rem - plane * 36;
-            py = 2 * (rloc / 6) + (plane >> 1); px = 2 * (rloc % 6) + (plane & 1);
-            off = (uint32_t)(plane * a.plane_bytes) + (uint32_t)((gi * 36 + rloc) * 16);
-        }
-        pix_tab[i] = make_uint2((uint32_t)(gi * 224 + 2 * py * 8 + (px >> 1)) | ((uint32_t)(px & 1) << 16) | ((uint32_t)gi << 17) | ((uint32_t)exists << 19), off);
+        const int gi = pc / 144, rem = pc - gi * 144;
+        const int plane = rem / 36, rloc = rem - plane * 36;
+        const int py = 2 * (rloc / 6) + (plane >> 1), px = 2 * (rloc % 6) + (plane & 1);
+        const uint32_t off = (uint32_t)(plane * a.plane_bytes) + (uint32_t)((gi * 36 + rloc) * 16);
+        pix_tab[i] = make_uint2((uint32_t)(gi * 224 + 2 * py * 8 + (px >> 1)) | ((uint32_t)(px & 1) << 16) | ((uint32_t)gi << 17) | ((uint32_t)exists << 20), off);
     }
     uint32_t wf[4][4]; int bias[4][2]; float mult[4][2];
 #pragma unroll
@@ -146,10 +140,9 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
     __syncthreads();                               // barriers and the abort flag are set up
 
     const float q_lo = (float)(-a.x_zp), q_hi = (float)(255 - a.x_zp);
-    // this thread's 8 channels: chunk t >> 1 (a plane of 169 chunks per image, or four parity planes further), half t & 1
-    int8_t* const y_thread = a.plane_bytes == 0 ? a.y + (t >> 1) * (169 * 16) + (t & 1) * 8
-                                                : a.y + (size_t)(t >> 1) * 4 * (size_t)a.plane_bytes + (t & 1) * 8;
-    const size_t img_bytes = a.plane_bytes == 0 ? 2 * 169 * 16 : 36 * 16;
+    // this thread's 8 channels: chunk t >> 1 (four parity planes further), half t & 1
+    int8_t* const y_thread = a.y + (size_t)(t >> 1) * 4 * (size_t)a.plane_bytes + (t & 1) * 8;
+    constexpr size_t img_bytes = 36 * 16;
     int it = 0;
     for (int base = blockIdx.x * C1M_G; base < a.n_images; base += stride, ++it) {
         const int s = it & 1;
@@ -159,11 +152,13 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
         // ---- quantize C1M_G images: float4 in, four uint8 out
         uint32_t (*img)[28][8] = img2[s];
         const int n_here = min(C1M_G, a.n_images - base);
-        for (int i = tid; i < C1M_G * 196; i += C1M_THREADS) {
-            const int gi = i / 196, p4 = i - gi * 196;        // 196 float4 per image, 7 per row
+        // pooled rows and columns 0..11 read input rows 0..25 only (26 rows of 7 float4)
+        constexpr int f4_per_img = 182;
+        for (int i = tid; i < C1M_G * f4_per_img; i += C1M_THREADS) {
+            const int gi = i / f4_per_img, p4 = i - gi * f4_per_img;        // 7 float4 per row
             uint32_t word = 0;
             if (gi < n_here) {
-                const float4 v = reinterpret_cast<const float4*>(stage[s])[i];
+                const float4 v = reinterpret_cast<const float4*>(stage[s])[gi * 196 + p4];
                 // sat_u8(rne(clamp(t, -512, 511)) + zp) == rne(clamp(t, -zp, 255 - zp)) + zp: the bounds are integers
                 // inside [-512, 511] and rounding is monotonic; a NaN becomes the lower bound either way.
                 const int q0 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.x, a.x_scale), q_lo), q_hi)) + a.x_zp;
@@ -190,7 +185,7 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const uint2 e = pix_tab[u * 16 + g + 8 * h];
-                ok[h] = (e.x >> 19) != 0 && base + (int)((e.x >> 17) & 3u) < a.n_images;
+                ok[h] = (e.x >> 20) != 0 && base + (int)((e.x >> 17) & 7u) < a.n_images;
                 out_off[h] = e.y;
                 const uint32_t* row = &img[0][0][0] + (e.x & 0xffffu) + t * 8;       // patch row t of the pooled pixel
                 afrag[h] = __byte_perm(row[0], row[1], (e.x & 0x10000u) ? 0x5432u : 0x3210u);
@@ -243,6 +238,18 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
 //   warp 0 producer, warp 1 MMA issuer (TMEM: two sets of 4 x 64 columns, so the epilogue of a tile overlaps the
 //   MMAs of the next), warps 2-17 epilogue.
 // =============================================================================================
+// Optional per-role cycle counters of the kernel below (debug builds with -DZB_TC_CONV_TIMERS only).
+#ifdef ZB_TC_CONV_TIMERS
+__device__ unsigned long long g_c2_timers[256 * 8];
+#define ZB_C2T_DECL() long long c2t_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long c2t0_ = clock64()
+#define ZB_C2T(slot) do { const long long n_ = clock64(); c2t_[slot] += n_ - c2t0_; c2t0_ = n_; } while (0)
+#define ZB_C2T_DUMP(lo, hi) do { for (int i_ = (lo); i_ < (hi); ++i_) g_c2_timers[blockIdx.x * 8 + i_] = (unsigned long long)c2t_[i_]; } while (0)
+#else
+#define ZB_C2T_DECL() do {} while (0)
+#define ZB_C2T(slot) do {} while (0)
+#define ZB_C2T_DUMP(lo, hi) do {} while (0)
+#endif
+
 struct TcConvParityArgs {
     const int8_t* x; long long plane_bytes;
     const int8_t* w;                 // [9 taps][2 chunks][64][16] int8, then the paired blocks (TcConvParityCfg::W_ALL_BYTES)
@@ -310,17 +317,21 @@ __global__ void __launch_bounds__(576, 1) tc_conv3x3_pool_parity_kernel(const __
         // ------------------------------------------------------------------ producer
         if (ptx::elect_one()) {
             int it = 0;
+            ZB_C2T_DECL();
             for (int t = blockIdx.x; t < a.n_tiles; t += gridDim.x, ++it) {
                 const int s = it % Cfg::STAGES;
                 const uint32_t ph = (uint32_t)(it / Cfg::STAGES) & 1u;
                 if (!ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag)) break;
+                ZB_C2T(3);
                 ptx::mbar_arrive_expect_tx(full(s), Cfg::STAGE_BYTES);
                 const int8_t* src = a.x + (size_t)t * (128 * 16);
                 const uint32_t dst = ptx::smem_u32(sA + s * Cfg::STAGE_BYTES);
 #pragma unroll
                 for (int pl = 0; pl < 8; ++pl)
                     ptx::bulk_g2s(dst + (uint32_t)(pl * Cfg::PLANE_BYTES), src + (size_t)pl * (size_t)a.plane_bytes, Cfg::PLANE_BYTES, full(s));
+                ZB_C2T(7);
             }
+            ZB_C2T_DUMP(3, 4);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -328,13 +339,16 @@ __global__ void __launch_bounds__(576, 1) tc_conv3x3_pool_parity_kernel(const __
             constexpr uint32_t idesc64 = ptx::idesc_i8(128, 64, true, true), idesc128 = ptx::idesc_i8(128, 128, true, true);
             const uint32_t w_addr = ptx::smem_u32(sW);
             int it = 0;
+            ZB_C2T_DECL();
             for (int t = blockIdx.x; t < a.n_tiles; t += gridDim.x, ++it) {
                 const int s = it % Cfg::STAGES;
                 const uint32_t ph = (uint32_t)(it / Cfg::STAGES) & 1u;
                 const int b = it & 1;
                 const uint32_t bph = (uint32_t)(it >> 1) & 1u;
                 if (!ptx::mbar_wait(tempty(b), bph ^ 1u, abort_flag)) break;
+                ZB_C2T(0);
                 if (!ptx::mbar_wait(full(s), ph, abort_flag)) break;
+                ZB_C2T(1);
                 ptx::tc_fence_after();
                 const uint32_t a_addr = ptx::smem_u32(sA + s * Cfg::STAGE_BYTES);
                 // Input pixel (2py + ry, 2px + rx), ry = dy + kh, rx = dx + kw, 0..3 each: one shifted view of one plane.
@@ -361,7 +375,9 @@ __global__ void __launch_bounds__(576, 1) tc_conv3x3_pool_parity_kernel(const __
                 }
                 ptx::mma_commit(empty(s));
                 ptx::mma_commit(tfull(b));
+                ZB_C2T(2);
             }
+            ZB_C2T_DUMP(0, 3);
         }
     } else {
         // ------------------------------------------------------------------ epilogue: 16 warps, four per TMEM lane
@@ -374,6 +390,7 @@ __global__ void __launch_bounds__(576, 1) tc_conv3x3_pool_parity_kernel(const __
 #pragma unroll
         for (int j = 0; j < 16; ++j) { mult[j] = a.mult[cg * 16 + j]; bias[j] = a.bias[cg * 16 + j]; }
         int it = 0;
+        ZB_C2T_DECL();
         for (int t = blockIdx.x; t < a.n_tiles; t += gridDim.x, ++it) {
             const int b = it & 1;
             const uint32_t bph = (uint32_t)(it >> 1) & 1u;
@@ -381,6 +398,7 @@ __global__ void __launch_bounds__(576, 1) tc_conv3x3_pool_parity_kernel(const __
             if (lane == 0) ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
+            ZB_C2T(4);
             ptx::tc_fence_after();
             const int R = t * 128 + row;
             const int n = R / 36, q = R - 36 * n;
@@ -392,6 +410,7 @@ __global__ void __launch_bounds__(576, 1) tc_conv3x3_pool_parity_kernel(const __
 #pragma unroll
             for (int m = 0; m < 4; ++m) ptx::tmem_ld16(taddr + (uint32_t)(m * 64), v[m]);
             ptx::tmem_wait_ld();
+            ZB_C2T(5);
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(tempty(b));   // this warp has its values: the set may be overwritten once all 16 arrived
@@ -408,7 +427,9 @@ __global__ void __launch_bounds__(576, 1) tc_conv3x3_pool_parity_kernel(const __
                 pk[j4] = relu_s8x4(pack_sat_s8x4(r[0], r[1], r[2], r[3]));
             }
             if (live) *reinterpret_cast<uint4*>(yw) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            ZB_C2T(6);
         }
+        if (warp == 2 && lane == 0) ZB_C2T_DUMP(4, 7);
     }
 
     // ---------------------------------------------------------------------- teardown
