@@ -120,7 +120,7 @@ def fused_step_costs(batch, n_classes=10):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at batch 65536, from the ncu captures
 # summarised under profiles/ (index = fused step).
-NCU_DRAM_TRAFFIC_B65536 = [206.5e6 + 254.2e6, 302.1e6 + 81.7e6, 105.7e6 + 9.6e6, 33.6e6 + 0.0]
+NCU_DRAM_TRAFFIC_B65536 = [205.9e6 + 253.1e6, 302.1e6 + 80.6e6, 105.7e6 + 9.6e6, 33.6e6 + 0.0]
 
 
 def cpu_reference_rate(batch_hint, scales, budget_s=12.0):
