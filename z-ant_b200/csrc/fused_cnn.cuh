@@ -357,23 +357,22 @@ __global__ void __launch_bounds__(576, 1) tc_conv3x3_pool_parity_kernel(const __
                 // MMA is bound by its 6 KB of shared-memory operands, not by its 32 cycles of math).
 #pragma unroll
                 for (int kh = 0; kh < 3; ++kh) {
-                    auto view = [&](int dy, int rx) {
+#pragma unroll
+                    for (int dy = 0; dy < 2; ++dy) {
                         const int ry = dy + kh;
-                        const int plane = (ry & 1) * 2 + (rx & 1), shift = (ry >> 1) * 6 + (rx >> 1);
-                        return ptx::smem_desc_kmajor(a_addr + (uint32_t)(plane * Cfg::PLANE_BYTES + shift * 16), 4 * Cfg::PLANE_BYTES, 128);
-                    };
-                    auto w64 = [&](int kw) { return ptx::smem_desc_kmajor(w_addr + (uint32_t)((kh * 3 + kw) * Cfg::W_TAP_BYTES), 64 * 16, 128); };
-                    auto w128 = [&](int j) { return ptx::smem_desc_kmajor(w_addr + (uint32_t)(Cfg::W_BYTES + (kh * 2 + j) * Cfg::W_PAIR_BYTES), 128 * 16, 128); };
-                    const uint32_t d0 = tmem_base + (uint32_t)(b * 256), d1 = d0 + 128u;   // window rows dy = 0 and 1: members (dy, 0), (dy, 1)
-                    // consecutive MMAs alternate between the two window rows (independent accumulators)
-                    ptx::mma_i8(d0, view(0, 1), w128(0), idesc128, kh > 0);              // the first MMA of a set initialises both members
-                    ptx::mma_i8(d1, view(1, 1), w128(0), idesc128, kh > 0);
-                    ptx::mma_i8(d0, view(0, 2), w128(1), idesc128, true);
-                    ptx::mma_i8(d1, view(1, 2), w128(1), idesc128, true);
-                    ptx::mma_i8(d0, view(0, 0), w64(0), idesc64, true);
-                    ptx::mma_i8(d1, view(1, 0), w64(0), idesc64, true);
-                    ptx::mma_i8(d0 + 64u, view(0, 3), w64(2), idesc64, true);
-                    ptx::mma_i8(d1 + 64u, view(1, 3), w64(2), idesc64, true);
+                        auto view = [&](int rx) {
+                            const int plane = (ry & 1) * 2 + (rx & 1), shift = (ry >> 1) * 6 + (rx >> 1);
+                            return ptx::smem_desc_kmajor(a_addr + (uint32_t)(plane * Cfg::PLANE_BYTES + shift * 16), 4 * Cfg::PLANE_BYTES, 128);
+                        };
+                        auto w64 = [&](int kw) { return ptx::smem_desc_kmajor(w_addr + (uint32_t)((kh * 3 + kw) * Cfg::W_TAP_BYTES), 64 * 16, 128); };
+                        auto w128 = [&](int j) { return ptx::smem_desc_kmajor(w_addr + (uint32_t)(Cfg::W_BYTES + (kh * 2 + j) * Cfg::W_PAIR_BYTES), 128 * 16, 128); };
+                        const uint32_t d = tmem_base + (uint32_t)(b * 256 + dy * 128);     // members (dy, 0) and (dy, 1): 2 x 64 columns
+                        // (alternating the two window rows between consecutive MMAs measured the same)
+                        ptx::mma_i8(d, view(1), w128(0), idesc128, kh > 0);               // the first MMA of a set initialises both members
+                        ptx::mma_i8(d, view(2), w128(1), idesc128, true);
+                        ptx::mma_i8(d, view(0), w64(0), idesc64, true);
+                        ptx::mma_i8(d + 64u, view(3), w64(2), idesc64, true);
+                    }
                 }
                 ptx::mma_commit(empty(s));
                 ptx::mma_commit(tfull(b));
