@@ -1162,7 +1162,7 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
         k.mult = (const float*)pl->aux(a_m4); k.bias = (const int32_t*)pl->aux(a_b4);
         k.y = pl->p<float>(y); k.M = (int)B; k.K = 512; k.NCLS = (int)NCLS;
         k.y_scale = f2a.y_scale; k.y_zp = f2a.y_zp; k.dq_scale = dqa.x_scale; k.dq_zp = dqa.x_zp;
-        // class counts up to 10 (the configuration's) and up to 16 have their own instantiation: the per-class loop is unrolled
+        // one or two column blocks of 8 classes
         auto launch = [&](auto nc) -> int32_t {
             constexpr int NC = decltype(nc)::value;
             constexpr int smem = fcout_smem_bytes<NC, 512>();
@@ -1175,7 +1175,7 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
             fc_out_dequant_kernel<NC, 512><<<blocks, FCOUT_THREADS, smem, ctx->stream>>>(k);
             return check_launch(ctx, "fc_out_dequant_kernel");
         };
-        return NCLS <= 10 ? launch(std::integral_constant<int, 10>{}) : launch(std::integral_constant<int, 16>{});
+        return NCLS <= 8 ? launch(std::integral_constant<int, 8>{}) : launch(std::integral_constant<int, 16>{});
     });
     for (int k = 0; k < 11; ++k) pl->t[N[k].out[0]].elided = true;   // interior tensors live only inside the fused kernels
     consumed = 12;
