@@ -86,6 +86,21 @@ def test_small_cnn_int8_with_biases_bit_exact(zb, ctx, oracle, models, scales, a
         assert len(np.unique(want[g.id_of("pool2")])) > 16
 
 
+@pytest.mark.parametrize("n_classes,batch", [(1, 3), (3, 33), (8, 17), (9, 40)])
+def test_small_cnn_int8_class_counts_and_ragged_batches(zb, ctx, oracle, models, scales, n_classes, batch):
+    """The last fused kernel has one instantiation per block of eight classes, and the batch sizes here end in
+    partly filled tiles of every stage (groups of 4 images, 128 pool windows, 128 and 16 rows)."""
+    g = models.small_cnn_int8(batch, act_scales=scales, n_classes=n_classes, bias_amplitude=(100, 1000, 5000, 300))
+    x = models.small_cnn_input(batch, 321)
+    want = graph_oracle.run(oracle, g, x)
+    plan = zb.Plan(ctx, g, fuse=True)
+    assert any("Fused" in n for n in plan.step_names())
+    got = plan.run(x)
+    assert got.shape == (batch, n_classes)
+    assert np.array_equal(got.view(np.uint32), want[g.output].view(np.uint32))
+    plan.close()
+
+
 def test_int8_close_to_fp32(zb, ctx, models, scales):
     """Sanity of the quantisation itself: int8 logits track the FP32 logits."""
     batch = 64

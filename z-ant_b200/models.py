@@ -104,24 +104,25 @@ def quantize_weights(w, axis):
     return q, s
 
 
-def small_cnn_int8(batch, seed=DEFAULT_SEED, act_scales=None, bias_amplitude=None):
+def small_cnn_int8(batch, seed=DEFAULT_SEED, act_scales=None, bias_amplitude=None, n_classes=10):
     """Configuration 2: the same CNN in QLinear form.  QuantizeLinear(1/255, uint8) on the input,
     QLinearConv / QLinearMatMul with int8 per-output-channel weights and int32 zero biases, int8
     activations with zero point 0 (scales from `act_scales`), ReLU and MaxPool on the int8 codes,
     DequantizeLinear at the end.  `bias_amplitude` (four integers, one per layer) replaces the zero
-    biases of the configuration with seeded uniform int32 values in [-amplitude, amplitude] (tests)."""
+    biases of the configuration with seeded uniform int32 values in [-amplitude, amplitude] (tests);
+    `n_classes` below 10 keeps the first columns of the last layer (tests)."""
     if act_scales is None:
         act_scales = dict(relu1=0.02, relu2=0.05, relu3=0.05, logits=0.1)
     w = small_cnn_weights(seed)
     q1, s1 = quantize_weights(w["w1"], 0)
     q2, s2 = quantize_weights(w["w2"], 0)
     q3, s3 = quantize_weights(w["w3"], 1)
-    q4, s4 = quantize_weights(w["w4"], 1)
+    q4, s4 = quantize_weights(w["w4"][:, :n_classes], 1)
     sx = float(np.float32(1.0) / np.float32(255.0))
     a1, a2, a3, a4 = (act_scales[k] for k in ("relu1", "relu2", "relu3", "logits"))
     brng = np.random.default_rng(seed + 17)
     b1, b2, b3, b4 = (np.zeros(n, np.int32) if bias_amplitude is None else brng.integers(-amp, amp + 1, n).astype(np.int32)
-                      for n, amp in zip((32, 64, 512, 10), bias_amplitude or (0, 0, 0, 0)))
+                      for n, amp in zip((32, 64, 512, n_classes), bias_amplitude or (0, 0, 0, 0)))
     g = Graph("small_cnn_int8")
     x = g.tensor("x", F32, (batch, 1, 28, 28))
     xq = g.tensor("xq", U8, (batch, 1, 28, 28))
@@ -129,11 +130,11 @@ def small_cnn_int8(batch, seed=DEFAULT_SEED, act_scales=None, bias_amplitude=Non
     c2 = g.tensor("conv2", I8, (batch, 64, 11, 11)); r2 = g.tensor("relu2", I8, (batch, 64, 11, 11)); p2 = g.tensor("pool2", I8, (batch, 64, 5, 5))
     fl = g.tensor("flat", I8, (batch, 1600))
     f1 = g.tensor("fc1", I8, (batch, 512)); r3 = g.tensor("relu3", I8, (batch, 512))
-    f2 = g.tensor("fc2", I8, (batch, 10)); y = g.tensor("logits", F32, (batch, 10))
+    f2 = g.tensor("fc2", I8, (batch, n_classes)); y = g.tensor("logits", F32, (batch, n_classes))
     W1 = g.tensor("W1", I8, (32, 1, 3, 3), q1); S1 = g.tensor("S1", F32, (32,), s1); B1 = g.tensor("B1", I32, (32,), b1)
     W2 = g.tensor("W2", I8, (64, 32, 3, 3), q2); S2 = g.tensor("S2", F32, (64,), s2); B2 = g.tensor("B2", I32, (64,), b2)
     W3 = g.tensor("W3", I8, (1600, 512), q3); S3 = g.tensor("S3", F32, (512,), s3); B3 = g.tensor("B3", I32, (512,), b3)
-    W4 = g.tensor("W4", I8, (512, 10), q4); S4 = g.tensor("S4", F32, (10,), s4); B4 = g.tensor("B4", I32, (10,), b4)
+    W4 = g.tensor("W4", I8, (512, n_classes), q4); S4 = g.tensor("S4", F32, (n_classes,), s4); B4 = g.tensor("B4", I32, (n_classes,), b4)
     qconv = dict(strides=(1, 1), pads=(0, 0, 0, 0), dilations=(1, 1), group=1, auto_pad="NOTSET")
     g.node("QuantizeLinear", [x], [xq], y_scale=sx, y_zp=0)
     g.node("QLinearConv", [xq, W1, S1, -1, B1], [c1], x_scale=sx, x_zp=0, y_scale=a1, y_zp=0, **qconv)
@@ -148,7 +149,7 @@ def small_cnn_int8(batch, seed=DEFAULT_SEED, act_scales=None, bias_amplitude=Non
     g.node("QLinearMatMul", [r3, W4, S4, -1, B4], [f2], x_scale=a3, x_zp=0, y_scale=a4, y_zp=0)
     g.node("DequantizeLinear", [f2], [y], x_scale=a4, x_zp=0)
     g.input, g.output = x, y
-    g.meta = dict(macs_per_image=194688 + 2230272 + 819200 + 5120, act_scales=dict(act_scales))
+    g.meta = dict(macs_per_image=194688 + 2230272 + 819200 + 512 * n_classes, act_scales=dict(act_scales))
     return g
 
 
