@@ -11,7 +11,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as ge  # noqa: E402
 
-REFERENCE_MODELS = "/root/reference/datasets/models"
+# the reference checkout, where one sits beside this repository (or where ZANT_REFERENCE_MODELS points); the test that
+# reads its model files is skipped elsewhere
+REFERENCE_MODELS = os.environ.get("ZANT_REFERENCE_MODELS", os.path.join(os.path.dirname(ROOT), "reference", "datasets", "models"))
 
 
 @pytest.fixture(scope="module")
