@@ -135,6 +135,11 @@ int32_t zant_b200_ctx_create(int32_t device, size_t arena_bytes, zant_ctx** out)
 int32_t zant_b200_ctx_destroy(zant_ctx* ctx);
 /* Use a caller-owned cudaStream_t (passed as void*) instead of the context's own. */
 int32_t zant_b200_ctx_set_stream(zant_ctx* ctx, void* cuda_stream);
+/* Caps the staging arena that host-pointer calls grow on demand (0 = no cap, the default).  A call
+ * whose host buffers and workspace need more returns ZANT_E_ARENA_EXHAUSTED and changes nothing;
+ * device-pointer calls and plans (which own their arena) are not affected.  No reference
+ * counterpart: the reference allocates temporaries from the process heap. */
+int32_t zant_b200_ctx_set_arena_limit(zant_ctx* ctx, size_t max_bytes);
 /* The stream kernels are launched on (a cudaStream_t as void*). */
 void* zant_b200_ctx_stream(zant_ctx* ctx);
 int32_t zant_b200_ctx_synchronize(zant_ctx* ctx);
@@ -147,6 +152,22 @@ void zant_b200_ctx_reset_launch_count(zant_ctx* ctx);
  * global traffic), best of four timed launches.  No reference counterpart; it is the
  * denominator of the roofline fractions reported for tensor-bound kernels. */
 int32_t zant_b200_measure_int8_peak(zant_ctx* ctx, int32_t iters, double* tera_ops_per_s);
+
+/* Failure-path self test (no reference counterpart).  Launches one CTA that allocates tensor
+ * memory and waits, with the same bounded wait the tensor-core kernels use but a budget of
+ * `budget_us` microseconds (clamped to [1, 100000]), on a barrier that nothing arrives on.  The
+ * wait gives up, the kernel frees its tensor memory, records the time-out in the context's status
+ * word and returns; nothing faults or hangs.  The launch itself returns ZANT_OK; the next
+ * zant_b200_ctx_synchronize (or any call that waits for the stream) returns
+ * ZANT_E_DEVICE_TIMEOUT once and clears the word, after which the context works as before. */
+int32_t zant_b200_selftest_bounded_wait(zant_ctx* ctx, uint32_t budget_us);
+
+/* Test hook (no reference counterpart): makes the `nth` next device allocation of this library
+ * (1 = the very next one) fail as if the driver had answered cudaErrorMemoryAllocation, without
+ * touching the driver; 0 disarms it.  Entry points that allocate (zant_b200_ctx_create, host-buffer
+ * staging, zant_b200_plan_finalize) then return ZANT_E_MEM_ERROR, the reference's MemError
+ * (src/Utils/errorHandler.zig:36-52), and leave their handles usable or destroyable. */
+int32_t zant_b200_debug_fail_alloc(int32_t nth);
 
 /* ------------------------------------------------------------------------------------------
  * Shape helpers (host only; usable without a GPU)
@@ -232,6 +253,18 @@ int32_t zant_b200_gemm_f32(zant_ctx* ctx,
                            const float* c, const size_t* c_shape, size_t c_rank,
                            float alpha, float beta, int32_t trans_a, int32_t trans_b,
                            float* y, const size_t* y_shape, size_t y_rank);
+
+/* tensMath.gemm_lean as generated code calls it (src/codeGen/hardcoded/hardcoded_sentiment_it.zig:137):
+ * lean_gemm (op_gemm.zig:91-185) without the rank check of the allocating wrapper.  Operands of rank 2..4
+ * (C: 1..4) are taken as [1,..,1,rows,cols]; everything else as zant_b200_gemm_f32.  (The reference reads
+ * shape[2] and shape[3] of rank-2 operands when C has to be broadcast, which is out of bounds; here that
+ * case is the ONNX Gemm result.) */
+int32_t zant_b200_gemm_lean_f32(zant_ctx* ctx,
+                                const float* a, const size_t* a_shape, size_t a_rank,
+                                const float* b, const size_t* b_shape, size_t b_rank,
+                                const float* c, const size_t* c_shape, size_t c_rank,
+                                float alpha, float beta, int32_t trans_a, int32_t trans_b,
+                                float* y, const size_t* y_shape, size_t y_rank);
 
 /* tensMath.onnx_maxpool_lean = lean_onnx_maxpool (op_pooling.zig:570-659).  SAME_* pads are
  * derived from the OUTPUT shape and the undilated kernel, as the reference does. */
@@ -440,13 +473,17 @@ int32_t zant_b200_qlinearconv_nhwc(zant_ctx* ctx,
  * per-channel requantisation constants that the kernel reads besides x, w, bias and y are kept
  * in a fixed device array inside the library (32 KiB per GPU, held until the process exits).
  *   - same arithmetic, argument meaning and error codes as zant_b200_qlinearconv;
- *   - x, w, bias, y: DEVICE pointers of the current device; w_scale, w_zp: host arrays;
+ *   - x, w, bias, y: DEVICE pointers of the current device (another GPU's memory is refused with
+ *     ZANT_E_INVALID_INPUT); w_scale, w_zp: host arrays;
  *   - at most 4096 output channels, otherwise ZANT_E_TOO_LARGE;
- *   - the first call on a device resolves the array's device address: issue it before any
- *     stream capture starts;
+ *   - the first call on a device resolves the array's device address;
+ *   - never call it on a stream that is being captured (ZANT_E_UNSUPPORTED): every call copies its
+ *     per-channel constants from host buffers of the calling thread into the array;
  *   - all calls on a device share the array, so calls whose kernels could overlap on the GPU
  *     race: keep them on one stream or order them with events;
- *   - asynchronous: returns after enqueueing on the stream. */
+ *   - it returns once the small constant copy (from pageable host memory, so it may wait for
+ *     earlier work of the stream) is handed over and the kernel is enqueued; it does not wait
+ *     for the kernel. */
 int32_t zant_b200_qlinearconv_noalloc(void* cuda_stream,
                                       int32_t x_dtype, const void* x, const size_t* x_shape, size_t x_rank,
                                       float x_scale, int32_t x_zp,
@@ -611,6 +648,36 @@ int32_t zant_b200_plan_profile_read(zant_plan* plan, float* sum_ms, int32_t* run
 void* zant_b200_plan_tensor_ptr(zant_plan* plan, int32_t id);
 /* Copies a tensor's current contents to `host_dst` (tensor-sized) after draining the stream. */
 int32_t zant_b200_plan_read_tensor(zant_plan* plan, int32_t id, void* host_dst);
+
+/* ------------------------------------------------------------------------------------------
+ * Sample-sharded predict over several GPUs of one machine.  The reference bakes the batch into the
+ * generated predict() (src/codeGen/predict.zig:34-40, :317-336) and is single-threaded; this is the
+ * extension that splits one host batch across devices.  Samples are independent, so there is no
+ * collective: device i gets the contiguous samples of zant_b200_shard_range(n, world, i) and writes
+ * its results into the matching slice of the caller's output buffer.  One context, one stream, one
+ * arena and one host worker thread per device.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct zant_multi zant_multi;
+
+/* `devices` NULL or n_devices 0: the comma-separated list in the environment variable
+ * ZANT_B200_DEVICES ("0,2,3"), else every visible device.  A device may appear more than once (two
+ * contexts on one GPU).  `arena_bytes` as for zant_b200_ctx_create. */
+int32_t zant_b200_multi_create(const int32_t* devices, size_t n_devices, size_t arena_bytes, zant_multi** out);
+/* Destroys the contexts and stops the workers; destroy the shards' plans first. */
+int32_t zant_b200_multi_destroy(zant_multi* multi);
+size_t zant_b200_multi_size(zant_multi* multi);
+/* Context of shard i: build that shard's plan on it. */
+zant_ctx* zant_b200_multi_ctx(zant_multi* multi, size_t i);
+/* Registers the finalized plan of shard i.  Its batch (leading dimension of its input and output)
+ * must be the number of samples zant_b200_shard_range gives shard i for the batches later passed
+ * to zant_b200_predict_sharded. */
+int32_t zant_b200_multi_set_plan(zant_multi* multi, size_t i, zant_plan* plan);
+/* predict() for `n_samples` samples in HOST buffers (pageable or pinned): all shards run at once,
+ * the call returns when every result is in `host_out`.  `status_per_device` (zant_b200_multi_size
+ * entries, may be NULL) receives each shard's status; the return value is the first failure, so one
+ * failing device is reported without hiding what the others did. */
+int32_t zant_b200_predict_sharded(zant_multi* multi, const void* host_in, void* host_out, size_t n_samples,
+                                  int32_t* status_per_device);
 
 #ifdef __cplusplus
 }

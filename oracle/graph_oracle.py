@@ -22,7 +22,11 @@ def run(zo, g, x):
         elif op == "MatMul":
             y = zo.mat_mul(ins[0], ins[1])
         elif op == "Gemm":
-            y = zo.gemm(ins[0], ins[1], ins[2] if len(ins) > 2 else None, a.get("alpha", 1.0), a.get("beta", 1.0),
+            # gemm_lean multiplies the last two dimensions whatever the rank (op_gemm.zig:128, :150-156); the
+            # restated function takes the reference's [b,c,rows,cols] form, so lower ranks get leading ones
+            def four_d(t):
+                return None if t is None else t.reshape((1,) * (4 - t.ndim) + tuple(t.shape))
+            y = zo.gemm(four_d(ins[0]), four_d(ins[1]), four_d(ins[2]) if len(ins) > 2 else None, a.get("alpha", 1.0), a.get("beta", 1.0),
                         bool(a.get("trans_a", 0)), bool(a.get("trans_b", 0)))
         elif op == "MaxPool":
             y = zo.onnx_maxpool_lean(ins[0], oshape, a["kernel_shape"], a.get("strides", (1, 1)), a.get("dilations", (1, 1)),

@@ -11,9 +11,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as ge  # noqa: E402
 
-# the reference checkout, where one sits beside this repository (or where ZANT_REFERENCE_MODELS points); the test that
-# reads its model files is skipped elsewhere
-REFERENCE_MODELS = os.environ.get("ZANT_REFERENCE_MODELS", os.path.join(os.path.dirname(ROOT), "reference", "datasets", "models"))
+# Two small model files of the reference (datasets/models/mnist-8/mnist-8.onnx, datasets/models/debug_model/debug_model.onnx)
+# are kept as fixtures beside the golden vectors, so that these tests run wherever the repository does.
+GOLDEN = os.path.join(ROOT, "tests", "golden")
 
 
 @pytest.fixture(scope="module")
@@ -54,11 +54,10 @@ def test_batch_override_and_errors(pkg):
         oi.read_model(b"\x08\x08")            # a ModelProto without a graph
 
 
-@pytest.mark.skipif(not os.path.exists(os.path.join(REFERENCE_MODELS, "mnist-8", "mnist-8.onnx")), reason="reference model files are not on this machine")
 def test_reads_the_references_mnist_model(pkg, oracle):
     """The MNIST model the reference ships: decoded, shapes inferred, run by the oracle."""
     zb, models, oi = pkg
-    m = oi.read_model(os.path.join(REFERENCE_MODELS, "mnist-8", "mnist-8.onnx"))
+    m = oi.read_model(os.path.join(GOLDEN, "mnist-8.onnx"))
     ops = [n["op"] for n in m["nodes"]]
     assert ops.count("Conv") == 2 and ops.count("MaxPool") == 2 and "MatMul" in ops
     g = oi.to_graph(m, batch=2)
@@ -66,6 +65,40 @@ def test_reads_the_references_mnist_model(pkg, oracle):
     x = np.random.default_rng(0).random((2, 1, 28, 28), dtype=np.float32)
     y = graph_oracle.run(oracle, g, x)[g.output]
     assert y.shape == (2, 10) and np.isfinite(y).all() and len(np.unique(y)) == 20
+
+
+def test_reads_the_references_debug_model(pkg, oracle):
+    """The reference's debug model (Gemm, Relu, Gemm, Relu, Softmax on a symbolic batch)."""
+    zb, models, oi = pkg
+    g = oi.to_graph(oi.read_model(os.path.join(GOLDEN, "debug_model.onnx")), batch=3)
+    assert [n["op"] for n in g.nodes] == ["Gemm", "Relu", "Gemm", "Relu", "Softmax"]
+    x = np.random.default_rng(1).random(g.tensors[g.input]["shape"], dtype=np.float32)
+    y = graph_oracle.run(oracle, g, x)[g.output]
+    assert np.allclose(y.sum(axis=1), 1.0, atol=1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,batch", [("mnist-8.onnx", 1), ("mnist-8.onnx", 6), ("debug_model.onnx", 3)])
+def test_reference_models_run_as_plans(pkg, oracle, name, batch):
+    """The reference's own model files through ingest -> Plan on the GPU against the oracle running the same graph
+    (the call sequence of a generated predict(), src/codeGen/hardcoded/hardcoded_mnist8.zig:140-288)."""
+    zb, models, oi = pkg
+    g = oi.to_graph(oi.read_model(os.path.join(GOLDEN, name)), batch=batch)
+    x = np.random.default_rng(7).random(g.tensors[g.input]["shape"], dtype=np.float32)
+    want = graph_oracle.run(oracle, g, x)
+    ctx = zb.Context(0)
+    try:
+        for fuse in (False, True):
+            plan = zb.Plan(ctx, g, fuse=fuse)
+            got = plan.run(x)
+            ref = want[g.output]
+            tol = 1e-4 * np.maximum(np.abs(ref), 1e-2 * np.abs(ref).max())       # the FP32 contract
+            assert np.all(np.abs(got - ref) <= tol)
+            if name.startswith("mnist"):                                          # no transcendental op: bit-identical
+                assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+            plan.close()
+    finally:
+        ctx.close()
 
 
 @pytest.mark.gpu

@@ -3,9 +3,9 @@
 A caller with a fixed memory budget (or one that mirrors Z-Ant's static-array-only generated code)
 cannot create a Context, because a Context owns a cudaMalloc'd arena.  The no-allocation variant
 keeps its per-channel constants in a fixed device array inside the library.  This test calls it
-through the C ABI twice in a row with different layer shapes — the second call finds the first
-call's constants still in the shared array and must overwrite what it uses — and requires
-bit-identical results to the regular entry point, which is itself checked against the oracle.
+through the C ABI several times in a row with different layer shapes — each later call finds the
+previous call's constants still in the shared array and must overwrite what it uses — and requires
+bit-identical results to the regular entry point and to the CPU oracle.
 The file name sorts last on purpose: a run that stops at the first failure has then already run
 every other test.
 """
@@ -24,12 +24,14 @@ def _case(rng, N, C, H, W, M, k, group, xdt, per_channel):
     return x, w, ws, bias
 
 
-def test_noalloc_matches_regular_entry_point_twice(zb, ctx):
+def test_noalloc_matches_regular_entry_point_twice(zb, ctx, oracle):
     torch = pytest.importorskip("torch")
     rng = np.random.default_rng(2024)
     cases = [
         dict(N=2, C=16, H=12, W=11, M=24, k=3, group=1, xdt=I8, per_channel=True, pads=(1, 1, 1, 1), stride=(1, 1), act="relu", x_zp=0, y_zp=0),
         dict(N=3, C=8, H=9, W=9, M=8, k=3, group=8, xdt=U8, per_channel=False, pads=(0, 1, 1, 0), stride=(2, 2), act=None, x_zp=128, y_zp=3),
+        # per-channel weight zero points: the second half of the shared array
+        dict(N=1, C=6, H=7, W=8, M=10, k=3, group=1, xdt=I8, per_channel=True, pads=(1, 0, 0, 1), stride=(1, 1), act="relu6", x_zp=-5, y_zp=-2),
     ]
     for c in cases:                                     # two calls in a row on the same shared array
         x, w, ws, bias = _case(rng, c["N"], c["C"], c["H"], c["W"], c["M"], c["k"], c["group"], c["xdt"], c["per_channel"])
@@ -43,6 +45,7 @@ def test_noalloc_matches_regular_entry_point_twice(zb, ctx):
                                **dict(kw, bias=bd))
         torch.cuda.synchronize()
         assert np.array_equal(yd.cpu().numpy(), want)
+        assert np.array_equal(want, oracle.qlinearconv(x, 0.02, c["x_zp"], w, ws, wz, 0.4, c["y_zp"], y_dtype=I8, **kw))
 
 
 def test_noalloc_rejects_what_it_cannot_hold(zb):
@@ -58,3 +61,27 @@ def test_noalloc_rejects_what_it_cannot_hold(zb):
     with pytest.raises(zb.ZantError) as e:
         zb.qlinearconv_noalloc(x, 0.1, 0, host_w, [0.1], None, 0.1, 0, y4)
     assert e.value.name == "InvalidInput"
+
+
+def test_noalloc_refuses_a_capturing_stream(zb):
+    """Every call copies its constants from host buffers, which a captured graph would re-read at each replay:
+    the entry point refuses a stream that is being captured, and works again once the capture has ended."""
+    torch = pytest.importorskip("torch")
+    x = torch.ones((1, 2, 4, 4), dtype=torch.int8, device="cuda")
+    w = torch.ones((3, 2, 1, 1), dtype=torch.int8, device="cuda")
+    y = torch.zeros((1, 3, 4, 4), dtype=torch.int8, device="cuda")
+    dummy = torch.zeros(16, device="cuda")
+    zb.qlinearconv_noalloc(x, 1.0, 0, w, [1.0], None, 1.0, 0, y)          # first call on the device: before any capture
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=s, capture_error_mode="thread_local"):
+        dummy.add_(1.0)
+        with pytest.raises(zb.ZantError) as e:
+            zb.qlinearconv_noalloc(x, 1.0, 0, w, [1.0], None, 1.0, 0, y, stream=torch.cuda.current_stream().cuda_stream)
+        assert e.value.name == "Unsupported"
+    torch.cuda.synchronize()
+    y.zero_()
+    zb.qlinearconv_noalloc(x, 1.0, 0, w, [1.0], None, 1.0, 0, y)
+    torch.cuda.synchronize()
+    assert int(y.sum()) == 2 * 3 * 16

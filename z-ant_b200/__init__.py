@@ -274,6 +274,14 @@ class Context:
     def set_stream(self, cuda_stream_ptr):
         check(lib().zant_b200_ctx_set_stream(self._h, C.c_void_p(cuda_stream_ptr)))
 
+    def set_arena_limit(self, max_bytes):
+        """Caps the staging arena of host-pointer calls (0 = grow on demand)."""
+        check(lib().zant_b200_ctx_set_arena_limit(self._h, C.c_size_t(int(max_bytes))))
+
+    def selftest_bounded_wait(self, budget_us=50):
+        """Launches the bounded-wait self test; the next synchronize() raises DeviceTimeout once."""
+        check(lib().zant_b200_selftest_bounded_wait(self._h, C.c_uint32(int(budget_us))))
+
     def measure_int8_peak(self, iters=20000):
         """Attainable int8 tensor rate (TOP/s) from the resident-tile tcgen05 probe."""
         v = C.c_double(0.0)
@@ -327,6 +335,19 @@ class Context:
         check(lib().zant_b200_gemm_f32(self._h, _ptr(a), as_, C.c_size_t(ar), _ptr(b), bs, C.c_size_t(br), _ptr(c), cs, C.c_size_t(cr),
                                        C.c_float(alpha), C.c_float(beta), C.c_int32(int(transA)), C.c_int32(int(transB)),
                                        _ptr(y), ys, C.c_size_t(yr)))
+        return y
+
+    def gemm_lean(self, a, b, c=None, alpha=1.0, beta=1.0, transA=False, transB=False, out=None):
+        """gemm_lean as generated code calls it: operands of rank 2..4, the last two dimensions are multiplied."""
+        a = _host(a, np.float32); b = _host(b, np.float32); c = _host(c, np.float32)
+        sa, sb = _shape(a), _shape(b)
+        yshape = tuple(sa[:-2]) + (sa[-1] if transA else sa[-2], sb[-2] if transB else sb[-1])
+        y = self._out(out, yshape, F32)
+        as_, ar = _sz(sa); bs, br = _sz(sb); ys, yr = _sz(yshape)
+        cs, cr = _sz(None if c is None else _shape(c))
+        check(lib().zant_b200_gemm_lean_f32(self._h, _ptr(a), as_, C.c_size_t(ar), _ptr(b), bs, C.c_size_t(br), _ptr(c), cs, C.c_size_t(cr),
+                                            C.c_float(alpha), C.c_float(beta), C.c_int32(int(transA)), C.c_int32(int(transB)),
+                                            _ptr(y), ys, C.c_size_t(yr)))
         return y
 
     def onnx_maxpool_lean(self, x, y_shape, kernel, strides, dilations, pads, auto_pad="NOTSET", out=None):
@@ -678,6 +699,11 @@ def qlinearconv_noalloc(x, x_scale, x_zp, w, w_scale, w_zp, y_scale, y_zp, out, 
     return out
 
 
+def debug_fail_alloc(nth):
+    """Test hook: the `nth` next device allocation of the library fails (0 disarms)."""
+    check(lib().zant_b200_debug_fail_alloc(C.c_int32(int(nth))))
+
+
 def qconv_output_shape(x_shape, w_shape, stride, pads, dilations, auto_pad="NOTSET"):
     """ONNX output shape of QLinearConv (explicit pads unless auto_pad says otherwise)."""
     sh = stride[0] if len(stride) > 0 else 1
@@ -847,3 +873,68 @@ class Plan:
     @property
     def launches_per_run(self):
         return int(lib().zant_b200_plan_launches_per_run(self._h))
+
+
+class _ShardContext(Context):
+    """Context of one shard of a ShardedPredict (owned by the multi handle, not closed by itself)."""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    def close(self):
+        self._h = C.c_void_p(None)
+
+
+class ShardedPredict:
+    """predict() over several GPUs of one machine (zant_b200_multi_* / zant_b200_predict_sharded):
+    `make_graph(batch)` builds the graph of one shard; the global batch is split by shard_range, every
+    device runs its own plan on its own context, stream and worker thread, and writes its slice of
+    the output.  No collective."""
+
+    def __init__(self, make_graph, global_batch, devices=None, fuse=True, arena_bytes=0):
+        L = lib()
+        L.zant_b200_multi_size.restype = C.c_size_t
+        L.zant_b200_multi_ctx.restype = C.c_void_p
+        self._h = C.c_void_p(None)
+        devs = None if not devices else (C.c_int32 * len(devices))(*devices)
+        check(L.zant_b200_multi_create(devs, C.c_size_t(0 if not devices else len(devices)), C.c_size_t(arena_bytes), C.byref(self._h)))
+        self.world = int(L.zant_b200_multi_size(self._h))
+        self.global_batch = int(global_batch)
+        self.plans, self.contexts = [], []
+        try:
+            for i in range(self.world):
+                _b, count = shard_range(self.global_batch, self.world, i)
+                ctx = _ShardContext(C.c_void_p(L.zant_b200_multi_ctx(self._h, C.c_size_t(i))))
+                self.contexts.append(ctx)
+                if count == 0:
+                    self.plans.append(None)
+                    continue
+                plan = Plan(ctx, make_graph(count), fuse=fuse)
+                self.plans.append(plan)
+                check(L.zant_b200_multi_set_plan(self._h, C.c_size_t(i), plan._h))
+        except Exception:
+            self.close()
+            raise
+        first = next(p for p in self.plans if p is not None)
+        self.sample_in = tuple(first.in_shape[1:]); self.sample_out = tuple(first.out_shape[1:])
+        self.in_dtype, self.out_dtype = first.in_dtype, first.out_dtype
+
+    def run(self, x, out=None, return_status=False):
+        """x: host array (numpy, or a CPU torch tensor, pinned or not) of the global batch."""
+        x = _host(x, NP_DTYPE[self.in_dtype]) if not hasattr(x, "data_ptr") else x
+        y = np.zeros((self.global_batch,) + self.sample_out, NP_DTYPE[self.out_dtype]) if out is None else out
+        st = (C.c_int32 * self.world)()
+        rc = lib().zant_b200_predict_sharded(self._h, _ptr(x), _ptr(y), C.c_size_t(self.global_batch), st)
+        if return_status:
+            return y, rc, list(st)
+        check(rc)
+        return y
+
+    def close(self):
+        for p in self.plans:
+            if p is not None:
+                p.close()
+        self.plans = []
+        if self._h:
+            lib().zant_b200_multi_destroy(self._h)
+            self._h = C.c_void_p(None)

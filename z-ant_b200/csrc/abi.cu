@@ -16,6 +16,7 @@
 #include "geometry.hpp"
 #include "ops.cuh"
 #include "tc_peak.cuh"
+#include "selftest.cuh"
 #include "tc_conv_generic.cuh"
 #include "tc_conv_nchw.cuh"
 #include "dwconv_q8.cuh"
@@ -69,10 +70,13 @@ int32_t zant_b200_ctx_create(int32_t device, size_t arena_bytes, zant_ctx** out)
     e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) { delete c; return fail(ZANT_E_CUDA, "cudaStreamCreate: %s", cudaGetErrorString(e)); }
     const size_t want = arena_bytes ? arena_bytes : (size_t)256 << 20;
-    e = cudaMalloc((void**)&c->arena, want);
-    if (e != cudaSuccess) { cudaStreamDestroy(c->stream); delete c; return fail(ZANT_E_CUDA, "cudaMalloc(%zu): %s", want, cudaGetErrorString(e)); }
+    e = dev_malloc((void**)&c->arena, want);
+    if (e != cudaSuccess) {
+        cudaGetLastError(); cudaStreamDestroy(c->stream); delete c;
+        return fail(e == cudaErrorMemoryAllocation ? ZANT_E_MEM_ERROR : ZANT_E_CUDA, "cudaMalloc(%zu): %s", want, cudaGetErrorString(e));
+    }
     c->arena_bytes = want;
-    e = cudaMalloc((void**)&c->status_word, sizeof(int));
+    e = dev_malloc((void**)&c->status_word, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(c->status_word, 0, sizeof(int));
     if (e != cudaSuccess) { cudaFree(c->arena); cudaStreamDestroy(c->stream); delete c; return fail(ZANT_E_CUDA, "status word: %s", cudaGetErrorString(e)); }
     *out = c;
@@ -97,6 +101,12 @@ int32_t zant_b200_ctx_set_stream(zant_ctx* ctx, void* cuda_stream) {
     if (ctx->own_stream && ctx->stream) ZB_CUDA(cudaStreamDestroy(ctx->stream));
     ctx->stream = static_cast<cudaStream_t>(cuda_stream);
     ctx->own_stream = false;
+    return ZANT_OK;
+}
+
+int32_t zant_b200_ctx_set_arena_limit(zant_ctx* ctx, size_t max_bytes) {
+    ZB_NEED_CTX(ctx);
+    ctx->arena_limit = max_bytes;
     return ZANT_OK;
 }
 
@@ -132,6 +142,20 @@ int32_t zant_b200_measure_int8_peak(zant_ctx* ctx, int32_t iters, double* tera_o
     cudaEventDestroy(e0); cudaEventDestroy(e1);
     const double ops = (double)ctx->sm_count * iters * 2.0 * (2.0 * 128 * 256 * 32);
     *tera_ops_per_s = ops / (best * 1e-3) / 1e12;
+    return ZANT_OK;
+}
+
+int32_t zant_b200_selftest_bounded_wait(zant_ctx* ctx, uint32_t budget_us) {
+    ZB_NEED_CTX(ctx);
+    if (budget_us == 0) budget_us = 1;
+    if (budget_us > 100000) budget_us = 100000;                 // a tenth of a second at most
+    const long long cycles = (long long)budget_us * 2000;       // ~2 GHz SM clock
+    bounded_wait_selftest_kernel<<<1, 64, 0, ctx->stream>>>(cycles, ctx->status_word);
+    return check_launch(ctx, "bounded_wait_selftest_kernel");
+}
+
+int32_t zant_b200_debug_fail_alloc(int32_t nth) {
+    alloc_failures_armed().store(nth > 0 ? nth : 0);
     return ZANT_OK;
 }
 
@@ -243,6 +267,25 @@ int32_t zant_b200_gemm_f32(zant_ctx* ctx, const float* a, const size_t* a_shape,
     Stager s(ctx);
     const int ia = s.in(a, numel(a_shape, 4) * 4), ib = s.in(b, numel(b_shape, 4) * 4);
     const int ic = s.in(c, c ? numel(c_shape, 4) * 4 : 0), iy = s.out(y, numel(y_shape, 4) * 4);
+    ZB_TRY(s.commit());
+    ZB_TRY(run_gemm_f32(ctx, g, s.ptr<float>(ia), s.ptr<float>(ib), s.ptr<float>(ic), alpha, beta, trans_a != 0, trans_b != 0, s.ptr<float>(iy)));
+    return s.finish();
+}
+
+int32_t zant_b200_gemm_lean_f32(zant_ctx* ctx, const float* a, const size_t* a_shape, size_t a_rank,
+                                const float* b, const size_t* b_shape, size_t b_rank,
+                                const float* c, const size_t* c_shape, size_t c_rank,
+                                float alpha, float beta, int32_t trans_a, int32_t trans_b,
+                                float* y, const size_t* y_shape, size_t y_rank) {
+    ZB_NEED(a_shape, "a_shape"); ZB_NEED(b_shape, "b_shape"); ZB_NEED(y_shape, "y_shape");
+    if (c && !c_shape) return fail(ZANT_E_NULL_POINTER, "c_shape is NULL");
+    GemmGeom g;
+    ZB_TRY(gemm_check_lean(a_shape, a_rank, b_shape, b_rank, c_shape, c_rank, c != nullptr, trans_a != 0, trans_b != 0, beta, y_shape, y_rank, g));
+    ZB_NEED(a, "a"); ZB_NEED(b, "b"); ZB_NEED(y, "y");
+    ZB_NEED_CTX(ctx);
+    Stager s(ctx);
+    const int ia = s.in(a, numel(a_shape, a_rank) * 4), ib = s.in(b, numel(b_shape, b_rank) * 4);
+    const int ic = s.in(c, c ? numel(c_shape, c_rank) * 4 : 0), iy = s.out(y, numel(y_shape, y_rank) * 4);
     ZB_TRY(s.commit());
     ZB_TRY(run_gemm_f32(ctx, g, s.ptr<float>(ia), s.ptr<float>(ib), s.ptr<float>(ic), alpha, beta, trans_a != 0, trans_b != 0, s.ptr<float>(iy)));
     return s.finish();
@@ -599,6 +642,7 @@ int32_t zant_b200_qlinearconv_nhwc(zant_ctx* ctx, int32_t x_dtype, const void* x
                                    const size_t* dilations, size_t n_dil, size_t group, int32_t auto_pad, int32_t activation) {
     ZB_NEED(x_shape, "x_shape"); ZB_NEED(w_shape, "w_shape"); ZB_NEED(y_shape, "y_shape");
     if (!q8_dtype(x_dtype) || !q8_dtype(y_dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearConv tensors must be int8 or uint8");
+    ZB_TRY(check_zero_point(x_dtype, x_zp, "QLinearConv x"));
     if (x_rank != 4 || y_rank != 4) return fail(ZANT_E_INVALID_DIMENSIONS, "channels-last QLinearConv takes rank-4 tensors");
     // the geometry is that of the NCHW operator on the permuted shapes
     const size_t xs[4] = {x_shape[0], x_shape[3], x_shape[1], x_shape[2]}, ys[4] = {y_shape[0], y_shape[3], y_shape[1], y_shape[2]};
@@ -637,6 +681,7 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
                               const size_t* dilations, size_t n_dil, size_t group, int32_t auto_pad, int32_t activation) {
     ZB_NEED(x_shape, "x_shape"); ZB_NEED(w_shape, "w_shape"); ZB_NEED(y_shape, "y_shape");
     if (!q8_dtype(x_dtype) || !q8_dtype(y_dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearConv tensors must be int8 or uint8");
+    ZB_TRY(check_zero_point(x_dtype, x_zp, "QLinearConv x"));
     ConvGeom g;
     ZB_TRY(conv_resolve_onnx(x_shape, x_rank, w_shape, w_rank, y_shape, y_rank, stride, n_stride, pads, n_pads, dilations, n_dil, group, auto_pad, g));
     ZB_NEED(w_scale, "w_scale");
@@ -725,6 +770,7 @@ int32_t zant_b200_qlinearmatmul(zant_ctx* ctx, int32_t a_dtype, const void* a, c
     ZB_NEED(a_shape, "a_shape"); ZB_NEED(b_shape, "b_shape"); ZB_NEED(y_shape, "y_shape");
     if (a_rank != 2 || b_rank != 2 || y_rank != 2) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearMatMul takes 2-D operands");
     if (!q8_dtype(a_dtype)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "A must be int8 or uint8");
+    ZB_TRY(check_zero_point(a_dtype, a_zp, "QLinearMatMul a"));
     if (!q8_dtype(y_dtype) && y_dtype != ZANT_I32) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "Y must be int8, uint8 or int32");
     const size_t M = a_shape[0], K = a_shape[1], N = b_shape[1];
     if (b_shape[0] != K) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "A cols %zu != B rows %zu", K, b_shape[0]);

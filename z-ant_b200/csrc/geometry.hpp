@@ -29,6 +29,16 @@ inline size_t numel(const size_t* s, size_t r) {
 inline size_t dtype_size(int32_t dt) { return (dt == ZANT_F32 || dt == ZANT_I32) ? 4 : 1; }
 inline bool dtype_valid(int32_t dt) { return dt >= ZANT_F32 && dt <= ZANT_I32; }
 
+// ONNX gives a zero point the type of its tensor.  The fast quantized kernels rely on it: they fill
+// padded pixels with the zero point as a byte, so a value outside the type's range would make them
+// disagree with the generic kernel.  Such a value is refused everywhere instead.
+inline int32_t check_zero_point(int32_t dtype, int32_t zp, const char* what) {
+    const int lo = dtype == ZANT_U8 ? 0 : -128, hi = dtype == ZANT_U8 ? 255 : 127;
+    if ((dtype == ZANT_I8 || dtype == ZANT_U8) && (zp < lo || zp > hi))
+        return fail(ZANT_E_INVALID_INPUT, "%s zero point %d is outside [%d, %d]", what, zp, lo, hi);
+    return ZANT_OK;
+}
+
 // ------------------------------------------------------------------------------------ conv
 // Everything a convolution kernel needs; produced by both the reference-rule resolver (f32
 // Conv) and the ONNX-rule resolver (QLinearConv).
@@ -318,6 +328,24 @@ inline int32_t gemm_check(const size_t* as, size_t ar, const size_t* bs, size_t 
         return fail(ZANT_E_OUTPUT_TENSOR_DIFFERENT_SIZE, "output is not [..,%zu,%zu]", g.rows, g.cols);
     if (g.rows * g.cols == 0 || g.K == 0) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "empty operand");
     return ZANT_OK;
+}
+
+// gemm_lean as generated code calls it (src/codeGen/hardcoded/hardcoded_sentiment_it.zig:137): lean_gemm itself
+// has no rank check, multiplies the last two dimensions (op_gemm.zig:128, op_mat_mul.zig:92-172) and reads C's
+// last two (one) dimensions for the broadcast (op_gemm.zig:150-156).  Operands of rank 1..3 are therefore taken
+// as [1,..,1,rows,cols]; for rank-4 operands the rules are those of gemm_check.
+inline int32_t gemm_check_lean(const size_t* as, size_t ar, const size_t* bs, size_t br,
+                               const size_t* cs, size_t cr, bool has_c, bool ta, bool tb, float beta,
+                               const size_t* ys, size_t yr, GemmGeom& g) {
+    if (ar < 2 || ar > 4 || br < 2 || br > 4 || yr < 2 || yr > 4 || (has_c && (cr < 1 || cr > 4)))
+        return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "Gemm operands must have rank 2..4 (C: 1..4)");
+    auto promote = [](const size_t* sh, size_t r, size_t out[4]) {
+        for (size_t i = 0; i < 4; ++i) out[i] = i + r < 4 ? 1 : sh[i + r - 4];
+    };
+    size_t a4[4], b4[4], c4[4] = {1, 1, 1, 1}, y4[4];
+    promote(as, ar, a4); promote(bs, br, b4); promote(ys, yr, y4);
+    if (has_c) promote(cs, cr, c4);
+    return gemm_check(a4, 4, b4, 4, has_c ? c4 : nullptr, has_c ? 4 : 0, has_c, ta, tb, beta, y4, 4, g);
 }
 
 // ------------------------------------------------------------------------------------ Add broadcast

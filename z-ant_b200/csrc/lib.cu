@@ -3,3 +3,4 @@
 #include "abi.cu"
 #include "plan.cu"
 #include "noalloc.cu"
+#include "multi.cu"

@@ -10,10 +10,16 @@
 //
 // Limits and rules for the caller
 //   * at most ZANT_NOALLOC_MAX_CHANNELS output channels; more is rejected with ZANT_E_TOO_LARGE;
-//   * x, w, bias and y must be DEVICE pointers of the current device (nothing is staged);
-//     w_scale / w_zp are small HOST arrays;
+//   * x, w, bias and y must be DEVICE pointers of the current device (nothing is staged; memory
+//     of another GPU is refused with ZANT_E_INVALID_INPUT); w_scale / w_zp are small HOST arrays;
 //   * the first call on each device looks up the device address of the array
-//     (cudaGetSymbolAddress).  Make that first call before any stream capture begins;
+//     (cudaGetSymbolAddress);
+//   * no call may be made on a stream that is being captured: every call copies its constants
+//     from host buffers of the calling thread into the array, and a captured copy would re-read
+//     those buffers at every replay.  Such a call is refused with ZANT_E_UNSUPPORTED;
+//   * the call returns once the constants have been handed to the driver (a small copy from
+//     pageable host memory, which may wait for earlier work of the stream) and the kernel is
+//     enqueued; it does not wait for the kernel;
 //   * every call on a device shares the one array and overwrites the constants it needs, so two
 //     calls whose kernels may overlap on the GPU (different streams, no dependency) race on it:
 //     serialise them, e.g. by issuing them on one stream;
@@ -56,10 +62,11 @@ int32_t scratch_address(int device, void** out) {
     return ZANT_OK;
 }
 
-bool device_pointer(const void* p) {
+// Device memory of `device` (or managed memory, which every device may touch).
+bool device_pointer(const void* p, int device) {
     cudaPointerAttributes a;
     if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
-    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+    return a.type == cudaMemoryTypeManaged || (a.type == cudaMemoryTypeDevice && a.device == device);
 }
 
 }  // namespace
@@ -74,6 +81,7 @@ extern "C" int32_t zant_b200_qlinearconv_noalloc(
     if (!x || !w || !y || !x_shape || !w_shape || !y_shape || !w_scale) return fail(ZANT_E_NULL_POINTER, "x, w, y, shapes and w_scale are required");
     const bool q8x = x_dtype == ZANT_I8 || x_dtype == ZANT_U8, q8y = y_dtype == ZANT_I8 || y_dtype == ZANT_U8;
     if (!q8x || !q8y) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearConv tensors must be int8 or uint8");
+    if (int32_t zs = check_zero_point(x_dtype, x_zp, "QLinearConv x")) return zs;
     ConvGeom g;
     int32_t st = conv_resolve_onnx(x_shape, x_rank, w_shape, w_rank, y_shape, y_rank, stride, n_stride, pads, n_pads, dilations, n_dil, group, auto_pad, g);
     if (st != ZANT_OK) return st;
@@ -86,8 +94,14 @@ extern "C" int32_t zant_b200_qlinearconv_noalloc(
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) { cudaGetLastError(); return fail(ZANT_E_CUDA_UNAVAILABLE, "no CUDA device (%s); there is no CPU fallback", cudaGetErrorString(e)); }
-    if (!device_pointer(x) || !device_pointer(w) || !device_pointer(y) || (bias && !device_pointer(bias)))
-        return fail(ZANT_E_INVALID_INPUT, "x, w, bias and y must be device pointers: this entry point stages nothing");
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    e = cudaStreamIsCapturing(stream, &capture);
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(ZANT_E_CUDA, "cudaStreamIsCapturing: %s", cudaGetErrorString(e)); }
+    if (capture != cudaStreamCaptureStatusNone)
+        return fail(ZANT_E_UNSUPPORTED, "the stream is being captured: this entry point copies per-call constants from host buffers and cannot be recorded");
+    if (!device_pointer(x, device) || !device_pointer(w, device) || !device_pointer(y, device) || (bias && !device_pointer(bias, device)))
+        return fail(ZANT_E_INVALID_INPUT, "x, w, bias and y must be device pointers of the current device %d: this entry point stages nothing", device);
     void* scratch = nullptr;
     st = scratch_address(device, &scratch);
     if (st != ZANT_OK) return st;
@@ -101,7 +115,6 @@ extern "C" int32_t zant_b200_qlinearconv_noalloc(
         h_mult[m] = xw / y_scale;
         h_wzp[m] = w_zp ? w_zp[n_w_scale == 1 ? 0 : m] : 0;
     }
-    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
     float* d_mult = reinterpret_cast<float*>(scratch);
     int32_t* d_wzp = reinterpret_cast<int32_t*>(static_cast<unsigned char*>(scratch) + 4 * ZANT_NOALLOC_MAX_CHANNELS);
     e = cudaMemcpyAsync(d_mult, h_mult, sizeof(float) * g.M, cudaMemcpyHostToDevice, stream);

@@ -238,7 +238,7 @@ int32_t zant_b200_plan_finalize(zant_plan* plan, int32_t input_id, int32_t outpu
         off += align_up(plan->scratch_bytes[a] ? plan->scratch_bytes[a] : 1, kArenaAlign);
     }
     plan->arena_bytes = off;
-    ZB_CUDA(cudaMalloc((void**)&plan->arena, off));
+    ZB_ALLOC(plan->arena, off);
     for (auto& t : plan->t) {
         if (t.alias >= 0 || t.elided) continue;
         t.arena_ptr = plan->arena + t.offset;
@@ -272,6 +272,8 @@ int32_t zant_b200_plan_run(zant_plan* plan, const void* input, void* output) {
     while (plan->t[out_root].alias >= 0) out_root = plan->t[out_root].alias;
     PlanTensor& tor = plan->t[out_root];
     const bool in_dev = is_device_ptr(input), out_dev = is_device_ptr(output);
+    if (is_foreign_device_ptr(input, ctx->device) || is_foreign_device_ptr(output, ctx->device))
+        return fail(ZANT_E_INVALID_INPUT, "input/output is device memory of another GPU than the plan's device %d", ctx->device);
     if (plan->graph_exec && !plan->profiling) {
         // replay: everything runs on the arena's own buffers
         ZB_CUDA(cudaMemcpyAsync(ti.arena_ptr, input, ti.bytes, in_dev ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, ctx->stream));
@@ -433,7 +435,7 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
             ZB_TRY(need_inputs(n, 2, 3, "Gemm"));
             const int x = n.in[0], w = n.in[1], c = opt_in(n, 2), y = n.out[0];
             GemmGeom g;
-            ZB_TRY(gemm_check(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(),
+            ZB_TRY(gemm_check_lean(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(),
                               c >= 0 ? T(c).shape.data() : nullptr, c >= 0 ? T(c).shape.size() : 0, c >= 0,
                               a.trans_a != 0, a.trans_b != 0, a.beta, T(y).shape.data(), T(y).shape.size(), g));
             const float alpha = a.alpha, beta = a.beta; const bool ta = a.trans_a != 0, tb = a.trans_b != 0;
@@ -658,6 +660,7 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
             ZB_TRY(want_dtype(pl, wz, ZANT_I32, "QLinearConv w_zp")); ZB_TRY(want_dtype(pl, b, ZANT_I32, "QLinearConv bias"));
             const int32_t xd = T(x).dtype, yd = T(y).dtype;
             if ((xd != ZANT_I8 && xd != ZANT_U8) || (yd != ZANT_I8 && yd != ZANT_U8)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearConv x/y dtype");
+            ZB_TRY(check_zero_point(xd, a.x_zp, "QLinearConv x"));
             if (!T(w).is_const || !T(ws).is_const || (wz >= 0 && !T(wz).is_const)) return fail(ZANT_E_UNSUPPORTED, "QLinearConv weights and scales must be initializers");
             ConvGeom g;
             if (a.channels_last) {
@@ -772,6 +775,7 @@ static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
             ZB_TRY(want_dtype(pl, wz, ZANT_I32, "QLinearMatMul b_zp")); ZB_TRY(want_dtype(pl, b, ZANT_I32, "QLinearMatMul bias"));
             const int32_t xd = T(x).dtype, yd = T(y).dtype;
             if (xd != ZANT_I8 && xd != ZANT_U8) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearMatMul a dtype");
+            ZB_TRY(check_zero_point(xd, a.x_zp, "QLinearMatMul a"));
             if (yd == ZANT_F32) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearMatMul y dtype");
             if (!T(w).is_const || !T(ws).is_const || (wz >= 0 && !T(wz).is_const)) return fail(ZANT_E_UNSUPPORTED, "QLinearMatMul weights and scales must be initializers");
             if (T(x).shape.size() != 2 || T(w).shape.size() != 2 || T(y).shape.size() != 2) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearMatMul takes 2-D operands");

@@ -1,5 +1,5 @@
 // Inline-PTX building blocks for sm_100a: mbarriers with BOUNDED waits, 1-D bulk async copies
-// (TMA engine, no tensor map, no cluster multicast), TMEM allocation and tcgen05 MMA / load.
+// (TMA engine, no tensor map, one destination CTA), TMEM allocation and tcgen05 MMA / load.
 //
 // Every wait in this file gives up after a clock budget and reports failure to its caller, so a
 // kernel built from these pieces cannot spin forever: the caller sets its abort flag, lets the
@@ -48,18 +48,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // About two seconds at 2 GHz; a healthy pipeline waits microseconds.
 constexpr long long kWaitBudgetCycles = 4000000000LL;
 
-// Waits for the phase with the given parity.  Returns false when the budget ran out or when
-// another role already raised `*abort_flag` (a shared-memory int).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// Waits for the phase with the given parity.  Returns false when the budget (in SM clock cycles) ran
+// out or when another role already raised `*abort_flag` (a shared-memory int).  The production kernels
+// use the default budget; the bounded-wait self test passes a budget of microseconds.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long budget_cycles = kWaitBudgetCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    const uint32_t check_mask = budget_cycles < (1LL << 24) ? 3u : 255u;   // short budgets look at the clock more often
     uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if (++spins > 32) __nanosleep(40);
-        if ((spins & 255u) == 0u) {
+        if ((spins & check_mask) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1; return false; }
+            if (clock64() - t0 > budget_cycles) { *abort_flag = 1; return false; }
         }
     }
 }
@@ -72,7 +75,7 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 
 // ---------------------------------------------------------------------------- bulk async copy (1-D)
 // global -> shared, completion counted in bytes on an mbarrier.  Addresses 16-byte aligned, size a
-// multiple of 16.  The destination is this CTA's own shared memory; no multicast.
+// multiple of 16.  The destination is this CTA's own shared memory and nothing else.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src_gmem, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst_smem), "l"(src_gmem), "r"(bytes), "r"(bar) : "memory");
@@ -81,7 +84,7 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src_gmem
 // ---------------------------------------------------------------------------- tiled TMA loads
 // Box of a tensor map -> this CTA's shared memory (128-byte aligned), completion counted in bytes
 // on an mbarrier.  The innermost coordinate times the element size must be a multiple of 16 bytes.
-// No cluster multicast.  `tmap` is the generic address of a CUtensorMap kernel parameter.
+// One destination CTA.  `tmap` is the generic address of a CUtensorMap kernel parameter.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap, int x, int y, int z, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                  ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");

@@ -2,6 +2,7 @@
 #pragma once
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -67,15 +68,26 @@ inline log_fn_t& log_fn_ref() {
     return fn;
 }
 
+// Environment switch: set and neither empty nor "0".
+inline bool env_flag(const char* name) {
+    const char* v = std::getenv(name);
+    return v && *v && std::strcmp(v, "0") != 0;
+}
+
+// One line per event to the installed callback; without a callback, to stderr when the environment
+// variable ZANT_B200_LOG is set (the run-time analogue of the generator's -Dlog option,
+// src/codeGen/math_handler.zig:35-43).
 inline void log_line(const char* fmt, ...) {
     log_fn_t fn = log_fn_ref();
-    if (!fn) return;
+    static const bool to_stderr = env_flag("ZANT_B200_LOG");
+    if (!fn && !to_stderr) return;
     char buf[512];
     va_list ap;
     va_start(ap, fmt);
     vsnprintf(buf, sizeof(buf), fmt, ap);
     va_end(ap);
-    fn(buf);
+    if (fn) fn(buf);
+    else std::fprintf(stderr, "%s\n", buf);
 }
 
 // Records a failure (status + message) for zant_b200_last_error() and returns the status.
