@@ -153,6 +153,10 @@ void zant_b200_ctx_reset_launch_count(zant_ctx* ctx);
  * denominator of the roofline fractions reported for tensor-bound kernels. */
 int32_t zant_b200_measure_int8_peak(zant_ctx* ctx, int32_t iters, double* tera_ops_per_s);
 
+/* The same probe issued back to back for `seconds` (clamped to [0.05, 10]) and timed as one span: the rate the
+ * tensor cores sustain under the power cap, the denominator for kernels timed inside a seconds-long loop. */
+int32_t zant_b200_measure_int8_peak_sustained(zant_ctx* ctx, double seconds, double* tera_ops_per_s);
+
 /* Failure-path self test (no reference counterpart).  Launches one CTA that allocates tensor
  * memory and waits, with the same bounded wait the tensor-core kernels use but a budget of
  * `budget_us` microseconds (clamped to [1, 100000]), on a barrier that nothing arrives on.  The
@@ -638,6 +642,11 @@ int32_t zant_b200_plan_launches_per_run(zant_plan* plan);
 /* Number of launch steps of a finalized plan and the name of step i ("QLinearConv", ...). */
 int32_t zant_b200_plan_step_count(zant_plan* plan);
 const char* zant_b200_plan_step_name(zant_plan* plan, int32_t step);
+/* Algorithmic work of step i: multiply-accumulates of the contractions it covers, and bytes = every tensor
+ * that crosses the step's boundary (inputs and initializers read, results written), each counted once at its
+ * storage type; tensors interior to a fused step do not count.  These are the numerators of the roofline
+ * figures the benchmark reports per step.  Either pointer may be NULL. */
+int32_t zant_b200_plan_step_cost(zant_plan* plan, int32_t step, double* macs, double* bytes);
 /* Per-step device timing: when enabled, every run records one CUDA event before each step and
  * one after the last on the context's stream (no synchronisation is added).  _read drains the
  * stream, adds the elapsed milliseconds of every recorded run to sum_ms[step] (step_count

@@ -288,6 +288,11 @@ class Context:
         check(lib().zant_b200_measure_int8_peak(self._h, C.c_int32(iters), C.byref(v)))
         return v.value
 
+    def measure_int8_peak_sustained(self, seconds=2.0):
+        out = C.c_double(0.0)
+        check(lib().zant_b200_measure_int8_peak_sustained(self._h, C.c_double(float(seconds)), C.byref(out)))
+        return out.value
+
     def launch_count(self):
         return int(lib().zant_b200_ctx_launch_count(self._h))
 
@@ -850,6 +855,16 @@ class Plan:
     def step_names(self):
         L = lib()
         return [L.zant_b200_plan_step_name(self._h, C.c_int32(i)).decode() for i in range(L.zant_b200_plan_step_count(self._h))]
+
+    def step_costs(self):
+        """[(macs, bytes)] per step: the algorithmic work behind the roofline figures."""
+        L = lib()
+        out = []
+        for i in range(L.zant_b200_plan_step_count(self._h)):
+            m, b = C.c_double(0), C.c_double(0)
+            check(L.zant_b200_plan_step_cost(self._h, C.c_int32(i), C.byref(m), C.byref(b)))
+            out.append((m.value, b.value))
+        return out
 
     def use_graph(self, enable=True):
         """Replays all steps as one captured CUDA graph per run (batch-1 latency)."""

@@ -145,6 +145,38 @@ int32_t zant_b200_measure_int8_peak(zant_ctx* ctx, int32_t iters, double* tera_o
     return ZANT_OK;
 }
 
+int32_t zant_b200_measure_int8_peak_sustained(zant_ctx* ctx, double seconds, double* tera_ops_per_s) {
+    ZB_NEED(tera_ops_per_s, "tera_ops_per_s");
+    ZB_NEED_CTX(ctx);
+    if (!(seconds > 0.05)) seconds = 0.05;
+    if (seconds > 10.0) seconds = 10.0;
+    ZB_CUDA(cudaFuncSetAttribute(tc_peak_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PEAK_SMEM));
+    const int iters = 20000;                                   // ~15 ms per launch at the burst rate
+    cudaEvent_t e0, e1;
+    ZB_CUDA(cudaEventCreate(&e0)); ZB_CUDA(cudaEventCreate(&e1));
+    tc_peak_i8_kernel<<<ctx->sm_count, 128, PEAK_SMEM, ctx->stream>>>(iters, ctx->status_word);   // warm-up
+    ZB_TRY(check_launch(ctx, "tc_peak_i8_kernel"));
+    ZB_TRY(drain_and_check_status(ctx));
+    // launches back to back, in batches that are timed on the device, until the requested time has passed
+    double total_ms = 0.0; long long launches = 0;
+    while (total_ms < seconds * 1e3) {
+        ZB_CUDA(cudaEventRecord(e0, ctx->stream));
+        for (int k = 0; k < 16; ++k) {
+            tc_peak_i8_kernel<<<ctx->sm_count, 128, PEAK_SMEM, ctx->stream>>>(iters, ctx->status_word);
+            ZB_TRY(check_launch(ctx, "tc_peak_i8_kernel"));
+        }
+        ZB_CUDA(cudaEventRecord(e1, ctx->stream));
+        ZB_TRY(drain_and_check_status(ctx));
+        float ms = 0.0f;
+        ZB_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        total_ms += ms; launches += 16;
+    }
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    const double ops = (double)launches * ctx->sm_count * iters * 2.0 * (2.0 * 128 * 256 * 32);
+    *tera_ops_per_s = ops / (total_ms * 1e-3) / 1e12;
+    return ZANT_OK;
+}
+
 int32_t zant_b200_selftest_bounded_wait(zant_ctx* ctx, uint32_t budget_us) {
     ZB_NEED_CTX(ctx);
     if (budget_us == 0) budget_us = 1;

@@ -61,6 +61,7 @@ struct zant_plan {
     size_t arena_bytes = 0;
     std::vector<std::function<int32_t()>> steps;
     std::vector<std::string> step_names;
+    std::vector<double> step_macs, step_bytes;   // algorithmic work of each step: multiply-accumulates, bytes crossing the step's boundary
     int launches_per_run = 0;
     bool profiling = false;
     cudaGraphExec_t graph_exec = nullptr;   // replay of all steps on arena buffers
@@ -192,7 +193,60 @@ int32_t zant_b200_plan_node(zant_plan* plan, int32_t op, const int32_t* inputs, 
 }
 
 static int32_t build_node(zant_plan* pl, size_t node_index, int32_t fuse);
+static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t fuse);
 static int32_t try_fuse(zant_plan* pl, size_t node_index, size_t& consumed);
+
+// Multiply-accumulates of one node (contractions only; everything else counts as 0).
+static double node_macs(const zant_plan* pl, const PlanNode& n) {
+    auto shape = [&](int id) -> const std::vector<size_t>& { return pl->t[id].shape; };
+    auto count = [&](int id) { double c = 1; for (size_t d : shape(id)) c *= (double)d; return c; };
+    switch (n.op) {
+        case ZANT_OP_CONV:
+        case ZANT_OP_QLINEAR_CONV: {
+            if (n.in.size() < 2 || n.out.empty() || shape(n.in[1]).size() != 4) return 0;
+            const auto& w = shape(n.in[1]);
+            return count(n.out[0]) * (double)w[1] * (double)w[2] * (double)w[3];
+        }
+        case ZANT_OP_MATMUL:
+        case ZANT_OP_QLINEAR_MATMUL:
+        case ZANT_OP_GEMM: {
+            if (n.in.size() < 2 || n.out.empty() || shape(n.in[0]).size() < 2) return 0;
+            const auto& a = shape(n.in[0]);
+            const size_t k = (n.op == ZANT_OP_GEMM && n.a.trans_a) ? a[a.size() - 2] : a[a.size() - 1];
+            return count(n.out[0]) * (double)k;
+        }
+        default: return 0;
+    }
+}
+
+// Cost of the steps that cover nodes [first, first + count): MACs of the nodes; bytes = every tensor that is read
+// from outside the group (initializers included) or written by it and still materialised, each counted once.
+static void record_step_cost(zant_plan* pl, size_t first_step, size_t first, size_t count) {
+    double macs = 0, bytes = 0;
+    std::vector<char> produced(pl->t.size(), 0), seen(pl->t.size(), 0);
+    auto root = [&](int id) { while (pl->t[id].alias >= 0) id = pl->t[id].alias; return id; };
+    for (size_t i = first; i < first + count; ++i) for (int o : pl->nodes[i].out) produced[root(o)] = 1;
+    for (size_t i = first; i < first + count; ++i) {
+        const PlanNode& n = pl->nodes[i];
+        macs += node_macs(pl, n);
+        if (n.op == ZANT_OP_RESHAPE) continue;
+        for (int id : n.in) {
+            if (id < 0) continue;
+            const int r = root(id);
+            if (!produced[r] && !seen[r]) { seen[r] = 1; bytes += (double)pl->t[id].bytes; }
+        }
+        for (int o : n.out) {
+            const int r = root(o);
+            if (!pl->t[r].elided && !seen[r]) { seen[r] = 1; bytes += (double)pl->t[o].bytes; }
+        }
+    }
+    pl->step_macs.resize(pl->steps.size(), 0.0);
+    pl->step_bytes.resize(pl->steps.size(), 0.0);
+    if (pl->steps.size() > first_step) {       // a group may emit several steps: the work is booked on its last one
+        pl->step_macs.back() = macs;
+        pl->step_bytes.back() = bytes;
+    }
+}
 
 int32_t zant_b200_plan_finalize(zant_plan* plan, int32_t input_id, int32_t output_id, int32_t fuse) {
     if (!plan) return fail(ZANT_E_BAD_HANDLE, "plan is NULL");
@@ -204,7 +258,7 @@ int32_t zant_b200_plan_finalize(zant_plan* plan, int32_t input_id, int32_t outpu
     ZB_CUDA(cudaSetDevice(ctx->device));
 
     // 1. validate nodes, derive constants, record launch closures
-    plan->steps.clear(); plan->step_names.clear();
+    plan->steps.clear(); plan->step_names.clear(); plan->step_macs.clear(); plan->step_bytes.clear();
     size_t i = 0;
     while (i < plan->nodes.size()) {
         size_t consumed = 0;
@@ -356,6 +410,14 @@ const char* zant_b200_plan_step_name(zant_plan* plan, int32_t step) {
     return plan->step_names[step].c_str();
 }
 
+int32_t zant_b200_plan_step_cost(zant_plan* plan, int32_t step, double* macs, double* bytes) {
+    if (!plan || !plan->finalized) return fail(ZANT_E_BAD_HANDLE, "plan is NULL or not finalized");
+    if (step < 0 || step >= (int32_t)plan->steps.size()) return fail(ZANT_E_INVALID_INPUT, "step %d of %zu", step, plan->steps.size());
+    if (macs) *macs = step < (int32_t)plan->step_macs.size() ? plan->step_macs[step] : 0.0;
+    if (bytes) *bytes = step < (int32_t)plan->step_bytes.size() ? plan->step_bytes[step] : 0.0;
+    return ZANT_OK;
+}
+
 int32_t zant_b200_plan_profile(zant_plan* plan, int32_t enable) {
     if (!plan || !plan->finalized) return fail(ZANT_E_BAD_HANDLE, "plan is NULL or not finalized");
     plan->profiling = enable != 0;
@@ -401,7 +463,14 @@ int32_t zant_b200_plan_read_tensor(zant_plan* plan, int32_t id, void* host_dst) 
 // --------------------------------------------------------------------------------------------
 // One node -> one (or a few) kernel launches, using the same resolvers as the single-op ABI.
 // --------------------------------------------------------------------------------------------
-static int32_t build_node(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
+static int32_t build_node(zant_plan* pl, size_t node_index, int32_t fuse) {
+    const size_t first_step = pl->steps.size();
+    ZB_TRY(build_node_impl(pl, node_index, fuse));
+    record_step_cost(pl, first_step, node_index, 1);
+    return ZANT_OK;
+}
+
+static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t /*fuse*/) {
     const PlanNode& n = pl->nodes[node_index];
     const zant_node_attrs& a = n.a;
     zant_ctx* ctx = pl->ctx;
@@ -1183,5 +1252,15 @@ static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
     });
     for (int k = 0; k < 11; ++k) pl->t[N[k].out[0]].elided = true;   // interior tensors live only inside the fused kernels
     consumed = 12;
+    {
+        // algorithmic work of the four fused steps: tensors that cross a kernel boundary once at their storage type,
+        // weights included; of the 13 x 13 pooled pixels of stage 1 only the 12 x 12 that stage 2's pool reads exist
+        const double Bd = (double)B, nc = (double)NCLS;
+        const double macs[4] = {Bd * 194688.0, Bd * 2230272.0, Bd * 819200.0, Bd * 512.0 * nc};
+        const double bytes[4] = {Bd * (784.0 * 4 + 144.0 * 32) + 288.0, Bd * (144.0 * 32 + 1600.0) + 64.0 * 288, Bd * (1600.0 + 512.0) + 1600.0 * 512,
+                                 Bd * (512.0 + 4.0 * nc) + 512.0 * nc};
+        pl->step_macs.resize(pl->steps.size(), 0.0); pl->step_bytes.resize(pl->steps.size(), 0.0);
+        for (int k = 0; k < 4; ++k) { pl->step_macs[pl->steps.size() - 4 + k] = macs[k]; pl->step_bytes[pl->steps.size() - 4 + k] = bytes[k]; }
+    }
     return ZANT_OK;
 }

@@ -171,7 +171,9 @@ def qconv_case(name, batch=None, seed=DEFAULT_SEED):
         c["N"] = batch
     rng = np.random.default_rng(seed + sum(ord(ch) for ch in name))
     x = rng.integers(-128, 128, (c["N"], c["C"], c["H"], c["W"]), dtype=np.int8)
-    w = rng.integers(-127, 128, (c["K"], c["C"] // c["group"], c["k"], c["k"]), dtype=np.int8)
+    # the weights come from a generator of their own, so that they do not depend on the batch size
+    wrng = np.random.default_rng(DEFAULT_SEED + 7919 + sum(ord(ch) for ch in name))
+    w = wrng.integers(-127, 128, (c["K"], c["C"] // c["group"], c["k"], c["k"]), dtype=np.int8)
     c.update(x=x, w=w, x_scale=0.02, w_scale=np.array([0.02], np.float32), y_scale=0.02,
              stride=(c["s"], c["s"]), pads=(c["p"],) * 4, dilations=(1, 1))
     oh = (c["H"] + 2 * c["p"] - c["k"]) // c["s"] + 1
