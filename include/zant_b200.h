@@ -135,6 +135,15 @@ int32_t zant_b200_ctx_create(int32_t device, size_t arena_bytes, zant_ctx** out)
 int32_t zant_b200_ctx_destroy(zant_ctx* ctx);
 /* Use a caller-owned cudaStream_t (passed as void*) instead of the context's own. */
 int32_t zant_b200_ctx_set_stream(zant_ctx* ctx, void* cuda_stream);
+/* Float precision of the contractions (Conv, MatMul, Gemm) issued through this context.  Off (the default, unless
+ * the environment variable ZANT_B200_TF32 is set when the context is created): the exact FP32 kernels, which keep
+ * the reference's order of operations (sequential fp32 accumulation, op_mat_mul.zig:132-148) and are bit-identical
+ * to it.  On: tensor-core kernels (tcgen05 kind::tf32, operands rounded to TF32, fp32 accumulation) whose results
+ * are within 2e-3 of the reference, |y - ref| <= 2e-3 * max(|ref|, 1e-2 * max|ref|).  A plan takes the setting of
+ * its context when it is finalized; zant_b200_conv_f32 takes it at each call.  No reference counterpart. */
+int32_t zant_b200_ctx_set_tf32(zant_ctx* ctx, int32_t enable);
+int32_t zant_b200_ctx_get_tf32(zant_ctx* ctx);
+
 /* Caps the staging arena that host-pointer calls grow on demand (0 = no cap, the default).  A call
  * whose host buffers and workspace need more returns ZANT_E_ARENA_EXHAUSTED and changes nothing;
  * device-pointer calls and plans (which own their arena) are not affected.  No reference

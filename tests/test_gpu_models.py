@@ -223,7 +223,7 @@ def test_tiny_yolo_int8_bit_exact(zb, ctx, oracle, models):
     got = plan.run(x)
     assert np.array_equal(got.view(np.uint32), want[q.output].view(np.uint32))
     assert np.array_equal(plan.read_tensor(q.meta["head13"]), want[q.meta["head13"]])
-    assert "QLinearConv(tc-implicit)" in plan.step_names()
+    assert any(n.startswith("QLinearConv(tc-implicit)") for n in plan.step_names())
     # the quantized detector tracks the FP32 one
     ref = graph_oracle.run(oracle, f, x)[f.output]
     assert np.abs(got - ref).max() <= 0.2 * np.abs(ref).max()

@@ -17,6 +17,7 @@
 #include "ops.cuh"
 #include "tc_peak.cuh"
 #include "selftest.cuh"
+#include "tc_gemm_tf32.cuh"
 #include "tc_conv_generic.cuh"
 #include "tc_conv_nchw.cuh"
 #include "dwconv_q8.cuh"
@@ -79,6 +80,7 @@ int32_t zant_b200_ctx_create(int32_t device, size_t arena_bytes, zant_ctx** out)
     e = dev_malloc((void**)&c->status_word, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(c->status_word, 0, sizeof(int));
     if (e != cudaSuccess) { cudaFree(c->arena); cudaStreamDestroy(c->stream); delete c; return fail(ZANT_E_CUDA, "status word: %s", cudaGetErrorString(e)); }
+    c->tf32 = env_flag("ZANT_B200_TF32");
     *out = c;
     log_line("zant_b200 context on device %d (%s, %d SMs)", device, prop.name, prop.multiProcessorCount);
     return ZANT_OK;
@@ -103,6 +105,14 @@ int32_t zant_b200_ctx_set_stream(zant_ctx* ctx, void* cuda_stream) {
     ctx->own_stream = false;
     return ZANT_OK;
 }
+
+int32_t zant_b200_ctx_set_tf32(zant_ctx* ctx, int32_t enable) {
+    ZB_NEED_CTX(ctx);
+    ctx->tf32 = enable != 0;
+    return ZANT_OK;
+}
+
+int32_t zant_b200_ctx_get_tf32(zant_ctx* ctx) { return (ctx && ctx->tf32) ? 1 : 0; }
 
 int32_t zant_b200_ctx_set_arena_limit(zant_ctx* ctx, size_t max_bytes) {
     ZB_NEED_CTX(ctx);
@@ -257,6 +267,18 @@ int32_t zant_b200_conv_f32(zant_ctx* ctx, const float* x, const size_t* x_shape,
     if (bias && bias_len != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "bias holds %zu values for %d filters", bias_len, g.M);
     ZB_NEED_CTX(ctx);
     log_line("Running Conv [%d,%d,%d,%d] * [%d,%d,%d,%d]", g.N, g.C, g.H, g.W, g.M, g.Cg, g.KH, g.KW);
+    if (ctx->tf32 && !is_device_ptr(w) && !(bias && is_device_ptr(bias)) && g.M <= 2048 && (long long)g.N * g.OH * g.OW >= 128) {
+        // tensor-core path (2e-3 contract): weights blocked on the host, im2col gather + tcgen05 kind::tf32 GEMM
+        TfGemmPrep prep;
+        tf_gemm_prepare(w, g.M, g.C * g.KH * g.KW, (long long)g.C * g.KH * g.KW, 1, bias, prep, (long long)g.N * g.OH * g.OW);
+        Stager s(ctx);
+        const int ix = s.in(x, numel(x_shape, 4) * 4), iy = s.out(y, numel(y_shape, 4) * 4);
+        const int iw = s.in(prep.w_blk.data(), prep.w_blk.size() * 4), ib = s.in(prep.bias.data(), prep.bias.size() * 4);
+        const int ia = s.scratch(tf_gemm_a_bytes((size_t)g.N * g.OH * g.OW, prep));
+        ZB_TRY(s.commit());
+        ZB_TRY(run_conv_tf32(ctx, g, s.ptr<float>(ix), prep, s.ptr<float>(iw), s.ptr<float>(ib), s.ptr<float>(ia), FACT_NONE, 0.0f, s.ptr<float>(iy)));
+        return s.finish();
+    }
     Stager s(ctx);
     const int ix = s.in(x, numel(x_shape, 4) * 4), iw = s.in(w, numel(w_shape, 4) * 4);
     const int ib = s.in(bias, (size_t)g.M * 4), iy = s.out(y, numel(y_shape, 4) * 4);
@@ -273,6 +295,18 @@ int32_t zant_b200_mat_mul_f32(zant_ctx* ctx, const float* a, const size_t* a_sha
     ZB_TRY(matmul_check(a_shape, a_rank, b_shape, b_rank, y_shape, y_rank, g));
     ZB_NEED(a, "a"); ZB_NEED(b, "b"); ZB_NEED(y, "y");
     ZB_NEED_CTX(ctx);
+    if (ctx->tf32 && !is_device_ptr(b) && g.N <= 2048 && g.M >= 128 && g.K <= 0x7fffffffULL && g.M <= 0x7fffffffULL) {
+        TfGemmPrep prep;
+        tf_gemm_prepare(b, (int)g.N, (int)g.K, 1, (long long)g.N, nullptr, prep, (long long)g.M);
+        Stager s(ctx);
+        const int ia = s.in(a, g.M * g.K * 4), iy = s.out(y, g.M * g.N * 4);
+        const int iw = s.in(prep.w_blk.data(), prep.w_blk.size() * 4), ibz = s.in(prep.bias.data(), prep.bias.size() * 4);
+        const int ik = s.scratch(tf_gemm_a_bytes(g.M, prep));
+        ZB_TRY(s.commit());
+        ZB_TRY(run_matmul_tf32(ctx, s.ptr<float>(ia), (long long)g.M, (int)g.K, (long long)g.K, 1, prep, s.ptr<float>(iw), s.ptr<float>(ibz), s.ptr<float>(ik),
+                               FACT_NONE, 0.0f, s.ptr<float>(iy)));
+        return s.finish();
+    }
     Stager s(ctx);
     const int ia = s.in(a, g.M * g.K * 4), ib = s.in(b, g.K * g.N * 4), iy = s.out(y, g.M * g.N * 4);
     ZB_TRY(s.commit());

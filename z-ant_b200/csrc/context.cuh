@@ -19,6 +19,7 @@ struct zant_ctx {
     uint64_t launches = 0;
     int sm_count = 148;
     int* status_word = nullptr;   // device int: kernels with bounded waits report here
+    bool tf32 = false;            // float contractions on the tensor cores (kind::tf32, 2e-3 contract) instead of the exact FP32 kernels
 };
 
 namespace zb {

@@ -33,6 +33,7 @@ struct QDwArgs {
     int log2LW;                // lanes per plane = 1 << log2LW (covers OW / 4 columns of 4 outputs)
     uint32_t pad_word;
     float y_scale; int y_zp; int act; int out_u8;
+    const uint8_t* lut;       // optional table applied to the output codes (see Requant)
     int six;
 };
 
@@ -51,9 +52,10 @@ __device__ __forceinline__ uint32_t dw_requant4(const int acc[4], float m, const
         uint32_t pk = pack_sat_s8x4(rq_round(acc[0], m), rq_round(acc[1], m), rq_round(acc[2], m), rq_round(acc[3], m));
         if (p.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
         if (p.act == ZANT_QACT_RELU6) pk = __vmins4(pk, 0x01010101u * (uint32_t)(p.six & 255));
+        if (p.lut) pk = lut4(p.lut, pk);
         return pk;
     }
-    const Requant rq{p.y_scale, p.y_zp, p.act};
+    const Requant rq{p.y_scale, p.y_zp, p.act, p.lut};
     uint32_t pk = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -333,7 +335,7 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
     const int cols = (g.OW + 3) / 4;
     for (a.log2LW = 0; (1 << a.log2LW) < cols; ++a.log2LW) {}
     a.pad_word = 0x01010101u * (uint32_t)(x_zp & 255);
-    a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0;
+    a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0; a.lut = rq.lut;
     const bool lean = !y_u8 && rq.y_zp == 0 && mult_finite;
     if (lean) {
         float v = 6.0f / rq.y_scale;

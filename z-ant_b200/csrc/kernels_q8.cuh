@@ -22,7 +22,19 @@ template <bool U8> __device__ __forceinline__ int sat_q(int t) {
 
 struct Requant {
     float y_scale; int y_zp; int act;   // zant_qact
+    // Optional 256-entry table (device memory) applied to the finished output code, indexed by the unsigned
+    // view of the byte: an element-wise operator between two quantized tensors (LeakyRelu, a Relu or Clip that
+    // changes scale) folded into the producer.  Exact by construction: the producer computes the very code the
+    // separate operator would have read.
+    const uint8_t* lut = nullptr;
 };
+
+__device__ __forceinline__ int lut1(const uint8_t* lut, int code) { return (int)__ldg(lut + (code & 255)); }
+// four packed codes through the table
+__device__ __forceinline__ uint32_t lut4(const uint8_t* lut, uint32_t pk) {
+    return (uint32_t)__ldg(lut + (pk & 255u)) | ((uint32_t)__ldg(lut + ((pk >> 8) & 255u)) << 8) |
+           ((uint32_t)__ldg(lut + ((pk >> 16) & 255u)) << 16) | ((uint32_t)__ldg(lut + (pk >> 24)) << 24);
+}
 
 template <bool YU8>
 __device__ __forceinline__ int requant_one(int acc, float M, const Requant& r) {
@@ -32,6 +44,7 @@ __device__ __forceinline__ int requant_one(int acc, float M, const Requant& r) {
         t = max(t, sat_q<YU8>(r.y_zp));
         if (r.act == ZANT_QACT_RELU6) t = min(t, sat_q<YU8>(rne_clamped(__fdiv_rn(6.0f, r.y_scale)) + r.y_zp));
     }
+    if (r.lut) { t = lut1(r.lut, t); if (!YU8) t = (int)(int8_t)t; }
     return t;
 }
 

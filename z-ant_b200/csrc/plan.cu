@@ -24,6 +24,7 @@
 #include "dwconv_q8.cuh"
 #include "smallc_conv_q8.cuh"
 #include "tc_conv_nhwc.cuh"
+#include "tc_gemm_tf32.cuh"
 #include "status.hpp"
 
 using namespace zb;
@@ -79,6 +80,8 @@ struct zant_plan {
     int add_scratch(size_t bytes) { scratch_bytes.push_back(bytes); return (int)scratch_bytes.size() - 1; }
     // One buffer for the im2col matrices of all tensor-core steps: steps run one after another on
     // one stream, so they can share it; it is as large as the largest request.
+    // float activation that the fusion pass asks the next Conv step to apply, and the tensor that step writes instead of its own
+    int pending_fact = 0; float pending_slope = 0.0f; int pending_y = -1; bool pending_used = false;
     int im2col_scratch = -1;
     int shared_im2col_scratch(size_t bytes) {
         if (im2col_scratch < 0) im2col_scratch = add_scratch(bytes);
@@ -123,6 +126,15 @@ void build_unary_lut(int32_t dtype, float s_in, int zp_in, float s_out, int zp_o
         t = std::min(std::max(t, lo), hi);
         lut[code] = (uint8_t)t;
     }
+}
+
+// Table of a Relu / LeakyRelu / Clip node between two quantized tensors of type `dt`.
+void activation_lut(const PlanNode& n, int32_t dt, uint8_t lut[256]) {
+    const zant_node_attrs& a = n.a;
+    const float p0 = a.alpha, p1 = a.beta;
+    if (n.op == ZANT_OP_RELU) build_unary_lut(dt, a.x_scale, a.x_zp, a.y_scale, a.y_zp, [](float v) { return v > 0.0f ? v : 0.0f; }, lut);
+    else if (n.op == ZANT_OP_LEAKY_RELU) build_unary_lut(dt, a.x_scale, a.x_zp, a.y_scale, a.y_zp, [p0](float v) { volatile float s = p0 * v; return v <= 0.0f ? (float)s : v; }, lut);
+    else build_unary_lut(dt, a.x_scale, a.x_zp, a.y_scale, a.y_zp, [p0, p1](float v) { return std::fmin(std::fmax(v, p0), p1); }, lut);
 }
 
 }  // namespace
@@ -195,6 +207,9 @@ int32_t zant_b200_plan_node(zant_plan* plan, int32_t op, const int32_t* inputs, 
 static int32_t build_node(zant_plan* pl, size_t node_index, int32_t fuse);
 static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t fuse);
 static int32_t try_fuse(zant_plan* pl, size_t node_index, size_t& consumed);
+static int32_t try_fuse_small_cnn(zant_plan* pl, size_t node_index, size_t& consumed);
+static int32_t try_fuse_qconv_group(zant_plan* pl, size_t node_index, size_t& consumed);
+static int32_t try_fuse_fconv_group(zant_plan* pl, size_t node_index, size_t& consumed);
 
 // Multiply-accumulates of one node (contractions only; everything else counts as 0).
 static double node_macs(const zant_plan* pl, const PlanNode& n) {
@@ -461,6 +476,155 @@ int32_t zant_b200_plan_read_tensor(zant_plan* plan, int32_t id, void* host_dst) 
 }  // extern "C"
 
 // --------------------------------------------------------------------------------------------
+// QLinearConv, alone or as the head of a fused group.  `fz` carries what the fusion pass found behind the node:
+// an activation override (a Relu that keeps scale and zero point), a 256-entry table (LeakyRelu, Clip, a Relu
+// that changes scale) applied to the finished codes, the tensor the step writes instead of the node's own
+// output, and a 2x2 / stride-2 MaxPool that the implicit-GEMM kernel can apply in its epilogue.
+// --------------------------------------------------------------------------------------------
+struct QConvFusion {
+    int activation = -1;     // >= 0: replaces the node's own activation attribute
+    int lut_aux = -1;        // aux id of the table, -1 = none
+    int y_act = -1;          // tensor written when the pool is not fused (-1: the node's output)
+    int y_pool = -1;         // pooled tensor; >= 0 asks for the fused pool
+    bool pool_done = false;  // out: the step writes y_pool
+};
+
+static int32_t build_qconv(zant_plan* pl, const PlanNode& n, QConvFusion& fz) {
+    const zant_node_attrs& a = n.a;
+    zant_ctx* ctx = pl->ctx;
+    auto T = [&](int id) -> const PlanTensor& { return pl->t[id]; };
+    ZB_TRY(need_inputs(n, 3, 5, "QLinearConv"));
+    const int x = n.in[0], w = n.in[1], ws = n.in[2], wz = opt_in(n, 3), b = opt_in(n, 4), y0 = n.out[0];
+    if (x < 0 || w < 0 || ws < 0) return fail(ZANT_E_INVALID_INPUT, "QLinearConv needs x, w, w_scale");
+    ZB_TRY(want_dtype(pl, w, ZANT_I8, "QLinearConv w")); ZB_TRY(want_dtype(pl, ws, ZANT_F32, "QLinearConv w_scale"));
+    ZB_TRY(want_dtype(pl, wz, ZANT_I32, "QLinearConv w_zp")); ZB_TRY(want_dtype(pl, b, ZANT_I32, "QLinearConv bias"));
+    const int32_t xd = T(x).dtype, yd = T(y0).dtype;
+    if ((xd != ZANT_I8 && xd != ZANT_U8) || (yd != ZANT_I8 && yd != ZANT_U8)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearConv x/y dtype");
+    ZB_TRY(check_zero_point(xd, a.x_zp, "QLinearConv x"));
+    if (!T(w).is_const || !T(ws).is_const || (wz >= 0 && !T(wz).is_const)) return fail(ZANT_E_UNSUPPORTED, "QLinearConv weights and scales must be initializers");
+    ConvGeom g;
+    if (a.channels_last) {
+        // the geometry is that of the NCHW operator on the permuted shapes
+        if (T(x).shape.size() != 4 || T(y0).shape.size() != 4) return fail(ZANT_E_INVALID_DIMENSIONS, "channels-last QLinearConv takes rank-4 tensors");
+        const size_t xs[4] = {T(x).shape[0], T(x).shape[3], T(x).shape[1], T(x).shape[2]}, ys[4] = {T(y0).shape[0], T(y0).shape[3], T(y0).shape[1], T(y0).shape[2]};
+        ZB_TRY(conv_resolve_onnx(xs, 4, T(w).shape.data(), T(w).shape.size(), ys, 4,
+                                 a.strides, a.n_strides, a.pads, a.n_pads, a.dilations, a.n_dilations, a.group, a.auto_pad < 0 ? 0 : a.auto_pad, g));
+    } else {
+        ZB_TRY(conv_resolve_onnx(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(), T(y0).shape.data(), T(y0).shape.size(),
+                                 a.strides, a.n_strides, a.pads, a.n_pads, a.dilations, a.n_dilations, a.group, a.auto_pad < 0 ? 0 : a.auto_pad, g));
+    }
+    const size_t nws = numel(T(ws).shape.data(), T(ws).shape.size());
+    if (nws != 1 && nws != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv w_scale size");
+    if (b >= 0 && numel(T(b).shape.data(), T(b).shape.size()) != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv bias size");
+    std::vector<float> mult;
+    requant_multipliers(a.x_scale, (const float*)T(ws).host.data(), nws, a.y_scale, (size_t)g.M, mult);
+    std::vector<int32_t> wzv((size_t)g.M, 0);
+    if (wz >= 0) {
+        const size_t nwz = numel(T(wz).shape.data(), T(wz).shape.size());
+        if (nwz != 1 && nwz != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv w_zp size");
+        for (int m = 0; m < g.M; ++m) wzv[m] = ((const int32_t*)T(wz).host.data())[nwz == 1 ? 0 : m];
+    }
+    const int xzp = a.x_zp;
+    const Requant rq0{a.y_scale, a.y_zp, fz.activation >= 0 ? fz.activation : a.activation};
+    const int lut_aux = fz.lut_aux;
+    // the requantisation parameters with the table's device address, resolved at launch time (the arena exists by then)
+    auto rq_of = [pl, rq0, lut_aux]() { Requant r = rq0; r.lut = lut_aux >= 0 ? (const uint8_t*)pl->aux(lut_aux) : nullptr; return r; };
+    bool wz_zero = true;
+    for (int32_t v : wzv) wz_zero = wz_zero && v == 0;
+    const bool const_bias = b < 0 || T(b).is_const;
+    const int y = fz.y_act >= 0 ? fz.y_act : y0;          // written unless the pool is fused too
+    const std::string tail = std::string(fz.activation >= 0 ? "+Relu" : "") + (lut_aux >= 0 ? "+ActivationLut" : "");
+    auto push = [&](const std::string& name, std::function<int32_t()> fn) { pl->steps.push_back(std::move(fn)); pl->step_names.push_back(name); };
+    fz.pool_done = false;
+
+    if (a.channels_last) {
+        TcConvPlan ncp;
+        if (!const_bias || !tc_conv_nhwc_plan(g, wz_zero, xzp, ncp)) return fail(ZANT_E_UNSUPPORTED, "shape not taken by the channels-last QLinearConv kernel");
+        std::vector<int8_t> w_blk; std::vector<float> mp; std::vector<int32_t> bp;
+        tc_conv_nhwc_prepare(ncp, (const int8_t*)T(w).host.data(), mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, w_blk, mp, bp);
+        const int aw = pl->add_aux(w_blk.data(), w_blk.size()), am = pl->add_aux(mp.data(), mp.size() * 4), ab = pl->add_aux(bp.data(), bp.size() * 4);
+        const double max_product = tc_conv_max_product(mp, bp, (long long)g.Cg * g.KH * g.KW);
+        push("QLinearConv(tc-nhwc)" + tail, [=]() {
+            if (!tc_conv_ptr_ok(pl->ptr(x)) || !tc_conv_ptr_ok(pl->ptr(y))) return fail(ZANT_E_INVALID_INPUT, "channels-last QLinearConv buffers must be 16-byte aligned");
+            return tc_conv_nhwc_run(ctx, ncp, pl->ptr(x), xd == ZANT_U8, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
+                                    (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), max_product);
+        });
+        return ZANT_OK;
+    }
+    if (const_bias && qconv_smallc_eligible(g, wz_zero)) {
+        // 3x3 on at most four input channels (network stems); arena tensors are 256-byte aligned
+        std::vector<uint32_t> wfrag; std::vector<int32_t> bf;
+        qconv_smallc_prepare(g, (const int8_t*)T(w).host.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, wfrag, bf);
+        const int aw = pl->add_aux(wfrag.data(), wfrag.size() * 4), am = pl->add_aux(mult.data(), mult.size() * 4), ab = pl->add_aux(bf.data(), bf.size() * 4);
+        const double max_product = tc_conv_max_product(mult, bf, (long long)g.C * 9);
+        push("QLinearConv(small-c)" + tail, [=]() {
+            if (!qconv_smallc_ptr_ok(pl->ptr(x))) return fail(ZANT_E_INVALID_INPUT, "QLinearConv input buffer must be 4-byte aligned");
+            return run_qconv_smallc(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, (const uint32_t*)pl->aux(aw), (const float*)pl->aux(am),
+                                    (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), max_product);
+        });
+        return ZANT_OK;
+    }
+    TcConvPlan tcp;
+    if (const_bias && (long long)g.N * g.OH * g.OW >= 256) {
+        // implicit GEMM from NCHW (stride 1): weights blocked once here, one launch per run; with a fused pool the
+        // epilogue writes the pooled tensor only.  Arena tensors are 256-byte aligned; a caller-bound input that is
+        // not 16-byte aligned is refused at run time.
+        const bool pooled = fz.y_pool >= 0 && tc_conv_plan(g, wz_zero, tcp, true);
+        if (pooled || tc_conv_plan(g, wz_zero, tcp, false)) {
+            std::vector<int8_t> w_blk; std::vector<float> mp; std::vector<int32_t> bp;
+            tc_conv_prepare(tcp, (const int8_t*)T(w).host.data(), mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, w_blk, mp, bp);
+            const int aw = pl->add_aux(w_blk.data(), w_blk.size()), am = pl->add_aux(mp.data(), mp.size() * 4), ab = pl->add_aux(bp.data(), bp.size() * 4);
+            const double max_product = tc_conv_max_product(mp, bp, (long long)g.Cg * g.KH * g.KW);
+            const int yw = pooled ? fz.y_pool : y;
+            fz.pool_done = pooled;
+            push("QLinearConv(tc-implicit)" + tail + (pooled ? "+MaxPool" : ""), [=]() {
+                if (!tc_conv_ptr_ok(pl->ptr(x))) return fail(ZANT_E_INVALID_INPUT, "QLinearConv input buffer must be 16-byte aligned");
+                return tc_conv_run(ctx, tcp, pl->ptr(x), xd == ZANT_U8, xzp, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
+                                   (const int32_t*)pl->aux(ab), pl->ptr(yw), yd == ZANT_U8, rq_of(), max_product);
+            });
+            return ZANT_OK;
+        }
+    }
+    if (const_bias && qdwconv_eligible(g, wz_zero)) {
+        // depthwise 3x3: one HBM-bound pass; arena tensors are 256-byte aligned
+        std::vector<uint32_t> wrow; std::vector<int32_t> bf;
+        qdwconv_prepare(g, (const int8_t*)T(w).host.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, wrow, bf);
+        bool finite = true;
+        for (float f : mult) finite = finite && std::isfinite(f);
+        const int aw = pl->add_aux(wrow.data(), wrow.size() * 4), am = pl->add_aux(mult.data(), mult.size() * 4), ab = pl->add_aux(bf.data(), bf.size() * 4);
+        push("QLinearConv(depthwise)" + tail, [=]() {
+            if (!qdwconv_ptr_ok(pl->ptr(x)) || !qdwconv_ptr_ok(pl->ptr(y))) return fail(ZANT_E_INVALID_INPUT, "depthwise QLinearConv buffers must be 4-byte aligned");
+            return run_qdwconv(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, (const uint32_t*)pl->aux(aw), (const float*)pl->aux(am),
+                               (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), finite);
+        });
+        return ZANT_OK;
+    }
+    if (qconv_tc_eligible(g, wz_zero) && const_bias) {
+        // tensor-core path: weights re-blocked once here, im2col + tcgen05 GEMM per run
+        auto prep = std::make_shared<QGemmPrep>();
+        qconv_gemm_prepare(g, (const int8_t*)T(w).host.data(), mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, *prep);
+        const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size()), am = pl->add_aux(prep->mult.data(), prep->mult.size() * 4);
+        const int ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
+        const int sa = pl->shared_im2col_scratch(qgemm_a_bytes((size_t)g.N * g.OH * g.OW, *prep));
+        prep->w_blk.clear(); prep->w_blk.shrink_to_fit();
+        push("QLinearConv(tc)" + tail, [=]() {
+            return run_qconv_tc(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, *prep, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
+                                (const int32_t*)pl->aux(ab), (uint8_t*)pl->scratch(sa), pl->ptr(y), yd == ZANT_U8, rq_of());
+        });
+        return ZANT_OK;
+    }
+    const int am = pl->add_aux(mult.data(), mult.size() * 4), az = pl->add_aux(wzv.data(), wzv.size() * 4);
+    push("QLinearConv" + tail, [=]() {
+        QConvArgs q{};
+        q.x = pl->ptr(x); q.w = pl->p<int8_t>(w); q.y = pl->ptr(y);
+        q.mult = (const float*)pl->aux(am); q.w_zp = (const int32_t*)pl->aux(az); q.bias = pl->p<int32_t>(b);
+        q.x_zp = xzp; q.rq = rq_of(); q.g = g;
+        return run_qconv_generic(ctx, q, xd, yd);
+    });
+    return ZANT_OK;
+}
+
+// --------------------------------------------------------------------------------------------
 // One node -> one (or a few) kernel launches, using the same resolvers as the single-op ABI.
 // --------------------------------------------------------------------------------------------
 static int32_t build_node(zant_plan* pl, size_t node_index, int32_t fuse) {
@@ -489,6 +653,23 @@ static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t /*fuse*
                                     a.n_pads ? a.pads : nullptr, a.n_pads, a.n_dilations ? a.dilations : nullptr, a.n_dilations,
                                     a.group, ap, ap ? std::strlen(ap) : 0, g));
             if (b >= 0 && numel(T(b).shape.data(), T(b).shape.size()) != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "Conv bias size");
+            if (ctx->tf32 && T(w).is_const && (b < 0 || T(b).is_const) && g.M <= 2048 && (long long)g.N * g.OH * g.OW >= 128) {
+                // tensor-core float path: weights blocked once here; im2col gather + tcgen05 kind::tf32 GEMM per run, with the
+                // activation the fusion pass found behind the node in the epilogue
+                auto prep = std::make_shared<TfGemmPrep>();
+                const int K = g.C * g.KH * g.KW;
+                tf_gemm_prepare((const float*)T(w).host.data(), g.M, K, K, 1, b >= 0 ? (const float*)T(b).host.data() : nullptr, *prep, (long long)g.N * g.OH * g.OW);
+                const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size() * 4), ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
+                const int sa = pl->shared_im2col_scratch(tf_gemm_a_bytes((size_t)g.N * g.OH * g.OW, *prep));
+                prep->w_blk.clear(); prep->w_blk.shrink_to_fit();
+                const int fact = pl->pending_fact; const float fslope = pl->pending_slope;
+                const int yw = pl->pending_y >= 0 ? pl->pending_y : y;
+                push(fact == FACT_NONE ? "Conv(tf32)" : (fact == FACT_RELU ? "Conv(tf32)+Relu" : "Conv(tf32)+LeakyRelu"), [=]() {
+                    return run_conv_tf32(ctx, g, pl->p<float>(x), *prep, (const float*)pl->aux(aw), (const float*)pl->aux(ab), (float*)pl->scratch(sa), fact, fslope, pl->p<float>(yw));
+                });
+                pl->pending_used = true;
+                return ZANT_OK;
+            }
             push("Conv", [=]() { return run_conv_f32(ctx, g, pl->p<float>(x), pl->p<float>(w), pl->p<float>(b), pl->p<float>(y)); });
             return ZANT_OK;
         }
@@ -497,6 +678,19 @@ static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t /*fuse*
             const int x = n.in[0], w = n.in[1], y = n.out[0];
             MatGeom g;
             ZB_TRY(matmul_check(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(), T(y).shape.data(), T(y).shape.size(), g));
+            if (ctx->tf32 && T(w).is_const && T(w).dtype == ZANT_F32 && g.N <= 2048 && g.M >= 128 && g.K <= 0x7fffffffULL && g.M <= 0x7fffffffULL) {
+                auto prep = std::make_shared<TfGemmPrep>();
+                tf_gemm_prepare((const float*)T(w).host.data(), (int)g.N, (int)g.K, 1, (long long)g.N, nullptr, *prep, (long long)g.M);
+                const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size() * 4), ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
+                const int sa = pl->shared_im2col_scratch(tf_gemm_a_bytes(g.M, *prep));
+                prep->w_blk.clear(); prep->w_blk.shrink_to_fit();
+                const MatGeom gg = g;
+                push("MatMul(tf32)", [=]() {
+                    return run_matmul_tf32(ctx, pl->p<float>(x), (long long)gg.M, (int)gg.K, (long long)gg.K, 1, *prep, (const float*)pl->aux(aw), (const float*)pl->aux(ab),
+                                           (float*)pl->scratch(sa), FACT_NONE, 0.0f, pl->p<float>(y));
+                });
+                return ZANT_OK;
+            }
             push("MatMul", [=]() { return run_matmul_f32(ctx, g, pl->p<float>(x), pl->p<float>(w), pl->p<float>(y)); });
             return ZANT_OK;
         }
@@ -508,6 +702,24 @@ static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t /*fuse*
                               c >= 0 ? T(c).shape.data() : nullptr, c >= 0 ? T(c).shape.size() : 0, c >= 0,
                               a.trans_a != 0, a.trans_b != 0, a.beta, T(y).shape.data(), T(y).shape.size(), g));
             const float alpha = a.alpha, beta = a.beta; const bool ta = a.trans_a != 0, tb = a.trans_b != 0;
+            {
+                // tensor-core float path for the fully-connected form: Y = A B' + row vector C (alpha = beta = 1)
+                const bool c_row = c < 0 || (T(c).is_const && beta == 1.0f && g.c_mode != 0 && g.c_rows == 1 && g.c_cols == g.cols && numel(T(c).shape.data(), T(c).shape.size()) == g.cols);
+                if (ctx->tf32 && !ta && alpha == 1.0f && T(w).is_const && c_row && g.batch == 1 && g.cols <= 2048 && g.rows >= 128 && g.K <= 0x7fffffffULL && g.rows <= 0x7fffffffULL) {
+                    auto prep = std::make_shared<TfGemmPrep>();
+                    tf_gemm_prepare((const float*)T(w).host.data(), (int)g.cols, (int)g.K, tb ? (long long)g.K : 1, tb ? 1 : (long long)g.cols,
+                                    c >= 0 ? (const float*)T(c).host.data() : nullptr, *prep, (long long)g.rows);
+                    const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size() * 4), ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
+                    const int sa = pl->shared_im2col_scratch(tf_gemm_a_bytes(g.rows, *prep));
+                    prep->w_blk.clear(); prep->w_blk.shrink_to_fit();
+                    const GemmGeom gg = g;
+                    push("Gemm(tf32)", [=]() {
+                        return run_matmul_tf32(ctx, pl->p<float>(x), (long long)gg.rows, (int)gg.K, (long long)gg.K, 1, *prep, (const float*)pl->aux(aw), (const float*)pl->aux(ab),
+                                               (float*)pl->scratch(sa), FACT_NONE, 0.0f, pl->p<float>(y));
+                    });
+                    return ZANT_OK;
+                }
+            }
             push("Gemm", [=]() { return run_gemm_f32(ctx, g, pl->p<float>(x), pl->p<float>(w), pl->p<float>(c), alpha, beta, ta, tb, pl->p<float>(y)); });
             return ZANT_OK;
         }
@@ -623,9 +835,7 @@ static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t /*fuse*
             if (dt == ZANT_I32) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "activation on int32");
             // Quantized tensors: dequantise, activate, requantise through a 256-entry table.
             uint8_t lut[256];
-            if (n.op == ZANT_OP_RELU) build_unary_lut(dt, a.x_scale, a.x_zp, a.y_scale, a.y_zp, [](float v) { return v > 0.0f ? v : 0.0f; }, lut);
-            else if (n.op == ZANT_OP_LEAKY_RELU) build_unary_lut(dt, a.x_scale, a.x_zp, a.y_scale, a.y_zp, [p0](float v) { volatile float s = p0 * v; return v <= 0.0f ? (float)s : v; }, lut);
-            else build_unary_lut(dt, a.x_scale, a.x_zp, a.y_scale, a.y_zp, [p0, p1](float v) { return std::fmin(std::fmax(v, p0), p1); }, lut);
+            activation_lut(n, dt, lut);
             const int aux = pl->add_aux(lut, 256);
             push("ActivationLut", [=]() { return run_lut(ctx, pl->p<char>(x), pl->p<char>(y), cnt, (const uint8_t*)pl->aux(aux)); });
             return ZANT_OK;
@@ -722,119 +932,8 @@ static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t /*fuse*
             return ZANT_OK;
         }
         case ZANT_OP_QLINEAR_CONV: {
-            ZB_TRY(need_inputs(n, 3, 5, "QLinearConv"));
-            const int x = n.in[0], w = n.in[1], ws = n.in[2], wz = opt_in(n, 3), b = opt_in(n, 4), y = n.out[0];
-            if (x < 0 || w < 0 || ws < 0) return fail(ZANT_E_INVALID_INPUT, "QLinearConv needs x, w, w_scale");
-            ZB_TRY(want_dtype(pl, w, ZANT_I8, "QLinearConv w")); ZB_TRY(want_dtype(pl, ws, ZANT_F32, "QLinearConv w_scale"));
-            ZB_TRY(want_dtype(pl, wz, ZANT_I32, "QLinearConv w_zp")); ZB_TRY(want_dtype(pl, b, ZANT_I32, "QLinearConv bias"));
-            const int32_t xd = T(x).dtype, yd = T(y).dtype;
-            if ((xd != ZANT_I8 && xd != ZANT_U8) || (yd != ZANT_I8 && yd != ZANT_U8)) return fail(ZANT_E_INPUT_ARRAY_WRONG_TYPE, "QLinearConv x/y dtype");
-            ZB_TRY(check_zero_point(xd, a.x_zp, "QLinearConv x"));
-            if (!T(w).is_const || !T(ws).is_const || (wz >= 0 && !T(wz).is_const)) return fail(ZANT_E_UNSUPPORTED, "QLinearConv weights and scales must be initializers");
-            ConvGeom g;
-            if (a.channels_last) {
-                // the geometry is that of the NCHW operator on the permuted shapes
-                if (T(x).shape.size() != 4 || T(y).shape.size() != 4) return fail(ZANT_E_INVALID_DIMENSIONS, "channels-last QLinearConv takes rank-4 tensors");
-                const size_t xs[4] = {T(x).shape[0], T(x).shape[3], T(x).shape[1], T(x).shape[2]}, ys[4] = {T(y).shape[0], T(y).shape[3], T(y).shape[1], T(y).shape[2]};
-                ZB_TRY(conv_resolve_onnx(xs, 4, T(w).shape.data(), T(w).shape.size(), ys, 4,
-                                         a.strides, a.n_strides, a.pads, a.n_pads, a.dilations, a.n_dilations, a.group, a.auto_pad < 0 ? 0 : a.auto_pad, g));
-            } else {
-                ZB_TRY(conv_resolve_onnx(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(), T(y).shape.data(), T(y).shape.size(),
-                                         a.strides, a.n_strides, a.pads, a.n_pads, a.dilations, a.n_dilations, a.group, a.auto_pad < 0 ? 0 : a.auto_pad, g));
-            }
-            const size_t nws = numel(T(ws).shape.data(), T(ws).shape.size());
-            if (nws != 1 && nws != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv w_scale size");
-            if (b >= 0 && numel(T(b).shape.data(), T(b).shape.size()) != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv bias size");
-            std::vector<float> mult;
-            requant_multipliers(a.x_scale, (const float*)T(ws).host.data(), nws, a.y_scale, (size_t)g.M, mult);
-            std::vector<int32_t> wzv((size_t)g.M, 0);
-            if (wz >= 0) {
-                const size_t nwz = numel(T(wz).shape.data(), T(wz).shape.size());
-                if (nwz != 1 && nwz != (size_t)g.M) return fail(ZANT_E_INPUT_TENSORS_WRONG_SHAPE, "QLinearConv w_zp size");
-                for (int m = 0; m < g.M; ++m) wzv[m] = ((const int32_t*)T(wz).host.data())[nwz == 1 ? 0 : m];
-            }
-            const int xzp = a.x_zp; const Requant rq{a.y_scale, a.y_zp, a.activation};
-            bool wz_zero = true;
-            for (int32_t v : wzv) wz_zero = wz_zero && v == 0;
-            if (a.channels_last) {
-                TcConvPlan ncp;
-                if (!(b < 0 || T(b).is_const) || !tc_conv_nhwc_plan(g, wz_zero, xzp, ncp)) return fail(ZANT_E_UNSUPPORTED, "shape not taken by the channels-last QLinearConv kernel");
-                std::vector<int8_t> w_blk; std::vector<float> mp; std::vector<int32_t> bp;
-                tc_conv_nhwc_prepare(ncp, (const int8_t*)T(w).host.data(), mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, w_blk, mp, bp);
-                const int aw = pl->add_aux(w_blk.data(), w_blk.size()), am = pl->add_aux(mp.data(), mp.size() * 4), ab = pl->add_aux(bp.data(), bp.size() * 4);
-                const double max_product = tc_conv_max_product(mp, bp, (long long)g.Cg * g.KH * g.KW);
-                push("QLinearConv(tc-nhwc)", [=]() {
-                    if (!tc_conv_ptr_ok(pl->ptr(x)) || !tc_conv_ptr_ok(pl->ptr(y))) return fail(ZANT_E_INVALID_INPUT, "channels-last QLinearConv buffers must be 16-byte aligned");
-                    return tc_conv_nhwc_run(ctx, ncp, pl->ptr(x), xd == ZANT_U8, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
-                                            (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq, max_product);
-                });
-                return ZANT_OK;
-            }
-            if ((b < 0 || T(b).is_const) && qconv_smallc_eligible(g, wz_zero)) {
-                // 3x3 on at most four input channels (network stems); arena tensors are 256-byte aligned
-                std::vector<uint32_t> wfrag; std::vector<int32_t> bf;
-                qconv_smallc_prepare(g, (const int8_t*)T(w).host.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, wfrag, bf);
-                const int aw = pl->add_aux(wfrag.data(), wfrag.size() * 4), am = pl->add_aux(mult.data(), mult.size() * 4), ab = pl->add_aux(bf.data(), bf.size() * 4);
-                const double max_product = tc_conv_max_product(mult, bf, (long long)g.C * 9);
-                push("QLinearConv(small-c)", [=]() {
-                    if (!qconv_smallc_ptr_ok(pl->ptr(x))) return fail(ZANT_E_INVALID_INPUT, "QLinearConv input buffer must be 4-byte aligned");
-                    return run_qconv_smallc(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, (const uint32_t*)pl->aux(aw), (const float*)pl->aux(am),
-                                            (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq, max_product);
-                });
-                return ZANT_OK;
-            }
-            TcConvPlan tcp;
-            if ((b < 0 || T(b).is_const) && (long long)g.N * g.OH * g.OW >= 256 && tc_conv_plan(g, wz_zero, tcp)) {
-                // implicit GEMM from NCHW (stride 1): weights blocked once here, one launch per run.
-                // Arena tensors are 256-byte aligned; a caller-bound input that is not 16-byte aligned is refused at run time.
-                std::vector<int8_t> w_blk; std::vector<float> mp; std::vector<int32_t> bp;
-                tc_conv_prepare(tcp, (const int8_t*)T(w).host.data(), mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, w_blk, mp, bp);
-                const int aw = pl->add_aux(w_blk.data(), w_blk.size()), am = pl->add_aux(mp.data(), mp.size() * 4), ab = pl->add_aux(bp.data(), bp.size() * 4);
-                const double max_product = tc_conv_max_product(mp, bp, (long long)g.Cg * g.KH * g.KW);
-                push("QLinearConv(tc-implicit)", [=]() {
-                    if (!tc_conv_ptr_ok(pl->ptr(x))) return fail(ZANT_E_INVALID_INPUT, "QLinearConv input buffer must be 16-byte aligned");
-                    return tc_conv_run(ctx, tcp, pl->ptr(x), xd == ZANT_U8, xzp, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
-                                       (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq, max_product);
-                });
-                return ZANT_OK;
-            }
-            if ((b < 0 || T(b).is_const) && qdwconv_eligible(g, wz_zero)) {
-                // depthwise 3x3: one HBM-bound pass; arena tensors are 256-byte aligned
-                std::vector<uint32_t> wrow; std::vector<int32_t> bf;
-                qdwconv_prepare(g, (const int8_t*)T(w).host.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, wrow, bf);
-                bool finite = true;
-                for (float f : mult) finite = finite && std::isfinite(f);
-                const int aw = pl->add_aux(wrow.data(), wrow.size() * 4), am = pl->add_aux(mult.data(), mult.size() * 4), ab = pl->add_aux(bf.data(), bf.size() * 4);
-                push("QLinearConv(depthwise)", [=]() {
-                    if (!qdwconv_ptr_ok(pl->ptr(x)) || !qdwconv_ptr_ok(pl->ptr(y))) return fail(ZANT_E_INVALID_INPUT, "depthwise QLinearConv buffers must be 4-byte aligned");
-                    return run_qdwconv(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, (const uint32_t*)pl->aux(aw), (const float*)pl->aux(am),
-                                       (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq, finite);
-                });
-                return ZANT_OK;
-            }
-            if (qconv_tc_eligible(g, wz_zero) && (b < 0 || T(b).is_const)) {
-                // tensor-core path: weights re-blocked once here, im2col + tcgen05 GEMM per run
-                auto prep = std::make_shared<QGemmPrep>();
-                qconv_gemm_prepare(g, (const int8_t*)T(w).host.data(), mult.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, *prep);
-                const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size()), am = pl->add_aux(prep->mult.data(), prep->mult.size() * 4);
-                const int ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
-                const int sa = pl->shared_im2col_scratch(qgemm_a_bytes((size_t)g.N * g.OH * g.OW, *prep));
-                prep->w_blk.clear(); prep->w_blk.shrink_to_fit();
-                push("QLinearConv(tc)", [=]() {
-                    return run_qconv_tc(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, *prep, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
-                                        (const int32_t*)pl->aux(ab), (uint8_t*)pl->scratch(sa), pl->ptr(y), yd == ZANT_U8, rq);
-                });
-                return ZANT_OK;
-            }
-            const int am = pl->add_aux(mult.data(), mult.size() * 4), az = pl->add_aux(wzv.data(), wzv.size() * 4);
-            push("QLinearConv", [=]() {
-                QConvArgs q{};
-                q.x = pl->ptr(x); q.w = pl->p<int8_t>(w); q.y = pl->ptr(y);
-                q.mult = (const float*)pl->aux(am); q.w_zp = (const int32_t*)pl->aux(az); q.bias = pl->p<int32_t>(b);
-                q.x_zp = xzp; q.rq = rq; q.g = g;
-                return run_qconv_generic(ctx, q, xd, yd);
-            });
-            return ZANT_OK;
+            QConvFusion none;
+            return build_qconv(pl, n, none);
         }
         case ZANT_OP_QLINEAR_MATMUL: {
             ZB_TRY(need_inputs(n, 3, 5, "QLinearMatMul"));
@@ -994,6 +1093,115 @@ bool positive_finite(const std::vector<float>& m) {
 }  // namespace
 
 static int32_t try_fuse(zant_plan* pl, size_t i0, size_t& consumed) {
+    consumed = 0;
+    ZB_TRY(try_fuse_small_cnn(pl, i0, consumed));
+    if (consumed) return ZANT_OK;
+    ZB_TRY(try_fuse_qconv_group(pl, i0, consumed));
+    if (consumed) return ZANT_OK;
+    return try_fuse_fconv_group(pl, i0, consumed);
+}
+
+// Float Conv -> Relu | LeakyRelu on the tensor-core path (context in TF32 mode): the activation runs in the GEMM's
+// epilogue.  The exact FP32 path is left node by node: it mirrors the reference's call sequence.
+static int32_t try_fuse_fconv_group(zant_plan* pl, size_t i0, size_t& consumed) {
+    consumed = 0;
+    if (!pl->ctx->tf32 || i0 + 1 >= pl->nodes.size()) return ZANT_OK;
+    const PlanNode& conv = pl->nodes[i0];
+    const PlanNode& act = pl->nodes[i0 + 1];
+    if (conv.op != ZANT_OP_CONV || conv.out.size() != 1) return ZANT_OK;
+    if ((act.op != ZANT_OP_RELU && act.op != ZANT_OP_LEAKY_RELU) || act.in.size() != 1 || act.out.size() != 1 || act.in[0] != conv.out[0]) return ZANT_OK;
+    if (pl->t[act.out[0]].dtype != ZANT_F32 || pl->t[act.out[0]].bytes != pl->t[conv.out[0]].bytes) return ZANT_OK;
+    ChainCtx c{pl, std::vector<int>(pl->t.size(), 0)};
+    for (const PlanNode& n : pl->nodes) for (int id : n.in) if (id >= 0) c.consumers[id]++;
+    if (!only_feeds_next(c, conv.out[0])) return ZANT_OK;
+    pl->pending_fact = act.op == ZANT_OP_RELU ? FACT_RELU : FACT_LEAKY;
+    pl->pending_slope = act.a.alpha;
+    pl->pending_y = act.out[0];
+    pl->pending_used = false;
+    const size_t first_step = pl->steps.size();
+    const int32_t st = build_node_impl(pl, i0, 1);
+    const bool used = pl->pending_used;
+    pl->pending_fact = FACT_NONE; pl->pending_slope = 0.0f; pl->pending_y = -1; pl->pending_used = false;
+    if (st != ZANT_OK) return st;
+    if (used) { pl->t[conv.out[0]].elided = true; consumed = 2; }
+    else consumed = 1;
+    record_step_cost(pl, first_step, i0, consumed);
+    return ZANT_OK;
+}
+
+// --------------------------------------------------------------------------------------------
+// Generic epilogue fusion: QLinearConv -> [Relu | LeakyRelu | Clip] -> [MaxPool 2x2 / stride 2].
+// The generator emits one call per node (src/codeGen/predict.zig:73-92, src/codeGen/math_handler.zig:45-105), so
+// between a convolution and the pool behind it two full-size int8 tensors are written and read back.  Here the
+// activation becomes part of the producer's epilogue (an activation flag when it keeps scale and zero point, else
+// a 256-entry table applied to the finished code), and the pool is applied in the epilogue of the implicit-GEMM
+// kernel where its tiling allows; the tensors in between are never materialised.  Every step is the composition of
+// the exact per-node functions on the same integer codes, so results stay bit-identical to the node-by-node plan.
+// Conditions: each interior tensor has exactly one consumer and is not the graph output; the pool has a 2x2
+// window, stride 2, no padding, no dilation (MaxPool rule: src/Core/Tensor/TensorMath/op_pooling.zig:570-659).
+// --------------------------------------------------------------------------------------------
+static int32_t try_fuse_qconv_group(zant_plan* pl, size_t i0, size_t& consumed) {
+    consumed = 0;
+    const PlanNode& conv = pl->nodes[i0];
+    if (conv.op != ZANT_OP_QLINEAR_CONV || conv.out.size() != 1 || conv.in.size() < 3) return ZANT_OK;
+    ChainCtx c{pl, std::vector<int>(pl->t.size(), 0)};
+    for (const PlanNode& n : pl->nodes) for (int id : n.in) if (id >= 0) c.consumers[id]++;
+    auto T = [&](int id) -> const PlanTensor& { return pl->t[id]; };
+    auto q8 = [&](int id) { return T(id).dtype == ZANT_I8 || T(id).dtype == ZANT_U8; };
+    QConvFusion fz;
+    size_t j = i0 + 1;
+    int cur = conv.out[0];
+    if (!q8(cur)) return ZANT_OK;
+    std::vector<int> interior;
+    // activation behind the convolution
+    if (j < pl->nodes.size() && only_feeds_next(c, cur)) {
+        const PlanNode& act = pl->nodes[j];
+        const bool is_act = act.op == ZANT_OP_RELU || act.op == ZANT_OP_LEAKY_RELU || act.op == ZANT_OP_CLIP;
+        if (is_act && act.in.size() == 1 && act.out.size() == 1 && act.in[0] == cur && T(act.out[0]).dtype == T(cur).dtype &&
+            T(act.out[0]).bytes == T(cur).bytes && act.a.x_scale == conv.a.y_scale && act.a.x_zp == conv.a.y_zp) {
+            if (identity_scale_relu(act)) {
+                fz.activation = conv.a.activation == ZANT_QACT_NONE ? ZANT_QACT_RELU : conv.a.activation;
+            } else {
+                uint8_t lut[256];
+                activation_lut(act, T(cur).dtype, lut);
+                fz.lut_aux = pl->add_aux(lut, 256);
+            }
+            interior.push_back(cur);
+            cur = act.out[0];
+            ++j;
+        }
+    }
+    // pool behind that
+    bool want_pool = false;
+    if (!conv.a.channels_last && j < pl->nodes.size() && only_feeds_next(c, cur)) {
+        const PlanNode& pool = pl->nodes[j];
+        if (pool.op == ZANT_OP_MAXPOOL && pool.in.size() == 1 && pool.out.size() == 1 && pool.in[0] == cur && pool2x2(pool.a) &&
+            T(pool.out[0]).dtype == T(cur).dtype && T(cur).shape.size() == 4 && T(pool.out[0]).shape.size() == 4) {
+            const auto& si = T(cur).shape; const auto& so = T(pool.out[0]).shape;
+            if (so[0] == si[0] && so[1] == si[1] && so[2] == si[2] / 2 && so[3] == si[3] / 2 && so[2] > 0 && so[3] > 0) {
+                want_pool = true;
+                fz.y_pool = pool.out[0];
+            }
+        }
+    }
+    if (interior.empty() && !want_pool) return ZANT_OK;        // nothing behind the node: the plain path builds it
+    fz.y_act = cur;
+    const size_t first_step = pl->steps.size();
+    ZB_TRY(build_qconv(pl, conv, fz));
+    if (fz.pool_done) { interior.push_back(cur); ++j; }
+    if (interior.empty()) {
+        // the pool was asked for but the chosen kernel cannot take it: nothing was fused after all
+        record_step_cost(pl, first_step, i0, 1);
+        consumed = 1;
+        return ZANT_OK;
+    }
+    for (int id : interior) pl->t[id].elided = true;
+    consumed = j - i0;
+    record_step_cost(pl, first_step, i0, consumed);
+    return ZANT_OK;
+}
+
+static int32_t try_fuse_small_cnn(zant_plan* pl, size_t i0, size_t& consumed) {
     consumed = 0;
     if (i0 + 12 > pl->nodes.size()) return ZANT_OK;
     const int kOps[12] = {ZANT_OP_QUANTIZE_LINEAR, ZANT_OP_QLINEAR_CONV, ZANT_OP_RELU, ZANT_OP_MAXPOOL, ZANT_OP_QLINEAR_CONV, ZANT_OP_RELU,

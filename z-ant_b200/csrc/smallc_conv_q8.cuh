@@ -48,6 +48,7 @@ struct SmallcArgs {
     int KS;
     uint32_t pad_word;
     float y_scale; int y_zp; int act; int out_u8;
+    const uint8_t* lut;       // optional table applied to the output codes (see Requant)
     int six; int small_products;
     int vec_ok;                       // output words of a thread are aligned (base and OW)
 };
@@ -91,7 +92,7 @@ __global__ void __launch_bounds__(kSmallcThreads) qconv3x3_smallc_kernel(const S
     }
     // pixel (within a unit) that this lane supplies to MMA nt: column g <-> pixel 2*NTL*(g/2) + 2*nt + g%2
     const int bpix0 = 2 * NTL * (g >> 1) + (g & 1);
-    const Requant rq{a.y_scale, a.y_zp, a.act};
+    const Requant rq{a.y_scale, a.y_zp, a.act, a.lut};
     const uint32_t six4 = 0x01010101u * (uint32_t)(a.six & 255);
     const size_t ohw = (size_t)a.OH * a.OW;
     const int words_per_row = a.P >> 2;
@@ -159,6 +160,7 @@ __global__ void __launch_bounds__(kSmallcThreads) qconv3x3_smallc_kernel(const S
                                                    tc_conv_round<true>(v2, mult[mt][h]), tc_conv_round<true>(v3, mult[mt][h]));
                             if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
                             if (a.act == ZANT_QACT_RELU6) pk = __vmins4(pk, six4);
+                            if (a.lut) pk = lut4(a.lut, pk);
                             wd[p] = pk;
                         } else {
                             const int q0 = a.out_u8 ? requant_one<true>(v0, mult[mt][h], rq) : requant_one<false>(v0, mult[mt][h], rq);
@@ -252,7 +254,7 @@ inline int32_t run_qconv_smallc(zant_ctx* ctx, const ConvGeom& g, const void* x,
     const int NTL = (g.OW % 32 == 0 || g.OW >= 256) ? 4 : 2;
     a.upr = (g.OW + 8 * NTL - 1) / (8 * NTL);
     a.pad_word = 0x01010101u * (uint32_t)(x_zp & 255);
-    a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0;
+    a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0; a.lut = rq.lut;
     const bool lean = !y_u8 && rq.y_zp == 0 && std::isfinite(max_product);
     a.small_products = max_product < 4194304.0 ? 1 : 0;
     if (lean) {

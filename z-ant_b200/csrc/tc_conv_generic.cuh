@@ -270,7 +270,7 @@ inline int32_t run_qconv_tc(zant_ctx* ctx, const ConvGeom& g, const void* x, boo
     }
     TcGemmArgs k{};
     k.a = (const int8_t*)a_blk; k.w = w_blk_dev; k.mult = mult_dev; k.bias = bias_dev; k.y = (int8_t*)y;
-    k.M = (int)M; k.N = p.N_pad; k.K16 = p.K16; k.y_scale = rq.y_scale; k.y_zp = rq.y_zp; k.act = rq.act; k.status = ctx->status_word;
+    k.M = (int)M; k.N = p.N_pad; k.K16 = p.K16; k.y_scale = rq.y_scale; k.y_zp = rq.y_zp; k.act = rq.act; k.lut = rq.lut; k.status = ctx->status_word;
     k.n_valid = g.M; k.ohw = g.OH * g.OW; k.out_u8 = y_u8 ? 1 : 0;
     const int tiles = (int)((M + 127) / 128) * (p.N_pad / p.NT);
     if (p.NT == 64) return x_u8 ? launch_tc_gemm<64, 3>(ctx, k, tiles) : launch_tc_gemm<64, 2>(ctx, k, tiles);

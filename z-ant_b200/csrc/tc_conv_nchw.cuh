@@ -72,6 +72,9 @@ struct TcConvArgs {
     int six;                          // lean epilogue: sat8(rne(6 / y_scale)), used by ReLU6
     int small_products;               // lean epilogue: every |accumulator * multiplier| is below 2^22 (host-checked bound)
     int m_pad;                        // filters rounded up to the tile width
+    const uint8_t* lut;               // optional 256-entry table applied to the output codes (see Requant)
+    int pool;                         // NCHW kernel: 1 = a 2x2 / stride-2 MaxPool follows; y is the POOLED tensor [N, M, OH/2, OW/2]
+    int POH, POW;                     // pooled output dimensions (floor)
     int* status;
 };
 
@@ -490,7 +493,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         const int e = ew * 32 + lane;
         const uint32_t epi_bar = grp == 0 ? 1u : 3u;           // named barrier of the group (2 belongs to warps 2..9 in their other roles)
         volatile int* grp_ok = epi_ok + grp;
-        const Requant rq{a.y_scale, a.y_zp, a.act};
+        const Requant rq{a.y_scale, a.y_zp, a.act, a.lut};
         const int oh_l = row / a.PW, ow_l = row - oh_l * a.PW;
         const bool row_live = oh_l < a.BH && ow_l < a.BW;        // this MMA row is an output of the tile
         const int pix_off = oh_l * a.BW + ow_l;
@@ -564,6 +567,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                             uint32_t w4 = pack_sat_s8x4(q0, q1, q2, q3);
                             if (a.act != ZANT_QACT_NONE) w4 = relu_s8x4(w4);
                             if (a.act == ZANT_QACT_RELU6) w4 = __vmins4(w4, six4);
+                            if (a.lut) w4 = lut4(a.lut, w4);
                             pk[j4] = w4;
                         }
                     };
@@ -607,8 +611,46 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
             ptx::named_barrier_sync(epi_bar, n_epi * 32);
             ZB_TACC(3);
 
-            // copy-out: per filter one contiguous run of the NCHW output
             const int ncv = min(NT, a.M - T.nt * NT);
+            if (a.pool) {
+                // A 2x2 / stride-2 MaxPool follows: the pooled bytes are written instead of the block's own.  The window's
+                // two rows are two rows of this block (BH even), or this block and the previous one (BH == 1: blocks are
+                // single output rows, an even block only stages).  Tiles and row blocks start at even rows and columns, so
+                // windows never straddle a tile.  The maximum is taken on the finished codes, which is what the separate
+                // MaxPool operator does on the int8 tensor.
+                const bool pair = a.BH == 1;
+                if (!pair || (rb & 1)) {
+                    const uint8_t* ob_top = pair ? sOut + (size_t)((blk_it ^ 1) & 1) * NT * kTcConvOutPitch : ob;
+                    const int rows = pair ? 2 : min(a.BH, a.OH - hb);
+                    const int cols = a.wseg == 1 ? a.OW : min(a.BW, a.OW - T.w0);
+                    const int pr_n = rows >> 1, pc_n = cols >> 1, half = (pc_n + 1) >> 1;
+                    const int per_c = pr_n * half;
+                    const int prow0 = (pair ? hb - 1 : hb) >> 1;
+                    for (int c = ew; c < ncv; c += n_epi) {
+                        uint8_t* dst_c = a.y + (((size_t)T.img * a.M + (size_t)(T.nt * NT + c)) * a.POH + prow0) * a.POW + (T.w0 >> 1);
+                        for (int j = lane; j < per_c; j += 32) {
+                            const int pr = j / half, k = j - pr * half;
+                            const uint8_t* p0 = (pair ? ob_top : ob + (size_t)(2 * pr) * a.BW) + c * kTcConvOutPitch + 4 * k;
+                            const uint8_t* p1 = pair ? ob + c * kTcConvOutPitch + 4 * k : p0 + a.BW;
+                            const uint32_t w0 = (uint32_t)*reinterpret_cast<const uint16_t*>(p0) | ((uint32_t)*reinterpret_cast<const uint16_t*>(p0 + 2) << 16);
+                            const uint32_t w1 = (uint32_t)*reinterpret_cast<const uint16_t*>(p1) | ((uint32_t)*reinterpret_cast<const uint16_t*>(p1 + 2) << 16);
+                            uint32_t m = a.out_u8 ? __vmaxu4(w0, w1) : __vmaxs4(w0, w1);
+                            m = a.out_u8 ? __vmaxu4(m, m >> 8) : __vmaxs4(m, m >> 8);     // bytes 0 and 2: the two windows' maxima
+                            uint8_t* d = dst_c + (size_t)pr * a.POW + 2 * k;
+                            if (2 * k + 1 < pc_n) {
+                                if ((reinterpret_cast<uintptr_t>(d) & 1u) == 0) *reinterpret_cast<uint16_t*>(d) = (uint16_t)__byte_perm(m, 0u, 0x4420u);
+                                else { d[0] = (uint8_t)m; d[1] = (uint8_t)(m >> 16); }
+                            } else {
+                                d[0] = (uint8_t)m;
+                            }
+                        }
+                    }
+                    if (pair) ptx::named_barrier_sync(epi_bar, n_epi * 32);   // both buffers are read: the next block's staging waits
+                }
+                ZB_TACC(4);
+                continue;
+            }
+            // copy-out: per filter one contiguous run of the NCHW output
             const int L = a.wseg == 1 ? min(a.BH, a.OH - hb) * a.OW : min(a.BW, a.OW - T.w0);
             const int nvec = L >> a.log2V, tail_bytes = L - (nvec << a.log2V);
             const int slots = nvec + (tail_bytes ? 1 : 0);
@@ -658,8 +700,11 @@ inline int tc_gcd(int a, int b) { while (b) { const int t = a % b; a = b; b = t;
 
 // Chooses tiling for `g`.  Returns false when the kernel does not apply (the caller then uses the
 // im2col path or the generic kernel).
-inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
+// `pool`: the epilogue also applies a 2x2 / stride-2 MaxPool (no padding, floor) and writes only the pooled tensor; tiles and
+// row blocks then start at even rows and columns (BH even, or single-row blocks in pairs).
+inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p, bool pool = false) {
     if (g.G != 1 || !w_zp_all_zero || g.sh != 1 || g.sw != 1) return false;
+    if (pool && (g.OH < 2 || g.OW < 2)) return false;
     if (g.M > kTcConvMaxFilters || g.N <= 0 || g.OH <= 0 || g.OW <= 0) return false;
     TcConvArgs& a = p.a;
     a = TcConvArgs{};
@@ -674,9 +719,13 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
     const int halo_w = (a.KW - 1) * a.dw, halo_h = (a.KH - 1) * a.dh;
     if (halo_w > 32 || halo_h > 32) return false;
     if (!pointwise && (g.pl > halo_w || g.pr > halo_w || g.pt > halo_h || g.pb > halo_h)) return false;   // every tile overlaps the image
+    if (pool && pointwise) return false;      // the pooled epilogue belongs to the patch form of the kernel
     a.BW = std::min(a.OW, 128 - halo_w);
+    if (pool && a.BW < a.OW && (a.BW & 1)) a.BW -= 1;          // column segments start at even columns
     a.PW = a.BW + halo_w;
     a.BH = std::max(1, std::min(a.OH, 128 / a.PW));
+    if (pool && a.BH > 1 && (a.BH & 1)) a.BH -= 1;            // row blocks hold whole window rows
+    a.pool = pool ? 1 : 0; a.POH = g.OH / 2; a.POW = g.OW / 2;
     a.wseg = (a.OW + a.BW - 1) / a.BW;
     a.full_width = a.wseg == 1 ? 1 : 0;
     a.direct = pointwise ? 1 : 0;
@@ -702,6 +751,7 @@ inline bool tc_conv_plan(const ConvGeom& g, bool w_zp_all_zero, TcConvPlan& p) {
     bool placed = false;
     for (int rb = (a.direct || halo_h == 0) ? 1 : 4; rb >= 1 && !placed; rb /= 2) {
         if (2 * rb * p.NT > 512 || (rb > 1 && rb > blocks_in_image)) continue;
+        if (pool && base.BH == 1 && (rb & 1)) continue;        // single-row blocks pool in pairs
         a = base;
         a.RB = rb; a.BHT = rb * a.BH;
         a.PH = a.BHT + halo_h;
@@ -871,7 +921,7 @@ inline int32_t tc_conv_run(zant_ctx* ctx, const TcConvPlan& p, const void* x, bo
     TcConvArgs a = p.a;
     a.x = (const uint8_t*)x; a.y = (uint8_t*)y; a.w = w_blk_dev; a.mult = mult_dev; a.bias = bias_dev;
     a.pad_word = 0x01010101u * (uint32_t)(x_zp & 255);
-    a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0;
+    a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0; a.lut = rq.lut;
     if (!tc_conv_ptr_ok(y)) { a.V = 1; a.log2V = 0; }
     const bool lean = !y_u8 && rq.y_zp == 0 && mult_finite;
     a.small_products = max_product < 4194304.0 ? 1 : 0;

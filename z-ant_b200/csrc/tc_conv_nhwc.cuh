@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
         const int part = ew >> 2;
         constexpr int cols = NT / 4;
         const int row = quarter * 32 + lane;
-        const Requant rq{a.y_scale, a.y_zp, a.act};
+        const Requant rq{a.y_scale, a.y_zp, a.act, a.lut};
         const int oh_l = row / a.PW, ow_l = row - oh_l * a.PW;
         const bool row_live = oh_l < a.BH && ow_l < a.BW;
         const uint32_t six4 = 0x01010101u * (uint32_t)(a.six & 255);
@@ -245,6 +245,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
                                                             tc_conv_round<CL>((int)v[j4 * 4 + 2] + b4.z, m4.z), tc_conv_round<CL>((int)v[j4 * 4 + 3] + b4.w, m4.w));
                                 if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
                                 if (a.act == ZANT_QACT_RELU6) pk = __vmins4(pk, six4);
+                                if (a.lut) pk = lut4(a.lut, pk);
                                 wd[j4] = pk;
                             }
                         };
@@ -418,7 +419,7 @@ inline int32_t tc_conv_nhwc_run(zant_ctx* ctx, const TcConvPlan& p, const void* 
                                 const int32_t* bias_dev, void* y, bool y_u8, const Requant& rq, double max_product) {
     TcConvArgs a = p.a;
     a.x = (const uint8_t*)x; a.y = (uint8_t*)y; a.w = w_blk_dev; a.mult = mult_dev; a.bias = bias_dev;
-    a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0;
+    a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0; a.lut = rq.lut;
     const bool lean = !y_u8 && rq.y_zp == 0 && std::isfinite(max_product);
     a.small_products = max_product < 4194304.0 ? 1 : 0;
     if (lean) {

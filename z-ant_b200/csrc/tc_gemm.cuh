@@ -34,6 +34,7 @@ struct TcGemmArgs {
     int8_t* y;             // [M][N] row-major
     int M, N, K16;         // N = padded column count (multiple of NT), K16 = K/16, a multiple of KC
     float y_scale; int y_zp; int act;
+    const uint8_t* lut;       // MODE 2 only: optional table applied to the output codes (see Requant)
     int* status;
     // MODE & 2 (convolution output): valid columns (output channels), positions per image (OH*OW)
     // and output type; rows are (image, position) and the result is stored NCHW.
@@ -199,7 +200,7 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constan
             } else {
                 // rows are (image, position): consecutive lanes hold consecutive positions, so for a
                 // fixed channel a warp writes 32 consecutive bytes of the NCHW output
-                const Requant rq{a.y_scale, a.y_zp, a.act};
+                const Requant rq{a.y_scale, a.y_zp, a.act, a.lut};
                 const int img = grow / a.ohw, pos = grow - img * a.ohw;
                 uint8_t* ybase = reinterpret_cast<uint8_t*>(a.y) + (size_t)img * a.n_valid * a.ohw + pos;
 #pragma unroll 1
