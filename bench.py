@@ -414,8 +414,8 @@ def run_gpu_arm(args, rank, world, local):
     ctx = zb.Context(local)
     stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local))
     fuse = not args.no_fuse
-    if args.dtype == "tf32":
-        ctx.set_tf32(True)
+    if args.dtype in ("tf32", "tf32x3"):
+        ctx.set_tf32(1 if args.dtype == "tf32" else 2)
 
     int8_peak = ctx.measure_int8_peak(20000)          # resident-tile tcgen05 probe, ~15 ms per launch, best of four
     peaks = measured_peaks()
@@ -626,7 +626,7 @@ def run_gpu_arm(args, rank, world, local):
                    parallelism=f"sample-sharded x{world}, no collective")
         line = dict(metric=wl.metric, value=value, unit="images/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
                     ms_per_step=ms / args.steps, higher_is_better=True, scaling=args.scaling, vs_baseline=None,
-                    dtype=("tf32" if args.dtype == "tf32" else wl.dtype), data="synthetic", config=cfg,
+                    dtype=(args.dtype if args.dtype != "native" else wl.dtype), data="synthetic", config=cfg,
                     roofline=roof, int8_peak_tops=int8_peak, bf16_tflops_measured=peaks["bf16_tflops"],
                     per_kernel=top_rows, ms_by_step_kind={k: round(v, 4) for k, v in sorted(by_kind.items(), key=lambda kv: -kv[1])},
                     cpu_baseline=cpu,
@@ -639,15 +639,9 @@ def run_gpu_arm(args, rank, world, local):
     for p in extra_plans:
         p.close()
     plan.close()
-    # tensors that were used on the contexts' streams go back to torch's allocator before those streams are destroyed
-    del x_dev, y_dev
-    if wl.flush_l2:
-        del flush, clean
+    # The contexts (and their streams) stay alive until the process exits: torch's allocators record events on every
+    # stream a buffer was used on when that buffer is freed, which for the pinned host buffers happens at interpreter exit.
     torch.cuda.synchronize()
-    torch.cuda.empty_cache()
-    if ctx2 is not None:
-        ctx2.close()
-    ctx.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -662,7 +656,8 @@ def main():
                     help="small_cnn_int8 is the headline workload; the qconv cases time one standalone operator")
     ap.add_argument("--batch", type=int, default=0, help="images per GPU per step (weak) or in total (strong); 0 = the workload's own")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
-    ap.add_argument("--dtype", default="native", choices=["native", "tf32"], help="tf32: float contractions on the tensor cores (2e-3 contract)")
+    ap.add_argument("--dtype", default="native", choices=["native", "tf32", "tf32x3"],
+                    help="tf32: float contractions on the tensor cores, one pass; tf32x3: the same with split operands (three MMAs per K step)")
     ap.add_argument("--graph", action="store_true", help="replay the plan as one CUDA graph in the timed region")
     ap.add_argument("--no-fuse", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")

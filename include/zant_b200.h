@@ -138,9 +138,13 @@ int32_t zant_b200_ctx_set_stream(zant_ctx* ctx, void* cuda_stream);
 /* Float precision of the contractions (Conv, MatMul, Gemm) issued through this context.  Off (the default, unless
  * the environment variable ZANT_B200_TF32 is set when the context is created): the exact FP32 kernels, which keep
  * the reference's order of operations (sequential fp32 accumulation, op_mat_mul.zig:132-148) and are bit-identical
- * to it.  On: tensor-core kernels (tcgen05 kind::tf32, operands rounded to TF32, fp32 accumulation) whose results
- * are within 2e-3 of the reference, |y - ref| <= 2e-3 * max(|ref|, 1e-2 * max|ref|).  A plan takes the setting of
- * its context when it is finalized; zant_b200_conv_f32 takes it at each call.  No reference counterpart. */
+ * to it.  1: tensor-core kernels (tcgen05 kind::tf32, operands rounded to TF32, fp32 accumulation), one MMA per K step;
+ * the error of an output is about 3e-4 of the root sum of squares of its products: within 2e-3 of the output's scale,
+ * |y - ref| <= 2e-3 * max(|ref|, 1e-1 * max|ref|), but not relative to outputs that are near-cancellations.  2: the
+ * same kernels with every operand split into two TF32 parts (three MMAs per K step), which recovers about 21 bits of the
+ * products: within |y - ref| <= 2e-3 * max(|ref|, 1e-2 * max|ref|) with a wide margin (in practice within the 1e-4 rule
+ * of the FP32 path), at about half the speed of mode 1.  A plan takes the setting of its context when it is finalized;
+ * zant_b200_conv_f32 and zant_b200_mat_mul_f32 take it at each call.  No reference counterpart. */
 int32_t zant_b200_ctx_set_tf32(zant_ctx* ctx, int32_t enable);
 int32_t zant_b200_ctx_get_tf32(zant_ctx* ctx);
 

@@ -353,3 +353,38 @@ def test_qlinearmatmul_tensor_core_path(ctx, oracle, M, K, N, adt, ydt, azp, yzp
     assert ctx.launch_count() - before == 2
     want = oracle.qlinearmatmul(a, 0.02, azp, b, bs, None, ys, yzp, bias, ydt, act)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("dt,scale,zp", [(U8, 1 / 255, 0), (I8, 0.02, 0), (I8, 0.013, -7), (U8, 0.031, 128), (I8, 0.1, 127), (U8, 3.7e-3, 255)])
+def test_quantize_rounding_boundaries(ctx, oracle, dt, scale, zp):
+    """QuantizeLinear takes the division only where a multiply cannot prove the rounding.  The values that decide it: every
+    k + 0.5 of the output range times the scale, the floats next to each of them, the clamp bounds, and non-finite inputs."""
+    s = np.float32(scale)
+    lo, hi = (0, 255) if dt == U8 else (-128, 127)
+    ks = np.arange(lo - zp - 3, hi - zp + 4, dtype=np.float32)
+    centre = ((ks + np.float32(0.5)) * s).astype(np.float32)
+    xs = [centre, np.nextafter(centre, np.float32(np.inf)), np.nextafter(centre, np.float32(-np.inf)), (ks * s).astype(np.float32)]
+    for _ in range(3):                                        # a few more steps away from the boundary, both ways
+        xs.append(np.nextafter(xs[1] if len(xs) % 2 else xs[2], np.float32(np.inf if len(xs) % 2 else -np.inf)))
+    special = np.array([np.inf, -np.inf, np.nan, 0.0, -0.0, 1e30, -1e30, 1e-40], np.float32)
+    x = np.concatenate(xs + [special]).astype(np.float32)
+    x = np.concatenate([x, np.zeros((-len(x)) % 4, np.float32)])          # the vector path takes whole float4s
+    got, want = ctx.quantize_linear(x, scale, zp, dt), oracle.quantize_linear(x, scale, zp, dt)
+    assert np.array_equal(got, want)
+
+
+def test_fused_cnn_input_quantisation_on_rounding_boundaries(zb, ctx, oracle):
+    """The fused first stage of the int8 CNN quantises its float input itself: images made of rounding-boundary values."""
+    import graph_oracle
+    from zant_b200 import models
+    g = models.small_cnn_int8(6)
+    s = np.float32(1.0) / np.float32(255.0)
+    ks = np.arange(0, 28 * 28, dtype=np.float32) % 256
+    centre = ((ks + np.float32(0.5)) * s).astype(np.float32).reshape(1, 1, 28, 28)
+    x = np.concatenate([centre, np.nextafter(centre, np.float32(np.inf)), np.nextafter(centre, np.float32(-np.inf)),
+                        centre[:, :, ::-1], np.full_like(centre, 2.0), np.full_like(centre, -1.0)]).astype(np.float32)
+    want = graph_oracle.run(oracle, g, x)[g.output]
+    plan = zb.Plan(ctx, g, fuse=True)
+    assert any("Fused" in n for n in plan.step_names())
+    assert np.array_equal(plan.run(x).view(np.uint32), want.view(np.uint32))
+    plan.close()

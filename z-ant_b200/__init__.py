@@ -274,9 +274,9 @@ class Context:
     def set_stream(self, cuda_stream_ptr):
         check(lib().zant_b200_ctx_set_stream(self._h, C.c_void_p(cuda_stream_ptr)))
 
-    def set_tf32(self, enable=True):
-        """Float contractions on the tensor cores (2e-3 contract) instead of the exact FP32 kernels."""
-        check(lib().zant_b200_ctx_set_tf32(self._h, C.c_int32(int(enable))))
+    def set_tf32(self, mode=1):
+        """Float contractions: 0 = exact FP32 kernels, 1 = tensor cores (TF32, one pass), 2 = tensor cores with split operands."""
+        check(lib().zant_b200_ctx_set_tf32(self._h, C.c_int32(int(mode))))
 
     def set_arena_limit(self, max_bytes):
         """Caps the staging arena of host-pointer calls (0 = grow on demand)."""

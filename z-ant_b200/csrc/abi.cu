@@ -80,7 +80,7 @@ int32_t zant_b200_ctx_create(int32_t device, size_t arena_bytes, zant_ctx** out)
     e = dev_malloc((void**)&c->status_word, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(c->status_word, 0, sizeof(int));
     if (e != cudaSuccess) { cudaFree(c->arena); cudaStreamDestroy(c->stream); delete c; return fail(ZANT_E_CUDA, "status word: %s", cudaGetErrorString(e)); }
-    c->tf32 = env_flag("ZANT_B200_TF32");
+    if (const char* v = std::getenv("ZANT_B200_TF32")) c->tf32 = (v[0] == '2') ? 2 : (env_flag("ZANT_B200_TF32") ? 1 : 0);
     *out = c;
     log_line("zant_b200 context on device %d (%s, %d SMs)", device, prop.name, prop.multiProcessorCount);
     return ZANT_OK;
@@ -108,11 +108,12 @@ int32_t zant_b200_ctx_set_stream(zant_ctx* ctx, void* cuda_stream) {
 
 int32_t zant_b200_ctx_set_tf32(zant_ctx* ctx, int32_t enable) {
     ZB_NEED_CTX(ctx);
-    ctx->tf32 = enable != 0;
+    if (enable < 0 || enable > 2) return fail(ZANT_E_INVALID_INPUT, "TF32 mode %d (0 exact FP32, 1 TF32, 2 split TF32)", enable);
+    ctx->tf32 = enable;
     return ZANT_OK;
 }
 
-int32_t zant_b200_ctx_get_tf32(zant_ctx* ctx) { return (ctx && ctx->tf32) ? 1 : 0; }
+int32_t zant_b200_ctx_get_tf32(zant_ctx* ctx) { return ctx ? ctx->tf32 : 0; }
 
 int32_t zant_b200_ctx_set_arena_limit(zant_ctx* ctx, size_t max_bytes) {
     ZB_NEED_CTX(ctx);
@@ -270,7 +271,7 @@ int32_t zant_b200_conv_f32(zant_ctx* ctx, const float* x, const size_t* x_shape,
     if (ctx->tf32 && !is_device_ptr(w) && !(bias && is_device_ptr(bias)) && g.M <= 2048 && (long long)g.N * g.OH * g.OW >= 128) {
         // tensor-core path (2e-3 contract): weights blocked on the host, im2col gather + tcgen05 kind::tf32 GEMM
         TfGemmPrep prep;
-        tf_gemm_prepare(w, g.M, g.C * g.KH * g.KW, (long long)g.C * g.KH * g.KW, 1, bias, prep, (long long)g.N * g.OH * g.OW);
+        tf_gemm_prepare(w, g.M, g.C * g.KH * g.KW, (long long)g.C * g.KH * g.KW, 1, bias, prep, (long long)g.N * g.OH * g.OW, ctx->tf32 == 2);
         Stager s(ctx);
         const int ix = s.in(x, numel(x_shape, 4) * 4), iy = s.out(y, numel(y_shape, 4) * 4);
         const int iw = s.in(prep.w_blk.data(), prep.w_blk.size() * 4), ib = s.in(prep.bias.data(), prep.bias.size() * 4);
@@ -297,7 +298,7 @@ int32_t zant_b200_mat_mul_f32(zant_ctx* ctx, const float* a, const size_t* a_sha
     ZB_NEED_CTX(ctx);
     if (ctx->tf32 && !is_device_ptr(b) && g.N <= 2048 && g.M >= 128 && g.K <= 0x7fffffffULL && g.M <= 0x7fffffffULL) {
         TfGemmPrep prep;
-        tf_gemm_prepare(b, (int)g.N, (int)g.K, 1, (long long)g.N, nullptr, prep, (long long)g.M);
+        tf_gemm_prepare(b, (int)g.N, (int)g.K, 1, (long long)g.N, nullptr, prep, (long long)g.M, ctx->tf32 == 2);
         Stager s(ctx);
         const int ia = s.in(a, g.M * g.K * 4), iy = s.out(y, g.M * g.N * 4);
         const int iw = s.in(prep.w_blk.data(), prep.w_blk.size() * 4), ibz = s.in(prep.bias.data(), prep.bias.size() * 4);

@@ -19,7 +19,7 @@ struct zant_ctx {
     uint64_t launches = 0;
     int sm_count = 148;
     int* status_word = nullptr;   // device int: kernels with bounded waits report here
-    bool tf32 = false;            // float contractions on the tensor cores (kind::tf32, 2e-3 contract) instead of the exact FP32 kernels
+    int tf32 = 0;                 // float contractions: 0 = the exact FP32 kernels, 1 = tensor cores (kind::tf32, single pass), 2 = tensor cores, split operands (3 x TF32)
 };
 
 namespace zb {

@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
         for (int b = 0; b < 2; ++b) { bias[j][b] = __ldg(a.biasfrag + (j * 32 + lane) * 2 + b); mult[j][b] = __ldg(a.multfrag + (j * 32 + lane) * 2 + b); }
     __syncthreads();                               // barriers and the abort flag are set up
 
-    const float q_lo = (float)(-a.x_zp), q_hi = (float)(255 - a.x_zp);
+    const QuantFast qf = quant_fast(a.x_scale, (float)(-a.x_zp), (float)(255 - a.x_zp));
     // this thread's 8 channels: chunk t >> 1 (four parity planes further), half t & 1
     int8_t* const y_thread = a.y + (size_t)(t >> 1) * 4 * (size_t)a.plane_bytes + (t & 1) * 8;
     constexpr size_t img_bytes = 36 * 16;
@@ -161,10 +161,11 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
                 const float4 v = reinterpret_cast<const float4*>(stage[s])[gi * 196 + p4];
                 // sat_u8(rne(clamp(t, -512, 511)) + zp) == rne(clamp(t, -zp, 255 - zp)) + zp: the bounds are integers
                 // inside [-512, 511] and rounding is monotonic; a NaN becomes the lower bound either way.
-                const int q0 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.x, a.x_scale), q_lo), q_hi)) + a.x_zp;
-                const int q1 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.y, a.x_scale), q_lo), q_hi)) + a.x_zp;
-                const int q2 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.z, a.x_scale), q_lo), q_hi)) + a.x_zp;
-                const int q3 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.w, a.x_scale), q_lo), q_hi)) + a.x_zp;
+                // (quantize_fast: the division only where the multiply cannot prove the rounding)
+                const int q0 = quantize_fast(v.x, qf) + a.x_zp;
+                const int q1 = quantize_fast(v.y, qf) + a.x_zp;
+                const int q2 = quantize_fast(v.z, qf) + a.x_zp;
+                const int q3 = quantize_fast(v.w, qf) + a.x_zp;
                 word = (uint32_t)q0 | ((uint32_t)q1 << 8) | ((uint32_t)q2 << 16) | ((uint32_t)q3 << 24);
             }
             const int r = p4 / 7, c4 = p4 - r * 7;

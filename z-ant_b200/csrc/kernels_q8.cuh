@@ -16,6 +16,36 @@ __device__ __forceinline__ int rne_clamped(float v) {
     return __float2int_rn(v);
 }
 
+// QuantizeLinear's rne(clamp(x / scale, lo, hi)) without the division on the common path.
+// q = rint(clamp(x * r, lo, hi)) with r = fl(1 / scale) is the wanted integer unless x / scale lies within a few units
+// in the last place of a rounding boundary (k + 0.5) or of a clamp bound.  The residual e = fma(-q, scale, x) is the
+// exact x - q * scale rounded once, so |e| < h with h a little below scale / 2 proves that x / scale lies strictly inside
+// (q - 0.5, q + 0.5); a q at a clamp bound is proved by the sign of e alone (the true quotient is beyond the bound or
+// inside the last half-step).  Everything else - about one value in a few thousand - takes the correctly rounded division.
+// The reference formula rounds the fp32 quotient d = fl(x / scale), so the proof needs a margin of half a unit in the
+// last place of d around the boundaries: with |d| < 256 that is below 8e-6, and h leaves 1e-4.
+// `lo` and `hi` are integers in [-255, 255] (the clamp of the reference formula with the zero point folded in).  A scale
+// that is not positive and finite disables the fast path (h = -1 and unreachable bounds).
+struct QuantFast { float scale, r, h, lo, hi, klo, khi; };
+
+__host__ __device__ inline QuantFast quant_fast(float scale, float lo, float hi) {
+    QuantFast q;
+    const bool usable = scale > 0.0f && scale < 3.0e38f && (1.0f / scale) < 3.0e38f && lo >= -255.0f && hi <= 255.0f;
+    q.scale = scale; q.r = usable ? 1.0f / scale : 0.0f; q.h = usable ? scale * 0.4999f : -1.0f; q.lo = lo; q.hi = hi;
+    q.klo = usable ? lo : -1.0e30f; q.khi = usable ? hi : 1.0e30f;
+    return q;
+}
+
+__device__ __forceinline__ int quantize_fast(float x, const QuantFast& q) {
+    const float t = __fmul_rn(x, q.r);
+    const float c = fminf(fmaxf(t, q.lo), q.hi);         // a NaN becomes lo, as in the division form
+    const float k = rintf(c);
+    const float e = __fmaf_rn(-k, q.scale, x);
+    const bool proved = fabsf(e) < q.h || (k == q.khi && e > 0.0f) || (k == q.klo && e < 0.0f);
+    if (proved) return (int)k;
+    return __float2int_rn(fminf(fmaxf(__fdiv_rn(x, q.scale), q.lo), q.hi));
+}
+
 template <bool U8> __device__ __forceinline__ int sat_q(int t) {
     return U8 ? min(max(t, 0), 255) : min(max(t, -128), 127);
 }
@@ -79,16 +109,20 @@ __global__ void quantize_linear_k(const float* __restrict__ x, void* __restrict_
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
     size_t done = 0;
-    if (vec) {
+    // sat(rne(clamp(t, -512, 511)) + zp) == rne(clamp(t, lo - zp, hi - zp)) + zp for a zero point inside the type's range:
+    // the bounds are integers inside [-512, 511] and rounding is monotonic
+    const bool zp_ok = YU8 ? (zp >= 0 && zp <= 255) : (zp >= -128 && zp <= 127);
+    if (vec && zp_ok) {
+        const QuantFast qf = quant_fast(scale, (float)((YU8 ? 0 : -128) - zp), (float)((YU8 ? 255 : 127) - zp));
         const size_t n4 = n / 4;
         const float4* x4 = reinterpret_cast<const float4*>(x);
         uint32_t* y4 = reinterpret_cast<uint32_t*>(y);
         for (size_t i = tid; i < n4; i += stride) {
             const float4 v = x4[i];
-            const int a = sat_q<YU8>(rne_clamped(__fdiv_rn(v.x, scale)) + zp);
-            const int b = sat_q<YU8>(rne_clamped(__fdiv_rn(v.y, scale)) + zp);
-            const int c = sat_q<YU8>(rne_clamped(__fdiv_rn(v.z, scale)) + zp);
-            const int d = sat_q<YU8>(rne_clamped(__fdiv_rn(v.w, scale)) + zp);
+            const int a = quantize_fast(v.x, qf) + zp;
+            const int b = quantize_fast(v.y, qf) + zp;
+            const int c = quantize_fast(v.z, qf) + zp;
+            const int d = quantize_fast(v.w, qf) + zp;
             y4[i] = (uint32_t)(a & 255) | ((uint32_t)(b & 255) << 8) | ((uint32_t)(c & 255) << 16) | ((uint32_t)(d & 255) << 24);
         }
         done = n4 * 4;

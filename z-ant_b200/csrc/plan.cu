@@ -658,7 +658,7 @@ static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t /*fuse*
                 // activation the fusion pass found behind the node in the epilogue
                 auto prep = std::make_shared<TfGemmPrep>();
                 const int K = g.C * g.KH * g.KW;
-                tf_gemm_prepare((const float*)T(w).host.data(), g.M, K, K, 1, b >= 0 ? (const float*)T(b).host.data() : nullptr, *prep, (long long)g.N * g.OH * g.OW);
+                tf_gemm_prepare((const float*)T(w).host.data(), g.M, K, K, 1, b >= 0 ? (const float*)T(b).host.data() : nullptr, *prep, (long long)g.N * g.OH * g.OW, ctx->tf32 == 2);
                 const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size() * 4), ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
                 const int sa = pl->shared_im2col_scratch(tf_gemm_a_bytes((size_t)g.N * g.OH * g.OW, *prep));
                 prep->w_blk.clear(); prep->w_blk.shrink_to_fit();
@@ -680,7 +680,7 @@ static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t /*fuse*
             ZB_TRY(matmul_check(T(x).shape.data(), T(x).shape.size(), T(w).shape.data(), T(w).shape.size(), T(y).shape.data(), T(y).shape.size(), g));
             if (ctx->tf32 && T(w).is_const && T(w).dtype == ZANT_F32 && g.N <= 2048 && g.M >= 128 && g.K <= 0x7fffffffULL && g.M <= 0x7fffffffULL) {
                 auto prep = std::make_shared<TfGemmPrep>();
-                tf_gemm_prepare((const float*)T(w).host.data(), (int)g.N, (int)g.K, 1, (long long)g.N, nullptr, *prep, (long long)g.M);
+                tf_gemm_prepare((const float*)T(w).host.data(), (int)g.N, (int)g.K, 1, (long long)g.N, nullptr, *prep, (long long)g.M, ctx->tf32 == 2);
                 const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size() * 4), ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
                 const int sa = pl->shared_im2col_scratch(tf_gemm_a_bytes(g.M, *prep));
                 prep->w_blk.clear(); prep->w_blk.shrink_to_fit();
@@ -708,7 +708,7 @@ static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t /*fuse*
                 if (ctx->tf32 && !ta && alpha == 1.0f && T(w).is_const && c_row && g.batch == 1 && g.cols <= 2048 && g.rows >= 128 && g.K <= 0x7fffffffULL && g.rows <= 0x7fffffffULL) {
                     auto prep = std::make_shared<TfGemmPrep>();
                     tf_gemm_prepare((const float*)T(w).host.data(), (int)g.cols, (int)g.K, tb ? (long long)g.K : 1, tb ? 1 : (long long)g.cols,
-                                    c >= 0 ? (const float*)T(c).host.data() : nullptr, *prep, (long long)g.rows);
+                                    c >= 0 ? (const float*)T(c).host.data() : nullptr, *prep, (long long)g.rows, ctx->tf32 == 2);
                     const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size() * 4), ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
                     const int sa = pl->shared_im2col_scratch(tf_gemm_a_bytes(g.rows, *prep));
                     prep->w_blk.clear(); prep->w_blk.shrink_to_fit();

@@ -13,6 +13,12 @@
 // TF32 (nearest, ties away) when they are blocked - the gather does it for A, the host for the weights -
 // because the tensor core would otherwise truncate them, which biases long sums.
 //
+// Two precisions.  Single pass: one MMA per K step on the rounded operands; the error of a sum is about
+// 3e-4 * sqrt(sum of squared products), i.e. small against the output's scale but not against an output that is
+// itself a near-cancellation.  Split ("3 x TF32"): every operand is carried as hi = tf32(v) and lo = tf32(v - hi),
+// and a K step issues A_hi*W_hi + A_lo*W_hi + A_hi*W_lo, which recovers about 21 bits of the products; a pipeline stage
+// then holds [hi chunks][lo chunks] of both operands.
+//
 // Persistent CTAs, one per SM; warp roles as in the int8 GEMM:
 //   warp 0    producer (bulk copies, STAGES-deep mbarrier ring)     warp 1   TMEM owner + MMA issuer
 //   warps 2-9 epilogue: TMEM -> registers, + bias, ReLU / LeakyReLU, store (row-major or NCHW)
@@ -33,8 +39,8 @@ namespace zb {
 enum FAct { FACT_NONE = 0, FACT_RELU = 1, FACT_LEAKY = 2 };
 
 struct TfGemmArgs {
-    const float* a;        // [ceil(M/128)][K4][128][4]
-    const float* w;        // [N/NT][K4][NT][4]
+    const float* a;        // [ceil(M/128)][K4/KC stages][parts][KC][128][4]   (parts: hi, and lo in the split form)
+    const float* w;        // [N/NT][K4/KC stages][parts][KC][NT][4]
     const float* bias;     // [N] (zeros when the operator has none)
     float* y;
     int M, N, K4;          // N = padded column count (multiple of NT), K4 = chunks of four floats, a multiple of KC
@@ -64,10 +70,13 @@ __device__ __forceinline__ float round_tf32(float v) {
     return __uint_as_float(u);
 }
 
-template <int NT, int KC, int STAGES>
+template <int NT, int KC, int STAGES, bool SPLIT = false>
 struct TfGemmCfg {
-    static constexpr int A_STAGE = KC * 128 * 16;
-    static constexpr int W_STAGE = KC * NT * 16;
+    static constexpr int PARTS = SPLIT ? 2 : 1;
+    static constexpr int A_PART = KC * 128 * 16;
+    static constexpr int W_PART = KC * NT * 16;
+    static constexpr int A_STAGE = PARTS * A_PART;
+    static constexpr int W_STAGE = PARTS * W_PART;
     static constexpr int STAGE = A_STAGE + W_STAGE;
     static constexpr int MAX_N = 2048;                       // bias kept in shared memory
     static constexpr int OFF_CONST = STAGES * STAGE;
@@ -80,9 +89,9 @@ struct TfGemmCfg {
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
-template <int NT, int KC, int STAGES>
+template <int NT, int KC, int STAGES, bool SPLIT>
 __global__ void __launch_bounds__(320, 1) tc_gemm_tf32_kernel(const __grid_constant__ TfGemmArgs a) {
-    using Cfg = TfGemmCfg<NT, KC, STAGES>;
+    using Cfg = TfGemmCfg<NT, KC, STAGES, SPLIT>;
     extern __shared__ __align__(1024) uint8_t smem[];
     float* sBias = reinterpret_cast<float*>(smem + Cfg::OFF_CONST);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
@@ -123,8 +132,8 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_tf32_kernel(const __grid_const
             int it = 0;
             for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
                 const int m = t / n_tiles, n = t - m * n_tiles;
-                const uint8_t* ga = reinterpret_cast<const uint8_t*>(a.a) + (size_t)m * a.K4 * 2048;
-                const uint8_t* gw = reinterpret_cast<const uint8_t*>(a.w) + (size_t)n * a.K4 * (NT * 16);
+                const uint8_t* ga = reinterpret_cast<const uint8_t*>(a.a) + (size_t)m * a.K4 * (Cfg::PARTS * 2048);
+                const uint8_t* gw = reinterpret_cast<const uint8_t*>(a.w) + (size_t)n * a.K4 * (Cfg::PARTS * NT * 16);
                 for (int ks = 0; ks < k_stages; ++ks, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
@@ -157,7 +166,16 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_tf32_kernel(const __grid_const
                     for (int kk = 0; kk < KC / 2; ++kk) {
                         const uint64_t da = ptx::smem_desc_kmajor(sa + (uint32_t)(kk * 2 * 2048), 2048, 128);
                         const uint64_t db = ptx::smem_desc_kmajor(sw + (uint32_t)(kk * 2 * NT * 16), NT * 16, 128);
-                        mma_tf32(d_tmem, da, db, idesc, (ks | kk) != 0);
+                        if constexpr (SPLIT) {
+                            // the two correction terms first, the leading term last
+                            const uint64_t da_lo = ptx::smem_desc_kmajor(sa + (uint32_t)(Cfg::A_PART + kk * 2 * 2048), 2048, 128);
+                            const uint64_t db_lo = ptx::smem_desc_kmajor(sw + (uint32_t)(Cfg::W_PART + kk * 2 * NT * 16), NT * 16, 128);
+                            mma_tf32(d_tmem, da_lo, db, idesc, (ks | kk) != 0);
+                            mma_tf32(d_tmem, da, db_lo, idesc, true);
+                            mma_tf32(d_tmem, da, db, idesc, true);
+                        } else {
+                            mma_tf32(d_tmem, da, db, idesc, (ks | kk) != 0);
+                        }
                     }
                     ptx::mma_commit(empty(s));
                 }
@@ -242,7 +260,27 @@ struct TfIm2colArgs {
     ConvGeom g;
     long long rows;        // N * OH * OW
     int K, K4;             // K = Cg * KH * KW (reference order c, kh, kw); K4 chunks including padding
+    int KC, parts;         // chunks per pipeline stage; 1 = rounded operand only, 2 = hi and lo parts
 };
+
+// Where chunk `kc` (part `part`) of row `r` of row tile `tile` lives, in float4 units: [tile][stage][part][KC][128]
+__device__ __forceinline__ long long tf_chunk_index(long long tile, int kc, int part, int r, int K4, int KC, int parts) {
+    const int stage = kc / KC, j = kc - stage * KC;
+    return ((tile * (K4 / KC) + stage) * parts + part) * (long long)KC * 128 + (long long)j * 128 + r;
+}
+
+__device__ __forceinline__ void tf_store_chunk(float* a, long long tile, int kc, int r, int K4, int KC, int parts, const float v[4]) {
+    float hi[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) hi[j] = round_tf32(v[j]);
+    reinterpret_cast<float4*>(a)[tf_chunk_index(tile, kc, 0, r, K4, KC, parts)] = make_float4(hi[0], hi[1], hi[2], hi[3]);
+    if (parts == 2) {
+        float lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) lo[j] = round_tf32(__fsub_rn(v[j], hi[j]));
+        reinterpret_cast<float4*>(a)[tf_chunk_index(tile, kc, 1, r, K4, KC, parts)] = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
 
 // A[(n, oh, ow)][k], k = (c, kh, kw) in that order, as [row tile][K4][128][4]; taps outside the image and the K
 // padding are zero.  One thread writes one 16-byte chunk; consecutive threads take consecutive rows (pixels).
@@ -256,60 +294,57 @@ __global__ void __launch_bounds__(256) im2col_f32_blocked_kernel(const TfIm2colA
         const int r = (int)(i & 127);
         const long long tk = i >> 7;
         const int kc = (int)(tk % p.K4);
-        const long long row = (tk / p.K4) * 128 + r;
-        float4 out = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const long long tile = tk / p.K4;
+        const long long row = tile * 128 + r;
+        float vals[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         if (row < p.rows) {
             const int ow = (int)(row % g.OW); long long t = row / g.OW;
             const int oh = (int)(t % g.OH); const int n = (int)(t / g.OH);
-            float vals[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int k = kc * 4 + j;
-                float v = 0.0f;
                 if (k < p.K) {
                     const int c = k / khw, tap = k - c * khw;
                     const int kh = tap / g.KW, kw = tap - kh * g.KW;
                     const int ih = oh * g.sh - g.pt + kh * g.dh, iw = ow * g.sw - g.pl + kw * g.dw;
-                    if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) v = round_tf32(__ldg(p.x + (((size_t)n * g.C + c) * g.H + ih) * g.W + iw));
+                    if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) vals[j] = __ldg(p.x + (((size_t)n * g.C + c) * g.H + ih) * g.W + iw);
                 }
-                vals[j] = v;
             }
-            out = make_float4(vals[0], vals[1], vals[2], vals[3]);
         }
-        reinterpret_cast<float4*>(p.a)[i] = out;
+        tf_store_chunk(p.a, tile, kc, r, p.K4, p.KC, p.parts, vals);
     }
 }
 
 // A row-major (or transposed) matrix [M][K] with element strides (sm, sk) -> blocked, rounded to TF32.
 __global__ void __launch_bounds__(256) block_matrix_f32_kernel(const float* __restrict__ x, float* __restrict__ a, long long M, int K, int K4,
-                                                               long long sm, long long sk) {
+                                                               long long sm, long long sk, int KC, int parts) {
     const long long rows_pad = (M + 127) / 128 * 128;
     const long long total = rows_pad * K4;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int r = (int)(i & 127);
         const long long tk = i >> 7;
         const int kc = (int)(tk % K4);
-        const long long row = (tk / K4) * 128 + r;
+        const long long tile = tk / K4;
+        const long long row = tile * 128 + r;
         float vals[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         if (row < M) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int k = kc * 4 + j;
-                if (k < K) vals[j] = round_tf32(__ldg(x + row * sm + (long long)k * sk));
+                if (k < K) vals[j] = __ldg(x + row * sm + (long long)k * sk);
             }
         }
-        reinterpret_cast<float4*>(a)[i] = make_float4(vals[0], vals[1], vals[2], vals[3]);
+        tf_store_chunk(a, tile, kc, r, K4, KC, parts, vals);
     }
 }
 
 // Host-side preparation of the right operand (weights) of one contraction.
 struct TfGemmPrep {
     int NT = 0, N_pad = 0, n_out = 0, K = 0, K4 = 0;
-    std::vector<float> w_blk;      // [N_pad/NT][K4][NT][4], rounded to TF32
+    int KC = 8, parts = 1;         // chunks of K per pipeline stage (8 = 32 floats; 4 in the split form); 2 parts = hi and lo
+    std::vector<float> w_blk;      // [N_pad/NT][K4/KC][parts][KC][NT][4], rounded to TF32
     std::vector<float> bias;       // [N_pad]
 };
-
-constexpr int kTfKC = 8;           // chunks per pipeline stage: 32 floats of K
 
 inline float host_round_tf32(float v) {
     uint32_t u;
@@ -322,7 +357,10 @@ inline float host_round_tf32(float v) {
 }
 
 // w(n, k) = w[n * sn + k * sk]: a convolution's [M][C][KH][KW] weight is (sn = K, sk = 1); a MatMul's B [K][N] is (1, N).
-inline void tf_gemm_prepare(const float* w, int n_out, int K, long long sn, long long sk, const float* bias, TfGemmPrep& p, long long rows = 0) {
+// `split`: the 3 x TF32 form (hi and lo parts of both operands).
+inline void tf_gemm_prepare(const float* w, int n_out, int K, long long sn, long long sk, const float* bias, TfGemmPrep& p, long long rows = 0, bool split = false) {
+    p.parts = split ? 2 : 1;
+    p.KC = split ? 4 : 8;
     p.NT = n_out <= 64 ? 64 : (n_out <= 128 ? 128 : 256);
     if (p.NT == 256 && rows > 0) {
         const long long mt = (rows + 127) / 128;
@@ -332,52 +370,65 @@ inline void tf_gemm_prepare(const float* w, int n_out, int K, long long sn, long
     p.n_out = n_out;
     p.N_pad = (n_out + p.NT - 1) / p.NT * p.NT;
     p.K = K;
-    p.K4 = (K + 4 * kTfKC - 1) / (4 * kTfKC) * kTfKC;
-    p.w_blk.assign((size_t)p.N_pad * p.K4 * 4, 0.0f);
+    p.K4 = (K + 4 * p.KC - 1) / (4 * p.KC) * p.KC;
+    p.w_blk.assign((size_t)p.N_pad * p.K4 * 4 * p.parts, 0.0f);
     p.bias.assign(p.N_pad, 0.0f);
     for (int n = 0; n < n_out; ++n) {
-        float* dst_tile = p.w_blk.data() + (size_t)(n / p.NT) * p.K4 * p.NT * 4 + (size_t)(n % p.NT) * 4;
-        for (int k = 0; k < K; ++k) dst_tile[(size_t)(k >> 2) * p.NT * 4 + (k & 3)] = host_round_tf32(w[n * sn + k * sk]);
+        float* tile = p.w_blk.data() + (size_t)(n / p.NT) * p.K4 * p.parts * p.NT * 4;
+        for (int k = 0; k < K; ++k) {
+            const int kc = k >> 2, stage = kc / p.KC, j = kc % p.KC;
+            const float v = w[n * sn + k * sk];
+            const float hi = host_round_tf32(v);
+            const size_t at = (((size_t)stage * p.parts) * p.KC + j) * p.NT * 4 + (size_t)(n % p.NT) * 4 + (k & 3);
+            tile[at] = hi;
+            if (split) tile[at + (size_t)p.KC * p.NT * 4] = host_round_tf32(v - hi);
+        }
         if (bias) p.bias[n] = bias[n];
     }
 }
 
-inline size_t tf_gemm_a_bytes(size_t rows, const TfGemmPrep& p) { return (rows + 127) / 128 * 128 * (size_t)p.K4 * 16; }
+inline size_t tf_gemm_a_bytes(size_t rows, const TfGemmPrep& p) { return (rows + 127) / 128 * 128 * (size_t)p.K4 * 16 * p.parts; }
 
-template <int NT>
+template <int NT, bool SPLIT>
 inline int32_t launch_tf_gemm(zant_ctx* ctx, const TfGemmArgs& k, int tiles) {
     constexpr int STAGES = NT == 256 ? 4 : 6;
-    using Cfg = TfGemmCfg<NT, kTfKC, STAGES>;
+    constexpr int KC = SPLIT ? 4 : 8;          // the same bytes per stage in both forms
+    using Cfg = TfGemmCfg<NT, KC, STAGES, SPLIT>;
     static bool attr_set = false;
     if (!attr_set) {
-        ZB_CUDA(cudaFuncSetAttribute(tc_gemm_tf32_kernel<NT, kTfKC, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        ZB_CUDA(cudaFuncSetAttribute(tc_gemm_tf32_kernel<NT, KC, STAGES, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set = true;
     }
-    tc_gemm_tf32_kernel<NT, kTfKC, STAGES><<<std::min(tiles, ctx->sm_count), Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
-    return check_launch(ctx, "tc_gemm_tf32_kernel");
+    tc_gemm_tf32_kernel<NT, KC, STAGES, SPLIT><<<std::min(tiles, ctx->sm_count), Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
+    return check_launch(ctx, SPLIT ? "tc_gemm_tf32_kernel<split>" : "tc_gemm_tf32_kernel");
 }
 
 // GEMM on a blocked left operand.  `ohw` > 0 stores NCHW (rows = (image, position)), 0 stores row-major [M][n_out].
 inline int32_t run_tf_gemm(zant_ctx* ctx, const TfGemmPrep& p, const float* a_blk, const float* w_blk_dev, const float* bias_dev, long long M,
                            int ohw, int act, float slope, float* y) {
     if (M <= 0) return ZANT_OK;
-    if (M > 0x7fffffffLL - 128 || p.N_pad > TfGemmCfg<64, kTfKC, 4>::MAX_N) return fail(ZANT_E_TOO_LARGE, "TF32 GEMM dimensions");
+    if (M > 0x7fffffffLL - 128 || p.N_pad > TfGemmCfg<64, 8, 4>::MAX_N) return fail(ZANT_E_TOO_LARGE, "TF32 GEMM dimensions");
     TfGemmArgs k{};
     k.a = a_blk; k.w = w_blk_dev; k.bias = bias_dev; k.y = y; k.M = (int)M; k.N = p.N_pad; k.K4 = p.K4; k.n_valid = p.n_out; k.ohw = ohw;
     k.act = act; k.slope = slope; k.status = ctx->status_word;
     const long long tiles_ll = (M + 127) / 128 * (p.N_pad / p.NT);
     if (tiles_ll > 0x7fffffffLL) return fail(ZANT_E_TOO_LARGE, "TF32 GEMM tiles");
     const int tiles = (int)tiles_ll;
-    if (p.NT == 64) return launch_tf_gemm<64>(ctx, k, tiles);
-    if (p.NT == 128) return launch_tf_gemm<128>(ctx, k, tiles);
-    return launch_tf_gemm<256>(ctx, k, tiles);
+    if (p.parts == 2) {
+        if (p.NT == 64) return launch_tf_gemm<64, true>(ctx, k, tiles);
+        if (p.NT == 128) return launch_tf_gemm<128, true>(ctx, k, tiles);
+        return launch_tf_gemm<256, true>(ctx, k, tiles);
+    }
+    if (p.NT == 64) return launch_tf_gemm<64, false>(ctx, k, tiles);
+    if (p.NT == 128) return launch_tf_gemm<128, false>(ctx, k, tiles);
+    return launch_tf_gemm<256, false>(ctx, k, tiles);
 }
 
 // Convolution (group 1, any stride / dilation / padding): im2col gather + GEMM.  `a_blk` is scratch of tf_gemm_a_bytes(N*OH*OW).
 inline int32_t run_conv_tf32(zant_ctx* ctx, const ConvGeom& g, const float* x, const TfGemmPrep& p, const float* w_blk_dev, const float* bias_dev,
                              float* a_blk, int act, float slope, float* y) {
     TfIm2colArgs ia{};
-    ia.x = x; ia.a = a_blk; ia.g = g; ia.rows = (long long)g.N * g.OH * g.OW; ia.K = p.K; ia.K4 = p.K4;
+    ia.x = x; ia.a = a_blk; ia.g = g; ia.rows = (long long)g.N * g.OH * g.OW; ia.K = p.K; ia.K4 = p.K4; ia.KC = p.KC; ia.parts = p.parts;
     if (ia.rows <= 0) return ZANT_OK;
     const long long chunks = (ia.rows + 127) / 128 * 128 * (long long)p.K4;
     im2col_f32_blocked_kernel<<<grid_for((size_t)chunks, 256, ctx->sm_count, 16), 256, 0, ctx->stream>>>(ia);
@@ -390,7 +441,7 @@ inline int32_t run_matmul_tf32(zant_ctx* ctx, const float* a, long long M, int K
                                const float* w_blk_dev, const float* bias_dev, float* a_blk, int act, float slope, float* y) {
     if (M <= 0) return ZANT_OK;
     const long long chunks = (M + 127) / 128 * 128 * (long long)p.K4;
-    block_matrix_f32_kernel<<<grid_for((size_t)chunks, 256, ctx->sm_count, 16), 256, 0, ctx->stream>>>(a, a_blk, M, K, p.K4, sm, sk);
+    block_matrix_f32_kernel<<<grid_for((size_t)chunks, 256, ctx->sm_count, 16), 256, 0, ctx->stream>>>(a, a_blk, M, K, p.K4, sm, sk, p.KC, p.parts);
     ZB_TRY(check_launch(ctx, "block_matrix_f32_kernel"));
     return run_tf_gemm(ctx, p, a_blk, w_blk_dev, bias_dev, M, 0, act, slope, y);
 }

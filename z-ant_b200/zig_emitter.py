@@ -139,3 +139,165 @@ def emit_lib(graph, model_name="model", fuse=True):
     w("    result.* = &output_buffer;")
     w("}")
     return "\n".join(L) + "\n"
+
+
+# ------------------------------------------------------------------------------------------------
+# Chain recognition (the generator-side view of what zant_b200_plan_finalize fuses)
+# ------------------------------------------------------------------------------------------------
+def fusion_groups(graph, tf32=False):
+    """Groups of consecutive nodes that the plan runs as one step: [(first node, count, label)].
+
+    The rules are those of the plan's fusion pass: QLinearConv -> [Relu | LeakyRelu | Clip on the same scale as the
+    convolution's output] -> [MaxPool 2x2, stride 2, no padding], every interior tensor read by exactly one node and not
+    the graph output; in TF32 mode also Conv -> Relu | LeakyRelu.  Whether the pool really joins the group is decided at
+    finalize time by the kernel that takes the convolution (it needs the implicit-GEMM tiling), so groups that end in
+    MaxPool are an upper bound: the plan may leave the pool as a step of its own.  The whole example CNN in QLinear form
+    (12 nodes) is recognised by the plan as four fused steps and is reported here as one group."""
+    readers = {}
+    for n in graph.nodes:
+        for t in n["inputs"]:
+            if t >= 0:
+                readers[t] = readers.get(t, 0) + 1
+
+    def only_feeds_next(t):
+        return readers.get(t, 0) == 1 and t != graph.output and graph.tensors[t]["data"] is None
+
+    def pool2x2(a):
+        return (tuple(a.get("kernel_shape", ())) == (2, 2) and tuple(a.get("strides", ())) == (2, 2) and not any(a.get("pads", (0,) * 4))
+                and tuple(a.get("dilations", (1, 1))) == (1, 1) and a.get("auto_pad") in (None, "NOTSET", "VALID"))
+
+    ops = [n["op"] for n in graph.nodes]
+    small_cnn = ["QuantizeLinear", "QLinearConv", "Relu", "MaxPool", "QLinearConv", "Relu", "MaxPool", "Reshape", "QLinearMatMul", "Relu",
+                 "QLinearMatMul", "DequantizeLinear"]
+    groups, i = [], 0
+    while i < len(graph.nodes):
+        if ops[i:i + 12] == small_cnn and graph.tensors[graph.nodes[i]["inputs"][0]]["shape"][1:] == [1, 28, 28]:
+            groups.append((i, 12, "example CNN chain: 4 fused kernels"))
+            i += 12
+            continue
+        n = graph.nodes[i]
+        j, cur, label = i + 1, n["outputs"][0], None
+        if n["op"] == "QLinearConv" and graph.tensors[cur]["dtype"] in (I8, U8):
+            label = "QLinearConv"
+            if j < len(graph.nodes) and only_feeds_next(cur):
+                a = graph.nodes[j]
+                if (a["op"] in ("Relu", "LeakyRelu", "Clip") and a["inputs"] == [cur] and a["attrs"].get("x_scale") == n["attrs"].get("y_scale")
+                        and a["attrs"].get("x_zp", 0) == n["attrs"].get("y_zp", 0)):
+                    label += "+" + a["op"]
+                    cur = a["outputs"][0]
+                    j += 1
+            if not n["attrs"].get("channels_last") and j < len(graph.nodes) and only_feeds_next(cur):
+                p = graph.nodes[j]
+                si, so = graph.tensors[cur]["shape"], graph.tensors[p["outputs"][0]]["shape"]
+                if p["op"] == "MaxPool" and p["inputs"] == [cur] and pool2x2(p["attrs"]) and len(si) == 4 and so == [si[0], si[1], si[2] // 2, si[3] // 2]:
+                    label += "+MaxPool"
+                    j += 1
+        elif tf32 and n["op"] == "Conv" and j < len(graph.nodes) and only_feeds_next(cur):
+            a = graph.nodes[j]
+            if a["op"] in ("Relu", "LeakyRelu") and a["inputs"] == [cur] and graph.tensors[a["outputs"][0]]["dtype"] == F32:
+                label = "Conv+" + a["op"]
+                j += 1
+        if label is not None and j - i > 1:
+            groups.append((i, j - i, label))
+            i = j
+        else:
+            i += 1
+    return groups
+
+
+# ------------------------------------------------------------------------------------------------
+# Reference-style emission: one tensMath call per node, as src/codeGen/math_handler.zig writes them, including the
+# operators whose emitters the reference leaves as stubs (LeakyRelu :65-66, Resize :83-84, Flatten :59-60,
+# GlobalAveragePool via ReduceMean, Add of two activations :140-156) and the quantized operators.
+# ------------------------------------------------------------------------------------------------
+def _usize_slice(vals):
+    return "&[_]usize{ " + ", ".join(str(int(v)) for v in vals) + " }"
+
+
+def _f(v):
+    return np.format_float_scientific(np.float32(v), unique=True)
+
+
+def emit_node_call(graph, node):
+    """The Zig statement (without the trailing ` catch return;`) that runs one node through the tensMath module."""
+    op, a = node["op"], node["attrs"]
+    t = lambda i: "tensor_" + _ident(graph.tensors[i]["name"])     # noqa: E731
+    ins = [t(i) if i >= 0 else None for i in node["inputs"]]
+    out = t(node["outputs"][0])
+    in_t = _ZIG_T[graph.tensors[node["inputs"][0]]["dtype"]]
+    out_t = _ZIG_T[graph.tensors[node["outputs"][0]]["dtype"]]
+    ap = a.get("auto_pad")
+    if op == "Conv":
+        bias = f"&{ins[2]}" if len(ins) > 2 and ins[2] else "null"
+        pads = _usize_slice(a["pads"]) if a.get("pads") is not None else "null"
+        dil = _usize_slice(a["dilations"]) if a.get("dilations") is not None else "null"
+        return (f'tensMath.conv_lean(T, &{ins[0]}, @constCast(&{ins[1]}), &{out}, {bias}, {_usize_slice(a.get("strides", (1,)))}, {pads}, {dil}, '
+                f'{a.get("group", 1) or 1}, {chr(34) + ap + chr(34) if ap else "null"})')
+    if op == "MatMul":
+        return f"tensMath.mat_mul_lean(T, &{ins[0]}, @constCast(&{ins[1]}), &{out})"
+    if op == "Gemm":
+        c = f"@constCast(&{ins[2]})" if len(ins) > 2 and ins[2] else "null"
+        return (f"tensMath.gemm_lean(T, &{ins[0]}, @constCast(&{ins[1]}), {c}, {_f(a.get('alpha', 1.0))}, {_f(a.get('beta', 1.0))}, "
+                f"{'true' if a.get('trans_a') else 'false'}, {'true' if a.get('trans_b') else 'false'}, &{out})")
+    if op == "MaxPool":
+        return (f"tensMath.onnx_maxpool_lean({in_t}, &{ins[0]}, &{out}, {_usize_slice(a['kernel_shape'])}, {_usize_slice(a.get('strides', (1, 1)))}, "
+                f"{_usize_slice(a.get('dilations', (1, 1)))}, {_usize_slice(a.get('pads', (0, 0, 0, 0)))}, tensMath.AutoPadType.{ap or 'NOTSET'})")
+    if op == "Relu" and in_t == "f32":
+        return f"tensMath.ReLU_lean(T, &{ins[0]}, &{out})"
+    if op == "LeakyRelu" and in_t == "f32":           # a stub in the reference's generator
+        return f"tensMath.leakyReLU_lean(T, &{ins[0]}, {_f(a['alpha'])}, &{out})"
+    if op in ("Sigmoid", "Softmax", "Tanh", "Ceil"):
+        return f"tensMath.{op.lower()}_lean(T, &{ins[0]}, &{out})"
+    if op in ("Mul", "Div"):
+        return f"tensMath.{op.lower()}_lean(T, &{ins[0]}, @constCast(&{ins[1]}), &{out})"
+    if op == "Add":                                   # also between two activations, which the reference cannot emit
+        return f"tensMath.sum_tensors_lean(T, T, &{ins[0]}, @constCast(&{ins[1]}), &{out})"
+    if op == "Concat":
+        return (f"blk: {{ const list = [_]Tensor({out_t}){{ {', '.join(ins)} }}; const r = tensMath.concatenate({out_t}, &allocator, &list, {int(a['axis'])}) catch return; "
+                f"@memcpy({out}.data, r.data); var rr = r; rr.deinit(); break :blk; }}")
+    if op == "Resize":                                # a stub in the reference's generator
+        scales = "&[_]f32{ " + ", ".join(_f(v) for v in a["scales"]) + " }"
+        return (f'blk: {{ var r = tensMath.resize({out_t}, &{ins[0]}, "nearest", {scales}, null, "{a.get("coord_mode", "half_pixel")}") catch return; '
+                f"@memcpy({out}.data, r.data); r.deinit(); break :blk; }}")
+    if op == "ReduceMean":                            # GlobalAveragePool is ReduceMean over H and W
+        axes = "&[_]i64{ " + ", ".join(str(int(v)) for v in a.get("axes", ())) + " }" if a.get("axes") else "null"
+        return (f"tensMath.reduce_mean_lean(T, &{ins[0]}, &{out}, {axes}, {'true' if a.get('keepdims', 1) else 'false'}, "
+                f"{'true' if a.get('noop_with_empty_axes') else 'false'})")
+    if op == "Reshape":                               # Flatten is a Reshape to [N, -1]
+        return f"tensMath.reshape_lean({out_t}, &{ins[0]}, {_usize_slice(graph.tensors[node['outputs'][0]]['shape'])}, false, &{out})"
+    if op == "Transpose":
+        perm = _usize_slice(a["perm"]) if a.get("perm") is not None else "null"
+        return f"tensMath.transpose_onnx_lean({out_t}, &{ins[0]}, {perm}, &{out})"
+    if op == "QuantizeLinear":
+        return f"tensMath.quantizelinear_lean({out_t}, &{ins[0]}, &scalar_f32({_f(a['y_scale'])}), &scalar({out_t}, {int(a['y_zp'])}), &{out})"
+    if op == "DequantizeLinear":
+        return f"tensMath.dequantizelinear_lean({in_t}, &{ins[0]}, &scalar_f32({_f(a['x_scale'])}), &scalar({in_t}, {int(a['x_zp'])}), &{out})"
+    if op == "QLinearConv":
+        wz = f"&{ins[3]}" if len(ins) > 3 and ins[3] else "null"
+        bias = f"&{ins[4]}" if len(ins) > 4 and ins[4] else "null"
+        return (f"tensMath.qlinearconv_lean({in_t}, {out_t}, &{ins[0]}, &scalar_f32({_f(a['x_scale'])}), &scalar({in_t}, {int(a['x_zp'])}), @constCast(&{ins[1]}), "
+                f"&{ins[2]}, {wz}, &scalar_f32({_f(a['y_scale'])}), &scalar({out_t}, {int(a['y_zp'])}), {bias}, &{out}, {_usize_slice(a.get('strides', (1, 1)))}, "
+                f"{_usize_slice(a.get('pads', (0, 0, 0, 0)))}, {_usize_slice(a.get('dilations', (1, 1)))}, {a.get('group', 1) or 1}, tensMath.AutoPadType.{ap or 'NOTSET'})")
+    if op == "QLinearMatMul":
+        wz = f"&{ins[3]}" if len(ins) > 3 and ins[3] else "null"
+        return (f"tensMath.qlinearmatmul_lean({in_t}, {out_t}, &{ins[0]}, &scalar_f32({_f(a['x_scale'])}), &scalar({in_t}, {int(a['x_zp'])}), @constCast(&{ins[1]}), "
+                f"&{ins[2]}, {wz}, &scalar_f32({_f(a['y_scale'])}), &scalar({out_t}, {int(a['y_zp'])}), &{out})")
+    raise NotImplementedError(f"no reference-style emitter for {op} on {in_t}: use the plan form (emit_lib)")
+
+
+def emit_predict_calls(graph, model_name="model"):
+    """The body of a reference-style predict(): one statement per node in graph order, each followed by ` catch return;`
+    exactly as src/codeGen/math_handler.zig:107 appends it, with the fused groups the plan form would build named in
+    comments.  Tensors are the `tensor_<name>` globals of the generated library (src/codeGen/predict.zig:110-142)."""
+    groups = {first: (count, label) for first, count, label in fusion_groups(graph)}
+    lines = [f"// predict() body of {model_name}: {len(graph.nodes)} nodes, reference-style calls into the tensMath module"]
+    i = 0
+    while i < len(graph.nodes):
+        if i in groups:
+            count, label = groups[i]
+            lines.append(f"    // nodes {i}..{i + count - 1} form one fused step in the plan form: {label}")
+        n = graph.nodes[i]
+        call = emit_node_call(graph, n)
+        lines.append(f"    {call}{'' if call.startswith('blk:') else ' catch return;'}  // {n['op']}")
+        i += 1
+    return "\n".join(lines) + "\n"
