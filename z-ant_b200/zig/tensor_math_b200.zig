@@ -436,3 +436,35 @@ pub fn qlinearconv_lean(comptime XT: type, comptime YT: type, x: *Tensor(XT), x_
 pub fn qlinearmatmul_lean(comptime AT: type, comptime YT: type, a: *Tensor(AT), a_scale: *const Tensor(f32), a_zero_point: *const Tensor(AT), b: *Tensor(i8), b_scale: *const Tensor(f32), b_zero_point: ?*const Tensor(i32), y_scale: *const Tensor(f32), y_zero_point: *const Tensor(YT), output: *Tensor(YT)) !void {
     try check(zant_b200_qlinearmatmul(context(), dtypeOf(AT), a.data.ptr, a.shape.ptr, a.shape.len, a_scale.data[0], @intCast(a_zero_point.data[0]), b.data.ptr, b.shape.ptr, b.shape.len, b_scale.data.ptr, if (b_zero_point) |z| z.data.ptr else null, b_scale.size, y_scale.data[0], @intCast(y_zero_point.data[0]), null, 0, dtypeOf(YT), output.data.ptr, output.shape.ptr, output.shape.len, 0));
 }
+
+extern fn zant_b200_lut_q8(ctx: ?*Ctx, x: *const anyopaque, lut: *const [256]u8, y: *anyopaque, n: usize) i32;
+
+pub const QActivation = enum { relu, leaky_relu, clip };
+
+/// Relu / LeakyRelu / Clip between two quantized tensors (QDQ graphs): dequantise, activate, requantise,
+///   y = sat(rne(f(float(q - x_zp) * x_scale) / y_scale) + y_zp),
+/// evaluated once per code into a 256-entry table on the host and applied on the device.  `alpha` is the LeakyRelu
+/// slope or the Clip minimum, `beta` the Clip maximum.  No reference counterpart (the reference has no quantized ops).
+pub fn qlinear_activation_lean(comptime T: type, input: *Tensor(T), x_scale: f32, x_zp: i32, kind: QActivation, alpha: f32, beta: f32, y_scale: f32, y_zp: i32, output: *Tensor(T)) !void {
+    comptime std.debug.assert(T == i8 or T == u8);
+    var lut: [256]u8 = undefined;
+    const lo: i32 = if (T == u8) 0 else -128;
+    const hi: i32 = if (T == u8) 255 else 127;
+    for (0..256) |code| {
+        const q: i32 = if (T == u8) @intCast(code) else @as(i32, @as(i8, @bitCast(@as(u8, @intCast(code)))));
+        const x: f32 = @as(f32, @floatFromInt(q - x_zp)) * x_scale;
+        const a: f32 = switch (kind) {
+            .relu => if (x > 0) x else 0,
+            .leaky_relu => if (x <= 0) alpha * x else x,
+            .clip => @min(@max(x, alpha), beta),
+        };
+        const v: f32 = @min(@max(a / y_scale, -512.0), 511.0);
+        // @round is half-away-from-zero; the back end rounds half to even
+        var r: f32 = @floor(v);
+        const d = v - r;
+        if (d > 0.5 or (d == 0.5 and @mod(r, 2.0) != 0)) r += 1;
+        const t: i32 = @min(@max(@as(i32, @intFromFloat(r)) + y_zp, lo), hi);
+        lut[code] = @bitCast(@as(i8, @truncate(t)));
+    }
+    try check(zant_b200_lut_q8(context(), input.data.ptr, &lut, output.data.ptr, input.size));
+}

@@ -246,6 +246,10 @@ def emit_node_call(graph, node):
         return f"tensMath.ReLU_lean(T, &{ins[0]}, &{out})"
     if op == "LeakyRelu" and in_t == "f32":           # a stub in the reference's generator
         return f"tensMath.leakyReLU_lean(T, &{ins[0]}, {_f(a['alpha'])}, &{out})"
+    if op in ("Relu", "LeakyRelu", "Clip"):          # between two quantized tensors: requantising activation
+        kind = {"Relu": ".relu", "LeakyRelu": ".leaky_relu", "Clip": ".clip"}[op]
+        return (f"tensMath.qlinear_activation_lean({in_t}, &{ins[0]}, {_f(a['x_scale'])}, {int(a['x_zp'])}, {kind}, {_f(a.get('alpha', 0.0))}, "
+                f"{_f(a.get('beta', 0.0))}, {_f(a['y_scale'])}, {int(a['y_zp'])}, &{out})")
     if op in ("Sigmoid", "Softmax", "Tanh", "Ceil"):
         return f"tensMath.{op.lower()}_lean(T, &{ins[0]}, &{out})"
     if op in ("Mul", "Div"):
