@@ -140,7 +140,7 @@ int32_t zant_b200_ctx_set_stream(zant_ctx* ctx, void* cuda_stream);
  * the reference's order of operations (sequential fp32 accumulation, op_mat_mul.zig:132-148) and are bit-identical
  * to it.  1: tensor-core kernels (tcgen05 kind::tf32, operands rounded to TF32, fp32 accumulation), one MMA per K step;
  * the error of an output is about 3e-4 of the root sum of squares of its products: within 2e-3 of the output's scale,
- * |y - ref| <= 2e-3 * max(|ref|, 1e-1 * max|ref|), but not relative to outputs that are near-cancellations.  2: the
+ * |y - ref| <= 2e-3 * max|ref|, but not relative to outputs that are near-cancellations.  2: the
  * same kernels with every operand split into two TF32 parts (three MMAs per K step), which recovers about 21 bits of the
  * products: within |y - ref| <= 2e-3 * max(|ref|, 1e-2 * max|ref|) with a wide margin (in practice within the 1e-4 rule
  * of the FP32 path), at about half the speed of mode 1.  A plan takes the setting of its context when it is finalized;

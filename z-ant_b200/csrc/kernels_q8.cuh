@@ -60,6 +60,10 @@ struct Requant {
 };
 
 __device__ __forceinline__ int lut1(const uint8_t* lut, int code) { return (int)__ldg(lut + (code & 255)); }
+// the same from a copy of the table in shared memory (64 words over 32 banks: cheap next to divergent global loads)
+__device__ __forceinline__ uint32_t lut4_smem(const uint8_t* lut, uint32_t pk) {
+    return (uint32_t)lut[pk & 255u] | ((uint32_t)lut[(pk >> 8) & 255u] << 8) | ((uint32_t)lut[(pk >> 16) & 255u] << 16) | ((uint32_t)lut[pk >> 24] << 24);
+}
 // four packed codes through the table
 __device__ __forceinline__ uint32_t lut4(const uint8_t* lut, uint32_t pk) {
     return (uint32_t)__ldg(lut + (pk & 255u)) | ((uint32_t)__ldg(lut + ((pk >> 8) & 255u)) << 8) |

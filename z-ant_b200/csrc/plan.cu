@@ -659,13 +659,15 @@ static int32_t build_node_impl(zant_plan* pl, size_t node_index, int32_t /*fuse*
                 auto prep = std::make_shared<TfGemmPrep>();
                 const int K = g.C * g.KH * g.KW;
                 tf_gemm_prepare((const float*)T(w).host.data(), g.M, K, K, 1, b >= 0 ? (const float*)T(b).host.data() : nullptr, *prep, (long long)g.N * g.OH * g.OW, ctx->tf32 == 2);
+                tf_conv_table(g, *prep);
                 const int aw = pl->add_aux(prep->w_blk.data(), prep->w_blk.size() * 4), ab = pl->add_aux(prep->bias.data(), prep->bias.size() * 4);
+                const int at = pl->add_aux(prep->ktab.data(), prep->ktab.size() * 4);
                 const int sa = pl->shared_im2col_scratch(tf_gemm_a_bytes((size_t)g.N * g.OH * g.OW, *prep));
                 prep->w_blk.clear(); prep->w_blk.shrink_to_fit();
                 const int fact = pl->pending_fact; const float fslope = pl->pending_slope;
                 const int yw = pl->pending_y >= 0 ? pl->pending_y : y;
                 push(fact == FACT_NONE ? "Conv(tf32)" : (fact == FACT_RELU ? "Conv(tf32)+Relu" : "Conv(tf32)+LeakyRelu"), [=]() {
-                    return run_conv_tf32(ctx, g, pl->p<float>(x), *prep, (const float*)pl->aux(aw), (const float*)pl->aux(ab), (float*)pl->scratch(sa), fact, fslope, pl->p<float>(yw));
+                    return run_conv_tf32(ctx, g, pl->p<float>(x), *prep, (const float*)pl->aux(aw), (const float*)pl->aux(ab), (const int32_t*)pl->aux(at), (float*)pl->scratch(sa), fact, fslope, pl->p<float>(yw));
                 });
                 pl->pending_used = true;
                 return ZANT_OK;

@@ -67,6 +67,8 @@ __device__ __forceinline__ void mma_m16n8k16_s8(int (&d)[4], uint32_t a0, uint32
 template <int MT, int NTL, bool XU8, bool LEAN>
 __global__ void __launch_bounds__(kSmallcThreads) qconv3x3_smallc_kernel(const SmallcArgs a) {
     extern __shared__ __align__(16) uint8_t s_in[];      // [C][RIN][P]
+    __shared__ uint8_t s_lut[256];                       // copy of the optional activation table
+    if (a.lut) for (int i = threadIdx.x; i < 256; i += blockDim.x) s_lut[i] = __ldg(a.lut + i);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     constexpr int PXU = 8 * NTL;
@@ -160,7 +162,7 @@ __global__ void __launch_bounds__(kSmallcThreads) qconv3x3_smallc_kernel(const S
                                                    tc_conv_round<true>(v2, mult[mt][h]), tc_conv_round<true>(v3, mult[mt][h]));
                             if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
                             if (a.act == ZANT_QACT_RELU6) pk = __vmins4(pk, six4);
-                            if (a.lut) pk = lut4(a.lut, pk);
+                            if (a.lut) pk = lut4_smem(s_lut, pk);
                             wd[p] = pk;
                         } else {
                             const int q0 = a.out_u8 ? requant_one<true>(v0, mult[mt][h], rq) : requant_one<false>(v0, mult[mt][h], rq);

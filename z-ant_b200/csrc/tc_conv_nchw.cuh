@@ -82,7 +82,7 @@ constexpr int kTcConvMaxStages = 6;
 constexpr int kTcConvMaxFilters = 1024;
 constexpr int kTcConvThreads = 576;                             // 2 + 8 producer + 8 epilogue warps
 constexpr int kTcConvOutPitch = 128;                            // bytes per filter in the output staging buffer
-constexpr int kTcConvTail = 2 * kTcConvMaxFilters * 4 + 512;   // constants + barriers after the stages
+constexpr int kTcConvTail = 2 * kTcConvMaxFilters * 4 + 512 + 256;   // constants + barriers + the activation table after the stages
 
 // out[p] = bytes (a[p], b[p], c[p], d[p]) for p = 0..3
 __device__ __forceinline__ void transpose_4x4_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t out[4]) {
@@ -112,8 +112,7 @@ __device__ unsigned long long g_tc_conv_timers[256 * 32];
 
 // Requantisation of the lean epilogue: rq_round (the float-to-int conversion saturates at the int32 range and
 // the saturating pack that follows clamps to int8, which equals the reference's clamp for zero point 0).  Both
-// CLAMP instantiations are the same code; an earlier form rounded on the FMA pipe by adding 1.5 * 2^23 (with a
-// clamp first when products could reach 2^22), which measured 2-4 % slower than the conversion on this part.
+// CLAMP instantiations are the same code.
 template <bool CLAMP>
 __device__ __forceinline__ int tc_conv_round(int acc, float m) { return rq_round(acc, m); }
 
@@ -177,6 +176,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 2 * kTcConvMaxFilters * 4 + 400);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 2 * kTcConvMaxFilters * 4 + 404);
     volatile int* epi_ok = reinterpret_cast<volatile int*>(tail + 2 * kTcConvMaxFilters * 4 + 408);
+    uint8_t* sLut = tail + 2 * kTcConvMaxFilters * 4 + 512;
     const uint32_t bar0 = ptx::smem_u32(bars);
     const int S = a.stages;
     auto full = [&](int s) { return bar0 + 8u * s; };
@@ -203,6 +203,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         ptx::mbar_fence_init();
     }
     for (int i = tid; i < a.m_pad; i += kTcConvThreads) { sMult[i] = __ldg(a.mult + i); sBias[i] = __ldg(a.bias + i); }
+    if (a.lut && tid < 256) sLut[tid] = __ldg(a.lut + tid);
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), 2 * a.RB * NT);
         ptx::tmem_relinquish();
@@ -567,7 +568,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                             uint32_t w4 = pack_sat_s8x4(q0, q1, q2, q3);
                             if (a.act != ZANT_QACT_NONE) w4 = relu_s8x4(w4);
                             if (a.act == ZANT_QACT_RELU6) w4 = __vmins4(w4, six4);
-                            if (a.lut) w4 = lut4(a.lut, w4);
+                            if (a.lut) w4 = lut4_smem(sLut, w4);
                             pk[j4] = w4;
                         }
                     };

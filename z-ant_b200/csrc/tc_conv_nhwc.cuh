@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2 * kTcConvMaxFilters * 4);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 2 * kTcConvMaxFilters * 4 + 400);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 2 * kTcConvMaxFilters * 4 + 404);
+    uint8_t* sLut = tail + 2 * kTcConvMaxFilters * 4 + 512;          // copy of the optional activation table
     const uint32_t bar0 = ptx::smem_u32(bars);
     const int S = a.stages;
     auto full = [&](int s) { return bar0 + 8u * s; };
@@ -84,6 +85,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
         ptx::mbar_fence_init();
     }
     for (int i = tid; i < a.m_pad; i += kTcConvThreads) { sMult[i] = __ldg(a.mult + i); sBias[i] = __ldg(a.bias + i); }
+    if (a.lut && tid < 256) sLut[tid] = __ldg(a.lut + tid);
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), 2 * a.RB * NT);
         ptx::tmem_relinquish();
@@ -245,7 +247,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
                                                             tc_conv_round<CL>((int)v[j4 * 4 + 2] + b4.z, m4.z), tc_conv_round<CL>((int)v[j4 * 4 + 3] + b4.w, m4.w));
                                 if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
                                 if (a.act == ZANT_QACT_RELU6) pk = __vmins4(pk, six4);
-                                if (a.lut) pk = lut4(a.lut, pk);
+                                if (a.lut) pk = lut4_smem(sLut, pk);
                                 wd[j4] = pk;
                             }
                         };

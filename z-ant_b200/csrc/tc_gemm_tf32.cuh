@@ -261,6 +261,8 @@ struct TfIm2colArgs {
     long long rows;        // N * OH * OW
     int K, K4;             // K = Cg * KH * KW (reference order c, kh, kw); K4 chunks including padding
     int KC, parts;         // chunks per pipeline stage; 1 = rounded operand only, 2 = hi and lo parts
+    const int2* ktab;      // [K4 * 4]: x = element offset of tap k from the patch origin (c*H*W + kh*dh*W + kw*dw),
+                           //           y = kh*dh | kw*dw << 16, or -1 for the K padding
 };
 
 // Where chunk `kc` (part `part`) of row `r` of row tile `tile` lives, in float4 units: [tile][stage][part][KC][128]
@@ -282,36 +284,38 @@ __device__ __forceinline__ void tf_store_chunk(float* a, long long tile, int kc,
     }
 }
 
-// A[(n, oh, ow)][k], k = (c, kh, kw) in that order, as [row tile][K4][128][4]; taps outside the image and the K
-// padding are zero.  One thread writes one 16-byte chunk; consecutive threads take consecutive rows (pixels).
+// A[(n, oh, ow)][k], k = (c, kh, kw) in that order, in the blocked layout; taps outside the image and the K padding
+// are zero.  One CTA per row tile: a thread owns one of the tile's 128 rows (its pixel is decoded once) and walks the
+// K chunks; where each k reads is a table built on the host (no division in the loop).  A warp's 32 lanes read 32
+// consecutive pixels of one tap and write 512 contiguous bytes.
 __global__ void __launch_bounds__(256) im2col_f32_blocked_kernel(const TfIm2colArgs p) {
     const ConvGeom& g = p.g;
-    const long long rows_pad = (p.rows + 127) / 128 * 128;
-    const long long total = rows_pad * p.K4;
-    const int khw = g.KH * g.KW;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        // i = (tile * K4 + kc) * 128 + r
-        const int r = (int)(i & 127);
-        const long long tk = i >> 7;
-        const int kc = (int)(tk % p.K4);
-        const long long tile = tk / p.K4;
+    const int tid = threadIdx.x, r = tid & 127;
+    const long long n_tiles = (p.rows + 127) / 128;
+    const long long plane = (long long)g.H * g.W;
+    for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const long long row = tile * 128 + r;
-        float vals[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (row < p.rows) {
-            const int ow = (int)(row % g.OW); long long t = row / g.OW;
-            const int oh = (int)(t % g.OH); const int n = (int)(t / g.OH);
+        const bool row_ok = row < p.rows;
+        int ih0 = 0, iw0 = 0;
+        long long base = 0;
+        if (row_ok) {
+            const int ow = (int)(row % g.OW); const long long t = row / g.OW;
+            const int oh = (int)(t % g.OH); const long long n = t / g.OH;
+            ih0 = oh * g.sh - g.pt; iw0 = ow * g.sw - g.pl;
+            base = n * g.C * plane + (long long)ih0 * g.W + iw0;
+        }
+        for (int kc = tid >> 7; kc < p.K4; kc += 2) {
+            float vals[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int k = kc * 4 + j;
-                if (k < p.K) {
-                    const int c = k / khw, tap = k - c * khw;
-                    const int kh = tap / g.KW, kw = tap - kh * g.KW;
-                    const int ih = oh * g.sh - g.pt + kh * g.dh, iw = ow * g.sw - g.pl + kw * g.dw;
-                    if (ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) vals[j] = __ldg(p.x + (((size_t)n * g.C + c) * g.H + ih) * g.W + iw);
+                for (int j = 0; j < 4; ++j) {
+                    const int2 e = __ldg(p.ktab + kc * 4 + j);            // the same entry for the whole warp
+                    const int dy = e.y & 0xffff, dx = e.y >> 16;
+                    if (e.y >= 0 && (unsigned)(ih0 + dy) < (unsigned)g.H && (unsigned)(iw0 + dx) < (unsigned)g.W) vals[j] = __ldg(p.x + base + e.x);
                 }
             }
+            tf_store_chunk(p.a, tile, kc, r, p.K4, p.KC, p.parts, vals);
         }
-        tf_store_chunk(p.a, tile, kc, r, p.K4, p.KC, p.parts, vals);
     }
 }
 
@@ -344,6 +348,7 @@ struct TfGemmPrep {
     int KC = 8, parts = 1;         // chunks of K per pipeline stage (8 = 32 floats; 4 in the split form); 2 parts = hi and lo
     std::vector<float> w_blk;      // [N_pad/NT][K4/KC][parts][KC][NT][4], rounded to TF32
     std::vector<float> bias;       // [N_pad]
+    std::vector<int32_t> ktab;     // convolutions: [K4 * 4][2], where each k of the im2col row reads (see TfIm2colArgs)
 };
 
 inline float host_round_tf32(float v) {
@@ -387,6 +392,17 @@ inline void tf_gemm_prepare(const float* w, int n_out, int K, long long sn, long
     }
 }
 
+// The gather table of a convolution's im2col rows: k = (c, kh, kw) in the weight tensor's order.
+inline void tf_conv_table(const ConvGeom& g, TfGemmPrep& p) {
+    p.ktab.assign((size_t)p.K4 * 4 * 2, -1);
+    const int khw = g.KH * g.KW;
+    for (int k = 0; k < p.K; ++k) {
+        const int c = k / khw, tap = k % khw, kh = tap / g.KW, kw = tap % g.KW;
+        p.ktab[2 * k] = c * g.H * g.W + kh * g.dh * g.W + kw * g.dw;
+        p.ktab[2 * k + 1] = (kh * g.dh) | ((kw * g.dw) << 16);
+    }
+}
+
 inline size_t tf_gemm_a_bytes(size_t rows, const TfGemmPrep& p) { return (rows + 127) / 128 * 128 * (size_t)p.K4 * 16 * p.parts; }
 
 template <int NT, bool SPLIT>
@@ -426,12 +442,14 @@ inline int32_t run_tf_gemm(zant_ctx* ctx, const TfGemmPrep& p, const float* a_bl
 
 // Convolution (group 1, any stride / dilation / padding): im2col gather + GEMM.  `a_blk` is scratch of tf_gemm_a_bytes(N*OH*OW).
 inline int32_t run_conv_tf32(zant_ctx* ctx, const ConvGeom& g, const float* x, const TfGemmPrep& p, const float* w_blk_dev, const float* bias_dev,
-                             float* a_blk, int act, float slope, float* y) {
+                             const int32_t* ktab_dev, float* a_blk, int act, float slope, float* y) {
     TfIm2colArgs ia{};
     ia.x = x; ia.a = a_blk; ia.g = g; ia.rows = (long long)g.N * g.OH * g.OW; ia.K = p.K; ia.K4 = p.K4; ia.KC = p.KC; ia.parts = p.parts;
     if (ia.rows <= 0) return ZANT_OK;
-    const long long chunks = (ia.rows + 127) / 128 * 128 * (long long)p.K4;
-    im2col_f32_blocked_kernel<<<grid_for((size_t)chunks, 256, ctx->sm_count, 16), 256, 0, ctx->stream>>>(ia);
+    ia.ktab = reinterpret_cast<const int2*>(ktab_dev);
+    if ((long long)g.C * g.H * g.W > 0x7fffffffLL || g.KH * g.dh > 0x7fff || g.KW * g.dw > 0x7fff) return fail(ZANT_E_TOO_LARGE, "convolution geometry exceeds the gather table's range");
+    const long long n_tiles = (ia.rows + 127) / 128;
+    im2col_f32_blocked_kernel<<<(unsigned)std::min<long long>(n_tiles, (long long)ctx->sm_count * 16), 256, 0, ctx->stream>>>(ia);
     ZB_TRY(check_launch(ctx, "im2col_f32_blocked_kernel"));
     return run_tf_gemm(ctx, p, a_blk, w_blk_dev, bias_dev, ia.rows, g.OH * g.OW, act, slope, y);
 }
