@@ -99,7 +99,9 @@ def test_tiny_yolo_fp32_in_tf32_mode(zb, tctx, oracle, res, batch):
     want = graph_oracle.run(oracle, g, x)
     plan = zb.Plan(tctx, g)
     names = plan.step_names()
-    assert "Conv(tf32)+LeakyRelu" in names and "LeakyRelu" not in names
+    assert "Conv(tf32)+LeakyRelu" in names
+    if res == 416:
+        assert "LeakyRelu" not in names and "Conv" not in names      # at 96 x 96 the deepest layers have too few pixels for a tile and stay exact
     got = plan.run(x)
     for name, out, ref in (("head26", got, want[g.output]), ("head13", plan.read_tensor(g.meta["head13"]), want[g.meta["head13"]])):
         ok, worst = within_tf32(out, ref, tctx.mode, floor=1e-1 if (tctx.mode == 2 and res == 416) else None)
