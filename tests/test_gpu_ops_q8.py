@@ -388,3 +388,17 @@ def test_fused_cnn_input_quantisation_on_rounding_boundaries(zb, ctx, oracle):
     assert any("Fused" in n for n in plan.step_names())
     assert np.array_equal(plan.run(x).view(np.uint32), want.view(np.uint32))
     plan.close()
+
+
+@pytest.mark.parametrize("dt,a_s,a_zp,b_s,b_zp,y_s,y_zp,act", [
+    (I8, 0.031, 0, 0.017, -4, 0.045, 0, None), (U8, 0.031, 120, 0.017, 117, 0.045, 120, "relu"), (I8, 0.1, 0, 0.1, 0, 0.1, 0, None),
+    (I8, 0.05, 3, 0.025, -7, 0.0125, 5, "relu6"), (I8, 0.047244094, 0, 0.1, 0, 0.1, 0, None), (U8, 0.02, 0, 0.02, 255, 0.01, 7, None)])
+def test_qlinearadd_every_code_pair(ctx, oracle, dt, a_s, a_zp, b_s, b_zp, y_s, y_zp, act):
+    """All 65536 pairs of codes: the vector kernel takes the division only where a multiply cannot prove the rounding (exact
+    halves are common here: equal scales, scale ratios of two)."""
+    codes = np.arange(256, dtype=np.uint8).view(np.int8 if dt == I8 else np.uint8)
+    a = np.repeat(codes, 256).reshape(1, 256, 16, 16)
+    b = np.tile(codes, 256).reshape(1, 256, 16, 16)
+    got = ctx.qlinearadd(a, a_s, a_zp, b, b_s, b_zp, y_s, y_zp, act)
+    want = oracle.qlinearadd(a, a_s, a_zp, b, b_s, b_zp, y_s, y_zp, act)
+    assert np.array_equal(got, want)

@@ -226,6 +226,40 @@ __global__ void qadd_k(const void* __restrict__ a, float a_s, int a_zp, const vo
     }
 }
 
+// The same, sixteen values per thread (16-byte loads and stores); the division by y_s goes through quantize_fast, which
+// proves the rounding from a multiply and a residual and divides only where it cannot.  Requires 16-byte aligned buffers
+// and a y_zp inside the type's range; the tail (n % 16 values) is left to qadd_k.
+template <bool U8>
+__global__ void __launch_bounds__(256) qadd_vec_k(const uint4* __restrict__ a, float a_s, int a_zp, const uint4* __restrict__ b, float b_s, int b_zp,
+                                                  float y_s, int y_zp, int act, uint4* __restrict__ y, size_t n16) {
+    const int t_lo = U8 ? 0 : -128, t_hi = U8 ? 255 : 127;
+    const QuantFast qf = quant_fast(y_s, (float)(t_lo - y_zp), (float)(t_hi - y_zp));
+    const int lo = sat_q<U8>(y_zp);
+    const int six = sat_q<U8>(rne_clamped(__fdiv_rn(6.0f, y_s)) + y_zp);
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 va = __ldg(a + i), vb = __ldg(b + i);
+        const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+        uint32_t out[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            uint32_t pk = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int qa = U8 ? (int)((wa[w] >> (8 * j)) & 255u) : (int)(int8_t)(wa[w] >> (8 * j));
+                const int qb = U8 ? (int)((wb[w] >> (8 * j)) & 255u) : (int)(int8_t)(wb[w] >> (8 * j));
+                const float fa = __fmul_rn(__int2float_rn(qa - a_zp), a_s);
+                const float fb = __fmul_rn(__int2float_rn(qb - b_zp), b_s);
+                int t = quantize_fast(__fadd_rn(fa, fb), qf) + y_zp;
+                if (act != ZANT_QACT_NONE) t = max(t, lo);
+                if (act == ZANT_QACT_RELU6) t = min(t, six);
+                pk |= (uint32_t)(t & 255) << (8 * j);
+            }
+            out[w] = pk;
+        }
+        y[i] = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+}
+
 // ---------------------------------------------------------------------------- Quantized GlobalAveragePool
 // One warp per (n,c) plane: exact int32 sum by shuffle reduction (integer addition is
 // associative, so the order is free), then the three rounded fp32 steps.

@@ -238,9 +238,23 @@ inline int32_t run_qmatmul_generic(zant_ctx* ctx, const QMatArgs& p, int32_t a_d
 inline int32_t run_qadd(zant_ctx* ctx, int32_t dtype, const void* a, float a_s, int a_zp, const void* b, float b_s, int b_zp,
                         float y_s, int y_zp, int act, void* y, size_t n) {
     if (n == 0) return ZANT_OK;
-    const int grid = grid_for(n, 256, ctx->sm_count);
-    if (dtype == ZANT_U8) qadd_k<true><<<grid, 256, 0, ctx->stream>>>(a, a_s, a_zp, b, b_s, b_zp, y_s, y_zp, act, y, n);
-    else qadd_k<false><<<grid, 256, 0, ctx->stream>>>(a, a_s, a_zp, b, b_s, b_zp, y_s, y_zp, act, y, n);
+    const bool u8 = dtype == ZANT_U8;
+    const bool zp_ok = u8 ? (y_zp >= 0 && y_zp <= 255) : (y_zp >= -128 && y_zp <= 127);
+    size_t done = 0;
+    if (zp_ok && n >= 16 && aligned16(a) && aligned16(b) && aligned16(y)) {
+        const size_t n16 = n / 16;
+        const int grid = grid_for(n16, 256, ctx->sm_count);
+        if (u8) qadd_vec_k<true><<<grid, 256, 0, ctx->stream>>>((const uint4*)a, a_s, a_zp, (const uint4*)b, b_s, b_zp, y_s, y_zp, act, (uint4*)y, n16);
+        else qadd_vec_k<false><<<grid, 256, 0, ctx->stream>>>((const uint4*)a, a_s, a_zp, (const uint4*)b, b_s, b_zp, y_s, y_zp, act, (uint4*)y, n16);
+        ZB_TRY(check_launch(ctx, "qadd_vec_k"));
+        done = n16 * 16;
+        if (done == n) return ZANT_OK;
+    }
+    const char* pa = (const char*)a + done; const char* pb = (const char*)b + done; char* py = (char*)y + done;
+    const size_t rest = n - done;
+    const int grid = grid_for(rest, 256, ctx->sm_count);
+    if (u8) qadd_k<true><<<grid, 256, 0, ctx->stream>>>(pa, a_s, a_zp, pb, b_s, b_zp, y_s, y_zp, act, py, rest);
+    else qadd_k<false><<<grid, 256, 0, ctx->stream>>>(pa, a_s, a_zp, pb, b_s, b_zp, y_s, y_zp, act, py, rest);
     return check_launch(ctx, "qadd_k");
 }
 

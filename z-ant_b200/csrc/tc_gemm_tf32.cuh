@@ -213,27 +213,28 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_tf32_kernel(const __grid_const
                 col_stride = 1;
             }
 #pragma unroll 1
-            for (int h = 0; h < Cfg::COLS_PER_WARP / 32; ++h) {
-                uint32_t v[32];
-                ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
+            for (int h = 0; h < Cfg::COLS_PER_WARP / 16; ++h) {
+                const int col0 = n * NT + tcol0 + h * 16;
+                if (col0 >= a.n_valid) break;                      // column padding of the last tile: nothing to compute or store
+                uint32_t v[16];
+                ptx::tmem_ld16(taddr + (uint32_t)(h * 16), v);
                 ptx::tmem_wait_ld();
-                const int col0 = n * NT + tcol0 + h * 32;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
+                for (int j = 0; j < 16; ++j) {
                     float r = __fadd_rn(__uint_as_float(v[j]), sBias[col0 + j]);
                     if (a.act == FACT_RELU) r = r > 0.0f ? r : 0.0f;
                     else if (a.act == FACT_LEAKY) r = r <= 0.0f ? __fmul_rn(a.slope, r) : r;
                     v[j] = __float_as_uint(r);
                 }
                 if (!row_ok) continue;
-                if (a.ohw == 0 && (a.n_valid & 3) == 0 && col0 + 32 <= a.n_valid) {
-                    // row-major: the lane's 32 columns are contiguous (rows start at multiples of 16 bytes)
+                if (a.ohw == 0 && (a.n_valid & 3) == 0 && col0 + 16 <= a.n_valid) {
+                    // row-major: the lane's 16 columns are contiguous (rows start at multiples of 16 bytes)
                     uint4* dst = reinterpret_cast<uint4*>(ybase + col0);
 #pragma unroll
-                    for (int j4 = 0; j4 < 8; ++j4) dst[j4] = make_uint4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
+                    for (int j4 = 0; j4 < 4; ++j4) dst[j4] = make_uint4(v[4 * j4], v[4 * j4 + 1], v[4 * j4 + 2], v[4 * j4 + 3]);
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
+                    for (int j = 0; j < 16; ++j)
                         if (col0 + j < a.n_valid) ybase[(size_t)(col0 + j) * col_stride] = __uint_as_float(v[j]);
                 }
             }
@@ -266,9 +267,11 @@ struct TfIm2colArgs {
 };
 
 // Where chunk `kc` (part `part`) of row `r` of row tile `tile` lives, in float4 units: [tile][stage][part][KC][128]
+// (KC is 4 or 8: shifts instead of divisions)
 __device__ __forceinline__ long long tf_chunk_index(long long tile, int kc, int part, int r, int K4, int KC, int parts) {
-    const int stage = kc / KC, j = kc - stage * KC;
-    return ((tile * (K4 / KC) + stage) * parts + part) * (long long)KC * 128 + (long long)j * 128 + r;
+    const int sh = KC == 8 ? 3 : 2;
+    const int stage = kc >> sh, j = kc & (KC - 1);
+    return (((tile * (K4 >> sh) + stage) * parts + part) << (sh + 7)) + (j << 7) + r;
 }
 
 __device__ __forceinline__ void tf_store_chunk(float* a, long long tile, int kc, int r, int K4, int KC, int parts, const float v[4]) {
