@@ -392,3 +392,18 @@ def test_movement_operators_in_a_plan(zb, ctx, oracle):
     ref = np.take(np.transpose(xin, (0, 2, 3, 1))[:, 1:3, :, 0:6:2], np.array([[2, 0], [1, 1]]), axis=2)
     assert np.array_equal(want[y], ref)
     plan.close()
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 8, 8), (1, 5, 26, 28), (3, 2, 6, 12), (1, 1, 2, 4)])
+def test_maxpool_2x2_stride2_float_fast_path(ctx, oracle, shape):
+    """The vector form of the 2x2 / stride-2 pool on float planes whose rows are whole float4s, with NaNs and infinities in
+    the windows: the reference's comparison chain skips NaNs and starts at -inf."""
+    x = rnd(np.random.default_rng(sum(shape)), shape)
+    flat = x.reshape(-1)
+    flat[::7] = np.nan
+    flat[3::11] = -np.inf
+    flat[5::13] = np.inf
+    x[0, 0, 0:2, 0:2] = np.nan                        # a window of NaNs only
+    k, s, d, p = (2, 2), (2, 2), (1, 1), (0, 0, 0, 0)
+    got, want = ctx.onnx_maxpool(x, k, s, d, p, "NOTSET", False), oracle.onnx_maxpool(x, k, s, d, p, "NOTSET", False)
+    assert got.shape == want.shape and np.array_equal(got.view(np.uint32), want.view(np.uint32))

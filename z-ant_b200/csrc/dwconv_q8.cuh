@@ -86,32 +86,75 @@ __device__ __forceinline__ uint32_t dw_load_unaligned(const QDwArgs& p, long lon
     return v;
 }
 
-template <int STRIDE, bool XU8, bool LEAN, bool ALIGNED>
+// SMEM: for planes whose rows are not whole words (W % 4 != 0: 14 x 14, 7 x 7, odd sizes).  The CTA's planes (8 warps x
+// planes per warp, consecutive in memory) are first copied into shared memory with rows padded to whole 8-byte groups
+// (pad bytes = the input zero point), the sliding-row arithmetic then reads aligned words from there and writes its
+// packed output words into a padded output image in shared memory, and a last phase copies the output rows out.  Global
+// memory is touched by row-wise byte copies of consecutive rows only; the arithmetic is that of the aligned form.
+template <int STRIDE, bool XU8, bool LEAN, bool ALIGNED, bool SMEM = false>
 __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
+    extern __shared__ __align__(16) uint8_t dw_smem[];
     const int lane = threadIdx.x & 31;
     const int LW = 1 << p.log2LW;
     const int ppw = 32 >> p.log2LW;                          // planes per warp
     const int sub = lane >> p.log2LW, col = lane & (LW - 1);
     const int warps = (gridDim.x * blockDim.x) >> 5;
     const int groups = (p.planes + ppw - 1) / ppw;
-    const int in_words = p.W >> 2;                           // 4-byte words per input row
+    const int Wp = SMEM ? (p.W + 7) / 8 * 8 : p.W;           // padded row pitches of the shared-memory images
+    const int OWp = SMEM ? (p.OW + 3) / 4 * 4 : p.OW;
+    const int in_words = SMEM ? Wp >> 2 : p.W >> 2;          // 4-byte words per input row
     const bool col_ok = col * 4 < p.OW;
     const int out_valid = p.OW - col * 4;                    // output columns of this lane (>= 4: all)
-    for (int g = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; g < groups; g += warps) {
+    const int wib = threadIdx.x >> 5;                        // warp in block
+    const int P = 8 * ppw;                                   // planes per CTA pass (SMEM)
+    uint8_t* const s_in = dw_smem;
+    uint8_t* const s_out = dw_smem + (size_t)P * p.H * Wp;
+    const int g_first = SMEM ? (int)blockIdx.x * 8 + wib : (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    const int g_step = SMEM ? (int)gridDim.x * 8 : warps;
+    for (int g = g_first; SMEM ? (g - wib < groups) : (g < groups); g += g_step) {
         const int plane = g * ppw + sub;
         const bool live = plane < p.planes && col_ok;
+        if (SMEM) {
+            // phase 1: the pass's planes are one contiguous run of bytes in global memory (it starts at a multiple of
+            // 8 planes, hence at a word boundary): consecutive threads load consecutive words and scatter their bytes
+            // into the padded image.  The pad columns are written once, before the first pass.
+            const int plane0 = (g - wib) * ppw;
+            const int n_pl = min(P, p.planes - plane0);
+            const int n_bytes = n_pl * p.H * p.W;
+            const uint8_t* src = p.x + (size_t)plane0 * p.H * p.W;
+            if (g == g_first) {
+                for (int rr = threadIdx.x; rr < P * p.H; rr += 256)
+                    for (int i = p.W; i < Wp; ++i) s_in[(size_t)rr * Wp + i] = (uint8_t)p.pad_word;
+            }
+            for (int w = threadIdx.x; w * 4 < n_bytes; w += 256) {
+                const int b0 = w * 4;
+                uint32_t v;
+                if (b0 + 4 <= n_bytes) v = __ldg(reinterpret_cast<const uint32_t*>(src) + w);
+                else { v = 0; for (int i = 0; b0 + i < n_bytes; ++i) v |= (uint32_t)__ldg(src + b0 + i) << (8 * i); }
+                int row = b0 / p.W, iw = b0 - row * p.W;            // row counts the rows of all planes of the pass
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (b0 + i < n_bytes) s_in[(size_t)row * Wp + iw] = (uint8_t)(v >> (8 * i));
+                    if (++iw == p.W) { iw = 0; ++row; }
+                }
+            }
+            __syncthreads();
+        }
         const int c = live ? plane % p.C : 0;
         const uint32_t k0 = __ldg(p.wrow + c * 3), k1 = __ldg(p.wrow + c * 3 + 1), k2 = __ldg(p.wrow + c * 3 + 2);
         const float m = __ldg(p.mult + c);
         const int b = __ldg(p.bias + c);
-        const uint32_t* xin = reinterpret_cast<const uint32_t*>(p.x + (size_t)(live ? plane : 0) * p.H * p.W);
-        uint32_t* yout = reinterpret_cast<uint32_t*>(p.y + (size_t)(live ? plane : 0) * p.OH * p.OW) + col;
-        const int ow_words = p.OW >> 2;
+        const int pl_local = wib * ppw + sub;                 // SMEM: this lane's plane within the pass
+        const uint32_t* xin = SMEM ? reinterpret_cast<const uint32_t*>(s_in + (size_t)pl_local * p.H * Wp)
+                                   : reinterpret_cast<const uint32_t*>(p.x + (size_t)(live ? plane : 0) * p.H * p.W);
+        uint32_t* yout = SMEM ? reinterpret_cast<uint32_t*>(s_out + (size_t)pl_local * p.OH * OWp) + col
+                              : reinterpret_cast<uint32_t*>(p.y + (size_t)(live ? plane : 0) * p.OH * p.OW) + col;
+        const int ow_words = SMEM ? OWp >> 2 : p.OW >> 2;
         const long long xplane = (long long)(live ? plane : 0) * p.H * p.W;
         uint8_t* yplane = p.y + (size_t)(live ? plane : 0) * p.OH * p.OW + col * 4;
         auto store_row = [&](int oh, uint32_t pk) {
             if (!live) return;
-            if (ALIGNED) { yout[(size_t)oh * ow_words] = pk; return; }
+            if (ALIGNED || SMEM) { yout[(size_t)oh * ow_words] = pk; return; }
             uint8_t* d = yplane + (size_t)oh * p.OW;
 #pragma unroll
             for (int i = 0; i < 4; ++i)
@@ -129,6 +172,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
             // are issued before this trip's arithmetic so that their latency is covered
             auto load_row = [&](int ih) -> uint32_t {
                 if (!(live && ih >= 0 && ih < p.H)) return p.pad_word;
+                if (SMEM) return xin[ih * in_words + col];
                 if (ALIGNED) return __ldg(xin + (size_t)ih * in_words + col);
                 return dw_load_unaligned(p, xplane + (long long)ih * p.W + col * 4, p.W - col * 4);
             };
@@ -169,6 +213,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
             const bool c0 = live && col * 8 < p.W, c1 = live && col * 8 + 4 < p.W;
             auto load_w = [&](int ih, int k, bool on) -> uint32_t {
                 if (!(on && ih < p.H)) return p.pad_word;
+                if (SMEM) return xin[ih * in_words + col * 2 + k];
                 if (ALIGNED) return __ldg(xin + (size_t)ih * in_words + col * 2 + k);
                 return dw_load_unaligned(p, xplane + (long long)ih * p.W + col * 8 + k * 4, p.W - col * 8 - k * 4);
             };
@@ -205,6 +250,27 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
                     }
                 }
                 store_row(oh, dw_requant4<LEAN>(cur, m, p));
+            }
+        }
+        if (SMEM) {
+            // phase 3: the pass's outputs are one contiguous run too: consecutive threads gather four bytes from the
+            // padded image and store consecutive words
+            __syncthreads();
+            const int plane0 = (g - wib) * ppw;
+            const int n_pl = min(P, p.planes - plane0);
+            const int n_bytes = n_pl * p.OH * p.OW;
+            uint8_t* dst = p.y + (size_t)plane0 * p.OH * p.OW;
+            for (int w = threadIdx.x; w * 4 < n_bytes; w += 256) {
+                const int b0 = w * 4;
+                int row = b0 / p.OW, ow = b0 - row * p.OW;
+                uint32_t v = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (b0 + i < n_bytes) v |= (uint32_t)s_out[(size_t)row * OWp + ow] << (8 * i);
+                    if (++ow == p.OW) { ow = 0; ++row; }
+                }
+                if (b0 + 4 <= n_bytes) reinterpret_cast<uint32_t*>(dst)[w] = v;
+                else for (int i = 0; b0 + i < n_bytes; ++i) dst[b0 + i] = (uint8_t)(v >> (8 * i));
             }
         }
     }
@@ -323,6 +389,26 @@ inline int32_t qdwconv_launch_s(zant_ctx* ctx, const QDwArgs& a, int grid, bool 
     return check_launch(ctx, "qdwconv3x3_kernel");
 }
 
+template <int STRIDE, bool XU8, bool LEAN>
+inline int32_t qdwconv_launch_smem_t(zant_ctx* ctx, const QDwArgs& a, int grid, size_t smem) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        ZB_CUDA(cudaFuncSetAttribute(qdwconv3x3_kernel<STRIDE, XU8, LEAN, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        attr_set = true;
+    }
+    qdwconv3x3_kernel<STRIDE, XU8, LEAN, true, true><<<grid, 256, smem, ctx->stream>>>(a);
+    return check_launch(ctx, "qdwconv3x3_kernel<smem>");
+}
+
+inline int32_t qdwconv_launch_smem(zant_ctx* ctx, const QDwArgs& a, int grid, size_t smem, int stride, bool x_u8, bool lean) {
+    if (stride == 1) {
+        if (x_u8) return lean ? qdwconv_launch_smem_t<1, true, true>(ctx, a, grid, smem) : qdwconv_launch_smem_t<1, true, false>(ctx, a, grid, smem);
+        return lean ? qdwconv_launch_smem_t<1, false, true>(ctx, a, grid, smem) : qdwconv_launch_smem_t<1, false, false>(ctx, a, grid, smem);
+    }
+    if (x_u8) return lean ? qdwconv_launch_smem_t<2, true, true>(ctx, a, grid, smem) : qdwconv_launch_smem_t<2, true, false>(ctx, a, grid, smem);
+    return lean ? qdwconv_launch_smem_t<2, false, true>(ctx, a, grid, smem) : qdwconv_launch_smem_t<2, false, false>(ctx, a, grid, smem);
+}
+
 // x and y must be 4-byte aligned (the caller checks with qdwconv_ptr_ok).
 inline bool qdwconv_ptr_ok(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
 
@@ -360,6 +446,15 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
         }
     }
     const bool aligned = g.W % 4 == 0 && g.OW % 4 == 0;
+    if (!aligned) {
+        // rows that are not whole words: stage the planes through shared memory when a pass (8 warps x planes per warp) fits
+        const int Wp = (g.W + 7) / 8 * 8, OWp = (g.OW + 3) / 4 * 4;
+        const size_t smem = (size_t)8 * ppw * ((size_t)g.H * Wp + (size_t)g.OH * OWp);
+        if (smem <= 96 * 1024) {
+            const int sgrid = (int)std::min<long long>((groups + 7) / 8, (long long)ctx->sm_count * 4);
+            return qdwconv_launch_smem(ctx, a, sgrid, smem, g.sh, x_u8, lean);
+        }
+    }
     if (g.sh == 1) return aligned ? qdwconv_launch_s<1, true>(ctx, a, grid, x_u8, lean) : qdwconv_launch_s<1, false>(ctx, a, grid, x_u8, lean);
     return aligned ? qdwconv_launch_s<2, true>(ctx, a, grid, x_u8, lean) : qdwconv_launch_s<2, false>(ctx, a, grid, x_u8, lean);
 }

@@ -230,6 +230,22 @@ __global__ void maxpool2x2s2_q8(const uint2* __restrict__ x, uint32_t* __restric
     }
 }
 
+// The float form: a thread reads a float4 of two input rows and stores two outputs.  The maximum is taken with the
+// reference's comparison chain (start at -inf, take a value only if it is greater), in the window's kh, kw order, so NaNs
+// are skipped exactly as there.
+__global__ void maxpool2x2s2_f32(const float4* __restrict__ x, float2* __restrict__ y, size_t planes_rows, int ow2, int w4) {
+    const size_t total = planes_rows * (size_t)ow2;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / ow2;
+        const int c = (int)(i - row * ow2);
+        const float4 a = __ldg(x + (row * 2) * (size_t)w4 + c), b = __ldg(x + (row * 2 + 1) * (size_t)w4 + c);
+        float m0 = -INFINITY, m1 = -INFINITY;
+        m0 = a.x > m0 ? a.x : m0; m0 = a.y > m0 ? a.y : m0; m0 = b.x > m0 ? b.x : m0; m0 = b.y > m0 ? b.y : m0;
+        m1 = a.z > m1 ? a.z : m1; m1 = a.w > m1 ? a.w : m1; m1 = b.z > m1 ? b.z : m1; m1 = b.w > m1 ? b.w : m1;
+        y[i] = make_float2(m0, m1);
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // Element-wise activations: float4 body when both pointers are 16-byte aligned, scalar tail.
 // ------------------------------------------------------------------------------------------

@@ -79,6 +79,16 @@ inline int32_t run_maxpool(zant_ctx* ctx, const PoolGeom& g, const T* x, T* y) {
             return check_launch(ctx, "maxpool2x2s2_q8");
         }
     }
+    if constexpr (std::is_same<T, float>::value) {
+        const bool fast = g.KH == 2 && g.KW == 2 && g.sh == 2 && g.sw == 2 && g.dh == 1 && g.dw == 1 && g.pt == 0 && g.pl == 0 &&
+                          g.W % 4 == 0 && g.H == 2 * g.OH && g.W == 2 * g.OW &&
+                          (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(y) & 7u) == 0;
+        if (fast) {
+            const size_t pairs = total / 2;
+            maxpool2x2s2_f32<<<grid_for(pairs, 256, ctx->sm_count, 16), 256, 0, ctx->stream>>>((const float4*)x, (float2*)y, (size_t)g.NC * g.OH, g.OW / 2, g.W / 4);
+            return check_launch(ctx, "maxpool2x2s2_f32");
+        }
+    }
     maxpool_nchw<T><<<grid_for(total, 256, ctx->sm_count), 256, 0, ctx->stream>>>(x, y, g);
     return check_launch(ctx, "maxpool_nchw");
 }
