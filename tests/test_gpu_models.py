@@ -186,8 +186,8 @@ def test_mobilenetv2_int8_bit_exact(zb, ctx, oracle, models, batch, res):
     got = plan.run(x)
     assert np.array_equal(got.view(np.uint32), want[g.output].view(np.uint32))
     names = plan.step_names()
-    # pointwise convs: implicit GEMM; the stride-2 stem: im2col + GEMM; depthwise: its own kernel where rows are whole words
-    assert "QLinearConv(tc-implicit)" in names and "QLinearConv(tc)" in names and "QLinearConv(depthwise)" in names
+    # pointwise convs: the filters-on-lanes kernel; the smallest planes: im2col + GEMM; depthwise: its own kernel
+    assert "QLinearConv(tc-pointwise)" in names and "QLinearConv(tc)" in names and "QLinearConv(depthwise)" in names
     # spot-check intermediates of each operator kind: depthwise conv, residual add, global pool
     kinds = {}
     for n in g.nodes:

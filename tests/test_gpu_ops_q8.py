@@ -194,8 +194,8 @@ def test_qlinearconv_depthwise3x3(zb, ctx, oracle, case):
     assert len(np.unique(want)) > 16
 
 
-# stride-1 cases run the implicit-GEMM kernel (one launch), the others im2col + GEMM (two launches)
-TC_QCONV_LAUNCHES = [1, 2, 2, 1, 2, 1, 2, 2, 2, 2]
+# stride-1 cases run the implicit-GEMM or the pointwise kernel (one launch), the others im2col + GEMM (two launches)
+TC_QCONV_LAUNCHES = [1, 2, 2, 1, 2, 1, 1, 2, 2, 2]
 
 IMPLICIT_QCONV = [
     # N C H W M k stride pads dil xdt ydt xzp yzp per_channel bias act
@@ -232,6 +232,45 @@ def test_qlinearconv_implicit_gemm(ctx, oracle, case):
     want = oracle.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
     assert np.array_equal(got, want)
     assert launches == 1
+    assert len(np.unique(want)) > 16
+
+
+# 1x1 / stride 1 / no padding.  Planes of whole words and more than 32 filters: filters on the accumulator lanes, activations
+# straight from NCHW (tc_pw_nchw.cuh); the other cases take the implicit-GEMM kernel or im2col + GEMM.
+POINTWISE_QCONV = [
+    # N C H W M xdt ydt xzp yzp per_channel bias act
+    (2, 32, 112, 112, 16, I8, I8, 0, 0, True, True, "relu6"),       # 12544-pixel planes (49 tiles), half a lane quarter of filters, 32-byte stores
+    (2, 16, 112, 112, 96, I8, I8, 0, 0, True, True, None),          # 16 channels: half a K step of zero weights
+    (3, 24, 56, 56, 144, U8, I8, 128, 0, True, True, "relu"),       # 13 tiles per image, the last of 64 pixels; two filter tiles, the second of 16
+    (2, 144, 28, 28, 32, I8, I8, -3, 0, False, True, "relu6"),      # 784-byte planes: tiles of 208 pixels, 16-byte stores; five K steps in stages of two
+    (3, 64, 14, 14, 384, U8, U8, 7, 9, True, True, None),           # 196-byte planes: word copies in, bulk copy out; three filter tiles; general requantisation
+    (2, 960, 7, 7, 160, I8, I8, 0, 0, True, True, "relu"),          # 49-byte planes (im2col + GEMM)
+    (3, 960, 14, 14, 160, I8, I8, 0, 0, True, True, "relu"),        # the deepest K the pointwise kernel takes
+    (6, 320, 7, 7, 1280, I8, I8, 2, 0, True, False, None),          # ten filter tiles
+    (5, 20, 9, 9, 10, I8, U8, -1, 30, True, True, "relu"),          # 81-byte planes
+    (5, 20, 6, 6, 10, I8, U8, -1, 30, True, True, "relu"),          # 36-byte planes, 10 filters: the staged tile (360 bytes per image) is copied out by threads
+    (6, 12, 6, 10, 20, U8, I8, 9, 0, False, True, None),            # 60-byte planes, word copies
+    (2, 8, 4, 36, 6, I8, I8, 0, 0, True, True, "relu"),             # 144-pixel planes: a second pixel block of 16
+    (1, 64, 16, 17, 130, I8, I8, 0, -4, True, True, None),          # 272 pixels: two tiles of 144; non-zero output zero point
+]
+
+
+@pytest.mark.parametrize("case", POINTWISE_QCONV, ids=[f"pointwise{i}" for i in range(len(POINTWISE_QCONV))])
+def test_qlinearconv_pointwise(ctx, oracle, case):
+    N, C, H, W, M, xdt, ydt, xzp, yzp, per_ch, has_bias, act = case
+    rng = np.random.default_rng(N * 43 + C + M + W)
+    x = q(rng, (N, C, H, W), xdt)
+    w = rng.integers(-127, 128, (M, C, 1, 1), dtype=np.int8)
+    ws = (rng.random(M if per_ch else 1, dtype=np.float32) * 0.02 + 0.001).astype(np.float32)
+    bias = rng.integers(-3000, 3000, M).astype(np.int32) if has_bias else None
+    y_scale = 0.015 * np.sqrt(C)
+    kw = dict(bias=bias, y_dtype=ydt, stride=(1, 1), pads=(0, 0, 0, 0), dilations=(1, 1), group=1, activation=act)
+    before = ctx.launch_count()
+    got = ctx.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
+    launches = ctx.launch_count() - before
+    want = oracle.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
+    assert np.array_equal(got, want)
+    assert launches == 1 if (H * W) % 4 == 0 else launches <= 2
     assert len(np.unique(want)) > 16
 
 

@@ -20,6 +20,7 @@
 #include "tc_gemm_tf32.cuh"
 #include "tc_conv_generic.cuh"
 #include "tc_conv_nchw.cuh"
+#include "tc_pw_nchw.cuh"
 #include "dwconv_q8.cuh"
 #include "smallc_conv_q8.cuh"
 #include "tc_conv_nhwc.cuh"
@@ -776,6 +777,22 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
         ZB_TRY(s.commit());
         ZB_TRY(run_qconv_smallc(ctx, g, s.ptr<char>(ix), x_dtype == ZANT_U8, x_zp, s.ptr<uint32_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
                                 s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, tc_conv_max_product(mult, bf, (long long)g.C * 9)));
+        return s.finish();
+    }
+    PwConvPlan pwp;
+    if (host_consts && (!is_device_ptr(x) || pw_conv_ptr_ok(x, nullptr)) && (!is_device_ptr(y) || pw_conv_ptr_ok(nullptr, y)) &&
+        pw_conv_plan(g, wz_zero, ctx->sm_count, pwp)) {
+        // 1x1: filters on the accumulator lanes, activations straight from NCHW as the MN-major operand
+        std::vector<int8_t> w_blk; std::vector<int32_t> bf;
+        pw_conv_prepare(pwp, w, bias, x_zp, w_blk, bf);
+        bool finite = true;
+        for (float f : mult) finite = finite && std::isfinite(f);
+        Stager s(ctx);
+        const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
+        const int iw = s.in(w_blk.data(), w_blk.size()), im = s.in(mult.data(), mult.size() * 4), ib = s.in(bf.data(), bf.size() * 4);
+        ZB_TRY(s.commit());
+        ZB_TRY(pw_conv_run(ctx, pwp, s.ptr<char>(ix), x_dtype == ZANT_U8, s.ptr<int8_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
+                           s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, finite));
         return s.finish();
     }
     TcConvPlan tcp;

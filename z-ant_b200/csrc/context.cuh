@@ -31,6 +31,18 @@ namespace zb {
             return zb::fail(ZANT_E_CUDA, "%s -> %s", #expr, cudaGetErrorString(_e));          \
     } while (0)
 
+// Opt-in to more than 48 KiB of dynamic shared memory.  The attribute belongs to the function ON ONE DEVICE, so it is
+// set once per device (a process may drive several: one worker thread per device, each with its own context).
+#define ZB_SMEM_ATTR(ctx, kernel, bytes)                                                      \
+    do {                                                                                      \
+        static std::atomic<unsigned long long> zb_done_{0ull};                                \
+        const unsigned long long zb_bit_ = 1ull << ((ctx)->device & 63);                      \
+        if (!(zb_done_.load(std::memory_order_acquire) & zb_bit_)) {                          \
+            ZB_CUDA(cudaFuncSetAttribute((kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes))); \
+            zb_done_.fetch_or(zb_bit_, std::memory_order_release);                            \
+        }                                                                                     \
+    } while (0)
+
 // Device allocations: an out-of-memory answer is the reference's MemError (src/Utils/errorHandler.zig:36-52).
 #define ZB_ALLOC(ptr, bytes)                                                                  \
     do {                                                                                      \

@@ -391,11 +391,7 @@ inline int32_t qdwconv_launch_s(zant_ctx* ctx, const QDwArgs& a, int grid, bool 
 
 template <int STRIDE, bool XU8, bool LEAN>
 inline int32_t qdwconv_launch_smem_t(zant_ctx* ctx, const QDwArgs& a, int grid, size_t smem) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        ZB_CUDA(cudaFuncSetAttribute(qdwconv3x3_kernel<STRIDE, XU8, LEAN, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-        attr_set = true;
-    }
+    ZB_SMEM_ATTR(ctx, (qdwconv3x3_kernel<STRIDE, XU8, LEAN, true, true>), 96 * 1024);
     qdwconv3x3_kernel<STRIDE, XU8, LEAN, true, true><<<grid, 256, smem, ctx->stream>>>(a);
     return check_launch(ctx, "qdwconv3x3_kernel<smem>");
 }

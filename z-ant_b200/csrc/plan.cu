@@ -21,6 +21,7 @@
 #include "tc_gemm.cuh"
 #include "tc_conv_generic.cuh"
 #include "tc_conv_nchw.cuh"
+#include "tc_pw_nchw.cuh"
 #include "dwconv_q8.cuh"
 #include "smallc_conv_q8.cuh"
 #include "tc_conv_nhwc.cuh"
@@ -561,6 +562,21 @@ static int32_t build_qconv(zant_plan* pl, const PlanNode& n, QConvFusion& fz) {
             if (!qconv_smallc_ptr_ok(pl->ptr(x))) return fail(ZANT_E_INVALID_INPUT, "QLinearConv input buffer must be 4-byte aligned");
             return run_qconv_smallc(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, (const uint32_t*)pl->aux(aw), (const float*)pl->aux(am),
                                     (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), max_product);
+        });
+        return ZANT_OK;
+    }
+    PwConvPlan pwp;
+    if (const_bias && pw_conv_plan(g, wz_zero, ctx->sm_count, pwp)) {
+        // 1x1: filters on the accumulator lanes, activations straight from NCHW as the MN-major operand
+        std::vector<int8_t> w_blk; std::vector<int32_t> bf;
+        pw_conv_prepare(pwp, (const int8_t*)T(w).host.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, w_blk, bf);
+        bool finite = true;
+        for (float f : mult) finite = finite && std::isfinite(f);
+        const int aw = pl->add_aux(w_blk.data(), w_blk.size()), am = pl->add_aux(mult.data(), mult.size() * 4), ab = pl->add_aux(bf.data(), bf.size() * 4);
+        push("QLinearConv(tc-pointwise)" + tail, [=]() {
+            if (!pw_conv_ptr_ok(pl->ptr(x), pl->ptr(y))) return fail(ZANT_E_INVALID_INPUT, "pointwise QLinearConv buffers must be 16-byte (input) and 32-byte (output) aligned");
+            return pw_conv_run(ctx, pwp, pl->ptr(x), xd == ZANT_U8, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
+                               (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), finite);
         });
         return ZANT_OK;
     }
@@ -1408,11 +1424,7 @@ static int32_t try_fuse_small_cnn(zant_plan* pl, size_t i0, size_t& consumed) {
     });
     push("Fused[QLinearConv+Relu+MaxPool] tcgen05", [=]() {
         using Cfg = TcConvParityCfg;
-        static bool attr_set = false;
-        if (!attr_set) {
-            ZB_CUDA(cudaFuncSetAttribute(tc_conv3x3_pool_parity_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-            attr_set = true;
-        }
+        ZB_SMEM_ATTR(ctx, (tc_conv3x3_pool_parity_kernel), Cfg::SMEM_BYTES);
         TcConvParityArgs k{};
         k.x = (const int8_t*)pl->scratch(s_pool1); k.plane_bytes = plane_bytes; k.w = (const int8_t*)pl->aux(a_w2);
         for (int m = 0; m < 64; ++m) { k.mult[m] = m2[m]; k.bias[m] = b2[m]; }
@@ -1424,11 +1436,7 @@ static int32_t try_fuse_small_cnn(zant_plan* pl, size_t i0, size_t& consumed) {
     const zant_node_attrs f1a = f1.a, f2a = f2.a, dqa = N[11].a;
     push("Fused[Reshape+QLinearMatMul+Relu] tcgen05", [=]() {
         using Cfg = TcGemmCfg<FC_NT, FC_KC, FC_STAGES>;
-        static bool attr_set = false;
-        if (!attr_set) {
-            ZB_CUDA(cudaFuncSetAttribute(tc_gemm_i8_kernel<FC_NT, FC_KC, FC_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-            attr_set = true;
-        }
+        ZB_SMEM_ATTR(ctx, (tc_gemm_i8_kernel<FC_NT, FC_KC, FC_STAGES>), Cfg::SMEM_BYTES);
         TcGemmArgs k{};
         k.a = (const int8_t*)pl->scratch(s_pool2); k.w = (const int8_t*)pl->aux(a_w3);
         k.mult = (const float*)pl->aux(a_m3); k.bias = (const int32_t*)pl->aux(a_b3);
@@ -1449,11 +1457,7 @@ static int32_t try_fuse_small_cnn(zant_plan* pl, size_t i0, size_t& consumed) {
         auto launch = [&](auto nc) -> int32_t {
             constexpr int NC = decltype(nc)::value;
             constexpr int smem = fcout_smem_bytes<NC, 512>();
-            static bool attr_set = false;
-            if (!attr_set) {
-                ZB_CUDA(cudaFuncSetAttribute(fc_out_dequant_kernel<NC, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-                attr_set = true;
-            }
+            ZB_SMEM_ATTR(ctx, (fc_out_dequant_kernel<NC, 512>), smem);
             const int blocks = std::min<int>((int)((B + 127) / 128), ctx->sm_count * 3);
             fc_out_dequant_kernel<NC, 512><<<blocks, FCOUT_THREADS, smem, ctx->stream>>>(k);
             return check_launch(ctx, "fc_out_dequant_kernel");

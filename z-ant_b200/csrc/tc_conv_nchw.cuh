@@ -849,11 +849,7 @@ inline void tc_conv_prepare(const TcConvPlan& p, const int8_t* w, const float* m
 
 template <int NT, bool XU8, bool LEAN>
 inline int32_t tc_conv_launch_t(zant_ctx* ctx, const TcConvPlan& p, const TcConvArgs& a, const CUtensorMap& x_map, int grid) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        ZB_CUDA(cudaFuncSetAttribute(tc_conv_nchw_kernel<NT, XU8, LEAN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
-        attr_set = true;
-    }
+    ZB_SMEM_ATTR(ctx, (tc_conv_nchw_kernel<NT, XU8, LEAN>), 232448);
     tc_conv_nchw_kernel<NT, XU8, LEAN><<<grid, kTcConvThreads, p.smem_bytes, ctx->stream>>>(a, x_map);
     return check_launch(ctx, "tc_conv_nchw_kernel");
 }

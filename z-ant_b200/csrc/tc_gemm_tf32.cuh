@@ -413,11 +413,7 @@ inline int32_t launch_tf_gemm(zant_ctx* ctx, const TfGemmArgs& k, int tiles) {
     constexpr int STAGES = NT == 256 ? 4 : 6;
     constexpr int KC = SPLIT ? 4 : 8;          // the same bytes per stage in both forms
     using Cfg = TfGemmCfg<NT, KC, STAGES, SPLIT>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        ZB_CUDA(cudaFuncSetAttribute(tc_gemm_tf32_kernel<NT, KC, STAGES, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        attr_set = true;
-    }
+    ZB_SMEM_ATTR(ctx, (tc_gemm_tf32_kernel<NT, KC, STAGES, SPLIT>), Cfg::SMEM_BYTES);
     tc_gemm_tf32_kernel<NT, KC, STAGES, SPLIT><<<std::min(tiles, ctx->sm_count), Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
     return check_launch(ctx, SPLIT ? "tc_gemm_tf32_kernel<split>" : "tc_gemm_tf32_kernel");
 }

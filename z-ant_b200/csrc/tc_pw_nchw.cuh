@@ -1,0 +1,489 @@
+// Pointwise (1x1, stride 1, no padding, group 1) QLinearConv on tcgen05 with the FILTERS on the accumulator's lanes.
+//
+// Per image a 1x1 convolution is the product  Y[M filters][HW pixels] = W[M][C] . X[C][HW].  With NCHW tensors both X
+// and Y keep the pixel index contiguous, so the natural tcgen05 form is
+//     D (TMEM: lane = filter, column = pixel)  =  A (weights [128 filters][K], K-major)  x  B (activations, N-major),
+// where the B operand of a stage is a box [K chunk][128 pixels] of the input exactly as it lies in memory: a tiled TMA
+// load with the 128-byte swizzle drops it into shared memory in the "MN-major" operand form, nothing is transposed.
+// In the epilogue a thread owns one filter and reads 32 consecutive pixels of it from TMEM: the multiplier and bias are
+// two registers, four results pack into one word, and the 32 bytes leave as one 32-byte store into the filter's NCHW
+// plane.  (The implicit-GEMM kernel for k x k filters puts pixels on the lanes and has to transpose bytes through
+// shared memory on the way out; for 1x1 filters this form has neither that nor a patch to build.)
+//
+// A CTA keeps the weights of ONE tile of 128 filters resident in shared memory (K <= 960) and walks over (image,
+// pixel tile) pairs; a pixel tile is up to 256 pixels (two accumulator buffers of 256 TMEM columns each, so the
+// epilogue of a tile overlaps the MMAs of the next).
+// Planes whose size is a multiple of 4 but not of 16 bytes (14 x 14) have no tensor map: four copier warps bring the
+// rows in with word loads, writing the same swizzled form, and the output tile - for a whole image the block
+// [128 filters][HW] is contiguous in NCHW - is staged in shared memory and leaves as one bulk copy.
+//
+// Warp roles (704 threads, one persistent CTA per SM):
+//   warp 0  TMA loader     warp 1  TMEM owner + MMA issuer     warps 2-17  epilogue     warps 18-21  copiers (no tensor map)
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <vector>
+
+#include "context.cuh"
+#include "fused_cnn.cuh"
+#include "geometry.hpp"
+#include "kernels_q8.cuh"
+#include "ptx_sm100.cuh"
+
+namespace zb {
+
+struct PwConvArgs {
+    const uint8_t* x; uint8_t* y; const int8_t* w; const float* mult; const int32_t* bias;
+    int N, C, M, HW;
+    int k_steps;          // K steps of 32 channels (C rounded up)
+    int KS;               // K steps per stage (a stage holds KS * 32 channels)
+    int n_px;             // pixels per tile: a multiple of 16, at most 256
+    int px_tiles;         // tiles per image
+    int PB;               // 128-pixel blocks per tile (1 or 2)
+    int cpm;              // CTAs per filter tile
+    int mode;             // 0: tensor map; 1: word copies in, staged tile out (HW % 4 == 0, at most 256 pixels: one tile per image)
+    int bulk_out;         // mode 1: the staged tile leaves as one bulk copy (its address and size are multiples of 16)
+    int wide_store;       // mode 0: every 32-pixel chunk starts at a 32-byte boundary (HW and n_px are multiples of 32)
+    int stages, stage_bytes, off_stages, off_out, off_tail;
+    float y_scale; int y_zp; int act; int out_u8; int six;
+    const uint8_t* lut;
+    int* status;
+};
+
+constexpr int kPwThreads = 704;
+constexpr int kPwMaxStages = 8;
+constexpr int kPwTail = 1024;                 // barriers, TMEM slot, flags, activation table
+constexpr uint32_t kIdescBMnMajor = 1u << 16; // bit 16 of the instruction descriptor: B is MN-major (its N index is the contiguous one)
+
+__device__ __forceinline__ void st_global_32B(uint8_t* p, const uint32_t (&v)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+
+// shared -> global bulk copy of this thread's bulk group; the group is committed and, later, waited for by the same thread
+__device__ __forceinline__ void bulk_s2g(void* dst_gmem, uint32_t src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(src_smem), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+template <bool XU8, bool LEAN>
+__global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_constant__ PwConvArgs a, const __grid_constant__ CUtensorMap x_map) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint8_t* sA = smem;                                  // [k16][128 filters][16]
+    uint8_t* sStages = smem + a.off_stages;
+    uint8_t* sOut = smem + a.off_out;
+    uint8_t* tail = smem + a.off_tail;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 256);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 260);
+    volatile int* epi_ok = reinterpret_cast<volatile int*>(tail + 264);
+    volatile int* cp_ok = reinterpret_cast<volatile int*>(tail + 268);
+    uint8_t* sLut = tail + 512;
+    const uint32_t bar0 = ptx::smem_u32(bars);
+    const int S = a.stages;
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (kPwMaxStages + s); };
+    auto tfull = [&](int b) { return bar0 + 8u * (2 * kPwMaxStages + b); };
+    auto tempty = [&](int b) { return bar0 + 8u * (2 * kPwMaxStages + 2 + b); };
+    const uint32_t wfull = bar0 + 8u * (2 * kPwMaxStages + 4);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int mt = (int)blockIdx.x / a.cpm, j0 = (int)blockIdx.x - mt * a.cpm;
+    const int tiles = a.N * a.px_tiles;
+    const int KC = a.KS * 32;
+    const int k_iters = (a.k_steps + a.KS - 1) / a.KS;
+    const uint32_t blk_bytes = (uint32_t)KC * 128u;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), 1); ptx::mbar_init(empty(s), 1); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 16); }
+        ptx::mbar_init(wfull, 1);
+        *abort_flag = 0; *epi_ok = 1; *cp_ok = 1;
+        ptx::mbar_fence_init();
+    }
+    if (a.lut && tid < 256) sLut[tid] = __ldg(a.lut + tid);
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), 512);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ loader: the filter tile's weights once, then (mode 0) one box per stage and block
+        if (lane == 0) {
+            const uint32_t w_bytes = (uint32_t)a.k_steps * 4096u;
+            ptx::mbar_arrive_expect_tx(wfull, w_bytes);
+            ptx::bulk_g2s(ptx::smem_u32(sA), a.w + (size_t)mt * w_bytes, w_bytes, wfull);
+            if (a.mode == 0) {
+                int s = 0; uint32_t ph = 0;
+                bool alive = true;
+                for (int t = j0; t < tiles && alive; t += a.cpm) {
+                    const int img = t / a.px_tiles, p0 = (t - img * a.px_tiles) * a.n_px;
+                    for (int ki = 0; ki < k_iters; ++ki) {
+                        if (!ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag)) { alive = false; break; }
+                        const uint32_t dst = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
+                        ptx::mbar_arrive_expect_tx(full(s), (uint32_t)a.PB * blk_bytes);
+                        for (int blk = 0; blk < a.PB; ++blk)
+                            ptx::tma_load_3d(dst + (uint32_t)blk * blk_bytes, &x_map, (p0 + blk * 128) >> 2, ki * KC, img, full(s));
+                        if (++s == S) { s = 0; ph ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (ptx::elect_one()) {
+            const uint32_t n_blk0 = (uint32_t)min(a.n_px, 128), n_blk1 = (uint32_t)(a.n_px - 128);
+            const uint32_t idesc0 = ptx::idesc_i8(128, (int)n_blk0, true, !XU8) | kIdescBMnMajor;
+            const uint32_t idesc1 = a.PB > 1 ? (ptx::idesc_i8(128, (int)n_blk1, true, !XU8) | kIdescBMnMajor) : 0u;
+            const uint64_t da0 = ptx::smem_desc_kmajor(ptx::smem_u32(sA), 128 * 16, 128);
+            int s = 0; uint32_t ph = 0;
+            int tile_it = 0;
+            if (!ptx::mbar_wait(wfull, 0, abort_flag)) goto mma_done;
+            for (int t = j0; t < tiles; t += a.cpm, ++tile_it) {
+                const int b = tile_it & 1;
+                const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
+                if (!ptx::mbar_wait(tempty(b), bph ^ 1u, abort_flag)) goto mma_done;
+                const uint32_t d_tmem = tmem_base + (uint32_t)(b * 256);
+                for (int ki = 0; ki < k_iters; ++ki) {
+                    if (!ptx::mbar_wait(full(s), ph, abort_flag)) goto mma_done;
+                    ptx::tc_fence_after();
+                    const uint32_t stage0 = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
+                    // B = [channel][128 pixels] rows of 128 bytes: eight channels are 1024 bytes, a K step of 32 channels 4096
+                    const uint64_t db0 = ptx::smem_desc_mnmajor_sw128(stage0, blk_bytes, 1024);
+                    const int ks_here = min(a.KS, a.k_steps - ki * a.KS);
+                    for (int kk = 0; kk < ks_here; ++kk) {
+                        const uint64_t da = da0 + (uint64_t)((ki * a.KS + kk) * 256);        // 4096 bytes per K step, in 16-byte units
+                        const bool acc = (ki | kk) != 0;
+                        ptx::mma_i8(d_tmem, da, db0 + (uint64_t)(kk * 256), idesc0, acc);
+                        if (a.PB > 1) ptx::mma_i8(d_tmem + 128u, da, db0 + (uint64_t)((blk_bytes >> 4) + kk * 256), idesc1, acc);
+                    }
+                    ptx::mma_commit(empty(s));
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+                ptx::mma_commit(tfull(b));
+            }
+        mma_done:;
+        }
+    } else if (warp >= 18) {
+        // ------------------------------------------------------------------ copiers (no tensor map): a stage's channels, row by row,
+        // into the form a swizzled TMA box has: one 128-byte row per channel and 128-pixel block, 16-byte chunk k of row r at
+        // chunk position k ^ (r % 8).  Channels past C are skipped: their weights are zero and any finite byte serves.
+        if (a.mode != 0) {
+            const int cw = warp - 18, ct = tid - 18 * 32;
+            int s = 0; uint32_t ph = 0;
+            bool alive = true;
+            for (int t = j0; t < tiles && alive; t += a.cpm) {
+                const uint8_t* ximg = a.x + (size_t)t * a.C * a.HW;              // one tile per image
+                for (int ki = 0; ki < k_iters; ++ki) {
+                    if (ct == 0) *cp_ok = ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag) ? 1 : 0;
+                    ptx::named_barrier_sync(2, 128);
+                    if (!*cp_ok) { alive = false; break; }
+                    uint8_t* dst = sStages + (size_t)s * a.stage_bytes;
+                    const int c_lo = ki * KC;
+                    {
+                        // a warp takes every fourth row; a lane the words lane and lane + 32 of a row (HW <= 256).  All loads of a
+                        // batch of eight rows are issued before the first store, so that their latencies overlap.
+                        const int wpr = a.HW >> 2;
+                        const bool w1 = lane + 32 < wpr, w0 = lane < wpr;
+                        const uint32_t px0 = (uint32_t)lane * 4u, px1 = px0 + 128u;
+                        const uint32_t o0 = ((px0 >> 4) << 4), o1 = blk_bytes + (((px1 & 127u) >> 4) << 4);   // chunk position before the swizzle
+                        for (int r0 = cw; r0 < KC; r0 += 32) {
+                            uint32_t v0[8], v1[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int rr = r0 + 4 * j;
+                                const bool ok = rr < KC && c_lo + rr < a.C;
+                                const uint32_t* src = reinterpret_cast<const uint32_t*>(ximg + (size_t)(c_lo + (ok ? rr : 0)) * a.HW);
+                                v0[j] = ok && w0 ? __ldg(src + lane) : 0u;
+                                v1[j] = ok && w1 ? __ldg(src + lane + 32) : 0u;
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const int rr = r0 + 4 * j;
+                                if (rr < KC) {
+                                    uint8_t* drow = dst + rr * 128;
+                                    const uint32_t x7 = ((uint32_t)rr & 7u) << 4;
+                                    if (w0) *reinterpret_cast<uint32_t*>(drow + ((o0 ^ x7) | (px0 & 15u))) = v0[j];
+                                    if (w1) *reinterpret_cast<uint32_t*>(drow + (((o1 - blk_bytes) ^ x7) | (px1 & 15u)) + blk_bytes) = v1[j];
+                                }
+                            }
+                        }
+                    }
+                    ptx::fence_proxy_async_smem();
+                    ptx::named_barrier_sync(2, 128);
+                    if (ct == 0) ptx::mbar_arrive(full(s));
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue: 16 warps; a TMEM lane quarter (32 filters) is
+        // served by four warps that take the tile's 32-pixel chunks in turn
+        const int quarter = warp & 3, cg = (warp - 2) >> 2;
+        const int e = tid - 64;
+        const int m_local = quarter * 32 + lane, m = mt * 128 + m_local;
+        const bool live = m < a.M;
+        const float mlt = live ? __ldg(a.mult + m) : 1.0f;
+        const int bs = live ? __ldg(a.bias + m) : 0;
+        const Requant rq{a.y_scale, a.y_zp, a.act, a.lut ? sLut : nullptr};
+        const uint32_t lo4 = a.act == ZANT_QACT_NONE ? 0x80808080u : 0u;
+        const uint32_t hi4 = a.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(a.six & 255) : 0x7f7f7f7fu;
+        const bool quarter_live = mt * 128 + quarter * 32 < a.M;      // a quarter whose 32 filters do not exist only keeps the barriers going
+        const int rows_here = min(128, a.M - mt * 128);
+        int tile_it = 0;
+        for (int t = j0; t < tiles; t += a.cpm, ++tile_it) {
+            const int b = tile_it & 1;
+            const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
+            const int img = t / a.px_tiles, p0 = (t - img * a.px_tiles) * a.n_px;
+            const int n_valid = min(a.n_px, a.HW - p0);
+            if (a.mode == 0) {
+                int ok = 1;
+                if (lane == 0) ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+            } else {
+                // the previous tile's bulk copy must have read the staging buffer before anybody overwrites it
+                if (e == 0) { if (a.bulk_out) bulk_wait_read(); *epi_ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0; }
+                ptx::named_barrier_sync(1, 512);
+                if (!*epi_ok) break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * 256);
+            uint8_t* yrow = a.y + ((size_t)img * a.M + (size_t)m) * a.HW + p0;
+            // 16 accumulators -> four packed words
+            auto requant16 = [&](const uint32_t (&v)[16], uint32_t* pk) {
+#pragma unroll
+                for (int j4 = 0; j4 < 4; ++j4) {
+                    if constexpr (LEAN) {
+                        // the activation is a clamp of the packed codes to [lo4, hi4] (the whole int8 range when there is none)
+                        const uint32_t w4 = pack_sat_s8x4(rq_round((int)v[j4 * 4 + 0] + bs, mlt), rq_round((int)v[j4 * 4 + 1] + bs, mlt),
+                                                          rq_round((int)v[j4 * 4 + 2] + bs, mlt), rq_round((int)v[j4 * 4 + 3] + bs, mlt));
+                        pk[j4] = __vmins4(__vmaxs4(w4, lo4), hi4);
+                    } else {
+                        uint32_t w4 = 0;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int acc = (int)v[j4 * 4 + j] + bs;
+                            int q = a.out_u8 ? requant_one<true>(acc, mlt, Requant{rq.y_scale, rq.y_zp, rq.act, nullptr})
+                                             : requant_one<false>(acc, mlt, Requant{rq.y_scale, rq.y_zp, rq.act, nullptr});
+                            if (a.lut) q = (int)sLut[q & 255];
+                            w4 |= (uint32_t)(q & 255) << (8 * j);
+                        }
+                        pk[j4] = w4;
+                    }
+                }
+            };
+            // This warp's 32-pixel chunks (cg, cg + 4), each as two halves of 16 columns: the TMEM load of the next half is in
+            // flight while the current one is requantised (a wait covers every load issued so far, so a load is issued right
+            // after the wait that precedes the arithmetic it overlaps).
+            uint32_t va[16], vb[16];
+            int ch = cg;
+            bool has = quarter_live && ch * 32 < n_valid;
+            if (has) ptx::tmem_ld16(taddr + (uint32_t)(ch * 32), va);
+            while (has) {
+                uint32_t pk[8];
+                ptx::tmem_wait_ld();
+                ptx::tmem_ld16(taddr + (uint32_t)(ch * 32 + 16), vb);
+                requant16(va, pk);
+                ptx::tmem_wait_ld();
+                const int nch = ch + 4;
+                const bool nhas = nch * 32 < n_valid;
+                if (nhas) ptx::tmem_ld16(taddr + (uint32_t)(nch * 32), va);
+                requant16(vb, pk + 4);
+                if (LEAN && a.lut) {
+#pragma unroll
+                    for (int j4 = 0; j4 < 8; ++j4) pk[j4] = lut4_smem(sLut, pk[j4]);
+                }
+                const int c0 = ch * 32;
+                if (a.mode == 0) {
+                    // HW, p0 and c0 are multiples of 16: the chunk's valid part is 16 or 32 bytes
+                    if (live) {
+                        if (c0 + 32 <= n_valid) {
+                            if (a.wide_store) st_global_32B(yrow + c0, pk);
+                            else {
+                                *reinterpret_cast<uint4*>(yrow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                                *reinterpret_cast<uint4*>(yrow + c0 + 16) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                            }
+                        } else {
+                            *reinterpret_cast<uint4*>(yrow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        }
+                    }
+                } else {
+                    uint32_t* o = reinterpret_cast<uint32_t*>(sOut + (size_t)m_local * a.HW + c0);
+#pragma unroll
+                    for (int j4 = 0; j4 < 8; ++j4)
+                        if (c0 + j4 * 4 < n_valid) o[j4] = pk[j4];
+                }
+                ch = nch; has = nhas;
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(tempty(b));
+            if (a.mode != 0) {
+                // the staged block [rows_here][HW] is the image's contiguous run of these filters' planes
+                ptx::fence_proxy_async_smem();
+                ptx::named_barrier_sync(1, 512);
+                uint8_t* dst = a.y + ((size_t)img * a.M + (size_t)mt * 128) * a.HW;
+                const int bytes = rows_here * a.HW;
+                if (a.bulk_out) {
+                    if (e == 0) bulk_s2g(dst, ptx::smem_u32(sOut), (uint32_t)bytes);
+                } else {
+                    for (int i = e; i < bytes; i += 512) dst[i] = sOut[i];
+                    ptx::named_barrier_sync(1, 512);
+                }
+            }
+        }
+        if (a.mode != 0 && a.bulk_out && e == 0) bulk_wait_all();
+    }
+
+    if (*abort_flag) {
+        for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) ptx::tmem_dealloc(tmem_base, 512);
+    if (tid == 0 && *abort_flag) atomicExch(a.status, (int)DEV_ERR_WAIT_TIMEOUT);
+}
+
+// =============================================================================================
+// Host side
+// =============================================================================================
+struct PwConvPlan {
+    PwConvArgs a{};
+    int m_tiles = 0;
+    size_t smem_bytes = 0;
+    size_t w_bytes = 0;          // blocked weights: [filter tile][k16][128][16]
+};
+
+// Chooses the tiling; false when the kernel does not take the shape (the caller falls back to the implicit-GEMM kernel).
+inline bool pw_conv_plan(const ConvGeom& g, bool w_zp_all_zero, int sm_count, PwConvPlan& p) {
+    if (g.G != 1 || !w_zp_all_zero || g.KH != 1 || g.KW != 1 || g.sh != 1 || g.sw != 1) return false;
+    if (g.pt != 0 || g.pl != 0 || g.pb != 0 || g.pr != 0) return false;
+    const long long hw = (long long)g.H * g.W;
+    if (g.N <= 0 || hw <= 0 || hw > (1 << 24) || g.C > 960 || g.C % 4 != 0) return false;
+    if ((long long)g.N * hw < 256) return false;
+    // up to 32 filters fill one lane quarter only (one of the SM's four schedulers would do the whole epilogue): with
+    // planes that a tensor map covers, the pixels-on-lanes form of the implicit-GEMM kernel is the better one
+    if (g.M <= 32 && hw % 16 == 0 && hw >= 128) return false;
+    PwConvArgs& a = p.a;
+    a = PwConvArgs{};
+    a.N = g.N; a.C = g.C; a.M = g.M; a.HW = (int)hw;
+    a.k_steps = (g.C + 31) / 32;
+    a.KS = a.k_steps >= 2 ? 2 : 1;
+    p.m_tiles = (g.M + 127) / 128;
+    if (p.m_tiles > sm_count) return false;
+    if (hw % 16 == 0 && hw >= 128) {
+        a.mode = 0;
+        a.px_tiles = (int)((hw + 255) / 256);
+        a.n_px = (int)(((hw + a.px_tiles - 1) / a.px_tiles + 15) / 16 * 16);
+        a.wide_store = (hw % 32 == 0 && a.n_px % 32 == 0) ? 1 : 0;
+    } else {
+        if (hw > 256 || hw % 4 != 0) return false;      // rows that are not whole words stay with the im2col path (the byte copies cost more than they save)
+        a.mode = 1;
+        a.px_tiles = 1;
+        a.n_px = (int)((hw + 15) / 16 * 16);
+        const long long last_rows = g.M - (p.m_tiles - 1) * 128;
+        a.bulk_out = (((long long)g.M * hw) % 16 == 0 && (128 * hw) % 16 == 0 && (last_rows * hw) % 16 == 0) ? 1 : 0;
+    }
+    a.PB = a.n_px > 128 ? 2 : 1;
+    const long long tiles = (long long)g.N * a.px_tiles;
+    if (tiles > 0x7fffffffLL) return false;
+    a.cpm = (int)std::max<long long>(1, std::min<long long>(sm_count / p.m_tiles, tiles));
+    a.stage_bytes = a.PB * a.KS * 32 * 128;
+    const int a_bytes = a.k_steps * 4096;
+    const int out_bytes = a.mode == 0 ? 0 : (int)((128 * hw + 1023) / 1024 * 1024);
+    const int budget = 232448 - kPwTail - a_bytes - out_bytes;
+    a.stages = std::min(kPwMaxStages, budget / a.stage_bytes);
+    if (a.stages < 2) return false;
+    a.off_stages = a_bytes;                                  // a multiple of 4096: the stages are 1024-byte aligned
+    a.off_out = a.off_stages + a.stages * a.stage_bytes;
+    a.off_tail = a.off_out + out_bytes;
+    p.smem_bytes = (size_t)a.off_tail + kPwTail;
+    p.w_bytes = (size_t)p.m_tiles * a_bytes;
+    return true;
+}
+
+// Blocks `w` ([M][C] int8) as [filter tile][k16][128][16] (zero beyond M and C) and folds the input zero point into the bias.
+inline void pw_conv_prepare(const PwConvPlan& p, const int8_t* w, const int32_t* bias, int x_zp, std::vector<int8_t>& w_blk, std::vector<int32_t>& bias_f) {
+    const PwConvArgs& a = p.a;
+    w_blk.assign(p.w_bytes, 0);
+    bias_f.assign(a.M, 0);
+    const size_t tile_bytes = (size_t)a.k_steps * 4096;
+    for (int m = 0; m < a.M; ++m) {
+        long long sum = 0;
+        for (int c = 0; c < a.C; ++c) {
+            const int8_t v = w[(size_t)m * a.C + c];
+            w_blk[(size_t)(m / 128) * tile_bytes + (size_t)(c / 16) * 2048 + (size_t)(m % 128) * 16 + (c % 16)] = v;
+            sum += v;
+        }
+        bias_f[m] = (int32_t)((bias ? bias[m] : 0) - (long long)x_zp * sum);
+    }
+}
+
+template <bool XU8, bool LEAN>
+inline int32_t pw_conv_launch_t(zant_ctx* ctx, const PwConvPlan& p, const PwConvArgs& a, const CUtensorMap& x_map, int grid) {
+    ZB_SMEM_ATTR(ctx, (tc_pw_nchw_kernel<XU8, LEAN>), 232448);
+    tc_pw_nchw_kernel<XU8, LEAN><<<grid, kPwThreads, p.smem_bytes, ctx->stream>>>(a, x_map);
+    return check_launch(ctx, "tc_pw_nchw_kernel");
+}
+
+// Tensor map over the NCHW input in 4-byte elements, (HW / 4, C, N); box = 128 pixels x a stage's channels, 128-byte swizzle.
+// Channels past C and pixels past HW read as zero.
+inline int32_t pw_conv_encode_map(const PwConvArgs& a, const void* x, CUtensorMap* map) {
+    const cuuint64_t HW = (cuuint64_t)a.HW, C = (cuuint64_t)a.C, N = (cuuint64_t)a.N;
+    const cuuint64_t dims[3] = {HW / 4, C, N}, strides[2] = {HW, C * HW};
+    const cuuint32_t box[3] = {32, (cuuint32_t)(a.KS * 32), 1}, estr[3] = {1, 1, 1};
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+            cudaGetLastError();
+            return fail(ZANT_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        }
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ZANT_E_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return ZANT_OK;
+}
+
+// Buffers the kernel takes: x 16-byte aligned (tensor map, word loads), y 32-byte aligned (32-byte stores, bulk copies).
+inline bool pw_conv_ptr_ok(const void* x, const void* y) {
+    return (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0;
+}
+
+inline int32_t pw_conv_run(zant_ctx* ctx, const PwConvPlan& p, const void* x, bool x_u8, const int8_t* w_blk_dev, const float* mult_dev,
+                           const int32_t* bias_dev, void* y, bool y_u8, const Requant& rq, bool mult_finite) {
+    PwConvArgs a = p.a;
+    a.x = (const uint8_t*)x; a.y = (uint8_t*)y; a.w = w_blk_dev; a.mult = mult_dev; a.bias = bias_dev;
+    a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0; a.lut = rq.lut;
+    const bool lean = !y_u8 && rq.y_zp == 0 && mult_finite;
+    if (lean) {
+        float v = 6.0f / rq.y_scale;
+        v = std::fmin(std::fmax(v, -512.0f), 511.0f);
+        a.six = std::min(std::max((int)std::nearbyintf(v), -128), 127);
+    }
+    a.status = ctx->status_word;
+    const int grid = p.m_tiles * a.cpm;
+    alignas(64) CUtensorMap x_map{};
+    if (a.mode == 0) ZB_TRY(pw_conv_encode_map(a, x, &x_map));
+    if (x_u8) return lean ? pw_conv_launch_t<true, true>(ctx, p, a, x_map, grid) : pw_conv_launch_t<true, false>(ctx, p, a, x_map, grid);
+    return lean ? pw_conv_launch_t<false, true>(ctx, p, a, x_map, grid) : pw_conv_launch_t<false, false>(ctx, p, a, x_map, grid);
+}
+
+}  // namespace zb
