@@ -110,6 +110,18 @@ def test_qlinear_global_avgpool(ctx, oracle, dt, hw):
 
 
 @pytest.mark.parametrize("dt", [I8, U8])
+@pytest.mark.parametrize("shape", [(8, 640, 7, 7), (5, 1001, 5, 13), (4099, 1, 1, 3), (17, 300, 16, 16)])
+def test_qlinear_global_avgpool_many_small_planes(ctx, oracle, dt, shape):
+    """At least 4096 planes of at most 256 bytes: the thread-per-plane kernel (word loads, masked first and last word)."""
+    x = q(np.random.default_rng(shape[1]), shape, dt)
+    zp = 3 if dt == I8 else 131
+    got = ctx.qlinear_global_avgpool(x, 0.05, zp, 0.02, -1 if dt == I8 else 9)
+    want = oracle.qlinear_global_avgpool(x, 0.05, zp, 0.02, -1 if dt == I8 else 9)
+    assert np.array_equal(got, want)
+    assert len(np.unique(want)) > 16
+
+
+@pytest.mark.parametrize("dt", [I8, U8])
 def test_maxpool_q8(ctx, oracle, dt):
     x = q(np.random.default_rng(6), (2, 16, 13, 13), dt)
     for args in (((2, 2), (2, 2), (1, 1), (0, 0, 0, 0), "NOTSET"), ((2, 2), (1, 1), (1, 1), (0, 0, 0, 0), "SAME_UPPER"),
@@ -176,6 +188,10 @@ DW_QCONV = [
     (1, 9, 4, 40, 1, I8, I8, -1, 0, True, False, "relu6"),        # four rows, 5 lanes of 8 per plane
     (2, 3, 5, 64, 1, I8, U8, 0, 9, True, True, None),             # five rows
     (1, 2, 9, 128, 1, U8, I8, 200, 0, True, True, None),          # widest plane the kernel takes
+    (3, 40, 28, 28, 2, I8, I8, 0, 0, True, True, "relu6"),        # stride 2 from whole-word rows onto 14 x 14: only the output is staged
+    (2, 12, 12, 20, 2, U8, U8, 5, 3, True, True, None),           # the same onto 6 x 10
+    (4, 7, 9, 9, 1, I8, I8, 2, 0, True, True, "relu"),            # 81-byte planes: a word spans two planes (flat form)
+    (3, 10, 6, 7, 1, U8, I8, 130, 0, True, False, None),          # 42-byte planes, uint8 input
 ]
 
 

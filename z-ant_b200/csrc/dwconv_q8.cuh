@@ -91,7 +91,9 @@ __device__ __forceinline__ uint32_t dw_load_unaligned(const QDwArgs& p, long lon
 // (pad bytes = the input zero point), the sliding-row arithmetic then reads aligned words from there and writes its
 // packed output words into a padded output image in shared memory, and a last phase copies the output rows out.  Global
 // memory is touched by row-wise byte copies of consecutive rows only; the arithmetic is that of the aligned form.
-template <int STRIDE, bool XU8, bool LEAN, bool ALIGNED, bool SMEM = false>
+// SIN: the input planes are staged too; false with SMEM = true is the form for input rows of whole words (aligned loads
+// straight from global memory) whose OUTPUT rows are not (stride 2 from 28 x 28 to 14 x 14): only the output is staged.
+template <int STRIDE, bool XU8, bool LEAN, bool ALIGNED, bool SMEM = false, bool SIN = SMEM>
 __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
     extern __shared__ __align__(16) uint8_t dw_smem[];
     const int lane = threadIdx.x & 31;
@@ -100,21 +102,22 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
     const int sub = lane >> p.log2LW, col = lane & (LW - 1);
     const int warps = (gridDim.x * blockDim.x) >> 5;
     const int groups = (p.planes + ppw - 1) / ppw;
-    const int Wp = SMEM ? (p.W + 7) / 8 * 8 : p.W;           // padded row pitches of the shared-memory images
+    const int Wp = SIN ? (p.W + 7) / 8 * 8 : p.W;            // padded row pitches of the shared-memory images
     const int OWp = SMEM ? (p.OW + 3) / 4 * 4 : p.OW;
-    const int in_words = SMEM ? Wp >> 2 : p.W >> 2;          // 4-byte words per input row
+    const int in_words = SIN ? Wp >> 2 : p.W >> 2;           // 4-byte words per input row
     const bool col_ok = col * 4 < p.OW;
     const int out_valid = p.OW - col * 4;                    // output columns of this lane (>= 4: all)
     const int wib = threadIdx.x >> 5;                        // warp in block
     const int P = 8 * ppw;                                   // planes per CTA pass (SMEM)
     uint8_t* const s_in = dw_smem;
-    uint8_t* const s_out = dw_smem + (size_t)P * p.H * Wp;
+    uint8_t* const s_out = dw_smem + (SIN ? (size_t)P * p.H * Wp : 0);
     const int g_first = SMEM ? (int)blockIdx.x * 8 + wib : (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5);
     const int g_step = SMEM ? (int)gridDim.x * 8 : warps;
     for (int g = g_first; SMEM ? (g - wib < groups) : (g < groups); g += g_step) {
         const int plane = g * ppw + sub;
         const bool live = plane < p.planes && col_ok;
-        if (SMEM) {
+        if (SMEM && !SIN) __syncthreads();                       // the previous pass's copy-out has left the output image
+        if (SIN) {
             // phase 1: the pass's planes are one contiguous run of bytes in global memory (it starts at a multiple of
             // 8 planes, hence at a word boundary): consecutive threads load consecutive words and scatter their bytes
             // into the padded image.  The pad columns are written once, before the first pass.
@@ -145,7 +148,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
         const float m = __ldg(p.mult + c);
         const int b = __ldg(p.bias + c);
         const int pl_local = wib * ppw + sub;                 // SMEM: this lane's plane within the pass
-        const uint32_t* xin = SMEM ? reinterpret_cast<const uint32_t*>(s_in + (size_t)pl_local * p.H * Wp)
+        const uint32_t* xin = SIN ? reinterpret_cast<const uint32_t*>(s_in + (size_t)pl_local * p.H * Wp)
                                    : reinterpret_cast<const uint32_t*>(p.x + (size_t)(live ? plane : 0) * p.H * p.W);
         uint32_t* yout = SMEM ? reinterpret_cast<uint32_t*>(s_out + (size_t)pl_local * p.OH * OWp) + col
                               : reinterpret_cast<uint32_t*>(p.y + (size_t)(live ? plane : 0) * p.OH * p.OW) + col;
@@ -172,7 +175,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
             // are issued before this trip's arithmetic so that their latency is covered
             auto load_row = [&](int ih) -> uint32_t {
                 if (!(live && ih >= 0 && ih < p.H)) return p.pad_word;
-                if (SMEM) return xin[ih * in_words + col];
+                if (SIN) return xin[ih * in_words + col];
                 if (ALIGNED) return __ldg(xin + (size_t)ih * in_words + col);
                 return dw_load_unaligned(p, xplane + (long long)ih * p.W + col * 4, p.W - col * 4);
             };
@@ -213,7 +216,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
             const bool c0 = live && col * 8 < p.W, c1 = live && col * 8 + 4 < p.W;
             auto load_w = [&](int ih, int k, bool on) -> uint32_t {
                 if (!(on && ih < p.H)) return p.pad_word;
-                if (SMEM) return xin[ih * in_words + col * 2 + k];
+                if (SIN) return xin[ih * in_words + col * 2 + k];
                 if (ALIGNED) return __ldg(xin + (size_t)ih * in_words + col * 2 + k);
                 return dw_load_unaligned(p, xplane + (long long)ih * p.W + col * 8 + k * 4, p.W - col * 8 - k * 4);
             };
@@ -352,6 +355,113 @@ __global__ void __launch_bounds__(256) qdwconv3x3_s1w8_kernel(const QDwArgs p) {
     }
 }
 
+// Stride 1 on planes whose rows are not whole words (14 x 14, 7 x 7, odd sizes), "flat" form.  The tensor is one run of
+// bytes and a thread owns one aligned 4-byte word of the OUTPUT: four consecutive flat positions, which may lie in two
+// rows or even two planes.  Output position f reads input bytes f - W - 1 .. f - W + 1, f - 1 .. f + 1 and
+// f + W - 1 .. f + W + 1, so the three filter rows of a word are three 6-byte runs of the input at fixed distances from
+// the word: two or three aligned words each (L1 serves the overlap between neighbouring threads), a funnel shift to
+// the run's first byte and three byte permutes give the four 3-byte windows.  Taps that fall outside the plane
+// (first / last row, first / last column) are replaced by the input zero point through per-thread byte masks.
+// The pattern of rows, columns and planes within a word repeats every lcm(H*W, 4) bytes: a thread keeps its position
+// within that period for the whole launch (the masks are computed once) and strides over the tensor period by period.
+// Loads and stores are whole aligned words, consecutive threads touch consecutive words.
+// TWO: a word may span two planes (H*W is not a multiple of 4), i.e. two channels with their own weights and constants.
+template <bool XU8, bool LEAN, bool TWO>
+__global__ void __launch_bounds__(256) qdwconv3x3_flat_kernel(const QDwArgs p, int Lw, int Lp, int kgroups) {
+    const int t = threadIdx.x;
+    if (t >= Lw * kgroups) return;
+    const int P = p.H * p.W;
+    const int g = t / Lw, wj = t - g * Lw;
+    // per-thread geometry of the word's four bytes
+    uint32_t m[3][4];
+    int second = 4;                        // first byte that belongs to the word's second plane (4: none)
+    int pp0 = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int fb = 4 * wj + k, pl = fb / P, f = fb - pl * P;
+        const int row = f / p.W, col = f - row * p.W;
+        if (k == 0) pp0 = pl;
+        else if (pl != pp0 && second == 4) second = k;
+        const uint32_t cm = (col > 0 ? 0x000000ffu : 0u) | 0x0000ff00u | (col < p.W - 1 ? 0x00ff0000u : 0u);
+        m[0][k] = row > 0 ? cm : 0u; m[1][k] = cm; m[2][k] = row < p.H - 1 ? cm : 0u;
+    }
+    // the three runs start o = (r - 1) * W - 1 bytes from the word: word offset q, byte rsh within it
+    int q[3]; uint32_t rsh[3];
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+        const int o = (r - 1) * p.W - 1;
+        q[r] = o >= 0 ? o >> 2 : -((3 - o) >> 2);
+        rsh[r] = (uint32_t)(o - 4 * q[r]);
+    }
+    const int NB = p.planes * P;                         // bytes of the tensor (the host admits less than 2^31)
+    const int NW = (NB + 3) >> 2;
+    const uint32_t* x32 = reinterpret_cast<const uint32_t*>(p.x);
+    uint32_t* y32 = reinterpret_cast<uint32_t*>(p.y);
+    const int step_planes = (int)gridDim.x * kgroups * Lp;
+    const int stepC = step_planes % p.C;
+    int cA = (int)(((long long)((int)blockIdx.x * kgroups + g) * Lp + pp0) % p.C);
+    const uint32_t lo4 = p.act == ZANT_QACT_NONE ? 0x80808080u : 0u;
+    const uint32_t hi4 = p.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(p.six & 255) : 0x7f7f7f7fu;
+    const Requant rq{p.y_scale, p.y_zp, p.act, p.lut};
+    for (int J = ((int)blockIdx.x * kgroups + g) * Lw + wj; J < NW; J += (int)gridDim.x * kgroups * Lw) {
+        // channel constants of the word's plane(s)
+        const int cB = cA + 1 == p.C ? 0 : cA + 1;
+        uint32_t wa[3], wb[3];
+        float mA, mB; int bA, bB;
+#pragma unroll
+        for (int r = 0; r < 3; ++r) wa[r] = __ldg(p.wrow + cA * 3 + r);
+        mA = __ldg(p.mult + cA); bA = __ldg(p.bias + cA);
+        if (TWO) {
+#pragma unroll
+            for (int r = 0; r < 3; ++r) wb[r] = __ldg(p.wrow + cB * 3 + r);
+            mB = __ldg(p.mult + cB); bB = __ldg(p.bias + cB);
+        }
+        cA += stepC; if (cA >= p.C) cA -= p.C;
+        // words whose every load lies inside the tensor take the plain loads
+        const bool interior = J + q[0] >= 0 && (long long)(J + q[2] + 3) * 4 <= (long long)NB;
+        auto ldw = [&](int idx) -> uint32_t {
+            if (interior) return __ldg(x32 + idx);
+            if (idx < 0 || idx >= NW) return p.pad_word;
+            if ((long long)(idx + 1) * 4 <= (long long)NB) return __ldg(x32 + idx);
+            uint32_t v = 0;
+            for (int i = 0; idx * 4 + i < NB; ++i) v |= (uint32_t)__ldg(p.x + (size_t)idx * 4 + i) << (8 * i);
+            return v;
+        };
+        int acc[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[k] = (TWO && k >= second) ? bB : bA;
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            const uint32_t A = ldw(J + q[r]), B = ldw(J + q[r] + 1);
+            const uint32_t C = rsh[r] == 3u ? ldw(J + q[r] + 2) : 0u;
+            const uint32_t X0 = __funnelshift_r(A, B, 8u * rsh[r]), X1 = __funnelshift_r(B, C, 8u * rsh[r]);
+            const uint32_t w[4] = {X0, __byte_perm(X0, X1, 0x4321), __byte_perm(X0, X1, 0x5432), __byte_perm(X0, X1, 0x6543)};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t v = (w[k] & m[r][k]) | (p.pad_word & ~m[r][k]);
+                acc[k] = dw_dp4a<XU8>(v, (TWO && k >= second) ? wb[r] : wa[r], acc[k]);
+            }
+        }
+        uint32_t pk;
+        if (LEAN) {
+            pk = pack_sat_s8x4(rq_round(acc[0], mA), rq_round(acc[1], (TWO && 1 >= second) ? mB : mA),
+                               rq_round(acc[2], (TWO && 2 >= second) ? mB : mA), rq_round(acc[3], (TWO && 3 >= second) ? mB : mA));
+            pk = __vmins4(__vmaxs4(pk, lo4), hi4);
+            if (p.lut) pk = lut4(p.lut, pk);
+        } else {
+            pk = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float mk = (TWO && k >= second) ? mB : mA;
+                const int qv = p.out_u8 ? requant_one<true>(acc[k], mk, rq) : requant_one<false>(acc[k], mk, rq);
+                pk |= (uint32_t)(qv & 255) << (8 * k);
+            }
+        }
+        if ((long long)J * 4 + 4 <= (long long)NB) y32[J] = pk;
+        else for (int i = 0; J * 4 + i < NB; ++i) p.y[(size_t)J * 4 + i] = (uint8_t)(pk >> (8 * i));
+    }
+}
+
 // Shapes the kernel covers: 3x3, group == channels == filters, pads 1 on every side, dilation 1,
 // stride 1 or 2 on both axes (even sizes for stride 2), at most 128 output columns, weight zero points 0.
 inline bool qdwconv_eligible(const ConvGeom& g, bool w_zp_all_zero) {
@@ -390,19 +500,24 @@ inline int32_t qdwconv_launch_s(zant_ctx* ctx, const QDwArgs& a, int grid, bool 
 }
 
 template <int STRIDE, bool XU8, bool LEAN>
-inline int32_t qdwconv_launch_smem_t(zant_ctx* ctx, const QDwArgs& a, int grid, size_t smem) {
-    ZB_SMEM_ATTR(ctx, (qdwconv3x3_kernel<STRIDE, XU8, LEAN, true, true>), 96 * 1024);
-    qdwconv3x3_kernel<STRIDE, XU8, LEAN, true, true><<<grid, 256, smem, ctx->stream>>>(a);
+inline int32_t qdwconv_launch_smem_t(zant_ctx* ctx, const QDwArgs& a, int grid, size_t smem, bool stage_in) {
+    if (stage_in) {
+        ZB_SMEM_ATTR(ctx, (qdwconv3x3_kernel<STRIDE, XU8, LEAN, true, true, true>), 96 * 1024);
+        qdwconv3x3_kernel<STRIDE, XU8, LEAN, true, true, true><<<grid, 256, smem, ctx->stream>>>(a);
+    } else {
+        ZB_SMEM_ATTR(ctx, (qdwconv3x3_kernel<STRIDE, XU8, LEAN, true, true, false>), 96 * 1024);
+        qdwconv3x3_kernel<STRIDE, XU8, LEAN, true, true, false><<<grid, 256, smem, ctx->stream>>>(a);
+    }
     return check_launch(ctx, "qdwconv3x3_kernel<smem>");
 }
 
-inline int32_t qdwconv_launch_smem(zant_ctx* ctx, const QDwArgs& a, int grid, size_t smem, int stride, bool x_u8, bool lean) {
+inline int32_t qdwconv_launch_smem(zant_ctx* ctx, const QDwArgs& a, int grid, size_t smem, int stride, bool x_u8, bool lean, bool stage_in) {
     if (stride == 1) {
-        if (x_u8) return lean ? qdwconv_launch_smem_t<1, true, true>(ctx, a, grid, smem) : qdwconv_launch_smem_t<1, true, false>(ctx, a, grid, smem);
-        return lean ? qdwconv_launch_smem_t<1, false, true>(ctx, a, grid, smem) : qdwconv_launch_smem_t<1, false, false>(ctx, a, grid, smem);
+        if (x_u8) return lean ? qdwconv_launch_smem_t<1, true, true>(ctx, a, grid, smem, stage_in) : qdwconv_launch_smem_t<1, true, false>(ctx, a, grid, smem, stage_in);
+        return lean ? qdwconv_launch_smem_t<1, false, true>(ctx, a, grid, smem, stage_in) : qdwconv_launch_smem_t<1, false, false>(ctx, a, grid, smem, stage_in);
     }
-    if (x_u8) return lean ? qdwconv_launch_smem_t<2, true, true>(ctx, a, grid, smem) : qdwconv_launch_smem_t<2, true, false>(ctx, a, grid, smem);
-    return lean ? qdwconv_launch_smem_t<2, false, true>(ctx, a, grid, smem) : qdwconv_launch_smem_t<2, false, false>(ctx, a, grid, smem);
+    if (x_u8) return lean ? qdwconv_launch_smem_t<2, true, true>(ctx, a, grid, smem, stage_in) : qdwconv_launch_smem_t<2, true, false>(ctx, a, grid, smem, stage_in);
+    return lean ? qdwconv_launch_smem_t<2, false, true>(ctx, a, grid, smem, stage_in) : qdwconv_launch_smem_t<2, false, false>(ctx, a, grid, smem, stage_in);
 }
 
 // x and y must be 4-byte aligned (the caller checks with qdwconv_ptr_ok).
@@ -442,13 +557,35 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
         }
     }
     const bool aligned = g.W % 4 == 0 && g.OW % 4 == 0;
+    if (!aligned && g.sh == 1) {
+        // rows that are not whole words, stride 1: the flat form, when its period fits a CTA
+        const long long P = (long long)g.H * g.W, nb = (long long)a.planes * P;
+        const int Lp = P % 4 == 0 ? 1 : (P % 2 == 0 ? 2 : 4);
+        const long long Lw = P * Lp / 4;
+        if (P >= 8 && Lw <= 256 && nb < 0x7fffffffLL - 64) {      // P >= 8: a word spans at most two planes
+            const int kg = (int)std::max<long long>(1, 256 / Lw);
+            const long long periods = ((nb + 3) / 4 + Lw - 1) / Lw;
+            const int fgrid = (int)std::min<long long>((periods + kg - 1) / kg, (long long)ctx->sm_count * 8);
+            auto go = [&](auto kernel) -> int32_t {
+                kernel<<<fgrid, 256, 0, ctx->stream>>>(a, (int)Lw, Lp, kg);
+                return check_launch(ctx, "qdwconv3x3_flat_kernel");
+            };
+            if (Lp == 1) {
+                if (x_u8) return lean ? go(qdwconv3x3_flat_kernel<true, true, false>) : go(qdwconv3x3_flat_kernel<true, false, false>);
+                return lean ? go(qdwconv3x3_flat_kernel<false, true, false>) : go(qdwconv3x3_flat_kernel<false, false, false>);
+            }
+            if (x_u8) return lean ? go(qdwconv3x3_flat_kernel<true, true, true>) : go(qdwconv3x3_flat_kernel<true, false, true>);
+            return lean ? go(qdwconv3x3_flat_kernel<false, true, true>) : go(qdwconv3x3_flat_kernel<false, false, true>);
+        }
+    }
     if (!aligned) {
         // rows that are not whole words: stage the planes through shared memory when a pass (8 warps x planes per warp) fits
+        const bool stage_in = g.W % 4 != 0;      // input rows of whole words are read straight from global memory
         const int Wp = (g.W + 7) / 8 * 8, OWp = (g.OW + 3) / 4 * 4;
-        const size_t smem = (size_t)8 * ppw * ((size_t)g.H * Wp + (size_t)g.OH * OWp);
+        const size_t smem = (size_t)8 * ppw * ((stage_in ? (size_t)g.H * Wp : 0) + (size_t)g.OH * OWp);
         if (smem <= 96 * 1024) {
-            const int sgrid = (int)std::min<long long>((groups + 7) / 8, (long long)ctx->sm_count * 4);
-            return qdwconv_launch_smem(ctx, a, sgrid, smem, g.sh, x_u8, lean);
+            const int sgrid = (int)std::min<long long>((groups + 7) / 8, (long long)ctx->sm_count * (stage_in ? 4 : 8));
+            return qdwconv_launch_smem(ctx, a, sgrid, smem, g.sh, x_u8, lean, stage_in);
         }
     }
     if (g.sh == 1) return aligned ? qdwconv_launch_s<1, true>(ctx, a, grid, x_u8, lean) : qdwconv_launch_s<1, false>(ctx, a, grid, x_u8, lean);

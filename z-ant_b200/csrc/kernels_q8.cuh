@@ -283,6 +283,37 @@ __global__ void qgap_k(const void* __restrict__ x, void* __restrict__ y, size_t 
     }
 }
 
+// Small planes (a few dozen bytes, as behind the last stage of a mobile network): one THREAD per plane.  The plane's bytes are
+// summed four at a time (dp4a against ones) from the aligned words that hold them, the bytes of the neighbouring planes
+// masked out of the first and last word; neighbouring threads read neighbouring runs, so every fetched line is used in full.
+// x must be 4-byte aligned; the word that holds the tensor's last bytes is read byte by byte when it is not whole.
+template <bool U8>
+__global__ void qgap_small_k(const uint8_t* __restrict__ x, void* __restrict__ y, size_t planes, int hw,
+                             float x_s, int x_zp, float y_s, int y_zp) {
+    const size_t total = planes * (size_t)hw;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t pidx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; pidx < planes; pidx += stride) {
+        const size_t a = pidx * hw, b = a + hw;                  // the plane's bytes [a, b)
+        int s = 0;
+        for (size_t w = a >> 2; w * 4 < b; ++w) {
+            uint32_t v;
+            if (w * 4 + 4 <= total) v = __ldg(reinterpret_cast<const uint32_t*>(x) + w);
+            else { v = 0; for (size_t i = w * 4; i < total; ++i) v |= (uint32_t)__ldg(x + i) << (8 * (i & 3)); }
+            uint32_t keep = 0xffffffffu;
+            if (w * 4 < a) keep &= 0xffffffffu << (8 * (uint32_t)(a - w * 4));
+            if (w * 4 + 4 > b) keep &= 0xffffffffu >> (8 * (uint32_t)(w * 4 + 4 - b));
+            v &= keep;
+            if (U8) asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(s) : "r"(v), "r"(0x01010101u), "r"(s));
+            else asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(s) : "r"(v), "r"(0x01010101u), "r"(s));
+        }
+        s -= hw * x_zp;
+        const float f = __fmul_rn(__int2float_rn(s), x_s);
+        const float mean = __fdiv_rn(f, (float)hw);
+        const float v = __fdiv_rn(mean, y_s);
+        store_q<U8>(y, pidx, sat_q<U8>(rne_clamped(v) + y_zp));
+    }
+}
+
 // ---------------------------------------------------------------------------- 256-entry table lookup
 __global__ void lut_q8_k(const uint8_t* __restrict__ x, uint8_t* __restrict__ y, size_t n, const uint8_t* __restrict__ lut_g, bool vec) {
     __shared__ uint8_t lut[256];

@@ -271,6 +271,13 @@ inline int32_t run_qadd(zant_ctx* ctx, int32_t dtype, const void* a, float a_s, 
 inline int32_t run_qgap(zant_ctx* ctx, int32_t dtype, const void* x, void* y, size_t planes, int hw,
                         float x_s, int x_zp, float y_s, int y_zp) {
     if (planes == 0) return ZANT_OK;
+    if (hw <= 256 && planes >= 4096 && (reinterpret_cast<uintptr_t>(x) & 3u) == 0) {
+        // many small planes: a thread per plane
+        const int grid = grid_for(planes, 128, ctx->sm_count);
+        if (dtype == ZANT_U8) qgap_small_k<true><<<grid, 128, 0, ctx->stream>>>((const uint8_t*)x, y, planes, hw, x_s, x_zp, y_s, y_zp);
+        else qgap_small_k<false><<<grid, 128, 0, ctx->stream>>>((const uint8_t*)x, y, planes, hw, x_s, x_zp, y_s, y_zp);
+        return check_launch(ctx, "qgap_small_k");
+    }
     const int grid = grid_for(planes * 32, 256, ctx->sm_count);
     if (dtype == ZANT_U8) qgap_k<true><<<grid, 256, 0, ctx->stream>>>(x, y, planes, hw, x_s, x_zp, y_s, y_zp);
     else qgap_k<false><<<grid, 256, 0, ctx->stream>>>(x, y, planes, hw, x_s, x_zp, y_s, y_zp);

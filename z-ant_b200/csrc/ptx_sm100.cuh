@@ -67,6 +67,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// The same wait for roles that are far ahead of the critical path (a loader several stages ahead, an MMA issuer or an
+// epilogue warp of a memory-bound kernel): the thread sleeps between polls, so that a waiting warp issues a few
+// instructions per microsecond instead of competing for issue slots with the warps that do the arithmetic.
+__device__ __forceinline__ bool mbar_wait_sleeping(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                   long long budget_cycles = kWaitBudgetCycles) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t polls = 0;
+    while (true) {
+        __nanosleep(polls < 8u ? 64u : 256u);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++polls & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > budget_cycles) { *abort_flag = 1; return false; }
+        }
+    }
+}
+
 // Generic-proxy writes to shared memory (st.shared) must be fenced before the async proxy
 // (TMA, tcgen05.mma) reads them.
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -99,10 +99,11 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
     const int KC = a.KS * 32;
     const int k_iters = (a.k_steps + a.KS - 1) / a.KS;
     const uint32_t blk_bytes = (uint32_t)KC * 128u;
+    const int live_q = min(4, (a.M - mt * 128 + 31) >> 5);      // lane quarters (of 32 filters) of this CTA's filter tile that exist
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), 1); ptx::mbar_init(empty(s), 1); }
-        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 16); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 4 * live_q); }
         ptx::mbar_init(wfull, 1);
         *abort_flag = 0; *epi_ok = 1; *cp_ok = 1;
         ptx::mbar_fence_init();
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
                 for (int t = j0; t < tiles && alive; t += a.cpm) {
                     const int img = t / a.px_tiles, p0 = (t - img * a.px_tiles) * a.n_px;
                     for (int ki = 0; ki < k_iters; ++ki) {
-                        if (!ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag)) { alive = false; break; }
+                        if (!ptx::mbar_wait_sleeping(empty(s), ph ^ 1u, abort_flag)) { alive = false; break; }
                         const uint32_t dst = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
                         ptx::mbar_arrive_expect_tx(full(s), (uint32_t)a.PB * blk_bytes);
                         for (int blk = 0; blk < a.PB; ++blk)
@@ -148,14 +149,14 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
             const uint64_t da0 = ptx::smem_desc_kmajor(ptx::smem_u32(sA), 128 * 16, 128);
             int s = 0; uint32_t ph = 0;
             int tile_it = 0;
-            if (!ptx::mbar_wait(wfull, 0, abort_flag)) goto mma_done;
+            if (!ptx::mbar_wait_sleeping(wfull, 0, abort_flag)) goto mma_done;
             for (int t = j0; t < tiles; t += a.cpm, ++tile_it) {
                 const int b = tile_it & 1;
                 const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
-                if (!ptx::mbar_wait(tempty(b), bph ^ 1u, abort_flag)) goto mma_done;
+                if (!ptx::mbar_wait_sleeping(tempty(b), bph ^ 1u, abort_flag)) goto mma_done;
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * 256);
                 for (int ki = 0; ki < k_iters; ++ki) {
-                    if (!ptx::mbar_wait(full(s), ph, abort_flag)) goto mma_done;
+                    if (!ptx::mbar_wait_sleeping(full(s), ph, abort_flag)) goto mma_done;
                     ptx::tc_fence_after();
                     const uint32_t stage0 = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
                     // B = [channel][128 pixels] rows of 128 bytes: eight channels are 1024 bytes, a K step of 32 channels 4096
@@ -185,7 +186,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
             for (int t = j0; t < tiles && alive; t += a.cpm) {
                 const uint8_t* ximg = a.x + (size_t)t * a.C * a.HW;              // one tile per image
                 for (int ki = 0; ki < k_iters; ++ki) {
-                    if (ct == 0) *cp_ok = ptx::mbar_wait(empty(s), ph ^ 1u, abort_flag) ? 1 : 0;
+                    if (ct == 0) *cp_ok = ptx::mbar_wait_sleeping(empty(s), ph ^ 1u, abort_flag) ? 1 : 0;
                     ptx::named_barrier_sync(2, 128);
                     if (!*cp_ok) { alive = false; break; }
                     uint8_t* dst = sStages + (size_t)s * a.stage_bytes;
@@ -230,7 +231,11 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
         // ------------------------------------------------------------------ epilogue: 16 warps; a TMEM lane quarter (32 filters) is
         // served by four warps that take the tile's 32-pixel chunks in turn
         const int quarter = warp & 3, cg = (warp - 2) >> 2;
-        const int e = tid - 64;
+        const bool leader = warp == 4 && lane == 0;                   // a thread of quarter 0, which always exists
+        const uint32_t n_epi = (uint32_t)live_q * 128u;               // epilogue threads that take part (the others return at once)
+        int e = 0;                                                    // index among them: the live warps in ascending order
+        for (int wv = 2; wv < warp; ++wv) e += (wv & 3) < live_q ? 32 : 0;
+        e += lane;
         const int m_local = quarter * 32 + lane, m = mt * 128 + m_local;
         const bool live = m < a.M;
         const float mlt = live ? __ldg(a.mult + m) : 1.0f;
@@ -238,23 +243,23 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
         const Requant rq{a.y_scale, a.y_zp, a.act, a.lut ? sLut : nullptr};
         const uint32_t lo4 = a.act == ZANT_QACT_NONE ? 0x80808080u : 0u;
         const uint32_t hi4 = a.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(a.six & 255) : 0x7f7f7f7fu;
-        const bool quarter_live = mt * 128 + quarter * 32 < a.M;      // a quarter whose 32 filters do not exist only keeps the barriers going
+        const bool quarter_live = quarter < live_q;                   // warps of a quarter whose 32 filters do not exist have nothing to do
         const int rows_here = min(128, a.M - mt * 128);
         int tile_it = 0;
-        for (int t = j0; t < tiles; t += a.cpm, ++tile_it) {
+        for (int t = quarter_live ? j0 : tiles; t < tiles; t += a.cpm, ++tile_it) {
             const int b = tile_it & 1;
             const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
             const int img = t / a.px_tiles, p0 = (t - img * a.px_tiles) * a.n_px;
             const int n_valid = min(a.n_px, a.HW - p0);
             if (a.mode == 0) {
                 int ok = 1;
-                if (lane == 0) ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
+                if (lane == 0) ok = ptx::mbar_wait_sleeping(tfull(b), bph, abort_flag) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
             } else {
                 // the previous tile's bulk copy must have read the staging buffer before anybody overwrites it
-                if (e == 0) { if (a.bulk_out) bulk_wait_read(); *epi_ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0; }
-                ptx::named_barrier_sync(1, 512);
+                if (leader) { if (a.bulk_out) bulk_wait_read(); *epi_ok = ptx::mbar_wait_sleeping(tfull(b), bph, abort_flag) ? 1 : 0; }
+                ptx::named_barrier_sync(1, n_epi);
                 if (!*epi_ok) break;
             }
             ptx::tc_fence_after();
@@ -288,7 +293,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
             // after the wait that precedes the arithmetic it overlaps).
             uint32_t va[16], vb[16];
             int ch = cg;
-            bool has = quarter_live && ch * 32 < n_valid;
+            bool has = ch * 32 < n_valid;
             if (has) ptx::tmem_ld16(taddr + (uint32_t)(ch * 32), va);
             while (has) {
                 uint32_t pk[8];
@@ -332,18 +337,18 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
             if (a.mode != 0) {
                 // the staged block [rows_here][HW] is the image's contiguous run of these filters' planes
                 ptx::fence_proxy_async_smem();
-                ptx::named_barrier_sync(1, 512);
+                ptx::named_barrier_sync(1, n_epi);
                 uint8_t* dst = a.y + ((size_t)img * a.M + (size_t)mt * 128) * a.HW;
                 const int bytes = rows_here * a.HW;
                 if (a.bulk_out) {
-                    if (e == 0) bulk_s2g(dst, ptx::smem_u32(sOut), (uint32_t)bytes);
+                    if (leader) bulk_s2g(dst, ptx::smem_u32(sOut), (uint32_t)bytes);
                 } else {
-                    for (int i = e; i < bytes; i += 512) dst[i] = sOut[i];
-                    ptx::named_barrier_sync(1, 512);
+                    for (int i = e; i < bytes; i += (int)n_epi) dst[i] = sOut[i];
+                    ptx::named_barrier_sync(1, n_epi);
                 }
             }
         }
-        if (a.mode != 0 && a.bulk_out && e == 0) bulk_wait_all();
+        if (a.mode != 0 && a.bulk_out && leader) bulk_wait_all();
     }
 
     if (*abort_flag) {
