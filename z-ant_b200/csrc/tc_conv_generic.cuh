@@ -175,6 +175,7 @@ struct QGemmPrep {
     std::vector<float> mult;       // [N_pad]
     std::vector<int32_t> bias;     // [N_pad], includes -x_zp * sum(w)
     bool tap_major = false;        // K order (tap, channel) instead of the weight tensor's (channel, tap)
+    bool mult_finite = true;       // every multiplier is finite (the lean epilogue's precondition)
 };
 
 // w: [n_out][K] int8 row-major (a convolution's [M][C][KH][KW] weight is exactly that).
@@ -203,6 +204,7 @@ inline void qgemm_prepare(const int8_t* w, int n_out, int K, const float* mult, 
             sum += wr[k];
         }
         p.mult[n] = mult[n];
+        p.mult_finite = p.mult_finite && std::isfinite(mult[n]);
         p.bias[n] = (bias ? bias[n] : 0) - x_zp * sum;
     }
 }
@@ -253,7 +255,8 @@ inline int32_t run_qconv_tc(zant_ctx* ctx, const ConvGeom& g, const void* x, boo
         pa.x = (const uint8_t*)x; pa.a = a_blk; pa.C = g.C; pa.HW = g.H * g.W; pa.M = (int)M; pa.K16 = p.K16;
         pointwise_blocked_kernel<<<dim3((unsigned)m_tiles, (unsigned)((p.K16 + 3) / 4)), 256, 0, ctx->stream>>>(pa);
         ZB_TRY(check_launch(ctx, "pointwise_blocked_kernel"));
-    } else if (p.tap_major && (long long)g.KH * g.KW * ((g.C + 63) / 64) <= 65535) {
+    } else if ((p.tap_major || (g.KH * g.KW == 1 && g.C % 16 == 0)) && (long long)g.KH * g.KW * ((g.C + 63) / 64) <= 65535) {
+        // (with a single tap the two K orders are the same: 1x1 filters on planes that are not whole words come here)
         TapMajorArgs ta{};
         ta.x = (const uint8_t*)x; ta.a = a_blk; ta.g = g; ta.M = (int)M; ta.K16 = p.K16; ta.cgroups = (g.C + 63) / 64; ta.pad_value = x_zp;
         im2col_tapmajor_kernel<<<dim3((unsigned)m_tiles, (unsigned)(g.KH * g.KW * ta.cgroups)), 256, 0, ctx->stream>>>(ta);
@@ -268,6 +271,12 @@ inline int32_t run_qconv_tc(zant_ctx* ctx, const ConvGeom& g, const void* x, boo
     k.a = (const int8_t*)a_blk; k.w = w_blk_dev; k.mult = mult_dev; k.bias = bias_dev; k.y = (int8_t*)y;
     k.M = (int)M; k.N = p.N_pad; k.K16 = p.K16; k.y_scale = rq.y_scale; k.y_zp = rq.y_zp; k.act = rq.act; k.lut = rq.lut; k.status = ctx->status_word;
     k.n_valid = g.M; k.ohw = g.OH * g.OW; k.out_u8 = y_u8 ? 1 : 0;
+    k.lean = (!y_u8 && rq.y_zp == 0 && p.mult_finite) ? 1 : 0;
+    if (k.lean) {
+        float v6 = 6.0f / rq.y_scale;
+        v6 = std::fmin(std::fmax(v6, -512.0f), 511.0f);
+        k.six = std::min(std::max((int)std::nearbyintf(v6), -128), 127);
+    }
     const int tiles = (int)((M + 127) / 128) * (p.N_pad / p.NT);
     if (p.NT == 64) return x_u8 ? launch_tc_gemm<64, 3>(ctx, k, tiles) : launch_tc_gemm<64, 2>(ctx, k, tiles);
     if (p.NT == 128) return x_u8 ? launch_tc_gemm<128, 3>(ctx, k, tiles) : launch_tc_gemm<128, 2>(ctx, k, tiles);

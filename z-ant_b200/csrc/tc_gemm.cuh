@@ -39,6 +39,9 @@ struct TcGemmArgs {
     // MODE & 2 (convolution output): valid columns (output channels), positions per image (OH*OW)
     // and output type; rows are (image, position) and the result is stored NCHW.
     int n_valid; int ohw; int out_u8;
+    // MODE & 2: int8 output with zero point 0 and finite multipliers (host-checked): requantisation by rni and a saturating
+    // pack, the activation as a clamp of the packed codes to [0 | -128, six | 127]
+    int lean; int six;
 };
 
 template <int NT, int KC, int STAGES>
@@ -203,12 +206,34 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constan
                 const Requant rq{a.y_scale, a.y_zp, a.act, a.lut};
                 const int img = grow / a.ohw, pos = grow - img * a.ohw;
                 uint8_t* ybase = reinterpret_cast<uint8_t*>(a.y) + (size_t)img * a.n_valid * a.ohw + pos;
+                const uint32_t lo4 = a.act == ZANT_QACT_NONE ? 0x80808080u : 0u;
+                const uint32_t hi4 = a.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(a.six & 255) : 0x7f7f7f7fu;
 #pragma unroll 1
                 for (int h = 0; h < Cfg::COLS_PER_WARP / 32; ++h) {
+                    const int col0 = n * NT + tcol0 + h * 32;
+                    if (col0 >= a.n_valid) break;                 // the tile's remaining columns are padding
                     uint32_t v[32];
                     ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
                     ptx::tmem_wait_ld();
-                    const int col0 = n * NT + tcol0 + h * 32;
+                    if (a.lean) {
+                        // four columns at a time: constants as vectors, one saturating pack, the activation on the packed word
+                        uint8_t* yc = ybase + (size_t)col0 * a.ohw;
+#pragma unroll
+                        for (int j4 = 0; j4 < 8; ++j4) {
+                            const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
+                            const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
+                            uint32_t w4 = pack_sat_s8x4(rq_round((int)v[j4 * 4 + 0] + b4.x, m4.x), rq_round((int)v[j4 * 4 + 1] + b4.y, m4.y),
+                                                        rq_round((int)v[j4 * 4 + 2] + b4.z, m4.z), rq_round((int)v[j4 * 4 + 3] + b4.w, m4.w));
+                            w4 = __vmins4(__vmaxs4(w4, lo4), hi4);
+                            if (a.lut) w4 = lut4(a.lut, w4);
+                            if (grow < a.M) {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    if (col0 + j4 * 4 + i < a.n_valid) yc[(size_t)(j4 * 4 + i) * a.ohw] = (uint8_t)(w4 >> (8 * i));
+                            }
+                        }
+                        continue;
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int col = col0 + j;
