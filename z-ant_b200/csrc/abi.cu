@@ -787,12 +787,15 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
         pw_conv_prepare(pwp, w, bias, x_zp, w_blk, bf);
         bool finite = true;
         for (float f : mult) finite = finite && std::isfinite(f);
+        std::vector<int32_t> caps;
+        const bool capped = finite && y_dtype == ZANT_I8 && y_zp == 0 && requant_relu_caps(mult.data(), mult.size(), activation, lean_six(y_scale), caps);
         Stager s(ctx);
         const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
         const int iw = s.in(w_blk.data(), w_blk.size()), im = s.in(mult.data(), mult.size() * 4), ib = s.in(bf.data(), bf.size() * 4);
+        const int ic = capped ? s.in(caps.data(), caps.size() * 4) : -1;
         ZB_TRY(s.commit());
         ZB_TRY(pw_conv_run(ctx, pwp, s.ptr<char>(ix), x_dtype == ZANT_U8, s.ptr<int8_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
-                           s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, finite));
+                           s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, finite, capped ? s.ptr<int32_t>(ic) : nullptr));
         return s.finish();
     }
     TcConvPlan tcp;
@@ -814,12 +817,15 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
         qdwconv_prepare(g, w, bias, x_zp, wrow, bf);
         bool finite = true;
         for (float f : mult) finite = finite && std::isfinite(f);
+        std::vector<int32_t> caps;
+        const bool capped = finite && y_dtype == ZANT_I8 && y_zp == 0 && requant_relu_caps(mult.data(), mult.size(), activation, lean_six(y_scale), caps);
         Stager s(ctx);
         const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
         const int iw = s.in(wrow.data(), wrow.size() * 4), im = s.in(mult.data(), mult.size() * 4), ib = s.in(bf.data(), bf.size() * 4);
+        const int ic = capped ? s.in(caps.data(), caps.size() * 4) : -1;
         ZB_TRY(s.commit());
         ZB_TRY(run_qdwconv(ctx, g, s.ptr<char>(ix), x_dtype == ZANT_U8, x_zp, s.ptr<uint32_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
-                           s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, finite));
+                           s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, finite, capped ? s.ptr<int32_t>(ic) : nullptr));
         return s.finish();
     }
     if (qconv_tc_eligible(g, wz_zero) && host_consts) {

@@ -35,6 +35,8 @@ struct QDwArgs {
     float y_scale; int y_zp; int act; int out_u8;
     const uint8_t* lut;       // optional table applied to the output codes (see Requant)
     int six;
+    const int32_t* cap;       // lean epilogue, act_mode 1: per-channel accumulator bound of the activation (requant_relu_caps)
+    int act_mode;             // lean epilogue: 0 no activation, 1 clamp of the accumulator to [0, cap], 2 clamp of the packed codes
 };
 
 template <bool XU8>
@@ -46,12 +48,21 @@ __device__ __forceinline__ int dw_dp4a(uint32_t x, uint32_t w, int acc) {
 }
 
 // Requantises four accumulators of one channel and packs them (little endian = ascending columns).
-template <bool LEAN>
-__device__ __forceinline__ uint32_t dw_requant4(const int acc[4], float m, const QDwArgs& p) {
+// `cp`: the channel's accumulator bound (act_mode 1).  ACC: the kernel takes the accumulator form of the activation (measured
+// faster in the row-sliding kernel, slower in the 8-column and flat ones, which keep the clamp of the packed codes).
+template <bool LEAN, bool ACC = true>
+__device__ __forceinline__ uint32_t dw_requant4(const int acc[4], float m, int cp, const QDwArgs& p) {
     if (LEAN) {
-        uint32_t pk = pack_sat_s8x4(rq_round(acc[0], m), rq_round(acc[1], m), rq_round(acc[2], m), rq_round(acc[3], m));
-        if (p.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
-        if (p.act == ZANT_QACT_RELU6) pk = __vmins4(pk, 0x01010101u * (uint32_t)(p.six & 255));
+        uint32_t pk;
+        if (ACC && p.act_mode == 1) {
+            // ReLU / ReLU6 as a clamp of the accumulator: one instruction per value
+            pk = pack_sat_s8x4(rq_round(__viaddmin_s32_relu(acc[0], 0, cp), m), rq_round(__viaddmin_s32_relu(acc[1], 0, cp), m),
+                               rq_round(__viaddmin_s32_relu(acc[2], 0, cp), m), rq_round(__viaddmin_s32_relu(acc[3], 0, cp), m));
+        } else {
+            pk = pack_sat_s8x4(rq_round(acc[0], m), rq_round(acc[1], m), rq_round(acc[2], m), rq_round(acc[3], m));
+            if (p.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
+            if (p.act == ZANT_QACT_RELU6) pk = __vmins4(pk, 0x01010101u * (uint32_t)(p.six & 255));
+        }
         if (p.lut) pk = lut4(p.lut, pk);
         return pk;
     }
@@ -147,6 +158,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
         const uint32_t k0 = __ldg(p.wrow + c * 3), k1 = __ldg(p.wrow + c * 3 + 1), k2 = __ldg(p.wrow + c * 3 + 2);
         const float m = __ldg(p.mult + c);
         const int b = __ldg(p.bias + c);
+        const int cp = p.act_mode == 1 ? __ldg(p.cap + c) : 0x7fffffff;
         const int pl_local = wib * ppw + sub;                 // SMEM: this lane's plane within the pass
         const uint32_t* xin = SIN ? reinterpret_cast<const uint32_t*>(s_in + (size_t)pl_local * p.H * Wp)
                                    : reinterpret_cast<const uint32_t*>(p.x + (size_t)(live ? plane : 0) * p.H * p.W);
@@ -205,7 +217,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
                     // output row ih - 1 has now seen its three input rows
                     const int oh = ih - 1;
                     if (oh >= 0 && oh < p.OH) {
-                        store_row(oh, dw_requant4<LEAN>(a_prev, m, p));
+                        store_row(oh, dw_requant4<LEAN>(a_prev, m, cp, p));
                     }
                     a_prev[0] = a_prev[1] = a_prev[2] = a_prev[3] = b;   // the slot becomes output row ih + 2
                 }
@@ -252,7 +264,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_kernel(const QDwArgs p) {
                         nxt[2] = dw_dp4a<XU8>(w2, k0, nxt[2]); nxt[3] = dw_dp4a<XU8>(w3, k0, nxt[3]);
                     }
                 }
-                store_row(oh, dw_requant4<LEAN>(cur, m, p));
+                store_row(oh, dw_requant4<LEAN>(cur, m, cp, p));
             }
         }
         if (SMEM) {
@@ -321,7 +333,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_s1w8_kernel(const QDwArgs p) {
             }
         };
         auto emit = [&](int* row) {                          // requantise, store, and recycle the slot
-            const uint2 pk = make_uint2(dw_requant4<LEAN>(row, m, p), dw_requant4<LEAN>(row + 4, m, p));
+            const uint2 pk = make_uint2(dw_requant4<LEAN, false>(row, m, 0, p), dw_requant4<LEAN, false>(row + 4, m, 0, p));
             if (live) *yr = pk;
             yr += wu2;
 #pragma unroll
@@ -446,7 +458,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_flat_kernel(const QDwArgs p, i
         if (LEAN) {
             pk = pack_sat_s8x4(rq_round(acc[0], mA), rq_round(acc[1], (TWO && 1 >= second) ? mB : mA),
                                rq_round(acc[2], (TWO && 2 >= second) ? mB : mA), rq_round(acc[3], (TWO && 3 >= second) ? mB : mA));
-            pk = __vmins4(__vmaxs4(pk, lo4), hi4);
+            if (p.act_mode != 0) pk = __vmins4(__vmaxs4(pk, lo4), hi4);
             if (p.lut) pk = lut4(p.lut, pk);
         } else {
             pk = 0;
@@ -524,7 +536,7 @@ inline int32_t qdwconv_launch_smem(zant_ctx* ctx, const QDwArgs& a, int grid, si
 inline bool qdwconv_ptr_ok(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
 
 inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool x_u8, int x_zp, const uint32_t* wrow_dev, const float* mult_dev,
-                           const int32_t* bias_dev, void* y, bool y_u8, const Requant& rq, bool mult_finite) {
+                           const int32_t* bias_dev, void* y, bool y_u8, const Requant& rq, bool mult_finite, const int32_t* cap_dev = nullptr) {
     QDwArgs a{};
     a.x = (const uint8_t*)x; a.y = (uint8_t*)y; a.wrow = wrow_dev; a.mult = mult_dev; a.bias = bias_dev;
     a.planes = g.N * g.C; a.C = g.C; a.H = g.H; a.W = g.W; a.OH = g.OH; a.OW = g.OW;
@@ -534,11 +546,9 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
     a.pad_word = 0x01010101u * (uint32_t)(x_zp & 255);
     a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0; a.lut = rq.lut;
     const bool lean = !y_u8 && rq.y_zp == 0 && mult_finite;
-    if (lean) {
-        float v = 6.0f / rq.y_scale;
-        v = std::fmin(std::fmax(v, -512.0f), 511.0f);
-        a.six = std::min(std::max((int)std::nearbyintf(v), -128), 127);
-    }
+    if (lean) a.six = lean_six(rq.y_scale);
+    a.cap = cap_dev;
+    a.act_mode = rq.act == ZANT_QACT_NONE ? 0 : (cap_dev ? 1 : 2);
     const int ppw = 32 >> a.log2LW;
     const long long groups = ((long long)a.planes + ppw - 1) / ppw;
     const int grid = (int)std::min<long long>((groups + 7) / 8, (long long)ctx->sm_count * 16);

@@ -4,7 +4,10 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <cmath>
 #include <cstdint>
+#include <vector>
 
 #include "geometry.hpp"
 
@@ -88,6 +91,38 @@ __device__ __forceinline__ int requant_one(int acc, float M, const Requant& r) {
 // instruction saturates to [-128,127]; for zero point 0 that equals
 // sat(rne(clamp(v,-512,511)) + 0) for every v, so the results are bit-identical.
 __device__ __forceinline__ int rq_round(int acc, float M) { return __float2int_rn(__fmul_rn(__int2float_rn(acc), M)); }
+
+// ReLU / ReLU6 of the lean epilogues moved in front of the requantisation.  With a positive multiplier
+// r(a) = rne(fl(float(a) * M)) is non-decreasing in the accumulator a and r(0) = 0, so for int8 codes with zero point 0
+//     clamp(sat8(r(a)), 0, six)  ==  sat8(r(clamp(a, 0, cap)))      where cap = the smallest a >= 0 with r(a) >= six,
+// provided r(cap) == six (the codes do not jump over six: any multiplier below 1 qualifies).  clamp(a + bias, 0, cap) is
+// ONE instruction (__viaddmin_s32_relu), against several per packed word for byte-wise max / min on the finished codes.
+// Fills cap[m] per filter (INT_MAX: no upper clamp - plain ReLU, a six that saturates, or codes that never reach six) and
+// returns false when some filter does not qualify (the caller then clamps the packed codes instead).
+inline bool requant_relu_caps(const float* mult, size_t n, int act, int six, std::vector<int32_t>& cap) {
+    cap.assign(n, 0x7fffffff);
+    if (act != ZANT_QACT_RELU && act != ZANT_QACT_RELU6) return false;
+    for (size_t m = 0; m < n; ++m) {
+        const float M = mult[m];
+        if (!(M > 0.0f) || !std::isfinite(M)) return false;
+        if (act != ZANT_QACT_RELU6 || six >= 127) continue;
+        auto r = [M](long long a) { return nearbyintf((float)(int)a * M); };      // the device's int -> float, multiply, rne
+        if (r(0x7fffffffLL) < (float)six) continue;
+        long long lo = 0, hi = 0x7fffffffLL;                                      // r(lo) < six unless six == 0; r(hi) >= six
+        if (r(0) >= (float)six) hi = 0;
+        while (lo < hi) { const long long mid = lo + (hi - lo) / 2; if (r(mid) >= (float)six) hi = mid; else lo = mid + 1; }
+        if (r(hi) != (float)six) return false;
+        cap[m] = (int32_t)hi;
+    }
+    return true;
+}
+
+// sat8(rne(6 / y_scale)): the code of 6.0 for int8 outputs with zero point 0 (the lean epilogues' ReLU6 bound)
+inline int lean_six(float y_scale) {
+    float v = 6.0f / y_scale;
+    v = std::fmin(std::fmax(v, -512.0f), 511.0f);
+    return std::min(std::max((int)std::nearbyintf(v), -128), 127);
+}
 
 // bytes (little endian) = sat8(a0), sat8(a1), sat8(a2), sat8(a3)
 __device__ __forceinline__ uint32_t pack_sat_s8x4(int a0, int a1, int a2, int a3) {

@@ -573,10 +573,13 @@ static int32_t build_qconv(zant_plan* pl, const PlanNode& n, QConvFusion& fz) {
         bool finite = true;
         for (float f : mult) finite = finite && std::isfinite(f);
         const int aw = pl->add_aux(w_blk.data(), w_blk.size()), am = pl->add_aux(mult.data(), mult.size() * 4), ab = pl->add_aux(bf.data(), bf.size() * 4);
+        std::vector<int32_t> caps;
+        const bool capped = finite && yd == ZANT_I8 && rq0.y_zp == 0 && requant_relu_caps(mult.data(), mult.size(), rq0.act, lean_six(rq0.y_scale), caps);
+        const int ac = capped ? pl->add_aux(caps.data(), caps.size() * 4) : -1;
         push("QLinearConv(tc-pointwise)" + tail, [=]() {
             if (!pw_conv_ptr_ok(pl->ptr(x), pl->ptr(y))) return fail(ZANT_E_INVALID_INPUT, "pointwise QLinearConv buffers must be 16-byte (input) and 32-byte (output) aligned");
             return pw_conv_run(ctx, pwp, pl->ptr(x), xd == ZANT_U8, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
-                               (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), finite);
+                               (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), finite, ac >= 0 ? (const int32_t*)pl->aux(ac) : nullptr);
         });
         return ZANT_OK;
     }
@@ -608,10 +611,13 @@ static int32_t build_qconv(zant_plan* pl, const PlanNode& n, QConvFusion& fz) {
         bool finite = true;
         for (float f : mult) finite = finite && std::isfinite(f);
         const int aw = pl->add_aux(wrow.data(), wrow.size() * 4), am = pl->add_aux(mult.data(), mult.size() * 4), ab = pl->add_aux(bf.data(), bf.size() * 4);
+        std::vector<int32_t> caps;
+        const bool capped = finite && yd == ZANT_I8 && rq0.y_zp == 0 && requant_relu_caps(mult.data(), mult.size(), rq0.act, lean_six(rq0.y_scale), caps);
+        const int ac = capped ? pl->add_aux(caps.data(), caps.size() * 4) : -1;
         push("QLinearConv(depthwise)" + tail, [=]() {
             if (!qdwconv_ptr_ok(pl->ptr(x)) || !qdwconv_ptr_ok(pl->ptr(y))) return fail(ZANT_E_INVALID_INPUT, "depthwise QLinearConv buffers must be 4-byte aligned");
             return run_qdwconv(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, (const uint32_t*)pl->aux(aw), (const float*)pl->aux(am),
-                               (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), finite);
+                               (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), finite, ac >= 0 ? (const int32_t*)pl->aux(ac) : nullptr);
         });
         return ZANT_OK;
     }

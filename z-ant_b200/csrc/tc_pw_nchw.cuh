@@ -50,6 +50,8 @@ struct PwConvArgs {
     int wide_store;       // mode 0: every 32-pixel chunk starts at a 32-byte boundary (HW and n_px are multiples of 32)
     int stages, stage_bytes, off_stages, off_out, off_tail;
     float y_scale; int y_zp; int act; int out_u8; int six;
+    const int32_t* cap;   // lean epilogue, act_mode 1: per-filter accumulator bound of the activation (requant_relu_caps)
+    int act_mode;         // lean epilogue: 0 no activation, 1 clamp of the accumulator to [0, cap], 2 clamp of the packed codes
     const uint8_t* lut;
     int* status;
 };
@@ -240,6 +242,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
         const bool live = m < a.M;
         const float mlt = live ? __ldg(a.mult + m) : 1.0f;
         const int bs = live ? __ldg(a.bias + m) : 0;
+        const int cp = (live && a.act_mode == 1) ? __ldg(a.cap + m) : 0x7fffffff;
         const Requant rq{a.y_scale, a.y_zp, a.act, a.lut ? sLut : nullptr};
         const uint32_t lo4 = a.act == ZANT_QACT_NONE ? 0x80808080u : 0u;
         const uint32_t hi4 = a.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(a.six & 255) : 0x7f7f7f7fu;
@@ -270,10 +273,15 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
 #pragma unroll
                 for (int j4 = 0; j4 < 4; ++j4) {
                     if constexpr (LEAN) {
-                        // the activation is a clamp of the packed codes to [lo4, hi4] (the whole int8 range when there is none)
-                        const uint32_t w4 = pack_sat_s8x4(rq_round((int)v[j4 * 4 + 0] + bs, mlt), rq_round((int)v[j4 * 4 + 1] + bs, mlt),
-                                                          rq_round((int)v[j4 * 4 + 2] + bs, mlt), rq_round((int)v[j4 * 4 + 3] + bs, mlt));
-                        pk[j4] = __vmins4(__vmaxs4(w4, lo4), hi4);
+                        if (a.act_mode == 1) {
+                            // ReLU / ReLU6 as a clamp of the accumulator, fused with the bias add
+                            pk[j4] = pack_sat_s8x4(rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 0], bs, cp), mlt), rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 1], bs, cp), mlt),
+                                                   rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 2], bs, cp), mlt), rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 3], bs, cp), mlt));
+                        } else {
+                            const uint32_t w4 = pack_sat_s8x4(rq_round((int)v[j4 * 4 + 0] + bs, mlt), rq_round((int)v[j4 * 4 + 1] + bs, mlt),
+                                                              rq_round((int)v[j4 * 4 + 2] + bs, mlt), rq_round((int)v[j4 * 4 + 3] + bs, mlt));
+                            pk[j4] = a.act_mode == 0 ? w4 : __vmins4(__vmaxs4(w4, lo4), hi4);
+                        }
                     } else {
                         uint32_t w4 = 0;
 #pragma unroll
@@ -472,17 +480,16 @@ inline bool pw_conv_ptr_ok(const void* x, const void* y) {
     return (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0;
 }
 
+// `cap_dev`: per-filter accumulator bounds from requant_relu_caps when that returned true, else null.
 inline int32_t pw_conv_run(zant_ctx* ctx, const PwConvPlan& p, const void* x, bool x_u8, const int8_t* w_blk_dev, const float* mult_dev,
-                           const int32_t* bias_dev, void* y, bool y_u8, const Requant& rq, bool mult_finite) {
+                           const int32_t* bias_dev, void* y, bool y_u8, const Requant& rq, bool mult_finite, const int32_t* cap_dev) {
     PwConvArgs a = p.a;
     a.x = (const uint8_t*)x; a.y = (uint8_t*)y; a.w = w_blk_dev; a.mult = mult_dev; a.bias = bias_dev;
     a.y_scale = rq.y_scale; a.y_zp = rq.y_zp; a.act = rq.act; a.out_u8 = y_u8 ? 1 : 0; a.lut = rq.lut;
     const bool lean = !y_u8 && rq.y_zp == 0 && mult_finite;
-    if (lean) {
-        float v = 6.0f / rq.y_scale;
-        v = std::fmin(std::fmax(v, -512.0f), 511.0f);
-        a.six = std::min(std::max((int)std::nearbyintf(v), -128), 127);
-    }
+    if (lean) a.six = lean_six(rq.y_scale);
+    a.cap = cap_dev;
+    a.act_mode = rq.act == ZANT_QACT_NONE ? 0 : (cap_dev ? 1 : 2);
     a.status = ctx->status_word;
     const int grid = p.m_tiles * a.cpm;
     alignas(64) CUtensorMap x_map{};
