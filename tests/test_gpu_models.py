@@ -86,6 +86,25 @@ def test_small_cnn_int8_with_biases_bit_exact(zb, ctx, oracle, models, scales, a
         assert len(np.unique(want[g.id_of("pool2")])) > 16
 
 
+@pytest.mark.parametrize("zp", [7, 128])
+def test_small_cnn_int8_with_an_input_zero_point(zb, ctx, oracle, models, scales, zp):
+    """uint8 input codes with a non-zero zero point through the fused chain: stage 1 quantises with explicit clamps (zero
+    point 0 takes the conversion + saturating pack alone) and folds -zp * sum(w) into its bias."""
+    batch = 9
+    g = models.small_cnn_int8(batch, act_scales=scales, bias_amplitude=(100, 1000, 5000, 300))
+    assert g.nodes[0]["op"] == "QuantizeLinear" and g.nodes[1]["op"] == "QLinearConv"
+    g.nodes[0]["attrs"]["y_zp"] = zp
+    g.nodes[1]["attrs"]["x_zp"] = zp
+    x = models.small_cnn_input(batch, 321) - (0.25 if zp else 0.0)      # some inputs below zero: the lower clamp matters
+    want = graph_oracle.run(oracle, g, x)
+    plan = zb.Plan(ctx, g, fuse=True)
+    got = plan.run(x)
+    assert any("Fused" in n for n in plan.step_names())
+    assert np.array_equal(got.view(np.uint32), want[g.output].view(np.uint32))
+    plan.close()
+    assert len(np.unique(want[g.id_of("pool1")])) > 16
+
+
 @pytest.mark.parametrize("n_classes,batch", [(1, 3), (3, 33), (8, 17), (9, 40)])
 def test_small_cnn_int8_class_counts_and_ragged_batches(zb, ctx, oracle, models, scales, n_classes, batch):
     """The last fused kernel has one instantiation per block of eight classes, and the batch sizes here end in

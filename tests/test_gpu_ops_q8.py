@@ -268,6 +268,8 @@ POINTWISE_QCONV = [
     (6, 12, 6, 10, 20, U8, I8, 9, 0, False, True, None),            # 60-byte planes, word copies
     (2, 8, 4, 36, 6, I8, I8, 0, 0, True, True, "relu"),             # 144-pixel planes: a second pixel block of 16
     (1, 64, 16, 17, 130, I8, I8, 0, -4, True, True, None),          # 272 pixels: two tiles of 144; non-zero output zero point
+    (2, 32, 28, 28, 96, I8, I8, 0, 0, True, True, "relu6"),         # ReLU6 with a six below 127: the clamp of the accumulator (per-filter bounds)
+    (2, 48, 14, 14, 64, U8, I8, 128, 0, False, True, "relu6"),      # the same on 14 x 14 planes, one multiplier for all filters
 ]
 
 

@@ -156,7 +156,16 @@ __global__ void __launch_bounds__(C1M_THREADS, 3) conv1_mma_relu_pool_kernel(con
         for (int i = tid; i < C1M_G * f4_per_img; i += C1M_THREADS) {
             const int gi = i / f4_per_img, p4 = i - gi * f4_per_img;        // 7 float4 per row
             uint32_t word = 0;
-            if (gi < n_here) {
+            if (gi < n_here && a.x_zp == 0) {
+                // zero point 0: sat_u8(rne(clamp(t, -512, 511))) is the float -> int32 conversion (rne, a NaN gives 0) followed
+                // by the pack instruction's own saturation to [0, 255]; no clamps, no adds (the ALU pipe bounds this kernel)
+                const float4 v = reinterpret_cast<const float4*>(stage[s])[gi * 196 + p4];
+                const int q0 = __float2int_rn(__fdiv_rn(v.x, a.x_scale)), q1 = __float2int_rn(__fdiv_rn(v.y, a.x_scale));
+                const int q2 = __float2int_rn(__fdiv_rn(v.z, a.x_scale)), q3 = __float2int_rn(__fdiv_rn(v.w, a.x_scale));
+                uint32_t hi;
+                asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
+                asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(word) : "r"(q1), "r"(q0), "r"(hi));
+            } else if (gi < n_here) {
                 const float4 v = reinterpret_cast<const float4*>(stage[s])[gi * 196 + p4];
                 // sat_u8(rne(clamp(t, -512, 511)) + zp) == rne(clamp(t, -zp, 255 - zp)) + zp: the bounds are integers
                 // inside [-512, 511] and rounding is monotonic; a NaN becomes the lower bound either way.
