@@ -59,9 +59,8 @@ __device__ __forceinline__ uint32_t dw_requant4(const int acc[4], float m, int c
             pk = pack_sat_s8x4(rq_round(__viaddmin_s32_relu(acc[0], 0, cp), m), rq_round(__viaddmin_s32_relu(acc[1], 0, cp), m),
                                rq_round(__viaddmin_s32_relu(acc[2], 0, cp), m), rq_round(__viaddmin_s32_relu(acc[3], 0, cp), m));
         } else {
-            pk = pack_sat_s8x4(rq_round(acc[0], m), rq_round(acc[1], m), rq_round(acc[2], m), rq_round(acc[3], m));
-            if (p.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
-            if (p.act == ZANT_QACT_RELU6) pk = __vmins4(pk, 0x01010101u * (uint32_t)(p.six & 255));
+            pk = pack_act_s8x4(rq_round(acc[0], m), rq_round(acc[1], m), rq_round(acc[2], m), rq_round(acc[3], m), p.act != ZANT_QACT_NONE,
+                               p.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(p.six & 255) : 0x7f7f7f7fu);
         }
         if (p.lut) pk = lut4(p.lut, pk);
         return pk;
@@ -412,7 +411,6 @@ __global__ void __launch_bounds__(256) qdwconv3x3_flat_kernel(const QDwArgs p, i
     const int step_planes = (int)gridDim.x * kgroups * Lp;
     const int stepC = step_planes % p.C;
     int cA = (int)(((long long)((int)blockIdx.x * kgroups + g) * Lp + pp0) % p.C);
-    const uint32_t lo4 = p.act == ZANT_QACT_NONE ? 0x80808080u : 0u;
     const uint32_t hi4 = p.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(p.six & 255) : 0x7f7f7f7fu;
     const Requant rq{p.y_scale, p.y_zp, p.act, p.lut};
     for (int J = ((int)blockIdx.x * kgroups + g) * Lw + wj; J < NW; J += (int)gridDim.x * kgroups * Lw) {
@@ -456,9 +454,8 @@ __global__ void __launch_bounds__(256) qdwconv3x3_flat_kernel(const QDwArgs p, i
         }
         uint32_t pk;
         if (LEAN) {
-            pk = pack_sat_s8x4(rq_round(acc[0], mA), rq_round(acc[1], (TWO && 1 >= second) ? mB : mA),
-                               rq_round(acc[2], (TWO && 2 >= second) ? mB : mA), rq_round(acc[3], (TWO && 3 >= second) ? mB : mA));
-            if (p.act_mode != 0) pk = __vmins4(__vmaxs4(pk, lo4), hi4);
+            pk = pack_act_s8x4(rq_round(acc[0], mA), rq_round(acc[1], (TWO && 1 >= second) ? mB : mA),
+                               rq_round(acc[2], (TWO && 2 >= second) ? mB : mA), rq_round(acc[3], (TWO && 3 >= second) ? mB : mA), p.act_mode != 0, hi4);
             if (p.lut) pk = lut4(p.lut, pk);
         } else {
             pk = 0;

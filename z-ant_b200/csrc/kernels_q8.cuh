@@ -132,6 +132,22 @@ __device__ __forceinline__ uint32_t pack_sat_s8x4(int a0, int a1, int a2, int a3
     return d;
 }
 
+// bytes (little endian) = satu8(a0) .. satu8(a3), i.e. each clamped to [0, 255]
+__device__ __forceinline__ uint32_t pack_sat_u8x4(int a0, int a1, int a2, int a3) {
+    uint32_t hi, d;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(a3), "r"(a2));
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a1), "r"(a0), "r"(hi));
+    return d;
+}
+
+// Four requantised values as packed int8 codes (zero point 0) under the lean activation.  ReLU / ReLU6: the unsigned
+// saturation of the pack is the lower clamp, one byte-wise unsigned minimum with `hi4` (the upper bound in every byte: the
+// code of 6, or 127) the upper one - byte-wise max / min are several instructions each on this part, so one of them is
+// saved against clamping signed codes from both sides.
+__device__ __forceinline__ uint32_t pack_act_s8x4(int q0, int q1, int q2, int q3, bool relu, uint32_t hi4) {
+    return relu ? __vminu4(pack_sat_u8x4(q0, q1, q2, q3), hi4) : pack_sat_s8x4(q0, q1, q2, q3);
+}
+
 // ReLU on four packed int8 values with zero point 0.
 __device__ __forceinline__ uint32_t relu_s8x4(uint32_t v) { return __vmaxs4(v, 0u); }
 

@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(kSmallcThreads) qconv3x3_smallc_kernel(const S
     // pixel (within a unit) that this lane supplies to MMA nt: column g <-> pixel 2*NTL*(g/2) + 2*nt + g%2
     const int bpix0 = 2 * NTL * (g >> 1) + (g & 1);
     const Requant rq{a.y_scale, a.y_zp, a.act, a.lut};
-    const uint32_t six4 = 0x01010101u * (uint32_t)(a.six & 255);
+    const uint32_t hi4 = a.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(a.six & 255) : 0x7f7f7f7fu;   // upper bound of the lean activation
     const size_t ohw = (size_t)a.OH * a.OW;
     const int words_per_row = a.P >> 2;
     const int tiles = a.N * a.bands;
@@ -153,15 +153,8 @@ __global__ void __launch_bounds__(kSmallcThreads) qconv3x3_smallc_kernel(const S
                     for (int p = 0; p < NTL / 2; ++p) {
                         const int v0 = acc[mt][2 * p][2 * h], v1 = acc[mt][2 * p][2 * h + 1], v2 = acc[mt][2 * p + 1][2 * h], v3 = acc[mt][2 * p + 1][2 * h + 1];
                         if constexpr (LEAN) {
-                            uint32_t pk;
-                            if (a.small_products)
-                                pk = pack_sat_s8x4(tc_conv_round<false>(v0, mult[mt][h]), tc_conv_round<false>(v1, mult[mt][h]),
-                                                   tc_conv_round<false>(v2, mult[mt][h]), tc_conv_round<false>(v3, mult[mt][h]));
-                            else
-                                pk = pack_sat_s8x4(tc_conv_round<true>(v0, mult[mt][h]), tc_conv_round<true>(v1, mult[mt][h]),
-                                                   tc_conv_round<true>(v2, mult[mt][h]), tc_conv_round<true>(v3, mult[mt][h]));
-                            if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
-                            if (a.act == ZANT_QACT_RELU6) pk = __vmins4(pk, six4);
+                            uint32_t pk = pack_act_s8x4(rq_round(v0, mult[mt][h]), rq_round(v1, mult[mt][h]), rq_round(v2, mult[mt][h]), rq_round(v3, mult[mt][h]),
+                                                        a.act != ZANT_QACT_NONE, hi4);
                             if (a.lut) pk = lut4_smem(s_lut, pk);
                             wd[p] = pk;
                         } else {

@@ -499,7 +499,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
         const bool row_live = oh_l < a.BH && ow_l < a.BW;        // this MMA row is an output of the tile
         const int pix_off = oh_l * a.BW + ow_l;
         const size_t ohw = (size_t)a.OH * a.OW;
-        const uint32_t six4 = 0x01010101u * (uint32_t)(a.six & 255);
+        const uint32_t hi4 = a.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(a.six & 255) : 0x7f7f7f7fu;   // upper bound of the lean activation
         // copy-out work split, fixed for the launch: a warp pass covers co_cpp filters x co_lpc lanes
         // (a power of two that holds the vectors of a full tile's run)
         int co_shift = 0;
@@ -565,9 +565,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nchw_kernel(const _
                             const int q1 = tc_conv_round<CL>((int)v[j4 * 4 + 1] + b4[j4].y, m4[j4].y);
                             const int q2 = tc_conv_round<CL>((int)v[j4 * 4 + 2] + b4[j4].z, m4[j4].z);
                             const int q3 = tc_conv_round<CL>((int)v[j4 * 4 + 3] + b4[j4].w, m4[j4].w);
-                            uint32_t w4 = pack_sat_s8x4(q0, q1, q2, q3);
-                            if (a.act != ZANT_QACT_NONE) w4 = relu_s8x4(w4);
-                            if (a.act == ZANT_QACT_RELU6) w4 = __vmins4(w4, six4);
+                            uint32_t w4 = pack_act_s8x4(q0, q1, q2, q3, a.act != ZANT_QACT_NONE, hi4);
                             if (a.lut) w4 = lut4_smem(sLut, w4);
                             pk[j4] = w4;
                         }

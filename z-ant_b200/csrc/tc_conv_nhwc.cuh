@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
         const Requant rq{a.y_scale, a.y_zp, a.act, a.lut};
         const int oh_l = row / a.PW, ow_l = row - oh_l * a.PW;
         const bool row_live = oh_l < a.BH && ow_l < a.BW;
-        const uint32_t six4 = 0x01010101u * (uint32_t)(a.six & 255);
+        const uint32_t hi4 = a.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(a.six & 255) : 0x7f7f7f7fu;   // upper bound of the lean activation
         const int tcol0 = part * cols;
         // With one 64-filter tile a warp serves the same 16 filters in every tile: their constants stay in registers
         // (as broadcast shared-memory loads they would take about a third of the shared-memory pipe's time, which the
@@ -243,10 +243,9 @@ __global__ void __launch_bounds__(kTcConvThreads, 1) tc_conv_nhwc_kernel(const _
                                     m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
                                     b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
                                 }
-                                uint32_t pk = pack_sat_s8x4(tc_conv_round<CL>((int)v[j4 * 4 + 0] + b4.x, m4.x), tc_conv_round<CL>((int)v[j4 * 4 + 1] + b4.y, m4.y),
-                                                            tc_conv_round<CL>((int)v[j4 * 4 + 2] + b4.z, m4.z), tc_conv_round<CL>((int)v[j4 * 4 + 3] + b4.w, m4.w));
-                                if (a.act != ZANT_QACT_NONE) pk = relu_s8x4(pk);
-                                if (a.act == ZANT_QACT_RELU6) pk = __vmins4(pk, six4);
+                                uint32_t pk = pack_act_s8x4(tc_conv_round<CL>((int)v[j4 * 4 + 0] + b4.x, m4.x), tc_conv_round<CL>((int)v[j4 * 4 + 1] + b4.y, m4.y),
+                                                            tc_conv_round<CL>((int)v[j4 * 4 + 2] + b4.z, m4.z), tc_conv_round<CL>((int)v[j4 * 4 + 3] + b4.w, m4.w),
+                                                            a.act != ZANT_QACT_NONE, hi4);
                                 if (a.lut) pk = lut4_smem(sLut, pk);
                                 wd[j4] = pk;
                             }

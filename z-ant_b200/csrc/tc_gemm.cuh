@@ -206,7 +206,6 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constan
                 const Requant rq{a.y_scale, a.y_zp, a.act, a.lut};
                 const int img = grow / a.ohw, pos = grow - img * a.ohw;
                 uint8_t* ybase = reinterpret_cast<uint8_t*>(a.y) + (size_t)img * a.n_valid * a.ohw + pos;
-                const uint32_t lo4 = a.act == ZANT_QACT_NONE ? 0x80808080u : 0u;
                 const uint32_t hi4 = a.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(a.six & 255) : 0x7f7f7f7fu;
 #pragma unroll 1
                 for (int h = 0; h < Cfg::COLS_PER_WARP / 32; ++h) {
@@ -222,9 +221,9 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constan
                         for (int j4 = 0; j4 < 8; ++j4) {
                             const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
                             const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
-                            uint32_t w4 = pack_sat_s8x4(rq_round((int)v[j4 * 4 + 0] + b4.x, m4.x), rq_round((int)v[j4 * 4 + 1] + b4.y, m4.y),
-                                                        rq_round((int)v[j4 * 4 + 2] + b4.z, m4.z), rq_round((int)v[j4 * 4 + 3] + b4.w, m4.w));
-                            w4 = __vmins4(__vmaxs4(w4, lo4), hi4);
+                            uint32_t w4 = pack_act_s8x4(rq_round((int)v[j4 * 4 + 0] + b4.x, m4.x), rq_round((int)v[j4 * 4 + 1] + b4.y, m4.y),
+                                                        rq_round((int)v[j4 * 4 + 2] + b4.z, m4.z), rq_round((int)v[j4 * 4 + 3] + b4.w, m4.w),
+                                                        a.act != ZANT_QACT_NONE, hi4);
                             if (a.lut) w4 = lut4(a.lut, w4);
                             if (grow < a.M) {
 #pragma unroll

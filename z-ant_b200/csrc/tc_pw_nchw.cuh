@@ -244,7 +244,6 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
         const int bs = live ? __ldg(a.bias + m) : 0;
         const int cp = (live && a.act_mode == 1) ? __ldg(a.cap + m) : 0x7fffffff;
         const Requant rq{a.y_scale, a.y_zp, a.act, a.lut ? sLut : nullptr};
-        const uint32_t lo4 = a.act == ZANT_QACT_NONE ? 0x80808080u : 0u;
         const uint32_t hi4 = a.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(a.six & 255) : 0x7f7f7f7fu;
         const bool quarter_live = quarter < live_q;                   // warps of a quarter whose 32 filters do not exist have nothing to do
         const int rows_here = min(128, a.M - mt * 128);
@@ -278,9 +277,8 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
                             pk[j4] = pack_sat_s8x4(rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 0], bs, cp), mlt), rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 1], bs, cp), mlt),
                                                    rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 2], bs, cp), mlt), rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 3], bs, cp), mlt));
                         } else {
-                            const uint32_t w4 = pack_sat_s8x4(rq_round((int)v[j4 * 4 + 0] + bs, mlt), rq_round((int)v[j4 * 4 + 1] + bs, mlt),
-                                                              rq_round((int)v[j4 * 4 + 2] + bs, mlt), rq_round((int)v[j4 * 4 + 3] + bs, mlt));
-                            pk[j4] = a.act_mode == 0 ? w4 : __vmins4(__vmaxs4(w4, lo4), hi4);
+                            pk[j4] = pack_act_s8x4(rq_round((int)v[j4 * 4 + 0] + bs, mlt), rq_round((int)v[j4 * 4 + 1] + bs, mlt),
+                                                   rq_round((int)v[j4 * 4 + 2] + bs, mlt), rq_round((int)v[j4 * 4 + 3] + bs, mlt), a.act_mode != 0, hi4);
                         }
                     } else {
                         uint32_t w4 = 0;
