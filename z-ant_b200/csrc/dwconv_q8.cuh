@@ -343,8 +343,13 @@ __global__ void __launch_bounds__(256) qdwconv3x3_s1w8_kernel(const QDwArgs p) {
         step(padrow, nullptr, nullptr, A);
         step(load(), nullptr, A, B);
         int ih = 1;
-        for (; ih + 2 < p.H; ih += 3) {                      // three input rows per trip: the slots return to their roles
-            const uint2 r0 = load(), r1 = load(), r2 = load();
+        // three input rows per trip (the slots return to their roles); the next trip's rows are requested before this
+        // trip's arithmetic, so that their latency is covered by it
+        uint2 n0 = padrow, n1 = padrow, n2 = padrow;
+        if (ih + 2 < p.H) { n0 = load(); n1 = load(); n2 = load(); }
+        for (; ih + 2 < p.H; ih += 3) {
+            const uint2 r0 = n0, r1 = n1, r2 = n2;
+            if (ih + 5 < p.H) { n0 = load(); n1 = load(); n2 = load(); }
             step(r0, A, B, C); emit(A);                      // A becomes output row ih + 2
             step(r1, B, C, A); emit(B);
             step(r2, C, A, B); emit(C);
