@@ -432,24 +432,36 @@ __global__ void __launch_bounds__(256) qdwconv3x3_flat_kernel(const QDwArgs p, i
             mB = __ldg(p.mult + cB); bB = __ldg(p.bias + cB);
         }
         cA += stepC; if (cA >= p.C) cA -= p.C;
-        // words whose every load lies inside the tensor take the plain loads
-        const bool interior = J + q[0] >= 0 && (long long)(J + q[2] + 3) * 4 <= (long long)NB;
-        auto ldw = [&](int idx) -> uint32_t {
-            if (interior) return __ldg(x32 + idx);
-            if (idx < 0 || idx >= NW) return p.pad_word;
-            if ((long long)(idx + 1) * 4 <= (long long)NB) return __ldg(x32 + idx);
-            uint32_t v = 0;
-            for (int i = 0; idx * 4 + i < NB; ++i) v |= (uint32_t)__ldg(p.x + (size_t)idx * 4 + i) << (8 * i);
-            return v;
-        };
+        // The three runs' words.  Words whose every load lies inside the tensor (all but the first and last few of the launch)
+        // take plain loads in one straight block; the others check every index.
+        uint32_t wA[3], wB[3], wC[3];
+        if (J + q[0] >= 0 && (long long)(J + q[2] + 3) * 4 <= (long long)NB) {
+#pragma unroll
+            for (int r = 0; r < 3; ++r) {
+                const uint32_t* src = x32 + (J + q[r]);
+                wA[r] = __ldg(src); wB[r] = __ldg(src + 1);
+                wC[r] = rsh[r] == 3u ? __ldg(src + 2) : 0u;
+            }
+        } else {
+            auto ldw = [&](int idx) -> uint32_t {
+                if (idx < 0 || idx >= NW) return p.pad_word;
+                if ((long long)(idx + 1) * 4 <= (long long)NB) return __ldg(x32 + idx);
+                uint32_t v = 0;
+                for (int i = 0; idx * 4 + i < NB; ++i) v |= (uint32_t)__ldg(p.x + (size_t)idx * 4 + i) << (8 * i);
+                return v;
+            };
+#pragma unroll
+            for (int r = 0; r < 3; ++r) {
+                wA[r] = ldw(J + q[r]); wB[r] = ldw(J + q[r] + 1);
+                wC[r] = rsh[r] == 3u ? ldw(J + q[r] + 2) : 0u;
+            }
+        }
         int acc[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) acc[k] = (TWO && k >= second) ? bB : bA;
 #pragma unroll
         for (int r = 0; r < 3; ++r) {
-            const uint32_t A = ldw(J + q[r]), B = ldw(J + q[r] + 1);
-            const uint32_t C = rsh[r] == 3u ? ldw(J + q[r] + 2) : 0u;
-            const uint32_t X0 = __funnelshift_r(A, B, 8u * rsh[r]), X1 = __funnelshift_r(B, C, 8u * rsh[r]);
+            const uint32_t X0 = __funnelshift_r(wA[r], wB[r], 8u * rsh[r]), X1 = __funnelshift_r(wB[r], wC[r], 8u * rsh[r]);
             const uint32_t w[4] = {X0, __byte_perm(X0, X1, 0x4321), __byte_perm(X0, X1, 0x5432), __byte_perm(X0, X1, 0x6543)};
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
