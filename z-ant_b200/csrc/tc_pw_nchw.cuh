@@ -269,18 +269,28 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
             uint8_t* yrow = a.y + ((size_t)img * a.M + (size_t)m) * a.HW + p0;
             // 16 accumulators -> four packed words
             auto requant16 = [&](const uint32_t (&v)[16], uint32_t* pk) {
+                if constexpr (LEAN) {
+                    // one (uniform) branch per 16 values, none inside the unrolled loops
+                    if (a.act_mode == 1) {
+                        // ReLU / ReLU6 as a clamp of the accumulator, fused with the bias add
 #pragma unroll
-                for (int j4 = 0; j4 < 4; ++j4) {
-                    if constexpr (LEAN) {
-                        if (a.act_mode == 1) {
-                            // ReLU / ReLU6 as a clamp of the accumulator, fused with the bias add
+                        for (int j4 = 0; j4 < 4; ++j4)
                             pk[j4] = pack_sat_s8x4(rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 0], bs, cp), mlt), rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 1], bs, cp), mlt),
                                                    rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 2], bs, cp), mlt), rq_round(__viaddmin_s32_relu((int)v[j4 * 4 + 3], bs, cp), mlt));
-                        } else {
-                            pk[j4] = pack_act_s8x4(rq_round((int)v[j4 * 4 + 0] + bs, mlt), rq_round((int)v[j4 * 4 + 1] + bs, mlt),
-                                                   rq_round((int)v[j4 * 4 + 2] + bs, mlt), rq_round((int)v[j4 * 4 + 3] + bs, mlt), a.act_mode != 0, hi4);
-                        }
+                    } else if (a.act_mode == 0) {
+#pragma unroll
+                        for (int j4 = 0; j4 < 4; ++j4)
+                            pk[j4] = pack_sat_s8x4(rq_round((int)v[j4 * 4 + 0] + bs, mlt), rq_round((int)v[j4 * 4 + 1] + bs, mlt),
+                                                   rq_round((int)v[j4 * 4 + 2] + bs, mlt), rq_round((int)v[j4 * 4 + 3] + bs, mlt));
                     } else {
+#pragma unroll
+                        for (int j4 = 0; j4 < 4; ++j4)
+                            pk[j4] = pack_act_s8x4(rq_round((int)v[j4 * 4 + 0] + bs, mlt), rq_round((int)v[j4 * 4 + 1] + bs, mlt),
+                                                   rq_round((int)v[j4 * 4 + 2] + bs, mlt), rq_round((int)v[j4 * 4 + 3] + bs, mlt), true, hi4);
+                    }
+                } else {
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; ++j4) {
                         uint32_t w4 = 0;
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
