@@ -162,6 +162,11 @@ QCONV_SWEEP = {
     "3b": dict(N=256, C=256, H=14, W=14, K=512, k=3, s=2, p=1, group=1),
     "3c": dict(N=256, C=256, H=56, W=56, K=64, k=1, s=1, p=0, group=1),
     "3d": dict(N=256, C=128, H=56, W=56, K=128, k=3, s=1, p=1, group=128),
+    # single layers of the MobileNetV2-style network (ReLU6 fused), sized for profiler captures
+    "4a": dict(N=64, C=16, H=112, W=112, K=96, k=1, s=1, p=0, group=1, act="relu6", y_scale=0.1),     # expansion 1x1, output-heavy
+    "4b": dict(N=256, C=64, H=14, W=14, K=384, k=1, s=1, p=0, group=1, act="relu6", y_scale=0.1),     # 1x1 on 196-byte planes
+    "4c": dict(N=128, C=384, H=14, W=14, K=384, k=3, s=1, p=1, group=384, act="relu6", y_scale=0.1),  # depthwise on 14 x 14
+    "4d": dict(N=256, C=160, H=7, W=7, K=960, k=1, s=1, p=0, group=1, act="relu6", y_scale=0.1),      # 1x1 on 49-byte planes
 }
 
 
@@ -174,7 +179,7 @@ def qconv_case(name, batch=None, seed=DEFAULT_SEED):
     # the weights come from a generator of their own, so that they do not depend on the batch size
     wrng = np.random.default_rng(DEFAULT_SEED + 7919 + sum(ord(ch) for ch in name))
     w = wrng.integers(-127, 128, (c["K"], c["C"] // c["group"], c["k"], c["k"]), dtype=np.int8)
-    c.update(x=x, w=w, x_scale=0.02, w_scale=np.array([0.02], np.float32), y_scale=0.02,
+    c.update(x=x, w=w, x_scale=0.02, w_scale=np.array([0.02], np.float32), y_scale=c.get("y_scale", 0.02), act=c.get("act"),
              stride=(c["s"], c["s"]), pads=(c["p"],) * 4, dilations=(1, 1))
     oh = (c["H"] + 2 * c["p"] - c["k"]) // c["s"] + 1
     c["macs"] = c["N"] * c["K"] * oh * oh * (c["C"] // c["group"]) * c["k"] * c["k"]
@@ -199,7 +204,7 @@ def qconv_graph(name, batch=None, seed=DEFAULT_SEED, channels_last=False):
     ws = g.tensor("w_scale", F32, (1,), c["w_scale"])
     y = g.tensor("y", I8, (c["N"], oh, oh, c["K"]) if channels_last else (c["N"], c["K"], oh, oh))
     g.node("QLinearConv", [x, w, ws, -1, -1], [y], x_scale=c["x_scale"], x_zp=0, y_scale=c["y_scale"], y_zp=0,
-           strides=c["stride"], pads=c["pads"], dilations=c["dilations"], group=c["group"], auto_pad="NOTSET", activation=None,
+           strides=c["stride"], pads=c["pads"], dilations=c["dilations"], group=c["group"], auto_pad="NOTSET", activation=c["act"],
            channels_last=1 if channels_last else 0)
     g.input, g.output = x, y
     return g, c
