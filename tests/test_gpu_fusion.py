@@ -62,7 +62,7 @@ CASES = [
     (1, 16, 56, 56, 32, 3, 1, "leaky", True, U8, "+ActivationLut+MaxPool"),                  # unsigned codes: unsigned maximum
     (1, 16, 104, 104, 128, 3, 1, None, True, I8, "tc-implicit)+MaxPool"),                    # pool alone, two filter tiles
     (2, 16, 28, 28, 32, 3, 1, "relu_rescale", False, I8, "+ActivationLut"),                  # activation alone (table)
-    (2, 64, 28, 28, 32, 1, 0, "leaky", True, I8, "tc-implicit)+ActivationLut"),              # 1x1, 32 filters: table fused, pool stays a step
+    (2, 64, 28, 28, 32, 1, 0, "leaky", True, I8, "tc-pointwise)+ActivationLut"),             # 1x1, 32 filters (four pixel groups on the lanes): table fused, pool stays a step
     (2, 64, 28, 28, 96, 1, 0, "leaky", True, I8, "tc-pointwise)+ActivationLut"),             # 1x1, 96 filters: the filters-on-lanes kernel with the table
     (2, 3, 64, 64, 16, 3, 1, "leaky", True, I8, "small-c)+ActivationLut"),                   # stem kernel: table fused, pool separate
     (2, 16, 13, 13, 32, 3, 1, "leaky", False, I8, "+ActivationLut"),                         # im2col path (odd width)

@@ -270,6 +270,9 @@ POINTWISE_QCONV = [
     (1, 64, 16, 17, 130, I8, I8, 0, -4, True, True, None),          # 272 pixels: two tiles of 144; non-zero output zero point
     (2, 32, 28, 28, 96, I8, I8, 0, 0, True, True, "relu6"),         # ReLU6 with a six below 127: the clamp of the accumulator (per-filter bounds)
     (2, 48, 14, 14, 64, U8, I8, 128, 0, False, True, "relu6"),      # the same on 14 x 14 planes, one multiplier for all filters
+    (3, 96, 56, 56, 24, I8, I8, 0, 0, True, True, None),            # 24 filters: four pixel groups of 32 lanes (block-diagonal weights), tiles of 4 x 208 pixels, the last one partly empty
+    (2, 200, 24, 24, 40, U8, U8, 3, 7, True, True, "relu"),         # 40 filters: two groups of 64 lanes, 7 K steps per group, general requantisation
+    (2, 64, 16, 16, 12, I8, I8, 0, 0, True, False, "relu6"),        # 12 filters but too few pixels for eight groups: the implicit-GEMM kernel
 ]
 
 

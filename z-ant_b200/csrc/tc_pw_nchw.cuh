@@ -17,6 +17,12 @@
 // rows in with word loads, writing the same swizzled form, and the output tile - for a whole image the block
 // [128 filters][HW] is contiguous in NCHW - is staged in shared memory and leaves as one bulk copy.
 //
+// Few filters (at most 64): a tile of 128 lanes would leave lane quarters idle, and the epilogue - the part that bounds the
+// kernel - would run on one or two of the SM's four schedulers.  The lanes then carry G = 128 / m_pad GROUPS of m_pad filters,
+// each group working on its own run of pixels: A is block-diagonal, [group g][filter] x [group g'][channel] = W[filter][channel]
+// for g == g' and zero elsewhere, K is G times as deep, and K iteration (g', channel chunk) loads the TMA box of group g''s
+// pixels.  The zero blocks cost MMA time, of which there is plenty; every lane of the epilogue has work.
+//
 // Warp roles (704 threads, one persistent CTA per SM):
 //   warp 0  TMA loader     warp 1  TMEM owner + MMA issuer     warps 2-17  epilogue     warps 18-21  copiers (no tensor map)
 #pragma once
@@ -44,6 +50,9 @@ struct PwConvArgs {
     int n_px;             // pixels per tile: a multiple of 16, at most 256
     int px_tiles;         // tiles per image
     int PB;               // 128-pixel blocks per tile (1 or 2)
+    int G;                // pixel groups on the lanes (1, or 128 / m_pad when there are at most 64 filters: see the kernel's header)
+    int m_pad;            // lanes per group: 16, 32 or 64 filters (128 when G == 1)
+    int a_steps;          // K steps of the resident A operand: k_steps, or G * (K iterations per group) * KS for the block-diagonal form
     int cpm;              // CTAs per filter tile
     int mode;             // 0: tensor map; 1: word copies in, staged tile out (HW % 4 == 0, at most 256 pixels: one tile per image)
     int bulk_out;         // mode 1: the staged tile leaves as one bulk copy (its address and size are multiples of 16)
@@ -99,9 +108,11 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
     const int mt = (int)blockIdx.x / a.cpm, j0 = (int)blockIdx.x - mt * a.cpm;
     const int tiles = a.N * a.px_tiles;
     const int KC = a.KS * 32;
-    const int k_iters = (a.k_steps + a.KS - 1) / a.KS;
+    const int k_iters = (a.k_steps + a.KS - 1) / a.KS;          // K iterations (stages) per pixel group
+    const int k_total = a.G * k_iters;                          // K iterations of a tile
+    const int tile_px = a.G * a.n_px;                           // pixels of a tile
     const uint32_t blk_bytes = (uint32_t)KC * 128u;
-    const int live_q = min(4, (a.M - mt * 128 + 31) >> 5);      // lane quarters (of 32 filters) of this CTA's filter tile that exist
+    const int live_q = a.G > 1 ? 4 : min(4, (a.M - mt * 128 + 31) >> 5);   // lane quarters of this CTA's tile that carry filters
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), 1); ptx::mbar_init(empty(s), 1); }
@@ -123,21 +134,23 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
     if (warp == 0) {
         // ------------------------------------------------------------------ loader: the filter tile's weights once, then (mode 0) one box per stage and block
         if (lane == 0) {
-            const uint32_t w_bytes = (uint32_t)a.k_steps * 4096u;
+            const uint32_t w_bytes = (uint32_t)a.a_steps * 4096u;
             ptx::mbar_arrive_expect_tx(wfull, w_bytes);
             ptx::bulk_g2s(ptx::smem_u32(sA), a.w + (size_t)mt * w_bytes, w_bytes, wfull);
             if (a.mode == 0) {
                 int s = 0; uint32_t ph = 0;
                 bool alive = true;
                 for (int t = j0; t < tiles && alive; t += a.cpm) {
-                    const int img = t / a.px_tiles, p0 = (t - img * a.px_tiles) * a.n_px;
-                    for (int ki = 0; ki < k_iters; ++ki) {
+                    const int img = t / a.px_tiles, p0 = (t - img * a.px_tiles) * tile_px;
+                    int pg = 0, ki = 0;                                   // pixel group and channel chunk of the K iteration
+                    for (int it = 0; it < k_total; ++it) {
                         if (!ptx::mbar_wait_sleeping(empty(s), ph ^ 1u, abort_flag)) { alive = false; break; }
                         const uint32_t dst = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
                         ptx::mbar_arrive_expect_tx(full(s), (uint32_t)a.PB * blk_bytes);
                         for (int blk = 0; blk < a.PB; ++blk)
-                            ptx::tma_load_3d(dst + (uint32_t)blk * blk_bytes, &x_map, (p0 + blk * 128) >> 2, ki * KC, img, full(s));
+                            ptx::tma_load_3d(dst + (uint32_t)blk * blk_bytes, &x_map, (p0 + pg * a.n_px + blk * 128) >> 2, ki * KC, img, full(s));
                         if (++s == S) { s = 0; ph ^= 1u; }
+                        if (++ki == k_iters) { ki = 0; ++pg; }
                     }
                 }
             }
@@ -157,13 +170,14 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
                 const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
                 if (!ptx::mbar_wait_sleeping(tempty(b), bph ^ 1u, abort_flag)) goto mma_done;
                 const uint32_t d_tmem = tmem_base + (uint32_t)(b * 256);
-                for (int ki = 0; ki < k_iters; ++ki) {
+                for (int ki = 0; ki < k_total; ++ki) {
                     if (!ptx::mbar_wait_sleeping(full(s), ph, abort_flag)) goto mma_done;
                     ptx::tc_fence_after();
                     const uint32_t stage0 = ptx::smem_u32(sStages + (size_t)s * a.stage_bytes);
                     // B = [channel][128 pixels] rows of 128 bytes: eight channels are 1024 bytes, a K step of 32 channels 4096
                     const uint64_t db0 = ptx::smem_desc_mnmajor_sw128(stage0, blk_bytes, 1024);
-                    const int ks_here = min(a.KS, a.k_steps - ki * a.KS);
+                    // (the block-diagonal A holds whole stages of K steps per group, zero where the channels end)
+                    const int ks_here = a.G > 1 ? a.KS : min(a.KS, a.k_steps - ki * a.KS);
                     for (int kk = 0; kk < ks_here; ++kk) {
                         const uint64_t da = da0 + (uint64_t)((ki * a.KS + kk) * 256);        // 4096 bytes per K step, in 16-byte units
                         const bool acc = (ki | kk) != 0;
@@ -238,7 +252,9 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
         int e = 0;                                                    // index among them: the live warps in ascending order
         for (int wv = 2; wv < warp; ++wv) e += (wv & 3) < live_q ? 32 : 0;
         e += lane;
-        const int m_local = quarter * 32 + lane, m = mt * 128 + m_local;
+        const int m_local = quarter * 32 + lane;
+        const int grp = a.G > 1 ? m_local / a.m_pad : 0;              // this lane's pixel group (block-diagonal form)
+        const int m = a.G > 1 ? m_local - grp * a.m_pad : mt * 128 + m_local;
         const bool live = m < a.M;
         const float mlt = live ? __ldg(a.mult + m) : 1.0f;
         const int bs = live ? __ldg(a.bias + m) : 0;
@@ -251,8 +267,9 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
         for (int t = quarter_live ? j0 : tiles; t < tiles; t += a.cpm, ++tile_it) {
             const int b = tile_it & 1;
             const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
-            const int img = t / a.px_tiles, p0 = (t - img * a.px_tiles) * a.n_px;
-            const int n_valid = min(a.n_px, a.HW - p0);
+            const int img = t / a.px_tiles, p0 = (t - img * a.px_tiles) * tile_px + grp * a.n_px;   // this lane's first pixel
+            const int n_valid = min(a.n_px, a.HW - p0);                 // this lane's pixels (all lanes' when G == 1)
+            const int n_loop = a.G > 1 ? min(a.n_px, a.HW - (t - img * a.px_tiles) * tile_px) : n_valid;   // warp-uniform chunk bound
             if (a.mode == 0) {
                 int ok = 1;
                 if (lane == 0) ok = ptx::mbar_wait_sleeping(tfull(b), bph, abort_flag) ? 1 : 0;
@@ -309,7 +326,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
             // after the wait that precedes the arithmetic it overlaps).
             uint32_t va[16], vb[16];
             int ch = cg;
-            bool has = ch * 32 < n_valid;
+            bool has = ch * 32 < n_loop;
             if (has) ptx::tmem_ld16(taddr + (uint32_t)(ch * 32), va);
             while (has) {
                 uint32_t pk[8];
@@ -318,7 +335,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
                 requant16(va, pk);
                 ptx::tmem_wait_ld();
                 const int nch = ch + 4;
-                const bool nhas = nch * 32 < n_valid;
+                const bool nhas = nch * 32 < n_loop;
                 if (nhas) ptx::tmem_ld16(taddr + (uint32_t)(nch * 32), va);
                 requant16(vb, pk + 4);
                 if (LEAN && a.lut) {
@@ -328,7 +345,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
                 const int c0 = ch * 32;
                 if (a.mode == 0) {
                     // HW, p0 and c0 are multiples of 16: the chunk's valid part is 16 or 32 bytes
-                    if (live) {
+                    if (live && c0 < n_valid) {
                         if (c0 + 32 <= n_valid) {
                             if (a.wide_store) st_global_32B(yrow + c0, pk);
                             else {
@@ -393,20 +410,29 @@ inline bool pw_conv_plan(const ConvGeom& g, bool w_zp_all_zero, int sm_count, Pw
     const long long hw = (long long)g.H * g.W;
     if (g.N <= 0 || hw <= 0 || hw > (1 << 24) || g.C > 960 || g.C % 4 != 0) return false;
     if ((long long)g.N * hw < 256) return false;
-    // up to 32 filters fill one lane quarter only (one of the SM's four schedulers would do the whole epilogue): with
-    // planes that a tensor map covers, the pixels-on-lanes form of the implicit-GEMM kernel is the better one
-    if (g.M <= 32 && hw % 16 == 0 && hw >= 128) return false;
     PwConvArgs& a = p.a;
     a = PwConvArgs{};
     a.N = g.N; a.C = g.C; a.M = g.M; a.HW = (int)hw;
     a.k_steps = (g.C + 31) / 32;
     a.KS = a.k_steps >= 2 ? 2 : 1;
+    a.G = 1; a.m_pad = 128; a.a_steps = a.k_steps;
     p.m_tiles = (g.M + 127) / 128;
     if (p.m_tiles > sm_count) return false;
     if (hw % 16 == 0 && hw >= 128) {
         a.mode = 0;
-        a.px_tiles = (int)((hw + 255) / 256);
-        a.n_px = (int)(((hw + a.px_tiles - 1) / a.px_tiles + 15) / 16 * 16);
+        // at most 64 filters: G groups of m_pad lanes, each on its own run of pixels (block-diagonal A, G times the K depth),
+        // when the deeper A still fits beside the stages
+        if (g.M <= 64) {
+            const int m_pad = g.M <= 16 ? 16 : (g.M <= 32 ? 32 : 64), G = 128 / m_pad;
+            const int steps = G * ((a.k_steps + a.KS - 1) / a.KS) * a.KS;
+            if (steps <= 30 && hw >= (long long)G * 64) { a.G = G; a.m_pad = m_pad; a.a_steps = steps; }
+        }
+        // up to 32 filters fill one lane quarter only (one of the SM's four schedulers would do the whole epilogue): without
+        // the groups the pixels-on-lanes form of the implicit-GEMM kernel is the better one
+        if (a.G == 1 && g.M <= 32) return false;
+        const long long tile_max = 256LL * a.G;
+        a.px_tiles = (int)((hw + tile_max - 1) / tile_max);
+        a.n_px = (int)(((hw + (long long)a.px_tiles * a.G - 1) / ((long long)a.px_tiles * a.G) + 15) / 16 * 16);
         a.wide_store = (hw % 32 == 0 && a.n_px % 32 == 0) ? 1 : 0;
     } else {
         if (hw > 256 || hw % 4 != 0) return false;      // rows that are not whole words stay with the im2col path (the byte copies cost more than they save)
@@ -421,7 +447,7 @@ inline bool pw_conv_plan(const ConvGeom& g, bool w_zp_all_zero, int sm_count, Pw
     if (tiles > 0x7fffffffLL) return false;
     a.cpm = (int)std::max<long long>(1, std::min<long long>(sm_count / p.m_tiles, tiles));
     a.stage_bytes = a.PB * a.KS * 32 * 128;
-    const int a_bytes = a.k_steps * 4096;
+    const int a_bytes = a.a_steps * 4096;
     const int out_bytes = a.mode == 0 ? 0 : (int)((128 * hw + 1023) / 1024 * 1024);
     const int budget = 232448 - kPwTail - a_bytes - out_bytes;
     a.stages = std::min(kPwMaxStages, budget / a.stage_bytes);
@@ -439,12 +465,21 @@ inline void pw_conv_prepare(const PwConvPlan& p, const int8_t* w, const int32_t*
     const PwConvArgs& a = p.a;
     w_blk.assign(p.w_bytes, 0);
     bias_f.assign(a.M, 0);
-    const size_t tile_bytes = (size_t)a.k_steps * 4096;
+    const size_t tile_bytes = (size_t)a.a_steps * 4096;
+    const int group_steps = a.a_steps / a.G;                  // K steps per pixel group (whole stages)
     for (int m = 0; m < a.M; ++m) {
         long long sum = 0;
         for (int c = 0; c < a.C; ++c) {
             const int8_t v = w[(size_t)m * a.C + c];
-            w_blk[(size_t)(m / 128) * tile_bytes + (size_t)(c / 16) * 2048 + (size_t)(m % 128) * 16 + (c % 16)] = v;
+            if (a.G == 1) {
+                w_blk[(size_t)(m / 128) * tile_bytes + (size_t)(c / 16) * 2048 + (size_t)(m % 128) * 16 + (c % 16)] = v;
+            } else {
+                // block-diagonal: lane g * m_pad + m, K index g * (group_steps * 32) + c
+                for (int gq = 0; gq < a.G; ++gq) {
+                    const int k = gq * group_steps * 32 + c, row = gq * a.m_pad + m;
+                    w_blk[(size_t)(k / 16) * 2048 + (size_t)row * 16 + (k % 16)] = v;
+                }
+            }
             sum += v;
         }
         bias_f[m] = (int32_t)((bias ? bias[m] : 0) - (long long)x_zp * sum);
