@@ -63,8 +63,10 @@ __device__ __forceinline__ void mma_m16n8k16_s8(int (&d)[4], uint32_t a0, uint32
                      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(b0));
 }
 
-// MT: 16-filter tiles (1..4); NTL: MMAs per unit along the pixels (2: 16 pixels, 4: 32 pixels).
-template <int MT, int NTL, bool XU8, bool LEAN>
+// MT: 16-filter tiles (1..4); NTL: MMAs per unit along the pixels (2: 16 pixels, 4: 32 pixels); KSC: K steps issued per
+// pixel block (1 for one input channel, 3 otherwise - a step whose groups do not exist multiplies zero weights), a
+// compile-time count so that the unrolled MMA loops carry no tests.
+template <int MT, int NTL, int KSC, bool XU8, bool LEAN>
 __global__ void __launch_bounds__(kSmallcThreads) qconv3x3_smallc_kernel(const SmallcArgs a) {
     extern __shared__ __align__(16) uint8_t s_in[];      // [C][RIN][P]
     __shared__ uint8_t s_lut[256];                       // copy of the optional activation table
@@ -96,6 +98,7 @@ __global__ void __launch_bounds__(kSmallcThreads) qconv3x3_smallc_kernel(const S
     const int bpix0 = 2 * NTL * (g >> 1) + (g & 1);
     const Requant rq{a.y_scale, a.y_zp, a.act, a.lut};
     const uint32_t hi4 = a.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(a.six & 255) : 0x7f7f7f7fu;   // upper bound of the lean activation
+    const bool relu = a.act != ZANT_QACT_NONE;
     const size_t ohw = (size_t)a.OH * a.OW;
     const int words_per_row = a.P >> 2;
     const int tiles = a.N * a.bands;
@@ -130,14 +133,12 @@ __global__ void __launch_bounds__(kSmallcThreads) qconv3x3_smallc_kernel(const S
                 const int ow = min(ow0 + bpix0 + 2 * nt, a.OW - 1);       // pixels past the row end are computed on valid data and dropped
                 const int j0 = row_base + ow * a.s;
 #pragma unroll
-                for (int ks = 0; ks < kSmallcMaxKs; ++ks) {
-                    if (ks < a.KS) {
-                        const int j = qoff[ks] + j0;
-                        const uint32_t* wp = reinterpret_cast<const uint32_t*>(s_in + (j & ~3));
-                        const uint32_t b0 = __byte_perm(wp[0], wp[1], 0x3210u + 0x1111u * (uint32_t)(j & 3));
+                for (int ks = 0; ks < KSC; ++ks) {
+                    const int j = qoff[ks] + j0;
+                    const uint32_t* wp = reinterpret_cast<const uint32_t*>(s_in + (j & ~3));
+                    const uint32_t b0 = __byte_perm(wp[0], wp[1], 0x3210u + 0x1111u * (uint32_t)(j & 3));
 #pragma unroll
-                        for (int mt = 0; mt < MT; ++mt) mma_m16n8k16_s8<XU8>(acc[mt][nt], wa[mt][ks][0], wa[mt][ks][1], b0);
-                    }
+                    for (int mt = 0; mt < MT; ++mt) mma_m16n8k16_s8<XU8>(acc[mt][nt], wa[mt][ks][0], wa[mt][ks][1], b0);
                 }
             }
             // ---- requantise; this thread holds pixels ow0 + 2*NTL*t .. + 2*NTL-1 of filters 16*mt + g and + 8
@@ -153,10 +154,8 @@ __global__ void __launch_bounds__(kSmallcThreads) qconv3x3_smallc_kernel(const S
                     for (int p = 0; p < NTL / 2; ++p) {
                         const int v0 = acc[mt][2 * p][2 * h], v1 = acc[mt][2 * p][2 * h + 1], v2 = acc[mt][2 * p + 1][2 * h], v3 = acc[mt][2 * p + 1][2 * h + 1];
                         if constexpr (LEAN) {
-                            uint32_t pk = pack_act_s8x4(rq_round(v0, mult[mt][h]), rq_round(v1, mult[mt][h]), rq_round(v2, mult[mt][h]), rq_round(v3, mult[mt][h]),
-                                                        a.act != ZANT_QACT_NONE, hi4);
-                            if (a.lut) pk = lut4_smem(s_lut, pk);
-                            wd[p] = pk;
+                            const int q0 = rq_round(v0, mult[mt][h]), q1 = rq_round(v1, mult[mt][h]), q2 = rq_round(v2, mult[mt][h]), q3 = rq_round(v3, mult[mt][h]);
+                            wd[p] = relu ? __vminu4(pack_sat_u8x4(q0, q1, q2, q3), hi4) : pack_sat_s8x4(q0, q1, q2, q3);
                         } else {
                             const int q0 = a.out_u8 ? requant_one<true>(v0, mult[mt][h], rq) : requant_one<false>(v0, mult[mt][h], rq);
                             const int q1 = a.out_u8 ? requant_one<true>(v1, mult[mt][h], rq) : requant_one<false>(v1, mult[mt][h], rq);
@@ -164,6 +163,10 @@ __global__ void __launch_bounds__(kSmallcThreads) qconv3x3_smallc_kernel(const S
                             const int q3 = a.out_u8 ? requant_one<true>(v3, mult[mt][h], rq) : requant_one<false>(v3, mult[mt][h], rq);
                             wd[p] = (uint32_t)(q0 & 255) | ((uint32_t)(q1 & 255) << 8) | ((uint32_t)(q2 & 255) << 16) | ((uint32_t)(q3 & 255) << 24);
                         }
+                    }
+                    if (LEAN && a.lut) {
+#pragma unroll
+                        for (int p = 0; p < NTL / 2; ++p) wd[p] = lut4_smem(s_lut, wd[p]);
                     }
                     if (f < a.M && owt < a.OW) {
                         uint8_t* dst = a.y + ((size_t)n * a.M + f) * ohw + (size_t)oh * a.OW + owt;
@@ -226,8 +229,12 @@ inline int32_t smallc_launch(zant_ctx* ctx, const SmallcArgs& a, int grid, size_
         kernel<<<grid, kSmallcThreads, smem, ctx->stream>>>(a);
         return check_launch(ctx, "qconv3x3_smallc_kernel");
     };
-    if (x_u8) return lean ? go(qconv3x3_smallc_kernel<MT, NTL, true, true>) : go(qconv3x3_smallc_kernel<MT, NTL, true, false>);
-    return lean ? go(qconv3x3_smallc_kernel<MT, NTL, false, true>) : go(qconv3x3_smallc_kernel<MT, NTL, false, false>);
+    if (a.KS == 1) {
+        if (x_u8) return lean ? go(qconv3x3_smallc_kernel<MT, NTL, 1, true, true>) : go(qconv3x3_smallc_kernel<MT, NTL, 1, true, false>);
+        return lean ? go(qconv3x3_smallc_kernel<MT, NTL, 1, false, true>) : go(qconv3x3_smallc_kernel<MT, NTL, 1, false, false>);
+    }
+    if (x_u8) return lean ? go(qconv3x3_smallc_kernel<MT, NTL, 3, true, true>) : go(qconv3x3_smallc_kernel<MT, NTL, 3, true, false>);
+    return lean ? go(qconv3x3_smallc_kernel<MT, NTL, 3, false, true>) : go(qconv3x3_smallc_kernel<MT, NTL, 3, false, false>);
 }
 
 // `max_product`: bound of |accumulator * multiplier| (tc_conv_max_product), infinity if a multiplier is not finite.
