@@ -228,7 +228,7 @@ inline size_t qgemm_a_bytes(size_t rows, const QGemmPrep& p) { return (rows + 12
 
 template <int NT, int KC, int MODE>
 inline int32_t launch_tc_gemm_kc(zant_ctx* ctx, const TcGemmArgs& k, int tiles) {
-    using Cfg = TcGemmCfg<NT, KC, 8>;
+    using Cfg = TcGemmCfg<NT, KC, 8, MODE>;
     ZB_SMEM_ATTR(ctx, (tc_gemm_i8_kernel<NT, KC, 8, MODE>), Cfg::SMEM_BYTES);
     tc_gemm_i8_kernel<NT, KC, 8, MODE><<<std::min(tiles, ctx->sm_count), Cfg::THREADS, Cfg::SMEM_BYTES, ctx->stream>>>(k);
     return check_launch(ctx, "tc_gemm_i8_kernel");

@@ -44,7 +44,7 @@ struct TcGemmArgs {
     int lean; int six;
 };
 
-template <int NT, int KC, int STAGES>
+template <int NT, int KC, int STAGES, int MODE = 0>
 struct TcGemmCfg {
     static constexpr int A_STAGE = KC * 128 * 16;
     static constexpr int W_STAGE = KC * NT * 16;
@@ -55,8 +55,12 @@ struct TcGemmCfg {
     static constexpr int OFF_BAR = OFF_CONST + 2 * MAX_N * 4;
     static constexpr int SMEM_BYTES = OFF_BAR + 512;
     static constexpr int TMEM_COLS = 2 * NT;
-    static constexpr int THREADS = 320;                      // producer, MMA, 8 epilogue warps
-    static constexpr int COLS_PER_WARP = NT / 2;             // the two epilogue groups split the tile's columns
+    // warps per TMEM lane quarter (they split the tile's columns): two for the row-major epilogue, which is bound by the
+    // operand feed anyway; four for the NCHW-storing one (with two per scheduler it was latency-bound: 35 % issue-active)
+    static constexpr int PARTS = ((MODE & 2) && NT >= 128) ? 4 : 2;
+    static constexpr int COLS_PER_WARP = NT / PARTS;
+    static constexpr int EPI_WARPS = 4 * PARTS;
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;      // producer, MMA issuer, epilogue warps
     static_assert(KC % 2 == 0, "a stage must hold whole 32-byte MMA K steps");
     static_assert(NT % 64 == 0 && NT <= 256, "tile width");
     static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
@@ -69,8 +73,8 @@ struct TcGemmCfg {
 // int8 or uint8, ReLU / ReLU6) and NCHW store; otherwise the lean int8 / zero-point-0 form with a
 // row-major [M][N] store.
 template <int NT, int KC, int STAGES, int MODE = 0>
-__global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constant__ TcGemmArgs a) {
-    using Cfg = TcGemmCfg<NT, KC, STAGES>;
+__global__ void __launch_bounds__(TcGemmCfg<NT, KC, STAGES, MODE>::THREADS, 1) tc_gemm_i8_kernel(const __grid_constant__ TcGemmArgs a) {
+    using Cfg = TcGemmCfg<NT, KC, STAGES, MODE>;
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sStages = smem + Cfg::OFF_STAGES;
     float* sMult = reinterpret_cast<float*>(smem + Cfg::OFF_CONST);
@@ -93,7 +97,7 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constan
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { ptx::mbar_init(full(s), 1); ptx::mbar_init(empty(s), 1); }
-        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 8); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), Cfg::EPI_WARPS); }
         *abort_flag = 0;
         *epi_ok = 1;
         ptx::mbar_fence_init();
@@ -159,9 +163,9 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constan
         // ------------------------------------------------------------------ epilogue: 8 warps; warp (2+q) and (6+q)
         // read lane quarter q; the first four warps take the tile's left half of the columns.
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int half = (warp - 2) >> 2;            // which part of the tile's columns (0 .. PARTS - 1)
         const int row = quarter * 32 + lane;
-        const int e = (warp - 2) * 32 + lane;     // 0..255
+        const int e = (warp - 2) * 32 + lane;     // 0 .. 32 * EPI_WARPS - 1
         const bool relu = a.act == ZANT_QACT_RELU;
         int tile_it = 0;
         for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tile_it) {
@@ -169,7 +173,7 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constan
             const int b = tile_it & 1;
             const uint32_t bph = (uint32_t)(tile_it >> 1) & 1u;
             if (e == 0) *epi_ok = ptx::mbar_wait(tfull(b), bph, abort_flag) ? 1 : 0;
-            ptx::named_barrier_sync(1, 256);
+            ptx::named_barrier_sync(1, 32 * Cfg::EPI_WARPS);
             if (!*epi_ok) break;
             ptx::tc_fence_after();
             const int tcol0 = half * Cfg::COLS_PER_WARP;
@@ -215,21 +219,29 @@ __global__ void __launch_bounds__(320, 1) tc_gemm_i8_kernel(const __grid_constan
                     ptx::tmem_ld32(taddr + (uint32_t)(h * 32), v);
                     ptx::tmem_wait_ld();
                     if (a.lean) {
-                        // four columns at a time: constants as vectors, one saturating pack, the activation on the packed word
+                        // four columns at a time: constants as vectors, one saturating pack, the activation on the packed word;
+                        // the common case (a row of the matrix, 32 real columns) stores without per-byte tests, the plane
+                        // stride kept in registers
                         uint8_t* yc = ybase + (size_t)col0 * a.ohw;
+                        const size_t st1 = (size_t)a.ohw, st2 = 2 * st1, st3 = 3 * st1, st4 = 4 * st1;
+                        const bool row_ok = grow < a.M, all_cols = col0 + 32 <= a.n_valid;
+                        const bool relu_act = a.act != ZANT_QACT_NONE;
 #pragma unroll
                         for (int j4 = 0; j4 < 8; ++j4) {
                             const float4 m4 = *reinterpret_cast<const float4*>(sMult + col0 + j4 * 4);
                             const int4 b4 = *reinterpret_cast<const int4*>(sBias + col0 + j4 * 4);
-                            uint32_t w4 = pack_act_s8x4(rq_round((int)v[j4 * 4 + 0] + b4.x, m4.x), rq_round((int)v[j4 * 4 + 1] + b4.y, m4.y),
-                                                        rq_round((int)v[j4 * 4 + 2] + b4.z, m4.z), rq_round((int)v[j4 * 4 + 3] + b4.w, m4.w),
-                                                        a.act != ZANT_QACT_NONE, hi4);
+                            const int q0 = rq_round((int)v[j4 * 4 + 0] + b4.x, m4.x), q1 = rq_round((int)v[j4 * 4 + 1] + b4.y, m4.y);
+                            const int q2 = rq_round((int)v[j4 * 4 + 2] + b4.z, m4.z), q3 = rq_round((int)v[j4 * 4 + 3] + b4.w, m4.w);
+                            uint32_t w4 = relu_act ? __vminu4(pack_sat_u8x4(q0, q1, q2, q3), hi4) : pack_sat_s8x4(q0, q1, q2, q3);
                             if (a.lut) w4 = lut4(a.lut, w4);
-                            if (grow < a.M) {
+                            if (row_ok && all_cols) {
+                                yc[0] = (uint8_t)w4; yc[st1] = (uint8_t)(w4 >> 8); yc[st2] = (uint8_t)(w4 >> 16); yc[st3] = (uint8_t)(w4 >> 24);
+                            } else if (row_ok) {
 #pragma unroll
                                 for (int i = 0; i < 4; ++i)
-                                    if (col0 + j4 * 4 + i < a.n_valid) yc[(size_t)(j4 * 4 + i) * a.ohw] = (uint8_t)(w4 >> (8 * i));
+                                    if (col0 + j4 * 4 + i < a.n_valid) yc[(size_t)i * st1] = (uint8_t)(w4 >> (8 * i));
                             }
+                            yc += st4;
                         }
                         continue;
                     }
