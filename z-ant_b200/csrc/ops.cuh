@@ -180,8 +180,14 @@ inline int32_t run_resize(zant_ctx* ctx, size_t esz, const void* x, void* y, con
     for (size_t d = r; d-- > 0;) { k.in_stride[d] = s; s *= xs[d]; k.out_shape[d] = os[d]; k.total *= os[d]; k.axis_offset[d] = axis_offset[d]; }
     if (k.total == 0) return ZANT_OK;
     const int grid = grid_for(k.total, 256, ctx->sm_count);
-    if (esz == 4) resize_gather<uint32_t><<<grid, 256, 0, ctx->stream>>>((const uint32_t*)x, (uint32_t*)y, table_dev, k);
-    else resize_gather<uint8_t><<<grid, 256, 0, ctx->stream>>>((const uint8_t*)x, (uint8_t*)y, table_dev, k);
+    const bool small = k.total < 0x7fffffffull && s < 0x7fffffffull;      // s: elements of the input
+    if (esz == 4) {
+        if (small) resize_gather<uint32_t, uint32_t><<<grid, 256, 0, ctx->stream>>>((const uint32_t*)x, (uint32_t*)y, table_dev, k);
+        else resize_gather<uint32_t, size_t><<<grid, 256, 0, ctx->stream>>>((const uint32_t*)x, (uint32_t*)y, table_dev, k);
+    } else {
+        if (small) resize_gather<uint8_t, uint32_t><<<grid, 256, 0, ctx->stream>>>((const uint8_t*)x, (uint8_t*)y, table_dev, k);
+        else resize_gather<uint8_t, size_t><<<grid, 256, 0, ctx->stream>>>((const uint8_t*)x, (uint8_t*)y, table_dev, k);
+    }
     return check_launch(ctx, "resize_gather");
 }
 
