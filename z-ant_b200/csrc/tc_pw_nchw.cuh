@@ -13,9 +13,12 @@
 // A CTA keeps the weights of ONE tile of 128 filters resident in shared memory (K <= 960) and walks over (image,
 // pixel tile) pairs; a pixel tile is up to 256 pixels (two accumulator buffers of 256 TMEM columns each, so the
 // epilogue of a tile overlaps the MMAs of the next).
-// Planes whose size is a multiple of 4 but not of 16 bytes (14 x 14) have no tensor map: four copier warps bring the
-// rows in with word loads, writing the same swizzled form, and the output tile - for a whole image the block
-// [128 filters][HW] is contiguous in NCHW - is staged in shared memory and leaves as one bulk copy.
+// Planes whose size is a multiple of 4 but not of 16 bytes (14 x 14) have no tensor map.  A stage's channel rows are one
+// contiguous, 16-byte aligned run of the input, so the loader brings them in with one 1-D bulk copy per stage into a ring of
+// raw buffers, and four copier warps re-lay a raw buffer out into the swizzled operand form with shared-memory word loads and
+// stores (copying from global memory with plain loads left the kernel waiting on their latency: too few bytes in flight).
+// The output tile - for a whole image the block [128 filters][HW] is contiguous in NCHW - is staged in shared memory and
+// leaves as one bulk copy.
 //
 // Few filters (at most 64): a tile of 128 lanes would leave lane quarters idle, and the epilogue - the part that bounds the
 // kernel - would run on one or two of the SM's four schedulers.  The lanes then carry G = 128 / m_pad GROUPS of m_pad filters,
@@ -58,6 +61,7 @@ struct PwConvArgs {
     int bulk_out;         // mode 1: the staged tile leaves as one bulk copy (its address and size are multiples of 16)
     int wide_store;       // mode 0: every 32-pixel chunk starts at a 32-byte boundary (HW and n_px are multiples of 32)
     int stages, stage_bytes, off_stages, off_out, off_tail;
+    int raws, raw_bytes, off_raw;   // mode 1: ring of raw buffers that bulk copies fill with a stage's channel rows as they lie in memory
     float y_scale; int y_zp; int act; int out_u8; int six;
     const int32_t* cap;   // lean epilogue, act_mode 1: per-filter accumulator bound of the activation (requant_relu_caps)
     int act_mode;         // lean epilogue: 0 no activation, 1 clamp of the accumulator to [0, cap], 2 clamp of the packed codes
@@ -103,6 +107,8 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
     auto tfull = [&](int b) { return bar0 + 8u * (2 * kPwMaxStages + b); };
     auto tempty = [&](int b) { return bar0 + 8u * (2 * kPwMaxStages + 2 + b); };
     const uint32_t wfull = bar0 + 8u * (2 * kPwMaxStages + 4);
+    auto raw_full = [&](int r) { return bar0 + 8u * (2 * kPwMaxStages + 5 + r); };
+    auto raw_empty = [&](int r) { return bar0 + 8u * (2 * kPwMaxStages + 9 + r); };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int mt = (int)blockIdx.x / a.cpm, j0 = (int)blockIdx.x - mt * a.cpm;
@@ -118,6 +124,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
         for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), 1); ptx::mbar_init(empty(s), 1); }
         for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 4 * live_q); }
         ptx::mbar_init(wfull, 1);
+        for (int r = 0; r < a.raws; ++r) { ptx::mbar_init(raw_full(r), 1); ptx::mbar_init(raw_empty(r), 1); }
         *abort_flag = 0; *epi_ok = 1; *cp_ok = 1;
         ptx::mbar_fence_init();
     }
@@ -151,6 +158,21 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
                             ptx::tma_load_3d(dst + (uint32_t)blk * blk_bytes, &x_map, (p0 + pg * a.n_px + blk * 128) >> 2, ki * KC, img, full(s));
                         if (++s == S) { s = 0; ph ^= 1u; }
                         if (++ki == k_iters) { ki = 0; ++pg; }
+                    }
+                }
+            } else {
+                // no tensor map: the stage's channel rows [c_lo, c_lo + KC) of the image, one contiguous run, into the raw ring
+                int r = 0; uint32_t ph = 0;
+                bool alive = true;
+                for (int t = j0; t < tiles && alive; t += a.cpm) {
+                    const uint8_t* ximg = a.x + (size_t)t * a.C * a.HW;              // one tile per image
+                    for (int ki = 0; ki < k_iters; ++ki) {
+                        if (!ptx::mbar_wait_sleeping(raw_empty(r), ph ^ 1u, abort_flag)) { alive = false; break; }
+                        const int c_lo = ki * KC;
+                        const uint32_t bytes = (uint32_t)(min(KC, a.C - c_lo) * a.HW);     // a multiple of 16: C and HW are multiples of 4
+                        ptx::mbar_arrive_expect_tx(raw_full(r), bytes);
+                        ptx::bulk_g2s(ptx::smem_u32(smem + a.off_raw + (size_t)r * a.raw_bytes), ximg + (size_t)c_lo * a.HW, bytes, raw_full(r));
+                        if (++r == a.raws) { r = 0; ph ^= 1u; }
                     }
                 }
             }
@@ -198,48 +220,37 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
         if (a.mode != 0) {
             const int cw = warp - 18, ct = tid - 18 * 32;
             int s = 0; uint32_t ph = 0;
+            int r = 0; uint32_t rph = 0;
             bool alive = true;
             for (int t = j0; t < tiles && alive; t += a.cpm) {
-                const uint8_t* ximg = a.x + (size_t)t * a.C * a.HW;              // one tile per image
                 for (int ki = 0; ki < k_iters; ++ki) {
-                    if (ct == 0) *cp_ok = ptx::mbar_wait_sleeping(empty(s), ph ^ 1u, abort_flag) ? 1 : 0;
+                    if (ct == 0) *cp_ok = (ptx::mbar_wait_sleeping(raw_full(r), rph, abort_flag) && ptx::mbar_wait_sleeping(empty(s), ph ^ 1u, abort_flag)) ? 1 : 0;
                     ptx::named_barrier_sync(2, 128);
                     if (!*cp_ok) { alive = false; break; }
                     uint8_t* dst = sStages + (size_t)s * a.stage_bytes;
+                    const uint8_t* raw = smem + a.off_raw + (size_t)r * a.raw_bytes;      // [row][HW] as in memory
                     const int c_lo = ki * KC;
                     {
-                        // a warp takes every fourth row; a lane the words lane and lane + 32 of a row (HW <= 256).  All loads of a
-                        // batch of eight rows are issued before the first store, so that their latencies overlap.
+                        // a warp takes every fourth row; a lane the words lane and lane + 32 of a row (HW <= 256)
                         const int wpr = a.HW >> 2;
                         const bool w1 = lane + 32 < wpr, w0 = lane < wpr;
                         const uint32_t px0 = (uint32_t)lane * 4u, px1 = px0 + 128u;
-                        const uint32_t o0 = ((px0 >> 4) << 4), o1 = blk_bytes + (((px1 & 127u) >> 4) << 4);   // chunk position before the swizzle
-                        for (int r0 = cw; r0 < KC; r0 += 32) {
-                            uint32_t v0[8], v1[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const int rr = r0 + 4 * j;
-                                const bool ok = rr < KC && c_lo + rr < a.C;
-                                const uint32_t* src = reinterpret_cast<const uint32_t*>(ximg + (size_t)(c_lo + (ok ? rr : 0)) * a.HW);
-                                v0[j] = ok && w0 ? __ldg(src + lane) : 0u;
-                                v1[j] = ok && w1 ? __ldg(src + lane + 32) : 0u;
-                            }
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const int rr = r0 + 4 * j;
-                                if (rr < KC) {
-                                    uint8_t* drow = dst + rr * 128;
-                                    const uint32_t x7 = ((uint32_t)rr & 7u) << 4;
-                                    if (w0) *reinterpret_cast<uint32_t*>(drow + ((o0 ^ x7) | (px0 & 15u))) = v0[j];
-                                    if (w1) *reinterpret_cast<uint32_t*>(drow + (((o1 - blk_bytes) ^ x7) | (px1 & 15u)) + blk_bytes) = v1[j];
-                                }
-                            }
+                        const uint32_t o0 = ((px0 >> 4) << 4);                          // chunk position before the swizzle
+#pragma unroll 4
+                        for (int rr = cw; rr < KC; rr += 4) {
+                            if (c_lo + rr >= a.C) break;                                // rows past C: zero weights, any finite byte serves
+                            const uint32_t* src = reinterpret_cast<const uint32_t*>(raw + (size_t)rr * a.HW);
+                            uint8_t* drow = dst + rr * 128;
+                            const uint32_t x7 = ((uint32_t)rr & 7u) << 4;
+                            if (w0) *reinterpret_cast<uint32_t*>(drow + ((o0 ^ x7) | (px0 & 15u))) = src[lane];
+                            if (w1) *reinterpret_cast<uint32_t*>(drow + ((o0 ^ x7) | (px1 & 15u)) + blk_bytes) = src[lane + 32];
                         }
                     }
                     ptx::fence_proxy_async_smem();
                     ptx::named_barrier_sync(2, 128);
-                    if (ct == 0) ptx::mbar_arrive(full(s));
+                    if (ct == 0) { ptx::mbar_arrive(full(s)); ptx::mbar_arrive(raw_empty(r)); }
                     if (++s == S) { s = 0; ph ^= 1u; }
+                    if (++r == a.raws) { r = 0; rph ^= 1u; }
                 }
             }
         }
@@ -449,12 +460,16 @@ inline bool pw_conv_plan(const ConvGeom& g, bool w_zp_all_zero, int sm_count, Pw
     a.stage_bytes = a.PB * a.KS * 32 * 128;
     const int a_bytes = a.a_steps * 4096;
     const int out_bytes = a.mode == 0 ? 0 : (int)((128 * hw + 1023) / 1024 * 1024);
-    const int budget = 232448 - kPwTail - a_bytes - out_bytes;
-    a.stages = std::min(kPwMaxStages, budget / a.stage_bytes);
+    a.raw_bytes = a.mode == 0 ? 0 : (int)(((long long)a.KS * 32 * hw + 127) / 128 * 128);
+    a.raws = a.mode == 0 ? 0 : 3;
+    int budget = 232448 - kPwTail - a_bytes - out_bytes - a.raws * a.raw_bytes;
+    if (a.mode != 0 && budget < 2 * a.stage_bytes) { a.raws = 2; budget += a.raw_bytes; }
+    a.stages = std::min(a.mode == 0 ? kPwMaxStages : 4, budget / a.stage_bytes);
     if (a.stages < 2) return false;
     a.off_stages = a_bytes;                                  // a multiple of 4096: the stages are 1024-byte aligned
-    a.off_out = a.off_stages + a.stages * a.stage_bytes;
-    a.off_tail = a.off_out + out_bytes;
+    a.off_raw = a.off_stages + a.stages * a.stage_bytes;     // 128-byte aligned (bulk copies want 16)
+    a.off_out = a.off_raw + a.raws * a.raw_bytes;
+    a.off_tail = (a.off_out + out_bytes + 127) / 128 * 128;
     p.smem_bytes = (size_t)a.off_tail + kPwTail;
     p.w_bytes = (size_t)p.m_tiles * a_bytes;
     return true;
