@@ -9,7 +9,7 @@ Headline workload (default): the reference's example CNN in QLinear int8 form (Q
 2x[QLinearConv, ReLU, MaxPool] -> 2x QLinearMatMul -> DequantizeLinear) on seeded synthetic 1x28x28 inputs,
 batch 65536 per GPU (weak scaling) or 65536 in total split across the ranks (`--scaling strong`); a step is
 one pass of the plan over the batch.  Other workloads: small_cnn_fp32 (the same network in FP32), qconv3a..3d
-(the standalone QLinearConv sweep), qconv4a..4d (single MobileNetV2-style layers), mobilenetv2_int8, tinyyolo_int8,
+(the standalone QLinearConv sweep), qconv4a..4e (single MobileNetV2-style layers), mobilenetv2_int8, tinyyolo_int8,
 tinyyolo_fp32.
 
 Every workload prints ONE JSON line on rank 0 with
@@ -280,7 +280,7 @@ class TinyYolo(Workload):
 
 
 WORKLOADS = ["small_cnn_int8", "small_cnn_fp32", "qconv3a", "qconv3b", "qconv3c", "qconv3d", "qconv3a_nhwc", "qconv3c_nhwc",
-             "qconv4a", "qconv4b", "qconv4c", "qconv4d",      # single MobileNetV2-style layers (profiler captures)
+             "qconv4a", "qconv4b", "qconv4c", "qconv4d", "qconv4e",      # single MobileNetV2-style layers (profiler captures)
              "mobilenetv2_int8", "tinyyolo_int8", "tinyyolo_fp32"]
 
 

@@ -64,7 +64,8 @@ CASES = [
     (2, 16, 28, 28, 32, 3, 1, "relu_rescale", False, I8, "+ActivationLut"),                  # activation alone (table)
     (2, 64, 28, 28, 32, 1, 0, "leaky", True, I8, "tc-pointwise)+ActivationLut"),             # 1x1, 32 filters (four pixel groups on the lanes): table fused, pool stays a step
     (2, 64, 28, 28, 96, 1, 0, "leaky", True, I8, "tc-pointwise)+ActivationLut"),             # 1x1, 96 filters: the filters-on-lanes kernel with the table
-    (2, 3, 64, 64, 16, 3, 1, "leaky", True, I8, "small-c)+ActivationLut"),                   # stem kernel: table fused, pool separate
+    (2, 3, 64, 64, 16, 3, 1, "leaky", True, I8, "tc-stem)+ActivationLut"),                   # stem (patches in shared memory): table fused, pool separate
+    (2, 4, 64, 64, 16, 3, 1, "leaky", True, I8, "small-c)+ActivationLut"),                   # four channels: warp-level stem kernel
     (2, 16, 13, 13, 32, 3, 1, "leaky", False, I8, "+ActivationLut"),                         # im2col path (odd width)
     (1, 8, 9, 9, 8, 3, 1, "leaky", True, I8, "QLinearConv+ActivationLut"),                   # generic kernel
 ]

@@ -380,6 +380,38 @@ def test_qlinearconv_small_channel_count(ctx, oracle, case):
     assert len(np.unique(want)) > 16
 
 
+STEM_QCONV = [
+    # N C H W M stride pads xdt ydt xzp yzp per_channel bias act      (3x3 on at most three channels, rows of whole 16-byte units:
+    #                                                                  patches written in shared memory for the filters-on-lanes kernel)
+    (3, 3, 96, 96, 32, 2, (0, 0, 1, 1), U8, I8, 0, 0, True, True, "relu6"),        # pads below and right only; 48 x 48 output, one tile and a bit
+    (4, 3, 64, 96, 24, 2, (1, 1, 1, 1), U8, I8, 128, 0, True, True, "relu"),       # 24 filters in 32-lane groups; zero point 128 in the padding
+    (2, 3, 50, 64, 64, 1, (1, 1, 1, 1), I8, U8, -7, 9, True, True, None),          # 64 filters (two groups), signed input, general requantisation
+    (1, 1, 72, 128, 16, 1, (0, 1, 1, 1), I8, I8, 5, -2, False, False, "relu"),     # one channel, eight groups, no padding above
+    (8, 2, 52, 64, 8, 2, (1, 1, 0, 0), U8, U8, 17, 3, True, True, "relu6"),        # eight filters; 26 x 32 output: groups of 112 pixels, the last ragged
+    (1, 3, 224, 224, 32, 2, (1, 1, 1, 1), U8, I8, 0, 0, True, True, "relu6"),      # the MobileNet stem itself: 13 tiles, the last partly empty
+    (1, 3, 64, 416, 16, 1, (1, 1, 1, 1), U8, I8, 0, 0, True, True, None),          # detector rows: a tile spans five output rows
+]
+
+
+@pytest.mark.parametrize("case", STEM_QCONV, ids=[f"stem{i}" for i in range(len(STEM_QCONV))])
+def test_qlinearconv_stem_patches(ctx, oracle, case):
+    N, C, H, W, M, s, pads, xdt, ydt, xzp, yzp, per_ch, has_bias, act = case
+    rng = np.random.default_rng(N * 43 + C + M + W)
+    x = q(rng, (N, C, H, W), xdt)
+    w = rng.integers(-127, 128, (M, C, 3, 3), dtype=np.int8)
+    ws = (rng.random(M if per_ch else 1, dtype=np.float32) * 0.02 + 0.001).astype(np.float32)
+    bias = rng.integers(-3000, 3000, M).astype(np.int32) if has_bias else None
+    y_scale = 0.03 * np.sqrt(C * 9)
+    kw = dict(bias=bias, y_dtype=ydt, stride=(s, s), pads=pads, dilations=(1, 1), group=1, activation=act)
+    before = ctx.launch_count()
+    got = ctx.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
+    launches = ctx.launch_count() - before
+    want = oracle.qlinearconv(x, 0.02, xzp, w, ws, None, y_scale, yzp, **kw)
+    assert got.shape == want.shape and np.array_equal(got, want)
+    assert launches == 1
+    assert len(np.unique(want)) > 16
+
+
 @pytest.mark.parametrize("case,launches", list(zip(TC_QCONV, TC_QCONV_LAUNCHES)), ids=[f"tcqconv{i}" for i in range(len(TC_QCONV))])
 def test_qlinearconv_tensor_core_path(ctx, oracle, case, launches):
     N, C, H, W, M, k, stride, pads, dil, xdt, ydt, xzp, yzp, per_ch, has_bias, act = case

@@ -767,22 +767,11 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
     bool wz_zero = true;
     for (int32_t v : wz) wz_zero = wz_zero && v == 0;
     const bool host_consts = !is_device_ptr(w) && !(bias && is_device_ptr(bias));
-    if (host_consts && qconv_smallc_eligible(g, wz_zero) && (!is_device_ptr(x) || qconv_smallc_ptr_ok(x))) {
-        // 3x3 on at most four input channels (network stems): warp-level MMAs with the filters as rows
-        std::vector<uint32_t> wfrag; std::vector<int32_t> bf;
-        qconv_smallc_prepare(g, w, bias, x_zp, wfrag, bf);
-        Stager s(ctx);
-        const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
-        const int iw = s.in(wfrag.data(), wfrag.size() * 4), im = s.in(mult.data(), mult.size() * 4), ib = s.in(bf.data(), bf.size() * 4);
-        ZB_TRY(s.commit());
-        ZB_TRY(run_qconv_smallc(ctx, g, s.ptr<char>(ix), x_dtype == ZANT_U8, x_zp, s.ptr<uint32_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
-                                s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, tc_conv_max_product(mult, bf, (long long)g.C * 9)));
-        return s.finish();
-    }
     PwConvPlan pwp;
     if (host_consts && (!is_device_ptr(x) || pw_conv_ptr_ok(x, nullptr)) && (!is_device_ptr(y) || pw_conv_ptr_ok(nullptr, y)) &&
-        pw_conv_plan(g, wz_zero, ctx->sm_count, pwp)) {
-        // 1x1: filters on the accumulator lanes, activations straight from NCHW as the MN-major operand
+        (pw_stem_plan(g, wz_zero, x_zp, ctx->sm_count, pwp) || pw_conv_plan(g, wz_zero, ctx->sm_count, pwp))) {
+        // 1x1: filters on the accumulator lanes, activations straight from NCHW as the MN-major operand; 3x3 stems: the same
+        // kernel on patches written in shared memory
         std::vector<int8_t> w_blk; std::vector<int32_t> bf;
         pw_conv_prepare(pwp, w, bias, x_zp, w_blk, bf);
         bool finite = true;
@@ -796,6 +785,18 @@ int32_t zant_b200_qlinearconv(zant_ctx* ctx, int32_t x_dtype, const void* x, con
         ZB_TRY(s.commit());
         ZB_TRY(pw_conv_run(ctx, pwp, s.ptr<char>(ix), x_dtype == ZANT_U8, s.ptr<int8_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
                            s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, finite, capped ? s.ptr<int32_t>(ic) : nullptr));
+        return s.finish();
+    }
+    if (host_consts && qconv_smallc_eligible(g, wz_zero) && (!is_device_ptr(x) || qconv_smallc_ptr_ok(x))) {
+        // 3x3 on at most four input channels (network stems): warp-level MMAs with the filters as rows
+        std::vector<uint32_t> wfrag; std::vector<int32_t> bf;
+        qconv_smallc_prepare(g, w, bias, x_zp, wfrag, bf);
+        Stager s(ctx);
+        const int ix = s.in(x, numel(x_shape, 4)), iy = s.out(y, numel(y_shape, 4));
+        const int iw = s.in(wfrag.data(), wfrag.size() * 4), im = s.in(mult.data(), mult.size() * 4), ib = s.in(bf.data(), bf.size() * 4);
+        ZB_TRY(s.commit());
+        ZB_TRY(run_qconv_smallc(ctx, g, s.ptr<char>(ix), x_dtype == ZANT_U8, x_zp, s.ptr<uint32_t>(iw), s.ptr<float>(im), s.ptr<int32_t>(ib),
+                                s.ptr<char>(iy), y_dtype == ZANT_U8, Requant{y_scale, y_zp, activation}, tc_conv_max_product(mult, bf, (long long)g.C * 9)));
         return s.finish();
     }
     TcConvPlan tcp;

@@ -552,6 +552,26 @@ static int32_t build_qconv(zant_plan* pl, const PlanNode& n, QConvFusion& fz) {
         });
         return ZANT_OK;
     }
+    PwConvPlan pwp;
+    const bool stem = const_bias && pw_stem_plan(g, wz_zero, xzp, ctx->sm_count, pwp);
+    if (stem || (const_bias && pw_conv_plan(g, wz_zero, ctx->sm_count, pwp))) {
+        // 1x1: filters on the accumulator lanes, activations straight from NCHW as the MN-major operand; 3x3 stems: the same
+        // kernel on patches written in shared memory
+        std::vector<int8_t> w_blk; std::vector<int32_t> bf;
+        pw_conv_prepare(pwp, (const int8_t*)T(w).host.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, w_blk, bf);
+        bool finite = true;
+        for (float f : mult) finite = finite && std::isfinite(f);
+        const int aw = pl->add_aux(w_blk.data(), w_blk.size()), am = pl->add_aux(mult.data(), mult.size() * 4), ab = pl->add_aux(bf.data(), bf.size() * 4);
+        std::vector<int32_t> caps;
+        const bool capped = finite && yd == ZANT_I8 && rq0.y_zp == 0 && requant_relu_caps(mult.data(), mult.size(), rq0.act, lean_six(rq0.y_scale), caps);
+        const int ac = capped ? pl->add_aux(caps.data(), caps.size() * 4) : -1;
+        push(std::string(stem ? "QLinearConv(tc-stem)" : "QLinearConv(tc-pointwise)") + tail, [=]() {
+            if (!pw_conv_ptr_ok(pl->ptr(x), pl->ptr(y))) return fail(ZANT_E_INVALID_INPUT, "pointwise QLinearConv buffers must be 16-byte (input) and 32-byte (output) aligned");
+            return pw_conv_run(ctx, pwp, pl->ptr(x), xd == ZANT_U8, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
+                               (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), finite, ac >= 0 ? (const int32_t*)pl->aux(ac) : nullptr);
+        });
+        return ZANT_OK;
+    }
     if (const_bias && qconv_smallc_eligible(g, wz_zero)) {
         // 3x3 on at most four input channels (network stems); arena tensors are 256-byte aligned
         std::vector<uint32_t> wfrag; std::vector<int32_t> bf;
@@ -562,24 +582,6 @@ static int32_t build_qconv(zant_plan* pl, const PlanNode& n, QConvFusion& fz) {
             if (!qconv_smallc_ptr_ok(pl->ptr(x))) return fail(ZANT_E_INVALID_INPUT, "QLinearConv input buffer must be 4-byte aligned");
             return run_qconv_smallc(ctx, g, pl->ptr(x), xd == ZANT_U8, xzp, (const uint32_t*)pl->aux(aw), (const float*)pl->aux(am),
                                     (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), max_product);
-        });
-        return ZANT_OK;
-    }
-    PwConvPlan pwp;
-    if (const_bias && pw_conv_plan(g, wz_zero, ctx->sm_count, pwp)) {
-        // 1x1: filters on the accumulator lanes, activations straight from NCHW as the MN-major operand
-        std::vector<int8_t> w_blk; std::vector<int32_t> bf;
-        pw_conv_prepare(pwp, (const int8_t*)T(w).host.data(), b >= 0 ? (const int32_t*)T(b).host.data() : nullptr, xzp, w_blk, bf);
-        bool finite = true;
-        for (float f : mult) finite = finite && std::isfinite(f);
-        const int aw = pl->add_aux(w_blk.data(), w_blk.size()), am = pl->add_aux(mult.data(), mult.size() * 4), ab = pl->add_aux(bf.data(), bf.size() * 4);
-        std::vector<int32_t> caps;
-        const bool capped = finite && yd == ZANT_I8 && rq0.y_zp == 0 && requant_relu_caps(mult.data(), mult.size(), rq0.act, lean_six(rq0.y_scale), caps);
-        const int ac = capped ? pl->add_aux(caps.data(), caps.size() * 4) : -1;
-        push("QLinearConv(tc-pointwise)" + tail, [=]() {
-            if (!pw_conv_ptr_ok(pl->ptr(x), pl->ptr(y))) return fail(ZANT_E_INVALID_INPUT, "pointwise QLinearConv buffers must be 16-byte (input) and 32-byte (output) aligned");
-            return pw_conv_run(ctx, pwp, pl->ptr(x), xd == ZANT_U8, (const int8_t*)pl->aux(aw), (const float*)pl->aux(am),
-                               (const int32_t*)pl->aux(ab), pl->ptr(y), yd == ZANT_U8, rq_of(), finite, ac >= 0 ? (const int32_t*)pl->aux(ac) : nullptr);
         });
         return ZANT_OK;
     }

@@ -26,6 +26,13 @@
 // for g == g' and zero elsewhere, K is G times as deep, and K iteration (g', channel chunk) loads the TMA box of group g''s
 // pixels.  The zero blocks cost MMA time, of which there is plenty; every lane of the epilogue has work.
 //
+// 3x3 stems (mode 2; at most three input channels, stride 1 or 2, at most 64 filters): K = 9 * cin <= 27 is one K step, the filters
+// run as pixel groups on the lanes, and the B operand of a group - row k = (channel, kh, kw), column = output pixel - is written
+// by the copier warps: the loader brings the input rows of a tile's output rows into a raw buffer (one bulk copy per channel),
+// a copier thread cuts four output pixels' bytes of the three taps of a filter row out of three aligned words (funnel shifts;
+// stride 2: every second byte by byte permutes), replaces what lies outside the image by the input zero point and stores the
+// words at their swizzled places.  That is an im2col matrix which only ever exists in shared memory, 27 bytes per output pixel for all filters.
+//
 // Warp roles (704 threads, one persistent CTA per SM):
 //   warp 0  TMA loader     warp 1  TMEM owner + MMA issuer     warps 2-17  epilogue     warps 18-21  copiers (no tensor map)
 #pragma once
@@ -57,11 +64,17 @@ struct PwConvArgs {
     int m_pad;            // lanes per group: 16, 32 or 64 filters (128 when G == 1)
     int a_steps;          // K steps of the resident A operand: k_steps, or G * (K iterations per group) * KS for the block-diagonal form
     int cpm;              // CTAs per filter tile
-    int mode;             // 0: tensor map; 1: word copies in, staged tile out (HW % 4 == 0, at most 256 pixels: one tile per image)
+    int mode;             // 0: tensor map; 1: bulk copies + re-layout in, staged tile out (HW % 4 == 0, at most 256 pixels: one tile per image);
+                          // 2: 3x3 stem, the B operand is built from input rows (see PwConvArgs::cin)
     int bulk_out;         // mode 1: the staged tile leaves as one bulk copy (its address and size are multiples of 16)
     int wide_store;       // mode 0: every 32-pixel chunk starts at a 32-byte boundary (HW and n_px are multiples of 32)
     int stages, stage_bytes, off_stages, off_out, off_tail;
-    int raws, raw_bytes, off_raw;   // mode 1: ring of raw buffers that bulk copies fill with a stage's channel rows as they lie in memory
+    int raws, raw_bytes, off_raw;   // modes 1, 2: ring of raw buffers that bulk copies fill with input rows as they lie in memory
+    // mode 2 (3x3 stems: at most three input channels, stride 1 or 2): geometry of the convolution whose patches the builder
+    // warps write as the B operand (K = 9 * cin, zero-padded to 32); HW above is the OUTPUT plane OH * OW
+    int cin, ih, iw, oh, ow, cs, pt, pl, band;   // input channels, input H and W, output H and W, stride, pads, input rows per raw buffer and channel
+    uint32_t pad_word;
+    uint32_t ow_magic;    // mode 2: floor(2^32 / ow) + 1; umulhi(p, ow_magic) == p / ow for every pixel index of the plane
     float y_scale; int y_zp; int act; int out_u8; int six;
     const int32_t* cap;   // lean epilogue, act_mode 1: per-filter accumulator bound of the activation (requant_relu_caps)
     int act_mode;         // lean epilogue: 0 no activation, 1 clamp of the accumulator to [0, cap], 2 clamp of the packed codes
@@ -86,6 +99,130 @@ __device__ __forceinline__ void bulk_s2g(void* dst_gmem, uint32_t src_smem, uint
 }
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Barrier slots of the kernel below, in 8-byte units from the start of its tail.
+__device__ __forceinline__ uint32_t pw_bar_full(uint32_t bar0, int s) { return bar0 + 8u * s; }
+__device__ __forceinline__ uint32_t pw_bar_empty(uint32_t bar0, int s) { return bar0 + 8u * (kPwMaxStages + s); }
+__device__ __forceinline__ uint32_t pw_bar_raw_full(uint32_t bar0, int r) { return bar0 + 8u * (2 * kPwMaxStages + 5 + r); }
+__device__ __forceinline__ uint32_t pw_bar_raw_empty(uint32_t bar0, int r) { return bar0 + 8u * (2 * kPwMaxStages + 9 + r); }
+
+// Shared-memory accesses by 32-bit address (and immediate offset), in program order.
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_u128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts_u128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+// Stem (mode 2), one of the four builder warps: the B operand of every fourth pixel group of this CTA's tiles (in the order
+// the MMA issuer consumes them), from the tiles' raw input rows.  Eight stages, two per warp: warp w builds the groups
+// w, w + 4, ... into the stages w, w + 4, w, ..., so four groups are under construction at a time, a warp does not wait for
+// the MMA that reads its previous group, and nothing but the mbarriers orders the warps.
+// A lane owns a 16-byte chunk of the stage's rows - 16 output pixels of one output row (ow % 16 == 0) - and every second
+// (channel, filter row) pair: the 16 * CS + 2 input bytes of the pair's window are read once (one or two 16-byte words and
+// the word on either side) and give the chunk in the rows of the three taps kw = 0, 1, 2, each stored as one 16-byte word.
+// CS: stride; PL: left padding.  The window of tap kw = 0 starts PL bytes in front of a 16-byte boundary.
+template <int CS, int PL>
+__device__ __forceinline__ void pw_stem_builder(const PwConvArgs& a, uint32_t smem0, uint32_t bar0, int cw, int lane, int j0, int tiles, int tile_px,
+                                                volatile int* abort_flag) {
+    constexpr int NX = 4 * CS;                                          // aligned words of the window; X[0] and X[NX + 1] are the neighbours
+    const int nc = a.n_px >> 4;                                         // chunks per group
+    const int ci = lane & 15, qh = lane >> 4;
+    const int plane = a.band * a.iw;                                    // bytes of a channel in a raw buffer
+    const int Q = 3 * a.cin;                                            // (channel, filter row) pairs
+    const uint32_t pad = a.pad_word;
+    const uint32_t ci7 = (uint32_t)ci & 7u, blk = ((uint32_t)ci >> 3) * 4096u;    // chunk in its 128-pixel block, the block
+    uint32_t n_built = 0;                                               // groups this warp has built: stage cw + 4 * (n_built % 2)
+    int g = 0, tile_it = 0;                                             // groups and tiles of this CTA so far
+    for (int t = j0; t < tiles; t += a.cpm, ++tile_it) {
+        const int img = t / a.px_tiles, p0 = (t - img * a.px_tiles) * tile_px;
+        const int ih_lo = (int)__umulhi((uint32_t)p0, a.ow_magic) * CS - a.pt;
+        const int r = tile_it % a.raws;
+        const uint32_t rph = (uint32_t)(tile_it / a.raws) & 1u;
+        // +16: the word in front of the first row is read
+        const uint32_t raw = smem0 + (uint32_t)(a.off_raw + r * a.raw_bytes + 16);
+#pragma unroll 1
+        for (int pg = 0; pg < a.G; ++pg, ++g) {
+            if ((g & 3) != cw) continue;
+            const int st = cw + 4 * (int)(n_built & 1u);                // the ring has eight stages: group g lives in stage g % 8
+            int ok = 1;
+            if (lane == 0)
+                ok = (ptx::mbar_wait_sleeping(pw_bar_raw_full(bar0, r), rph, abort_flag) &&
+                      ptx::mbar_wait_sleeping(pw_bar_empty(bar0, st), ((n_built >> 1) & 1u) ^ 1u, abort_flag)) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) return;
+            ++n_built;
+            const uint32_t dst = smem0 + (uint32_t)(a.off_stages + st * a.stage_bytes) + blk;
+            const int p = p0 + pg * a.n_px + 16 * ci;                   // first of the chunk's 16 output pixels
+            const int oy = (int)__umulhi((uint32_t)p, a.ow_magic), ox = p - oy * a.ow;
+            const bool act = ci < nc && p < a.HW;                       // (columns past the plane: never stored by the epilogue)
+            const int row0 = oy * CS - a.pt;                            // input row of kh = 0
+            const uint32_t base = raw + (uint32_t)((row0 - ih_lo) * a.iw + ox * CS);
+            const bool left = PL && ox == 0;                            // the first pixel of tap kw = 0 lies left of the image
+            const int room = a.iw - 15 * CS - (ox * CS - PL);           // taps kw >= room: the last pixel lies right of it
+#pragma unroll 1
+            for (int q = qh; q < Q; q += 2) {
+                const int c = q / 3, kh = q - 3 * c;
+                // rows above and below the image: the zero point
+                const bool ld = act && (unsigned)(row0 + kh) < (unsigned)a.ih;
+                const uint32_t ad = ld ? base + (uint32_t)(c * plane + kh * a.iw) : raw + 16u;
+                uint32_t X[NX + 2];
+                {
+                    X[0] = lds_u32<0>(ad - 4u);
+                    const uint4 A = lds_u128(ad);
+                    X[1] = A.x; X[2] = A.y; X[3] = A.z; X[4] = A.w;
+                    if (CS == 2) {
+                        const uint4 B = lds_u128(ad + 16u);
+                        X[5] = B.x; X[6] = B.y; X[7] = B.z; X[8] = B.w;
+                    }
+                    X[NX + 1] = lds_u32<4 * NX>(ad);
+                }
+                if (!ld) {
+#pragma unroll
+                    for (int i = 0; i < NX + 2; ++i) X[i] = pad;
+                }
+                // word j (four output pixels) of tap kw starts at byte 4 * CS * j + kw - PL of the window; X[1] holds byte 0
+                uint32_t v[3][4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (CS == 1) {
+                        v[0][j] = PL ? __funnelshift_r(X[j], X[j + 1], 24) : X[j + 1];
+                        v[1][j] = PL ? X[j + 1] : __funnelshift_r(X[j + 1], X[j + 2], 8);
+                        v[2][j] = PL ? __funnelshift_r(X[j + 1], X[j + 2], 8) : __funnelshift_r(X[j + 1], X[j + 2], 16);
+                    } else if (PL) {
+                        // bytes 8j - 1, + 1, + 3, + 5;  8j, + 2, + 4, + 6;  8j + 1, + 3, + 5, + 7
+                        v[0][j] = __byte_perm(__byte_perm(X[2 * j], X[2 * j + 1], 0x0753), X[2 * j + 2], 0x5210);
+                        v[1][j] = __byte_perm(X[2 * j + 1], X[2 * j + 2], 0x6420);
+                        v[2][j] = __byte_perm(X[2 * j + 1], X[2 * j + 2], 0x7531);
+                    } else {
+                        // bytes 8j, + 2, + 4, + 6;  8j + 1, + 3, + 5, + 7;  8j + 2, + 4, + 6, + 8
+                        v[0][j] = __byte_perm(X[2 * j + 1], X[2 * j + 2], 0x6420);
+                        v[1][j] = __byte_perm(X[2 * j + 1], X[2 * j + 2], 0x7531);
+                        v[2][j] = __byte_perm(__byte_perm(X[2 * j + 1], X[2 * j + 2], 0x0642), X[2 * j + 3], 0x4210);
+                    }
+                }
+                if (left) v[0][0] = (v[0][0] & 0xffffff00u) | (pad & 0xffu);
+#pragma unroll
+                for (int kw = 0; kw < 3; ++kw) {
+                    if (kw >= room) v[kw][3] = (v[kw][3] & 0x00ffffffu) | (pad & 0xff000000u);
+                    const uint32_t k = 3u * (uint32_t)q + (uint32_t)kw;
+                    if (act) sts_u128(dst + k * 128u + ((ci7 ^ (k & 7u)) << 4), v[kw][0], v[kw][1], v[kw][2], v[kw][3]);
+                }
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) { ptx::mbar_arrive(pw_bar_full(bar0, st)); ptx::mbar_arrive(pw_bar_raw_empty(bar0, r)); }
+        }
+    }
+}
 
 template <bool XU8, bool LEAN>
 __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_constant__ PwConvArgs a, const __grid_constant__ CUtensorMap x_map) {
@@ -124,7 +261,8 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
         for (int s = 0; s < S; ++s) { ptx::mbar_init(full(s), 1); ptx::mbar_init(empty(s), 1); }
         for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull(b), 1); ptx::mbar_init(tempty(b), 4 * live_q); }
         ptx::mbar_init(wfull, 1);
-        for (int r = 0; r < a.raws; ++r) { ptx::mbar_init(raw_full(r), 1); ptx::mbar_init(raw_empty(r), 1); }
+        // (stem: every pixel group's builder warp releases the tile's raw buffer)
+        for (int r = 0; r < a.raws; ++r) { ptx::mbar_init(raw_full(r), 1); ptx::mbar_init(raw_empty(r), a.mode == 2 ? a.G : 1); }
         *abort_flag = 0; *epi_ok = 1; *cp_ok = 1;
         ptx::mbar_fence_init();
     }
@@ -159,6 +297,23 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
                         if (++s == S) { s = 0; ph ^= 1u; }
                         if (++ki == k_iters) { ki = 0; ++pg; }
                     }
+                }
+            } else if (a.mode == 2) {
+                // stem: the input rows that the tile's output rows read, one bulk copy per channel, into the raw ring
+                int r = 0; uint32_t ph = 0;
+                bool alive = true;
+                for (int t = j0; t < tiles && alive; t += a.cpm) {
+                    const int img = t / a.px_tiles, p0 = (t - img * a.px_tiles) * tile_px;
+                    const int oh_a = p0 / a.ow, oh_b = min(a.oh - 1, (min(a.HW, p0 + tile_px) - 1) / a.ow);
+                    const int ih_lo = oh_a * a.cs - a.pt;                                   // first row of the band (may be -1)
+                    const int r0 = max(ih_lo, 0), r1 = min(a.ih, oh_b * a.cs - a.pt + 3);   // rows [r0, r1) exist
+                    if (!ptx::mbar_wait_sleeping(raw_empty(r), ph ^ 1u, abort_flag)) { alive = false; break; }
+                    const uint32_t bytes = (uint32_t)((r1 - r0) * a.iw);                    // a multiple of 16: iw is
+                    ptx::mbar_arrive_expect_tx(raw_full(r), bytes * (uint32_t)a.cin);
+                    for (int c = 0; c < a.cin; ++c)
+                        ptx::bulk_g2s(ptx::smem_u32(smem + a.off_raw + (size_t)r * a.raw_bytes + 16) + (uint32_t)((c * a.band + (r0 - ih_lo)) * a.iw),
+                                      a.x + (((size_t)img * a.cin + c) * a.ih + r0) * a.iw, bytes, raw_full(r));
+                    if (++r == a.raws) { r = 0; ph ^= 1u; }
                 }
             } else {
                 // no tensor map: the stage's channel rows [c_lo, c_lo + KC) of the image, one contiguous run, into the raw ring
@@ -217,7 +372,17 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
         // ------------------------------------------------------------------ copiers (no tensor map): a stage's channels, row by row,
         // into the form a swizzled TMA box has: one 128-byte row per channel and 128-pixel block, 16-byte chunk k of row r at
         // chunk position k ^ (r % 8).  Channels past C are skipped: their weights are zero and any finite byte serves.
-        if (a.mode != 0) {
+        if (a.mode == 2) {
+            const int cw = warp - 18;
+            const uint32_t smem0 = ptx::smem_u32(smem);
+            if (a.cs == 1) {
+                if (a.pl) pw_stem_builder<1, 1>(a, smem0, bar0, cw, lane, j0, tiles, tile_px, abort_flag);
+                else pw_stem_builder<1, 0>(a, smem0, bar0, cw, lane, j0, tiles, tile_px, abort_flag);
+            } else {
+                if (a.pl) pw_stem_builder<2, 1>(a, smem0, bar0, cw, lane, j0, tiles, tile_px, abort_flag);
+                else pw_stem_builder<2, 0>(a, smem0, bar0, cw, lane, j0, tiles, tile_px, abort_flag);
+            }
+        } else if (a.mode != 0) {
             const int cw = warp - 18, ct = tid - 18 * 32;
             int s = 0; uint32_t ph = 0;
             int r = 0; uint32_t rph = 0;
@@ -354,7 +519,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
                     for (int j4 = 0; j4 < 8; ++j4) pk[j4] = lut4_smem(sLut, pk[j4]);
                 }
                 const int c0 = ch * 32;
-                if (a.mode == 0) {
+                if (a.mode != 1) {
                     // HW, p0 and c0 are multiples of 16: the chunk's valid part is 16 or 32 bytes
                     if (live && c0 < n_valid) {
                         if (c0 + 32 <= n_valid) {
@@ -378,7 +543,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(tempty(b));
-            if (a.mode != 0) {
+            if (a.mode == 1) {
                 // the staged block [rows_here][HW] is the image's contiguous run of these filters' planes
                 ptx::fence_proxy_async_smem();
                 ptx::named_barrier_sync(1, n_epi);
@@ -392,7 +557,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
                 }
             }
         }
-        if (a.mode != 0 && a.bulk_out && leader) bulk_wait_all();
+        if (a.mode == 1 && a.bulk_out && leader) bulk_wait_all();
     }
 
     if (*abort_flag) {
@@ -472,6 +637,63 @@ inline bool pw_conv_plan(const ConvGeom& g, bool w_zp_all_zero, int sm_count, Pw
     a.off_tail = (a.off_out + out_bytes + 127) / 128 * 128;
     p.smem_bytes = (size_t)a.off_tail + kPwTail;
     p.w_bytes = (size_t)p.m_tiles * a_bytes;
+    return true;
+}
+
+// 3x3 stems (at most three input channels, stride 1 or 2, at most 64 filters) on the same kernel: the patches of the input are
+// written as the B operand in shared memory (mode 2).  False when the shape is not taken.  The weights ([M][cin][3][3]) go
+// through pw_conv_prepare as [M][9 * cin].
+inline bool pw_stem_plan(const ConvGeom& g, bool w_zp_all_zero, int x_zp, int sm_count, PwConvPlan& p) {
+    if (g.G != 1 || !w_zp_all_zero || g.C > 3 || g.C < 1 || g.KH != 3 || g.KW != 3 || g.dh != 1 || g.dw != 1) return false;
+    if (g.sh != g.sw || (g.sh != 1 && g.sh != 2)) return false;
+    if (g.pt > 1 || g.pl > 1 || g.pb > 1 || g.pr > 1 || g.pt < 0 || g.pl < 0) return false;
+    if (g.M > 64 || g.M < 1 || g.OH <= 0 || g.OW <= 0 || g.N <= 0) return false;
+    const long long hw = (long long)g.OH * g.OW;
+    // input rows are copied in bulk (16-byte units); the 16 output pixels of a stage chunk lie in one row
+    if (g.W % 16 != 0 || g.OW % 16 != 0 || hw % 16 != 0 || hw > (1 << 24) || (long long)g.H * g.W > (1 << 24)) return false;
+    // of a word's four input pixels only the first may lie left of the image and only the last right of it
+    if ((g.OW - 4) * g.sw + 2 - g.pl + 2 * g.sw >= g.W) return false;
+    PwConvArgs& a = p.a;
+    a = PwConvArgs{};
+    a.mode = 2;
+    a.N = g.N; a.C = 9 * g.C; a.M = g.M; a.HW = (int)hw;
+    a.cin = g.C; a.ih = g.H; a.iw = g.W; a.oh = g.OH; a.ow = g.OW; a.cs = g.sh; a.pt = g.pt; a.pl = g.pl;
+    a.pad_word = 0x01010101u * (uint32_t)(x_zp & 255);
+    // p / ow by one multiplication: exact while p * ow < 2^32, p < oh * ow
+    if (hw * g.OW >= (1LL << 32)) return false;
+    a.ow_magic = (uint32_t)((1ULL << 32) / (uint64_t)g.OW) + 1u;
+    a.k_steps = 1; a.KS = 1;
+    a.m_pad = g.M <= 16 ? 16 : (g.M <= 32 ? 32 : 64);
+    a.G = 128 / a.m_pad;
+    a.a_steps = a.G;
+    p.m_tiles = 1;
+    if (hw < (long long)a.G * 64 || (long long)g.N * hw < 4096) return false;
+    const long long tile_max = 256LL * a.G;
+    a.px_tiles = (int)((hw + tile_max - 1) / tile_max);
+    a.n_px = (int)(((hw + (long long)a.px_tiles * a.G - 1) / ((long long)a.px_tiles * a.G) + 15) / 16 * 16);
+    a.wide_store = (hw % 32 == 0 && a.n_px % 32 == 0) ? 1 : 0;
+    a.PB = a.n_px > 128 ? 2 : 1;
+    const long long tiles = (long long)g.N * a.px_tiles;
+    if (tiles > 0x7fffffffLL) return false;
+    a.cpm = (int)std::max<long long>(1, std::min<long long>(sm_count, tiles));
+    a.stage_bytes = a.PB * 4096;
+    const long long tile_px = (long long)a.G * a.n_px;
+    const long long rows_out = (tile_px + g.OW - 2) / g.OW + 1;             // output rows a tile can touch
+    a.band = (int)((rows_out - 1) * a.cs + 3);
+    const long long raw = 16 + (long long)a.cin * a.band * a.iw + 16;       // the words in front of the first and behind the last row are read
+    if (raw > 40000) return false;
+    a.raw_bytes = (int)((raw + 127) / 128 * 128);
+    a.raws = 3;                                                             // with two groups per tile the four builder warps work on two tiles
+
+    const int a_bytes = a.a_steps * 4096;
+    a.stages = 8;                                                           // builder warp w owns the stages w and w + 4
+    a.off_stages = a_bytes;
+    a.off_raw = a.off_stages + a.stages * a.stage_bytes;
+    a.off_out = a.off_raw + a.raws * a.raw_bytes;
+    a.off_tail = (a.off_out + 127) / 128 * 128;
+    p.smem_bytes = (size_t)a.off_tail + kPwTail;
+    if (p.smem_bytes > 232448) return false;
+    p.w_bytes = (size_t)a_bytes;
     return true;
 }
 

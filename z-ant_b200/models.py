@@ -167,6 +167,7 @@ QCONV_SWEEP = {
     "4b": dict(N=256, C=64, H=14, W=14, K=384, k=1, s=1, p=0, group=1, act="relu6", y_scale=0.1),     # 1x1 on 196-byte planes
     "4c": dict(N=128, C=384, H=14, W=14, K=384, k=3, s=1, p=1, group=384, act="relu6", y_scale=0.1),  # depthwise on 14 x 14
     "4d": dict(N=256, C=160, H=7, W=7, K=960, k=1, s=1, p=0, group=1, act="relu6", y_scale=0.1),      # 1x1 on 49-byte planes
+    "4e": dict(N=64, C=3, H=224, W=224, K=32, k=3, s=2, p=1, group=1, act="relu6", y_scale=0.1),      # the stem: 3x3, stride 2, three channels
 }
 
 
