@@ -396,19 +396,21 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
                     const uint8_t* raw = smem + a.off_raw + (size_t)r * a.raw_bytes;      // [row][HW] as in memory
                     const int c_lo = ki * KC;
                     {
-                        // a warp takes every fourth row; a lane the words lane and lane + 32 of a row (HW <= 256)
-                        const int wpr = a.HW >> 2;
-                        const bool w1 = lane + 32 < wpr, w0 = lane < wpr;
-                        const uint32_t px0 = (uint32_t)lane * 4u, px1 = px0 + 128u;
-                        const uint32_t o0 = ((px0 >> 4) << 4);                          // chunk position before the swizzle
-#pragma unroll 4
-                        for (int rr = cw; rr < KC; rr += 4) {
-                            if (c_lo + rr >= a.C) break;                                // rows past C: zero weights, any finite byte serves
-                            const uint32_t* src = reinterpret_cast<const uint32_t*>(raw + (size_t)rr * a.HW);
-                            uint8_t* drow = dst + rr * 128;
-                            const uint32_t x7 = ((uint32_t)rr & 7u) << 4;
-                            if (w0) *reinterpret_cast<uint32_t*>(drow + ((o0 ^ x7) | (px0 & 15u))) = src[lane];
-                            if (w1) *reinterpret_cast<uint32_t*>(drow + ((o0 ^ x7) | (px1 & 15u)) + blk_bytes) = src[lane + 32];
+                        // a warp takes two of every eight rows, a lane one 16-byte chunk (four words, the row's start is word
+                        // aligned only) of one of the two: four loads, one 16-byte store.  The last chunk of a row runs into the
+                        // next row: pixels past HW, which nothing stores.
+                        const int ci = lane & 15, nch = (a.HW + 15) >> 4;
+                        const uint32_t raw_s = ptx::smem_u32(raw) + (uint32_t)ci * 16u;
+                        const uint32_t dst_s = ptx::smem_u32(dst) + ((uint32_t)ci >> 3) * blk_bytes;
+                        const uint32_t ci7 = (uint32_t)ci & 7u;
+                        if (ci < nch) {
+#pragma unroll 2
+                            for (int rr = 2 * cw + (lane >> 4); rr < KC; rr += 8) {
+                                if (c_lo + rr >= a.C) break;                            // rows past C: zero weights, any finite byte serves
+                                const uint32_t src = raw_s + (uint32_t)(rr * a.HW);
+                                const uint32_t x0 = lds_u32<0>(src), x1 = lds_u32<4>(src), x2 = lds_u32<8>(src), x3 = lds_u32<12>(src);
+                                sts_u128(dst_s + (uint32_t)rr * 128u + ((ci7 ^ ((uint32_t)rr & 7u)) << 4), x0, x1, x2, x3);
+                            }
                         }
                     }
                     ptx::fence_proxy_async_smem();
