@@ -192,6 +192,11 @@ DW_QCONV = [
     (2, 12, 12, 20, 2, U8, U8, 5, 3, True, True, None),           # the same onto 6 x 10
     (4, 7, 9, 9, 1, I8, I8, 2, 0, True, True, "relu"),            # 81-byte planes: a word spans two planes (flat form)
     (3, 10, 6, 7, 1, U8, I8, 130, 0, True, False, None),          # 42-byte planes, uint8 input
+    (5, 52, 14, 14, 1, U8, U8, 128, 9, True, True, "relu6"),      # rows form: 16 batches of 16 planes and a tail of 4, general requantisation
+    (9, 30, 7, 7, 1, I8, I8, 3, 0, True, True, "relu"),           # rows form on 7 x 7: batches of 32 planes, a tail of 14
+    (4, 64, 7, 7, 1, U8, I8, 0, 0, False, True, "relu6"),         # rows form, whole batches only
+    (2, 40, 20, 14, 1, I8, I8, -6, 0, True, False, None),         # rows form, 20 rows of 14: 12 planes per batch
+    (32, 96, 14, 14, 1, I8, I8, 0, 0, True, True, "relu6"),       # rows form, more batches than CTAs: every CTA loops
 ]
 
 

@@ -20,7 +20,9 @@
 
 #include "context.cuh"
 #include "geometry.hpp"
+#include "fused_cnn.cuh"
 #include "kernels_q8.cuh"
+#include "ptx_sm100.cuh"
 
 namespace zb {
 
@@ -371,6 +373,148 @@ __global__ void __launch_bounds__(256) qdwconv3x3_s1w8_kernel(const QDwArgs p) {
     }
 }
 
+// Stride 1 on 14 x 14 and 7 x 7 planes (W is a template parameter), "rows" form.  A CTA takes batches of PB whole planes,
+// which are one run of bytes in NCHW: one bulk copy brings a batch into shared memory, one takes the results back, so every
+// global access is a full line however the rows lie.  A thread owns one output row of one plane: per filter row it reads the
+// W + 2 bytes col -1 .. col W of the input row as NA + 1 aligned shared-memory words, shifts them to the row's alignment,
+// puts the zero point in the two border bytes, and cuts the W three-byte windows out of the NA words (a window that starts
+// on a word needs no permute; the dp4a weight of the fourth byte is 0).  The W results are requantised four at a time and
+// stored to the output batch bytewise (two bytes at a time when the rows are 2-byte aligned).  Two input and two output
+// buffers: the next batch is in flight and the previous one is being written back while a batch is computed.
+// PB * H * W is a multiple of 16 (bulk copies), and a trailing batch of fewer planes is copied by the threads.
+struct QDwRowsArgs {
+    QDwArgs p;
+    int PB;                    // planes per batch
+    int batches;               // ceil(planes / PB)
+    int buf_bytes;             // PB * H * W
+    int* status;               // device status word: DEV_ERR_WAIT_TIMEOUT when a bounded wait gave up
+};
+
+template <bool XU8, bool LEAN, int W>
+__global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs a) {
+    constexpr int NA = (W + 2 + 3) / 4;                             // words that hold the bytes col -1 .. col W
+    extern __shared__ __align__(128) uint8_t dw_rows_smem[];
+    const QDwArgs& p = a.p;
+    const int P = p.H * W;
+    // [in 0][in 1][out 0][out 1][barriers]; an input buffer has 16 bytes in front (the word before the first row is read)
+    const int in_stride = (a.buf_bytes + 16 + 16 + 127) / 128 * 128, out_stride = (a.buf_bytes + 127) / 128 * 128;
+    uint8_t* s_in = dw_rows_smem;
+    uint8_t* s_out = dw_rows_smem + 2 * in_stride;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(dw_rows_smem + 2 * in_stride + 2 * out_stride);
+    __shared__ int abort_flag_s;
+    volatile int* abort_flag = &abort_flag_s;
+    const int t = threadIdx.x;
+    const int pl = t / p.H, r = t - pl * p.H;                       // plane of the batch, output row
+    const bool worker = pl < a.PB;
+    if (t == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bars[0]), 1); ptx::mbar_init(ptx::smem_u32(&bars[1]), 1);
+        abort_flag_s = 0;
+        ptx::mbar_fence_init();
+    }
+    __syncthreads();
+    auto planes_of = [&](int b) { return min(a.PB, p.planes - b * a.PB); };
+    auto issue_load = [&](int b, int buf) {
+        // whole batches by one bulk copy; a trailing partial batch is copied by the threads at its turn
+        if (planes_of(b) == a.PB) {
+            const uint32_t bar = ptx::smem_u32(&bars[buf]);
+            ptx::mbar_arrive_expect_tx(bar, (uint32_t)a.buf_bytes);
+            ptx::bulk_g2s(ptx::smem_u32(s_in + buf * in_stride + 16), p.x + (size_t)b * a.buf_bytes, (uint32_t)a.buf_bytes, bar);
+        }
+    };
+    const uint32_t hi4 = p.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(p.six & 255) : 0x7f7f7f7fu;
+    (void)hi4;
+    int it = 0;
+    if (t == 0 && (int)blockIdx.x < a.batches) issue_load((int)blockIdx.x, 0);
+    uint32_t phases = 0;                                            // bit b: phase of barrier b
+    for (int b = (int)blockIdx.x; b < a.batches; b += (int)gridDim.x, ++it) {
+        const int buf = it & 1;
+        const int nb = b + (int)gridDim.x;
+        if (t == 0) {
+            ptx::bulk_wait_read<1>();                               // the write-back that read s_out[buf] two batches ago
+            if (nb < a.batches) issue_load(nb, buf ^ 1);            // s_in[buf ^ 1] was last read before the barrier that ended the previous batch
+        }
+        const int n_pl = planes_of(b);
+        const bool whole = n_pl == a.PB;
+        uint8_t* in = s_in + buf * in_stride + 16;
+        uint8_t* out = s_out + buf * out_stride;
+        if (!whole) {
+            const uint8_t* src = p.x + (size_t)b * a.buf_bytes;
+            for (int i = t; i < n_pl * P; i += 256) in[i] = __ldg(src + i);
+        }
+        __syncthreads();
+        if (whole) {
+            if (!ptx::mbar_wait(ptx::smem_u32(&bars[0]) + 8u * (uint32_t)buf, (phases >> buf) & 1u, abort_flag)) break;
+            phases ^= 1u << buf;
+        }
+        if (worker && pl < n_pl) {
+            const int c = (int)(((long long)b * a.PB + pl) % p.C);
+            const float m = __ldg(p.mult + c);
+            const int bs = __ldg(p.bias + c);
+            const int cp = p.act_mode == 1 ? __ldg(p.cap + c) : 0x7fffffff;
+            int acc[4 * NA];
+#pragma unroll
+            for (int x = 0; x < 4 * NA; ++x) acc[x] = bs;
+#pragma unroll
+            for (int kr = 0; kr < 3; ++kr) {
+                const uint32_t wk = __ldg(p.wrow + c * 3 + kr);
+                const int iy = r + kr - 1;
+                uint32_t A[NA + 1];
+                if (iy >= 0 && iy < p.H) {
+                    const int sb = pl * P + iy * W - 1;              // byte of col -1 (may be -1: the 16 bytes in front)
+                    const uint32_t* wp = reinterpret_cast<const uint32_t*>(in + (sb & ~3));
+                    const uint32_t sh = 8u * (uint32_t)(sb & 3);
+                    uint32_t Wd[NA + 1];
+#pragma unroll
+                    for (int i = 0; i <= NA; ++i) Wd[i] = wp[i];
+#pragma unroll
+                    for (int i = 0; i < NA; ++i) A[i] = __funnelshift_r(Wd[i], Wd[i + 1], sh);
+                    // the zero point left of the first and right of the last column
+                    A[0] = (A[0] & 0xffffff00u) | (p.pad_word & 0xffu);
+                    constexpr int rb = W + 1;
+                    A[rb / 4] = (A[rb / 4] & ~(0xffu << (8 * (rb % 4)))) | (p.pad_word & (0xffu << (8 * (rb % 4))));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < NA; ++i) A[i] = p.pad_word;
+                }
+                A[NA] = 0;
+#pragma unroll
+                for (int x = 0; x < W; ++x) {
+                    const int j = x / 4, o = x % 4;
+                    const uint32_t win = o == 0 ? A[j] : __byte_perm(A[j], A[j + 1], o == 1 ? 0x4321 : (o == 2 ? 0x5432 : 0x6543));
+                    acc[x] = dw_dp4a<XU8>(win, wk, acc[x]);
+                }
+            }
+            // W results to out + pl * P + r * W, which has no alignment: single bytes (pairs when every row starts on an even byte)
+            uint8_t* dst = out + pl * P + r * W;
+#pragma unroll
+            for (int j = 0; j < (W + 3) / 4; ++j) {
+                const int a4[4] = {acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]};
+                const uint32_t pk = dw_requant4<LEAN, false>(a4, m, cp, p);
+                if (W % 2 == 0) {
+                    if (4 * j + 1 < W) *reinterpret_cast<uint16_t*>(dst + 4 * j) = (uint16_t)(pk & 0xffffu);
+                    if (4 * j + 3 < W) *reinterpret_cast<uint16_t*>(dst + 4 * j + 2) = (uint16_t)(pk >> 16);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (4 * j + k < W) dst[4 * j + k] = (uint8_t)(pk >> (8 * k));
+                }
+            }
+        }
+        if (whole) ptx::fence_proxy_async_smem();
+        __syncthreads();
+        if (whole) {
+            if (t == 0) ptx::bulk_s2g(p.y + (size_t)b * a.buf_bytes, ptx::smem_u32(out), (uint32_t)a.buf_bytes);
+        } else {
+            uint8_t* dstg = p.y + (size_t)b * a.buf_bytes;
+            for (int i = t; i < n_pl * P; i += 256) dstg[i] = out[i];
+        }
+    }
+    if (t == 0) {
+        ptx::bulk_wait_all();
+        if (*abort_flag) atomicExch(a.status, (int)DEV_ERR_WAIT_TIMEOUT);
+    }
+}
+
 // Stride 1 on planes whose rows are not whole words (14 x 14, 7 x 7, odd sizes), "flat" form.  The tensor is one run of
 // bytes and a thread owns one aligned 4-byte word of the OUTPUT: four consecutive flat positions, which may lie in two
 // rows or even two planes.  Output position f reads input bytes f - W - 1 .. f - W + 1, f - 1 .. f + 1 and
@@ -581,6 +725,36 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
         }
     }
     const bool aligned = g.W % 4 == 0 && g.OW % 4 == 0;
+    if (g.sh == 1 && (g.W == 14 || g.W == 7) && g.OW == g.W && g.OH == g.H && g.H <= 64 &&
+        ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0) {
+        // 14 x 14 and 7 x 7 planes: batches of whole planes through shared memory, a thread per output row
+        const int P = g.H * g.W;
+        int unit = 16;                                       // planes per 16-byte multiple: 16 / gcd(P, 16)
+        while (unit > 1 && (P * (unit / 2)) % 16 == 0) unit /= 2;
+        QDwRowsArgs ra{};
+        ra.p = a;
+        ra.PB = 256 / g.H / unit * unit;
+        if (ra.PB >= unit && a.planes >= 4 * ra.PB) {
+            ra.batches = (a.planes + ra.PB - 1) / ra.PB;
+            ra.buf_bytes = ra.PB * P;
+            ra.status = ctx->status_word;
+            const int in_stride = (ra.buf_bytes + 32 + 127) / 128 * 128, out_stride = (ra.buf_bytes + 127) / 128 * 128;
+            const size_t smem = (size_t)2 * in_stride + 2 * out_stride + 16;
+            const int rgrid = (int)std::min<long long>(ra.batches, (long long)ctx->sm_count * 6);
+            auto go = [&](auto kernel) -> int32_t {
+                kernel<<<rgrid, 256, smem, ctx->stream>>>(ra);
+                return check_launch(ctx, "qdwconv3x3_rows_kernel");
+            };
+            if (smem <= 48 * 1024) {
+                if (g.W == 14) {
+                    if (x_u8) return lean ? go(qdwconv3x3_rows_kernel<true, true, 14>) : go(qdwconv3x3_rows_kernel<true, false, 14>);
+                    return lean ? go(qdwconv3x3_rows_kernel<false, true, 14>) : go(qdwconv3x3_rows_kernel<false, false, 14>);
+                }
+                if (x_u8) return lean ? go(qdwconv3x3_rows_kernel<true, true, 7>) : go(qdwconv3x3_rows_kernel<true, false, 7>);
+                return lean ? go(qdwconv3x3_rows_kernel<false, true, 7>) : go(qdwconv3x3_rows_kernel<false, false, 7>);
+            }
+        }
+    }
     if (!aligned && g.sh == 1) {
         // rows that are not whole words, stride 1: the flat form, when its period fits a CTA
         const long long P = (long long)g.H * g.W, nb = (long long)a.planes * P;

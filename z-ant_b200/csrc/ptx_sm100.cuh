@@ -99,6 +99,17 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src_gmem
                  ::"r"(dst_smem), "l"(src_gmem), "r"(bytes), "r"(bar) : "memory");
 }
 
+// shared -> global, as a bulk group of the issuing thread; the group is committed here and waited for, later, by the same
+// thread: bulk_wait_read<N> until at most N of its groups still read their shared-memory source, bulk_wait_all until all
+// of them are complete.  Writes to the source by other threads need fence_proxy_async_smem and a barrier before the copy.
+__device__ __forceinline__ void bulk_s2g(void* dst_gmem, uint32_t src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(src_smem), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------- tiled TMA loads
 // Box of a tensor map -> this CTA's shared memory (128-byte aligned), completion counted in bytes
 // on an mbarrier.  The innermost coordinate times the element size must be a multiple of 16 bytes.

@@ -92,13 +92,9 @@ __device__ __forceinline__ void st_global_32B(uint8_t* p, const uint32_t (&v)[8]
                  ::"l"(p), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
 }
 
-// shared -> global bulk copy of this thread's bulk group; the group is committed and, later, waited for by the same thread
-__device__ __forceinline__ void bulk_s2g(void* dst_gmem, uint32_t src_smem, uint32_t bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(src_smem), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+using ptx::bulk_s2g;
+using ptx::bulk_wait_all;
+__device__ __forceinline__ void bulk_wait_read() { ptx::bulk_wait_read<0>(); }
 
 // Barrier slots of the kernel below, in 8-byte units from the start of its tail.
 __device__ __forceinline__ uint32_t pw_bar_full(uint32_t bar0, int s) { return bar0 + 8u * s; }
