@@ -379,8 +379,8 @@ __global__ void __launch_bounds__(256) qdwconv3x3_s1w8_kernel(const QDwArgs p) {
 // W + 2 bytes col -1 .. col W of the input row as NA + 1 aligned shared-memory words, shifts them to the row's alignment,
 // puts the zero point in the two border bytes, and cuts the W three-byte windows out of the NA words (a window that starts
 // on a word needs no permute; the dp4a weight of the fourth byte is 0).  The W results are requantised four at a time and
-// stored to the output batch bytewise (two bytes at a time when the rows are 2-byte aligned).  Two input and two output
-// buffers: the next batch is in flight and the previous one is being written back while a batch is computed.
+// stored to the output batch bytewise (two bytes at a time when the rows are 2-byte aligned).  Three input and two output
+// buffers: the next two batches are in flight and the previous one is being written back while a batch is computed.
 // PB * H * W is a multiple of 16 (bulk copies), and a trailing batch of fewer planes is copied by the threads.
 struct QDwRowsArgs {
     QDwArgs p;
@@ -396,18 +396,18 @@ __global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs 
     extern __shared__ __align__(128) uint8_t dw_rows_smem[];
     const QDwArgs& p = a.p;
     const int P = p.H * W;
-    // [in 0][in 1][out 0][out 1][barriers]; an input buffer has 16 bytes in front (the word before the first row is read)
+    // [in 0][in 1][in 2][out 0][out 1][barriers]; an input buffer has 16 bytes in front (the word before the first row is read)
     const int in_stride = (a.buf_bytes + 16 + 16 + 127) / 128 * 128, out_stride = (a.buf_bytes + 127) / 128 * 128;
     uint8_t* s_in = dw_rows_smem;
-    uint8_t* s_out = dw_rows_smem + 2 * in_stride;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(dw_rows_smem + 2 * in_stride + 2 * out_stride);
+    uint8_t* s_out = dw_rows_smem + 3 * in_stride;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(dw_rows_smem + 3 * in_stride + 2 * out_stride);
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
     const int t = threadIdx.x;
     const int pl = t / p.H, r = t - pl * p.H;                       // plane of the batch, output row
     const bool worker = pl < a.PB;
     if (t == 0) {
-        ptx::mbar_init(ptx::smem_u32(&bars[0]), 1); ptx::mbar_init(ptx::smem_u32(&bars[1]), 1);
+        for (int i = 0; i < 3; ++i) ptx::mbar_init(ptx::smem_u32(&bars[i]), 1);
         abort_flag_s = 0;
         ptx::mbar_fence_init();
     }
@@ -424,18 +424,22 @@ __global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs 
     const uint32_t hi4 = p.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(p.six & 255) : 0x7f7f7f7fu;
     (void)hi4;
     int it = 0;
-    if (t == 0 && (int)blockIdx.x < a.batches) issue_load((int)blockIdx.x, 0);
+    if (t == 0) {
+        if ((int)blockIdx.x < a.batches) issue_load((int)blockIdx.x, 0);
+        if ((int)(blockIdx.x + gridDim.x) < a.batches) issue_load((int)(blockIdx.x + gridDim.x), 1);
+    }
+    int ibuf = 0;                                                   // input buffer of this batch: it % 3
     uint32_t phases = 0;                                            // bit b: phase of barrier b
     for (int b = (int)blockIdx.x; b < a.batches; b += (int)gridDim.x, ++it) {
         const int buf = it & 1;
-        const int nb = b + (int)gridDim.x;
+        const int nb = b + 2 * (int)gridDim.x, nbuf = ibuf == 0 ? 2 : ibuf - 1;       // (it + 2) % 3
         if (t == 0) {
             ptx::bulk_wait_read<1>();                               // the write-back that read s_out[buf] two batches ago
-            if (nb < a.batches) issue_load(nb, buf ^ 1);            // s_in[buf ^ 1] was last read before the barrier that ended the previous batch
+            if (nb < a.batches) issue_load(nb, nbuf);               // that buffer was last read before the barrier that ended the previous batch
         }
         const int n_pl = planes_of(b);
         const bool whole = n_pl == a.PB;
-        uint8_t* in = s_in + buf * in_stride + 16;
+        uint8_t* in = s_in + ibuf * in_stride + 16;
         uint8_t* out = s_out + buf * out_stride;
         if (!whole) {
             const uint8_t* src = p.x + (size_t)b * a.buf_bytes;
@@ -443,8 +447,8 @@ __global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs 
         }
         __syncthreads();
         if (whole) {
-            if (!ptx::mbar_wait(ptx::smem_u32(&bars[0]) + 8u * (uint32_t)buf, (phases >> buf) & 1u, abort_flag)) break;
-            phases ^= 1u << buf;
+            if (!ptx::mbar_wait(ptx::smem_u32(&bars[0]) + 8u * (uint32_t)ibuf, (phases >> ibuf) & 1u, abort_flag)) break;
+            phases ^= 1u << ibuf;
         }
         if (worker && pl < n_pl) {
             const int c = (int)(((long long)b * a.PB + pl) % p.C);
@@ -508,6 +512,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs 
             uint8_t* dstg = p.y + (size_t)b * a.buf_bytes;
             for (int i = t; i < n_pl * P; i += 256) dstg[i] = out[i];
         }
+        ibuf = ibuf == 2 ? 0 : ibuf + 1;
     }
     if (t == 0) {
         ptx::bulk_wait_all();
@@ -739,8 +744,8 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
             ra.buf_bytes = ra.PB * P;
             ra.status = ctx->status_word;
             const int in_stride = (ra.buf_bytes + 32 + 127) / 128 * 128, out_stride = (ra.buf_bytes + 127) / 128 * 128;
-            const size_t smem = (size_t)2 * in_stride + 2 * out_stride + 16;
-            const int rgrid = (int)std::min<long long>(ra.batches, (long long)ctx->sm_count * 6);
+            const size_t smem = (size_t)3 * in_stride + 2 * out_stride + 32;
+            const int rgrid = (int)std::min<long long>(ra.batches, (long long)ctx->sm_count * 8);
             auto go = [&](auto kernel) -> int32_t {
                 kernel<<<rgrid, 256, smem, ctx->stream>>>(ra);
                 return check_launch(ctx, "qdwconv3x3_rows_kernel");
