@@ -429,16 +429,22 @@ __global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs 
         if ((int)(blockIdx.x + gridDim.x) < a.batches) issue_load((int)(blockIdx.x + gridDim.x), 1);
     }
     int ibuf = 0;                                                   // input buffer of this batch: it % 3
+    // channel of this thread's plane: (b * PB + pl) mod C, kept up to date by adding the grid's stride mod C
+    int c = (int)(((long long)blockIdx.x * a.PB + pl) % p.C);
+    const int c_step = (int)(((long long)gridDim.x * a.PB) % p.C);
     uint32_t phases = 0;                                            // bit b: phase of barrier b
     for (int b = (int)blockIdx.x; b < a.batches; b += (int)gridDim.x, ++it) {
         const int buf = it & 1;
         const int nb = b + 2 * (int)gridDim.x, nbuf = ibuf == 0 ? 2 : ibuf - 1;       // (it + 2) % 3
+        const int n_pl = planes_of(b);
+        const bool whole = n_pl == a.PB;
         if (t == 0) {
             ptx::bulk_wait_read<1>();                               // the write-back that read s_out[buf] two batches ago
             if (nb < a.batches) issue_load(nb, nbuf);               // that buffer was last read before the barrier that ended the previous batch
+            // one thread waits for this batch's bytes; the barrier below hands them to the others
+            if (whole && !ptx::mbar_wait(ptx::smem_u32(&bars[0]) + 8u * (uint32_t)ibuf, (phases >> ibuf) & 1u, abort_flag)) *abort_flag = 1;
         }
-        const int n_pl = planes_of(b);
-        const bool whole = n_pl == a.PB;
+        if (whole) phases ^= 1u << ibuf;
         uint8_t* in = s_in + ibuf * in_stride + 16;
         uint8_t* out = s_out + buf * out_stride;
         if (!whole) {
@@ -446,12 +452,8 @@ __global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs 
             for (int i = t; i < n_pl * P; i += 256) in[i] = __ldg(src + i);
         }
         __syncthreads();
-        if (whole) {
-            if (!ptx::mbar_wait(ptx::smem_u32(&bars[0]) + 8u * (uint32_t)ibuf, (phases >> ibuf) & 1u, abort_flag)) break;
-            phases ^= 1u << ibuf;
-        }
+        if (*abort_flag) break;
         if (worker && pl < n_pl) {
-            const int c = (int)(((long long)b * a.PB + pl) % p.C);
             const float m = __ldg(p.mult + c);
             const int bs = __ldg(p.bias + c);
             const int cp = p.act_mode == 1 ? __ldg(p.cap + c) : 0x7fffffff;
@@ -513,6 +515,7 @@ __global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs 
             for (int i = t; i < n_pl * P; i += 256) dstg[i] = out[i];
         }
         ibuf = ibuf == 2 ? 0 : ibuf + 1;
+        c += c_step; if (c >= p.C) c -= p.C;
     }
     if (t == 0) {
         ptx::bulk_wait_all();
