@@ -197,6 +197,11 @@ DW_QCONV = [
     (4, 64, 7, 7, 1, U8, I8, 0, 0, False, True, "relu6"),         # rows form, whole batches only
     (2, 40, 20, 14, 1, I8, I8, -6, 0, True, False, None),         # rows form, 20 rows of 14: 12 planes per batch
     (32, 96, 14, 14, 1, I8, I8, 0, 0, True, True, "relu6"),       # rows form, more batches than CTAs: every CTA loops
+    (6, 40, 14, 14, 2, I8, I8, 0, 0, True, True, "relu6"),        # rows form, stride 2 onto 7 x 7: batches of 32 planes and a tail of 16
+    (4, 48, 28, 28, 2, U8, I8, 0, 0, True, True, "relu6"),        # rows form, stride 2 onto 14 x 14: whole batches of 16 planes
+    (3, 30, 28, 28, 2, U8, U8, 131, 4, True, True, None),         # the same with zero points and a tail of 10 planes
+    (5, 32, 13, 14, 2, I8, I8, -3, 0, False, True, "relu"),       # 13 rows: the last output row reads the padding row below
+    (16, 144, 14, 14, 2, I8, I8, 0, 0, True, True, "relu6"),      # stride 2, every CTA loops
 ]
 
 

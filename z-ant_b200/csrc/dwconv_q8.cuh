@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <type_traits>
 #include <vector>
 
 #include "context.cuh"
@@ -373,38 +374,41 @@ __global__ void __launch_bounds__(256) qdwconv3x3_s1w8_kernel(const QDwArgs p) {
     }
 }
 
-// Stride 1 on 14 x 14 and 7 x 7 planes (W is a template parameter), "rows" form.  A CTA takes batches of PB whole planes,
+// Small planes, "rows" form: stride 1 on 14 x 14 and 7 x 7, stride 2 from 28 x 28 and 14 x 14 (W and the stride S are template
+// parameters; OW = W for stride 1, W / 2 for stride 2).  A CTA takes batches of PB whole planes,
 // which are one run of bytes in NCHW: one bulk copy brings a batch into shared memory, one takes the results back, so every
 // global access is a full line however the rows lie.  A thread owns one output row of one plane: per filter row it reads the
 // W + 2 bytes col -1 .. col W of the input row as NA + 1 aligned shared-memory words, shifts them to the row's alignment,
-// puts the zero point in the two border bytes, and cuts the W three-byte windows out of the NA words (a window that starts
-// on a word needs no permute; the dp4a weight of the fourth byte is 0).  The W results are requantised four at a time and
+// puts the zero point in the two border bytes, and cuts the OW three-byte windows (S bytes apart) out of the NA words (a window
+// that starts on a word needs no permute; the dp4a weight of the fourth byte is 0).  The OW results are requantised four at a time and
 // stored to the output batch bytewise (two bytes at a time when the rows are 2-byte aligned).  Three input and two output
 // buffers: the next two batches are in flight and the previous one is being written back while a batch is computed.
-// PB * H * W is a multiple of 16 (bulk copies), and a trailing batch of fewer planes is copied by the threads.
+// PB * H * W and PB * OH * OW are multiples of 16 (bulk copies), and a trailing batch of fewer planes is copied by the threads.
 struct QDwRowsArgs {
     QDwArgs p;
     int PB;                    // planes per batch
     int batches;               // ceil(planes / PB)
     int buf_bytes;             // PB * H * W
+    int out_bytes;             // PB * OH * OW
     int* status;               // device status word: DEV_ERR_WAIT_TIMEOUT when a bounded wait gave up
 };
 
-template <bool XU8, bool LEAN, int W>
+template <bool XU8, bool LEAN, int W, int S>
 __global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs a) {
     constexpr int NA = (W + 2 + 3) / 4;                             // words that hold the bytes col -1 .. col W
+    constexpr int OW = S == 1 ? W : W / 2;
     extern __shared__ __align__(128) uint8_t dw_rows_smem[];
     const QDwArgs& p = a.p;
-    const int P = p.H * W;
+    const int P = p.H * W, PO = p.OH * OW;
     // [in 0][in 1][in 2][out 0][out 1][barriers]; an input buffer has 16 bytes in front (the word before the first row is read)
-    const int in_stride = (a.buf_bytes + 16 + 16 + 127) / 128 * 128, out_stride = (a.buf_bytes + 127) / 128 * 128;
+    const int in_stride = (a.buf_bytes + 16 + 16 + 127) / 128 * 128, out_stride = (a.out_bytes + 127) / 128 * 128;
     uint8_t* s_in = dw_rows_smem;
     uint8_t* s_out = dw_rows_smem + 3 * in_stride;
     uint64_t* bars = reinterpret_cast<uint64_t*>(dw_rows_smem + 3 * in_stride + 2 * out_stride);
     __shared__ int abort_flag_s;
     volatile int* abort_flag = &abort_flag_s;
     const int t = threadIdx.x;
-    const int pl = t / p.H, r = t - pl * p.H;                       // plane of the batch, output row
+    const int pl = t / p.OH, r = t - pl * p.OH;                     // plane of the batch, output row
     const bool worker = pl < a.PB;
     if (t == 0) {
         for (int i = 0; i < 3; ++i) ptx::mbar_init(ptx::smem_u32(&bars[i]), 1);
@@ -457,13 +461,13 @@ __global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs 
             const float m = __ldg(p.mult + c);
             const int bs = __ldg(p.bias + c);
             const int cp = p.act_mode == 1 ? __ldg(p.cap + c) : 0x7fffffff;
-            int acc[4 * NA];
+            int acc[(OW + 3) / 4 * 4];
 #pragma unroll
-            for (int x = 0; x < 4 * NA; ++x) acc[x] = bs;
+            for (int x = 0; x < (OW + 3) / 4 * 4; ++x) acc[x] = bs;
 #pragma unroll
             for (int kr = 0; kr < 3; ++kr) {
                 const uint32_t wk = __ldg(p.wrow + c * 3 + kr);
-                const int iy = r + kr - 1;
+                const int iy = S * r + kr - 1;
                 uint32_t A[NA + 1];
                 if (iy >= 0 && iy < p.H) {
                     const int sb = pl * P + iy * W - 1;              // byte of col -1 (may be -1: the 16 bytes in front)
@@ -484,35 +488,35 @@ __global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs 
                 }
                 A[NA] = 0;
 #pragma unroll
-                for (int x = 0; x < W; ++x) {
-                    const int j = x / 4, o = x % 4;
+                for (int x = 0; x < OW; ++x) {
+                    const int j = (S * x) / 4, o = (S * x) % 4;
                     const uint32_t win = o == 0 ? A[j] : __byte_perm(A[j], A[j + 1], o == 1 ? 0x4321 : (o == 2 ? 0x5432 : 0x6543));
                     acc[x] = dw_dp4a<XU8>(win, wk, acc[x]);
                 }
             }
-            // W results to out + pl * P + r * W, which has no alignment: single bytes (pairs when every row starts on an even byte)
-            uint8_t* dst = out + pl * P + r * W;
+            // OW results to out + pl * PO + r * OW, which has no alignment: single bytes (pairs when every row starts on an even byte)
+            uint8_t* dst = out + pl * PO + r * OW;
 #pragma unroll
-            for (int j = 0; j < (W + 3) / 4; ++j) {
+            for (int j = 0; j < (OW + 3) / 4; ++j) {
                 const int a4[4] = {acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]};
                 const uint32_t pk = dw_requant4<LEAN, false>(a4, m, cp, p);
-                if (W % 2 == 0) {
-                    if (4 * j + 1 < W) *reinterpret_cast<uint16_t*>(dst + 4 * j) = (uint16_t)(pk & 0xffffu);
-                    if (4 * j + 3 < W) *reinterpret_cast<uint16_t*>(dst + 4 * j + 2) = (uint16_t)(pk >> 16);
+                if (OW % 2 == 0) {
+                    if (4 * j + 1 < OW) *reinterpret_cast<uint16_t*>(dst + 4 * j) = (uint16_t)(pk & 0xffffu);
+                    if (4 * j + 3 < OW) *reinterpret_cast<uint16_t*>(dst + 4 * j + 2) = (uint16_t)(pk >> 16);
                 } else {
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        if (4 * j + k < W) dst[4 * j + k] = (uint8_t)(pk >> (8 * k));
+                        if (4 * j + k < OW) dst[4 * j + k] = (uint8_t)(pk >> (8 * k));
                 }
             }
         }
         if (whole) ptx::fence_proxy_async_smem();
         __syncthreads();
         if (whole) {
-            if (t == 0) ptx::bulk_s2g(p.y + (size_t)b * a.buf_bytes, ptx::smem_u32(out), (uint32_t)a.buf_bytes);
+            if (t == 0) ptx::bulk_s2g(p.y + (size_t)b * a.out_bytes, ptx::smem_u32(out), (uint32_t)a.out_bytes);
         } else {
-            uint8_t* dstg = p.y + (size_t)b * a.buf_bytes;
-            for (int i = t; i < n_pl * P; i += 256) dstg[i] = out[i];
+            uint8_t* dstg = p.y + (size_t)b * a.out_bytes;
+            for (int i = t; i < n_pl * PO; i += 256) dstg[i] = out[i];
         }
         ibuf = ibuf == 2 ? 0 : ibuf + 1;
         c += c_step; if (c >= p.C) c -= p.C;
@@ -733,33 +737,37 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
         }
     }
     const bool aligned = g.W % 4 == 0 && g.OW % 4 == 0;
-    if (g.sh == 1 && (g.W == 14 || g.W == 7) && g.OW == g.W && g.OH == g.H && g.H <= 64 &&
-        ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0) {
-        // 14 x 14 and 7 x 7 planes: batches of whole planes through shared memory, a thread per output row
-        const int P = g.H * g.W;
-        int unit = 16;                                       // planes per 16-byte multiple: 16 / gcd(P, 16)
-        while (unit > 1 && (P * (unit / 2)) % 16 == 0) unit /= 2;
+    const bool rows_s1 = g.sh == 1 && (g.W == 14 || g.W == 7) && g.OW == g.W && g.OH == g.H;
+    const bool rows_s2 = g.sh == 2 && (g.W == 28 || g.W == 14) && g.OW == g.W / 2 && g.OH == (g.H + 1) / 2;
+    if ((rows_s1 || rows_s2) && g.OH <= 64 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0) {
+        // small planes: batches of whole planes through shared memory, a thread per output row
+        const int P = g.H * g.W, PO = g.OH * g.OW;
+        int unit = 16;                                       // planes per batch come in units that make both batch sizes multiples of 16 bytes
+        while (unit > 1 && (P * (unit / 2)) % 16 == 0 && (PO * (unit / 2)) % 16 == 0) unit /= 2;
         QDwRowsArgs ra{};
         ra.p = a;
-        ra.PB = 256 / g.H / unit * unit;
+        ra.PB = 256 / g.OH / unit * unit;
         if (ra.PB >= unit && a.planes >= 4 * ra.PB) {
             ra.batches = (a.planes + ra.PB - 1) / ra.PB;
             ra.buf_bytes = ra.PB * P;
+            ra.out_bytes = ra.PB * PO;
             ra.status = ctx->status_word;
-            const int in_stride = (ra.buf_bytes + 32 + 127) / 128 * 128, out_stride = (ra.buf_bytes + 127) / 128 * 128;
+            const int in_stride = (ra.buf_bytes + 32 + 127) / 128 * 128, out_stride = (ra.out_bytes + 127) / 128 * 128;
             const size_t smem = (size_t)3 * in_stride + 2 * out_stride + 32;
             const int rgrid = (int)std::min<long long>(ra.batches, (long long)ctx->sm_count * 8);
             auto go = [&](auto kernel) -> int32_t {
                 kernel<<<rgrid, 256, smem, ctx->stream>>>(ra);
                 return check_launch(ctx, "qdwconv3x3_rows_kernel");
             };
+            auto pick = [&](auto w_tag, auto s_tag) -> int32_t {
+                constexpr int KW = decltype(w_tag)::value, KS = decltype(s_tag)::value;
+                if (x_u8) return lean ? go(qdwconv3x3_rows_kernel<true, true, KW, KS>) : go(qdwconv3x3_rows_kernel<true, false, KW, KS>);
+                return lean ? go(qdwconv3x3_rows_kernel<false, true, KW, KS>) : go(qdwconv3x3_rows_kernel<false, false, KW, KS>);
+            };
             if (smem <= 48 * 1024) {
-                if (g.W == 14) {
-                    if (x_u8) return lean ? go(qdwconv3x3_rows_kernel<true, true, 14>) : go(qdwconv3x3_rows_kernel<true, false, 14>);
-                    return lean ? go(qdwconv3x3_rows_kernel<false, true, 14>) : go(qdwconv3x3_rows_kernel<false, false, 14>);
-                }
-                if (x_u8) return lean ? go(qdwconv3x3_rows_kernel<true, true, 7>) : go(qdwconv3x3_rows_kernel<true, false, 7>);
-                return lean ? go(qdwconv3x3_rows_kernel<false, true, 7>) : go(qdwconv3x3_rows_kernel<false, false, 7>);
+                using std::integral_constant;
+                if (rows_s1) return g.W == 14 ? pick(integral_constant<int, 14>{}, integral_constant<int, 1>{}) : pick(integral_constant<int, 7>{}, integral_constant<int, 1>{});
+                return g.W == 28 ? pick(integral_constant<int, 28>{}, integral_constant<int, 2>{}) : pick(integral_constant<int, 14>{}, integral_constant<int, 2>{});
             }
         }
     }
