@@ -737,7 +737,7 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
         }
     }
     const bool aligned = g.W % 4 == 0 && g.OW % 4 == 0;
-    const bool rows_s1 = g.sh == 1 && (g.W == 14 || g.W == 7) && g.OW == g.W && g.OH == g.H;
+    const bool rows_s1 = g.sh == 1 && (g.W == 28 || g.W == 14 || g.W == 7) && g.OW == g.W && g.OH == g.H;
     const bool rows_s2 = g.sh == 2 && (g.W == 28 || g.W == 14) && g.OW == g.W / 2 && g.OH == (g.H + 1) / 2;
     if ((rows_s1 || rows_s2) && g.OH <= 64 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15u) == 0) {
         // small planes: batches of whole planes through shared memory, a thread per output row
@@ -766,6 +766,7 @@ inline int32_t run_qdwconv(zant_ctx* ctx, const ConvGeom& g, const void* x, bool
             };
             if (smem <= 48 * 1024) {
                 using std::integral_constant;
+                if (rows_s1 && g.W == 28) return pick(integral_constant<int, 28>{}, integral_constant<int, 1>{});
                 if (rows_s1) return g.W == 14 ? pick(integral_constant<int, 14>{}, integral_constant<int, 1>{}) : pick(integral_constant<int, 7>{}, integral_constant<int, 1>{});
                 return g.W == 28 ? pick(integral_constant<int, 28>{}, integral_constant<int, 2>{}) : pick(integral_constant<int, 14>{}, integral_constant<int, 2>{});
             }
