@@ -69,6 +69,7 @@ struct PwConvArgs {
     int bulk_out;         // mode 1: the staged tile leaves as one bulk copy (its address and size are multiples of 16)
     int wide_store;       // mode 0: every 32-pixel chunk starts at a 32-byte boundary (HW and n_px are multiples of 32)
     int stages, stage_bytes, off_stages, off_out, off_tail;
+    int outs, out_stride;           // mode 1: staging buffers for the output tile (two when they fit: a tile is staged while the previous one is sent)
     int raws, raw_bytes, off_raw;   // modes 1, 2: ring of raw buffers that bulk copies fill with input rows as they lie in memory
     // mode 2 (3x3 stems: at most three input channels, stride 1 or 2): geometry of the convolution whose patches the builder
     // warps write as the B operand (K = 9 * cin, zero-padded to 32); HW above is the OUTPUT plane OH * OW
@@ -225,7 +226,7 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sA = smem;                                  // [k16][128 filters][16]
     uint8_t* sStages = smem + a.off_stages;
-    uint8_t* sOut = smem + a.off_out;
+    uint8_t* sOut0 = smem + a.off_out;
     uint8_t* tail = smem + a.off_tail;
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 256);
@@ -450,13 +451,14 @@ __global__ void __launch_bounds__(kPwThreads, 1) tc_pw_nchw_kernel(const __grid_
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
             } else {
-                // the previous tile's bulk copy must have read the staging buffer before anybody overwrites it
-                if (leader) { if (a.bulk_out) bulk_wait_read(); *epi_ok = ptx::mbar_wait_sleeping(tfull(b), bph, abort_flag) ? 1 : 0; }
+                // the bulk copy that last read this tile's staging buffer (the previous tile's, or with two buffers the one before) must be through
+                if (leader) { if (a.bulk_out) { if (a.outs == 2) ptx::bulk_wait_read<1>(); else ptx::bulk_wait_read<0>(); } *epi_ok = ptx::mbar_wait_sleeping(tfull(b), bph, abort_flag) ? 1 : 0; }
                 ptx::named_barrier_sync(1, n_epi);
                 if (!*epi_ok) break;
             }
             ptx::tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * 256);
+            uint8_t* sOut = sOut0 + ((a.outs == 2 && (tile_it & 1)) ? a.out_stride : 0);
             uint8_t* yrow = a.y + ((size_t)img * a.M + (size_t)m) * a.HW + p0;
             // 16 accumulators -> four packed words
             auto requant16 = [&](const uint32_t (&v)[16], uint32_t* pk) {
@@ -622,11 +624,14 @@ inline bool pw_conv_plan(const ConvGeom& g, bool w_zp_all_zero, int sm_count, Pw
     a.cpm = (int)std::max<long long>(1, std::min<long long>(sm_count / p.m_tiles, tiles));
     a.stage_bytes = a.PB * a.KS * 32 * 128;
     const int a_bytes = a.a_steps * 4096;
-    const int out_bytes = a.mode == 0 ? 0 : (int)((128 * hw + 1023) / 1024 * 1024);
+    a.out_stride = a.mode == 0 ? 0 : (int)((128 * hw + 1023) / 1024 * 1024);
     a.raw_bytes = a.mode == 0 ? 0 : (int)(((long long)a.KS * 32 * hw + 127) / 128 * 128);
     a.raws = a.mode == 0 ? 0 : 3;
-    int budget = 232448 - kPwTail - a_bytes - out_bytes - a.raws * a.raw_bytes;
+    a.outs = a.mode == 0 ? 0 : 2;
+    int budget = 232448 - kPwTail - a_bytes - a.outs * a.out_stride - a.raws * a.raw_bytes;
+    if (a.mode != 0 && budget < 4 * a.stage_bytes) { a.outs = 1; budget += a.out_stride; }
     if (a.mode != 0 && budget < 2 * a.stage_bytes) { a.raws = 2; budget += a.raw_bytes; }
+    const int out_bytes = a.outs * a.out_stride;
     a.stages = std::min(a.mode == 0 ? kPwMaxStages : 4, budget / a.stage_bytes);
     if (a.stages < 2) return false;
     a.off_stages = a_bytes;                                  // a multiple of 4096: the stages are 1024-byte aligned
