@@ -29,12 +29,14 @@
 // 3x3 stems (mode 2; at most three input channels, stride 1 or 2, at most 64 filters): K = 9 * cin <= 27 is one K step, the filters
 // run as pixel groups on the lanes, and the B operand of a group - row k = (channel, kh, kw), column = output pixel - is written
 // by the copier warps: the loader brings the input rows of a tile's output rows into a raw buffer (one bulk copy per channel),
-// a copier thread cuts four output pixels' bytes of the three taps of a filter row out of three aligned words (funnel shifts;
-// stride 2: every second byte by byte permutes), replaces what lies outside the image by the input zero point and stores the
-// words at their swizzled places.  That is an im2col matrix which only ever exists in shared memory, 27 bytes per output pixel for all filters.
+// a copier lane cuts the 16-byte chunks (16 output pixels) of the three taps of a filter row out of the 16 * stride + 2 input
+// bytes it read once (funnel shifts; stride 2: every second byte by byte permutes), replaces what lies outside the image by the
+// input zero point and stores the chunks at their swizzled places; each copier warp builds every fourth pixel group on its own
+// (pw_stem_builder).  That is an im2col matrix which only ever exists in shared memory, 27 bytes per output pixel for all filters.
 //
 // Warp roles (704 threads, one persistent CTA per SM):
-//   warp 0  TMA loader     warp 1  TMEM owner + MMA issuer     warps 2-17  epilogue     warps 18-21  copiers (no tensor map)
+//   warp 0  loader (TMA boxes or bulk copies)     warp 1  TMEM owner + MMA issuer     warps 2-17  epilogue
+//   warps 18-21  copiers (small planes: re-layout of the raw rows; stems: builders of the patch operand)
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
