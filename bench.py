@@ -632,7 +632,7 @@ def run_gpu_arm(args, rank, world, local):
         by_kind = {}
         for r in rows:
             by_kind[r["kernel"]] = by_kind.get(r["kernel"], 0.0) + r["ms"]
-        top_rows = rows if len(rows) <= 8 else sorted(rows, key=lambda r: -r["ms"])[:8]
+        top_rows = rows if (len(rows) <= 8 or args.all_steps) else sorted(rows, key=lambda r: -r["ms"])[:8]
         cpu = None
         if not args.skip_cpu and world == 1:
             cpu = cpu_reference_rate(wl, x_gpu=x_host.numpy(), y_gpu=y_host.numpy(), tf32_mode={"tf32": 1, "tf32x3": 2}.get(args.dtype, 0))
@@ -676,6 +676,7 @@ def main():
     ap.add_argument("--graph", action="store_true", help="replay the plan as one CUDA graph in the timed region")
     ap.add_argument("--no-fuse", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--all-steps", action="store_true", help="per_kernel lists every step of the plan in order (default: the eight longest)")
     ap.add_argument("--sustain-seconds", type=float, default=2.0, help="length of the sustained-rate loop (0 = skip)")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="chunks of the batch that the end-to-end path pipelines")
     args = ap.parse_args()
