@@ -425,8 +425,6 @@ __global__ void __launch_bounds__(256) qdwconv3x3_rows_kernel(const QDwRowsArgs 
             ptx::bulk_g2s(ptx::smem_u32(s_in + buf * in_stride + 16), p.x + (size_t)b * a.buf_bytes, (uint32_t)a.buf_bytes, bar);
         }
     };
-    const uint32_t hi4 = p.act == ZANT_QACT_RELU6 ? 0x01010101u * (uint32_t)(p.six & 255) : 0x7f7f7f7fu;
-    (void)hi4;
     int it = 0;
     if (t == 0) {
         if ((int)blockIdx.x < a.batches) issue_load((int)blockIdx.x, 0);
